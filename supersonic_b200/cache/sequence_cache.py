@@ -1,0 +1,248 @@
+"""The cache: a slot per live sequence, keys and values per cache entry in pages,
+fixed-size per-sequence state beside them.
+
+Layout.  Mixers state what they need (:class:`KvNeed`: kv heads, head size,
+window; :class:`StateNeed`: a number of float32 values).  Cache entries with the same need form a group
+with storage of its own: ``k`` and ``v`` of shape ``[entries, pages, kv_heads,
+PAGE_TOKENS, head_dim]`` and a page table ``[slots, pages_per_sequence]``.  A
+sequence's tokens ``64p .. 64p+63`` of one kv head are contiguous, so a decode
+block streams them and a bulk copy can fetch them.  A group with a window gives
+pages back as soon as every later query is past them.
+
+Per sequence the cache also keeps: its length (host), the state of its random
+generator (device), and for every :class:`StateNeed` entry a zeroed float32
+row (device).  The reference keeps ``kv_filled`` in ``LayerState`` and
+fixed-size conv/recurrent buffers for its other layer kind
+(crates/qwen35/src/state.rs:17-80, 314).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple, Union
+
+import torch
+
+from .allocators import CacheError, CacheFull, FreeList
+
+PAGE_SHIFT = 6
+PAGE_TOKENS = 1 << PAGE_SHIFT
+
+
+@dataclass(frozen=True)
+class KvNeed:
+    n_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None       # None: every earlier key stays
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    n_values: int                      # float32 values per sequence
+
+
+Need = Union[KvNeed, StateNeed]
+
+
+def pages_for(n_tokens: int) -> int:
+    return (n_tokens + PAGE_TOKENS - 1) >> PAGE_SHIFT
+
+
+class KvGroup:
+    """Storage and page bookkeeping of the cache entries that share one need."""
+
+    def __init__(self, need: KvNeed, entries: List[int], n_pages: int, max_slots: int,
+                 pages_per_seq: int, dtype: torch.dtype, device: torch.device):
+        self.need = need
+        self.entries = list(entries)
+        self.index_of = {e: i for i, e in enumerate(self.entries)}
+        self.n_pages = n_pages
+        self.pages_per_seq = pages_per_seq
+        self.pool = FreeList(n_pages, "page")
+        shape = (len(entries), n_pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim)
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        pin = device.type == "cuda"
+        self.table_host = torch.zeros((max_slots, pages_per_seq), dtype=torch.int32, pin_memory=pin)
+        self.table = torch.zeros((max_slots, pages_per_seq), dtype=torch.int32, device=device)
+        # per slot: page index within the sequence -> page id, only for pages now held
+        self.held: List[Dict[int, int]] = [dict() for _ in range(max_slots)]
+        self._dirty_lo, self._dirty_hi = max_slots, -1
+
+    def first_needed_page(self, length: int) -> int:
+        """First page a query at position >= ``length`` can still read."""
+        if self.need.window is None:
+            return 0
+        return max(0, length - self.need.window + 1) >> PAGE_SHIFT
+
+    def reserve(self, slot: int, length: int, new_length: int) -> None:
+        first = self.first_needed_page(length)
+        want = [p for p in range(first, pages_for(new_length)) if p not in self.held[slot]]
+        if not want:
+            return
+        if pages_for(new_length) > self.pages_per_seq:
+            raise CacheFull(f"{new_length} tokens exceed the {self.pages_per_seq * PAGE_TOKENS} "
+                            "a sequence may hold")
+        ids = self.pool.take_many(len(want))
+        for p, pid in zip(want, ids):
+            self.held[slot][p] = pid
+            self.table_host[slot, p] = pid
+        self._dirty_lo, self._dirty_hi = min(self._dirty_lo, slot), max(self._dirty_hi, slot)
+
+    def trim(self, slot: int, length: int) -> None:
+        """Give back pages that no later query reads (window groups only)."""
+        if self.need.window is None:
+            return
+        first = self.first_needed_page(length)
+        for p in [p for p in self.held[slot] if p < first]:
+            self.pool.give_back(self.held[slot].pop(p))
+
+    def release(self, slot: int) -> None:
+        for pid in self.held[slot].values():
+            self.pool.give_back(pid)
+        self.held[slot].clear()
+
+    def sync(self) -> None:
+        if self._dirty_hi >= self._dirty_lo:
+            lo, hi = self._dirty_lo, self._dirty_hi + 1
+            self.table[lo:hi].copy_(self.table_host[lo:hi], non_blocking=True)
+            self._dirty_lo, self._dirty_hi = self.table.shape[0], -1
+
+
+class SequenceCache:
+    """Slots, page groups and per-sequence state for one model.
+
+    ``needs`` maps a cache id (as named by the model's schedule) to what its mixer
+    needs.  ``max_tokens`` bounds the tokens all live sequences hold together
+    (each rounded up to whole pages); ``max_seq_tokens`` bounds one sequence.
+    """
+
+    def __init__(self, needs: Dict[int, Need], max_tokens: int, max_seq_tokens: int,
+                 dtype: torch.dtype, device, max_slots: Optional[int] = None):
+        device = torch.device(device)
+        if max_tokens <= 0 or max_seq_tokens <= 0:
+            raise CacheError("the cache needs room for at least one token")
+        self.device, self.dtype = device, dtype
+        self.n_pages = pages_for(max_tokens)
+        self.pages_per_seq = min(pages_for(max_seq_tokens), self.n_pages)
+        self.max_seq_tokens = self.pages_per_seq * PAGE_TOKENS
+        self.max_slots = max_slots if max_slots is not None else min(self.n_pages, 4096)
+        self.slots = FreeList(self.max_slots, "slot")
+        self._length = [0] * self.max_slots
+        # groups by need
+        by_need: Dict[KvNeed, List[int]] = {}
+        state_entries: List[Tuple[int, StateNeed]] = []
+        for cid, need in sorted(needs.items()):
+            if isinstance(need, KvNeed):
+                by_need.setdefault(need, []).append(cid)
+            elif isinstance(need, StateNeed):
+                state_entries.append((cid, need))
+            elif need is not None:
+                raise CacheError(f"cache entry {cid}: unknown need {need!r}")
+        self.kv_groups: List[KvGroup] = [
+            KvGroup(need, entries, self.n_pages, self.max_slots, self.pages_per_seq, dtype, device)
+            for need, entries in by_need.items()]
+        self._group_of: Dict[int, KvGroup] = {e: g for g in self.kv_groups for e in g.entries}
+        self._state: Dict[int, torch.Tensor] = {
+            cid: torch.zeros((self.max_slots, need.n_values), dtype=torch.float32, device=device)
+            for cid, need in state_entries}
+        self.rng_state = torch.zeros(self.max_slots, dtype=torch.int64, device=device)
+
+    # ---- slots ------------------------------------------------------------------------
+    def acquire(self, rng_seed: Optional[int] = None) -> int:
+        """A free slot with length 0, zeroed fixed state and a seeded generator."""
+        slot = self.slots.take()
+        self._length[slot] = 0
+        for t in self._state.values():
+            t[slot].zero_()
+        if rng_seed is not None:
+            self.seed(slot, rng_seed)
+        return slot
+
+    def seed(self, slot: int, seed: int) -> None:
+        seed &= (1 << 64) - 1
+        if seed == 0:
+            seed = 0x9E3779B97F4A7C15       # xorshift needs a non-zero state (qwen36_moe_decode.rs:1091-1094)
+        if seed >= 1 << 63:
+            seed -= 1 << 64
+        self.rng_state[slot] = seed
+
+    def release(self, slot: int) -> None:
+        """Give the slot and every page it holds back."""
+        if not self.slots.is_held(slot):
+            raise CacheError(f"slot {slot} is released but is not held")
+        for g in self.kv_groups:
+            g.release(slot)
+        self._length[slot] = 0
+        self.slots.give_back(slot)
+
+    def length(self, slot: int) -> int:
+        if not self.slots.is_held(slot):
+            raise CacheError(f"slot {slot} is not held")
+        return self._length[slot]
+
+    def live_slots(self) -> List[int]:
+        return [s for s in range(self.max_slots) if self.slots.is_held(s)]
+
+    # ---- per step -----------------------------------------------------------------------
+    def reserve(self, slot: int, n_new: int) -> None:
+        """Make room for ``n_new`` more tokens of ``slot`` in every group (all or nothing)."""
+        length = self.length(slot)
+        new_length = length + n_new
+        if new_length > self.max_seq_tokens:
+            raise CacheFull(f"slot {slot}: {new_length} tokens exceed the {self.max_seq_tokens} "
+                            "one sequence may hold")
+        for g in self.kv_groups:
+            need = len([p for p in range(g.first_needed_page(length), pages_for(new_length))
+                        if p not in g.held[slot]])
+            if need > g.pool.n_free:
+                raise CacheFull(f"slot {slot} needs {need} more pages of {PAGE_TOKENS} tokens, "
+                                f"{g.pool.n_free} of {g.n_pages} are free")
+        for g in self.kv_groups:
+            g.reserve(slot, length, new_length)
+
+    def advance(self, slot: int, n_new: int) -> None:
+        """Record that ``n_new`` tokens were appended; window groups drop what nothing reads."""
+        self._length[slot] = self.length(slot) + n_new
+        for g in self.kv_groups:
+            g.trim(slot, self._length[slot])
+
+    def sync(self) -> None:
+        """Upload page-table rows that changed since the last call."""
+        for g in self.kv_groups:
+            g.sync()
+
+    # ---- what parts read --------------------------------------------------------------
+    def kv(self, cache_id: int):
+        """(k, v, page_table, group) of one cache entry; k and v are ``[pages, kv_heads, 64, head_dim]``."""
+        g = self._group_of[cache_id]
+        i = g.index_of[cache_id]
+        return g.k[i], g.v[i], g.table, g
+
+    def state(self, cache_id: int) -> torch.Tensor:
+        """Fixed-size state ``[slots, n_values]`` float32 of one cache entry."""
+        return self._state[cache_id]
+
+    def free_tokens(self) -> int:
+        return min((g.pool.n_free for g in self.kv_groups), default=self.n_pages) * PAGE_TOKENS
+
+    def bytes_held(self) -> int:
+        n = sum(g.k.numel() * g.k.element_size() * 2 + g.table.numel() * 4 for g in self.kv_groups)
+        return n + sum(t.numel() * 4 for t in self._state.values()) + self.rng_state.numel() * 8
+
+    def check(self) -> None:
+        """Invariants: no slot or page lost or held twice; held pages match the tables."""
+        self.slots.check()
+        for g in self.kv_groups:
+            g.pool.check()
+            seen = set()
+            for slot in range(self.max_slots):
+                if g.held[slot] and not self.slots.is_held(slot):
+                    raise CacheError(f"free slot {slot} still holds pages")
+                for p, pid in g.held[slot].items():
+                    if pid in seen:
+                        raise CacheError(f"page {pid} is held twice")
+                    seen.add(pid)
+                    if int(g.table_host[slot, p]) != pid:
+                        raise CacheError(f"page table of slot {slot} disagrees at {p}")
+            if len(seen) != g.pool.n_held:
+                raise CacheError(f"{g.pool.n_held} pages are marked held but {len(seen)} are in use")

@@ -1,0 +1,224 @@
+"""Python faces of the plain CUDA kernels: tensors in, a launch on the current stream out.
+
+Every wrapper checks what the kernel assumes (device, dtype, contiguity, sizes)
+and raises; a non-zero status from the library raises :class:`KernelError`.
+There is no CPU path: without a CUDA device, or without the compiled library,
+these functions fail.  One wrapper per op, like the reference's
+``prefill_ffi`` (crates/kernel-ffi/src/prefill_ffi.rs:1104-3292) with its dtype
+codes (crates/gpu-hal/src/scalar_type.rs:25-32).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+_ERRORS = {2001: "unsupported dtype", 2002: "unsupported size", 2003: "unsupported configuration",
+           2004: "a bounded wait ran out"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _CODES[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
+
+
+def _check(status: int, what: str) -> None:
+    if status:
+        reason = _ERRORS.get(status) or f"CUDA error {status}"
+        raise KernelError(f"{what}: {reason}")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None, rows_contiguous=True):
+    if not t.is_cuda:
+        raise KernelError(f"{name} must live on a CUDA device (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, is {t.dtype}")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name} must have {dims} dims, has shape {tuple(t.shape)}")
+    if rows_contiguous and t.dim() >= 1 and t.numel() and t.stride(-1) != 1:
+        raise KernelError(f"{name} must be contiguous in its last dim")
+    if t.dim() > 2 and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+_lib_cache = {}
+
+
+def _fn(lib: str, name: str):
+    key = (lib, name)
+    if key not in _lib_cache:
+        f = getattr(load_library(lib), name)
+        f.restype = c_int
+        _lib_cache[key] = f
+    return _lib_cache[key]
+
+
+# ---- plain ops -------------------------------------------------------------------------
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = table[ids[t]] into the float32 residual stream."""
+    _need(ids, "ids", torch.int32, 1); _need(table, "table", None, 2); _need(out, "out", torch.float32, 2)
+    if not (table.is_contiguous() and out.is_contiguous()):
+        raise KernelError("embed: table and out must be contiguous")
+    if out.shape[0] != ids.shape[0] or out.shape[1] != table.shape[1]:
+        raise KernelError(f"embed: out {tuple(out.shape)} does not fit {ids.shape[0]} ids of width {table.shape[1]}")
+    _check(_fn("plain_ops", "ssb_embed")(
+        _ptr(ids), _ptr(table), c_int(dtype_code(table.dtype)), _ptr(out), c_int(ids.shape[0]),
+        c_int(table.shape[1]), c_int(table.shape[0]), _stream()), "embed")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * weight, x float32."""
+    _need(x, "x", torch.float32, 2); _need(weight, "weight", None, 1); _need(out, "out", None, 2)
+    if not (x.is_contiguous() and out.is_contiguous()):
+        raise KernelError("rmsnorm: x and out must be contiguous")
+    n = out.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        if rows.shape[0] != n:
+            raise KernelError("rmsnorm: one output row per gathered row")
+    elif x.shape[0] != n:
+        raise KernelError("rmsnorm: x and out differ in rows")
+    if x.shape[1] != out.shape[1] or weight.shape[0] != x.shape[1]:
+        raise KernelError("rmsnorm: widths differ")
+    _check(_fn("plain_ops", "ssb_rmsnorm")(
+        _ptr(x), _ptr(rows), _ptr(weight), c_int(dtype_code(weight.dtype)), c_float(eps), _ptr(out),
+        c_int(dtype_code(out.dtype)), c_int(n), c_int(x.shape[1]), _stream()), "rmsnorm")
+
+
+def gemm_nt_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out[m, n] (+)= sum_k a[m, k] w[n, k]; float32 accumulation in k order."""
+    _need(a, "a", None, 2); _need(w, "w", None, 2); _need(out, "out", None, 2)
+    if a.dtype != w.dtype:
+        raise KernelError(f"gemm: a is {a.dtype} but w is {w.dtype}")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    _check(_fn("plain_ops", "ssb_gemm_nt_plain")(
+        _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), c_int(dtype_code(a.dtype)), _ptr(out),
+        c_int(out.stride(0)), c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K),
+        c_int(1 if accumulate else 0), _stream()), "gemm_nt_plain")
+
+
+def rope_append(qkv: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                pos: torch.Tensor, slot: torch.Tensor, page_table: torch.Tensor,
+                k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], n_q: int, n_kv: int,
+                head_dim: int, rotary_dim: int, page_shift: int, write_cache: bool = True) -> None:
+    """Rotate q (and k) of every token in place; write k and v into the paged cache entry."""
+    _need(qkv, "qkv", None, 2); _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    T = qkv.shape[0]
+    if qkv.shape[1] < (n_q + 2 * n_kv) * head_dim and write_cache:
+        raise KernelError("rope_append: qkv rows are too narrow")
+    if pos.shape[0] != T or slot.shape[0] != T:
+        raise KernelError("rope_append: one position and one slot per token")
+    table_positions = 0
+    if cos is not None:
+        _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+        if cos.shape != sin.shape or cos.shape[1] != rotary_dim // 2 or not cos.is_contiguous() \
+                or not sin.is_contiguous():
+            raise KernelError("rope_append: cos/sin must be [positions, rotary_dim/2], contiguous")
+        table_positions = cos.shape[0]
+    if write_cache:
+        for c in (k_cache, v_cache):
+            _need(c, "cache", qkv.dtype)
+            if not c.is_contiguous():
+                raise KernelError("rope_append: cache entry must be contiguous")
+    _check(_fn("plain_ops", "ssb_rope_append")(
+        _ptr(qkv), c_int(qkv.stride(0)), c_int(dtype_code(qkv.dtype)), _ptr(cos), _ptr(sin),
+        c_int(table_positions), _ptr(pos), _ptr(slot), _ptr(page_table), c_int(page_table.shape[1]),
+        _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(n_q), c_int(n_kv), c_int(head_dim),
+        c_int(rotary_dim), c_int(page_shift), c_int(1 if write_cache else 0), _stream()), "rope_append")
+
+
+def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor,
+                    slot: torch.Tensor, page_table: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int,
+                    head_dim: int, page_shift: int, window: Optional[int], scale: float) -> None:
+    """Each token attends over keys [max(0, pos-window+1), pos] of its slot in the paged cache."""
+    _need(q, "q", None, 2); _need(out, "out", q.dtype, 2)
+    _need(k_cache, "k_cache", q.dtype); _need(v_cache, "v_cache", q.dtype)
+    _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    T = q.shape[0]
+    if out.shape[0] != T or out.shape[1] < n_q * head_dim or q.shape[1] < n_q * head_dim:
+        raise KernelError("attention: q/out shapes")
+    if head_dim > 512 or n_q % n_kv:
+        raise KernelError(f"attention_plain: head_dim {head_dim} (max 512), heads {n_q}/{n_kv} not supported")
+    _check(_fn("plain_ops", "ssb_attention_plain")(
+        _ptr(q), c_int(q.stride(0)), c_int(dtype_code(q.dtype)), _ptr(k_cache), _ptr(v_cache), _ptr(pos),
+        _ptr(slot), _ptr(page_table), c_int(page_table.shape[1]), _ptr(out), c_int(out.stride(0)),
+        c_int(T), c_int(n_q), c_int(n_kv), c_int(head_dim), c_int(page_shift),
+        c_int(int(window) if window else 0), c_float(scale), _stream()), "attention_plain")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, c] = silu(gate_up[t, c]) * gate_up[t, I + c]."""
+    _need(gate_up, "gate_up", None, 2); _need(out, "out", gate_up.dtype, 2)
+    T, inter = out.shape
+    if gate_up.shape[0] != T or gate_up.shape[1] != 2 * inter:
+        raise KernelError("swiglu: gate_up must be [T, 2*I] for out [T, I]")
+    _check(_fn("plain_ops", "ssb_swiglu")(
+        _ptr(gate_up), c_int(gate_up.stride(0)), _ptr(out), c_int(out.stride(0)),
+        c_int(dtype_code(out.dtype)), c_int(T), c_int(inter), _stream()), "swiglu")
+
+
+def add_into(out: torch.Tensor, x: torch.Tensor) -> None:
+    """out (float32) += x."""
+    _need(out, "out", torch.float32); _need(x, "x")
+    if not (out.is_contiguous() and x.is_contiguous()) or out.numel() != x.numel():
+        raise KernelError("add_into: contiguous tensors of equal size")
+    _check(_fn("plain_ops", "ssb_add_into")(
+        _ptr(out), _ptr(x), c_int(dtype_code(x.dtype)), c_longlong(out.numel()), _stream()), "add_into")
+
+
+# ---- sampling --------------------------------------------------------------------------
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _need(logits, "logits", torch.float32, 2); _need(out, "out", torch.int32, 1)
+    if out.shape[0] != logits.shape[0]:
+        raise KernelError("argmax: one output per row")
+    _check(_fn("sampling", "ssb_argmax")(
+        _ptr(logits), c_longlong(logits.stride(0)), c_int(logits.shape[0]), c_int(logits.shape[1]),
+        _ptr(out), _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
+           slots: Optional[torch.Tensor], rng_state: torch.Tensor, out: torch.Tensor,
+           drawn_u: Optional[torch.Tensor] = None) -> None:
+    _need(logits, "logits", torch.float32, 2); _need(out, "out", torch.int32, 1)
+    _need(rng_state, "rng_state", torch.int64, 1)
+    n = logits.shape[0]
+    if slots is not None:
+        _need(slots, "slots", torch.int32, 1)
+        if slots.shape[0] != n:
+            raise KernelError("sample: one slot per row")
+    elif rng_state.shape[0] < n:
+        raise KernelError("sample: one generator state per row")
+    if drawn_u is not None:
+        _need(drawn_u, "drawn_u", torch.float32, 1)
+    if out.shape[0] != n:
+        raise KernelError("sample: one output per row")
+    _check(_fn("sampling", "ssb_sample")(
+        _ptr(logits), c_longlong(logits.stride(0)), c_int(n), c_int(logits.shape[1]),
+        c_float(temperature), c_int(int(top_k)), c_float(top_p), _ptr(slots), _ptr(rng_state), _ptr(out),
+        _ptr(drawn_u), _stream()), "sample")

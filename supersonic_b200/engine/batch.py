@@ -1,0 +1,101 @@
+"""What one step runs: the tokens it is given, packed, with each token's sequence,
+position and cache slot.
+
+A step never pads: the tokens of all sequences lie back to back (``[sum T]``),
+so nothing but real tokens is computed and padding cannot change a result.
+The reference steps one sequence at a time (``prefill`` for a whole prompt,
+``decode_step(token, pos)`` after it: crates/runner/src/decode_engine.rs:10017-10061,
+10557-10569); a ragged batch is this engine's own design.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import torch
+
+
+@dataclass
+class StepEntry:
+    """One sequence's share of a step: its cache slot, its next tokens, and the
+    places among these tokens whose logits are wanted."""
+
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class StepBatch:
+    n_tokens: int
+    n_seqs: int
+    max_new: int                   # longest run of new tokens of one sequence
+    max_total: int                 # longest sequence after this step
+    is_decode: bool                # every sequence brings exactly one token
+    token_ids: torch.Tensor        # [T] int32
+    pos: torch.Tensor              # [T] int32: position of each token in its sequence
+    slot_of_token: torch.Tensor    # [T] int32
+    seq_slot: torch.Tensor         # [B] int32
+    seq_start: torch.Tensor        # [B] int32: tokens the sequence held before this step
+    cu_new: torch.Tensor           # [B+1] int32: where each sequence's new tokens begin
+    want_rows: torch.Tensor        # [W] int32: rows of the packed tokens whose logits are wanted
+    n_want: int
+    host_slots: List[int] = field(default_factory=list)
+    host_starts: List[int] = field(default_factory=list)
+    host_counts: List[int] = field(default_factory=list)
+
+
+def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], device,
+              vocab_size: Optional[int] = None) -> StepBatch:
+    """Lay the entries out back to back and move the index arrays to ``device`` in one copy."""
+    if not entries:
+        raise ValueError("a step needs at least one entry")
+    tokens: List[int] = []
+    pos: List[int] = []
+    slot_of: List[int] = []
+    want: List[int] = []
+    cu = [0]
+    slots, counts = [], []
+    for e, start in zip(entries, starts):
+        n = len(e.tokens)
+        if n == 0:
+            raise ValueError(f"slot {e.slot}: an entry must bring at least one token")
+        base = len(tokens)
+        for w in e.want:
+            if not 0 <= w < n:
+                raise ValueError(f"slot {e.slot}: wanted place {w} is outside its {n} tokens")
+            want.append(base + w)
+        tokens.extend(int(t) for t in e.tokens)
+        pos.extend(range(start, start + n))
+        slot_of.extend([e.slot] * n)
+        cu.append(base + n)
+        slots.append(e.slot)
+        counts.append(n)
+    if vocab_size is not None:
+        bad = [t for t in tokens if not 0 <= t < vocab_size]
+        if bad:
+            raise ValueError(f"token ids {bad[:8]} are outside the vocabulary of {vocab_size}")
+    if len(set(slots)) != len(slots):
+        raise ValueError("a slot appears twice in one step")
+    T, B, W = len(tokens), len(slots), len(want)
+    flat = tokens + pos + slot_of + slots + list(starts) + cu + want
+    host = torch.tensor(flat, dtype=torch.int32)
+    dev = torch.device(device)
+    if dev.type == "cuda":
+        host = host.pin_memory()
+    buf = host.to(dev, non_blocking=True)
+    o = [0]
+
+    def take(n):
+        v = buf[o[0]:o[0] + n]
+        o[0] += n
+        return v
+    token_ids, pos_t, slot_t = take(T), take(T), take(T)
+    seq_slot, seq_start, cu_new, want_rows = take(B), take(B), take(B + 1), take(W)
+    return StepBatch(
+        n_tokens=T, n_seqs=B, max_new=max(counts),
+        max_total=max(s + c for s, c in zip(starts, counts)),
+        is_decode=all(c == 1 for c in counts),
+        token_ids=token_ids, pos=pos_t, slot_of_token=slot_t, seq_slot=seq_slot, seq_start=seq_start,
+        cu_new=cu_new, want_rows=want_rows, n_want=W,
+        host_slots=slots, host_starts=list(starts), host_counts=counts)

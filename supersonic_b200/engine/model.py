@@ -1,0 +1,154 @@
+"""The model as the engine runs it: parts built from a :class:`ModelSpec`, a cache, and
+one step function.
+
+``step`` takes a batch of sequences that either all start (their prompts, of
+unequal lengths, in one step) or all go on by one token.  It runs exactly the
+tokens it is given, as one packed batch, against the cache earlier steps left,
+appends to the cache, and returns float32 logits at the wanted places.  Nothing
+in it depends on the architecture: the order of layers is the spec's schedule.
+
+The reference splits this in two engines, ``prefill_inner`` for a prompt
+(crates/runner/src/prefill_engine.rs:974-1382) and ``component_decode_step_4b_impl``
+for one token (crates/runner/src/decode_engine.rs:3631-3993), one sequence each.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache import KvNeed, SequenceCache, StateNeed
+from ..config import ModelSpec, load_config, spec_from_config
+from ..csrc.kernel_sets import kernel_set_for
+from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
+                     BuildContext, WeightAccess, lookup)
+from ..weights import WeightStore
+from .batch import StepBatch, StepEntry, pack_step
+
+_DTYPES = {"float32": torch.float32, "fp32": torch.float32, "f32": torch.float32,
+           "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"dtype {dtype} is not supported (float32 or bfloat16)")
+        return dtype
+    try:
+        return _DTYPES[str(dtype).lower()]
+    except KeyError:
+        raise ValueError(f"dtype {dtype!r} is not supported (float32 or bfloat16)") from None
+
+
+def _require_cuda(device: torch.device) -> None:
+    if device.type != "cuda":
+        raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device is available; the engine has no CPU path")
+    torch.cuda.set_device(device)
+
+
+@dataclass
+class StepContext:
+    batch: StepBatch
+    cache: SequenceCache
+    kernels: Any
+    dtype: torch.dtype
+
+
+class Model:
+    """Parts, cache and step function of one model on one device."""
+
+    def __init__(self, spec: ModelSpec, store: WeightStore, dtype="bfloat16", device="cuda:0",
+                 max_tokens: int = 4096, max_seq_tokens: Optional[int] = None,
+                 max_slots: Optional[int] = None, kernels: Optional[str] = None, config=None):
+        spec.validate()
+        self.spec, self.config = spec, config
+        self.dtype = parse_dtype(dtype)
+        self.device = torch.device(device)
+        _require_cuda(self.device)
+        self.kernels = kernel_set_for(self.dtype, kernels)
+        max_seq = min(max_seq_tokens or spec.max_positions, spec.max_positions, max_tokens)
+        weights = WeightAccess(store, self.device)
+        build = BuildContext(self.device, self.dtype, self.kernels, weights, max_positions=max_seq + 64)
+
+        def part(table, what, ps):
+            return lookup(table, ps.kind, what)(ps.params, ps.weights, build)
+
+        self.embedding = part(EMBEDDINGS, "embedding", spec.embedding)
+        self.blocks = []
+        for b in spec.blocks:
+            mixer = part(MIXERS, "mixer", b.mixer)
+            ff = part(FEED_FORWARDS, "feed-forward", b.feed_forward)
+            n1, n2 = part(NORMS, "norm", b.mixer_norm), part(NORMS, "norm", b.feed_forward_norm)
+            pos = part(POSITION_ENCODINGS, "position encoding", b.position) if b.position else None
+            self.blocks.append(lookup(BLOCKS, b.kind, "block")(mixer, ff, n1, n2, pos))
+        self.final_norm = part(NORMS, "norm", spec.final_norm)
+        self.head = part(HEADS, "head", spec.head)
+        weights.forget()
+
+        # what each cache entry must hold is asked of the mixer that writes it
+        needs: Dict[int, Any] = {}
+        for stop in spec.schedule:
+            need = self.blocks[stop.layer].mixer.cache_need()
+            if stop.writes_cache:
+                if stop.cache in needs and needs[stop.cache] != need:
+                    raise ValueError(f"cache entry {stop.cache} is written by mixers with different needs")
+                needs[stop.cache] = need
+            elif needs.get(stop.cache) != need:
+                raise ValueError(f"layer {stop.layer} reads cache entry {stop.cache}, whose layout "
+                                 f"{needs.get(stop.cache)} is not its own {need}")
+        self.cache = SequenceCache({c: n for c, n in needs.items() if n is not None}, max_tokens,
+                                   max_seq, self.dtype, self.device, max_slots)
+
+    # ---- construction from a folder ---------------------------------------------------
+    @staticmethod
+    def from_dir(model_dir: str, **kw) -> "Model":
+        """The model class is chosen by config.json's architecture; weights are checked
+        against the configuration before anything is built."""
+        config = load_config(model_dir)
+        store = WeightStore.from_dir(model_dir)
+        store.check(config.tensor_shapes())
+        return Model(spec_from_config(config), store, config=config, **kw)
+
+    @staticmethod
+    def from_config(config, store: WeightStore, **kw) -> "Model":
+        store.check(config.tensor_shapes())
+        return Model(spec_from_config(config), store, config=config, **kw)
+
+    @property
+    def vocab_size(self) -> int:
+        return self.spec.vocab_size
+
+    # ---- the step ---------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the entries' tokens; returns float32 logits ``[wanted, vocab]`` in the order
+        of the entries and of their ``want`` (an empty tensor if nothing is wanted)."""
+        cache = self.cache
+        starts = [cache.length(e.slot) for e in entries]
+        batch = pack_step(entries, starts, self.device, self.spec.vocab_size)
+        for e in entries:          # pages a failed step reserved stay with their slots
+            cache.reserve(e.slot, len(e.tokens))
+        cache.sync()
+        logits = self._forward(batch)
+        for e in entries:
+            cache.advance(e.slot, len(e.tokens))
+        return logits
+
+    def _forward(self, batch: StepBatch) -> torch.Tensor:
+        ctx = StepContext(batch, self.cache, self.kernels, self.dtype)
+        residual = self.embedding(ctx, batch.token_ids)
+        for stop in self.spec.schedule:
+            self.blocks[stop.layer].forward(ctx, residual, stop.cache, stop.writes_cache)
+        if batch.n_want == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        normed = self.final_norm(ctx, residual, rows=batch.want_rows)
+        return self.head(ctx, normed)
+
+    # ---- sequences --------------------------------------------------------------------
+    def open_sequence(self, rng_seed: Optional[int] = None) -> int:
+        return self.cache.acquire(rng_seed)
+
+    def close_sequence(self, slot: int) -> None:
+        self.cache.release(slot)

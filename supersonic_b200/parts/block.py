@@ -1,0 +1,22 @@
+"""Block arrangements.  ``pre_norm``: h += mixer(norm(h)); h += feed_forward(norm(h)),
+the residual stream kept and summed in float32 (crates/runner/src/prefill_engine.rs:1116-1222)."""
+from __future__ import annotations
+
+from .registry import register_block
+
+
+@register_block("pre_norm")
+class PreNormBlock:
+    """Interface of a block: ``forward(ctx, residual, cache_id, writes_cache)`` updates the
+    float32 residual stream ``[T, hidden]`` in place."""
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, position):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.position = position
+
+    def forward(self, ctx, residual, cache_id, writes_cache):
+        x = self.mixer_norm(ctx, residual)
+        self.mixer.forward(ctx, x, residual, cache_id, writes_cache, self.position)
+        x = self.feed_forward_norm(ctx, residual)
+        self.feed_forward.forward(ctx, x, residual)

@@ -1,0 +1,39 @@
+"""Feed-forwards.  ``swiglu``: down( silu(gate(x)) * up(x) ), silu(g) = g / (1 + exp(-g)),
+added to the residual (crates/runner/src/prefill_engine.rs:3226-3366;
+kernels/full_attention_cuda.cuh:1995-2010).  Gate and up run as one matrix product
+over row-concatenated weights."""
+from __future__ import annotations
+
+import torch
+
+from .registry import BuildContext, register_feed_forward
+
+
+@register_feed_forward("swiglu")
+class SwiGLU:
+    """params: ``hidden_size``, ``intermediate_size``; weights: ``gate``, ``up``, ``down``.
+
+    Interface of a feed-forward: ``forward(ctx, x, residual)`` reads the normed
+    activations ``x`` [T, hidden] and adds its output into ``residual`` (float32).
+    """
+
+    def __init__(self, params, weights, build: BuildContext):
+        self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        w = build.weights
+        gate, up = w.as_dtype(weights["gate"], build.dtype), w.as_dtype(weights["up"], build.dtype)
+        self.w_down = w.as_dtype(weights["down"], build.dtype)
+        for name, t, want in ((weights["gate"], gate, (self.inter, self.hidden)),
+                              (weights["up"], up, (self.inter, self.hidden)),
+                              (weights["down"], self.w_down, (self.hidden, self.inter))):
+            if tuple(t.shape) != want:
+                raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {want}")
+        self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
+        self.dtype = build.dtype
+
+    def forward(self, ctx, x, residual):
+        T = x.shape[0]
+        gate_up = torch.empty((T, 2 * self.inter), dtype=self.dtype, device=x.device)
+        ctx.kernels.linear(x, self.w_gate_up, gate_up)
+        z = torch.empty((T, self.inter), dtype=self.dtype, device=x.device)
+        ctx.kernels.swiglu(gate_up, z)
+        ctx.kernels.linear(z, self.w_down, residual, accumulate=True)
