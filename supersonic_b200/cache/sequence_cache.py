@@ -159,6 +159,77 @@ class SequenceCache:
         return slot
 
     def seed(self, slot: int, seed: int) -> None:
+        """Set the slot's xorshift64 generator state (a non-zero 64-bit value)."""
+        seed &= (1 << 64) - 1
+        if seed == 0:
+            seed = 0x9E3779B97F4A7C15       # xorshift needs a non-zero state (qwen36_moe_decode.rs:1091-1094)
+        if seed >= 1 << 63:
+            seed -= 1 << 64
+        self.rng_state[slot] = seed
+
+    def release(self, slot: int) -> None:
+        for pid in self.held[slot].values():
+            self.pool.give_back(pid)
+        self.held[slot].clear()
+
+    def sync(self) -> None:
+        if self._dirty_hi >= self._dirty_lo:
+            lo, hi = self._dirty_lo, self._dirty_hi + 1
+            self.table[lo:hi].copy_(self.table_host[lo:hi], non_blocking=True)
+            self._dirty_lo, self._dirty_hi = self.table.shape[0], -1
+
+
+class SequenceCache:
+    """Slots, page groups and per-sequence state for one model.
+
+    ``needs`` maps a cache id (as named by the model's schedule) to what its mixer
+    needs.  ``max_tokens`` bounds the tokens all live sequences hold together
+    (each rounded up to whole pages); ``max_seq_tokens`` bounds one sequence.
+    """
+
+    def __init__(self, needs: Dict[int, Need], max_tokens: int, max_seq_tokens: int,
+                 dtype: torch.dtype, device, max_slots: Optional[int] = None):
+        device = torch.device(device)
+        if max_tokens <= 0 or max_seq_tokens <= 0:
+            raise CacheError("the cache needs room for at least one token")
+        self.device, self.dtype = device, dtype
+        self.n_pages = pages_for(max_tokens)
+        self.pages_per_seq = min(pages_for(max_seq_tokens), self.n_pages)
+        self.max_seq_tokens = self.pages_per_seq * PAGE_TOKENS
+        self.max_slots = max_slots if max_slots is not None else min(self.n_pages, 4096)
+        self.slots = FreeList(self.max_slots, "slot")
+        self._length = [0] * self.max_slots
+        # groups by need
+        by_need: Dict[KvNeed, List[int]] = {}
+        state_entries: List[Tuple[int, StateNeed]] = []
+        for cid, need in sorted(needs.items()):
+            if isinstance(need, KvNeed):
+                by_need.setdefault(need, []).append(cid)
+            elif isinstance(need, StateNeed):
+                state_entries.append((cid, need))
+            elif need is not None:
+                raise CacheError(f"cache entry {cid}: unknown need {need!r}")
+        self.kv_groups: List[KvGroup] = [
+            KvGroup(need, entries, self.n_pages, self.max_slots, self.pages_per_seq, dtype, device)
+            for need, entries in by_need.items()]
+        self._group_of: Dict[int, KvGroup] = {e: g for g in self.kv_groups for e in g.entries}
+        self._state: Dict[int, torch.Tensor] = {
+            cid: torch.zeros((self.max_slots, need.n_values), dtype=torch.float32, device=device)
+            for cid, need in state_entries}
+        self.rng_state = torch.zeros(self.max_slots, dtype=torch.int64, device=device)
+
+    # ---- slots ------------------------------------------------------------------------
+    def acquire(self, rng_seed: Optional[int] = None) -> int:
+        """A free slot with length 0, zeroed fixed state and a seeded generator."""
+        slot = self.slots.take()
+        self._length[slot] = 0
+        for t in self._state.values():
+            t[slot].zero_()
+        if rng_seed is not None:
+            self.seed(slot, rng_seed)
+        return slot
+
+    def seed(self, slot: int, seed: int) -> None:
         seed &= (1 << 64) - 1
         if seed == 0:
             seed = 0x9E3779B97F4A7C15       # xorshift needs a non-zero state (qwen36_moe_decode.rs:1091-1094)

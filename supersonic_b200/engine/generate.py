@@ -1,0 +1,130 @@
+"""The generation loop above the step function.
+
+Requests are served in batches that start together: all prompts of a batch, of unequal
+lengths, in one step; then one token per live sequence per step.  A sequence ends at
+a stop token or at its token budget, leaves the batch and gives its slot back; the
+step shrinks.  No request joins a running batch; the next batch starts when the
+current one is done, in slots that were used before.
+
+Per sequence this is the reference's loop (crates/runner/src/llama31_engine.rs:1075-1551):
+the first token is sampled from the prompt's last logits; a stop token is appended
+to the output before the loop sees it; ``max_new_tokens == 0`` still runs the prompt.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+import torch
+
+from ..sampling import Sampler, SamplingParams, request_seed
+from .batch import StepEntry
+
+
+@dataclass
+class GenerationResult:
+    tokens: List[int] = field(default_factory=list)
+    finish_reason: str = "length"         # "stop" (a stop token) or "length" (the budget)
+    prompt_tokens: int = 0
+
+
+def finished(token: int, n_generated: int, max_new_tokens: int, stop_ids) -> Optional[str]:
+    """Why a sequence ends after producing ``token`` as its ``n_generated``-th, or None."""
+    if token in stop_ids:
+        return "stop"
+    if n_generated >= max_new_tokens:
+        return "length"
+    return None
+
+
+def plan_batch(waiting: Sequence[int], prompt_lens: Sequence[int], max_new_tokens: int,
+               free_tokens: int, free_slots: int, page_tokens: int,
+               batch_size: Optional[int]) -> List[int]:
+    """The next batch: requests in arrival order while their prompts plus budgets fit
+    the free pages and slots (each sequence's need rounded up to whole pages)."""
+    chosen: List[int] = []
+    room = free_tokens
+    for r in waiting:
+        if len(chosen) >= free_slots or (batch_size and len(chosen) >= batch_size):
+            break
+        need = -(-(prompt_lens[r] + max(max_new_tokens, 1)) // page_tokens) * page_tokens
+        if need > room:
+            break
+        chosen.append(r)
+        room -= need
+    return chosen
+
+
+class Generator:
+    """Drives ``model.step`` for whole requests.  ``model`` needs ``step``, ``open_sequence``,
+    ``close_sequence``, ``cache`` (``free_tokens``, ``slots.n_free``, ``max_seq_tokens``),
+    ``spec.stop_token_ids`` and ``device``; ``sampler`` maps logits and slots to tokens."""
+
+    def __init__(self, model, sampler: Optional[Callable] = None):
+        self.model = model
+        self.sampler = sampler or Sampler(model.kernels, model.cache.rng_state)
+        self.steps_run = 0
+
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 8,
+                 sampling: SamplingParams = SamplingParams(), stop_token_ids=None,
+                 ignore_eos: bool = False, include_stop_token: bool = True,
+                 batch_size: Optional[int] = None,
+                 on_step: Optional[Callable] = None) -> List[GenerationResult]:
+        from ..cache import PAGE_TOKENS
+        model, cache = self.model, self.model.cache
+        stop_ids = frozenset() if ignore_eos else frozenset(
+            model.spec.stop_token_ids if stop_token_ids is None else stop_token_ids)
+        prompts = [list(p) for p in prompts]
+        for i, p in enumerate(prompts):
+            if not p:
+                raise ValueError(f"prompt {i} is empty")
+            if len(p) + max_new_tokens > cache.max_seq_tokens:
+                raise ValueError(f"prompt {i}: {len(p)} tokens plus {max_new_tokens} new ones exceed "
+                                 f"the {cache.max_seq_tokens} a sequence may hold")
+        results = [GenerationResult(prompt_tokens=len(p)) for p in prompts]
+        waiting = list(range(len(prompts)))
+        lens = [len(p) for p in prompts]
+        while waiting:
+            batch = plan_batch(waiting, lens, max_new_tokens, cache.free_tokens(), cache.slots.n_free,
+                               PAGE_TOKENS, batch_size)
+            if not batch:
+                raise RuntimeError(f"request {waiting[0]} ({lens[waiting[0]]} prompt tokens) does not "
+                                   f"fit the cache even when it is empty of other requests")
+            waiting = waiting[len(batch):]
+            self._run_batch(batch, prompts, results, max_new_tokens, sampling, stop_ids,
+                            include_stop_token, on_step)
+        return results
+
+    def _run_batch(self, batch, prompts, results, max_new_tokens, sampling, stop_ids,
+                   include_stop_token, on_step):
+        model = self.model
+        slot_of = {r: model.open_sequence(request_seed(sampling.sampling_seed, r)) for r in batch}
+        live = list(batch)
+        try:
+            entries = [StepEntry(slot_of[r], prompts[r], [len(prompts[r]) - 1]) for r in live]
+            while live:
+                logits = model.step(entries)
+                self.steps_run += 1
+                if max_new_tokens <= 0:
+                    break
+                slots = torch.tensor([slot_of[r] for r in live], dtype=torch.int32).to(
+                    logits.device, non_blocking=True)
+                tokens = self.sampler(logits, slots, sampling).to("cpu").tolist()
+                if on_step:
+                    on_step(live, tokens)
+                still, entries = [], []
+                for r, tok in zip(live, tokens):
+                    res = results[r]
+                    why = finished(tok, len(res.tokens) + 1, max_new_tokens, stop_ids)
+                    if why != "stop" or include_stop_token:
+                        res.tokens.append(tok)
+                    if why:
+                        res.finish_reason = why
+                        model.close_sequence(slot_of.pop(r))
+                    else:
+                        still.append(r)
+                        entries.append(StepEntry(slot_of[r], [tok], [0]))
+                live = still
+        finally:
+            for slot in slot_of.values():
+                model.close_sequence(slot)

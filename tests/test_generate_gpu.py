@@ -1,0 +1,141 @@
+"""Generation on the GPU through the Python entry point and the command line: greedy
+tokens against the plain implementation, long decoding, the first tokens of a sequence,
+stop tokens, sampling that does not depend on the batch."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+import replay_helpers as rh
+
+pytestmark = pytest.mark.gpu
+
+
+def margin_ok(pc, pw, tokens, tol):
+    """True if the plain top two logits at the last position differ by more than ``tol``."""
+    top2 = np.sort(pl.forward(pc, pw, tokens)[-1])[-2:]
+    return top2[1] - top2[0] > tol
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_matches_plain(model_folders, name, dtype):
+    import supersonic_b200
+    d, pc, pw = model_folders[name]
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, pc["vocab_size"], n).tolist() for n in (5, 11, 17, 1, 66)]
+    eng = supersonic_b200.load(d, dtype=dtype, context_size=128, batch_size=3)
+    got = eng.generate(prompts, max_new_tokens=8, ignore_eos=True, batch_size=3)
+    tol = 1e-4 if dtype == "float32" else 4e-2
+    for p, g in zip(prompts, got):
+        assert len(g) == 8
+        want = pl.greedy_generate(pc, pw, p, 8)
+        for i in range(8):
+            if g[i] != want[i]:
+                # only a near-tie of the plain logits may explain a different token
+                assert not margin_ok(pc, pw, p + want[:i], tol), (name, dtype, p, i, g, want)
+                break
+    assert eng.model.cache.slots.n_held == 0
+    eng.model.cache.check()
+
+
+def test_stop_tokens_end_sequences_early(model_folders):
+    import supersonic_b200
+    d, pc, pw = model_folders["A"]
+    rng = np.random.default_rng(4)
+    prompts = [rng.integers(0, 256, n).tolist() for n in (9, 3, 30, 12)]
+    free = [pl.greedy_generate(pc, pw, p, 12) for p in prompts]
+    stops = sorted({f[2] for f in free[:2]} | {free[2][7]})          # ends sequences at different steps
+    eng = supersonic_b200.load(d, dtype="float32", context_size=128, batch_size=4)
+    res = eng.generate_detailed(prompts, max_new_tokens=12, stop_token_ids=stops, batch_size=4)
+    for p, r in zip(prompts, res):
+        want = pl.greedy_generate(pc, pw, p, 12, stop_ids=stops)
+        assert r.tokens == want
+        assert r.finish_reason == ("stop" if want[-1] in stops else "length")
+    assert len({len(r.tokens) for r in res}) > 1
+    # config.json's eos_token_id (7 for this model) is the default stop set
+    assert eng.model.spec.stop_token_ids == [7]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_stays_on_the_plain_logits(model_folders, dtype):
+    """300 decoded tokens (several pages) with teacher forcing through the step function."""
+    from supersonic_b200.engine import Model, StepEntry
+    d, pc, pw = model_folders["C"]
+    toks = np.random.default_rng(7).integers(0, pc["vocab_size"], 330).tolist()
+    ref = pl.forward(pc, pw, toks)
+    m = Model.from_dir(d, dtype=dtype, max_tokens=384)
+    s = m.open_sequence()
+    m.step([StepEntry(s, toks[:30], [])])
+    rows = [m.step([StepEntry(s, [toks[p]], [0])]) for p in range(30, 330)]
+    got = torch.cat(rows).double().cpu().numpy()
+    err = np.abs(got - ref[30:]).max(axis=1)
+    tol = 2e-5 if dtype == "float32" else 2e-2 * np.abs(ref).max()
+    assert err.max() < tol, f"first bad position {30 + int(np.argmax(err > tol))}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(model_folders, dtype):
+    """Positions 0, 1, 2 decoded one by one from an empty slot, for two sequences at once."""
+    from supersonic_b200.engine import Model, StepEntry
+    d, pc, pw = model_folders["B"]
+    a, b = [11, 200, 3, 77], [380, 0, 0, 5]
+    ra, rb = pl.forward(pc, pw, a), pl.forward(pc, pw, b)
+    m = Model.from_dir(d, dtype=dtype, max_tokens=128)
+    sa, sb = m.open_sequence(), m.open_sequence()
+    tol = 2e-5 if dtype == "float32" else 2e-2 * max(np.abs(ra).max(), np.abs(rb).max())
+    for p in range(4):
+        lg = m.step([StepEntry(sa, [a[p]], [0]), StepEntry(sb, [b[p]], [0])]).double().cpu().numpy()
+        assert np.abs(lg[0] - ra[p]).max() < tol and np.abs(lg[1] - rb[p]).max() < tol, p
+
+
+def test_sampling_does_not_depend_on_the_batch(model_folders):
+    import supersonic_b200
+    d, pc, pw = model_folders["B"]
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(0, 384, n).tolist() for n in (1, 7, 19, 40)]
+    eng = supersonic_b200.load(d, dtype="float32", context_size=128, batch_size=4)
+    kw = dict(max_new_tokens=12, temperature=0.7, sampling_seed=1234, ignore_eos=True)
+    together = eng.generate(prompts, batch_size=4, **kw)
+    assert together == eng.generate(prompts, batch_size=4, **kw)          # the seed decides
+    pairs = eng.generate(prompts, batch_size=2, **kw)
+    assert pairs == together                                              # the batch does not
+    assert eng.generate(prompts, batch_size=4, **{**kw, "sampling_seed": 99}) != together
+    assert eng.generate(prompts, batch_size=4, **{**kw, "top_k": 1}) == \
+        eng.generate(prompts, batch_size=4, max_new_tokens=12, ignore_eos=True)   # top_k 1 is greedy
+    # every sampled token is one the plain distribution allows under top-k
+    limited = eng.generate(prompts[:2], batch_size=2, **{**kw, "top_k": 5})
+    for p, g in zip(prompts[:2], limited):
+        seq = list(p)
+        for t in g:
+            probs = pl.sampling_distribution(pl.forward(pc, pw, seq)[-1], 0.7, top_k=5)
+            assert probs[t] > 0
+            seq.append(t)
+
+
+def test_command_line(model_folders):
+    d, pc, pw = model_folders["A"]
+    prompt = [5, 9, 100, 42]
+    want = pl.greedy_generate(pc, pw, prompt, 6)
+    cmd = [sys.executable, os.path.join(rh.ROOT, "bin", "supersonic"), "--model-dir", d, "--prompt-ids",
+           ",".join(map(str, prompt)), "--max-new-tokens", "6", "--dtype", "float32", "--ignore-eos",
+           "--emit-generated-json"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    line = [l for l in proc.stdout.splitlines() if l.startswith("[tokens] ")][0]
+    assert [int(t) for t in line.split()[1:]] == want
+    assert "[generated_json]" in proc.stdout and "[result] prompt_tokens=4 generated_tokens=6" in proc.stderr
+
+
+def test_no_cpu_path():
+    from supersonic_b200.engine import Model
+    from supersonic_b200.config import config_from_dict
+    from supersonic_b200.weights import random_store
+    import tiny_configs
+    c = config_from_dict(tiny_configs.A)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        Model.from_config(c, random_store(c, 0), device="cpu")

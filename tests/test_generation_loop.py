@@ -1,0 +1,151 @@
+"""The generation loop's decisions, on the CPU with a scripted model: batches of unequal
+prompts, stop tokens, sequences that end early, one batch after another in reused slots."""
+import pytest
+import torch
+
+from supersonic_b200.cache import KvNeed, SequenceCache
+from supersonic_b200.engine.generate import Generator, finished, plan_batch
+from supersonic_b200.sampling import SamplingParams, request_seed
+
+
+class ScriptedModel:
+    """Next token = (sum of the sequence's tokens) % vocab: depends on the whole history of
+    the right sequence, so any mix-up of slots or tokens shows."""
+
+    class _Spec:
+        stop_token_ids = [3]
+
+    def __init__(self, vocab=11, max_tokens=64 * 4, max_seq=128, max_slots=None):
+        self.vocab, self.spec, self.device = vocab, self._Spec(), "cpu"
+        self.kernels = None
+        self.cache = SequenceCache({0: KvNeed(1, 16)}, max_tokens, max_seq, torch.float32, "cpu", max_slots)
+        self.history = {}
+        self.step_sizes = []
+        self.slots_seen = []
+
+    def open_sequence(self, seed=None):
+        s = self.cache.acquire(seed)
+        self.history[s] = []
+        self.slots_seen.append(s)
+        return s
+
+    def close_sequence(self, s):
+        self.cache.release(s)
+        del self.history[s]
+
+    def step(self, entries):
+        self.step_sizes.append([len(e.tokens) for e in entries])
+        rows = []
+        for e in entries:
+            self.cache.reserve(e.slot, len(e.tokens)); self.cache.advance(e.slot, len(e.tokens))
+            self.history[e.slot].extend(e.tokens)
+            assert len(self.history[e.slot]) == self.cache.length(e.slot)
+            for w in e.want:
+                assert w == len(e.tokens) - 1
+                row = torch.zeros(self.vocab)
+                row[sum(self.history[e.slot]) % self.vocab] = 1.0
+                rows.append(row)
+        return torch.stack(rows)
+
+
+def greedy(logits, slots, params):
+    return logits.argmax(-1).to(torch.int32)
+
+
+def expected(prompt, n, vocab=11, stop=(3,), include_stop=True):
+    toks, out = list(prompt), []
+    while len(out) < n:
+        t = sum(toks) % vocab
+        toks.append(t)
+        if t in stop:
+            if include_stop:
+                out.append(t)
+            return out, "stop"
+        out.append(t)
+    return out, "length"
+
+
+def test_finished_rules():
+    assert finished(3, 1, 8, {3}) == "stop"
+    assert finished(4, 8, 8, {3}) == "length"
+    assert finished(4, 7, 8, {3}) is None
+    assert finished(3, 8, 8, {3}) == "stop"          # a stop token at the budget is still a stop
+
+
+def test_plan_batch_respects_pages_slots_and_batch_size():
+    lens = [10, 100, 30, 64]
+    assert plan_batch([0, 1, 2, 3], lens, 8, 64 * 4, 8, 64, None) == [0, 1, 2]     # 64+128+64 fit, 128 more not
+    assert plan_batch([0, 1, 2, 3], lens, 8, 64 * 100, 2, 64, None) == [0, 1]      # slots
+    assert plan_batch([0, 1, 2, 3], lens, 8, 64 * 100, 8, 64, 3) == [0, 1, 2]      # batch size
+    assert plan_batch([1], lens, 8, 64, 8, 64, None) == []                         # does not fit at all
+
+
+def test_unequal_prompts_early_ends_and_slot_reuse():
+    m = ScriptedModel(max_tokens=64 * 3, max_seq=128)
+    g = Generator(m, sampler=greedy)
+    prompts = [[1, 2], [5, 6, 7, 8, 9], [2], [4, 4, 4], [10, 1, 1, 1, 1, 1, 1], [6]]
+    res = g.generate(prompts, max_new_tokens=6, batch_size=3)
+    for p, r in zip(prompts, res):
+        want, why = expected(p, 6)
+        assert r.tokens == want and r.finish_reason == why and r.prompt_tokens == len(p)
+    # first step of each batch brings whole prompts, later steps one token per live sequence
+    assert m.step_sizes[0] == [2, 5, 1]
+    assert all(all(n == 1 for n in s) for s in m.step_sizes[1:] if s != [3, 7, 1])
+    assert [3, 7, 1] in m.step_sizes                       # second batch started together
+    assert sorted(set(m.slots_seen)) == [0, 1, 2] and len(m.slots_seen) == 6      # slots used again
+    assert m.cache.slots.n_held == 0 and m.cache.free_tokens() == 64 * 3
+    m.cache.check()
+    # steps shrink as sequences end
+    sizes = [len(s) for s in m.step_sizes]
+    assert any(a > b for a, b in zip(sizes, sizes[1:]))
+
+
+def test_stop_token_options_and_zero_budget():
+    prompts = [[1, 2], [7, 7]]
+    m = ScriptedModel()
+    g = Generator(m, sampler=greedy)
+    res = g.generate(prompts, max_new_tokens=5, include_stop_token=False)
+    assert [r.tokens for r in res] == [expected(p, 5, include_stop=False)[0] for p in prompts]
+    res = g.generate(prompts, max_new_tokens=5, ignore_eos=True)
+    assert all(len(r.tokens) == 5 and r.finish_reason == "length" for r in res)
+    res = g.generate(prompts, max_new_tokens=5, stop_token_ids=[9])
+    assert [r.tokens for r in res] == [expected(p, 5, stop=(9,))[0] for p in prompts]
+    before = len(m.step_sizes)
+    res = g.generate(prompts, max_new_tokens=0)
+    assert [r.tokens for r in res] == [[], []] and len(m.step_sizes) == before + 1   # the prompt still runs
+    assert m.cache.slots.n_held == 0
+
+
+def test_requests_that_cannot_fit_are_refused():
+    m = ScriptedModel(max_tokens=64 * 2, max_seq=128)
+    g = Generator(m, sampler=greedy)
+    with pytest.raises(ValueError, match="exceed"):
+        g.generate([[1] * 125], max_new_tokens=8)
+    with pytest.raises(ValueError, match="empty"):
+        g.generate([[]])
+    assert m.cache.slots.n_held == 0
+
+
+def test_a_failing_step_gives_slots_back():
+    m = ScriptedModel()
+    calls = []
+
+    def bad_sampler(logits, slots, params):
+        calls.append(1)
+        if len(calls) == 2:
+            raise RuntimeError("boom")
+        return greedy(logits, slots, params)
+    with pytest.raises(RuntimeError, match="boom"):
+        Generator(m, sampler=bad_sampler).generate([[1, 2], [2, 2]], max_new_tokens=5, ignore_eos=True)
+    assert m.cache.slots.n_held == 0
+    m.cache.check()
+
+
+def test_request_seeds_differ_and_are_stable():
+    seeds = {request_seed(42, i) for i in range(100)}
+    assert len(seeds) == 100 and 0 not in seeds and request_seed(42, 3) == request_seed(42, 3)
+    assert request_seed(42, 0) != request_seed(43, 0)
+    with pytest.raises(ValueError):
+        SamplingParams(top_p=0.0)
+    assert SamplingParams().greedy and SamplingParams(temperature=0.7, top_k=1).greedy
+    assert not SamplingParams(temperature=0.7).greedy

@@ -1,0 +1,268 @@
+"""Each plain kernel alone against a PyTorch float32 statement of the same operation, at
+sizes other than the tiny models' (odd widths, several pages, windows)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def ops():
+    from supersonic_b200.csrc import ops as o
+    return o
+
+
+def tol(dtype):
+    return dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    g = torch.Generator(device=DEV).manual_seed(0)
+    table = torch.randn(301, 72, device=DEV, generator=g).to(dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    out = torch.full((5, 72), 7.0, device=DEV)
+    ops().embed(ids, table, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype,wdtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                          (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("hidden", [72, 1000, 4096])
+def test_rmsnorm(dtype, wdtype, hidden):
+    g = torch.Generator(device=DEV).manual_seed(1)
+    x = torch.randn(9, hidden, device=DEV, generator=g) * 3
+    w = (1 + 0.1 * torch.randn(hidden, device=DEV, generator=g)).to(wdtype)
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    for r in (None, rows):
+        src = x if r is None else x[r.long()]
+        out = torch.empty(src.shape, dtype=dtype, device=DEV)
+        ops().rmsnorm(x, w, 1e-5, out, r)
+        ref = src * torch.rsqrt((src * src).mean(-1, keepdim=True) + 1e-5) * w.float()
+        torch.testing.assert_close(out.float(), ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(1, 301, 72), (7, 64, 200), (70, 130, 33), (129, 65, 257)])
+def test_gemm_plain(dtype, M, N, K):
+    g = torch.Generator(device=DEV).manual_seed(2)
+    a = torch.randn(M, K, device=DEV, generator=g).to(dtype)
+    w = torch.randn(N, K, device=DEV, generator=g).to(dtype)
+    ref = a.double() @ w.double().T
+    out = torch.empty(M, N, dtype=dtype, device=DEV)
+    ops().gemm_nt_plain(a, w, out)
+    torch.testing.assert_close(out.double(), ref, atol=1e-4 if dtype == torch.float32 else 0.15, rtol=1e-2)
+    acc = torch.ones(M, N, device=DEV)
+    ops().gemm_nt_plain(a, w, acc, accumulate=True)
+    torch.testing.assert_close(acc.double(), ref + 1, atol=1e-4, rtol=1e-5)
+    out32 = torch.empty(M, N, device=DEV)
+    ops().gemm_nt_plain(a, w, out32)
+    torch.testing.assert_close(out32.double(), ref, atol=1e-4, rtol=1e-5)
+    # a row-strided input (a slice of a wider buffer) gives the same result
+    wide = torch.zeros(M, K + 5, dtype=dtype, device=DEV)
+    wide[:, :K] = a
+    out2 = torch.empty(M, N, device=DEV)
+    ops().gemm_nt_plain(wide[:, :K], w, out2)
+    assert torch.equal(out2, out32)
+
+
+def _paged(n_pages, n_kv, hd, dtype, seed):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    k = torch.randn(n_pages, n_kv, 64, hd, device=DEV, generator=g).to(dtype)
+    v = torch.randn(n_pages, n_kv, 64, hd, device=DEV, generator=g).to(dtype)
+    return k, v
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_q,n_kv,hd,rot", [(4, 2, 16, 16), (3, 1, 48, 48), (5, 5, 32, 16), (2, 1, 32, 0)])
+def test_rope_append(dtype, n_q, n_kv, hd, rot):
+    g = torch.Generator(device=DEV).manual_seed(3)
+    T = 6
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * hd, device=DEV, generator=g).to(dtype)
+    before = qkv.clone()
+    pos = torch.tensor([0, 63, 64, 130, 5, 1], dtype=torch.int32, device=DEV)
+    slot = torch.tensor([0, 0, 0, 1, -1, 1], dtype=torch.int32, device=DEV)   # one padding row
+    table = torch.tensor([[3, 1, 9], [4, 0, 2]], dtype=torch.int32, device=DEV)
+    k, v = _paged(10, n_kv, hd, dtype, 4)
+    k0, v0 = k.clone(), v.clone()
+    half = rot // 2
+    ang = torch.arange(200, device=DEV, dtype=torch.float64)[:, None] * \
+        (1.0 / 10000 ** (torch.arange(max(half, 1), device=DEV, dtype=torch.float64) / max(half, 1)))[None, :half]
+    cos, sin = ang.cos().float().contiguous(), ang.sin().float().contiguous()
+    ops().rope_append(qkv, cos if rot else None, sin if rot else None, pos, slot, table, k, v,
+                      n_q, n_kv, hd, rot, 6, True)
+    for t in range(T):
+        s, p = int(slot[t]), int(pos[t])
+        x = before[t].float().view(n_q + 2 * n_kv, hd)
+        if s < 0:
+            assert torch.equal(qkv[t], before[t])
+            continue
+        want = x.clone()
+        if rot:
+            c, sn = cos[p], sin[p]
+            r = x[: n_q + n_kv]
+            want[: n_q + n_kv, :half] = r[:, :half] * c - r[:, half:rot] * sn
+            want[: n_q + n_kv, half:rot] = r[:, :half] * sn + r[:, half:rot] * c
+        torch.testing.assert_close(qkv[t].float().view(-1, hd), want.to(dtype).float(), **tol(dtype))
+        page = int(table[s, p // 64])
+        assert torch.equal(k[page, :, p % 64], qkv[t].view(-1, hd)[n_q:n_q + n_kv])
+        assert torch.equal(v[page, :, p % 64], before[t].view(-1, hd)[n_q + n_kv:])
+    touched = torch.zeros(10, 64, dtype=torch.bool, device=DEV)
+    for t in range(T):
+        if int(slot[t]) >= 0:
+            touched[int(table[int(slot[t]), int(pos[t]) // 64]), int(pos[t]) % 64] = True
+    assert torch.equal(k[~touched], k0[~touched]) and torch.equal(v[~touched], v0[~touched])
+
+
+def _attention_reference(q, k, v, pos, slot, table, n_q, n_kv, hd, window, scale):
+    out = torch.zeros(q.shape[0], n_q * hd, dtype=torch.float64, device=q.device)
+    for t in range(q.shape[0]):
+        s, p = int(slot[t]), int(pos[t])
+        if s < 0:
+            continue
+        lo = max(0, p - window + 1) if window else 0
+        js = torch.arange(lo, p + 1, device=q.device)
+        pages = table[s, js // 64].long()
+        kk, vv = k[pages, :, js % 64].double(), v[pages, :, js % 64].double()      # [n, n_kv, hd]
+        qq = q[t, : n_q * hd].double().view(n_q, hd)
+        for h in range(n_q):
+            sc = (kk[:, h // (n_q // n_kv)] @ qq[h]) * scale
+            out[t, h * hd:(h + 1) * hd] = torch.softmax(sc, 0) @ vv[:, h // (n_q // n_kv)]
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_q,n_kv,hd,window", [(4, 2, 16, None), (3, 1, 48, None), (6, 2, 128, 100),
+                                                (2, 2, 256, None), (8, 2, 64, 64)])
+def test_attention_plain(dtype, n_q, n_kv, hd, window):
+    g = torch.Generator(device=DEV).manual_seed(5)
+    pos = torch.tensor([0, 1, 63, 64, 127, 128, 300, 299, 17], dtype=torch.int32, device=DEV)
+    slot = torch.tensor([0, 0, 0, 0, 1, 1, 1, 2, -1], dtype=torch.int32, device=DEV)
+    perm = torch.randperm(15, generator=torch.Generator().manual_seed(6)).to(torch.int32)
+    table = perm.view(3, 5).to(DEV)
+    k, v = _paged(15, n_kv, hd, dtype, 7)
+    ld = (n_q + 2 * n_kv) * hd
+    q = torch.randn(len(pos), ld, device=DEV, generator=g).to(dtype)
+    out = torch.full((len(pos), n_q * hd), 5.0, dtype=dtype, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    ops().attention_plain(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, window, scale)
+    ref = _attention_reference(q, k, v, pos, slot, table, n_q, n_kv, hd, window, scale)
+    torch.testing.assert_close(out.double(), ref, **tol(dtype))
+    assert torch.all(out[-1] == 0)                                      # padding row
+
+
+def test_attention_finds_a_far_key_and_the_windows_edge():
+    """One key among hundreds carries nearly all the weight: reading a neighbouring row, a
+    wrong page or a key just outside the window changes the output completely."""
+    n_q = n_kv = 1
+    hd = 32
+    k = torch.zeros(8, 1, 64, hd, device=DEV)
+    v = torch.zeros(8, 1, 64, hd, device=DEV)
+    table = torch.tensor([[5, 2, 7, 0, 3, 1]], dtype=torch.int32, device=DEV)
+    g = torch.Generator(device=DEV).manual_seed(8)
+    for p in range(330):
+        page = int(table[0, p // 64])
+        k[page, 0, p % 64] = 0.01 * torch.randn(hd, device=DEV, generator=g)
+        v[page, 0, p % 64, 0] = float(p)                                # value = its own position
+    needle = 131
+    k[int(table[0, needle // 64]), 0, needle % 64] = 4.0
+    q = torch.full((1, hd), 4.0, device=DEV)
+    pos = torch.tensor([329], dtype=torch.int32, device=DEV)
+    slot = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.empty(1, hd, device=DEV)
+    for window, sees in ((None, True), (329 - needle + 1, True), (329 - needle, False)):
+        ops().attention_plain(q, k, v, pos, slot, table, out, 1, 1, hd, 6, window, 1.0)
+        if sees:
+            assert abs(out[0, 0].item() - needle) < 1e-3
+        else:
+            lo = 329 - window + 1
+            assert abs(out[0, 0].item() - (lo + 329) / 2) < 2.0          # near-uniform over the window
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_and_add(dtype):
+    g = torch.Generator(device=DEV).manual_seed(9)
+    gu = (3 * torch.randn(5, 2 * 200, device=DEV, generator=g)).to(dtype)
+    z = torch.empty(5, 200, dtype=dtype, device=DEV)
+    ops().swiglu(gu, z)
+    gg, uu = gu[:, :200].float(), gu[:, 200:].float()
+    torch.testing.assert_close(z.float(), (gg / (1 + torch.exp(-gg)) * uu).to(dtype).float(), **tol(dtype))
+    acc = torch.ones(5, 200, device=DEV)
+    ops().add_into(acc, z)
+    torch.testing.assert_close(acc, 1 + z.float())
+
+
+def test_argmax_lowest_index_wins():
+    lg = torch.randn(6, 128256, device=DEV, generator=torch.Generator(device=DEV).manual_seed(10))
+    lg[0, 77] = lg[0, 99000] = 50.0
+    lg[1, 128255] = 60.0
+    lg[2, :] = -float("inf")
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops().argmax(lg, out)
+    assert out[0] == 77 and out[1] == 128255 and out[2] == 0
+    assert torch.equal(out[3:].long(), lg[3:].argmax(-1))
+    view = torch.randn(4, 700, device=DEV)[:, :301]                     # a row stride that is not the width
+    o4 = torch.empty(4, dtype=torch.int32, device=DEV)
+    ops().argmax(view, o4)
+    assert torch.equal(o4.long(), view.argmax(-1))
+
+
+@pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 1.0), (0.7, 0, 1.0), (0.7, 40, 1.0),
+                                                     (1.0, 0, 0.9), (1.3, 25, 0.6)])
+def test_sample_follows_the_reference_rule(temperature, top_k, top_p):
+    """The drawn token is the one whose interval of the running sum (index order, over the
+    kept tokens) holds u * kept mass; u comes from each row's own xorshift64 state."""
+    import numpy as np
+    import plain_llama as pl
+    n, vocab = 12, 3001
+    lg = 3 * torch.randn(n, vocab, device=DEV, generator=torch.Generator(device=DEV).manual_seed(11))
+    seeds = [0x9E3779B97F4A7C15 * (i + 1) % (1 << 63) for i in range(n)]
+    state = torch.tensor(seeds, dtype=torch.int64, device=DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    u = torch.empty(n, device=DEV)
+    ops().sample(lg, temperature, top_k, top_p, None, state, out, u)
+    for i in range(n):
+        x = seeds[i]
+        x ^= (x << 13) & 0xFFFFFFFFFFFFFFFF; x ^= x >> 7; x ^= (x << 17) & 0xFFFFFFFFFFFFFFFF
+        assert int(state[i]) & 0xFFFFFFFFFFFFFFFF == x                  # the state moved one step
+        assert abs(u[i].item() - (x >> 40) / 2 ** 24) < 1e-7
+        p = pl.sampling_distribution(lg[i].double().cpu().numpy(), temperature, top_k, top_p)
+        cdf = np.cumsum(p)
+        t = int(out[i])
+        assert p[t] > 0, "a token outside the kept set was drawn"
+        lo, hi = cdf[t] - p[t], cdf[t]
+        assert lo - 1e-4 <= u[i].item() <= hi + 1e-4
+    # the same states draw the same tokens whatever rows they share a launch with
+    state2 = torch.tensor(seeds[:3], dtype=torch.int64, device=DEV)
+    out2 = torch.empty(3, dtype=torch.int32, device=DEV)
+    ops().sample(lg[:3].contiguous(), temperature, top_k, top_p, None, state2, out2)
+    assert torch.equal(out2, out[:3])
+
+
+def test_sample_uses_slots_for_its_generator():
+    lg = torch.randn(2, 500, device=DEV)
+    state = torch.tensor([11, 22, 33, 44], dtype=torch.int64, device=DEV) * 0x2545F4914F6CDD1D % (1 << 62)
+    before = state.clone()
+    slots = torch.tensor([3, 1], dtype=torch.int32, device=DEV)
+    out = torch.empty(2, dtype=torch.int32, device=DEV)
+    ops().sample(lg, 1.0, 0, 1.0, slots, state, out)
+    assert state[0] == before[0] and state[2] == before[2]
+    assert state[1] != before[1] and state[3] != before[3]
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    from supersonic_b200.csrc.ops import KernelError
+    with pytest.raises(KernelError, match="CUDA"):
+        ops().swiglu(torch.zeros(2, 4), torch.zeros(2, 2))
+    with pytest.raises(KernelError, match="float32 or bfloat16"):
+        ops().gemm_nt_plain(torch.zeros(2, 4, device=DEV, dtype=torch.float16),
+                            torch.zeros(3, 4, device=DEV, dtype=torch.float16), torch.zeros(2, 3, device=DEV))
+    with pytest.raises(KernelError, match="head_dim"):
+        ops().attention_plain(torch.zeros(1, 1024, device=DEV), torch.zeros(1, 1, 64, 1024, device=DEV),
+                              torch.zeros(1, 1, 64, 1024, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                              torch.zeros(1, dtype=torch.int32, device=DEV),
+                              torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.zeros(1, 1024, device=DEV),
+                              1, 1, 1024, 6, None, 1.0)

@@ -1,0 +1,271 @@
+"""Each part alone against the plain implementation, the order of layers as data (a layer
+twice, a layer reading another layer's cache, a window), and a toy mixer with state of its
+own that is registered, built and stepped without touching the framework."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+import tiny_configs
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def build_ctx(dtype, store=None, max_positions=512):
+    from supersonic_b200.csrc.kernel_sets import kernel_set_for
+    from supersonic_b200.parts import BuildContext, WeightAccess
+    from supersonic_b200.weights import WeightStore
+    store = store or WeightStore.from_tensors({})
+    return BuildContext(torch.device(DEV), dtype, kernel_set_for(dtype), WeightAccess(store, DEV), max_positions)
+
+
+def step_ctx(build, cache, entries):
+    from supersonic_b200.engine import StepContext, pack_step
+    starts = [cache.length(e.slot) for e in entries]
+    batch = pack_step(entries, starts, DEV)
+    for e in entries:
+        cache.reserve(e.slot, len(e.tokens))
+    cache.sync()
+    return StepContext(batch, cache, build.kernels, build.dtype)
+
+
+def tolerance(dtype, scale=1.0):
+    return 2e-5 * max(scale, 1.0) if dtype == torch.float32 else 2e-2 * max(scale, 1.0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_embedding_head(dtype):
+    from supersonic_b200.parts import EMBEDDINGS, HEADS, NORMS
+    from supersonic_b200.weights import WeightStore
+    g = torch.Generator().manual_seed(0)
+    w = {"n": (1 + 0.1 * torch.randn(72, generator=g)).bfloat16(), "e": torch.randn(301, 72, generator=g).bfloat16()}
+    b = build_ctx(dtype, WeightStore.from_tensors(w))
+    norm = NORMS["rmsnorm"]({"size": 72, "eps": 2e-5}, {"weight": "n"}, b)
+    emb = EMBEDDINGS["embedding"]({"vocab_size": 301, "hidden_size": 72}, {"weight": "e"}, b)
+    head = HEADS["linear_head"]({"vocab_size": 301, "hidden_size": 72}, {"weight": "e"}, b)
+    assert head.weight.data_ptr() == emb.table.data_ptr()               # tied: one buffer
+    ctx = type("C", (), {"kernels": b.kernels})()
+    ids = torch.tensor([3, 300, 0, 3], dtype=torch.int32, device=DEV)
+    h = emb(ctx, ids)
+    wn, we = w["n"].double().numpy(), w["e"].double().numpy()
+    assert h.dtype == torch.float32 and np.allclose(h.cpu().numpy(), pl.embedding(ids.tolist(), we))
+    n = norm(ctx, h)
+    ref = pl.rms_norm(pl.embedding(ids.tolist(), we), wn, 2e-5)
+    assert n.dtype == dtype and np.abs(n.double().cpu().numpy() - ref).max() < tolerance(dtype, np.abs(ref).max())
+    rows = torch.tensor([2, 1], dtype=torch.int32, device=DEV)
+    logits = head(ctx, norm(ctx, h, rows=rows))
+    ref_l = ref[[2, 1]] @ we.T
+    assert logits.dtype == torch.float32 and tuple(logits.shape) == (2, 301)
+    assert np.abs(logits.double().cpu().numpy() - ref_l).max() < tolerance(dtype, np.abs(ref_l).max())
+
+
+def test_rotary_tables_match_plain():
+    from supersonic_b200.parts import POSITION_ENCODINGS
+    for cfg in (tiny_configs.A, tiny_configs.B, tiny_configs.C):
+        hd = cfg["head_dim"]
+        rot = POSITION_ENCODINGS["rotary"](
+            {"head_dim": hd, "rotary_dim": hd, "theta": cfg["rope_theta"], "max_positions": 400,
+             "scaling": cfg["rope_scaling"]}, {}, build_ctx(torch.float32))
+        cos, sin = pl.rope_tables(cfg, 400)
+        assert np.abs(rot.cos.double().cpu().numpy() - cos).max() < 1e-7
+        assert np.abs(rot.sin.double().cpu().numpy() - sin).max() < 1e-7
+
+
+def _layer_weights(cfg, seed, std=0.1):
+    from supersonic_b200.config import config_from_dict
+    from supersonic_b200.weights import random_store
+    c = config_from_dict(cfg)
+    return c, random_store(c, seed, std=std)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_mixer_feed_forward_and_block_alone(dtype, name):
+    """Layer 0's parts built by hand and run over a prompt, then token by token."""
+    from supersonic_b200.cache import SequenceCache
+    from supersonic_b200.engine import StepEntry
+    from supersonic_b200.parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS
+    cfg, seed, std = tiny_configs.CONFIGS[name]
+    c, store = _layer_weights(cfg, seed, std)
+    pw = {n: store.get(n).double().numpy() for n in store.names()}
+    spec = c.build_spec().blocks[0]
+    b = build_ctx(dtype, store)
+    mixer = MIXERS[spec.mixer.kind](spec.mixer.params, spec.mixer.weights, b)
+    ff = FEED_FORWARDS[spec.feed_forward.kind](spec.feed_forward.params, spec.feed_forward.weights, b)
+    n1 = NORMS["rmsnorm"](spec.mixer_norm.params, spec.mixer_norm.weights, b)
+    n2 = NORMS["rmsnorm"](spec.feed_forward_norm.params, spec.feed_forward_norm.weights, b)
+    pos = POSITION_ENCODINGS[spec.position.kind](spec.position.params, spec.position.weights, b)
+    cache = SequenceCache({0: mixer.cache_need()}, 512, 256, dtype, DEV)
+    T, H = 75, c.hidden_size
+    x = torch.randn(T, H, generator=torch.Generator().manual_seed(3))
+    xd = x.double().numpy()
+    cos, sin = pl.rope_tables(cfg, T)
+    ref_mix = pl.attention_mixer(xd, pw, "model.layers.0", cfg, cos, sin)
+    ref_ff = pl.swiglu_ffn(xd, pw, "model.layers.0")
+    ref_block = pl.block(xd, pw, 0, cfg, cos, sin)
+
+    # feed-forward alone
+    ctx = type("C", (), {"kernels": b.kernels})()
+    res = torch.zeros(T, H, device=DEV)
+    ff.forward(ctx, x.to(DEV, dtype), res)
+    xq = x.to(dtype).double().numpy()                 # the part sees activations already rounded
+    ref_ffq = pl.swiglu_ffn(xq, pw, "model.layers.0")
+    assert np.abs(res.double().cpu().numpy() - ref_ffq).max() < tolerance(dtype, np.abs(ref_ff).max())
+
+    # mixer alone: 70 tokens at once, then 5 one by one, against whole-sequence plain attention
+    slot = cache.acquire()
+    ref_mixq = pl.attention_mixer(xq, pw, "model.layers.0", cfg, cos, sin)
+    got = []
+    for lo, hi in [(0, 70)] + [(i, i + 1) for i in range(70, 75)]:
+        sc = step_ctx(b, cache, [StepEntry(slot, [0] * (hi - lo))])
+        res = torch.zeros(hi - lo, H, device=DEV)
+        mixer.forward(sc, x[lo:hi].to(DEV, dtype), res, 0, True, pos)
+        cache.advance(slot, hi - lo)
+        got.append(res)
+    got = torch.cat(got).double().cpu().numpy()
+    assert np.abs(got - ref_mixq).max() < tolerance(dtype, np.abs(ref_mix).max())
+    cache.release(slot)
+
+    # the block arrangement
+    block = BLOCKS[spec.kind](mixer, ff, n1, n2, pos)
+    slot = cache.acquire()
+    res = x.to(DEV).clone()
+    sc = step_ctx(b, cache, [StepEntry(slot, [0] * T)])
+    block.forward(sc, res, 0, True)
+    assert np.abs(res.double().cpu().numpy() - ref_block).max() < tolerance(dtype, np.abs(ref_block).max())
+
+
+def _spec_with(cfg, schedule=None, window=None):
+    from dataclasses import replace
+    from supersonic_b200.config import config_from_dict
+    from supersonic_b200.config.base import PartSpec
+    spec = config_from_dict(cfg).build_spec()
+    blocks = list(spec.blocks)
+    if window is not None:
+        for i, w in window.items():
+            m = blocks[i].mixer
+            blocks[i] = replace(blocks[i], mixer=PartSpec(m.kind, {**m.params, "window": w}, m.weights))
+    return replace(spec, blocks=blocks, schedule=schedule or spec.schedule)
+
+
+def _plain_forward_scheduled(cfg, pw, tokens, schedule, window=None):
+    """The plain parts run in the order a schedule gives; a stop that does not write a cache
+    attends with its own queries over the keys and values of the stop that wrote it."""
+    T = len(tokens)
+    cos, sin = pl.rope_tables(cfg, T)
+    nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    h = pl.embedding(tokens, pw["model.embed_tokens.weight"])
+    kv = {}
+    for layer, cache, writes in schedule:
+        p = f"model.layers.{layer}"
+        x = pl.rms_norm(h, pw[f"{p}.input_layernorm.weight"], cfg["rms_norm_eps"])
+        q = pl.apply_rope((x @ pw[f"{p}.self_attn.q_proj.weight"].T).reshape(T, nq, hd), cos, sin)
+        if writes:
+            k = pl.apply_rope((x @ pw[f"{p}.self_attn.k_proj.weight"].T).reshape(T, nkv, hd), cos, sin)
+            kv[cache] = (k, (x @ pw[f"{p}.self_attn.v_proj.weight"].T).reshape(T, nkv, hd))
+        k, v = kv[cache]
+        a = pl.attention_scores(q, k, v, 1 / math.sqrt(hd), (window or {}).get(layer)).reshape(T, nq * hd)
+        h = h + a @ pw[f"{p}.self_attn.o_proj.weight"].T
+        h = h + pl.swiglu_ffn(pl.rms_norm(h, pw[f"{p}.post_attention_layernorm.weight"], cfg["rms_norm_eps"]), pw, p)
+    return pl.output_head(h, pw, cfg)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_order_of_layers_is_data(dtype, model_folders):
+    """Layer 1 twice (each time with a cache entry of its own), layer 0 reading the cache that
+    layer 2 wrote, and a window on layer 1: whole prompt, then token by token."""
+    from supersonic_b200.config.base import ScheduleEntry
+    from supersonic_b200.engine import Model, StepEntry
+    from supersonic_b200.weights import WeightStore
+    d, pc, pw = model_folders["B"]
+    order = [(0, 0, True), (1, 1, True), (2, 2, True), (2, 2, False), (1, 3, True)]
+    window = {1: 9}
+    # layer 2 reads its own cache a second time without writing: the same need by construction
+    spec = _spec_with(tiny_configs.B, [ScheduleEntry(l, c, w) for l, c, w in order], window)
+    m = Model(spec, WeightStore.from_dir(d), dtype=dtype, device=DEV, max_tokens=256)
+    assert len(m.cache.kv_groups) == 2                                   # full and windowed storage
+    toks = np.random.default_rng(5).integers(0, 384, 90).tolist()
+    ref = _plain_forward_scheduled(pc, pw, toks, order, window)
+    s = m.open_sequence()
+    got = [m.step([StepEntry(s, toks[:80], range(80))])]
+    got += [m.step([StepEntry(s, [toks[p]], [0])]) for p in range(80, 90)]
+    got = torch.cat(got).double().cpu().numpy()
+    tol = 2e-5 if dtype == "float32" else 2e-2 * np.abs(ref).max()
+    assert np.abs(got - ref).max() < tol
+    m.cache.check()
+    win = next(g for g in m.cache.kv_groups if g.need.window)
+    assert len(win.held[s]) == 1 and min(win.held[s]) == 1              # the window group dropped page 0
+
+
+def test_toy_mixer_with_its_own_state(model_folders):
+    """A mixer defined here, with a fixed-size state per sequence instead of keys and values,
+    is registered, built into a model and stepped: nothing in the framework's files changes."""
+    from dataclasses import replace
+    from supersonic_b200.cache import StateNeed
+    from supersonic_b200.config.base import PartSpec
+    from supersonic_b200.engine import Model, StepEntry
+    from supersonic_b200.parts import register_mixer
+    from supersonic_b200.weights import WeightStore
+
+    @register_mixer("toy_decay")
+    class ToyDecay:
+        """s <- decay * s + x_t ; out_t = s W^T.  State: one float32 vector per sequence."""
+
+        def __init__(self, params, weights, build):
+            self.hidden, self.decay = params["hidden_size"], params["decay"]
+            self.w = build.weights.as_dtype(weights["w"], torch.float32)
+
+        def cache_need(self):
+            return StateNeed(self.hidden)
+
+        def forward(self, ctx, x, residual, cache_id, writes_cache, position):
+            state = ctx.cache.state(cache_id)
+            b, row = ctx.batch, 0
+            for slot, n in zip(b.host_slots, b.host_counts):
+                s = state[slot]
+                for t in range(row, row + n):
+                    s = self.decay * s + x[t].float()
+                    residual[t] += s @ self.w.T
+                state[slot] = s
+                row += n
+
+    d, pc, pw = model_folders["A"]
+    spec = _spec_with(tiny_configs.A)
+    toy = PartSpec("toy_decay", {"hidden_size": 64, "decay": 0.5}, {"w": "model.layers.1.self_attn.o_proj.weight"})
+    spec = replace(spec, blocks=[spec.blocks[0], replace(spec.blocks[1], mixer=toy, position=None)])
+    m = Model(spec, WeightStore.from_dir(d), dtype="float32", device=DEV, max_tokens=256)
+    assert len(m.cache.kv_groups) == 1 and tuple(m.cache.state(1).shape)[1] == 64
+
+    def plain(tokens):
+        T = len(tokens)
+        cos, sin = pl.rope_tables(pc, T)
+        h = pl.block(pl.embedding(tokens, pw["model.embed_tokens.weight"]), pw, 0, pc, cos, sin)
+        x = pl.rms_norm(h, pw["model.layers.1.input_layernorm.weight"], pc["rms_norm_eps"])
+        s, outs = np.zeros(64), []
+        for t in range(T):
+            s = 0.5 * s + x[t]
+            outs.append(s @ pw["model.layers.1.self_attn.o_proj.weight"].T)
+        h = h + np.stack(outs)
+        h = h + pl.swiglu_ffn(pl.rms_norm(h, pw["model.layers.1.post_attention_layernorm.weight"],
+                                          pc["rms_norm_eps"]), pw, "model.layers.1")
+        return pl.output_head(h, pw, pc)
+
+    rng = np.random.default_rng(6)
+    a, b = rng.integers(0, 256, 20).tolist(), rng.integers(0, 256, 9).tolist()
+    sa, sb = m.open_sequence(), m.open_sequence()
+    got = m.step([StepEntry(sa, a[:15], range(15)), StepEntry(sb, b[:4], range(4))])
+    ga, gb = [got[:15]], [got[15:]]
+    for i in range(5):
+        got = m.step([StepEntry(sa, [a[15 + i]], [0]), StepEntry(sb, [b[4 + i]], [0])])
+        ga.append(got[:1]); gb.append(got[1:])
+    assert np.abs(torch.cat(ga).double().cpu().numpy() - plain(a)).max() < 2e-5
+    assert np.abs(torch.cat(gb).double().cpu().numpy() - plain(b)).max() < 2e-5
+    # a slot that is used again starts from a zeroed state
+    m.close_sequence(sa)
+    sc = m.open_sequence()
+    assert sc == sa
+    got = m.step([StepEntry(sc, b, range(9))])
+    assert np.abs(got.double().cpu().numpy() - plain(b)).max() < 2e-5

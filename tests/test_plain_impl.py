@@ -1,0 +1,95 @@
+"""The plain implementation checked against properties that hold by definition, and
+against the small golden file (CPU)."""
+import importlib.util
+import math
+import os
+
+import numpy as np
+
+import plain_llama as pl
+import tiny_configs
+
+
+def test_rope_frequencies_llama3_by_hand():
+    cfg = tiny_configs.B                      # theta 5e5, hd 32, factor 8, low 1, high 4, original 16
+    inv = pl.rope_inv_freq(cfg)
+    base = 1.0 / 500000.0 ** (np.arange(16) * 2 / 32)
+    wavelen = 2 * math.pi / base
+    c_inv = pl.rope_inv_freq(tiny_configs.C)  # theta 1e6, hd 48, factor 4, low 1, high 2, original 32
+    c_base = 1.0 / 1000000.0 ** (np.arange(24) * 2 / 48)
+    assert 2 * math.pi / c_base[0] < 16.0 and np.isclose(c_inv[0], c_base[0])     # short waves untouched
+    assert np.isclose(c_inv[-1], c_base[-1] / 4.0)
+    assert wavelen[-1] > 16.0 and np.isclose(inv[-1], base[-1] / 8.0)      # long waves divided by factor
+    mid = [i for i in range(16) if 4.0 <= wavelen[i] <= 16.0]
+    assert mid, "the configuration must exercise the blended band"
+    for i in mid:
+        s = (16.0 / wavelen[i] - 1.0) / 3.0
+        assert np.isclose(inv[i], (1 - s) * base[i] / 8.0 + s * base[i])
+    assert np.allclose(pl.rope_inv_freq(tiny_configs.A), 1.0 / 10000.0 ** (np.arange(8) * 2 / 16))
+
+
+def test_rope_is_a_rotation_of_half_split_pairs():
+    cos, sin = pl.rope_tables(tiny_configs.A, 9)
+    x = np.random.default_rng(0).normal(size=(9, 3, 16))
+    y = pl.apply_rope(x, cos, sin)
+    assert np.allclose((x ** 2).sum(-1), (y ** 2).sum(-1))
+    assert np.allclose(y[0], x[0])                                          # position 0: identity
+    t, i = 5, 3
+    c, s = cos[t, i], sin[t, i]
+    assert np.isclose(y[t, 1, i], x[t, 1, i] * c - x[t, 1, i + 8] * s)
+    assert np.isclose(y[t, 1, i + 8], x[t, 1, i] * s + x[t, 1, i + 8] * c)
+
+
+def test_rms_norm_and_swiglu_by_hand():
+    x = np.array([[3.0, 4.0]])
+    assert np.allclose(pl.rms_norm(x, np.array([2.0, 0.5]), 0.0), [[2 * 3 / math.sqrt(12.5), 0.5 * 4 / math.sqrt(12.5)]])
+    w = {"p.mlp.gate_proj.weight": np.array([[1.0], [0.0]]), "p.mlp.up_proj.weight": np.array([[2.0], [5.0]]),
+         "p.mlp.down_proj.weight": np.array([[1.0, 1.0]])}
+    g = 0.7
+    assert np.allclose(pl.swiglu_ffn(np.array([[g]]), w, "p"), g / (1 + math.exp(-g)) * 2 * g)
+
+
+def test_attention_is_causal_grouped_and_windowed():
+    rng = np.random.default_rng(1)
+    q, k, v = rng.normal(size=(6, 4, 8)), rng.normal(size=(6, 2, 8)), rng.normal(size=(6, 2, 8))
+    out = pl.attention_scores(q, k, v, 0.5)
+    assert np.allclose(out[0, 0], v[0, 0]) and np.allclose(out[0, 3], v[0, 1])       # heads 0,1 -> kv 0; 2,3 -> kv 1
+    k2, v2 = k.copy(), v.copy()
+    k2[4:], v2[4:] = 9.0, -9.0
+    assert np.allclose(pl.attention_scores(q, k2, v2, 0.5)[:4], out[:4])             # no look-ahead
+    s = (q[5, 1] @ k[:, 0].T) * 0.5
+    p = np.exp(s - s.max()); p /= p.sum()
+    assert np.allclose(out[5, 1], p @ v[:, 0])
+    w = pl.attention_scores(q, k, v, 0.5, window=2)
+    s2 = s[4:]; p2 = np.exp(s2 - s2.max()); p2 /= p2.sum()
+    assert np.allclose(w[5, 1], p2 @ v[4:, 0]) and np.allclose(w[0], out[0])
+
+
+def test_logits_do_not_depend_on_later_tokens(model_folders):
+    d, pc, pw = model_folders["A"]
+    a = pl.forward(pc, pw, [1, 2, 3, 4, 5, 6])
+    b = pl.forward(pc, pw, [1, 2, 3, 4, 200, 100])
+    assert np.allclose(a[:4], b[:4]) and not np.allclose(a[4], b[4])
+    assert a.shape == (6, pc["vocab_size"])
+
+
+def test_sampling_distribution():
+    logits = np.log(np.array([0.5, 0.2, 0.2, 0.1]))
+    assert np.allclose(pl.sampling_distribution(logits, 1.0), [0.5, 0.2, 0.2, 0.1])
+    assert np.allclose(pl.sampling_distribution(logits, 1.0, top_k=1), [1, 0, 0, 0])
+    assert np.allclose(pl.sampling_distribution(logits, 1.0, top_k=2), [5 / 9, 2 / 9, 2 / 9, 0])   # ties kept
+    assert np.allclose(pl.sampling_distribution(logits, 1.0, top_p=0.6), [5 / 9, 2 / 9, 2 / 9, 0])
+    assert np.allclose(pl.sampling_distribution(logits, 1.0, top_p=0.5), [1, 0, 0, 0])
+    p = pl.sampling_distribution(logits, 0.5)
+    assert np.allclose(p, np.array([0.25, 0.04, 0.04, 0.01]) / 0.34)
+    assert pl.greedy_token([1.0, 3.0, 3.0, 2.0]) == 1
+
+
+def test_golden_file():
+    here = os.path.dirname(os.path.abspath(__file__))
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(here, "golden", "make_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    gold = np.load(os.path.join(here, "golden", "plain_logits.npz"))
+    assert gold["tokens"].tolist() == mod.TOKENS
+    assert np.allclose(mod.compute()[:, :48], gold["logits"], atol=1e-6)

@@ -1,0 +1,101 @@
+"""bin/trace_run on the GPU against the plain implementation, in float32 and bfloat16:
+each request alone and whole; its last 32 tokens one by one; batches of unequal lengths
+whose shorter requests end earlier, one batch after another so that slots and pages are
+used again."""
+import numpy as np
+import pytest
+
+import plain_llama as pl
+import replay_helpers as rh
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"r0": 1, "r1": 7, "r2": 19, "r3": 40, "r4": 70, "r5": 33, "r6": 131, "r7": 64, "r8": 65}
+GROUPS = [["r0", "r1", "r2", "r3"], ["r4", "r5", "r8"], ["r6", "r7"]]
+F32_ATOL = 2e-5            # float32 accumulation on logits of order one
+BF16_REL = 2e-2            # a few bfloat16 roundings (2^-8 each) of logits' own scale
+
+
+def make_requests(vocab, seed):
+    rng = np.random.default_rng(seed)
+    return {rid: rng.integers(0, vocab, n).tolist() for rid, n in LENGTHS.items()}
+
+
+def build_trace(requests):
+    t = rh.Trace()
+    rh.whole(t, requests)
+    rh.tail_one_by_one(t, requests)
+    rh.batches(t, requests, GROUPS, prompt_of=lambda rid, n: max(1, n // 2))
+    return t
+
+
+@pytest.fixture(scope="module")
+def replayed(model_folders, tmp_path_factory):
+    cache = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in cache:
+            d, pc, pw = model_folders[name]
+            requests = make_requests(pc["vocab_size"], seed=len(name) + 11)
+            trace = build_trace(requests)
+            # no more room than the largest batch needs: later batches must reuse pages
+            out = rh.run_trace(d, dtype, trace, str(tmp_path_factory.mktemp(f"out-{name}-{dtype}")),
+                               vocab=pc["vocab_size"])
+            ref = {rid: pl.forward(pc, pw, toks) for rid, toks in requests.items()}
+            cache[(name, dtype)] = (requests, out, ref)
+        return cache[(name, dtype)]
+    return get
+
+
+def worst(requests, out, ref, tag):
+    """Largest error over all positions, as (error / allowed scale, request, position)."""
+    rows = []
+    for rid, toks in requests.items():
+        scale = np.abs(ref[rid]).max()
+        for p in range(len(toks)):
+            err = np.abs(out[(f"{tag}{rid}", p)].astype(np.float64) - ref[rid][p]).max()
+            rows.append((err, err / scale, rid, p))
+    return max(rows)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("tag,what", [("w", "alone and whole"), ("t", "last 32 one by one"),
+                                      ("b", "unequal batches, slots reused")])
+def test_float32_matches_plain(replayed, name, tag, what):
+    requests, out, ref = replayed(name, "float32")
+    err, _, rid, p = worst(requests, out, ref, tag)
+    assert err < F32_ATOL, f"{what}: first look at request {rid} position {p} (error {err:.3e})"
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("tag,what", [("w", "alone and whole"), ("t", "last 32 one by one"),
+                                      ("b", "unequal batches, slots reused")])
+def test_bfloat16_matches_plain(replayed, name, tag, what):
+    requests, out, ref = replayed(name, "bfloat16")
+    _, rel, rid, p = worst(requests, out, ref, tag)
+    assert rel < BF16_REL, f"{what}: first look at request {rid} position {p} (relative error {rel:.3e})"
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_float32_does_not_depend_on_how_tokens_are_cut(replayed, name):
+    requests, out, _ = replayed(name, "float32")
+    for rid, toks in requests.items():
+        for p in range(len(toks)):
+            w = out[(f"w{rid}", p)]
+            for tag in ("t", "b"):
+                assert np.abs(out[(f"{tag}{rid}", p)] - w).max() < F32_ATOL, (rid, p, tag)
+
+
+def test_greedy_continuation_agrees(replayed, model_folders):
+    """The argmax of the replayed logits is the plain implementation's next token wherever
+    the plain top two are further apart than the tolerance."""
+    for name in ("A", "B", "C"):
+        requests, out, ref = replayed(name, "bfloat16")
+        checked = 0
+        for rid, toks in requests.items():
+            for p in range(len(toks)):
+                top2 = np.sort(ref[rid][p])[-2:]
+                if top2[1] - top2[0] > 2 * BF16_REL * np.abs(ref[rid]).max():
+                    assert int(out[(f"b{rid}", p)].argmax()) == int(ref[rid][p].argmax())
+                    checked += 1
+        assert checked > 50
