@@ -114,7 +114,8 @@ def test_rope_append(dtype, n_q, n_kv, hd, rot):
     for t in range(T):
         if int(slot[t]) >= 0:
             touched[int(table[int(slot[t]), int(pos[t]) // 64]), int(pos[t]) % 64] = True
-    assert torch.equal(k[~touched], k0[~touched]) and torch.equal(v[~touched], v0[~touched])
+    kt, k0t, vt, v0t = (x.transpose(1, 2) for x in (k, k0, v, v0))         # [page, token, head, dim]
+    assert torch.equal(kt[~touched], k0t[~touched]) and torch.equal(vt[~touched], v0t[~touched])
 
 
 def _attention_reference(q, k, v, pos, slot, table, n_q, n_kv, hd, window, scale):
