@@ -33,6 +33,7 @@ BASE_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-shared"
 LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "plain_ops": {"sources": ["plain_ops.cu"], "flags": [], "link": []},
     "sampling": {"sources": ["sampling.cu"], "flags": [], "link": []},
+    "decode_ops": {"sources": ["decode_ops.cu"], "flags": [], "link": []},
 }
 HEADERS = ["common.cuh"]
 

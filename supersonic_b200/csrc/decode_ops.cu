@@ -1,0 +1,484 @@
+// Decode kernels for sm_100a: bandwidth-bound work for a handful of tokens per step.
+//
+//   ssb_skinny_gemm       out[b, n] = sum_k x[b, k] W[n, k] for b <= 64 rows, bfloat16 in, float32
+//                         accumulation on the tensor cores; optional RMSNorm of a float32 input on
+//                         the way in; epilogues: store, add into the float32 residual, SwiGLU.
+//                         Replaces the reference's cuBLAS GemmEx GEMV per projection
+//                         (kernels/full_attention_bridge_4b_cuda.cu:4768-4813) and its separate
+//                         rms_norm / swiglu / add kernels (full_attention_cuda.cuh:2826-2873,
+//                         1995-2010; prefill_helpers_cuda.cuh:60-70).
+//   ssb_attention_decode  one query token per sequence over its paged keys and values, all query
+//                         heads of a kv head together, the keys split over several blocks whose
+//                         partial results the last block to finish merges.  Replaces
+//                         supersonic_qwen35_full_attention_decode_*_kernel, one warp per query
+//                         head and two passes over the keys (full_attention_cuda.cuh:476-679).
+//
+// Softmax statistics, norms and all sums are float32.  No float atomics: every output element
+// is produced by one thread in a fixed order, so results do not depend on scheduling.
+#include "common.cuh"
+#include <math.h>
+
+typedef __nv_bfloat16 bf16;
+
+// ---------------------------------------------------------------------------------------
+// skinny GEMM
+// ---------------------------------------------------------------------------------------
+// A block owns 16*RM rows of W over all of K.  Its 8 warps take 32-wide chunks of K in turn;
+// a lane loads 16 bytes (8 consecutive k) of two W rows per 16-row tile and 16 bytes of one x
+// row per 8-row batch tile, and feeds them to mma.m16n8k16 with a k order permuted the same
+// way on both sides (a dot product does not care).  Warps' partial sums meet in shared memory.
+constexpr int SG_WARPS = 8;
+constexpr int SG_THREADS = SG_WARPS * 32;
+// chunks whose loads are issued before any is used: fewer for wide batches (registers)
+__host__ __device__ constexpr int sg_unroll(int nb) { return nb >= 4 ? 1 : (nb == 2 ? 2 : 4); }
+
+enum { SG_STORE = 0, SG_ACCUMULATE = 1, SG_SWIGLU = 2 };
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2,
+                                               unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+                 "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+template <int RM, int NB, bool NORM>
+__global__ void __launch_bounds__(SG_THREADS)
+skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restrict__ norm_w,
+                   int norm_w_is_f32, float eps, const bf16* __restrict__ W, int ldw,
+                   void* __restrict__ out, int ldo, int out_is_f32, int n_rows, int N, int K, int mode) {
+    extern __shared__ float smem[];
+    constexpr int ROWS = 16 * RM, COLS = 8 * NB, SG_UNROLL = sg_unroll(NB);
+    float* red = smem;                                  // [SG_WARPS][ROWS][COLS]
+    float* inv_rms = smem + SG_WARPS * ROWS * COLS;     // [COLS] (NORM only)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * ROWS;
+
+    if (NORM) {
+        // 1 / rms of each input row, float32, fixed order: warp w sums rows w, w + 8, ...
+        const float* xf = (const float*)x_in;
+        for (int b = warp; b < COLS; b += SG_WARPS) {
+            float s = 0.f;
+            if (b < n_rows)
+                for (int k = lane * 4; k < K; k += 128) {
+                    const float4 v = *reinterpret_cast<const float4*>(xf + (size_t)b * ldx + k);
+                    s = fmaf(v.x, v.x, s); s = fmaf(v.y, v.y, s); s = fmaf(v.z, v.z, s); s = fmaf(v.w, v.w, s);
+                }
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (lane == 0) inv_rms[b] = 1.0f / sqrtf(s / (float)K + eps);
+        }
+        __syncthreads();
+    }
+
+    float acc[RM][NB][4];
+#pragma unroll
+    for (int i = 0; i < RM; ++i)
+#pragma unroll
+        for (int j = 0; j < NB; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+
+    // rows this lane loads (clamped: rows past N are computed but never stored)
+    const bf16* w_row[RM][2];
+#pragma unroll
+    for (int i = 0; i < RM; ++i) {
+        w_row[i][0] = W + (size_t)min(n0 + i * 16 + g, N - 1) * ldw;
+        w_row[i][1] = W + (size_t)min(n0 + i * 16 + g + 8, N - 1) * ldw;
+    }
+    float my_inv[NB];
+    if (NORM) {
+#pragma unroll
+        for (int j = 0; j < NB; ++j) my_inv[j] = inv_rms[j * 8 + g];
+    }
+
+    const int n_chunks = (K + 31) / 32;
+    for (int c0 = warp; c0 < n_chunks; c0 += SG_WARPS * SG_UNROLL) {
+        uint4 wa[SG_UNROLL][RM][2];
+        uint4 xb[SG_UNROLL][NB];
+#pragma unroll
+        for (int u = 0; u < SG_UNROLL; ++u) {
+            const int k = (c0 + u * SG_WARPS) * 32 + t * 8;
+            const bool live = k < K;                     // K is a multiple of 8: all 8 or none
+#pragma unroll
+            for (int i = 0; i < RM; ++i) {
+                wa[u][i][0] = live ? ldg_stream(w_row[i][0] + k) : make_uint4(0, 0, 0, 0);
+                wa[u][i][1] = live ? ldg_stream(w_row[i][1] + k) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                const int b = j * 8 + g;
+                if (!live || b >= n_rows) {
+                    xb[u][j] = make_uint4(0, 0, 0, 0);
+                } else if (NORM) {
+                    const float* xp = (const float*)x_in + (size_t)b * ldx + k;
+                    const float4 v0 = *reinterpret_cast<const float4*>(xp);
+                    const float4 v1 = *reinterpret_cast<const float4*>(xp + 4);
+                    float w[8];
+                    if (norm_w_is_f32) {
+                        const float4 w0 = *reinterpret_cast<const float4*>((const float*)norm_w + k);
+                        const float4 w1 = *reinterpret_cast<const float4*>((const float*)norm_w + k + 4);
+                        w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w;
+                        w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
+                    } else {
+                        const uint4 wq = *reinterpret_cast<const uint4*>((const bf16*)norm_w + k);
+                        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wq);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = __bfloat1622float2(wp[e]);
+                            w[2 * e] = f.x; w[2 * e + 1] = f.y;
+                        }
+                    }
+                    const float s = my_inv[j];
+                    xb[u][j].x = pack_bf16(v0.x * s * w[0], v0.y * s * w[1]);
+                    xb[u][j].y = pack_bf16(v0.z * s * w[2], v0.w * s * w[3]);
+                    xb[u][j].z = pack_bf16(v1.x * s * w[4], v1.y * s * w[5]);
+                    xb[u][j].w = pack_bf16(v1.z * s * w[6], v1.w * s * w[7]);
+                } else {
+                    xb[u][j] = *reinterpret_cast<const uint4*>((const bf16*)x_in + (size_t)b * ldx + k);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < SG_UNROLL; ++u)
+#pragma unroll
+            for (int i = 0; i < RM; ++i)
+#pragma unroll
+                for (int j = 0; j < NB; ++j) {
+                    mma_bf16_16816(acc[i][j], wa[u][i][0].x, wa[u][i][1].x, wa[u][i][0].y, wa[u][i][1].y,
+                                   xb[u][j].x, xb[u][j].y);
+                    mma_bf16_16816(acc[i][j], wa[u][i][0].z, wa[u][i][1].z, wa[u][i][0].w, wa[u][i][1].w,
+                                   xb[u][j].z, xb[u][j].w);
+                }
+    }
+
+    // partial sums of the 8 warps meet in shared memory: red[warp][row][col]
+#pragma unroll
+    for (int i = 0; i < RM; ++i)
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            float* r = red + ((size_t)warp * ROWS + i * 16) * COLS + j * 8;
+            r[(g) * COLS + 2 * t] = acc[i][j][0];
+            r[(g) * COLS + 2 * t + 1] = acc[i][j][1];
+            r[(g + 8) * COLS + 2 * t] = acc[i][j][2];
+            r[(g + 8) * COLS + 2 * t + 1] = acc[i][j][3];
+        }
+    __syncthreads();
+
+    if (mode == SG_SWIGLU) {
+        // rows come as [8 gate | 8 up] per 16: out[b, n0/2 + j] = silu(gate_j) * up_j
+        for (int e = threadIdx.x; e < (ROWS / 2) * COLS; e += SG_THREADS) {
+            const int j = e % (ROWS / 2), b = e / (ROWS / 2);
+            const int r_gate = (j / 8) * 16 + (j % 8), n_out = n0 / 2 + j;
+            if (b >= n_rows || n0 + r_gate + 8 >= N) continue;
+            float gate = 0.f, up = 0.f;
+#pragma unroll
+            for (int w = 0; w < SG_WARPS; ++w) {
+                gate += red[((size_t)w * ROWS + r_gate) * COLS + b];
+                up += red[((size_t)w * ROWS + r_gate + 8) * COLS + b];
+            }
+            ((bf16*)out)[(size_t)b * ldo + n_out] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+        }
+        return;
+    }
+    for (int e = threadIdx.x; e < ROWS * COLS; e += SG_THREADS) {
+        const int r = e % ROWS, b = e / ROWS;
+        const int n = n0 + r;
+        if (b >= n_rows || n >= N) continue;
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < SG_WARPS; ++w) s += red[((size_t)w * ROWS + r) * COLS + b];
+        const size_t o = (size_t)b * ldo + n;
+        if (mode == SG_ACCUMULATE) ((float*)out)[o] += s;
+        else if (out_is_f32) ((float*)out)[o] = s;
+        else ((bf16*)out)[o] = __float2bfloat16_rn(s);
+    }
+}
+
+template <int RM, int NB, bool NORM>
+static int launch_skinny(const void* x, int ldx, const void* norm_w, int norm_w_is_f32, float eps,
+                         const bf16* W, int ldw, void* out, int ldo, int out_is_f32, int n_rows, int N,
+                         int K, int mode, cudaStream_t stream) {
+    constexpr int ROWS = 16 * RM, COLS = 8 * NB;
+    const size_t smem = (size_t)(SG_WARPS * ROWS * COLS + COLS) * sizeof(float);
+    auto kern = skinny_gemm_kernel<RM, NB, NORM>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    kern<<<(N + ROWS - 1) / ROWS, SG_THREADS, smem, stream>>>(x, ldx, norm_w, norm_w_is_f32, eps, W, ldw,
+                                                            out, ldo, out_is_f32, n_rows, N, K, mode);
+    return ssb_launch_status();
+}
+
+// x: bfloat16 [n_rows, K] (norm_w == null) or the float32 residual [n_rows, K] normalised on the
+// way in with norm_w (bfloat16 or float32) and eps.  W: bfloat16 [N, K].  mode 0: out[b, n]
+// (bfloat16 or float32); mode 1: out (float32) += ; mode 2: W's rows come as [8 gate | 8 up] per
+// 16 and out (bfloat16, [n_rows, N/2]) = silu(gate) * up.
+SSB_API int ssb_skinny_gemm(const void* x, int ldx, const void* norm_w, int norm_w_dtype, float eps,
+                            const void* W, int ldw, void* out, int ldo, int out_dtype, int n_rows, int N,
+                            int K, int mode, cudaStream_t stream) {
+    if (n_rows <= 0 || N <= 0) return 0;
+    if (n_rows > 64 || K <= 0 || K % 8 || ldw % 8 || ldx % 8) return SSB_ERR_BAD_SIZE;
+    if (((uintptr_t)x | (uintptr_t)W | (uintptr_t)norm_w) & 15) return SSB_ERR_BAD_SIZE;
+    if (mode == SG_ACCUMULATE && out_dtype != SSB_F32) return SSB_ERR_BAD_DTYPE;
+    if (mode == SG_SWIGLU && (out_dtype != SSB_BF16 || N % 16)) return SSB_ERR_BAD_SIZE;
+    const int f32o = out_dtype == SSB_F32, nwf = norm_w_dtype == SSB_F32;
+    const bf16* Wb = (const bf16*)W;
+#define SSB_SG(RM, NB) \
+    return norm_w ? launch_skinny<RM, NB, true>(x, ldx, norm_w, nwf, eps, Wb, ldw, out, ldo, f32o, n_rows, N, K, mode, stream) \
+                  : launch_skinny<RM, NB, false>(x, ldx, nullptr, 0, 0.f, Wb, ldw, out, ldo, f32o, n_rows, N, K, mode, stream)
+    if (n_rows <= 8) { SSB_SG(1, 1); }
+    if (n_rows <= 16) { SSB_SG(2, 2); }
+    if (n_rows <= 32) { SSB_SG(2, 4); }
+    SSB_SG(2, 8);
+#undef SSB_SG
+}
+
+// ---------------------------------------------------------------------------------------
+// decode attention, keys split over blocks
+// ---------------------------------------------------------------------------------------
+// Grid (sequence, kv head x query-head group, split).  A block's 4 warps walk the split's keys,
+// a warp per key; a lane owns VEC consecutive elements of the head dimension, so a key or value
+// row is one coalesced load per warp.  Up to AD_GROUP query heads share each key and value.
+// Partial (max, sum, weighted values) go to scratch; the block that finishes last for a
+// (sequence, head group) merges the splits in index order and writes the output.
+constexpr int AD_WARPS = 4;
+constexpr int AD_THREADS = AD_WARPS * 32;
+constexpr int AD_GROUP = 4;
+constexpr int AD_MAX_VEC = 8;
+
+template <int VEC>
+__device__ __forceinline__ void load_row(const bf16* p, int lane, int head_dim, float (&v)[VEC]) {
+    const int d = lane * VEC;
+    if (d + VEC <= head_dim) {
+        if (VEC == 8) {
+            const uint4 q = *reinterpret_cast<const uint4*>(p + d);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+        } else if (VEC == 4) {
+            const uint2 q = *reinterpret_cast<const uint2*>(p + d);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) { const float2 f = __bfloat1622float2(h[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+        } else if (VEC == 2) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + d));
+            v[0] = f.x; v[1] = f.y;
+        } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] = __bfloat162float(p[d + e]);
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) v[e] = (d + e < head_dim) ? __bfloat162float(p[d + e]) : 0.f;
+    }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(AD_THREADS)
+attention_decode_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ k_cache,
+                        const bf16* __restrict__ v_cache, const int* __restrict__ pos,
+                        const int* __restrict__ slot, const int* __restrict__ page_table, int max_pages,
+                        bf16* __restrict__ out, int ldo, int n_q, int n_kv, int head_dim, int page_shift,
+                        int window, float scale, int n_splits, float* __restrict__ scratch,
+                        int* __restrict__ counters) {
+    __shared__ float sm_m[AD_WARPS][AD_GROUP], sm_l[AD_WARPS][AD_GROUP];
+    __shared__ float sm_acc[AD_WARPS][AD_GROUP][32 * AD_MAX_VEC];
+    __shared__ int is_last;
+    const int b = blockIdx.x, split = blockIdx.z;
+    const int group = n_q / n_kv;
+    const int groups_per_kv = (group + AD_GROUP - 1) / AD_GROUP;
+    const int kvh = blockIdx.y / groups_per_kv, sub = blockIdx.y % groups_per_kv;
+    const int h0 = kvh * group + sub * AD_GROUP;                 // first query head of this block
+    const int n_heads = min(AD_GROUP, group - sub * AD_GROUP);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int s = slot[b];
+    if (s < 0) {                                                 // padding row: zeros, no bookkeeping
+        if (split == 0)
+            for (int e = threadIdx.x; e < n_heads * head_dim; e += AD_THREADS)
+                out[(size_t)b * ldo + (size_t)h0 * head_dim + e] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int p = pos[b];
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    // this split's keys: whole pages, split evenly
+    const int page_lo = lo >> page_shift, page_hi = p >> page_shift;
+    const int n_pages = page_hi - page_lo + 1;
+    const int per = (n_pages + n_splits - 1) / n_splits;
+    const int my_lo = max(lo, (page_lo + split * per) << page_shift);
+    const int my_hi = min(p, ((page_lo + (split + 1) * per) << page_shift) - 1);
+
+    float qv[AD_GROUP][VEC];
+#pragma unroll
+    for (int gi = 0; gi < AD_GROUP; ++gi) {
+        if (gi < n_heads) {
+            load_row<VEC>(q + (size_t)b * ldq + (size_t)(h0 + gi) * head_dim, lane, head_dim, qv[gi]);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) qv[gi][e] *= scale;
+        } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) qv[gi][e] = 0.f;
+        }
+    }
+    float m[AD_GROUP], l[AD_GROUP], acc[AD_GROUP][VEC];
+#pragma unroll
+    for (int gi = 0; gi < AD_GROUP; ++gi) {
+        m[gi] = -INFINITY; l[gi] = 0.f;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[gi][e] = 0.f;
+    }
+
+    const int* pt = page_table + (size_t)s * max_pages;
+    const int page_mask = (1 << page_shift) - 1;
+    for (int j0 = my_lo + warp * 2; j0 <= my_hi; j0 += AD_WARPS * 2) {
+        float kr[2][VEC], vr[2][VEC];
+        bool live[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int j = j0 + u;
+            live[u] = j <= my_hi;
+            const int jj = live[u] ? j : my_hi;
+            const size_t row = (((size_t)pt[jj >> page_shift] * n_kv + kvh) << page_shift) + (jj & page_mask);
+            load_row<VEC>(k_cache + row * head_dim, lane, head_dim, kr[u]);
+            load_row<VEC>(v_cache + row * head_dim, lane, head_dim, vr[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (!live[u]) continue;
+            float sc[AD_GROUP];
+#pragma unroll
+            for (int gi = 0; gi < AD_GROUP; ++gi) {
+                float d = 0.f;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) d = fmaf(qv[gi][e], kr[u][e], d);
+                sc[gi] = d;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int gi = 0; gi < AD_GROUP; ++gi) sc[gi] += __shfl_xor_sync(0xffffffffu, sc[gi], o);
+#pragma unroll
+            for (int gi = 0; gi < AD_GROUP; ++gi) {
+                const float m_new = fmaxf(m[gi], sc[gi]);
+                const float alpha = __expf(m[gi] - m_new);            // exp(-inf) = 0 on the first key
+                const float pj = __expf(sc[gi] - m_new);
+                l[gi] = l[gi] * alpha + pj;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) acc[gi][e] = fmaf(pj, vr[u][e], acc[gi][e] * alpha);
+                m[gi] = m_new;
+            }
+        }
+    }
+
+    // merge the 4 warps in warp order
+#pragma unroll
+    for (int gi = 0; gi < AD_GROUP; ++gi) {
+        if (lane == 0) { sm_m[warp][gi] = m[gi]; sm_l[warp][gi] = l[gi]; }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) sm_acc[warp][gi][lane * VEC + e] = acc[gi][e];
+    }
+    __syncthreads();
+    const int width = 32 * VEC;
+    // thread e of the block owns element (head gi, dim d) of the merged partial
+    for (int e = threadIdx.x; e < n_heads * width; e += AD_THREADS) {
+        const int gi = e / width, d = e % width;
+        if (d >= head_dim) continue;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) mm = fmaxf(mm, sm_m[w][gi]);
+        float ll = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) {
+            const float f = (sm_m[w][gi] == -INFINITY) ? 0.f : __expf(sm_m[w][gi] - mm);
+            ll += sm_l[w][gi] * f;
+            a += sm_acc[w][gi][d] * f;
+        }
+        if (n_splits == 1) {
+            out[(size_t)b * ldo + (size_t)(h0 + gi) * head_dim + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+        } else {
+            float* part = scratch + (((size_t)b * n_q + h0 + gi) * n_splits + split) * (head_dim + 2);
+            part[d] = a;
+            if (d == 0) { part[head_dim] = mm; part[head_dim + 1] = ll; }
+        }
+    }
+    if (n_splits == 1) return;
+
+    // the block that arrives last merges the splits, in split order
+    __threadfence();
+    __syncthreads();
+    int* counter = counters + (size_t)b * gridDim.y + blockIdx.y;
+    if (threadIdx.x == 0) {
+        const int arrived = atomicAdd(counter, 1);
+        is_last = (arrived == n_splits - 1);
+        if (is_last) *counter = 0;                               // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int e = threadIdx.x; e < n_heads * head_dim; e += AD_THREADS) {
+        const int gi = e / head_dim, d = e % head_dim;
+        const float* base = scratch + ((size_t)b * n_q + h0 + gi) * n_splits * (head_dim + 2);
+        float mm = -INFINITY;
+        for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, __ldcg(base + (size_t)sp * (head_dim + 2) + head_dim));
+        float ll = 0.f, a = 0.f;
+        for (int sp = 0; sp < n_splits; ++sp) {
+            const float* part = base + (size_t)sp * (head_dim + 2);
+            const float pm = __ldcg(part + head_dim);
+            const float f = (pm == -INFINITY) ? 0.f : __expf(pm - mm);
+            ll += __ldcg(part + head_dim + 1) * f;
+            a += __ldcg(part + d) * f;
+        }
+        out[(size_t)b * ldo + (size_t)(h0 + gi) * head_dim + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+    }
+}
+
+// Scratch: n_seqs * n_q * n_splits * (head_dim + 2) floats; counters: n_seqs * gridDim.y ints,
+// zero before the first launch (every launch leaves them zero).
+SSB_API long long ssb_attention_decode_scratch_floats(int n_seqs, int n_q, int head_dim, int n_splits) {
+    return (long long)n_seqs * n_q * n_splits * (head_dim + 2);
+}
+
+SSB_API int ssb_attention_decode_counters(int n_seqs, int n_q, int n_kv) {
+    const int group = n_q / n_kv;
+    return n_seqs * n_kv * ((group + AD_GROUP - 1) / AD_GROUP);
+}
+
+SSB_API int ssb_attention_decode(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                 const int* pos, const int* slot, const int* page_table, int max_pages,
+                                 void* out, int ldo, int n_seqs, int n_q, int n_kv, int head_dim,
+                                 int page_shift, int window, float scale, int n_splits, float* scratch,
+                                 int* counters, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (head_dim <= 0 || head_dim > 32 * AD_MAX_VEC || n_kv <= 0 || n_q % n_kv || n_splits < 1)
+        return SSB_ERR_BAD_SIZE;
+    if (n_splits > 1 && (!scratch || !counters)) return SSB_ERR_BAD_SIZE;
+    const int group = n_q / n_kv;
+    dim3 grid(n_seqs, n_kv * ((group + AD_GROUP - 1) / AD_GROUP), n_splits);
+    const int vec = (head_dim + 31) / 32;
+#define SSB_AD(V) \
+    attention_decode_kernel<V><<<grid, AD_THREADS, 0, stream>>>( \
+        (const bf16*)q, ldq, (const bf16*)k_cache, (const bf16*)v_cache, pos, slot, page_table, max_pages, \
+        (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters)
+    // vector loads need VEC elements aligned: rows are head_dim * 2 bytes apart
+    const bool aligned = (head_dim % vec == 0) && ((ldq * 2) % (vec * 2) == 0);
+    if (vec == 1) SSB_AD(1);
+    else if (vec == 2 && aligned) SSB_AD(2);
+    else if (vec <= 4 && head_dim % 4 == 0 && ldq % 4 == 0) SSB_AD(4);
+    else if (vec <= 8 && head_dim % 8 == 0 && ldq % 8 == 0) SSB_AD(8);
+    else return SSB_ERR_UNSUPPORTED;
+#undef SSB_AD
+    return ssb_launch_status();
+}

@@ -1,9 +1,87 @@
-"""The bfloat16 kernel set used for serving: fast kernels where one exists for the
-shape at hand, the plain kernel (same arithmetic, bfloat16 storage) otherwise."""
+"""The bfloat16 kernel set used for serving: a fast kernel where one exists for the shape at
+hand, the plain kernel (same arithmetic, bfloat16 storage) otherwise.
+
+Decode steps (up to 64 rows) run the skinny GEMM, with the RMSNorm folded into its
+input for very small batches and SwiGLU folded into its output, and the split-key
+attention kernel."""
 from __future__ import annotations
 
-from .kernel_sets import PlainKernels
+from typing import Dict, Optional
+
+import torch
+
+from . import ops
+from .kernel_sets import NormedInput, PlainKernels, as_tensor
+
+FUSED_NORM_MAX_ROWS = 4        # above this each block would re-read too much of the residual
+TARGET_BLOCKS = 296            # two blocks per SM
 
 
 class FastKernels(PlainKernels):
     name = "fast"
+
+    def __init__(self):
+        self._scratch: Dict[str, torch.Tensor] = {}
+        self._retired = []      # outgrown buffers stay alive: captured graphs still point at them
+
+    # ---- matrix products -------------------------------------------------------------
+    def _skinny(self, x, weight, out, mode):
+        if isinstance(x, NormedInput):
+            if (x._tensor is None and x.fusable and x.n_rows <= FUSED_NORM_MAX_ROWS
+                    and ops.skinny_gemm_ok(x.residual, weight, True) and x.weight.data_ptr() % 16 == 0):
+                ops.skinny_gemm(x.residual, weight, out, mode, norm_weight=x.weight, eps=x.eps)
+                return True
+            x = x.tensor()
+        if ops.skinny_gemm_ok(x, weight, False):
+            ops.skinny_gemm(x, weight, out, mode)
+            return True
+        return False
+
+    def linear(self, x, weight, out, accumulate=False):
+        rows = x.n_rows if isinstance(x, NormedInput) else x.shape[0]
+        if rows <= 64 and weight.dtype == torch.bfloat16 and (out.dtype == torch.float32 or not accumulate):
+            if self._skinny(x, weight, out, ops.SG_ACCUMULATE if accumulate else ops.SG_STORE):
+                return
+        ops.gemm_nt_plain(as_tensor(x), weight, out, accumulate)
+
+    def pack_gate_up(self, gate, up):
+        inter = gate.shape[0]
+        if inter % 8 or gate.dtype != torch.bfloat16:
+            return super().pack_gate_up(gate, up)
+        both = torch.stack([gate.view(inter // 8, 8, -1), up.view(inter // 8, 8, -1)], dim=1)
+        return both.reshape(2 * inter, -1).contiguous(), "interleaved"      # [8 gate | 8 up] per 16 rows
+
+    def gate_up_swiglu(self, x, w_gate_up, layout, out):
+        rows = x.n_rows if isinstance(x, NormedInput) else x.shape[0]
+        if layout == "interleaved" and rows <= 64 and self._skinny(x, w_gate_up, out, ops.SG_SWIGLU):
+            return
+        super().gate_up_swiglu(x, w_gate_up, layout, out)
+
+    # ---- attention -------------------------------------------------------------------
+    def _buffer(self, name: str, n: int, dtype, device, zero=False) -> torch.Tensor:
+        t = self._scratch.get(name)
+        if t is None or t.numel() < n or t.device != device:
+            if t is not None:
+                self._retired.append(t)
+            t = (torch.zeros if zero else torch.empty)(max(n, 4096), dtype=dtype, device=device)
+            self._scratch[name] = t
+        return t
+
+    def attention(self, q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim, page_shift,
+                  window: Optional[int], scale: float):
+        if batch.is_decode and q.dtype == torch.bfloat16 and head_dim <= 256 and head_dim % 16 == 0 \
+                and q.stride(0) % 8 == 0:
+            group = n_q // n_kv
+            blocks = batch.n_seqs * n_kv * ((group + 3) // 4)
+            pages = batch.kv_pages if not window else min(batch.kv_pages, (window >> page_shift) + 2)
+            n_splits = max(1, min(TARGET_BLOCKS // blocks, pages, 16))
+            scratch = counters = None
+            if n_splits > 1:
+                nf, nc = ops.attention_decode_scratch(batch.n_seqs, n_q, n_kv, head_dim, n_splits)
+                scratch = self._buffer("attn_partials", nf, torch.float32, q.device)
+                counters = self._buffer("attn_counters", nc, torch.int32, q.device, zero=True)
+            ops.attention_decode(q, k_cache, v_cache, batch.pos, batch.slot_of_token, page_table, out,
+                                 n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters)
+            return
+        super().attention(q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim, page_shift,
+                          window, scale)

@@ -14,6 +14,43 @@ import torch
 from . import ops
 
 
+class NormedInput:
+    """The input of a mixer or feed-forward: ``norm(residual)``, not yet computed.
+
+    ``tensor()`` runs the norm kernel (once) and gives the activations; a kernel set that
+    can apply the norm inside its matrix product reads ``residual``, ``weight`` and
+    ``eps`` instead and never materialises them."""
+
+    def __init__(self, ctx, residual, norm):
+        self.ctx, self.residual, self.norm = ctx, residual, norm
+        self._tensor = None
+
+    @property
+    def fusable(self) -> bool:
+        return getattr(self.norm, "fusable_rms", False)
+
+    @property
+    def weight(self):
+        return self.norm.weight
+
+    @property
+    def eps(self) -> float:
+        return self.norm.eps
+
+    @property
+    def n_rows(self) -> int:
+        return self.residual.shape[0]
+
+    def tensor(self) -> torch.Tensor:
+        if self._tensor is None:
+            self._tensor = self.norm(self.ctx, self.residual)
+        return self._tensor
+
+
+def as_tensor(x) -> torch.Tensor:
+    return x.tensor() if isinstance(x, NormedInput) else x
+
+
 class PlainKernels:
     name = "plain"
 
@@ -24,8 +61,19 @@ class PlainKernels:
         ops.rmsnorm(x, weight, eps, out, rows)
 
     def linear(self, x, weight, out, accumulate=False):
-        """out (+)= x @ weight^T."""
-        ops.gemm_nt_plain(x, weight, out, accumulate)
+        """out (+)= x @ weight^T; ``x`` may be a :class:`NormedInput`."""
+        ops.gemm_nt_plain(as_tensor(x), weight, out, accumulate)
+
+    def pack_gate_up(self, gate, up):
+        """Gate and up weights as one matrix, in the layout ``gate_up_swiglu`` wants."""
+        return torch.cat([gate, up], dim=0).contiguous(), "halves"
+
+    def gate_up_swiglu(self, x, w_gate_up, layout, out):
+        """out = silu(x @ gate^T) * (x @ up^T)."""
+        x = as_tensor(x)
+        gate_up = torch.empty((x.shape[0], w_gate_up.shape[0]), dtype=x.dtype, device=x.device)
+        self.linear(x, w_gate_up, gate_up)
+        ops.swiglu(gate_up, out, interleaved=(layout == "interleaved"))
 
     def rope_append(self, qkv, cos, sin, batch, page_table, k_cache, v_cache, n_q, n_kv, head_dim,
                     rotary_dim, page_shift, write_cache=True):

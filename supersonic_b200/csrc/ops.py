@@ -35,6 +35,8 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 
 def _check(status: int, what: str) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if status:
         reason = _ERRORS.get(status) or f"CUDA error {status}"
         raise KernelError(f"{what}: {reason}")
@@ -62,6 +64,7 @@ def _need(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None, ro
 
 
 _lib_cache = {}
+LAUNCHES = 0          # kernels launched through this module (graph replays are counted by their owner)
 
 
 def _fn(lib: str, name: str):
@@ -172,15 +175,17 @@ def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         c_int(int(window) if window else 0), c_float(scale), _stream()), "attention_plain")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, c] = silu(gate_up[t, c]) * gate_up[t, I + c]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+    """out[t, c] = silu(gate[t, c]) * up[t, c]; gate and up are the halves of a row of
+    ``gate_up``, or (interleaved) alternate as [8 gate | 8 up] per 16 columns."""
     _need(gate_up, "gate_up", None, 2); _need(out, "out", gate_up.dtype, 2)
     T, inter = out.shape
     if gate_up.shape[0] != T or gate_up.shape[1] != 2 * inter:
         raise KernelError("swiglu: gate_up must be [T, 2*I] for out [T, I]")
     _check(_fn("plain_ops", "ssb_swiglu")(
         _ptr(gate_up), c_int(gate_up.stride(0)), _ptr(out), c_int(out.stride(0)),
-        c_int(dtype_code(out.dtype)), c_int(T), c_int(inter), _stream()), "swiglu")
+        c_int(dtype_code(out.dtype)), c_int(T), c_int(inter), c_int(1 if interleaved else 0),
+        _stream()), "swiglu")
 
 
 def add_into(out: torch.Tensor, x: torch.Tensor) -> None:
@@ -222,3 +227,70 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
         _ptr(logits), c_longlong(logits.stride(0)), c_int(n), c_int(logits.shape[1]),
         c_float(temperature), c_int(int(top_k)), c_float(top_p), _ptr(slots), _ptr(rng_state), _ptr(out),
         _ptr(drawn_u), _stream()), "sample")
+
+
+# ---- decode kernels --------------------------------------------------------------------
+SG_STORE, SG_ACCUMULATE, SG_SWIGLU = 0, 1, 2
+
+
+def skinny_gemm_ok(x: torch.Tensor, w: torch.Tensor, normed: bool) -> bool:
+    """Whether the skinny GEMM takes these operands (else the plain kernels do)."""
+    return (w.dtype == torch.bfloat16 and x.shape[0] <= 64 and w.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and x.dtype == (torch.float32 if normed else torch.bfloat16))
+
+
+def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = SG_STORE,
+                norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0) -> None:
+    """out = x @ w^T for up to 64 rows.  With ``norm_weight`` x is the float32 residual and is
+    RMS-normalised on the way in.  mode: store, add into float32 ``out``, or SwiGLU over rows
+    of ``w`` that come as [8 gate | 8 up] per 16 (``out`` is [rows, N/2])."""
+    _need(x, "x", torch.float32 if norm_weight is not None else torch.bfloat16, 2)
+    _need(w, "w", torch.bfloat16, 2); _need(out, "out", None, 2)
+    B, K = x.shape
+    N = w.shape[0]
+    n_out = N // 2 if mode == SG_SWIGLU else N
+    if w.shape[1] != K or tuple(out.shape) != (B, n_out):
+        raise KernelError(f"skinny_gemm: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if norm_weight is not None:
+        _need(norm_weight, "norm_weight", None, 1)
+        if norm_weight.shape[0] != K:
+            raise KernelError("skinny_gemm: norm weight width")
+    _check(_fn("decode_ops", "ssb_skinny_gemm")(
+        _ptr(x), c_int(x.stride(0)), _ptr(norm_weight),
+        c_int(dtype_code(norm_weight.dtype) if norm_weight is not None else 0), c_float(eps), _ptr(w),
+        c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(dtype_code(out.dtype)), c_int(B),
+        c_int(N), c_int(K), c_int(mode), _stream()), "skinny_gemm")
+
+
+def attention_decode_scratch(n_seqs: int, n_q: int, n_kv: int, head_dim: int, n_splits: int):
+    """(float32 elements of scratch, int32 counters) one launch needs; counters start at zero."""
+    lib = load_library("decode_ops")
+    lib.ssb_attention_decode_scratch_floats.restype = c_longlong
+    return (int(lib.ssb_attention_decode_scratch_floats(c_int(n_seqs), c_int(n_q), c_int(head_dim),
+                                                        c_int(n_splits))),
+            int(lib.ssb_attention_decode_counters(c_int(n_seqs), c_int(n_q), c_int(n_kv))))
+
+
+def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor,
+                     slot: torch.Tensor, page_table: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int,
+                     head_dim: int, page_shift: int, window: Optional[int], scale: float, n_splits: int,
+                     scratch: Optional[torch.Tensor], counters: Optional[torch.Tensor]) -> None:
+    """One query token per sequence (row) over its cached keys, the keys split ``n_splits`` ways."""
+    _need(q, "q", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
+    _need(k_cache, "k_cache", torch.bfloat16); _need(v_cache, "v_cache", torch.bfloat16)
+    _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    B = q.shape[0]
+    if pos.shape[0] != B or slot.shape[0] != B or out.shape[0] != B:
+        raise KernelError("attention_decode: one position, slot and output row per sequence")
+    if n_splits > 1:
+        need_f, need_c = attention_decode_scratch(B, n_q, n_kv, head_dim, n_splits)
+        _need(scratch, "scratch", torch.float32); _need(counters, "counters", torch.int32)
+        if scratch.numel() < need_f or counters.numel() < need_c:
+            raise KernelError(f"attention_decode: scratch of {need_f} floats and {need_c} counters needed")
+    _check(_fn("decode_ops", "ssb_attention_decode")(
+        _ptr(q), c_int(q.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(pos), _ptr(slot), _ptr(page_table),
+        c_int(page_table.shape[1]), _ptr(out), c_int(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv),
+        c_int(head_dim), c_int(page_shift), c_int(int(window) if window else 0), c_float(scale),
+        c_int(n_splits), _ptr(scratch), _ptr(counters), _stream()), "attention_decode")

@@ -354,29 +354,33 @@ SSB_API int ssb_attention_plain(const void* q, int ldq, int dtype, const void* k
 }
 
 // ---------------------------------------------------------------------------------------
-// swiglu: z[t, c] = silu(gate[t, c]) * up[t, c]; gate and up are the two halves of a row
+// swiglu: z[t, c] = silu(gate[t, c]) * up[t, c].  Gate and up are the two halves of a row, or
+// (interleaved) come as [8 gate | 8 up] per 16 columns
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, int ld, T* __restrict__ z, int ldz, int inter,
-                              size_t total) {
+                              size_t total, int interleaved) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / inter;
     const int c = (int)(idx % inter);
-    const float g = ssb_to_float(gu[t * ld + c]);
-    const float u = ssb_to_float(gu[t * ld + inter + c]);
+    const int cg = interleaved ? (c / 8) * 16 + (c % 8) : c;
+    const int cu = interleaved ? cg + 8 : inter + c;
+    const float g = ssb_to_float(gu[t * ld + cg]);
+    const float u = ssb_to_float(gu[t * ld + cu]);
     z[t * ldz + c] = ssb_from_float<T>(g / (1.0f + expf(-g)) * u);
 }
 
 SSB_API int ssb_swiglu(const void* gate_up, int ld, void* z, int ldz, int dtype, int n_tokens, int inter,
-                       cudaStream_t stream) {
+                       int interleaved, cudaStream_t stream) {
+    if (interleaved && inter % 8) return SSB_ERR_BAD_SIZE;
     const size_t total = (size_t)n_tokens * inter;
     if (total == 0) return 0;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == SSB_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, ld, (float*)z, ldz, inter, total);
+        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, ld, (float*)z, ldz, inter, total, interleaved);
     else if (dtype == SSB_BF16)
-        swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, ld, (bf16*)z, ldz, inter, total);
+        swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, ld, (bf16*)z, ldz, inter, total, interleaved);
     else
         return SSB_ERR_BAD_DTYPE;
     return ssb_launch_status();

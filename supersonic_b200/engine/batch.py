@@ -40,9 +40,17 @@ class StepBatch:
     cu_new: torch.Tensor           # [B+1] int32: where each sequence's new tokens begin
     want_rows: torch.Tensor        # [W] int32: rows of the packed tokens whose logits are wanted
     n_want: int
+    kv_pages: int = 1              # pages the longest sequence spans (decode: rounded down to 2^n)
     host_slots: List[int] = field(default_factory=list)
     host_starts: List[int] = field(default_factory=list)
     host_counts: List[int] = field(default_factory=list)
+
+
+def decode_pages_bucket(longest: int, page_tokens: int = 64) -> int:
+    """Pages spanned by ``longest`` tokens, rounded down to a power of two: kernels size their
+    grids from it, and a captured decode step stays valid while the bucket does."""
+    pages = max(1, -(-longest // page_tokens))
+    return 1 << (pages.bit_length() - 1)
 
 
 def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], device,
@@ -78,6 +86,7 @@ def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], device,
     if len(set(slots)) != len(slots):
         raise ValueError("a slot appears twice in one step")
     T, B, W = len(tokens), len(slots), len(want)
+    longest = max(s + c for s, c in zip(starts, counts))
     flat = tokens + pos + slot_of + slots + list(starts) + cu + want
     host = torch.tensor(flat, dtype=torch.int32)
     dev = torch.device(device)
@@ -94,7 +103,7 @@ def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], device,
     seq_slot, seq_start, cu_new, want_rows = take(B), take(B), take(B + 1), take(W)
     return StepBatch(
         n_tokens=T, n_seqs=B, max_new=max(counts),
-        max_total=max(s + c for s, c in zip(starts, counts)),
+        max_total=longest, kv_pages=decode_pages_bucket(longest),
         is_decode=all(c == 1 for c in counts),
         token_ids=token_ids, pos=pos_t, slot_of_token=slot_t, seq_slot=seq_slot, seq_start=seq_start,
         cu_new=cu_new, want_rows=want_rows, n_want=W,

@@ -24,7 +24,7 @@ from ..csrc.kernel_sets import kernel_set_for
 from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
                      BuildContext, WeightAccess, lookup)
 from ..weights import WeightStore
-from .batch import StepBatch, StepEntry, pack_step
+from .batch import StepBatch, StepEntry, decode_pages_bucket, pack_step
 
 _DTYPES = {"float32": torch.float32, "fp32": torch.float32, "f32": torch.float32,
            "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
@@ -57,12 +57,66 @@ class StepContext:
     dtype: torch.dtype
 
 
+class DecodeGraph:
+    """One captured decode step for a fixed number of sequences and key-page bucket.
+
+    Token ids, positions and slots live in a fixed device buffer that each step
+    overwrites from pinned host memory; the captured kernels read them from there, so the
+    same graph serves any sequences at any positions within the bucket.  The reference has
+    no graphs: every op is a host call, several followed by a device synchronise
+    (kernels/full_attention_bridge_cuda.cu:1905-1906)."""
+
+    def __init__(self, model: "Model", n_seqs: int, kv_pages: int, pool=None):
+        from ..csrc import ops
+        B, dev = n_seqs, model.device
+        self.n_seqs = B
+        # a ring of pinned staging buffers: the host may run several steps ahead of the device
+        self.hosts = [torch.zeros(3 * B, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self.copied = [None] * len(self.hosts)
+        self.turn = 0
+        self.ints = torch.zeros(3 * B, dtype=torch.int32, device=dev)
+        self.ints[2 * B:] = -1                              # warm-up rows are padding: nothing is written
+        ar = torch.arange(B + 1, dtype=torch.int32, device=dev)
+        self.batch = StepBatch(
+            n_tokens=B, n_seqs=B, max_new=1, max_total=1, is_decode=True,
+            token_ids=self.ints[:B], pos=self.ints[B:2 * B], slot_of_token=self.ints[2 * B:],
+            seq_slot=self.ints[2 * B:], seq_start=self.ints[B:2 * B], cu_new=ar, want_rows=ar[:B].clone(),
+            n_want=B, kv_pages=kv_pages, host_slots=[], host_starts=[], host_counts=[1] * B)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):                       # warm-up outside capture (lazy set-up, attributes)
+            model._forward(self.batch)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        before = ops.LAUNCHES
+        with torch.cuda.graph(self.graph, pool=pool):
+            self.logits = model._forward(self.batch)
+        self.kernels_per_replay = ops.LAUNCHES - before
+        self.pool = self.graph.pool()
+
+    def run(self, tokens, positions, slots) -> torch.Tensor:
+        i = self.turn
+        self.turn = (i + 1) % len(self.hosts)
+        if self.copied[i] is not None:
+            self.copied[i].synchronize()                    # its last copy has left this buffer
+        h = self.hosts[i]
+        h.copy_(torch.tensor(list(tokens) + list(positions) + list(slots), dtype=torch.int32))
+        self.ints.copy_(h, non_blocking=True)
+        if self.copied[i] is None:
+            self.copied[i] = torch.cuda.Event()
+        self.copied[i].record()
+        self.graph.replay()
+        return self.logits
+
+
 class Model:
     """Parts, cache and step function of one model on one device."""
 
     def __init__(self, spec: ModelSpec, store: WeightStore, dtype="bfloat16", device="cuda:0",
                  max_tokens: int = 4096, max_seq_tokens: Optional[int] = None,
-                 max_slots: Optional[int] = None, kernels: Optional[str] = None, config=None):
+                 max_slots: Optional[int] = None, kernels: Optional[str] = None, config=None,
+                 use_graphs: bool = True):
         spec.validate()
         self.spec, self.config = spec, config
         self.dtype = parse_dtype(dtype)
@@ -101,6 +155,12 @@ class Model:
                                  f"{needs.get(stop.cache)} is not its own {need}")
         self.cache = SequenceCache({c: n for c, n in needs.items() if n is not None}, max_tokens,
                                    max_seq, self.dtype, self.device, max_slots)
+        # decode steps of the serving path replay captured graphs (one per batch size and page bucket)
+        self.use_graphs = use_graphs and self.kernels.name == "fast"
+        self._graphs: Dict[Any, DecodeGraph] = {}
+        self._graph_pool = None
+        self.graph_replays = 0
+        self.graph_kernels = 0
 
     # ---- construction from a folder ---------------------------------------------------
     @staticmethod
@@ -127,6 +187,8 @@ class Model:
         of the entries and of their ``want`` (an empty tensor if nothing is wanted)."""
         cache = self.cache
         starts = [cache.length(e.slot) for e in entries]
+        if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            return self._graph_step(entries, starts)
         batch = pack_step(entries, starts, self.device, self.spec.vocab_size)
         for e in entries:          # pages a failed step reserved stay with their slots
             cache.reserve(e.slot, len(e.tokens))
@@ -134,6 +196,30 @@ class Model:
         logits = self._forward(batch)
         for e in entries:
             cache.advance(e.slot, len(e.tokens))
+        return logits
+
+    def _graph_step(self, entries, starts) -> torch.Tensor:
+        cache = self.cache
+        slots = [e.slot for e in entries]
+        tokens = [int(e.tokens[0]) for e in entries]
+        if len(set(slots)) != len(slots):
+            raise ValueError("a slot appears twice in one step")
+        bad = [t for t in tokens if not 0 <= t < self.spec.vocab_size]
+        if bad:
+            raise ValueError(f"token ids {bad[:8]} are outside the vocabulary of {self.spec.vocab_size}")
+        for e in entries:
+            cache.reserve(e.slot, 1)
+        cache.sync()
+        key = (len(entries), decode_pages_bucket(max(starts) + 1))
+        graph = self._graphs.get(key)
+        if graph is None:
+            graph = self._graphs[key] = DecodeGraph(self, key[0], key[1], self._graph_pool)
+            self._graph_pool = graph.pool
+        logits = graph.run(tokens, starts, slots).clone()     # the graph's own buffer is reused next step
+        self.graph_replays += 1
+        self.graph_kernels += graph.kernels_per_replay
+        for e in entries:
+            cache.advance(e.slot, 1)
         return logits
 
     def _forward(self, batch: StepBatch) -> torch.Tensor:

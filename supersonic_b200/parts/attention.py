@@ -28,6 +28,8 @@ class Attention:
       activations ``x`` [T, hidden] and adds its output into ``residual`` (float32).
     """
 
+    takes_lazy_input = True
+
     def __init__(self, params, weights, build: BuildContext):
         self.hidden = int(params["hidden_size"])
         self.n_q, self.n_kv = int(params["num_heads"]), int(params["num_kv_heads"])
@@ -54,13 +56,13 @@ class Attention:
         return KvNeed(self.n_kv, self.head_dim, self.window)
 
     def forward(self, ctx, x, residual, cache_id, writes_cache, position):
-        T = x.shape[0]
+        T = ctx.batch.n_tokens
         kv = ctx.cache.kv(cache_id)
         width = (self.n_q + (2 * self.n_kv if writes_cache else 0)) * self.head_dim
-        qkv = torch.empty((T, width), dtype=self.dtype, device=x.device)
+        qkv = torch.empty((T, width), dtype=self.dtype, device=residual.device)
         ctx.kernels.linear(x, self.w_qkv if writes_cache else self.w_q, qkv)
         position.encode_and_append(ctx, qkv, kv, self.n_q, self.n_kv, writes_cache)
-        attn = torch.empty((T, self.n_q * self.head_dim), dtype=self.dtype, device=x.device)
+        attn = torch.empty((T, self.n_q * self.head_dim), dtype=self.dtype, device=residual.device)
         k_cache, v_cache, table, _ = kv
         ctx.kernels.attention(qkv, k_cache, v_cache, ctx.batch, table, attn, self.n_q, self.n_kv,
                               self.head_dim, PAGE_SHIFT, self.window, self.scale)

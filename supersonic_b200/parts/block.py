@@ -2,6 +2,7 @@
 the residual stream kept and summed in float32 (crates/runner/src/prefill_engine.rs:1116-1222)."""
 from __future__ import annotations
 
+from ..csrc.kernel_sets import NormedInput
 from .registry import register_block
 
 
@@ -15,8 +16,15 @@ class PreNormBlock:
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
         self.position = position
 
+    @staticmethod
+    def _input(ctx, residual, norm, part):
+        """Parts that set ``takes_lazy_input`` get the norm unapplied (a NormedInput) so that
+        their kernels may fold it in; all others get the normed activations."""
+        x = NormedInput(ctx, residual, norm)
+        return x if getattr(part, "takes_lazy_input", False) else x.tensor()
+
     def forward(self, ctx, residual, cache_id, writes_cache):
-        x = self.mixer_norm(ctx, residual)
+        x = self._input(ctx, residual, self.mixer_norm, self.mixer)
         self.mixer.forward(ctx, x, residual, cache_id, writes_cache, self.position)
-        x = self.feed_forward_norm(ctx, residual)
+        x = self._input(ctx, residual, self.feed_forward_norm, self.feed_forward)
         self.feed_forward.forward(ctx, x, residual)

@@ -17,6 +17,8 @@ class SwiGLU:
     activations ``x`` [T, hidden] and adds its output into ``residual`` (float32).
     """
 
+    takes_lazy_input = True
+
     def __init__(self, params, weights, build: BuildContext):
         self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
         w = build.weights
@@ -27,13 +29,10 @@ class SwiGLU:
                               (weights["down"], self.w_down, (self.hidden, self.inter))):
             if tuple(t.shape) != want:
                 raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {want}")
-        self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
+        self.w_gate_up, self.layout = build.kernels.pack_gate_up(gate, up)
         self.dtype = build.dtype
 
     def forward(self, ctx, x, residual):
-        T = x.shape[0]
-        gate_up = torch.empty((T, 2 * self.inter), dtype=self.dtype, device=x.device)
-        ctx.kernels.linear(x, self.w_gate_up, gate_up)
-        z = torch.empty((T, self.inter), dtype=self.dtype, device=x.device)
-        ctx.kernels.swiglu(gate_up, z)
+        z = torch.empty((residual.shape[0], self.inter), dtype=self.dtype, device=residual.device)
+        ctx.kernels.gate_up_swiglu(x, self.w_gate_up, self.layout, z)
         ctx.kernels.linear(z, self.w_down, residual, accumulate=True)

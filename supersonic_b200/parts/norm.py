@@ -17,6 +17,8 @@ class RMSNorm:
     ``rows`` (int32) picks rows of ``x`` instead of taking all.
     """
 
+    fusable_rms = True     # kernels may apply this norm (weight, eps) inside a matrix product
+
     def __init__(self, params, weights, build: BuildContext):
         self.size, self.eps = int(params["size"]), float(params["eps"])
         w = build.weights.stored(weights["weight"])

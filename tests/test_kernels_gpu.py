@@ -267,3 +267,94 @@ def test_kernels_refuse_what_they_cannot_do():
                               torch.zeros(1, dtype=torch.int32, device=DEV),
                               torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.zeros(1, 1024, device=DEV),
                               1, 1, 1024, 6, None, 1.0)
+
+
+# ---- decode kernels -----------------------------------------------------------------------
+@pytest.mark.parametrize("rows", [1, 3, 8, 9, 16, 31, 64])
+@pytest.mark.parametrize("N,K", [(301, 72), (48, 200), (1000, 4096), (272, 1440)])
+def test_skinny_gemm_store_and_accumulate(rows, N, K):
+    g = torch.Generator(device=DEV).manual_seed(20)
+    x = torch.randn(rows, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    ref = x.double() @ w.double().T
+    out = torch.empty(rows, N, device=DEV)
+    ops().skinny_gemm(x, w, out)
+    torch.testing.assert_close(out.double(), ref, atol=2e-5 * math.sqrt(K), rtol=1e-4)
+    ob = torch.empty(rows, N, dtype=torch.bfloat16, device=DEV)
+    ops().skinny_gemm(x, w, ob)
+    torch.testing.assert_close(ob.double(), ref, atol=2e-2, rtol=2e-2)
+    acc = torch.full((rows, N), 2.0, device=DEV)
+    ops().skinny_gemm(x, w, acc, mode=1)
+    torch.testing.assert_close(acc.double(), ref + 2, atol=2e-5 * math.sqrt(K), rtol=1e-4)
+    plain = torch.empty(rows, N, device=DEV)
+    ops().gemm_nt_plain(x, w, plain)
+    torch.testing.assert_close(out, plain, atol=2e-5 * math.sqrt(K), rtol=1e-4)
+
+
+@pytest.mark.parametrize("rows,wdtype", [(1, torch.bfloat16), (4, torch.float32), (8, torch.bfloat16)])
+def test_skinny_gemm_with_norm_on_the_way_in(rows, wdtype):
+    g = torch.Generator(device=DEV).manual_seed(21)
+    K, N = 1440, 200
+    res = 3 * torch.randn(rows, K, device=DEV, generator=g)
+    nw = (1 + 0.1 * torch.randn(K, device=DEV, generator=g)).to(wdtype)
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    normed = torch.empty(rows, K, dtype=torch.bfloat16, device=DEV)
+    ops().rmsnorm(res, nw, 1e-5, normed)
+    want = torch.empty(rows, N, device=DEV)
+    ops().skinny_gemm(normed, w, want)
+    got = torch.empty(rows, N, device=DEV)
+    ops().skinny_gemm(res, w, got, norm_weight=nw, eps=1e-5)
+    # same arithmetic except the order of the sum of squares: a last-bit difference of the
+    # scale can flip a bfloat16 rounding of single inputs
+    torch.testing.assert_close(got, want, atol=5e-3, rtol=0)
+    ref = (res.double() * torch.rsqrt((res.double() ** 2).mean(-1, keepdim=True) + 1e-5) * nw.double()) @ w.double().T
+    torch.testing.assert_close(got.double(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("rows", [1, 5, 40])
+def test_skinny_gemm_swiglu(rows):
+    g = torch.Generator(device=DEV).manual_seed(22)
+    K, inter = 72, 200
+    x = torch.randn(rows, K, device=DEV, generator=g).bfloat16()
+    gate = (torch.randn(inter, K, device=DEV, generator=g) / 4).bfloat16()
+    up = (torch.randn(inter, K, device=DEV, generator=g) / 4).bfloat16()
+    from supersonic_b200.csrc.fast_sets import FastKernels
+    packed, layout = FastKernels().pack_gate_up(gate, up)
+    assert layout == "interleaved" and torch.equal(packed[:8], gate[:8]) and torch.equal(packed[8:16], up[:8])
+    out = torch.empty(rows, inter, dtype=torch.bfloat16, device=DEV)
+    ops().skinny_gemm(x, packed, out, mode=2)
+    gg, uu = x.double() @ gate.double().T, x.double() @ up.double().T
+    torch.testing.assert_close(out.double(), gg / (1 + torch.exp(-gg)) * uu, atol=2e-2, rtol=2e-2)
+    # the unfused way over the same packed weights agrees
+    gu = torch.empty(rows, 2 * inter, dtype=torch.bfloat16, device=DEV)
+    ops().gemm_nt_plain(x, packed, gu)
+    z = torch.empty(rows, inter, dtype=torch.bfloat16, device=DEV)
+    ops().swiglu(gu, z, interleaved=True)
+    torch.testing.assert_close(out.float(), z.float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd,window", [(4, 2, 16, None), (3, 1, 48, None), (32, 8, 128, None),
+                                                (6, 2, 128, 100), (2, 2, 256, None), (8, 1, 64, 64),
+                                                (5, 5, 80, None)])
+@pytest.mark.parametrize("n_splits", [1, 3, 8])
+def test_attention_decode(n_q, n_kv, hd, window, n_splits):
+    g = torch.Generator(device=DEV).manual_seed(23)
+    pos = torch.tensor([0, 63, 64, 300, 299, 17, 128], dtype=torch.int32, device=DEV)
+    slot = torch.tensor([0, 1, 2, 3, 4, -1, 5], dtype=torch.int32, device=DEV)
+    table = torch.randperm(30, generator=torch.Generator().manual_seed(24)).to(torch.int32).view(6, 5).to(DEV)
+    k, v = _paged(30, n_kv, hd, torch.bfloat16, 25)
+    q = torch.randn(len(pos), (n_q + 2 * n_kv) * hd, device=DEV, generator=g).bfloat16()
+    scale = 1 / math.sqrt(hd)
+    nf, nc = ops().attention_decode_scratch(len(pos), n_q, n_kv, hd, n_splits)
+    scratch = torch.full((nf,), float("nan"), device=DEV)
+    counters = torch.zeros(nc, dtype=torch.int32, device=DEV)
+    ref = _attention_reference(q, k, v, pos, slot, table, n_q, n_kv, hd, window, scale)
+    for _ in range(2):                                                   # counters are left ready for reuse
+        out = torch.full((len(pos), n_q * hd), 5.0, dtype=torch.bfloat16, device=DEV)
+        ops().attention_decode(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, window, scale, n_splits,
+                               scratch, counters)
+        torch.testing.assert_close(out.double(), ref, atol=2e-2, rtol=2e-2)
+        assert torch.all(out[5] == 0) and torch.all(counters == 0)
+    plain = torch.empty_like(out)
+    ops().attention_plain(q, k, v, pos, slot, table, plain, n_q, n_kv, hd, 6, window, scale)
+    torch.testing.assert_close(out.float(), plain.float(), atol=1e-2, rtol=1e-2)
