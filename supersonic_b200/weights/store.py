@@ -159,6 +159,40 @@ def random_tensors(config, seed: int, device: str = "cpu", std: float = 0.02,
         yield name, x.to(torch.bfloat16)
 
 
+def random_tensor(config, seed: int, name: str, device: str = "cpu", std: float = 0.02,
+                  norm_jitter: float = 0.1) -> torch.Tensor:
+    """One tensor of :func:`random_tensors`, by name."""
+    shape = config.tensor_shapes()[name]
+    is_norm = getattr(config, "is_norm_tensor", lambda n: len(shape) == 1)
+    g = torch.Generator(device=device)
+    g.manual_seed(_tensor_seed(seed, name))
+    x = torch.randn(shape, generator=g, device=device, dtype=torch.float32)
+    x = 1.0 + norm_jitter * x if is_norm(name) else std * x
+    return x.to(torch.bfloat16)
+
+
+class RandomWeightStore(WeightStore):
+    """Random weights made on ``device`` when a tensor is asked for, never all at once."""
+
+    def __init__(self, config, seed: int, device: str = "cpu", std: float = 0.02, norm_jitter: float = 0.1):
+        self._shapes = {n: list(s) for n, s in config.tensor_shapes().items()}
+        self._args = (config, seed, str(device), std, norm_jitter)
+        super().__init__({n: None for n in self._shapes}, f"random(seed={seed})")
+
+    def shape(self, name: str) -> List[int]:
+        return list(self._shapes[name])
+
+    def stored_dtype(self, name: str) -> torch.dtype:
+        return torch.bfloat16
+
+    def get(self, name: str, device: Optional[torch.device] = None) -> torch.Tensor:
+        if name not in self._shapes:
+            raise WeightError(self.where, [name], [], [])
+        config, seed, made_on, std, jitter = self._args
+        t = random_tensor(config, seed, name, made_on, std, jitter)
+        return t if device is None or t.device == torch.device(device) else t.to(device)
+
+
 def random_store(config, seed: int, device: str = "cpu", std: float = 0.02,
                  norm_jitter: float = 0.1) -> WeightStore:
     """Random weights held in memory (on ``device``): no folder is written."""
