@@ -1,0 +1,253 @@
+// Decode attention for sm_100a: one query token per sequence over its paged keys and values.
+//
+// Grid (sequence, kv head x query-head group, split).  A block's 4 warps walk the split's keys,
+// 8 keys per warp and turn, all 16 loads of a turn in flight before any is used; a lane owns VEC
+// consecutive elements of the head dimension, so a key or value row is one coalesced load per
+// warp.  Up to AD_GROUP query heads share each key and value.  Partial (max, sum, weighted
+// values) go to scratch; the block that finishes last for a (sequence, head group) merges the
+// splits in index order and writes the output.  Nothing waits on another block.
+//
+// Replaces supersonic_qwen35_full_attention_decode_*_kernel of the reference: one warp per
+// query head, two passes over the keys (kernels/full_attention_cuda.cuh:476-679).
+#pragma once
+#include "common.cuh"
+#include <math.h>
+
+constexpr int AD_WARPS = 4;
+constexpr int AD_THREADS = AD_WARPS * 32;
+constexpr int AD_GROUP = 4;
+constexpr int AD_MAX_VEC = 8;
+constexpr int AD_TOK = 8;            // keys per warp and turn
+
+template <int VEC>
+__device__ __forceinline__ void ad_load_row(const __nv_bfloat16* p, int lane, int head_dim, float (&v)[VEC]) {
+    const int d = lane * VEC;
+    if (d + VEC <= head_dim) {
+        if (VEC == 8) {
+            const uint4 q = *reinterpret_cast<const uint4*>(p + d);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+        } else if (VEC == 4) {
+            const uint2 q = *reinterpret_cast<const uint2*>(p + d);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) { const float2 f = __bfloat1622float2(h[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+        } else if (VEC == 2) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + d));
+            v[0] = f.x; v[1] = f.y;
+        } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] = __bfloat162float(p[d + e]);
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) v[e] = (d + e < head_dim) ? __bfloat162float(p[d + e]) : 0.f;
+    }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(AD_THREADS)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k_cache,
+                        const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ pos,
+                        const int* __restrict__ slot, const int* __restrict__ page_table, int max_pages,
+                        __nv_bfloat16* __restrict__ out, int ldo, int n_q, int n_kv, int head_dim, int page_shift,
+                        int window, float scale, int n_splits, float* __restrict__ scratch,
+                        int* __restrict__ counters) {
+    __shared__ float sm_m[AD_WARPS][AD_GROUP], sm_l[AD_WARPS][AD_GROUP];
+    __shared__ float sm_acc[AD_WARPS][AD_GROUP][32 * VEC];
+    __shared__ int is_last;
+    const int b = blockIdx.x, split = blockIdx.z;
+    const int group = n_q / n_kv;
+    const int groups_per_kv = (group + AD_GROUP - 1) / AD_GROUP;
+    const int kvh = blockIdx.y / groups_per_kv, sub = blockIdx.y % groups_per_kv;
+    const int h0 = kvh * group + sub * AD_GROUP;                 // first query head of this block
+    const int n_heads = min(AD_GROUP, group - sub * AD_GROUP);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int s = slot[b];
+    if (s < 0) {                                                 // padding row: zeros, no bookkeeping
+        if (split == 0)
+            for (int e = threadIdx.x; e < n_heads * head_dim; e += AD_THREADS)
+                out[(size_t)b * ldo + (size_t)h0 * head_dim + e] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int p = pos[b];
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    // this split's keys: whole pages, split evenly
+    const int page_lo = lo >> page_shift, page_hi = p >> page_shift;
+    const int n_pages = page_hi - page_lo + 1;
+    const int per = (n_pages + n_splits - 1) / n_splits;
+    const int my_lo = max(lo, (page_lo + split * per) << page_shift);
+    const int my_hi = min(p, ((page_lo + (split + 1) * per) << page_shift) - 1);
+
+    float qv[AD_GROUP][VEC];
+#pragma unroll
+    for (int gi = 0; gi < AD_GROUP; ++gi) {
+        if (gi < n_heads) {
+            ad_load_row<VEC>(q + (size_t)b * ldq + (size_t)(h0 + gi) * head_dim, lane, head_dim, qv[gi]);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) qv[gi][e] *= scale;
+        } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) qv[gi][e] = 0.f;
+        }
+    }
+    float m[AD_GROUP], l[AD_GROUP], acc[AD_GROUP][VEC];
+#pragma unroll
+    for (int gi = 0; gi < AD_GROUP; ++gi) {
+        m[gi] = -INFINITY; l[gi] = 0.f;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[gi][e] = 0.f;
+    }
+
+    const int* pt = page_table + (size_t)s * max_pages;
+    const int page_mask = (1 << page_shift) - 1;
+    for (int j0 = my_lo + warp * AD_TOK; j0 <= my_hi; j0 += AD_WARPS * AD_TOK) {
+        float kr[AD_TOK][VEC], vr[AD_TOK][VEC];
+        size_t row[AD_TOK];
+#pragma unroll
+        for (int u = 0; u < AD_TOK; ++u) {
+            const int jj = min(j0 + u, my_hi);
+            row[u] = ((((size_t)pt[jj >> page_shift] * n_kv + kvh) << page_shift) + (jj & page_mask)) * head_dim;
+        }
+#pragma unroll
+        for (int u = 0; u < AD_TOK; ++u) ad_load_row<VEC>(k_cache + row[u], lane, head_dim, kr[u]);
+#pragma unroll
+        for (int u = 0; u < AD_TOK; ++u) ad_load_row<VEC>(v_cache + row[u], lane, head_dim, vr[u]);
+        float sc[AD_TOK][AD_GROUP];
+#pragma unroll
+        for (int u = 0; u < AD_TOK; ++u)
+#pragma unroll
+            for (int gi = 0; gi < AD_GROUP; ++gi) {
+                float d = 0.f;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) d = fmaf(qv[gi][e], kr[u][e], d);
+                sc[u][gi] = d;
+            }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int u = 0; u < AD_TOK; ++u)
+#pragma unroll
+                for (int gi = 0; gi < AD_GROUP; ++gi) sc[u][gi] += __shfl_xor_sync(0xffffffffu, sc[u][gi], o);
+#pragma unroll
+        for (int gi = 0; gi < AD_GROUP; ++gi) {
+            float m_new = m[gi];
+#pragma unroll
+            for (int u = 0; u < AD_TOK; ++u)
+                if (j0 + u <= my_hi) m_new = fmaxf(m_new, sc[u][gi]);
+            const float alpha = __expf(m[gi] - m_new);            // exp(-inf) = 0 before the first key
+            float lsum = l[gi] * alpha;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) acc[gi][e] *= alpha;
+#pragma unroll
+            for (int u = 0; u < AD_TOK; ++u) {
+                const float pj = (j0 + u <= my_hi) ? __expf(sc[u][gi] - m_new) : 0.f;
+                lsum += pj;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) acc[gi][e] = fmaf(pj, vr[u][e], acc[gi][e]);
+            }
+            l[gi] = lsum;
+            m[gi] = m_new;
+        }
+    }
+
+    // merge the 4 warps in warp order
+#pragma unroll
+    for (int gi = 0; gi < AD_GROUP; ++gi) {
+        if (lane == 0) { sm_m[warp][gi] = m[gi]; sm_l[warp][gi] = l[gi]; }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) sm_acc[warp][gi][lane * VEC + e] = acc[gi][e];
+    }
+    __syncthreads();
+    const int width = 32 * VEC;
+    // thread e of the block owns element (head gi, dim d) of the merged partial
+    for (int e = threadIdx.x; e < n_heads * width; e += AD_THREADS) {
+        const int gi = e / width, d = e % width;
+        if (d >= head_dim) continue;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) mm = fmaxf(mm, sm_m[w][gi]);
+        float ll = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) {
+            const float f = (sm_m[w][gi] == -INFINITY) ? 0.f : __expf(sm_m[w][gi] - mm);
+            ll += sm_l[w][gi] * f;
+            a += sm_acc[w][gi][d] * f;
+        }
+        if (n_splits == 1) {
+            out[(size_t)b * ldo + (size_t)(h0 + gi) * head_dim + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+        } else {
+            float* part = scratch + (((size_t)b * n_q + h0 + gi) * n_splits + split) * (head_dim + 2);
+            part[d] = a;
+            if (d == 0) { part[head_dim] = mm; part[head_dim + 1] = ll; }
+        }
+    }
+    if (n_splits == 1) return;
+
+    // the block that arrives last merges the splits, in split order
+    __threadfence();
+    __syncthreads();
+    int* counter = counters + (size_t)b * gridDim.y + blockIdx.y;
+    if (threadIdx.x == 0) {
+        const int arrived = atomicAdd(counter, 1);
+        is_last = (arrived == n_splits - 1);
+        if (is_last) *counter = 0;                               // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int e = threadIdx.x; e < n_heads * head_dim; e += AD_THREADS) {
+        const int gi = e / head_dim, d = e % head_dim;
+        const float* base = scratch + ((size_t)b * n_q + h0 + gi) * n_splits * (head_dim + 2);
+        float mm = -INFINITY;
+        for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, __ldcg(base + (size_t)sp * (head_dim + 2) + head_dim));
+        float ll = 0.f, a = 0.f;
+        for (int sp = 0; sp < n_splits; ++sp) {
+            const float* part = base + (size_t)sp * (head_dim + 2);
+            const float pm = __ldcg(part + head_dim);
+            const float f = (pm == -INFINITY) ? 0.f : __expf(pm - mm);
+            ll += __ldcg(part + head_dim + 1) * f;
+            a += __ldcg(part + d) * f;
+        }
+        out[(size_t)b * ldo + (size_t)(h0 + gi) * head_dim + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+    }
+}
+
+// Scratch one launch needs: floats for the partial results, ints for the arrival counters.
+static inline long long ad_scratch_floats(int n_seqs, int n_q, int head_dim, int n_splits) {
+    return (long long)n_seqs * n_q * n_splits * (head_dim + 2);
+}
+
+static inline int ad_counters(int n_seqs, int n_q, int n_kv) {
+    const int group = n_q / n_kv;
+    return n_seqs * n_kv * ((group + AD_GROUP - 1) / AD_GROUP);
+}
+
+// Checks the sizes, picks the vector width and launches.  ``counters`` must be zero on entry
+// (every launch leaves them zero); scratch and counters may be null when n_splits is 1.
+static inline int ad_launch(const void* q, int ldq, const void* k_cache, const void* v_cache, const int* pos,
+                            const int* slot, const int* page_table, int max_pages, void* out, int ldo,
+                            int n_seqs, int n_q, int n_kv, int head_dim, int page_shift, int window,
+                            float scale, int n_splits, float* scratch, int* counters, cudaStream_t stream) {
+    typedef __nv_bfloat16 bf16;
+    if (n_seqs <= 0) return 0;
+    if (head_dim <= 0 || head_dim > 32 * AD_MAX_VEC || n_kv <= 0 || n_q % n_kv || n_splits < 1)
+        return SSB_ERR_BAD_SIZE;
+    if (n_splits > 1 && (!scratch || !counters)) return SSB_ERR_BAD_SIZE;
+    const int group = n_q / n_kv;
+    dim3 grid(n_seqs, n_kv * ((group + AD_GROUP - 1) / AD_GROUP), n_splits);
+    const int vec = (head_dim + 31) / 32;
+#define SSB_AD(V) \
+    attention_decode_kernel<V><<<grid, AD_THREADS, 0, stream>>>( \
+        (const bf16*)q, ldq, (const bf16*)k_cache, (const bf16*)v_cache, pos, slot, page_table, max_pages, \
+        (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters)
+    // vector loads need VEC elements aligned: rows are head_dim * 2 bytes apart
+    if (vec == 1) SSB_AD(1);
+    else if (vec == 2 && head_dim % 2 == 0 && ldq % 2 == 0) SSB_AD(2);
+    else if (vec <= 4 && head_dim % 4 == 0 && ldq % 4 == 0) SSB_AD(4);
+    else if (vec <= 8 && head_dim % 8 == 0 && ldq % 8 == 0) SSB_AD(8);
+    else return SSB_ERR_UNSUPPORTED;
+#undef SSB_AD
+    return ssb_launch_status();
+}

@@ -35,7 +35,7 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "sampling": {"sources": ["sampling.cu"], "flags": [], "link": []},
     "decode_ops": {"sources": ["decode_ops.cu"], "flags": [], "link": []},
 }
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "attention_decode.cuh"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

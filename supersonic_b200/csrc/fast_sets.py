@@ -14,7 +14,7 @@ from . import ops
 from .kernel_sets import NormedInput, PlainKernels, as_tensor
 
 FUSED_NORM_MAX_ROWS = 4        # above this each block would re-read too much of the residual
-TARGET_BLOCKS = 296            # two blocks per SM
+TARGET_BLOCKS = 1184           # eight small blocks per SM
 
 
 class FastKernels(PlainKernels):
@@ -74,7 +74,7 @@ class FastKernels(PlainKernels):
             group = n_q // n_kv
             blocks = batch.n_seqs * n_kv * ((group + 3) // 4)
             pages = batch.kv_pages if not window else min(batch.kv_pages, (window >> page_shift) + 2)
-            n_splits = max(1, min(TARGET_BLOCKS // blocks, pages, 16))
+            n_splits = max(1, min(TARGET_BLOCKS // blocks, pages, 64))
             scratch = counters = None
             if n_splits > 1:
                 nf, nc = ops.attention_decode_scratch(batch.n_seqs, n_q, n_kv, head_dim, n_splits)
