@@ -34,8 +34,9 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "plain_ops": {"sources": ["plain_ops.cu"], "flags": [], "link": []},
     "sampling": {"sources": ["sampling.cu"], "flags": [], "link": []},
     "decode_ops": {"sources": ["decode_ops.cu"], "flags": [], "link": []},
+    "attention_decode_static": {"sources": ["attention_decode_static.cu"], "flags": [], "link": []},
 }
-HEADERS = ["common.cuh", "attention_decode.cuh"]
+HEADERS = ["common.cuh", "attention_decode.cuh", "attention_decode_static.h"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
