@@ -42,7 +42,11 @@ class FastKernels(PlainKernels):
         if rows <= 64 and weight.dtype == torch.bfloat16 and (out.dtype == torch.float32 or not accumulate):
             if self._skinny(x, weight, out, ops.SG_ACCUMULATE if accumulate else ops.SG_STORE):
                 return
-        ops.gemm_nt_plain(as_tensor(x), weight, out, accumulate)
+        x = as_tensor(x)
+        if rows > 64 and (out.dtype == torch.float32 or not accumulate) and ops.gemm_tc_ok(x, weight, out):
+            ops.gemm_tc(x, weight, out, ops.TC_ACCUMULATE if accumulate else ops.TC_STORE)
+            return
+        ops.gemm_nt_plain(x, weight, out, accumulate)
 
     def pack_gate_up(self, gate, up):
         inter = gate.shape[0]
@@ -55,6 +59,11 @@ class FastKernels(PlainKernels):
         rows = x.n_rows if isinstance(x, NormedInput) else x.shape[0]
         if layout == "interleaved" and rows <= 64 and self._skinny(x, w_gate_up, out, ops.SG_SWIGLU):
             return
+        if layout == "interleaved" and rows > 64:
+            xt = as_tensor(x)
+            if w_gate_up.shape[0] % 16 == 0 and ops.gemm_tc_ok(xt, w_gate_up, out):
+                ops.gemm_tc(xt, w_gate_up, out, ops.TC_SWIGLU)
+                return
         super().gate_up_swiglu(x, w_gate_up, layout, out)
 
     # ---- attention -------------------------------------------------------------------

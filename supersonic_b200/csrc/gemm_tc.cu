@@ -1,0 +1,307 @@
+// Prefill GEMM for sm_100a: C[M, N] = A[M, K] W[N, K]^T, bfloat16 in, float32 accumulators in
+// tensor memory.  One 128 x BN output tile per block; operands arrive through TMA
+// (cp.async.bulk.tensor, 128-byte swizzle) into a ring of shared-memory stages; one elected
+// thread issues tcgen05.mma (M 128, N BN, K 16 per instruction); tcgen05.commit hands stages
+// back and announces the finished accumulators; four warps read them with tcgen05.ld and write
+// the result: plain store, add into the float32 residual, or SwiGLU over [8 gate | 8 up] columns.
+//
+// Replaces the reference's scalar 16x16 tiled matmul used for every prefill projection
+// (kernels/full_attention_4b_cuda.cuh:2671-2743, launcher full_attention_bridge_4b_cuda.cu:3567-3613)
+// and its separate element_add / swiglu kernels (prefill_helpers_cuda.cuh:60-70;
+// full_attention_cuda.cuh:1995-2010).
+//
+// Every wait on an mbarrier is bounded: when one runs out, the block records a code in the
+// caller's error word, lets its copies land, frees its tensor memory and returns.
+#include "common.cuh"
+#include <cuda.h>
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
+constexpr int TC_THREADS = 192;           // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
+enum { TC_STORE = 0, TC_ACCUMULATE = 1, TC_SWIGLU = 2 };
+enum { TC_ERR_PRODUCER = 1, TC_ERR_MMA = 2, TC_ERR_EPILOGUE = 3 };
+
+// ---- PTX wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: false if the phase did not complete within about a second, or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    const long long t0 = clock64();
+    for (uint32_t i = 0;; ++i) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred P1;\nmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\nselp.b32 %0, 1, 0, P1;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((i & 255) == 255) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > 2000000000LL) return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                       uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
+// 8-row groups 1024 bytes apart (stride offset), leading offset unused (1), version 1.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// ---- kernel ---------------------------------------------------------------------------------
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               void* __restrict__ C, int ldc, int out_is_f32, int M, int N, int K, int mode, int m_tiles,
+               int* __restrict__ error_word) {
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);     // full[STAGES], empty[STAGES], acc_full
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);     // [0]: a role gave up; [1]: stays zero
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = (blockIdx.x % m_tiles) * TC_BM, n0 = (blockIdx.x / m_tiles) * BN;
+    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), acc_full = smem_u32(bars + 2 * STAGES);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(acc_full, 1);
+        abort_flag[0] = 0;
+        abort_flag[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {      // the whole warp allocates BN columns of tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t phase = (kb / STAGES) & 1;
+                if (!mbar_wait(empty0 + 8 * s, phase ^ 1, abort_flag)) {
+                    *abort_flag = 1; atomicCAS(error_word, 0, TC_ERR_PRODUCER); break;
+                }
+                const uint32_t a_dst = smem_u32(smem + s * STAGE_BYTES), w_dst = a_dst + A_BYTES;
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * TC_BK, m0);
+                tma_load_2d(w_dst, &map_w, full0 + 8 * s, kb * TC_BK, n0);
+                issued = kb + 1;
+            }
+            if (*abort_flag) {
+                // let copies that were issued but never consumed land before the block ends
+                for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
+                    mbar_wait(full0 + 8 * (kb % STAGES), (kb / STAGES) & 1, abort_flag + 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: D float32, A and B bfloat16, both K-major, N = BN, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t phase = (kb / STAGES) & 1;
+                if (!mbar_wait(full0 + 8 * s, phase, abort_flag)) {
+                    *abort_flag = 1; atomicCAS(error_word, 0, TC_ERR_MMA); ok = false; break;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+                const uint64_t da = smem_desc(a_addr), dw = smem_desc(a_addr + A_BYTES);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)        // 16 k = 32 bytes further along the swizzled row
+                    tc_mma(tmem, da + 2 * k, dw + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                tc_commit(empty0 + 8 * s);                  // the stage is free once these MMAs have read it
+            }
+            if (ok) tc_commit(acc_full);                    // accumulators complete
+        }
+    } else {
+        // epilogue: warp w may read tensor-memory lanes 32 * (w % 4) .. + 31 = rows of the tile
+        const int quarter = warp & 3;
+        const int row = m0 + quarter * 32 + lane;
+        bool ok = mbar_wait(acc_full, 0, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+            if (lane == 0) { *abort_flag = 1; atomicCAS(error_word, 0, TC_ERR_EPILOGUE); }
+        } else {
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + c * 32, r);
+                const int n = n0 + c * 32;
+                if (row >= M || n >= N) continue;
+                if (mode == TC_SWIGLU) {
+                    bf16* dst = (bf16*)C + (size_t)row * ldc + n / 2;
+                    uint32_t packed[8];
+#pragma unroll
+                    for (int g = 0; g < 2; ++g)
+#pragma unroll
+                        for (int j = 0; j < 8; j += 2) {
+                            const float g0 = __uint_as_float(r[g * 16 + j]), u0 = __uint_as_float(r[g * 16 + 8 + j]);
+                            const float g1 = __uint_as_float(r[g * 16 + j + 1]), u1 = __uint_as_float(r[g * 16 + 9 + j]);
+                            __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u0,
+                                                                      g1 / (1.0f + __expf(-g1)) * u1);
+                            packed[g * 4 + j / 2] = *reinterpret_cast<uint32_t*>(&v);
+                        }
+                    if (n + 32 <= N) {
+                        reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    } else {
+                        for (int j = 0; j < 16; ++j)            // N is a multiple of 16: whole groups only
+                            if (n + (j / 8) * 16 + 16 <= N) dst[j] = reinterpret_cast<bf16*>(packed)[j];
+                    }
+                } else if (out_is_f32) {
+                    float* dst = (float*)C + (size_t)row * ldc + n;
+                    if (n + 32 <= N) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            if (mode == TC_ACCUMULATE) {
+                                const float4 o = *reinterpret_cast<const float4*>(dst + j);
+                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                            }
+                            *reinterpret_cast<float4*>(dst + j) = v;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && n + j < N; ++j)
+                            dst[j] = __uint_as_float(r[j]) + (mode == TC_ACCUMULATE ? dst[j] : 0.f);
+                    }
+                } else {
+                    bf16* dst = (bf16*)C + (size_t)row * ldc + n;
+                    if (n + 32 <= N) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 v;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                            v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+                            v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+                            *reinterpret_cast<uint4*>(dst + j) = v;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// rows x cols bfloat16, row stride ld elements; boxes of box_rows x 64 elements, 128-byte swizzle
+static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return SSB_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : SSB_ERR_BAD_SIZE;
+}
+
+template <int BN, int STAGES>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int out_is_f32, int M, int N,
+                     int K, int mode, int* error_word, cudaStream_t stream) {
+    constexpr size_t smem = STAGES * (TC_BM + BN) * TC_BK * 2 + (2 * STAGES + 1) * 8 + 16 + 1024;
+    auto kern = gemm_tc_kernel<BN, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
+    kern<<<m_tiles * n_tiles, TC_THREADS, smem, stream>>>(ma, mw, C, ldc, out_is_f32, M, N, K, mode, m_tiles, error_word);
+    return ssb_launch_status();
+}
+
+// A: bfloat16 [M, K] (row stride lda), W: bfloat16 [N, K] (row stride ldw).  mode 0: C[m, n]
+// (bfloat16 or float32); mode 1: C (float32) += ; mode 2: W's rows come as [8 gate | 8 up] per 16
+// and C (bfloat16, [M, N/2]) = silu(gate) * up.  error_word: device int, zero while all is well.
+SSB_API int ssb_gemm_tc(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int out_dtype, int M,
+                        int N, int K, int mode, int tile_n, int* error_word, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || lda % 8 || ldw % 8 || N % 8 || !error_word) return SSB_ERR_BAD_SIZE;
+    if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)C) & 15) return SSB_ERR_BAD_SIZE;
+    if (mode == TC_ACCUMULATE && out_dtype != SSB_F32) return SSB_ERR_BAD_DTYPE;
+    if (mode == TC_SWIGLU && (out_dtype != SSB_BF16 || N % 16 || ldc % 8)) return SSB_ERR_BAD_SIZE;
+    if (mode != TC_SWIGLU && (out_dtype == SSB_F32 ? ldc % 4 : ldc % 8)) return SSB_ERR_BAD_SIZE;
+    const int bn = tile_n == 128 ? 128 : 256;
+    CUtensorMap ma, mw;
+    int rc = make_map(&ma, A, M, K, lda, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mw, W, N, K, ldw, bn);
+    if (rc) return rc;
+    const int f32o = out_dtype == SSB_F32;
+    if (bn == 128) return launch_tc<128, 6>(ma, mw, C, ldc, f32o, M, N, K, mode, error_word, stream);
+    return launch_tc<256, 4>(ma, mw, C, ldc, f32o, M, N, K, mode, error_word, stream);
+}

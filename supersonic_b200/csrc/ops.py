@@ -294,3 +294,55 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         c_int(page_table.shape[1]), _ptr(out), c_int(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv),
         c_int(head_dim), c_int(page_shift), c_int(int(window) if window else 0), c_float(scale),
         c_int(n_splits), _ptr(scratch), _ptr(counters), _stream()), "attention_decode")
+
+
+# ---- prefill GEMM on tcgen05 ---------------------------------------------------------------
+TC_STORE, TC_ACCUMULATE, TC_SWIGLU = 0, 1, 2
+_TC_ERRORS = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}
+_tc_error_words = {}
+
+
+def tc_error_word(device) -> torch.Tensor:
+    """The device word in which tcgen05 kernels record a wait that ran out (zero = all well)."""
+    key = torch.device(device)
+    if key not in _tc_error_words:
+        _tc_error_words[key] = torch.zeros(1, dtype=torch.int32, device=key)
+    return _tc_error_words[key]
+
+
+def check_device_errors(device=None) -> None:
+    """Raise if a kernel recorded a bounded wait that ran out (reads one word from each device used)."""
+    for dev, word in list(_tc_error_words.items()):
+        if device is not None and torch.device(device) != dev:
+            continue
+        code = int(word.item())
+        if code:
+            word.zero_()
+            raise KernelError(f"gemm_tc: a bounded wait ran out in {_TC_ERRORS.get(code, code)}; "
+                              "the result of that launch is invalid")
+
+
+def gemm_tc_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    """Whether the tcgen05 GEMM takes these operands (else the plain kernel does)."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
+            and w.shape[0] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+            and out.stride(0) % (4 if out.dtype == torch.float32 else 8) == 0)
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_STORE,
+            tile_n: Optional[int] = None) -> None:
+    """out = a @ w^T on the tensor cores (tcgen05, TMA-fed).  mode: store, add into float32
+    ``out``, or SwiGLU over rows of ``w`` that come as [8 gate | 8 up] per 16."""
+    _need(a, "a", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(out, "out", None, 2)
+    M, K = a.shape
+    N = w.shape[0]
+    n_out = N // 2 if mode == TC_SWIGLU else N
+    if w.shape[1] != K or tuple(out.shape) != (M, n_out):
+        raise KernelError(f"gemm_tc: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if tile_n is None:
+        tile_n = 256 if N > 128 else 128
+    _check(_fn("gemm_tc", "ssb_gemm_tc")(
+        _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)),
+        c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K), c_int(mode), c_int(tile_n),
+        _ptr(tc_error_word(a.device)), _stream()), "gemm_tc")

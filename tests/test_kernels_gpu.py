@@ -358,3 +358,46 @@ def test_attention_decode(n_q, n_kv, hd, window, n_splits):
     plain = torch.empty_like(out)
     ops().attention_plain(q, k, v, pos, slot, table, plain, n_q, n_kv, hd, 6, window, scale)
     torch.testing.assert_close(out.float(), plain.float(), atol=1e-2, rtol=1e-2)
+
+
+# ---- prefill GEMM on tcgen05 ------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (65, 128, 200), (200, 304, 72), (300, 1000, 4096),
+                                   (1024, 512, 1024), (129, 8, 64)])
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_gemm_tc(M, N, K, tile_n):
+    g = torch.Generator(device=DEV).manual_seed(30)
+    a = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    ref = a.double() @ w.double().T
+    out = torch.full((M, N), 9.0, device=DEV)
+    ops().gemm_tc(a, w, out, tile_n=tile_n)
+    ops().check_device_errors()
+    torch.testing.assert_close(out.double(), ref, atol=2e-5 * math.sqrt(K), rtol=1e-4)
+    ob = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops().gemm_tc(a, w, ob, tile_n=tile_n)
+    torch.testing.assert_close(ob.double(), ref, atol=2e-2, rtol=2e-2)
+    acc = torch.full((M, N), 2.0, device=DEV)
+    ops().gemm_tc(a, w, acc, mode=1, tile_n=tile_n)
+    torch.testing.assert_close(acc.double(), ref + 2, atol=2e-5 * math.sqrt(K), rtol=1e-4)
+    ops().check_device_errors()
+    # a row-strided input (a slice of a wider buffer) gives the same result
+    wide = torch.zeros(M, K + 8, dtype=torch.bfloat16, device=DEV)
+    wide[:, :K] = a
+    out2 = torch.empty(M, N, device=DEV)
+    ops().gemm_tc(wide[:, :K], w, out2, tile_n=tile_n)
+    assert torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("M,inter,K", [(130, 200, 72), (256, 1024, 512)])
+def test_gemm_tc_swiglu(M, inter, K):
+    g = torch.Generator(device=DEV).manual_seed(31)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    gate = (torch.randn(inter, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    up = (torch.randn(inter, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    from supersonic_b200.csrc.fast_sets import FastKernels
+    packed, layout = FastKernels().pack_gate_up(gate, up)
+    out = torch.empty(M, inter, dtype=torch.bfloat16, device=DEV)
+    ops().gemm_tc(x, packed, out, mode=2)
+    ops().check_device_errors()
+    gg, uu = x.double() @ gate.double().T, x.double() @ up.double().T
+    torch.testing.assert_close(out.double(), gg / (1 + torch.exp(-gg)) * uu, atol=2e-2, rtol=2e-2)
