@@ -34,6 +34,7 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "plain_ops": {"sources": ["plain_ops.cu"], "flags": [], "link": []},
     "sampling": {"sources": ["sampling.cu"], "flags": [], "link": []},
     "decode_ops": {"sources": ["decode_ops.cu"], "flags": [], "link": []},
+    "prefill_attention": {"sources": ["prefill_attention.cu"], "flags": [], "link": []},
     "gemm_tc": {"sources": ["gemm_tc.cu"], "flags": [], "link": []},
     "attention_decode_static": {"sources": ["attention_decode_static.cu"], "flags": [], "link": []},
 }

@@ -92,5 +92,9 @@ class FastKernels(PlainKernels):
             ops.attention_decode(q, k_cache, v_cache, batch.pos, batch.slot_of_token, page_table, out,
                                  n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters)
             return
+        if not batch.is_decode and ops.attention_prefill_ok(q, head_dim) and out.stride(0) % 2 == 0:
+            ops.attention_prefill(q, k_cache, v_cache, batch.cu_new, batch.seq_start, batch.seq_slot,
+                                  page_table, out, batch.max_new, n_q, n_kv, head_dim, page_shift, window, scale)
+            return
         super().attention(q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim, page_shift,
                           window, scale)

@@ -346,3 +346,31 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_
         _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)),
         c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K), c_int(mode), c_int(tile_n),
         _ptr(tc_error_word(a.device)), _stream()), "gemm_tc")
+
+
+# ---- prefill attention -------------------------------------------------------------------------
+def attention_prefill_ok(q: torch.Tensor, head_dim: int) -> bool:
+    return q.dtype == torch.bfloat16 and head_dim in (64, 128) and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+
+
+def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_new: torch.Tensor,
+                      seq_start: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor,
+                      out: torch.Tensor, max_new: int, n_q: int, n_kv: int, head_dim: int, page_shift: int,
+                      window: Optional[int], scale: float) -> None:
+    """Causal attention of each sequence's new tokens (packed rows of ``q``) over its cached keys,
+    which already include the new ones."""
+    _need(q, "q", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
+    _need(k_cache, "k_cache", torch.bfloat16); _need(v_cache, "v_cache", torch.bfloat16)
+    for name, t in (("cu_new", cu_new), ("seq_start", seq_start), ("seq_slot", seq_slot)):
+        _need(t, name, torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    n_seqs = seq_slot.shape[0]
+    if cu_new.shape[0] != n_seqs + 1 or seq_start.shape[0] != n_seqs:
+        raise KernelError("attention_prefill: cu_new has one more entry than there are sequences")
+    if out.shape[0] != q.shape[0] or out.shape[1] < n_q * head_dim or q.shape[1] < n_q * head_dim:
+        raise KernelError("attention_prefill: q/out shapes")
+    _check(_fn("prefill_attention", "ssb_attention_prefill")(
+        _ptr(q), c_int(q.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(cu_new), _ptr(seq_start),
+        _ptr(seq_slot), _ptr(page_table), c_int(page_table.shape[1]), _ptr(out), c_int(out.stride(0)),
+        c_int(n_seqs), c_int(max_new), c_int(n_q), c_int(n_kv), c_int(head_dim), c_int(page_shift),
+        c_int(int(window) if window else 0), c_float(scale), _stream()), "attention_prefill")

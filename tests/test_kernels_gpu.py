@@ -401,3 +401,60 @@ def test_gemm_tc_swiglu(M, inter, K):
     ops().check_device_errors()
     gg, uu = x.double() @ gate.double().T, x.double() @ up.double().T
     torch.testing.assert_close(out.double(), gg / (1 + torch.exp(-gg)) * uu, atol=2e-2, rtol=2e-2)
+
+
+# ---- prefill attention ---------------------------------------------------------------------------
+@pytest.mark.parametrize("n_q,n_kv,hd,window", [(8, 2, 128, None), (4, 4, 64, None), (6, 2, 128, 100),
+                                                (3, 1, 64, 64), (2, 1, 128, 1)])
+def test_attention_prefill(n_q, n_kv, hd, window):
+    """A ragged batch: sequences that start at 0 and sequences that continue a cached prefix,
+    lengths that end inside a page, on page borders and inside a 64-row tile."""
+    g = torch.Generator(device=DEV).manual_seed(40)
+    starts = [0, 0, 64, 37, 0, 200]
+    news = [1, 150, 64, 91, 64, 130]
+    n_seqs = len(starts)
+    pages_per = 6
+    table = torch.randperm(n_seqs * pages_per, generator=torch.Generator().manual_seed(41)).to(torch.int32)
+    table = table.view(n_seqs, pages_per).to(DEV)
+    k, v = _paged(n_seqs * pages_per, n_kv, hd, torch.bfloat16, 42)
+    cu = [0]
+    for n in news:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    q = torch.randn(T, (n_q + 2 * n_kv) * hd, device=DEV, generator=g).bfloat16()
+    slot = torch.arange(n_seqs, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    out = torch.full((T, n_q * hd), 5.0, dtype=torch.bfloat16, device=DEV)
+    ops().attention_prefill(q, k, v, torch.tensor(cu, dtype=torch.int32, device=DEV),
+                            torch.tensor(starts, dtype=torch.int32, device=DEV), slot, table, out, max(news),
+                            n_q, n_kv, hd, 6, window, scale)
+    pos = torch.tensor([s + i for s, n in zip(starts, news) for i in range(n)], dtype=torch.int32, device=DEV)
+    slot_tok = torch.tensor([b for b, n in enumerate(news) for _ in range(n)], dtype=torch.int32, device=DEV)
+    ref = _attention_reference(q, k, v, pos, slot_tok, table, n_q, n_kv, hd, window, scale)
+    torch.testing.assert_close(out.double(), ref, atol=2e-2, rtol=2e-2)
+    plain = torch.empty_like(out)
+    ops().attention_plain(q, k, v, pos, slot_tok, table, plain, n_q, n_kv, hd, 6, window, scale)
+    torch.testing.assert_close(out.float(), plain.float(), atol=2e-2, rtol=2e-2)
+
+
+def test_attention_prefill_finds_a_far_key():
+    """One key among hundreds carries the weight for the last query; its neighbours do not."""
+    hd = 128
+    k = torch.zeros(8, 1, 64, hd, dtype=torch.bfloat16, device=DEV)
+    v = torch.zeros(8, 1, 64, hd, dtype=torch.bfloat16, device=DEV)
+    table = torch.tensor([[5, 2, 7, 0, 3, 1]], dtype=torch.int32, device=DEV)
+    for p in range(330):
+        v[int(table[0, p // 64]), 0, p % 64, 0] = float(p % 128)          # exactly representable
+    needle = 131
+    k[int(table[0, needle // 64]), 0, needle % 64] = 2.0
+    q = torch.zeros(330, 3 * hd, dtype=torch.bfloat16, device=DEV)
+    q[329, :hd] = 2.0
+    out = torch.empty(330, hd, dtype=torch.bfloat16, device=DEV)
+    args = (torch.tensor([0, 330], dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+            torch.zeros(1, dtype=torch.int32, device=DEV), table, out, 330, 1, 1, hd, 6)
+    ops().attention_prefill(q, k, v, *args, None, 1.0)
+    assert abs(out[329, 0].item() - needle % 128) < 0.51
+    ops().attention_prefill(q, k, v, *args, 329 - needle + 1, 1.0)       # the window's last key is the needle
+    assert abs(out[329, 0].item() - needle % 128) < 0.51
+    ops().attention_prefill(q, k, v, *args, 329 - needle, 1.0)           # one shorter: the needle is outside
+    assert abs(out[329, 0].item() - needle % 128) > 10
