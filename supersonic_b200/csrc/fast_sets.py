@@ -14,6 +14,7 @@ from . import ops
 from .kernel_sets import NormedInput, PlainKernels, as_tensor
 
 FUSED_NORM_MAX_ROWS = 4        # above this each block would re-read too much of the residual
+SKINNY_MAX_ROWS = 16          # above this the tcgen05 GEMM streams the weights faster (measured)
 TARGET_BLOCKS = 1184           # eight small blocks per SM
 
 
@@ -39,14 +40,26 @@ class FastKernels(PlainKernels):
 
     def linear(self, x, weight, out, accumulate=False):
         rows = x.n_rows if isinstance(x, NormedInput) else x.shape[0]
-        if rows <= 64 and weight.dtype == torch.bfloat16 and (out.dtype == torch.float32 or not accumulate):
+        if rows <= SKINNY_MAX_ROWS and weight.dtype == torch.bfloat16 and (out.dtype == torch.float32 or not accumulate):
             if self._skinny(x, weight, out, ops.SG_ACCUMULATE if accumulate else ops.SG_STORE):
                 return
         x = as_tensor(x)
-        if rows > 64 and (out.dtype == torch.float32 or not accumulate) and ops.gemm_tc_ok(x, weight, out):
-            ops.gemm_tc(x, weight, out, ops.TC_ACCUMULATE if accumulate else ops.TC_STORE)
+        if rows > SKINNY_MAX_ROWS and (out.dtype == torch.float32 or not accumulate) and ops.gemm_tc_ok(x, weight, out):
+            ops.gemm_tc(x, weight, out, ops.TC_ACCUMULATE if accumulate else ops.TC_STORE,
+                        tile_n=self._tile_n(rows, weight.shape[0]))
             return
+        if rows <= 64 and weight.dtype == torch.bfloat16 and (out.dtype == torch.float32 or not accumulate):
+            if self._skinny(x, weight, out, ops.SG_ACCUMULATE if accumulate else ops.SG_STORE):
+                return
         ops.gemm_nt_plain(x, weight, out, accumulate)
+
+    @staticmethod
+    def _tile_n(rows: int, n: int) -> int:
+        """Output-tile width of the tcgen05 GEMM: wide tiles for prefill, narrow ones for a
+        handful of rows so that enough blocks stream the weights (measured on 8B shapes)."""
+        if rows > 64:
+            return 256 if n > 128 else 128
+        return 256 if n >= 16384 else 64
 
     def pack_gate_up(self, gate, up):
         inter = gate.shape[0]
@@ -57,13 +70,15 @@ class FastKernels(PlainKernels):
 
     def gate_up_swiglu(self, x, w_gate_up, layout, out):
         rows = x.n_rows if isinstance(x, NormedInput) else x.shape[0]
-        if layout == "interleaved" and rows <= 64 and self._skinny(x, w_gate_up, out, ops.SG_SWIGLU):
+        if layout == "interleaved" and rows <= SKINNY_MAX_ROWS and self._skinny(x, w_gate_up, out, ops.SG_SWIGLU):
             return
-        if layout == "interleaved" and rows > 64:
+        if layout == "interleaved" and rows > SKINNY_MAX_ROWS:
             xt = as_tensor(x)
             if w_gate_up.shape[0] % 16 == 0 and ops.gemm_tc_ok(xt, w_gate_up, out):
-                ops.gemm_tc(xt, w_gate_up, out, ops.TC_SWIGLU)
+                ops.gemm_tc(xt, w_gate_up, out, ops.TC_SWIGLU, tile_n=self._tile_n(rows, w_gate_up.shape[0]))
                 return
+        if layout == "interleaved" and rows <= 64 and self._skinny(x, w_gate_up, out, ops.SG_SWIGLU):
+            return
         super().gate_up_swiglu(x, w_gate_up, layout, out)
 
     # ---- attention -------------------------------------------------------------------

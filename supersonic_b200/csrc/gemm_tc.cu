@@ -295,13 +295,14 @@ SSB_API int ssb_gemm_tc(const void* A, int lda, const void* W, int ldw, void* C,
     if (mode == TC_ACCUMULATE && out_dtype != SSB_F32) return SSB_ERR_BAD_DTYPE;
     if (mode == TC_SWIGLU && (out_dtype != SSB_BF16 || N % 16 || ldc % 8)) return SSB_ERR_BAD_SIZE;
     if (mode != TC_SWIGLU && (out_dtype == SSB_F32 ? ldc % 4 : ldc % 8)) return SSB_ERR_BAD_SIZE;
-    const int bn = tile_n == 128 ? 128 : 256;
+    const int bn = tile_n == 64 ? 64 : (tile_n == 128 ? 128 : 256);
     CUtensorMap ma, mw;
     int rc = make_map(&ma, A, M, K, lda, TC_BM);
     if (rc) return rc;
     rc = make_map(&mw, W, N, K, ldw, bn);
     if (rc) return rc;
     const int f32o = out_dtype == SSB_F32;
+    if (bn == 64) return launch_tc<64, 8>(ma, mw, C, ldc, f32o, M, N, K, mode, error_word, stream);
     if (bn == 128) return launch_tc<128, 6>(ma, mw, C, ldc, f32o, M, N, K, mode, error_word, stream);
     return launch_tc<256, 4>(ma, mw, C, ldc, f32o, M, N, K, mode, error_word, stream);
 }

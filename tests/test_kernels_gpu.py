@@ -363,7 +363,7 @@ def test_attention_decode(n_q, n_kv, hd, window, n_splits):
 # ---- prefill GEMM on tcgen05 ------------------------------------------------------------------
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (65, 128, 200), (200, 304, 72), (300, 1000, 4096),
                                    (1024, 512, 1024), (129, 8, 64)])
-@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("tile_n", [64, 128, 256])
 def test_gemm_tc(M, N, K, tile_n):
     g = torch.Generator(device=DEV).manual_seed(30)
     a = torch.randn(M, K, device=DEV, generator=g).bfloat16()
