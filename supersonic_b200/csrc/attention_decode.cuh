@@ -46,6 +46,49 @@ __device__ __forceinline__ void ad_load_row(const __nv_bfloat16* p, int lane, in
     }
 }
 
+// A lane's VEC elements of a row as raw bits.  The loads are volatile asm so that the compiler
+// issues all of a turn's loads back to back and converts afterwards: a conversion right after
+// each load would make every load wait for the one before it.
+template <int VEC> struct AdRaw { uint32_t w[(VEC + 1) / 2]; };
+
+template <int VEC>
+__device__ __forceinline__ AdRaw<VEC> ad_load_raw(const __nv_bfloat16* p, int lane, int head_dim) {
+    AdRaw<VEC> r;
+    const int d = lane * VEC;
+#pragma unroll
+    for (int i = 0; i < (VEC + 1) / 2; ++i) r.w[i] = 0u;
+    if (d + VEC <= head_dim) {
+        if (VEC == 8) {
+            asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(r.w[0]), "=r"(r.w[1]), "=r"(r.w[2]), "=r"(r.w[3]) : "l"(p + d));
+        } else if (VEC == 4) {
+            asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(r.w[0]), "=r"(r.w[1]) : "l"(p + d));
+        } else if (VEC == 2) {
+            asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(r.w[0]) : "l"(p + d));
+        } else {
+            unsigned short h;
+            asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(h) : "l"(p + d));
+            r.w[0] = h;
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+            if (d + e < head_dim) {
+                unsigned short h;
+                asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(h) : "l"(p + d + e));
+                r.w[e / 2] |= (uint32_t)h << (16 * (e & 1));
+            }
+    }
+    return r;
+}
+
+template <int VEC>
+__device__ __forceinline__ void ad_unpack(const AdRaw<VEC>& r, float (&v)[VEC]) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+        v[e] = __uint_as_float(((r.w[e / 2] >> (16 * (e & 1))) & 0xffffu) << 16);      // bfloat16 -> float32
+}
+
 template <int VEC>
 __global__ void __launch_bounds__(AD_THREADS)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k_cache,
@@ -103,7 +146,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
     const int* pt = page_table + (size_t)s * max_pages;
     const int page_mask = (1 << page_shift) - 1;
     for (int j0 = my_lo + warp * AD_TOK; j0 <= my_hi; j0 += AD_WARPS * AD_TOK) {
-        float kr[AD_TOK][VEC], vr[AD_TOK][VEC];
+        AdRaw<VEC> k_raw[AD_TOK], v_raw[AD_TOK];
         size_t row[AD_TOK];
 #pragma unroll
         for (int u = 0; u < AD_TOK; ++u) {
@@ -111,19 +154,25 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
             row[u] = ((((size_t)pt[jj >> page_shift] * n_kv + kvh) << page_shift) + (jj & page_mask)) * head_dim;
         }
 #pragma unroll
-        for (int u = 0; u < AD_TOK; ++u) ad_load_row<VEC>(k_cache + row[u], lane, head_dim, kr[u]);
+        for (int u = 0; u < AD_TOK; ++u) k_raw[u] = ad_load_raw<VEC>(k_cache + row[u], lane, head_dim);
 #pragma unroll
-        for (int u = 0; u < AD_TOK; ++u) ad_load_row<VEC>(v_cache + row[u], lane, head_dim, vr[u]);
+        for (int u = 0; u < AD_TOK; ++u) v_raw[u] = ad_load_raw<VEC>(v_cache + row[u], lane, head_dim);
         float sc[AD_TOK][AD_GROUP];
 #pragma unroll
         for (int u = 0; u < AD_TOK; ++u)
 #pragma unroll
             for (int gi = 0; gi < AD_GROUP; ++gi) {
-                float d = 0.f;
-#pragma unroll
-                for (int e = 0; e < VEC; ++e) d = fmaf(qv[gi][e], kr[u][e], d);
-                sc[u][gi] = d;
+                sc[u][gi] = 0.f;
             }
+#pragma unroll
+        for (int u = 0; u < AD_TOK; ++u) {
+            float kr[VEC];
+            ad_unpack<VEC>(k_raw[u], kr);
+#pragma unroll
+            for (int gi = 0; gi < AD_GROUP; ++gi)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) sc[u][gi] = fmaf(qv[gi][e], kr[e], sc[u][gi]);
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
@@ -144,11 +193,19 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
             for (int u = 0; u < AD_TOK; ++u) {
                 const float pj = (j0 + u <= my_hi) ? __expf(sc[u][gi] - m_new) : 0.f;
                 lsum += pj;
-#pragma unroll
-                for (int e = 0; e < VEC; ++e) acc[gi][e] = fmaf(pj, vr[u][e], acc[gi][e]);
+                sc[u][gi] = pj;
             }
             l[gi] = lsum;
             m[gi] = m_new;
+        }
+#pragma unroll
+        for (int u = 0; u < AD_TOK; ++u) {
+            float vr[VEC];
+            ad_unpack<VEC>(v_raw[u], vr);
+#pragma unroll
+            for (int gi = 0; gi < AD_GROUP; ++gi)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) acc[gi][e] = fmaf(sc[u][gi], vr[e], acc[gi][e]);
         }
     }
 

@@ -1,0 +1,142 @@
+"""Times single kernels at given sizes with CUDA events (inputs larger than L2 are rotated
+so that weights come from DRAM), and reports bytes or FLOPs per second.
+
+    python -m supersonic_b200.csrc.microbench attention_decode --batch 64 --context 520
+    python -m supersonic_b200.csrc.microbench linear --rows 8 --n 6144 --k 4096 [--kernel skinny|tc64|tc128|tc256]
+    python -m supersonic_b200.csrc.microbench attention_prefill --tokens 2048 --seqs 1
+    python -m supersonic_b200.csrc.microbench gemm --rows 2048 --n 28672 --k 4096 --tile 256
+
+One JSON line per run.  It is also the small, self-ending workload that profiler captures
+are taken on.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+from . import ops
+
+DEV = "cuda:0"
+
+
+def _time(fn, iters, warmup=3):
+    """Microseconds per launch: ``iters`` launches captured in one CUDA graph (so that host
+    time per launch does not count) and replayed between two events."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(iters):
+                fn(i)
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / iters * 1e3
+
+
+def attention_decode(args):
+    n_q, n_kv, hd, B, ctx = args.heads, args.kv_heads, args.head_dim, args.batch, args.context
+    pages_per = (ctx + 63) // 64 + 1
+    n_pages = B * pages_per
+    k = torch.randn(n_pages, n_kv, 64, hd, device=DEV).bfloat16()
+    v = torch.randn(n_pages, n_kv, 64, hd, device=DEV).bfloat16()
+    table = torch.randperm(n_pages).to(torch.int32).view(B, pages_per).to(DEV)
+    pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=DEV)
+    slot = torch.arange(B, dtype=torch.int32, device=DEV)
+    q = torch.randn(B, (n_q + 2 * n_kv) * hd, device=DEV).bfloat16()
+    out = torch.empty(B, n_q * hd, dtype=torch.bfloat16, device=DEV)
+    splits = args.splits
+    nf, nc = ops.attention_decode_scratch(B, n_q, n_kv, hd, splits)
+    scratch = torch.empty(max(nf, 1), device=DEV)
+    counters = torch.zeros(max(nc, 1), dtype=torch.int32, device=DEV)
+    us = _time(lambda i: ops.attention_decode(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, None,
+                                              1 / math.sqrt(hd), splits, scratch, counters), args.iters)
+    nbytes = B * ctx * n_kv * hd * 2 * 2
+    return {"kernel": "attention_decode", "batch": B, "context": ctx, "splits": splits, "us": round(us, 2),
+            "GB/s": round(nbytes / us / 1e3, 1)}
+
+
+def linear(args):
+    B, N, K = args.rows, args.n, args.k
+    copies = max(2, int(400e6 // (N * K * 2)) + 1)
+    ws = [(torch.randn(N, K, device=DEV) * 0.02).bfloat16() for _ in range(copies)]
+    x = torch.randn(B, K, device=DEV).bfloat16()
+    out = torch.empty(B, N, dtype=torch.bfloat16, device=DEV)
+    if args.kernel == "skinny":
+        fn = lambda i: ops.skinny_gemm(x, ws[i % copies], out)
+    else:
+        tile = int(args.kernel[2:])
+        fn = lambda i: ops.gemm_tc(x, ws[i % copies], out, tile_n=tile)
+    us = _time(fn, args.iters)
+    ops.check_device_errors()
+    return {"kernel": args.kernel, "rows": B, "n": N, "k": K, "us": round(us, 2),
+            "GB/s": round(N * K * 2 / us / 1e3, 1)}
+
+
+def gemm(args):
+    M, N, K = args.rows, args.n, args.k
+    copies = max(2, int(300e6 // (N * K * 2)) + 1)
+    ws = [(torch.randn(N, K, device=DEV) * 0.02).bfloat16() for _ in range(copies)]
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    us = _time(lambda i: ops.gemm_tc(a, ws[i % copies], out, tile_n=args.tile), args.iters)
+    ops.check_device_errors()
+    return {"kernel": f"gemm_tc{args.tile}", "m": M, "n": N, "k": K, "us": round(us, 2),
+            "TFLOP/s": round(2.0 * M * N * K / us / 1e6, 1)}
+
+
+def attention_prefill(args):
+    n_q, n_kv, hd, S, T = args.heads, args.kv_heads, args.head_dim, args.seqs, args.tokens
+    pages_per = (T + 63) // 64
+    k = torch.randn(S * pages_per, n_kv, 64, hd, device=DEV).bfloat16()
+    v = torch.randn(S * pages_per, n_kv, 64, hd, device=DEV).bfloat16()
+    table = torch.randperm(S * pages_per).to(torch.int32).view(S, pages_per).to(DEV)
+    q = torch.randn(S * T, (n_q + 2 * n_kv) * hd, device=DEV).bfloat16()
+    out = torch.empty(S * T, n_q * hd, dtype=torch.bfloat16, device=DEV)
+    cu = torch.arange(S + 1, dtype=torch.int32, device=DEV) * T
+    start = torch.zeros(S, dtype=torch.int32, device=DEV)
+    slot = torch.arange(S, dtype=torch.int32, device=DEV)
+    us = _time(lambda i: ops.attention_prefill(q, k, v, cu, start, slot, table, out, T, n_q, n_kv, hd, 6, None,
+                                               1 / math.sqrt(hd)), args.iters)
+    flops = S * 4.0 * n_q * hd * T * (T + 1) / 2
+    return {"kernel": "attention_prefill", "seqs": S, "tokens": T, "us": round(us, 2),
+            "TFLOP/s": round(flops / us / 1e6, 1)}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    sub = ap.add_subparsers(dest="what", required=True)
+    for name in ("attention_decode", "linear", "gemm", "attention_prefill"):
+        p = sub.add_parser(name)
+        p.add_argument("--iters", type=int, default=20)
+        p.add_argument("--heads", type=int, default=32)
+        p.add_argument("--kv-heads", type=int, default=8)
+        p.add_argument("--head-dim", type=int, default=128)
+        p.add_argument("--batch", type=int, default=8)
+        p.add_argument("--context", type=int, default=520)
+        p.add_argument("--splits", type=int, default=8)
+        p.add_argument("--rows", type=int, default=8)
+        p.add_argument("--n", type=int, default=6144)
+        p.add_argument("--k", type=int, default=4096)
+        p.add_argument("--kernel", default="skinny")
+        p.add_argument("--tile", type=int, default=256)
+        p.add_argument("--seqs", type=int, default=1)
+        p.add_argument("--tokens", type=int, default=2048)
+    args = ap.parse_args(argv)
+    print(json.dumps(globals()[args.what](args)))
+
+
+if __name__ == "__main__":
+    main()
