@@ -18,6 +18,7 @@ constexpr int AD_THREADS = AD_WARPS * 32;
 constexpr int AD_GROUP = 4;
 constexpr int AD_MAX_VEC = 8;
 constexpr int AD_TOK = 8;            // keys per warp and turn
+constexpr int AD_MAX_SPLITS = 64;
 
 template <int VEC>
 __device__ __forceinline__ void ad_load_row(const __nv_bfloat16* p, int lane, int head_dim, float (&v)[VEC]) {
@@ -89,16 +90,24 @@ __device__ __forceinline__ void ad_unpack(const AdRaw<VEC>& r, float (&v)[VEC]) 
         v[e] = __uint_as_float(((r.w[e / 2] >> (16 * (e & 1))) & 0xffffu) << 16);      // bfloat16 -> float32
 }
 
-template <int VEC>
+// FUSE: the rows of ``q`` are the raw output of the fused q/k/v projection
+// ([q heads | k heads | v heads]); the kernel rotates the queries by the token's position, and
+// the block that owns the token's page also rotates its key, writes key and value into the
+// cache and attends to them from registers.  Needs head_dim == 32 * VEC and a full-width rotation.
+template <int VEC, bool FUSE>
 __global__ void __launch_bounds__(AD_THREADS)
-attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k_cache,
-                        const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ pos,
+attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* k_cache,
+                        __nv_bfloat16* v_cache, const int* __restrict__ pos,
                         const int* __restrict__ slot, const int* __restrict__ page_table, int max_pages,
                         __nv_bfloat16* __restrict__ out, int ldo, int n_q, int n_kv, int head_dim, int page_shift,
                         int window, float scale, int n_splits, float* __restrict__ scratch,
-                        int* __restrict__ counters) {
+                        int* __restrict__ counters, const float* __restrict__ cos_t,
+                        const float* __restrict__ sin_t) {
     __shared__ float sm_m[AD_WARPS][AD_GROUP], sm_l[AD_WARPS][AD_GROUP];
     __shared__ float sm_acc[AD_WARPS][AD_GROUP][32 * VEC];
+    __shared__ float sm_f[AD_GROUP][AD_MAX_SPLITS];          // per split: exp(max_split - max_all)
+    __shared__ float sm_pm[AD_GROUP][AD_MAX_SPLITS], sm_pl[AD_GROUP][AD_MAX_SPLITS];
+    __shared__ float sm_L[AD_GROUP];
     __shared__ int is_last;
     const int b = blockIdx.x, split = blockIdx.z;
     const int group = n_q / n_kv;
@@ -107,6 +116,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
     const int h0 = kvh * group + sub * AD_GROUP;                 // first query head of this block
     const int n_heads = min(AD_GROUP, group - sub * AD_GROUP);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();                                              // everything read below may be a predecessor's
     const int s = slot[b];
     if (s < 0) {                                                 // padding row: zeros, no bookkeeping
         if (split == 0)
@@ -121,13 +132,32 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
     const int n_pages = page_hi - page_lo + 1;
     const int per = (n_pages + n_splits - 1) / n_splits;
     const int my_lo = max(lo, (page_lo + split * per) << page_shift);
-    const int my_hi = min(p, ((page_lo + (split + 1) * per) << page_shift) - 1);
+    const bool owns_new = FUSE && my_lo <= p && p <= ((page_lo + (split + 1) * per) << page_shift) - 1;
+    // with FUSE the token's own key is not in the cache yet: cached keys end at p - 1
+    const int my_hi = min(FUSE ? p - 1 : p, ((page_lo + (split + 1) * per) << page_shift) - 1);
 
+    // rotation of this lane's elements: pairs (i, i + head_dim/2) live in lanes l and l ^ 16
+    float rc[VEC], rs[VEC];
+    if (FUSE) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            const int i = (lane & 15) * VEC + e;
+            rc[e] = cos_t[(size_t)p * (head_dim / 2) + i];
+            rs[e] = (lane < 16 ? -1.f : 1.f) * sin_t[(size_t)p * (head_dim / 2) + i];
+        }
+    }
     float qv[AD_GROUP][VEC];
 #pragma unroll
     for (int gi = 0; gi < AD_GROUP; ++gi) {
         if (gi < n_heads) {
             ad_load_row<VEC>(q + (size_t)b * ldq + (size_t)(h0 + gi) * head_dim, lane, head_dim, qv[gi]);
+            if (FUSE) {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    const float other = __shfl_xor_sync(0xffffffffu, qv[gi][e], 16);
+                    qv[gi][e] = qv[gi][e] * rc[e] + other * rs[e];
+                }
+            }
 #pragma unroll
             for (int e = 0; e < VEC; ++e) qv[gi][e] *= scale;
         } else {
@@ -209,6 +239,44 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
         }
     }
 
+    if (FUSE && owns_new && warp == 0) {
+        // the token's own key and value: from the projection's output, not from the cache
+        const __nv_bfloat16* k_src = q + (size_t)b * ldq + (size_t)(n_q + kvh) * head_dim;
+        const __nv_bfloat16* v_src = k_src + (size_t)n_kv * head_dim;
+        AdRaw<VEC> k_raw = ad_load_raw<VEC>(k_src, lane, head_dim);
+        const AdRaw<VEC> v_raw = ad_load_raw<VEC>(v_src, lane, head_dim);
+        float kr[VEC], vr[VEC];
+        ad_unpack<VEC>(k_raw, kr);
+        ad_unpack<VEC>(v_raw, vr);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, kr[e], 16);
+            kr[e] = __bfloat162float(__float2bfloat16_rn(kr[e] * rc[e] + other * rs[e]));   // as the cache will hold it
+        }
+        if (sub == 0) {
+            const size_t row = ((((size_t)pt[p >> page_shift] * n_kv + kvh) << page_shift) + (p & page_mask)) * head_dim;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                k_cache[row + lane * VEC + e] = __float2bfloat16_rn(kr[e]);
+                v_cache[row + lane * VEC + e] = __float2bfloat16_rn(vr[e]);
+            }
+        }
+#pragma unroll
+        for (int gi = 0; gi < AD_GROUP; ++gi) {
+            float sc = 0.f;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) sc = fmaf(qv[gi][e], kr[e], sc);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+            const float m_new = fmaxf(m[gi], sc);
+            const float alpha = __expf(m[gi] - m_new), pj = __expf(sc - m_new);
+            l[gi] = l[gi] * alpha + pj;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) acc[gi][e] = fmaf(pj, vr[e], acc[gi][e] * alpha);
+            m[gi] = m_new;
+        }
+    }
+
     // merge the 4 warps in warp order
 #pragma unroll
     for (int gi = 0; gi < AD_GROUP; ++gi) {
@@ -254,19 +322,44 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // 1. every split's (max, sum) of every head -> shared memory
+    for (int e = threadIdx.x; e < n_heads * n_splits; e += AD_THREADS) {
+        const int gi = e / n_splits, sp = e % n_splits;
+        const float* part = scratch + (((size_t)b * n_q + h0 + gi) * n_splits + sp) * (head_dim + 2);
+        sm_pm[gi][sp] = __ldcg(part + head_dim);
+        sm_pl[gi][sp] = __ldcg(part + head_dim + 1);
+    }
+    __syncthreads();
+    // 2. per head: overall max, each split's factor, overall sum (in split order)
+    if (threadIdx.x < n_heads) {
+        const int gi = threadIdx.x;
+        float mm = -INFINITY;
+        for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, sm_pm[gi][sp]);
+        float ll = 0.f;
+        for (int sp = 0; sp < n_splits; ++sp) {
+            const float f = (sm_pm[gi][sp] == -INFINITY) ? 0.f : __expf(sm_pm[gi][sp] - mm);
+            sm_f[gi][sp] = f;
+            ll += sm_pl[gi][sp] * f;
+        }
+        sm_L[gi] = ll;
+    }
+    __syncthreads();
+    // 3. weighted sum of the splits' values, in split order, loads four at a time
     for (int e = threadIdx.x; e < n_heads * head_dim; e += AD_THREADS) {
         const int gi = e / head_dim, d = e % head_dim;
-        const float* base = scratch + ((size_t)b * n_q + h0 + gi) * n_splits * (head_dim + 2);
-        float mm = -INFINITY;
-        for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, __ldcg(base + (size_t)sp * (head_dim + 2) + head_dim));
-        float ll = 0.f, a = 0.f;
-        for (int sp = 0; sp < n_splits; ++sp) {
-            const float* part = base + (size_t)sp * (head_dim + 2);
-            const float pm = __ldcg(part + head_dim);
-            const float f = (pm == -INFINITY) ? 0.f : __expf(pm - mm);
-            ll += __ldcg(part + head_dim + 1) * f;
-            a += __ldcg(part + d) * f;
+        const float* base = scratch + ((size_t)b * n_q + h0 + gi) * n_splits * (head_dim + 2) + d;
+        float a = 0.f;
+        int sp = 0;
+        for (; sp + 4 <= n_splits; sp += 4) {
+            const float v0 = __ldcg(base + (size_t)(sp + 0) * (head_dim + 2));
+            const float v1 = __ldcg(base + (size_t)(sp + 1) * (head_dim + 2));
+            const float v2 = __ldcg(base + (size_t)(sp + 2) * (head_dim + 2));
+            const float v3 = __ldcg(base + (size_t)(sp + 3) * (head_dim + 2));
+            a = fmaf(v0, sm_f[gi][sp], a); a = fmaf(v1, sm_f[gi][sp + 1], a);
+            a = fmaf(v2, sm_f[gi][sp + 2], a); a = fmaf(v3, sm_f[gi][sp + 3], a);
         }
+        for (; sp < n_splits; ++sp) a = fmaf(__ldcg(base + (size_t)sp * (head_dim + 2)), sm_f[gi][sp], a);
+        const float ll = sm_L[gi];
         out[(size_t)b * ldo + (size_t)(h0 + gi) * head_dim + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
     }
 }
@@ -286,19 +379,30 @@ static inline int ad_counters(int n_seqs, int n_q, int n_kv) {
 static inline int ad_launch(const void* q, int ldq, const void* k_cache, const void* v_cache, const int* pos,
                             const int* slot, const int* page_table, int max_pages, void* out, int ldo,
                             int n_seqs, int n_q, int n_kv, int head_dim, int page_shift, int window,
-                            float scale, int n_splits, float* scratch, int* counters, cudaStream_t stream) {
+                            float scale, int n_splits, float* scratch, int* counters, cudaStream_t stream,
+                            bool pdl = false, const float* cos_t = nullptr, const float* sin_t = nullptr) {
     typedef __nv_bfloat16 bf16;
     if (n_seqs <= 0) return 0;
-    if (head_dim <= 0 || head_dim > 32 * AD_MAX_VEC || n_kv <= 0 || n_q % n_kv || n_splits < 1)
+    if (head_dim <= 0 || head_dim > 32 * AD_MAX_VEC || n_kv <= 0 || n_q % n_kv || n_splits < 1 ||
+        n_splits > AD_MAX_SPLITS)
         return SSB_ERR_BAD_SIZE;
+    const bool fuse = cos_t != nullptr;
+    if (fuse && (!sin_t || head_dim % 32 || (head_dim != 32 && head_dim != 64 && head_dim != 128 && head_dim != 256)))
+        return SSB_ERR_UNSUPPORTED;
     if (n_splits > 1 && (!scratch || !counters)) return SSB_ERR_BAD_SIZE;
     const int group = n_q / n_kv;
     dim3 grid(n_seqs, n_kv * ((group + AD_GROUP - 1) / AD_GROUP), n_splits);
     const int vec = (head_dim + 31) / 32;
+    int rc = 0;
 #define SSB_AD(V) \
-    attention_decode_kernel<V><<<grid, AD_THREADS, 0, stream>>>( \
-        (const bf16*)q, ldq, (const bf16*)k_cache, (const bf16*)v_cache, pos, slot, page_table, max_pages, \
-        (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters)
+    rc = fuse ? ssb_launch(attention_decode_kernel<V, true>, grid, dim3(AD_THREADS), 0, stream, pdl, \
+                    (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
+                    (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters, \
+                    cos_t, sin_t) \
+              : ssb_launch(attention_decode_kernel<V, false>, grid, dim3(AD_THREADS), 0, stream, pdl, \
+                    (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
+                    (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters, \
+                    cos_t, sin_t)
     // vector loads need VEC elements aligned: rows are head_dim * 2 bytes apart
     if (vec == 1) SSB_AD(1);
     else if (vec == 2 && head_dim % 2 == 0 && ldq % 2 == 0) SSB_AD(2);
@@ -306,5 +410,5 @@ static inline int ad_launch(const void* q, int ldq, const void* k_cache, const v
     else if (vec <= 8 && head_dim % 8 == 0 && ldq % 8 == 0) SSB_AD(8);
     else return SSB_ERR_UNSUPPORTED;
 #undef SSB_AD
-    return ssb_launch_status();
+    return rc ? rc : ssb_launch_status();
 }

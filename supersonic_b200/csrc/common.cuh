@@ -42,3 +42,29 @@ __device__ __forceinline__ size_t ssb_cache_row(const int* __restrict__ page_tab
     const size_t tok = ((size_t)page * n_kv_heads + kv_head) << page_shift;
     return (tok + (size_t)(pos & ((1 << page_shift) - 1))) * (size_t)head_dim;
 }
+
+// Programmatic dependent launch: a kernel launched with the attribute may start while its
+// predecessor still runs.  Before ssb_pdl_wait() it must only read memory that no kernel of
+// the chain writes (weights); after it, everything the predecessor wrote is visible.
+// Both are no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void ssb_pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void ssb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launch with or without the programmatic-dependent-launch attribute.
+template <typename... KArgs, typename... Args>
+static inline int ssb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -68,21 +68,14 @@ skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restric
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * ROWS;
 
-    if (NORM) {
-        // 1 / rms of each input row, float32, fixed order: warp w sums rows w, w + 8, ...
-        const float* xf = (const float*)x_in;
-        for (int b = warp; b < COLS; b += SG_WARPS) {
-            float s = 0.f;
-            if (b < n_rows)
-                for (int k = lane * 4; k < K; k += 128) {
-                    const float4 v = *reinterpret_cast<const float4*>(xf + (size_t)b * ldx + k);
-                    s = fmaf(v.x, v.x, s); s = fmaf(v.y, v.y, s); s = fmaf(v.z, v.z, s); s = fmaf(v.w, v.w, s);
-                }
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (lane == 0) inv_rms[b] = 1.0f / sqrtf(s / (float)K + eps);
-        }
-        __syncthreads();
+    // The head of the block's slab of W goes to L2 ahead of use (one bulk prefetch per row).
+    // Weights are written by no kernel, so this may run before the predecessor has finished.
+    if (threadIdx.x < ROWS) {
+        const bf16* row = W + (size_t)min(n0 + (int)threadIdx.x, N - 1) * ldw;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(row), "r"(min(K * 2, 4096)) : "memory");
     }
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();                                     // x (and out) belong to the predecessor until here
 
     float acc[RM][NB][4];
 #pragma unroll
@@ -99,11 +92,13 @@ skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restric
         w_row[i][0] = W + (size_t)min(n0 + i * 16 + g, N - 1) * ldw;
         w_row[i][1] = W + (size_t)min(n0 + i * 16 + g + 8, N - 1) * ldw;
     }
-    float my_inv[NB];
-    if (NORM) {
+    // NORM: x is the float32 residual.  RMSNorm's per-row scale factors out of the product,
+    //   out[b, n] = rsqrt(mean_k x[b,k]^2 + eps) * sum_k (x[b,k] w[k]) W[n,k],
+    // so the loop multiplies by the norm weight only and sums the squares on the side; every
+    // x[b, k] passes through exactly one lane of the block, and the epilogue applies the scale.
+    float ssq[NB];
 #pragma unroll
-        for (int j = 0; j < NB; ++j) my_inv[j] = inv_rms[j * 8 + g];
-    }
+    for (int j = 0; j < NB; ++j) ssq[j] = 0.f;
 
     const int n_chunks = (K + 31) / 32;
     for (int c0 = warp; c0 < n_chunks; c0 += SG_WARPS * SG_UNROLL) {
@@ -142,11 +137,14 @@ skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restric
                             w[2 * e] = f.x; w[2 * e + 1] = f.y;
                         }
                     }
-                    const float s = my_inv[j];
-                    xb[u][j].x = pack_bf16(v0.x * s * w[0], v0.y * s * w[1]);
-                    xb[u][j].y = pack_bf16(v0.z * s * w[2], v0.w * s * w[3]);
-                    xb[u][j].z = pack_bf16(v1.x * s * w[4], v1.y * s * w[5]);
-                    xb[u][j].w = pack_bf16(v1.z * s * w[6], v1.w * s * w[7]);
+                    ssq[j] = fmaf(v0.x, v0.x, ssq[j]); ssq[j] = fmaf(v0.y, v0.y, ssq[j]);
+                    ssq[j] = fmaf(v0.z, v0.z, ssq[j]); ssq[j] = fmaf(v0.w, v0.w, ssq[j]);
+                    ssq[j] = fmaf(v1.x, v1.x, ssq[j]); ssq[j] = fmaf(v1.y, v1.y, ssq[j]);
+                    ssq[j] = fmaf(v1.z, v1.z, ssq[j]); ssq[j] = fmaf(v1.w, v1.w, ssq[j]);
+                    xb[u][j].x = pack_bf16(v0.x * w[0], v0.y * w[1]);
+                    xb[u][j].y = pack_bf16(v0.z * w[2], v0.w * w[3]);
+                    xb[u][j].z = pack_bf16(v1.x * w[4], v1.y * w[5]);
+                    xb[u][j].w = pack_bf16(v1.z * w[6], v1.w * w[7]);
                 } else {
                     xb[u][j] = *reinterpret_cast<const uint4*>((const bf16*)x_in + (size_t)b * ldx + k);
                 }
@@ -176,7 +174,26 @@ skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restric
             r[(g + 8) * COLS + 2 * t] = acc[i][j][2];
             r[(g + 8) * COLS + 2 * t + 1] = acc[i][j][3];
         }
+    if (NORM) {
+        float* part = inv_rms + COLS;                   // [SG_WARPS][COLS]
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            float v = ssq[j];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);    // the four lanes that share batch row g
+            if (t == 0) part[warp * COLS + j * 8 + g] = v;
+        }
+    }
     __syncthreads();
+    if (NORM) {
+        if (threadIdx.x < COLS) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < SG_WARPS; ++w) v += inv_rms[COLS + w * COLS + threadIdx.x];
+            inv_rms[threadIdx.x] = 1.0f / sqrtf(v / (float)K + eps);
+        }
+        __syncthreads();
+    }
 
     if (mode == SG_SWIGLU) {
         // rows come as [8 gate | 8 up] per 16: out[b, n0/2 + j] = silu(gate_j) * up_j
@@ -190,6 +207,7 @@ skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restric
                 gate += red[((size_t)w * ROWS + r_gate) * COLS + b];
                 up += red[((size_t)w * ROWS + r_gate + 8) * COLS + b];
             }
+            if (NORM) { gate *= inv_rms[b]; up *= inv_rms[b]; }
             ((bf16*)out)[(size_t)b * ldo + n_out] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
         }
         return;
@@ -201,6 +219,7 @@ skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restric
         float s = 0.f;
 #pragma unroll
         for (int w = 0; w < SG_WARPS; ++w) s += red[((size_t)w * ROWS + r) * COLS + b];
+        if (NORM) s *= inv_rms[b];
         const size_t o = (size_t)b * ldo + n;
         if (mode == SG_ACCUMULATE) ((float*)out)[o] += s;
         else if (out_is_f32) ((float*)out)[o] = s;
@@ -211,26 +230,26 @@ skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restric
 template <int RM, int NB, bool NORM>
 static int launch_skinny(const void* x, int ldx, const void* norm_w, int norm_w_is_f32, float eps,
                          const bf16* W, int ldw, void* out, int ldo, int out_is_f32, int n_rows, int N,
-                         int K, int mode, cudaStream_t stream) {
+                         int K, int mode, int pdl, cudaStream_t stream) {
     constexpr int ROWS = 16 * RM, COLS = 8 * NB;
-    const size_t smem = (size_t)(SG_WARPS * ROWS * COLS + COLS) * sizeof(float);
+    const size_t smem = (size_t)(SG_WARPS * ROWS * COLS + COLS + SG_WARPS * COLS) * sizeof(float);
     auto kern = skinny_gemm_kernel<RM, NB, NORM>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    kern<<<(N + ROWS - 1) / ROWS, SG_THREADS, smem, stream>>>(x, ldx, norm_w, norm_w_is_f32, eps, W, ldw,
-                                                            out, ldo, out_is_f32, n_rows, N, K, mode);
-    return ssb_launch_status();
+    return ssb_launch(kern, dim3((N + ROWS - 1) / ROWS), dim3(SG_THREADS), smem, stream, pdl != 0, x, ldx, norm_w,
+                      norm_w_is_f32, eps, W, ldw, out, ldo, out_is_f32, n_rows, N, K, mode);
 }
 
 // x: bfloat16 [n_rows, K] (norm_w == null) or the float32 residual [n_rows, K] normalised on the
 // way in with norm_w (bfloat16 or float32) and eps.  W: bfloat16 [N, K].  mode 0: out[b, n]
 // (bfloat16 or float32); mode 1: out (float32) += ; mode 2: W's rows come as [8 gate | 8 up] per
-// 16 and out (bfloat16, [n_rows, N/2]) = silu(gate) * up.
+// 16 and out (bfloat16, [n_rows, N/2]) = silu(gate) * up.  pdl: launch as a programmatic
+// dependent of the kernel before it on the stream (weights are prefetched while that one ends).
 SSB_API int ssb_skinny_gemm(const void* x, int ldx, const void* norm_w, int norm_w_dtype, float eps,
                             const void* W, int ldw, void* out, int ldo, int out_dtype, int n_rows, int N,
-                            int K, int mode, cudaStream_t stream) {
+                            int K, int mode, int pdl, cudaStream_t stream) {
     if (n_rows <= 0 || N <= 0) return 0;
     if (n_rows > 64 || K <= 0 || K % 8 || ldw % 8 || ldx % 8) return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)x | (uintptr_t)W | (uintptr_t)norm_w) & 15) return SSB_ERR_BAD_SIZE;
@@ -239,8 +258,8 @@ SSB_API int ssb_skinny_gemm(const void* x, int ldx, const void* norm_w, int norm
     const int f32o = out_dtype == SSB_F32, nwf = norm_w_dtype == SSB_F32;
     const bf16* Wb = (const bf16*)W;
 #define SSB_SG(RM, NB) \
-    return norm_w ? launch_skinny<RM, NB, true>(x, ldx, norm_w, nwf, eps, Wb, ldw, out, ldo, f32o, n_rows, N, K, mode, stream) \
-                  : launch_skinny<RM, NB, false>(x, ldx, nullptr, 0, 0.f, Wb, ldw, out, ldo, f32o, n_rows, N, K, mode, stream)
+    return norm_w ? launch_skinny<RM, NB, true>(x, ldx, norm_w, nwf, eps, Wb, ldw, out, ldo, f32o, n_rows, N, K, mode, pdl, stream) \
+                  : launch_skinny<RM, NB, false>(x, ldx, nullptr, 0, 0.f, Wb, ldw, out, ldo, f32o, n_rows, N, K, mode, pdl, stream)
     if (n_rows <= 8) { SSB_SG(1, 1); }
     if (n_rows <= 16) { SSB_SG(2, 2); }
     if (n_rows <= 32) { SSB_SG(2, 4); }
@@ -252,7 +271,9 @@ SSB_API int ssb_skinny_gemm(const void* x, int ldx, const void* norm_w, int norm
 // decode attention, keys split over blocks (kernel in attention_decode.cuh)
 // ---------------------------------------------------------------------------------------
 // Scratch: n_seqs * n_q * n_splits * (head_dim + 2) floats; counters: n_seqs * gridDim.y ints,
-// zero before the first launch (every launch leaves them zero).
+// zero before the first launch (every launch leaves them zero).  With cos_t/sin_t
+// ([positions, head_dim/2] float32) the rows of q are the raw fused projection [q | k | v]: the
+// kernel rotates queries and the token's key itself and appends key and value to the cache.
 SSB_API long long ssb_attention_decode_scratch_floats(int n_seqs, int n_q, int head_dim, int n_splits) {
     return ad_scratch_floats(n_seqs, n_q, head_dim, n_splits);
 }
@@ -265,7 +286,9 @@ SSB_API int ssb_attention_decode(const void* q, int ldq, const void* k_cache, co
                                  const int* pos, const int* slot, const int* page_table, int max_pages,
                                  void* out, int ldo, int n_seqs, int n_q, int n_kv, int head_dim,
                                  int page_shift, int window, float scale, int n_splits, float* scratch,
-                                 int* counters, cudaStream_t stream) {
+                                 int* counters, int pdl, const float* cos_t, const float* sin_t,
+                                 cudaStream_t stream) {
     return ad_launch(q, ldq, k_cache, v_cache, pos, slot, page_table, max_pages, out, ldo, n_seqs, n_q, n_kv,
-                     head_dim, page_shift, window, scale, n_splits, scratch, counters, stream);
+                     head_dim, page_shift, window, scale, n_splits, scratch, counters, stream, pdl != 0,
+                     cos_t, sin_t);
 }

@@ -13,7 +13,7 @@ import torch
 from . import ops
 from .kernel_sets import NormedInput, PlainKernels, as_tensor
 
-FUSED_NORM_MAX_ROWS = 4        # above this each block would re-read too much of the residual
+FUSED_NORM_MAX_ROWS = 8        # above this each block would re-read too much of the residual
 SKINNY_MAX_ROWS = 16          # above this the tcgen05 GEMM streams the weights faster (measured)
 TARGET_BLOCKS = 1184           # eight small blocks per SM
 
@@ -21,7 +21,9 @@ TARGET_BLOCKS = 1184           # eight small blocks per SM
 class FastKernels(PlainKernels):
     name = "fast"
 
-    def __init__(self):
+    def __init__(self, pdl: bool = True):
+        self.pdl = pdl           # decode kernels launch as programmatic dependents of their predecessors
+        self.fuse_rope = True    # decode attention rotates q/k and appends to the cache itself
         self._scratch: Dict[str, torch.Tensor] = {}
         self._retired = []      # outgrown buffers stay alive: captured graphs still point at them
 
@@ -30,11 +32,11 @@ class FastKernels(PlainKernels):
         if isinstance(x, NormedInput):
             if (x._tensor is None and x.fusable and x.n_rows <= FUSED_NORM_MAX_ROWS
                     and ops.skinny_gemm_ok(x.residual, weight, True) and x.weight.data_ptr() % 16 == 0):
-                ops.skinny_gemm(x.residual, weight, out, mode, norm_weight=x.weight, eps=x.eps)
+                ops.skinny_gemm(x.residual, weight, out, mode, norm_weight=x.weight, eps=x.eps, pdl=self.pdl)
                 return True
             x = x.tensor()
         if ops.skinny_gemm_ok(x, weight, False):
-            ops.skinny_gemm(x, weight, out, mode)
+            ops.skinny_gemm(x, weight, out, mode, pdl=self.pdl)
             return True
         return False
 
@@ -91,21 +93,42 @@ class FastKernels(PlainKernels):
             self._scratch[name] = t
         return t
 
+    def _decode_attention(self, q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim,
+                          page_shift, window, scale, cos=None, sin=None):
+        group = n_q // n_kv
+        blocks = batch.n_seqs * n_kv * ((group + 3) // 4)
+        pages = batch.kv_pages if not window else min(batch.kv_pages, (window >> page_shift) + 2)
+        n_splits = max(1, min(TARGET_BLOCKS // blocks, pages, 64))
+        scratch = counters = None
+        if n_splits > 1:
+            nf, nc = ops.attention_decode_scratch(batch.n_seqs, n_q, n_kv, head_dim, n_splits)
+            scratch = self._buffer("attn_partials", nf, torch.float32, q.device)
+            counters = self._buffer("attn_counters", nc, torch.int32, q.device, zero=True)
+        ops.attention_decode(q, k_cache, v_cache, batch.pos, batch.slot_of_token, page_table, out,
+                             n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters,
+                             pdl=self.pdl, cos=cos, sin=sin)
+
+    def rope_attention(self, qkv, position, kv, batch, out, n_q, n_kv, head_dim, page_shift, window,
+                       scale) -> bool:
+        tables = getattr(position, "rotary_tables", None)
+        if not (self.fuse_rope and batch.is_decode and tables and qkv.dtype == torch.bfloat16
+                and head_dim in (32, 64, 128, 256) and qkv.stride(0) % 8 == 0):
+            return False
+        cos, sin, rotary_dim = tables()
+        if rotary_dim != head_dim:
+            return False
+        position.check_range(batch)
+        k_cache, v_cache, page_table, _ = kv
+        self._decode_attention(qkv, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim,
+                               page_shift, window, scale, cos, sin)
+        return True
+
     def attention(self, q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim, page_shift,
                   window: Optional[int], scale: float):
         if batch.is_decode and q.dtype == torch.bfloat16 and head_dim <= 256 and head_dim % 16 == 0 \
                 and q.stride(0) % 8 == 0:
-            group = n_q // n_kv
-            blocks = batch.n_seqs * n_kv * ((group + 3) // 4)
-            pages = batch.kv_pages if not window else min(batch.kv_pages, (window >> page_shift) + 2)
-            n_splits = max(1, min(TARGET_BLOCKS // blocks, pages, 64))
-            scratch = counters = None
-            if n_splits > 1:
-                nf, nc = ops.attention_decode_scratch(batch.n_seqs, n_q, n_kv, head_dim, n_splits)
-                scratch = self._buffer("attn_partials", nf, torch.float32, q.device)
-                counters = self._buffer("attn_counters", nc, torch.int32, q.device, zero=True)
-            ops.attention_decode(q, k_cache, v_cache, batch.pos, batch.slot_of_token, page_table, out,
-                                 n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters)
+            self._decode_attention(q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim,
+                                   page_shift, window, scale)
             return
         if not batch.is_decode and ops.attention_prefill_ok(q, head_dim) and out.stride(0) % 2 == 0:
             ops.attention_prefill(q, k_cache, v_cache, batch.cu_new, batch.seq_start, batch.seq_slot,

@@ -80,6 +80,12 @@ class PlainKernels:
         ops.rope_append(qkv, cos, sin, batch.pos, batch.slot_of_token, page_table, k_cache, v_cache,
                         n_q, n_kv, head_dim, rotary_dim, page_shift, write_cache)
 
+    def rope_attention(self, qkv, position, kv, batch, out, n_q, n_kv, head_dim, page_shift, window,
+                       scale) -> bool:
+        """Position encoding, cache append and attention in one launch, if this set can do it
+        for this case; False means the caller runs the two steps separately."""
+        return False
+
     def attention(self, q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim, page_shift,
                   window: Optional[int], scale: float):
         ops.attention_plain(q, k_cache, v_cache, batch.pos, batch.slot_of_token, page_table, out,

@@ -75,13 +75,13 @@ def linear(args):
     x = torch.randn(B, K, device=DEV).bfloat16()
     out = torch.empty(B, N, dtype=torch.bfloat16, device=DEV)
     if args.kernel == "skinny":
-        fn = lambda i: ops.skinny_gemm(x, ws[i % copies], out)
+        fn = lambda i: ops.skinny_gemm(x, ws[i % copies], out, pdl=args.pdl)
     else:
         tile = int(args.kernel[2:])
         fn = lambda i: ops.gemm_tc(x, ws[i % copies], out, tile_n=tile)
     us = _time(fn, args.iters)
     ops.check_device_errors()
-    return {"kernel": args.kernel, "rows": B, "n": N, "k": K, "us": round(us, 2),
+    return {"kernel": args.kernel, "rows": B, "n": N, "k": K, "pdl": bool(args.pdl), "us": round(us, 2),
             "GB/s": round(N * K * 2 / us / 1e3, 1)}
 
 
@@ -132,6 +132,7 @@ def main(argv=None):
         p.add_argument("--k", type=int, default=4096)
         p.add_argument("--kernel", default="skinny")
         p.add_argument("--tile", type=int, default=256)
+        p.add_argument("--pdl", action="store_true", help="launch as programmatic dependents")
         p.add_argument("--seqs", type=int, default=1)
         p.add_argument("--tokens", type=int, default=2048)
     args = ap.parse_args(argv)

@@ -241,9 +241,10 @@ def skinny_gemm_ok(x: torch.Tensor, w: torch.Tensor, normed: bool) -> bool:
 
 
 def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = SG_STORE,
-                norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0) -> None:
+                norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, pdl: bool = False) -> None:
     """out = x @ w^T for up to 64 rows.  With ``norm_weight`` x is the float32 residual and is
-    RMS-normalised on the way in.  mode: store, add into float32 ``out``, or SwiGLU over rows
+    RMS-normalised on the way in.  ``pdl``: launch as a programmatic dependent of the kernel
+    before it on the stream (its weights are prefetched while that kernel ends).  mode: store, add into float32 ``out``, or SwiGLU over rows
     of ``w`` that come as [8 gate | 8 up] per 16 (``out`` is [rows, N/2])."""
     _need(x, "x", torch.float32 if norm_weight is not None else torch.bfloat16, 2)
     _need(w, "w", torch.bfloat16, 2); _need(out, "out", None, 2)
@@ -260,7 +261,7 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int =
         _ptr(x), c_int(x.stride(0)), _ptr(norm_weight),
         c_int(dtype_code(norm_weight.dtype) if norm_weight is not None else 0), c_float(eps), _ptr(w),
         c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(dtype_code(out.dtype)), c_int(B),
-        c_int(N), c_int(K), c_int(mode), _stream()), "skinny_gemm")
+        c_int(N), c_int(K), c_int(mode), c_int(1 if pdl else 0), _stream()), "skinny_gemm")
 
 
 def attention_decode_scratch(n_seqs: int, n_q: int, n_kv: int, head_dim: int, n_splits: int):
@@ -275,8 +276,13 @@ def attention_decode_scratch(n_seqs: int, n_q: int, n_kv: int, head_dim: int, n_
 def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor,
                      slot: torch.Tensor, page_table: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int,
                      head_dim: int, page_shift: int, window: Optional[int], scale: float, n_splits: int,
-                     scratch: Optional[torch.Tensor], counters: Optional[torch.Tensor]) -> None:
-    """One query token per sequence (row) over its cached keys, the keys split ``n_splits`` ways."""
+                     scratch: Optional[torch.Tensor], counters: Optional[torch.Tensor],
+                     pdl: bool = False, cos: Optional[torch.Tensor] = None,
+                     sin: Optional[torch.Tensor] = None) -> None:
+    """One query token per sequence (row) over its cached keys, the keys split ``n_splits`` ways.
+    With ``cos``/``sin`` ([positions, head_dim/2] float32) the rows of ``q`` are the raw fused
+    projection [q | k | v]: queries and the token's key are rotated inside the kernel, and key
+    and value are appended to the cache (no separate rope/append launch)."""
     _need(q, "q", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
     _need(k_cache, "k_cache", torch.bfloat16); _need(v_cache, "v_cache", torch.bfloat16)
     _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
@@ -284,6 +290,14 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     B = q.shape[0]
     if pos.shape[0] != B or slot.shape[0] != B or out.shape[0] != B:
         raise KernelError("attention_decode: one position, slot and output row per sequence")
+    if cos is not None:
+        _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+        if cos.shape != sin.shape or cos.shape[1] * 2 != head_dim or not (cos.is_contiguous() and sin.is_contiguous()):
+            raise KernelError("attention_decode: cos/sin must be [positions, head_dim/2], contiguous")
+        if head_dim not in (32, 64, 128, 256) or q.shape[1] < (n_q + 2 * n_kv) * head_dim:
+            raise KernelError("attention_decode: fused rotation needs head_dim 32/64/128/256 and [q|k|v] rows")
+    if n_splits > 64:
+        raise KernelError("attention_decode: at most 64 splits")
     if n_splits > 1:
         need_f, need_c = attention_decode_scratch(B, n_q, n_kv, head_dim, n_splits)
         _need(scratch, "scratch", torch.float32); _need(counters, "counters", torch.int32)
@@ -293,7 +307,8 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         _ptr(q), c_int(q.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(pos), _ptr(slot), _ptr(page_table),
         c_int(page_table.shape[1]), _ptr(out), c_int(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv),
         c_int(head_dim), c_int(page_shift), c_int(int(window) if window else 0), c_float(scale),
-        c_int(n_splits), _ptr(scratch), _ptr(counters), _stream()), "attention_decode")
+        c_int(n_splits), _ptr(scratch), _ptr(counters), c_int(1 if pdl else 0), _ptr(cos), _ptr(sin),
+        _stream()), "attention_decode")
 
 
 # ---- prefill GEMM on tcgen05 ---------------------------------------------------------------

@@ -61,9 +61,12 @@ class Attention:
         width = (self.n_q + (2 * self.n_kv if writes_cache else 0)) * self.head_dim
         qkv = torch.empty((T, width), dtype=self.dtype, device=residual.device)
         ctx.kernels.linear(x, self.w_qkv if writes_cache else self.w_q, qkv)
-        position.encode_and_append(ctx, qkv, kv, self.n_q, self.n_kv, writes_cache)
         attn = torch.empty((T, self.n_q * self.head_dim), dtype=self.dtype, device=residual.device)
-        k_cache, v_cache, table, _ = kv
-        ctx.kernels.attention(qkv, k_cache, v_cache, ctx.batch, table, attn, self.n_q, self.n_kv,
-                              self.head_dim, PAGE_SHIFT, self.window, self.scale)
+        if not (writes_cache and ctx.kernels.rope_attention(qkv, position, kv, ctx.batch, attn, self.n_q,
+                                                           self.n_kv, self.head_dim, PAGE_SHIFT,
+                                                           self.window, self.scale)):
+            position.encode_and_append(ctx, qkv, kv, self.n_q, self.n_kv, writes_cache)
+            k_cache, v_cache, table, _ = kv
+            ctx.kernels.attention(qkv, k_cache, v_cache, ctx.batch, table, attn, self.n_q, self.n_kv,
+                                  self.head_dim, PAGE_SHIFT, self.window, self.scale)
         ctx.kernels.linear(attn, self.w_o, residual, accumulate=True)

@@ -52,10 +52,17 @@ class Rotary:
         self.cos = angle.cos().to(torch.float32).contiguous()
         self.sin = angle.sin().to(torch.float32).contiguous()
 
-    def encode_and_append(self, ctx, qkv, kv, n_q, n_kv, write_cache=True):
-        if ctx.batch.max_total > self.max_positions:
-            raise ValueError(f"a sequence reaches {ctx.batch.max_total} tokens, beyond the "
+    def check_range(self, batch) -> None:
+        if batch.max_total > self.max_positions:
+            raise ValueError(f"a sequence reaches {batch.max_total} tokens, beyond the "
                              f"{self.max_positions} positions this model encodes")
+
+    def rotary_tables(self):
+        """(cos, sin, rotary_dim) for kernels that rotate inside another operation."""
+        return self.cos, self.sin, self.rotary_dim
+
+    def encode_and_append(self, ctx, qkv, kv, n_q, n_kv, write_cache=True):
+        self.check_range(ctx.batch)
         k_cache, v_cache, table, group = kv
         from ..cache import PAGE_SHIFT
         ctx.kernels.rope_append(qkv, self.cos, self.sin, ctx.batch, table, k_cache, v_cache, n_q, n_kv,

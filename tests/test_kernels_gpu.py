@@ -300,15 +300,19 @@ def test_skinny_gemm_with_norm_on_the_way_in(rows, wdtype):
     w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
     normed = torch.empty(rows, K, dtype=torch.bfloat16, device=DEV)
     ops().rmsnorm(res, nw, 1e-5, normed)
-    want = torch.empty(rows, N, device=DEV)
-    ops().skinny_gemm(normed, w, want)
+    unfused = torch.empty(rows, N, device=DEV)
+    ops().skinny_gemm(normed, w, unfused)
     got = torch.empty(rows, N, device=DEV)
     ops().skinny_gemm(res, w, got, norm_weight=nw, eps=1e-5)
-    # same arithmetic except the order of the sum of squares: a last-bit difference of the
-    # scale can flip a bfloat16 rounding of single inputs
-    torch.testing.assert_close(got, want, atol=5e-3, rtol=0)
+    # the fused kernel rounds x * w to bfloat16 and applies the row's scale to the float32 sum;
+    # the separate norm rounds x * scale * w: two roundings of equal size, both near the exact value
     ref = (res.double() * torch.rsqrt((res.double() ** 2).mean(-1, keepdim=True) + 1e-5) * nw.double()) @ w.double().T
     torch.testing.assert_close(got.double(), ref, atol=2e-2, rtol=2e-2)
+    err_fused, err_unfused = (got.double() - ref).abs().max().item(), (unfused.double() - ref).abs().max().item()
+    assert err_fused < 2.0 * err_unfused + 1e-6
+    acc = torch.full((rows, N), 2.0, device=DEV)
+    ops().skinny_gemm(res, w, acc, mode=1, norm_weight=nw, eps=1e-5)
+    torch.testing.assert_close(acc, got + 2, atol=1e-5, rtol=1e-6)
 
 
 @pytest.mark.parametrize("rows", [1, 5, 40])
@@ -458,3 +462,40 @@ def test_attention_prefill_finds_a_far_key():
     assert abs(out[329, 0].item() - needle % 128) < 0.51
     ops().attention_prefill(q, k, v, *args, 329 - needle, 1.0)           # one shorter: the needle is outside
     assert abs(out[329, 0].item() - needle % 128) > 10
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd,window", [(32, 8, 128, None), (4, 2, 64, None), (6, 2, 128, 100),
+                                                (2, 1, 32, None), (8, 8, 256, None)])
+@pytest.mark.parametrize("n_splits", [1, 4])
+def test_attention_decode_with_rotation_and_append_inside(n_q, n_kv, hd, window, n_splits):
+    """The fused launch equals rope_append followed by attention_decode: output, and the key
+    and value it leaves in the cache; positions include 0, page borders and a padding row."""
+    g = torch.Generator(device=DEV).manual_seed(50)
+    pos = torch.tensor([0, 63, 64, 300, 299, 17, 128], dtype=torch.int32, device=DEV)
+    slot = torch.tensor([0, 1, 2, 3, 4, -1, 5], dtype=torch.int32, device=DEV)
+    table = torch.randperm(30, generator=torch.Generator().manual_seed(51)).to(torch.int32).view(6, 5).to(DEV)
+    k0, v0 = _paged(30, n_kv, hd, torch.bfloat16, 52)
+    qkv0 = torch.randn(len(pos), (n_q + 2 * n_kv) * hd, device=DEV, generator=g).bfloat16()
+    ang = torch.arange(400, device=DEV, dtype=torch.float64)[:, None] * \
+        (1.0 / 10000 ** (torch.arange(hd // 2, device=DEV, dtype=torch.float64) * 2 / hd))[None, :]
+    cos, sin = ang.cos().float().contiguous(), ang.sin().float().contiguous()
+    scale = 1 / math.sqrt(hd)
+    nf, nc = ops().attention_decode_scratch(len(pos), n_q, n_kv, hd, n_splits)
+    scratch = torch.empty(max(nf, 1), device=DEV)
+    counters = torch.zeros(max(nc, 1), dtype=torch.int32, device=DEV)
+    # the two-step way
+    qkv_a, ka, va = qkv0.clone(), k0.clone(), v0.clone()
+    ops().rope_append(qkv_a, cos, sin, pos, slot, table, ka, va, n_q, n_kv, hd, hd, 6, True)
+    want = torch.empty(len(pos), n_q * hd, dtype=torch.bfloat16, device=DEV)
+    ops().attention_decode(qkv_a, ka, va, pos, slot, table, want, n_q, n_kv, hd, 6, window, scale, n_splits,
+                           scratch, counters)
+    # the fused way
+    qkv_b, kb, vb = qkv0.clone(), k0.clone(), v0.clone()
+    got = torch.full_like(want, 5.0)
+    ops().attention_decode(qkv_b, kb, vb, pos, slot, table, got, n_q, n_kv, hd, 6, window, scale, n_splits,
+                           scratch, counters, cos=cos, sin=sin)
+    torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+    assert torch.equal(qkv_b, qkv0)                                       # the projection's output is not touched
+    assert torch.equal(vb, va)                                            # values are copied as they are
+    torch.testing.assert_close(kb.float(), ka.float(), atol=0, rtol=2 ** -7)   # keys: at most the last bit
+    assert torch.all(got[5] == 0) and torch.all(counters == 0)
