@@ -52,13 +52,13 @@ __device__ __forceinline__ void ad_load_row(const __nv_bfloat16* p, int lane, in
 // each load would make every load wait for the one before it.
 template <int VEC> struct AdRaw { uint32_t w[(VEC + 1) / 2]; };
 
-template <int VEC>
+template <int VEC, bool FULL = false>
 __device__ __forceinline__ AdRaw<VEC> ad_load_raw(const __nv_bfloat16* p, int lane, int head_dim) {
     AdRaw<VEC> r;
     const int d = lane * VEC;
 #pragma unroll
     for (int i = 0; i < (VEC + 1) / 2; ++i) r.w[i] = 0u;
-    if (d + VEC <= head_dim) {
+    if (FULL || d + VEC <= head_dim) {                   // FULL: head_dim == 32 * VEC, no ragged lanes
         if (VEC == 8) {
             asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                          : "=r"(r.w[0]), "=r"(r.w[1]), "=r"(r.w[2]), "=r"(r.w[3]) : "l"(p + d));
@@ -94,7 +94,7 @@ __device__ __forceinline__ void ad_unpack(const AdRaw<VEC>& r, float (&v)[VEC]) 
 // ([q heads | k heads | v heads]); the kernel rotates the queries by the token's position, and
 // the block that owns the token's page also rotates its key, writes key and value into the
 // cache and attends to them from registers.  Needs head_dim == 32 * VEC and a full-width rotation.
-template <int VEC, bool FUSE>
+template <int VEC, bool FUSE, bool FULL>
 __global__ void __launch_bounds__(AD_THREADS)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* k_cache,
                         __nv_bfloat16* v_cache, const int* __restrict__ pos,
@@ -117,9 +117,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
     const int n_heads = min(AD_GROUP, group - sub * AD_GROUP);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     ssb_pdl_launch_dependents();
-    ssb_pdl_wait();                                              // everything read below may be a predecessor's
+    // Without FUSE the predecessor (rope + append) wrote this step's key into the cache: wait
+    // before reading anything.  With FUSE the cache holds earlier steps' keys only, and slots,
+    // positions and page tables are written before the step starts: the first keys and values
+    // are fetched before the wait, and only the query needs the predecessor.
+    if (!FUSE) ssb_pdl_wait();
     const int s = slot[b];
     if (s < 0) {                                                 // padding row: zeros, no bookkeeping
+        if (FUSE) ssb_pdl_wait();
         if (split == 0)
             for (int e = threadIdx.x; e < n_heads * head_dim; e += AD_THREADS)
                 out[(size_t)b * ldo + (size_t)h0 * head_dim + e] = __float2bfloat16_rn(0.f);
@@ -135,6 +140,27 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
     const bool owns_new = FUSE && my_lo <= p && p <= ((page_lo + (split + 1) * per) << page_shift) - 1;
     // with FUSE the token's own key is not in the cache yet: cached keys end at p - 1
     const int my_hi = min(FUSE ? p - 1 : p, ((page_lo + (split + 1) * per) << page_shift) - 1);
+
+    const int* pt = page_table + (size_t)s * max_pages;
+    const int page_mask = (1 << page_shift) - 1;
+    constexpr int TURN = AD_WARPS * AD_TOK;
+    // one turn = AD_TOK keys of this warp: all loads are issued first, into raw registers
+    auto issue = [&](int j0, AdRaw<VEC> (&k_raw)[AD_TOK], AdRaw<VEC> (&v_raw)[AD_TOK]) {
+        size_t row[AD_TOK];
+#pragma unroll
+        for (int u = 0; u < AD_TOK; ++u) {
+            const int jj = min(j0 + u, my_hi);
+            row[u] = ((((size_t)pt[jj >> page_shift] * n_kv + kvh) << page_shift) + (jj & page_mask)) * head_dim;
+        }
+#pragma unroll
+        for (int u = 0; u < AD_TOK; ++u) k_raw[u] = ad_load_raw<VEC, FULL>(k_cache + row[u], lane, head_dim);
+#pragma unroll
+        for (int u = 0; u < AD_TOK; ++u) v_raw[u] = ad_load_raw<VEC, FULL>(v_cache + row[u], lane, head_dim);
+    };
+    AdRaw<VEC> ka[AD_TOK], va[AD_TOK];
+    int j0 = my_lo + warp * AD_TOK;
+    if (j0 <= my_hi) issue(j0, ka, va);
+    if (FUSE) ssb_pdl_wait();                                    // the query (and this token's k, v) come from the predecessor
 
     // rotation of this lane's elements: pairs (i, i + head_dim/2) live in lanes l and l ^ 16
     float rc[VEC], rs[VEC];
@@ -173,27 +199,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
         for (int e = 0; e < VEC; ++e) acc[gi][e] = 0.f;
     }
 
-    const int* pt = page_table + (size_t)s * max_pages;
-    const int page_mask = (1 << page_shift) - 1;
-    for (int j0 = my_lo + warp * AD_TOK; j0 <= my_hi; j0 += AD_WARPS * AD_TOK) {
-        AdRaw<VEC> k_raw[AD_TOK], v_raw[AD_TOK];
-        size_t row[AD_TOK];
-#pragma unroll
-        for (int u = 0; u < AD_TOK; ++u) {
-            const int jj = min(j0 + u, my_hi);
-            row[u] = ((((size_t)pt[jj >> page_shift] * n_kv + kvh) << page_shift) + (jj & page_mask)) * head_dim;
-        }
-#pragma unroll
-        for (int u = 0; u < AD_TOK; ++u) k_raw[u] = ad_load_raw<VEC>(k_cache + row[u], lane, head_dim);
-#pragma unroll
-        for (int u = 0; u < AD_TOK; ++u) v_raw[u] = ad_load_raw<VEC>(v_cache + row[u], lane, head_dim);
+    auto consume = [&](int j0, const AdRaw<VEC> (&k_raw)[AD_TOK], const AdRaw<VEC> (&v_raw)[AD_TOK]) {
         float sc[AD_TOK][AD_GROUP];
 #pragma unroll
         for (int u = 0; u < AD_TOK; ++u)
 #pragma unroll
-            for (int gi = 0; gi < AD_GROUP; ++gi) {
-                sc[u][gi] = 0.f;
-            }
+            for (int gi = 0; gi < AD_GROUP; ++gi) sc[u][gi] = 0.f;
 #pragma unroll
         for (int u = 0; u < AD_TOK; ++u) {
             float kr[VEC];
@@ -237,14 +248,21 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) acc[gi][e] = fmaf(sc[u][gi], vr[e], acc[gi][e]);
         }
+    };
+    // one copy of the loop body (instruction fetch matters at this size): use a turn, then fetch the next
+#pragma unroll 1
+    while (j0 <= my_hi) {
+        consume(j0, ka, va);
+        j0 += TURN;
+        if (j0 <= my_hi) issue(j0, ka, va);
     }
 
     if (FUSE && owns_new && warp == 0) {
         // the token's own key and value: from the projection's output, not from the cache
         const __nv_bfloat16* k_src = q + (size_t)b * ldq + (size_t)(n_q + kvh) * head_dim;
         const __nv_bfloat16* v_src = k_src + (size_t)n_kv * head_dim;
-        AdRaw<VEC> k_raw = ad_load_raw<VEC>(k_src, lane, head_dim);
-        const AdRaw<VEC> v_raw = ad_load_raw<VEC>(v_src, lane, head_dim);
+        AdRaw<VEC> k_raw = ad_load_raw<VEC, FULL>(k_src, lane, head_dim);
+        const AdRaw<VEC> v_raw = ad_load_raw<VEC, FULL>(v_src, lane, head_dim);
         float kr[VEC], vr[VEC];
         ad_unpack<VEC>(k_raw, kr);
         ad_unpack<VEC>(v_raw, vr);
@@ -394,15 +412,13 @@ static inline int ad_launch(const void* q, int ldq, const void* k_cache, const v
     dim3 grid(n_seqs, n_kv * ((group + AD_GROUP - 1) / AD_GROUP), n_splits);
     const int vec = (head_dim + 31) / 32;
     int rc = 0;
+#define SSB_AD_ARGS (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
+        (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters, cos_t, sin_t
 #define SSB_AD(V) \
-    rc = fuse ? ssb_launch(attention_decode_kernel<V, true>, grid, dim3(AD_THREADS), 0, stream, pdl, \
-                    (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
-                    (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters, \
-                    cos_t, sin_t) \
-              : ssb_launch(attention_decode_kernel<V, false>, grid, dim3(AD_THREADS), 0, stream, pdl, \
-                    (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
-                    (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters, \
-                    cos_t, sin_t)
+    rc = fuse ? ssb_launch(attention_decode_kernel<V, true, true>, grid, dim3(AD_THREADS), 0, stream, pdl, SSB_AD_ARGS) \
+       : head_dim == 32 * V \
+              ? ssb_launch(attention_decode_kernel<V, false, true>, grid, dim3(AD_THREADS), 0, stream, pdl, SSB_AD_ARGS) \
+              : ssb_launch(attention_decode_kernel<V, false, false>, grid, dim3(AD_THREADS), 0, stream, pdl, SSB_AD_ARGS)
     // vector loads need VEC elements aligned: rows are head_dim * 2 bytes apart
     if (vec == 1) SSB_AD(1);
     else if (vec == 2 && head_dim % 2 == 0 && ldq % 2 == 0) SSB_AD(2);
@@ -410,5 +426,6 @@ static inline int ad_launch(const void* q, int ldq, const void* k_cache, const v
     else if (vec <= 8 && head_dim % 8 == 0 && ldq % 8 == 0) SSB_AD(8);
     else return SSB_ERR_UNSUPPORTED;
 #undef SSB_AD
+#undef SSB_AD_ARGS
     return rc ? rc : ssb_launch_status();
 }

@@ -68,11 +68,14 @@ skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restric
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * ROWS;
 
-    // The head of the block's slab of W goes to L2 ahead of use (one bulk prefetch per row).
-    // Weights are written by no kernel, so this may run before the predecessor has finished.
+    // The block's slab of W goes to L2 ahead of use (one bulk prefetch per row): all of it when
+    // the whole matrix fits L2 comfortably, else only the head of each row (a full prefetch of a
+    // large matrix by every resident block would evict itself).  Weights are written by no
+    // kernel, so this may run while the predecessor (attention, a norm) still works.
     if (threadIdx.x < ROWS) {
         const bf16* row = W + (size_t)min(n0 + (int)threadIdx.x, N - 1) * ldw;
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(row), "r"(min(K * 2, 4096)) : "memory");
+        const bool small = (size_t)N * K * 2 <= (size_t)64 << 20;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(row), "r"(small ? K * 2 : min(K * 2, 4096)) : "memory");
     }
     ssb_pdl_launch_dependents();
     ssb_pdl_wait();                                     // x (and out) belong to the predecessor until here

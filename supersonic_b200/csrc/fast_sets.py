@@ -13,7 +13,7 @@ import torch
 from . import ops
 from .kernel_sets import NormedInput, PlainKernels, as_tensor
 
-FUSED_NORM_MAX_ROWS = 8        # above this each block would re-read too much of the residual
+FUSED_NORM_MAX_ROWS = 0        # measured: a separate norm launch is faster than the folded one at every batch size
 SKINNY_MAX_ROWS = 16          # above this the tcgen05 GEMM streams the weights faster (measured)
 TARGET_BLOCKS = 1184           # eight small blocks per SM
 
@@ -26,6 +26,9 @@ class FastKernels(PlainKernels):
         self.fuse_rope = True    # decode attention rotates q/k and appends to the cache itself
         self._scratch: Dict[str, torch.Tensor] = {}
         self._retired = []      # outgrown buffers stay alive: captured graphs still point at them
+
+    def rmsnorm(self, x, weight, eps, out, rows=None):
+        ops.rmsnorm(x, weight, eps, out, rows, pdl=self.pdl and out.shape[0] <= 64)
 
     # ---- matrix products -------------------------------------------------------------
     def _skinny(self, x, weight, out, mode):

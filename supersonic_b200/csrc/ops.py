@@ -90,7 +90,7 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-            rows: Optional[torch.Tensor] = None) -> None:
+            rows: Optional[torch.Tensor] = None, pdl: bool = False) -> None:
     """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * weight, x float32."""
     _need(x, "x", torch.float32, 2); _need(weight, "weight", None, 1); _need(out, "out", None, 2)
     if not (x.is_contiguous() and out.is_contiguous()):
@@ -106,7 +106,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
         raise KernelError("rmsnorm: widths differ")
     _check(_fn("plain_ops", "ssb_rmsnorm")(
         _ptr(x), _ptr(rows), _ptr(weight), c_int(dtype_code(weight.dtype)), c_float(eps), _ptr(out),
-        c_int(dtype_code(out.dtype)), c_int(n), c_int(x.shape[1]), _stream()), "rmsnorm")
+        c_int(dtype_code(out.dtype)), c_int(n), c_int(x.shape[1]), c_int(1 if pdl else 0), _stream()), "rmsnorm")
 
 
 def gemm_nt_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

@@ -55,6 +55,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
                                const TW* __restrict__ w, float eps, TO* __restrict__ out, int hidden) {
     __shared__ float red[256];
     const int r = blockIdx.x;
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
     const float* src = x + (size_t)(rows ? rows[r] : r) * hidden;
     float part = 0.f;
     for (int c = threadIdx.x; c < hidden; c += 256) {
@@ -74,17 +76,19 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 }
 
 SSB_API int ssb_rmsnorm(const float* x, const int* rows, const void* w, int w_dtype, float eps,
-                        void* out, int out_dtype, int n_rows, int hidden, cudaStream_t stream) {
+                        void* out, int out_dtype, int n_rows, int hidden, int pdl, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    int rc = 0;
 #define SSB_RMS(TO, TW) \
-    rmsnorm_kernel<TO, TW><<<n_rows, 256, 0, stream>>>(x, rows, (const TW*)w, eps, (TO*)out, hidden)
+    rc = ssb_launch(rmsnorm_kernel<TO, TW>, dim3(n_rows), dim3(256), 0, stream, pdl != 0, x, rows, (const TW*)w, eps, \
+                    (TO*)out, hidden)
     if (out_dtype == SSB_F32 && w_dtype == SSB_F32) SSB_RMS(float, float);
     else if (out_dtype == SSB_F32 && w_dtype == SSB_BF16) SSB_RMS(float, bf16);
     else if (out_dtype == SSB_BF16 && w_dtype == SSB_F32) SSB_RMS(bf16, float);
     else if (out_dtype == SSB_BF16 && w_dtype == SSB_BF16) SSB_RMS(bf16, bf16);
     else return SSB_ERR_BAD_DTYPE;
 #undef SSB_RMS
-    return ssb_launch_status();
+    return rc ? rc : ssb_launch_status();
 }
 
 // ---------------------------------------------------------------------------------------
