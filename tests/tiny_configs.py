@@ -1,5 +1,5 @@
 """The tests' own tiny configurations of the architecture.  They differ in every size
-and option: layers, width, head counts and groups (4/2, 3/1, 6/2), head sizes (16, 32, 48),
+and option: layers, width, head counts and groups (4/2, 3/1, 6/2), head sizes (16, 32, 48, 64),
 ``num_heads * head_dim`` equal to the width or not, feed-forward width, vocabulary (a power
 of two, a multiple of 128, odd), norm epsilon, rotary base, frequency scaling (none and two
 llama3 blocks), tied and untied heads.  Weights are drawn wider than the usual 0.02 so that
@@ -25,5 +25,13 @@ C = dict(architectures=["LlamaForCausalLM"], vocab_size=301, hidden_size=72, int
                            original_max_position_embeddings=32),
          tie_word_embeddings=True)
 
+# head_dim 64: the size at which the tensor-core prefill attention and the fused decode attention run
+D = dict(architectures=["LlamaForCausalLM"], vocab_size=512, hidden_size=128, intermediate_size=320,
+         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+         max_position_embeddings=2048, rms_norm_eps=3e-6, rope_theta=250000.0,
+         rope_scaling=dict(rope_type="llama3", factor=2.0, low_freq_factor=1.0, high_freq_factor=3.0,
+                           original_max_position_embeddings=64),
+         tie_word_embeddings=False, eos_token_id=[3])
+
 # name -> (config.json contents, weight seed, std of matrices and embeddings)
-CONFIGS = {"A": (A, 0, 0.10), "B": (B, 1, 0.08), "C": (C, 2, 0.09)}
+CONFIGS = {"A": (A, 0, 0.10), "B": (B, 1, 0.08), "C": (C, 2, 0.09), "D": (D, 3, 0.07)}
