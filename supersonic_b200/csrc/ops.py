@@ -315,6 +315,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
 TC_STORE, TC_ACCUMULATE, TC_SWIGLU = 0, 1, 2
 _TC_ERRORS = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}
 _tc_error_words = {}
+_tc_unchecked = 0      # tcgen05 launches since the error words were last read
 
 
 def tc_error_word(device) -> torch.Tensor:
@@ -326,7 +327,12 @@ def tc_error_word(device) -> torch.Tensor:
 
 
 def check_device_errors(device=None) -> None:
-    """Raise if a kernel recorded a bounded wait that ran out (reads one word from each device used)."""
+    """Raise if a kernel recorded a bounded wait that ran out.  Reads one word per device, and
+    only if a kernel that could have set it was launched since the last look."""
+    global _tc_unchecked
+    if not _tc_unchecked:
+        return
+    _tc_unchecked = 0
     for dev, word in list(_tc_error_words.items()):
         if device is not None and torch.device(device) != dev:
             continue
@@ -357,6 +363,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_
         raise KernelError(f"gemm_tc: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
     if tile_n is None:
         tile_n = 256 if N > 128 else 128
+    global _tc_unchecked
+    _tc_unchecked += 1
     _check(_fn("gemm_tc", "ssb_gemm_tc")(
         _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)),
         c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K), c_int(mode), c_int(tile_n),

@@ -110,6 +110,8 @@ class Generator:
                 slots = torch.tensor([slot_of[r] for r in live], dtype=torch.int32).to(
                     logits.device, non_blocking=True)
                 tokens = self.sampler(logits, slots, sampling).to("cpu").tolist()
+                if hasattr(model, "check_errors"):
+                    model.check_errors()
                 if on_step:
                     on_step(live, tokens)
                 still, entries = [], []

@@ -232,6 +232,12 @@ class Model:
         normed = self.final_norm(ctx, residual, rows=batch.want_rows)
         return self.head(ctx, normed)
 
+    def check_errors(self) -> None:
+        """Raise if a kernel reported a bounded wait that ran out.  Call after results have been
+        brought to the host (it reads a device word, which waits for the stream)."""
+        from ..csrc import ops
+        ops.check_device_errors(self.device)
+
     # ---- sequences --------------------------------------------------------------------
     def open_sequence(self, rng_seed: Optional[int] = None) -> int:
         return self.cache.acquire(rng_seed)

@@ -49,6 +49,7 @@ class Replayer:
             logits = self.model.step(entries)
             if logits.shape[0]:
                 data = logits.detach().to("cpu").contiguous().numpy().astype("<f4", copy=False)
+                self.model.check_errors()
                 tmp = os.path.join(self.out_dir, f".{step}.f32.tmp")
                 with open(tmp, "wb") as f:
                     f.write(data.tobytes())
