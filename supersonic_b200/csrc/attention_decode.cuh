@@ -102,7 +102,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
                         __nv_bfloat16* __restrict__ out, int ldo, int n_q, int n_kv, int head_dim, int page_shift,
                         int window, float scale, int n_splits, float* __restrict__ scratch,
                         int* __restrict__ counters, const float* __restrict__ cos_t,
-                        const float* __restrict__ sin_t) {
+                        const float* __restrict__ sin_t, const char* __restrict__ prefetch_ptr,
+                        long long prefetch_bytes) {
     __shared__ float sm_m[AD_WARPS][AD_GROUP], sm_l[AD_WARPS][AD_GROUP];
     __shared__ float sm_acc[AD_WARPS][AD_GROUP][32 * VEC];
     __shared__ float sm_f[AD_GROUP][AD_MAX_SPLITS];          // per split: exp(max_split - max_all)
@@ -117,6 +118,18 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
     const int n_heads = min(AD_GROUP, group - sub * AD_GROUP);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     ssb_pdl_launch_dependents();
+    // This kernel moves little data and waits on latencies: meanwhile it asks L2 to fetch a slice
+    // of the weights that the kernels after it will stream (read-only memory, safe before the wait).
+    if (prefetch_bytes > 0 && threadIdx.x == 0) {
+        const long long n_blocks = (long long)gridDim.x * gridDim.y * gridDim.z;
+        const long long me = ((long long)blockIdx.x * gridDim.y + blockIdx.y) * gridDim.z + blockIdx.z;
+        const long long slice = ((prefetch_bytes + n_blocks - 1) / n_blocks + 15) & ~15LL;
+        const long long lo_b = me * slice, hi_b = min(lo_b + slice, prefetch_bytes & ~15LL);
+        for (long long o = lo_b; o < hi_b; o += 32768) {
+            const unsigned n = (unsigned)min(32768LL, hi_b - o);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(prefetch_ptr + o), "r"(n) : "memory");
+        }
+    }
     // Without FUSE the predecessor (rope + append) wrote this step's key into the cache: wait
     // before reading anything.  With FUSE the cache holds earlier steps' keys only, and slots,
     // positions and page tables are written before the step starts: the first keys and values
@@ -398,7 +411,8 @@ static inline int ad_launch(const void* q, int ldq, const void* k_cache, const v
                             const int* slot, const int* page_table, int max_pages, void* out, int ldo,
                             int n_seqs, int n_q, int n_kv, int head_dim, int page_shift, int window,
                             float scale, int n_splits, float* scratch, int* counters, cudaStream_t stream,
-                            bool pdl = false, const float* cos_t = nullptr, const float* sin_t = nullptr) {
+                            bool pdl = false, const float* cos_t = nullptr, const float* sin_t = nullptr,
+                            const void* prefetch_ptr = nullptr, long long prefetch_bytes = 0) {
     typedef __nv_bfloat16 bf16;
     if (n_seqs <= 0) return 0;
     if (head_dim <= 0 || head_dim > 32 * AD_MAX_VEC || n_kv <= 0 || n_q % n_kv || n_splits < 1 ||
@@ -413,7 +427,8 @@ static inline int ad_launch(const void* q, int ldq, const void* k_cache, const v
     const int vec = (head_dim + 31) / 32;
     int rc = 0;
 #define SSB_AD_ARGS (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
-        (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters, cos_t, sin_t
+        (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters, cos_t, sin_t, \
+        (const char*)prefetch_ptr, (((uintptr_t)prefetch_ptr & 15) ? 0LL : prefetch_bytes)
 #define SSB_AD(V) \
     rc = fuse ? ssb_launch(attention_decode_kernel<V, true, true>, grid, dim3(AD_THREADS), 0, stream, pdl, SSB_AD_ARGS) \
        : head_dim == 32 * V \

@@ -277,6 +277,7 @@ SSB_API int ssb_skinny_gemm(const void* x, int ldx, const void* norm_w, int norm
 // zero before the first launch (every launch leaves them zero).  With cos_t/sin_t
 // ([positions, head_dim/2] float32) the rows of q are the raw fused projection [q | k | v]: the
 // kernel rotates queries and the token's key itself and appends key and value to the cache.
+// prefetch_ptr/bytes: read-only memory (the next kernels' weights) to pull into L2 meanwhile.
 SSB_API long long ssb_attention_decode_scratch_floats(int n_seqs, int n_q, int head_dim, int n_splits) {
     return ad_scratch_floats(n_seqs, n_q, head_dim, n_splits);
 }
@@ -290,8 +291,8 @@ SSB_API int ssb_attention_decode(const void* q, int ldq, const void* k_cache, co
                                  void* out, int ldo, int n_seqs, int n_q, int n_kv, int head_dim,
                                  int page_shift, int window, float scale, int n_splits, float* scratch,
                                  int* counters, int pdl, const float* cos_t, const float* sin_t,
-                                 cudaStream_t stream) {
+                                 const void* prefetch_ptr, long long prefetch_bytes, cudaStream_t stream) {
     return ad_launch(q, ldq, k_cache, v_cache, pos, slot, page_table, max_pages, out, ldo, n_seqs, n_q, n_kv,
                      head_dim, page_shift, window, scale, n_splits, scratch, counters, stream, pdl != 0,
-                     cos_t, sin_t);
+                     cos_t, sin_t, prefetch_ptr, prefetch_bytes);
 }

@@ -14,6 +14,8 @@ from . import ops
 from .kernel_sets import NormedInput, PlainKernels, as_tensor
 
 FUSED_NORM_MAX_ROWS = 0        # measured: a separate norm launch is faster than the folded one at every batch size
+PREFETCH_BYTES = 64 << 20     # weights pulled into L2 during decode attention (L2 holds 126 MB)
+PREFETCH_MAX_ROWS = 16        # beyond this attention itself keeps the memory system busy
 SKINNY_MAX_ROWS = 16          # above this the tcgen05 GEMM streams the weights faster (measured)
 TARGET_BLOCKS = 1184           # eight small blocks per SM
 
@@ -24,6 +26,7 @@ class FastKernels(PlainKernels):
     def __init__(self, pdl: bool = True):
         self.pdl = pdl           # decode kernels launch as programmatic dependents of their predecessors
         self.fuse_rope = True    # decode attention rotates q/k and appends to the cache itself
+        self._next_weights = None
         self._scratch: Dict[str, torch.Tensor] = {}
         self._retired = []      # outgrown buffers stay alive: captured graphs still point at them
 
@@ -96,6 +99,11 @@ class FastKernels(PlainKernels):
             self._scratch[name] = t
         return t
 
+    def hint_next_weights(self, weight) -> None:
+        """The weights that will be streamed after the next latency-bound kernel (attention);
+        that kernel asks L2 to fetch the head of them while it waits on its own small loads."""
+        self._next_weights = weight
+
     def _decode_attention(self, q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim,
                           page_shift, window, scale, cos=None, sin=None):
         group = n_q // n_kv
@@ -109,7 +117,10 @@ class FastKernels(PlainKernels):
             counters = self._buffer("attn_counters", nc, torch.int32, q.device, zero=True)
         ops.attention_decode(q, k_cache, v_cache, batch.pos, batch.slot_of_token, page_table, out,
                              n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters,
-                             pdl=self.pdl, cos=cos, sin=sin)
+                             pdl=self.pdl, cos=cos, sin=sin,
+                             prefetch=self._next_weights if batch.n_seqs <= PREFETCH_MAX_ROWS else None,
+                             prefetch_bytes=PREFETCH_BYTES)
+        self._next_weights = None
 
     def rope_attention(self, qkv, position, kv, batch, out, n_q, n_kv, head_dim, page_shift, window,
                        scale) -> bool:

@@ -80,6 +80,9 @@ class PlainKernels:
         ops.rope_append(qkv, cos, sin, batch.pos, batch.slot_of_token, page_table, k_cache, v_cache,
                         n_q, n_kv, head_dim, rotary_dim, page_shift, write_cache)
 
+    def hint_next_weights(self, weight) -> None:
+        """Told by a block which weights will be streamed after its mixer; a set may use it."""
+
     def rope_attention(self, qkv, position, kv, batch, out, n_q, n_kv, head_dim, page_shift, window,
                        scale) -> bool:
         """Position encoding, cache append and attention in one launch, if this set can do it

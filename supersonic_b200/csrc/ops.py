@@ -278,11 +278,13 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      head_dim: int, page_shift: int, window: Optional[int], scale: float, n_splits: int,
                      scratch: Optional[torch.Tensor], counters: Optional[torch.Tensor],
                      pdl: bool = False, cos: Optional[torch.Tensor] = None,
-                     sin: Optional[torch.Tensor] = None) -> None:
+                     sin: Optional[torch.Tensor] = None, prefetch: Optional[torch.Tensor] = None,
+                     prefetch_bytes: int = 0) -> None:
     """One query token per sequence (row) over its cached keys, the keys split ``n_splits`` ways.
     With ``cos``/``sin`` ([positions, head_dim/2] float32) the rows of ``q`` are the raw fused
     projection [q | k | v]: queries and the token's key are rotated inside the kernel, and key
-    and value are appended to the cache (no separate rope/append launch)."""
+    and value are appended to the cache (no separate rope/append launch).  ``prefetch``: weights
+    that later kernels will stream; the first ``prefetch_bytes`` of it are pulled into L2 meanwhile."""
     _need(q, "q", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
     _need(k_cache, "k_cache", torch.bfloat16); _need(v_cache, "v_cache", torch.bfloat16)
     _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
@@ -308,6 +310,8 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         c_int(page_table.shape[1]), _ptr(out), c_int(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv),
         c_int(head_dim), c_int(page_shift), c_int(int(window) if window else 0), c_float(scale),
         c_int(n_splits), _ptr(scratch), _ptr(counters), c_int(1 if pdl else 0), _ptr(cos), _ptr(sin),
+        _ptr(prefetch), c_longlong(min(prefetch_bytes, prefetch.numel() * prefetch.element_size())
+                                   if prefetch is not None else 0),
         _stream()), "attention_decode")
 
 

@@ -25,6 +25,9 @@ class PreNormBlock:
 
     def forward(self, ctx, residual, cache_id, writes_cache):
         x = self._input(ctx, residual, self.mixer_norm, self.mixer)
+        first = getattr(self.feed_forward, "first_weights", None)
+        if first is not None:
+            ctx.kernels.hint_next_weights(first())
         self.mixer.forward(ctx, x, residual, cache_id, writes_cache, self.position)
         x = self._input(ctx, residual, self.feed_forward_norm, self.feed_forward)
         self.feed_forward.forward(ctx, x, residual)

@@ -32,6 +32,10 @@ class SwiGLU:
         self.w_gate_up, self.layout = build.kernels.pack_gate_up(gate, up)
         self.dtype = build.dtype
 
+    def first_weights(self):
+        """The weights this part streams first (a mixer before it may warm the cache with them)."""
+        return self.w_gate_up
+
     def forward(self, ctx, x, residual):
         z = torch.empty((residual.shape[0], self.inter), dtype=self.dtype, device=residual.device)
         ctx.kernels.gate_up_swiglu(x, self.w_gate_up, self.layout, z)
