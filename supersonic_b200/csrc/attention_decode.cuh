@@ -13,7 +13,7 @@
 #include "common.cuh"
 #include <math.h>
 
-constexpr int AD_WARPS = 4;
+constexpr int AD_WARPS = 4;          // warps of a block when many blocks fill the GPU; 8 when few do
 constexpr int AD_THREADS = AD_WARPS * 32;
 constexpr int AD_GROUP = 4;
 constexpr int AD_MAX_VEC = 8;
@@ -94,8 +94,8 @@ __device__ __forceinline__ void ad_unpack(const AdRaw<VEC>& r, float (&v)[VEC]) 
 // ([q heads | k heads | v heads]); the kernel rotates the queries by the token's position, and
 // the block that owns the token's page also rotates its key, writes key and value into the
 // cache and attends to them from registers.  Needs head_dim == 32 * VEC and a full-width rotation.
-template <int VEC, bool FUSE, bool FULL>
-__global__ void __launch_bounds__(AD_THREADS)
+template <int VEC, bool FUSE, bool FULL, int NW>
+__global__ void __launch_bounds__(NW * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* k_cache,
                         __nv_bfloat16* v_cache, const int* __restrict__ pos,
                         const int* __restrict__ slot, const int* __restrict__ page_table, int max_pages,
@@ -104,8 +104,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
                         int* __restrict__ counters, const float* __restrict__ cos_t,
                         const float* __restrict__ sin_t, const char* __restrict__ prefetch_ptr,
                         long long prefetch_bytes) {
-    __shared__ float sm_m[AD_WARPS][AD_GROUP], sm_l[AD_WARPS][AD_GROUP];
-    __shared__ float sm_acc[AD_WARPS][AD_GROUP][32 * VEC];
+    __shared__ float sm_m[NW][AD_GROUP], sm_l[NW][AD_GROUP];
+    __shared__ float sm_acc[NW][AD_GROUP][32 * VEC];
     __shared__ float sm_f[AD_GROUP][AD_MAX_SPLITS];          // per split: exp(max_split - max_all)
     __shared__ float sm_pm[AD_GROUP][AD_MAX_SPLITS], sm_pl[AD_GROUP][AD_MAX_SPLITS];
     __shared__ float sm_L[AD_GROUP];
@@ -139,7 +139,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
     if (s < 0) {                                                 // padding row: zeros, no bookkeeping
         if (FUSE) ssb_pdl_wait();
         if (split == 0)
-            for (int e = threadIdx.x; e < n_heads * head_dim; e += AD_THREADS)
+            for (int e = threadIdx.x; e < n_heads * head_dim; e += (NW * 32))
                 out[(size_t)b * ldo + (size_t)h0 * head_dim + e] = __float2bfloat16_rn(0.f);
         return;
     }
@@ -156,14 +156,23 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
 
     const int* pt = page_table + (size_t)s * max_pages;
     const int page_mask = (1 << page_shift) - 1;
-    constexpr int TURN = AD_WARPS * AD_TOK;
+    constexpr int TURN = NW * AD_TOK;
     // one turn = AD_TOK keys of this warp: all loads are issued first, into raw registers
+    // the block's page ids sit in the lanes of each warp (one global load up front) when there
+    // are at most 32 of them; a key's page is then a shuffle away instead of a dependent load
+    const int first_page = my_lo >> page_shift;
+    const int n_my_pages = (max(my_hi, my_lo) >> page_shift) - first_page + 1;
+    const bool pages_in_lanes = n_my_pages <= 32;
+    const int lane_page = (pages_in_lanes && lane < n_my_pages && first_page + lane <= page_hi)
+                              ? pt[first_page + lane] : 0;      // never past the sequence's last page
     auto issue = [&](int j0, AdRaw<VEC> (&k_raw)[AD_TOK], AdRaw<VEC> (&v_raw)[AD_TOK]) {
         size_t row[AD_TOK];
 #pragma unroll
         for (int u = 0; u < AD_TOK; ++u) {
             const int jj = min(j0 + u, my_hi);
-            row[u] = ((((size_t)pt[jj >> page_shift] * n_kv + kvh) << page_shift) + (jj & page_mask)) * head_dim;
+            const int idx = jj >> page_shift;
+            const int page = pages_in_lanes ? __shfl_sync(0xffffffffu, lane_page, idx - first_page) : pt[idx];
+            row[u] = ((((size_t)page * n_kv + kvh) << page_shift) + (jj & page_mask)) * head_dim;
         }
 #pragma unroll
         for (int u = 0; u < AD_TOK; ++u) k_raw[u] = ad_load_raw<VEC, FULL>(k_cache + row[u], lane, head_dim);
@@ -318,15 +327,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
     __syncthreads();
     const int width = 32 * VEC;
     // thread e of the block owns element (head gi, dim d) of the merged partial
-    for (int e = threadIdx.x; e < n_heads * width; e += AD_THREADS) {
+    for (int e = threadIdx.x; e < n_heads * width; e += (NW * 32)) {
         const int gi = e / width, d = e % width;
         if (d >= head_dim) continue;
         float mm = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < AD_WARPS; ++w) mm = fmaxf(mm, sm_m[w][gi]);
+        for (int w = 0; w < NW; ++w) mm = fmaxf(mm, sm_m[w][gi]);
         float ll = 0.f, a = 0.f;
 #pragma unroll
-        for (int w = 0; w < AD_WARPS; ++w) {
+        for (int w = 0; w < NW; ++w) {
             const float f = (sm_m[w][gi] == -INFINITY) ? 0.f : __expf(sm_m[w][gi] - mm);
             ll += sm_l[w][gi] * f;
             a += sm_acc[w][gi][d] * f;
@@ -354,7 +363,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
     if (!is_last) return;
     __threadfence();
     // 1. every split's (max, sum) of every head -> shared memory
-    for (int e = threadIdx.x; e < n_heads * n_splits; e += AD_THREADS) {
+    for (int e = threadIdx.x; e < n_heads * n_splits; e += (NW * 32)) {
         const int gi = e / n_splits, sp = e % n_splits;
         const float* part = scratch + (((size_t)b * n_q + h0 + gi) * n_splits + sp) * (head_dim + 2);
         sm_pm[gi][sp] = __ldcg(part + head_dim);
@@ -376,7 +385,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
     }
     __syncthreads();
     // 3. weighted sum of the splits' values, in split order, loads four at a time
-    for (int e = threadIdx.x; e < n_heads * head_dim; e += AD_THREADS) {
+    for (int e = threadIdx.x; e < n_heads * head_dim; e += (NW * 32)) {
         const int gi = e / head_dim, d = e % head_dim;
         const float* base = scratch + ((size_t)b * n_q + h0 + gi) * n_splits * (head_dim + 2) + d;
         float a = 0.f;
@@ -429,11 +438,13 @@ static inline int ad_launch(const void* q, int ldq, const void* k_cache, const v
 #define SSB_AD_ARGS (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
         (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters, cos_t, sin_t, \
         (const char*)prefetch_ptr, (((uintptr_t)prefetch_ptr & 15) ? 0LL : prefetch_bytes)
+    // few blocks (small batches): 8 warps each, so that a page of keys is one turn of the block
+    const bool wide = (long long)grid.x * grid.y * grid.z <= 600;
+#define SSB_AD_W(V, FUSE_, FULL_) \
+    (wide ? ssb_launch(attention_decode_kernel<V, FUSE_, FULL_, 8>, grid, dim3(256), 0, stream, pdl, SSB_AD_ARGS) \
+          : ssb_launch(attention_decode_kernel<V, FUSE_, FULL_, 4>, grid, dim3(128), 0, stream, pdl, SSB_AD_ARGS))
 #define SSB_AD(V) \
-    rc = fuse ? ssb_launch(attention_decode_kernel<V, true, true>, grid, dim3(AD_THREADS), 0, stream, pdl, SSB_AD_ARGS) \
-       : head_dim == 32 * V \
-              ? ssb_launch(attention_decode_kernel<V, false, true>, grid, dim3(AD_THREADS), 0, stream, pdl, SSB_AD_ARGS) \
-              : ssb_launch(attention_decode_kernel<V, false, false>, grid, dim3(AD_THREADS), 0, stream, pdl, SSB_AD_ARGS)
+    rc = fuse ? SSB_AD_W(V, true, true) : head_dim == 32 * V ? SSB_AD_W(V, false, true) : SSB_AD_W(V, false, false)
     // vector loads need VEC elements aligned: rows are head_dim * 2 bytes apart
     if (vec == 1) SSB_AD(1);
     else if (vec == 2 && head_dim % 2 == 0 && ldq % 2 == 0) SSB_AD(2);
@@ -441,6 +452,7 @@ static inline int ad_launch(const void* q, int ldq, const void* k_cache, const v
     else if (vec <= 8 && head_dim % 8 == 0 && ldq % 8 == 0) SSB_AD(8);
     else return SSB_ERR_UNSUPPORTED;
 #undef SSB_AD
+#undef SSB_AD_W
 #undef SSB_AD_ARGS
     return rc ? rc : ssb_launch_status();
 }

@@ -108,7 +108,10 @@ class FastKernels(PlainKernels):
                           page_shift, window, scale, cos=None, sin=None):
         group = n_q // n_kv
         blocks = batch.n_seqs * n_kv * ((group + 3) // 4)
-        pages = batch.kv_pages if not window else min(batch.kv_pages, (window >> page_shift) + 2)
+        # the bucket's upper end: up to one page per split while the bucket lasts
+        pages = 2 * batch.kv_pages - 1 if batch.kv_pages > 1 else 1
+        if window:
+            pages = min(pages, (window >> page_shift) + 2)
         n_splits = max(1, min(TARGET_BLOCKS // blocks, pages, 64))
         scratch = counters = None
         if n_splits > 1:

@@ -48,7 +48,8 @@ class StepBatch:
 
 def decode_pages_bucket(longest: int, page_tokens: int = 64) -> int:
     """Pages spanned by ``longest`` tokens, rounded down to a power of two: kernels size their
-    grids from it, and a captured decode step stays valid while the bucket does."""
+    grids from it (a sequence in the bucket spans fewer than twice as many pages), and a captured
+    decode step stays valid while the bucket does."""
     pages = max(1, -(-longest // page_tokens))
     return 1 << (pages.bit_length() - 1)
 
