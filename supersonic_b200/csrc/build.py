@@ -38,7 +38,8 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "gemm_tc": {"sources": ["gemm_tc.cu"], "flags": [], "link": []},
     "attention_decode_static": {"sources": ["attention_decode_static.cu"], "flags": [], "link": []},
 }
-HEADERS = ["common.cuh", "attention_decode.cuh", "attention_decode_static.h"]
+HEADERS = ["common.cuh", "mma_helpers.cuh", "attention_decode.cuh", "attention_decode_mma.cuh",
+           "attention_decode_static.h"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

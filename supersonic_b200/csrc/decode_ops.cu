@@ -16,6 +16,7 @@
 // Softmax statistics, norms and all sums are float32.  No float atomics: every output element
 // is produced by one thread in a fixed order, so results do not depend on scheduling.
 #include "attention_decode.cuh"
+#include "attention_decode_mma.cuh"
 #include "common.cuh"
 #include <math.h>
 
@@ -60,7 +61,8 @@ __global__ void __launch_bounds__(SG_THREADS)
 skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restrict__ norm_w,
                    int norm_w_is_f32, float eps, const bf16* __restrict__ W, int ldw,
                    void* __restrict__ out, int ldo, int out_is_f32, int n_rows, int N, int K, int mode) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(128) unsigned char adm_smem[];
+    float* smem = reinterpret_cast<float*>(adm_smem);
     constexpr int ROWS = 16 * RM, COLS = 8 * NB, SG_UNROLL = sg_unroll(NB);
     float* red = smem;                                  // [SG_WARPS][ROWS][COLS]
     float* inv_rms = smem + SG_WARPS * ROWS * COLS;     // [COLS] (NORM only)
@@ -291,7 +293,15 @@ SSB_API int ssb_attention_decode(const void* q, int ldq, const void* k_cache, co
                                  void* out, int ldo, int n_seqs, int n_q, int n_kv, int head_dim,
                                  int page_shift, int window, float scale, int n_splits, float* scratch,
                                  int* counters, int pdl, const float* cos_t, const float* sin_t,
-                                 const void* prefetch_ptr, long long prefetch_bytes, cudaStream_t stream) {
+                                 const void* prefetch_ptr, long long prefetch_bytes, int kind,
+                                 cudaStream_t stream) {
+    // kind 0: the tensor-core kernel where it applies, else the general one; 1: general; 2: tensor-core
+    const bool mma_ok = page_shift == 6 && adm_supported(n_q, n_kv, head_dim, ldq, cos_t != nullptr);
+    if (kind == 2 && !mma_ok) return SSB_ERR_UNSUPPORTED;
+    if (kind != 1 && mma_ok)
+        return adm_launch(q, ldq, k_cache, v_cache, pos, slot, page_table, max_pages, out, ldo, n_seqs, n_q, n_kv,
+                          head_dim, window, scale, n_splits, scratch, counters, stream, pdl != 0, cos_t, sin_t,
+                          prefetch_ptr, prefetch_bytes);
     return ad_launch(q, ldq, k_cache, v_cache, pos, slot, page_table, max_pages, out, ldo, n_seqs, n_q, n_kv,
                      head_dim, page_shift, window, scale, n_splits, scratch, counters, stream, pdl != 0,
                      cos_t, sin_t, prefetch_ptr, prefetch_bytes);

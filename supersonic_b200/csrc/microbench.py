@@ -62,9 +62,10 @@ def attention_decode(args):
     scratch = torch.empty(max(nf, 1), device=DEV)
     counters = torch.zeros(max(nc, 1), dtype=torch.int32, device=DEV)
     us = _time(lambda i: ops.attention_decode(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, None,
-                                              1 / math.sqrt(hd), splits, scratch, counters), args.iters)
+                                              1 / math.sqrt(hd), splits, scratch, counters, kind=args.kind),
+               args.iters)
     nbytes = B * ctx * n_kv * hd * 2 * 2
-    return {"kernel": "attention_decode", "batch": B, "context": ctx, "splits": splits, "us": round(us, 2),
+    return {"kernel": "attention_decode", "kind": args.kind, "batch": B, "context": ctx, "splits": splits, "us": round(us, 2),
             "GB/s": round(nbytes / us / 1e3, 1)}
 
 
@@ -132,6 +133,7 @@ def main(argv=None):
         p.add_argument("--k", type=int, default=4096)
         p.add_argument("--kernel", default="skinny")
         p.add_argument("--tile", type=int, default=256)
+        p.add_argument("--kind", type=int, default=0, help="attention_decode: 0 auto, 1 general, 2 tensor-core")
         p.add_argument("--pdl", action="store_true", help="launch as programmatic dependents")
         p.add_argument("--seqs", type=int, default=1)
         p.add_argument("--tokens", type=int, default=2048)

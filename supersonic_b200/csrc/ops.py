@@ -279,12 +279,14 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      scratch: Optional[torch.Tensor], counters: Optional[torch.Tensor],
                      pdl: bool = False, cos: Optional[torch.Tensor] = None,
                      sin: Optional[torch.Tensor] = None, prefetch: Optional[torch.Tensor] = None,
-                     prefetch_bytes: int = 0) -> None:
+                     prefetch_bytes: int = 0, kind: int = 0) -> None:
     """One query token per sequence (row) over its cached keys, the keys split ``n_splits`` ways.
     With ``cos``/``sin`` ([positions, head_dim/2] float32) the rows of ``q`` are the raw fused
     projection [q | k | v]: queries and the token's key are rotated inside the kernel, and key
     and value are appended to the cache (no separate rope/append launch).  ``prefetch``: weights
-    that later kernels will stream; the first ``prefetch_bytes`` of it are pulled into L2 meanwhile."""
+    that later kernels will stream; the first ``prefetch_bytes`` of it are pulled into L2 meanwhile.
+    ``kind``: 0 picks the tensor-core kernel where it applies (head_dim 64/128, at most 16 query
+    heads per kv head), 1 forces the general kernel, 2 the tensor-core one."""
     _need(q, "q", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
     _need(k_cache, "k_cache", torch.bfloat16); _need(v_cache, "v_cache", torch.bfloat16)
     _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
@@ -311,7 +313,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         c_int(head_dim), c_int(page_shift), c_int(int(window) if window else 0), c_float(scale),
         c_int(n_splits), _ptr(scratch), _ptr(counters), c_int(1 if pdl else 0), _ptr(cos), _ptr(sin),
         _ptr(prefetch), c_longlong(min(prefetch_bytes, prefetch.numel() * prefetch.element_size())
-                                   if prefetch is not None else 0),
+                                   if prefetch is not None else 0), c_int(kind),
         _stream()), "attention_decode")
 
 

@@ -9,6 +9,7 @@
 // (head, query) row found by an atomic counter, two passes over the keys, float32 output that a
 // cast kernel then rounds (kernels/full_attention_cuda.cuh:360-474; bridge_cuda.cu:83-144, 1157-1180).
 #include "common.cuh"
+#include "mma_helpers.cuh"
 #include <math.h>
 
 typedef __nv_bfloat16 bf16;
@@ -16,38 +17,6 @@ typedef __nv_bfloat16 bf16;
 constexpr int PA_BM = 64;            // query rows per block: 4 warps x 16
 constexpr int PA_BN = 64;            // keys per turn = one cache page
 constexpr int PA_THREADS = 128;
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
-// Tiles in shared memory are [row][HD] bfloat16 with the 16-byte chunks of a row XOR-ed by
-// (row & 7), so that ldmatrix reads eight rows of one chunk column without bank conflicts.
-template <int HD>
-__device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
-    return (uint32_t)(row * HD * 2 + ((chunk ^ (row & 7)) << 4));
-}
 
 template <int HD>
 __global__ void __launch_bounds__(PA_THREADS)

@@ -341,7 +341,10 @@ def test_skinny_gemm_swiglu(rows):
                                                 (6, 2, 128, 100), (2, 2, 256, None), (8, 1, 64, 64),
                                                 (5, 5, 80, None)])
 @pytest.mark.parametrize("n_splits", [1, 3, 8])
-def test_attention_decode(n_q, n_kv, hd, window, n_splits):
+@pytest.mark.parametrize("kind", [1, 2])
+def test_attention_decode(n_q, n_kv, hd, window, n_splits, kind):
+    if kind == 2 and (hd not in (64, 128) or n_q // n_kv > 16):
+        pytest.skip("the tensor-core kernel takes head_dim 64/128 and at most 16 query heads per kv head")
     g = torch.Generator(device=DEV).manual_seed(23)
     pos = torch.tensor([0, 63, 64, 300, 299, 17, 128], dtype=torch.int32, device=DEV)
     slot = torch.tensor([0, 1, 2, 3, 4, -1, 5], dtype=torch.int32, device=DEV)
@@ -356,7 +359,7 @@ def test_attention_decode(n_q, n_kv, hd, window, n_splits):
     for _ in range(2):                                                   # counters are left ready for reuse
         out = torch.full((len(pos), n_q * hd), 5.0, dtype=torch.bfloat16, device=DEV)
         ops().attention_decode(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, window, scale, n_splits,
-                               scratch, counters)
+                               scratch, counters, kind=kind)
         torch.testing.assert_close(out.double(), ref, atol=2e-2, rtol=2e-2)
         assert torch.all(out[5] == 0) and torch.all(counters == 0)
     plain = torch.empty_like(out)
@@ -467,7 +470,10 @@ def test_attention_prefill_finds_a_far_key():
 @pytest.mark.parametrize("n_q,n_kv,hd,window", [(32, 8, 128, None), (4, 2, 64, None), (6, 2, 128, 100),
                                                 (2, 1, 32, None), (8, 8, 256, None)])
 @pytest.mark.parametrize("n_splits", [1, 4])
-def test_attention_decode_with_rotation_and_append_inside(n_q, n_kv, hd, window, n_splits):
+@pytest.mark.parametrize("kind", [1, 2])
+def test_attention_decode_with_rotation_and_append_inside(n_q, n_kv, hd, window, n_splits, kind):
+    if kind == 2 and (hd not in (64, 128) or n_q // n_kv > 16):
+        pytest.skip("the tensor-core kernel takes head_dim 64/128 and at most 16 query heads per kv head")
     """The fused launch equals rope_append followed by attention_decode: output, and the key
     and value it leaves in the cache; positions include 0, page borders and a padding row."""
     g = torch.Generator(device=DEV).manual_seed(50)
@@ -488,12 +494,12 @@ def test_attention_decode_with_rotation_and_append_inside(n_q, n_kv, hd, window,
     ops().rope_append(qkv_a, cos, sin, pos, slot, table, ka, va, n_q, n_kv, hd, hd, 6, True)
     want = torch.empty(len(pos), n_q * hd, dtype=torch.bfloat16, device=DEV)
     ops().attention_decode(qkv_a, ka, va, pos, slot, table, want, n_q, n_kv, hd, 6, window, scale, n_splits,
-                           scratch, counters)
+                           scratch, counters, kind=1)
     # the fused way
     qkv_b, kb, vb = qkv0.clone(), k0.clone(), v0.clone()
     got = torch.full_like(want, 5.0)
     ops().attention_decode(qkv_b, kb, vb, pos, slot, table, got, n_q, n_kv, hd, 6, window, scale, n_splits,
-                           scratch, counters, cos=cos, sin=sin)
+                           scratch, counters, cos=cos, sin=sin, kind=kind)
     torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
     assert torch.equal(qkv_b, qkv0)                                       # the projection's output is not touched
     assert torch.equal(vb, va)                                            # values are copied as they are
