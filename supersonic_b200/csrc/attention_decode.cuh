@@ -120,12 +120,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
     ssb_pdl_launch_dependents();
     // This kernel moves little data and waits on latencies: meanwhile it asks L2 to fetch a slice
     // of the weights that the kernels after it will stream (read-only memory, safe before the wait).
-    if (prefetch_bytes > 0 && threadIdx.x == 0) {
+    if (prefetch_bytes > 0) {                                    // pieces of 32 KB, spread over the threads
         const long long n_blocks = (long long)gridDim.x * gridDim.y * gridDim.z;
         const long long me = ((long long)blockIdx.x * gridDim.y + blockIdx.y) * gridDim.z + blockIdx.z;
-        const long long slice = ((prefetch_bytes + n_blocks - 1) / n_blocks + 15) & ~15LL;
+        // one SM can only feed so many of these requests: at most 512 KB a block
+        const long long slice = min(((prefetch_bytes + n_blocks - 1) / n_blocks + 15) & ~15LL, 524288LL);
         const long long lo_b = me * slice, hi_b = min(lo_b + slice, prefetch_bytes & ~15LL);
-        for (long long o = lo_b; o < hi_b; o += 32768) {
+        for (long long o = lo_b + (long long)threadIdx.x * 32768; o < hi_b; o += (long long)blockDim.x * 32768) {
             const unsigned n = (unsigned)min(32768LL, hi_b - o);
             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(prefetch_ptr + o), "r"(n) : "memory");
         }

@@ -45,15 +45,19 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 
     ssb_pdl_launch_dependents();
-    if (prefetch_bytes > 0 && threadIdx.x == 0) {                // see attention_decode.cuh
-        const long long n_blocks = (long long)gridDim.x * gridDim.y * gridDim.z;
-        const long long me = ((long long)blockIdx.x * gridDim.y + blockIdx.y) * gridDim.z + blockIdx.z;
-        const long long slice = ((prefetch_bytes + n_blocks - 1) / n_blocks + 15) & ~15LL;
+    if (split >= n_splits) {
+        // Extra blocks of the grid that only ask L2 to fetch a slice of the weights the next
+        // kernels will stream (read-only memory: safe while the predecessor still runs).  One SM
+        // can only feed so many of these requests, so they are spread over many blocks.
+        const long long n_pre = (long long)gridDim.x * gridDim.y * (gridDim.z - n_splits);
+        const long long me = ((long long)blockIdx.x * gridDim.y + blockIdx.y) * (gridDim.z - n_splits) + (split - n_splits);
+        const long long slice = ((prefetch_bytes + n_pre - 1) / n_pre + 15) & ~15LL;
         const long long lo_b = me * slice, hi_b = min(lo_b + slice, prefetch_bytes & ~15LL);
-        for (long long o = lo_b; o < hi_b; o += 32768) {
+        for (long long o = lo_b + (long long)threadIdx.x * 32768; o < hi_b; o += (long long)blockDim.x * 32768) {
             const unsigned n = (unsigned)min(32768LL, hi_b - o);
             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(prefetch_ptr + o), "r"(n) : "memory");
         }
+        return;
     }
     if (!FUSE) ssb_pdl_wait();                                   // the cache holds this step's key already
     const int s = slot[b];
@@ -362,9 +366,11 @@ static inline int adm_launch(const void* q, int ldq, const void* k_cache, const 
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return SSB_ERR_BAD_SIZE;
     const bool fuse = cos_t != nullptr;
     if (fuse && !sin_t) return SSB_ERR_BAD_SIZE;
-    dim3 grid(n_seqs, n_kv, n_splits);
     const float scale_log2 = scale * 1.4426950408889634f;
-    const long long pre = ((uintptr_t)prefetch_ptr & 15) ? 0LL : prefetch_bytes;
+    const long long pre = (!prefetch_ptr || ((uintptr_t)prefetch_ptr & 15)) ? 0LL : prefetch_bytes;
+    // about 128 extra blocks do the prefetching (see the kernel)
+    const int extra = pre > 0 ? (128 + n_seqs * n_kv - 1) / (n_seqs * n_kv) : 0;
+    dim3 grid(n_seqs, n_kv, n_splits + extra);
     int rc = 0;
 #define SSB_ADM(HD_, FUSE_) do { \
         constexpr int smem_bytes = 4 * 64 * HD_ * 2; \

@@ -112,7 +112,12 @@ class FastKernels(PlainKernels):
         pages = 2 * batch.kv_pages - 1 if batch.kv_pages > 1 else 1
         if window:
             pages = min(pages, (window >> page_shift) + 2)
-        n_splits = max(1, min(TARGET_BLOCKS // blocks, pages, 64))
+        if head_dim in (64, 128) and group <= 16 and page_shift == 6:
+            # tensor-core kernel: a block streams pages back to back; split only long contexts,
+            # at least 8 pages a split, about two blocks per SM (measured)
+            n_splits = max(1, min(296 // (batch.n_seqs * n_kv), pages // 8, 64))
+        else:
+            n_splits = max(1, min(TARGET_BLOCKS // blocks, pages, 64))
         scratch = counters = None
         if n_splits > 1:
             nf, nc = ops.attention_decode_scratch(batch.n_seqs, n_q, n_kv, head_dim, n_splits)
