@@ -118,19 +118,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
     const int n_heads = min(AD_GROUP, group - sub * AD_GROUP);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     ssb_pdl_launch_dependents();
-    // This kernel moves little data and waits on latencies: meanwhile it asks L2 to fetch a slice
-    // of the weights that the kernels after it will stream (read-only memory, safe before the wait).
-    if (prefetch_bytes > 0) {                                    // pieces of 32 KB, spread over the threads
-        const long long n_blocks = (long long)gridDim.x * gridDim.y * gridDim.z;
-        const long long me = ((long long)blockIdx.x * gridDim.y + blockIdx.y) * gridDim.z + blockIdx.z;
-        // one SM can only feed so many of these requests: at most 512 KB a block
-        const long long slice = min(((prefetch_bytes + n_blocks - 1) / n_blocks + 15) & ~15LL, 524288LL);
-        const long long lo_b = me * slice, hi_b = min(lo_b + slice, prefetch_bytes & ~15LL);
-        for (long long o = lo_b + (long long)threadIdx.x * 32768; o < hi_b; o += (long long)blockDim.x * 32768) {
-            const unsigned n = (unsigned)min(32768LL, hi_b - o);
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(prefetch_ptr + o), "r"(n) : "memory");
-        }
-    }
     // Without FUSE the predecessor (rope + append) wrote this step's key into the cache: wait
     // before reading anything.  With FUSE the cache holds earlier steps' keys only, and slots,
     // positions and page tables are written before the step starts: the first keys and values
@@ -184,6 +171,19 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
     int j0 = my_lo + warp * AD_TOK;
     if (j0 <= my_hi) issue(j0, ka, va);
     if (FUSE) ssb_pdl_wait();                                    // the query (and this token's k, v) come from the predecessor
+    // This kernel moves little data and waits on latencies: meanwhile it asks L2 to fetch a slice
+    // of the weights that the kernels after it will stream (after the wait: so as not to compete with the projection before it).
+    if (prefetch_bytes > 0) {                                    // pieces of 32 KB, spread over the threads
+        const long long n_blocks = (long long)gridDim.x * gridDim.y * gridDim.z;
+        const long long me = ((long long)blockIdx.x * gridDim.y + blockIdx.y) * gridDim.z + blockIdx.z;
+        // one SM can only feed so many of these requests: at most 512 KB a block
+        const long long slice = min(((prefetch_bytes + n_blocks - 1) / n_blocks + 15) & ~15LL, 524288LL);
+        const long long lo_b = me * slice, hi_b = min(lo_b + slice, prefetch_bytes & ~15LL);
+        for (long long o = lo_b + (long long)threadIdx.x * 32768; o < hi_b; o += (long long)blockDim.x * 32768) {
+            const unsigned n = (unsigned)min(32768LL, hi_b - o);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(prefetch_ptr + o), "r"(n) : "memory");
+        }
+    }
 
     // rotation of this lane's elements: pairs (i, i + head_dim/2) live in lanes l and l ^ 16
     float rc[VEC], rs[VEC];

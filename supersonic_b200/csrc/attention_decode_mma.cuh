@@ -47,8 +47,11 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
     ssb_pdl_launch_dependents();
     if (split >= n_splits) {
         // Extra blocks of the grid that only ask L2 to fetch a slice of the weights the next
-        // kernels will stream (read-only memory: safe while the predecessor still runs).  One SM
-        // can only feed so many of these requests, so they are spread over many blocks.
+        // kernels will stream.  They wait for the predecessor first: the point is to use the
+        // memory system while attention waits on its small loads, not to compete with the
+        // projection before it.  One SM can only feed so many of these requests, so they are
+        // spread over many blocks.
+        ssb_pdl_wait();
         const long long n_pre = (long long)gridDim.x * gridDim.y * (gridDim.z - n_splits);
         const long long me = ((long long)blockIdx.x * gridDim.y + blockIdx.y) * (gridDim.z - n_splits) + (split - n_splits);
         const long long slice = ((prefetch_bytes + n_pre - 1) / n_pre + 15) & ~15LL;

@@ -15,7 +15,7 @@ from .kernel_sets import NormedInput, PlainKernels, as_tensor
 
 FUSED_NORM_MAX_ROWS = 0        # measured: a separate norm launch is faster than the folded one at every batch size
 PREFETCH_BYTES = 64 << 20     # weights pulled into L2 during decode attention (L2 holds 126 MB)
-PREFETCH_MAX_ROWS = 16        # beyond this attention itself keeps the memory system busy
+PREFETCH_MAX_ROWS = 0         # off: measured no gain (the projections are issue-bound, not DRAM-bound)
 SKINNY_MAX_ROWS = 16          # above this the tcgen05 GEMM streams the weights faster (measured)
 TARGET_BLOCKS = 1184           # eight small blocks per SM
 
@@ -112,10 +112,16 @@ class FastKernels(PlainKernels):
         pages = 2 * batch.kv_pages - 1 if batch.kv_pages > 1 else 1
         if window:
             pages = min(pages, (window >> page_shift) + 2)
-        if head_dim in (64, 128) and group <= 16 and page_shift == 6:
-            # tensor-core kernel: a block streams pages back to back; split only long contexts,
-            # at least 8 pages a split, about two blocks per SM (measured)
+        kind = 1
+        if head_dim in (64, 128) and group <= 16 and page_shift == 6 and (batch.n_seqs >= 32 or pages >= 32):
+            # tensor-core kernel (many sequences or long contexts): a block streams pages back to
+            # back; at least 8 pages a split, about two blocks per SM
+            kind = 2
             n_splits = max(1, min(296 // (batch.n_seqs * n_kv), pages // 8, 64))
+        elif batch.n_seqs <= 2:
+            n_splits = max(1, min(TARGET_BLOCKS // blocks, pages, 16))    # latency-bound: a page a block
+        elif pages < 32:
+            n_splits = min(2, pages)                                      # measured best for 3..31 sequences
         else:
             n_splits = max(1, min(TARGET_BLOCKS // blocks, pages, 64))
         scratch = counters = None
@@ -125,7 +131,7 @@ class FastKernels(PlainKernels):
             counters = self._buffer("attn_counters", nc, torch.int32, q.device, zero=True)
         ops.attention_decode(q, k_cache, v_cache, batch.pos, batch.slot_of_token, page_table, out,
                              n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters,
-                             pdl=self.pdl, cos=cos, sin=sin,
+                             pdl=self.pdl, cos=cos, sin=sin, kind=kind,
                              prefetch=self._next_weights if batch.n_seqs <= PREFETCH_MAX_ROWS else None,
                              prefetch_bytes=PREFETCH_BYTES)
         self._next_weights = None
