@@ -60,7 +60,9 @@ template <int RM, int NB, bool NORM>
 __global__ void __launch_bounds__(SG_THREADS)
 skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restrict__ norm_w,
                    int norm_w_is_f32, float eps, const bf16* __restrict__ W, int ldw,
-                   void* __restrict__ out, int ldo, int out_is_f32, int n_rows, int N, int K, int mode) {
+                   void* __restrict__ out, int ldo, int out_is_f32, int n_rows, int N, int K, int mode,
+                   const void* __restrict__ post_w, int post_w_is_f32, float post_eps, bf16* __restrict__ post_out,
+                   int* __restrict__ post_counter) {
     extern __shared__ __align__(128) unsigned char adm_smem[];
     float* smem = reinterpret_cast<float*>(adm_smem);
     constexpr int ROWS = 16 * RM, COLS = 8 * NB, SG_UNROLL = sg_unroll(NB);
@@ -230,12 +232,56 @@ skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restric
         else if (out_is_f32) ((float*)out)[o] = s;
         else ((bf16*)out)[o] = __float2bfloat16_rn(s);
     }
+    if (post_out == nullptr) return;
+
+    // RMSNorm of the finished rows, by the block that finishes last: out (float32, the residual
+    // stream) is complete once every block has added its columns.  Saves the separate norm launch
+    // between this projection and the next one.
+    __shared__ int post_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int arrived = atomicAdd(post_counter, 1);
+        post_last = (arrived == (int)gridDim.x - 1);
+        if (post_last) *post_counter = 0;               // ready for the next launch
+    }
+    __syncthreads();
+    if (!post_last) return;
+    __threadfence();
+    const float* res = (const float*)out;
+    for (int b = warp; b < n_rows; b += SG_WARPS) {     // a warp per row
+        float ssq = 0.f;
+        for (int k = lane * 4; k < N; k += 128) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(res + (size_t)b * ldo + k));
+            ssq = fmaf(v.x, v.x, ssq); ssq = fmaf(v.y, v.y, ssq); ssq = fmaf(v.z, v.z, ssq); ssq = fmaf(v.w, v.w, ssq);
+        }
+        for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+        const float inv = 1.0f / sqrtf(ssq / (float)N + post_eps);
+        for (int k = lane * 4; k < N; k += 128) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(res + (size_t)b * ldo + k));
+            float w0, w1, w2, w3;
+            if (post_w_is_f32) {
+                const float4 w = *reinterpret_cast<const float4*>((const float*)post_w + k);
+                w0 = w.x; w1 = w.y; w2 = w.z; w3 = w.w;
+            } else {
+                const uint2 wq = *reinterpret_cast<const uint2*>((const bf16*)post_w + k);
+                const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wq.x));
+                const float2 fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wq.y));
+                w0 = fa.x; w1 = fa.y; w2 = fb.x; w3 = fb.y;
+            }
+            uint2 packed;
+            packed.x = pack_bf16(v.x * inv * w0, v.y * inv * w1);
+            packed.y = pack_bf16(v.z * inv * w2, v.w * inv * w3);
+            *reinterpret_cast<uint2*>(post_out + (size_t)b * N + k) = packed;
+        }
+    }
 }
 
 template <int RM, int NB, bool NORM>
 static int launch_skinny(const void* x, int ldx, const void* norm_w, int norm_w_is_f32, float eps,
                          const bf16* W, int ldw, void* out, int ldo, int out_is_f32, int n_rows, int N,
-                         int K, int mode, int pdl, cudaStream_t stream) {
+                         int K, int mode, int pdl, const void* post_w, int post_w_is_f32, float post_eps,
+                         bf16* post_out, int* post_counter, cudaStream_t stream) {
     constexpr int ROWS = 16 * RM, COLS = 8 * NB;
     const size_t smem = (size_t)(SG_WARPS * ROWS * COLS + COLS + SG_WARPS * COLS) * sizeof(float);
     auto kern = skinny_gemm_kernel<RM, NB, NORM>;
@@ -244,7 +290,8 @@ static int launch_skinny(const void* x, int ldx, const void* norm_w, int norm_w_
         if (e != cudaSuccess) return (int)e;
     }
     return ssb_launch(kern, dim3((N + ROWS - 1) / ROWS), dim3(SG_THREADS), smem, stream, pdl != 0, x, ldx, norm_w,
-                      norm_w_is_f32, eps, W, ldw, out, ldo, out_is_f32, n_rows, N, K, mode);
+                      norm_w_is_f32, eps, W, ldw, out, ldo, out_is_f32, n_rows, N, K, mode, post_w, post_w_is_f32,
+                      post_eps, post_out, post_counter);
 }
 
 // x: bfloat16 [n_rows, K] (norm_w == null) or the float32 residual [n_rows, K] normalised on the
@@ -252,19 +299,25 @@ static int launch_skinny(const void* x, int ldx, const void* norm_w, int norm_w_
 // (bfloat16 or float32); mode 1: out (float32) += ; mode 2: W's rows come as [8 gate | 8 up] per
 // 16 and out (bfloat16, [n_rows, N/2]) = silu(gate) * up.  pdl: launch as a programmatic
 // dependent of the kernel before it on the stream (weights are prefetched while that one ends).
+// post_out (mode 1 only): bfloat16 [n_rows, N] that receives RMSNorm(out; post_w, post_eps) of the
+// finished rows, computed by the block that finishes last; post_counter: a zeroed int, left zero.
 SSB_API int ssb_skinny_gemm(const void* x, int ldx, const void* norm_w, int norm_w_dtype, float eps,
                             const void* W, int ldw, void* out, int ldo, int out_dtype, int n_rows, int N,
-                            int K, int mode, int pdl, cudaStream_t stream) {
+                            int K, int mode, int pdl, const void* post_w, int post_w_dtype, float post_eps,
+                            void* post_out, int* post_counter, cudaStream_t stream) {
     if (n_rows <= 0 || N <= 0) return 0;
     if (n_rows > 64 || K <= 0 || K % 8 || ldw % 8 || ldx % 8) return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)x | (uintptr_t)W | (uintptr_t)norm_w) & 15) return SSB_ERR_BAD_SIZE;
     if (mode == SG_ACCUMULATE && out_dtype != SSB_F32) return SSB_ERR_BAD_DTYPE;
     if (mode == SG_SWIGLU && (out_dtype != SSB_BF16 || N % 16)) return SSB_ERR_BAD_SIZE;
-    const int f32o = out_dtype == SSB_F32, nwf = norm_w_dtype == SSB_F32;
+    const int f32o = out_dtype == SSB_F32, nwf = norm_w_dtype == SSB_F32, pwf = post_w_dtype == SSB_F32;
+    if (post_out && (mode != SG_ACCUMULATE || !post_w || !post_counter || N % 4 || ldo % 4 ||
+                     (((uintptr_t)post_w | (uintptr_t)post_out | (uintptr_t)out) & 15)))
+        return SSB_ERR_BAD_SIZE;
     const bf16* Wb = (const bf16*)W;
 #define SSB_SG(RM, NB) \
-    return norm_w ? launch_skinny<RM, NB, true>(x, ldx, norm_w, nwf, eps, Wb, ldw, out, ldo, f32o, n_rows, N, K, mode, pdl, stream) \
-                  : launch_skinny<RM, NB, false>(x, ldx, nullptr, 0, 0.f, Wb, ldw, out, ldo, f32o, n_rows, N, K, mode, pdl, stream)
+    return norm_w ? launch_skinny<RM, NB, true>(x, ldx, norm_w, nwf, eps, Wb, ldw, out, ldo, f32o, n_rows, N, K, mode, pdl, post_w, pwf, post_eps, (bf16*)post_out, post_counter, stream) \
+                  : launch_skinny<RM, NB, false>(x, ldx, nullptr, 0, 0.f, Wb, ldw, out, ldo, f32o, n_rows, N, K, mode, pdl, post_w, pwf, post_eps, (bf16*)post_out, post_counter, stream)
     if (n_rows <= 8) { SSB_SG(1, 1); }
     if (n_rows <= 16) { SSB_SG(2, 2); }
     if (n_rows <= 32) { SSB_SG(2, 4); }

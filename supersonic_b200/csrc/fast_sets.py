@@ -26,6 +26,9 @@ class FastKernels(PlainKernels):
     def __init__(self, pdl: bool = True):
         self.pdl = pdl           # decode kernels launch as programmatic dependents of their predecessors
         self.fuse_rope = True    # decode attention rotates q/k and appends to the cache itself
+        # a residual-adding projection can also write the next norm of the residual (its last block
+        # does it); measured slower than the separate norm launch at batch 1 and 8, so it is off
+        self.fuse_post_norm = False
         self._next_weights = None
         self._scratch: Dict[str, torch.Tensor] = {}
         self._retired = []      # outgrown buffers stay alive: captured graphs still point at them
@@ -34,7 +37,7 @@ class FastKernels(PlainKernels):
         ops.rmsnorm(x, weight, eps, out, rows, pdl=self.pdl and out.shape[0] <= 64)
 
     # ---- matrix products -------------------------------------------------------------
-    def _skinny(self, x, weight, out, mode):
+    def _skinny(self, x, weight, out, mode, then_norm=None):
         if isinstance(x, NormedInput):
             if (x._tensor is None and x.fusable and x.n_rows <= FUSED_NORM_MAX_ROWS
                     and ops.skinny_gemm_ok(x.residual, weight, True) and x.weight.data_ptr() % 16 == 0):
@@ -42,14 +45,23 @@ class FastKernels(PlainKernels):
                 return True
             x = x.tensor()
         if ops.skinny_gemm_ok(x, weight, False):
-            ops.skinny_gemm(x, weight, out, mode, pdl=self.pdl)
+            post = None
+            if (then_norm is not None and mode == ops.SG_ACCUMULATE and self.fuse_post_norm and then_norm.fusable
+                    and then_norm._tensor is None and then_norm.residual is out and out.is_contiguous()
+                    and out.shape[1] % 4 == 0 and then_norm.weight.data_ptr() % 16 == 0):
+                normed = torch.empty(out.shape, dtype=torch.bfloat16, device=out.device)
+                post = (then_norm.weight, then_norm.eps, normed,
+                        self._buffer("post_norm_counter", 1, torch.int32, out.device, zero=True))
+            ops.skinny_gemm(x, weight, out, mode, pdl=self.pdl, post_norm=post)
+            if post is not None:
+                then_norm.provide(post[2])
             return True
         return False
 
-    def linear(self, x, weight, out, accumulate=False):
+    def linear(self, x, weight, out, accumulate=False, then_norm=None):
         rows = x.n_rows if isinstance(x, NormedInput) else x.shape[0]
         if rows <= SKINNY_MAX_ROWS and weight.dtype == torch.bfloat16 and (out.dtype == torch.float32 or not accumulate):
-            if self._skinny(x, weight, out, ops.SG_ACCUMULATE if accumulate else ops.SG_STORE):
+            if self._skinny(x, weight, out, ops.SG_ACCUMULATE if accumulate else ops.SG_STORE, then_norm):
                 return
         x = as_tensor(x)
         if rows > SKINNY_MAX_ROWS and (out.dtype == torch.float32 or not accumulate) and ops.gemm_tc_ok(x, weight, out):

@@ -41,6 +41,10 @@ class NormedInput:
     def n_rows(self) -> int:
         return self.residual.shape[0]
 
+    def provide(self, tensor: torch.Tensor) -> None:
+        """A kernel computed the norm on its way: ``tensor()`` will return this."""
+        self._tensor = tensor
+
     def tensor(self) -> torch.Tensor:
         if self._tensor is None:
             self._tensor = self.norm(self.ctx, self.residual)
@@ -60,8 +64,10 @@ class PlainKernels:
     def rmsnorm(self, x, weight, eps, out, rows=None):
         ops.rmsnorm(x, weight, eps, out, rows)
 
-    def linear(self, x, weight, out, accumulate=False):
-        """out (+)= x @ weight^T; ``x`` may be a :class:`NormedInput`."""
+    def linear(self, x, weight, out, accumulate=False, then_norm=None):
+        """out (+)= x @ weight^T; ``x`` may be a :class:`NormedInput`.  ``then_norm``: the
+        :class:`NormedInput` of ``out`` that will be asked for next, if this call is the last
+        change to ``out`` before it; a set may compute it on the way (here it is left alone)."""
         ops.gemm_nt_plain(as_tensor(x), weight, out, accumulate)
 
     def pack_gate_up(self, gate, up):

@@ -241,10 +241,13 @@ def skinny_gemm_ok(x: torch.Tensor, w: torch.Tensor, normed: bool) -> bool:
 
 
 def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = SG_STORE,
-                norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, pdl: bool = False) -> None:
+                norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, pdl: bool = False,
+                post_norm=None) -> None:
     """out = x @ w^T for up to 64 rows.  With ``norm_weight`` x is the float32 residual and is
     RMS-normalised on the way in.  ``pdl``: launch as a programmatic dependent of the kernel
-    before it on the stream (its weights are prefetched while that kernel ends).  mode: store, add into float32 ``out``, or SwiGLU over rows
+    before it on the stream (its weights are prefetched while that kernel ends).
+    ``post_norm`` = (weight, eps, out bfloat16 [rows, N], zeroed int32 counter), with mode accumulate:
+    the block that finishes last also writes RMSNorm(out) of the finished rows into it.  mode: store, add into float32 ``out``, or SwiGLU over rows
     of ``w`` that come as [8 gate | 8 up] per 16 (``out`` is [rows, N/2])."""
     _need(x, "x", torch.float32 if norm_weight is not None else torch.bfloat16, 2)
     _need(w, "w", torch.bfloat16, 2); _need(out, "out", None, 2)
@@ -257,11 +260,21 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int =
         _need(norm_weight, "norm_weight", None, 1)
         if norm_weight.shape[0] != K:
             raise KernelError("skinny_gemm: norm weight width")
+    pw = pout = pcount = None
+    peps = 0.0
+    if post_norm is not None:
+        pw, peps, pout, pcount = post_norm
+        _need(pw, "post norm weight", None, 1); _need(pout, "post norm out", torch.bfloat16, 2)
+        _need(pcount, "post norm counter", torch.int32)
+        if mode != SG_ACCUMULATE or pw.shape[0] != N or tuple(pout.shape) != (B, N) or not pout.is_contiguous():
+            raise KernelError("skinny_gemm: the post norm goes with mode accumulate and out-shaped tensors")
     _check(_fn("decode_ops", "ssb_skinny_gemm")(
         _ptr(x), c_int(x.stride(0)), _ptr(norm_weight),
         c_int(dtype_code(norm_weight.dtype) if norm_weight is not None else 0), c_float(eps), _ptr(w),
         c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(dtype_code(out.dtype)), c_int(B),
-        c_int(N), c_int(K), c_int(mode), c_int(1 if pdl else 0), _stream()), "skinny_gemm")
+        c_int(N), c_int(K), c_int(mode), c_int(1 if pdl else 0), _ptr(pw),
+        c_int(dtype_code(pw.dtype) if pw is not None else 0), c_float(peps), _ptr(pout), _ptr(pcount),
+        _stream()), "skinny_gemm")
 
 
 def attention_decode_scratch(n_seqs: int, n_q: int, n_kv: int, head_dim: int, n_splits: int):

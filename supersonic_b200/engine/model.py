@@ -55,6 +55,7 @@ class StepContext:
     cache: SequenceCache
     kernels: Any
     dtype: torch.dtype
+    next_norm: Any = None      # see parts/block.py
 
 
 class DecodeGraph:
@@ -225,8 +226,17 @@ class Model:
     def _forward(self, batch: StepBatch) -> torch.Tensor:
         ctx = StepContext(batch, self.cache, self.kernels, self.dtype)
         residual = self.embedding(ctx, batch.token_ids)
-        for stop in self.spec.schedule:
-            self.blocks[stop.layer].forward(ctx, residual, stop.cache, stop.writes_cache)
+        schedule = self.spec.schedule
+        x_in = None
+        for i, stop in enumerate(schedule):
+            block = self.blocks[stop.layer]
+            nxt = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+            next_in = nxt.input_norm(ctx, residual) if nxt is not None and hasattr(nxt, "input_norm") else None
+            if hasattr(block, "input_norm"):
+                block.forward(ctx, residual, stop.cache, stop.writes_cache, x_in=x_in, next_in=next_in)
+            else:                                           # a block arrangement without this protocol
+                block.forward(ctx, residual, stop.cache, stop.writes_cache)
+            x_in = next_in
         if batch.n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         normed = self.final_norm(ctx, residual, rows=batch.want_rows)

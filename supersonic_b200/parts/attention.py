@@ -69,4 +69,4 @@ class Attention:
             k_cache, v_cache, table, _ = kv
             ctx.kernels.attention(qkv, k_cache, v_cache, ctx.batch, table, attn, self.n_q, self.n_kv,
                                   self.head_dim, PAGE_SHIFT, self.window, self.scale)
-        ctx.kernels.linear(attn, self.w_o, residual, accumulate=True)
+        ctx.kernels.linear(attn, self.w_o, residual, accumulate=True, then_norm=getattr(ctx, "next_norm", None))

@@ -39,4 +39,4 @@ class SwiGLU:
     def forward(self, ctx, x, residual):
         z = torch.empty((residual.shape[0], self.inter), dtype=self.dtype, device=residual.device)
         ctx.kernels.gate_up_swiglu(x, self.w_gate_up, self.layout, z)
-        ctx.kernels.linear(z, self.w_down, residual, accumulate=True)
+        ctx.kernels.linear(z, self.w_down, residual, accumulate=True, then_norm=getattr(ctx, "next_norm", None))

@@ -505,3 +505,27 @@ def test_attention_decode_with_rotation_and_append_inside(n_q, n_kv, hd, window,
     assert torch.equal(vb, va)                                            # values are copied as they are
     torch.testing.assert_close(kb.float(), ka.float(), atol=0, rtol=2 ** -7)   # keys: at most the last bit
     assert torch.all(got[5] == 0) and torch.all(counters == 0)
+
+
+@pytest.mark.parametrize("rows,wdtype", [(1, torch.bfloat16), (8, torch.float32), (16, torch.bfloat16)])
+def test_skinny_gemm_writes_the_next_norm_of_the_residual(rows, wdtype):
+    """Mode accumulate with a post norm: the residual gets the product added, and the block
+    that finishes last leaves RMSNorm(residual) of the finished rows; twice in a row (the counter
+    is left ready)."""
+    g = torch.Generator(device=DEV).manual_seed(60)
+    K, N = 1440, 4096
+    x = torch.randn(rows, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    nw = (1 + 0.1 * torch.randn(N, device=DEV, generator=g)).to(wdtype)
+    res = torch.randn(rows, N, device=DEV, generator=g)
+    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        want_res = res.clone()
+        ops().skinny_gemm(x, w, want_res, mode=1)
+        want = torch.empty(rows, N, dtype=torch.bfloat16, device=DEV)
+        ops().rmsnorm(want_res, nw, 1e-5, want)
+        got = torch.full((rows, N), 7.0, dtype=torch.bfloat16, device=DEV)
+        ops().skinny_gemm(x, w, res, mode=1, post_norm=(nw, 1e-5, got, counter))
+        assert torch.equal(res, want_res) and int(counter.item()) == 0
+        # same formula; the sum of squares is added in another order
+        torch.testing.assert_close(got.float(), want.float(), atol=0, rtol=2 ** -7)
