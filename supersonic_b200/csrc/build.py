@@ -35,10 +35,11 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "sampling": {"sources": ["sampling.cu"], "flags": [], "link": []},
     "decode_ops": {"sources": ["decode_ops.cu"], "flags": [], "link": []},
     "prefill_attention": {"sources": ["prefill_attention.cu"], "flags": [], "link": []},
+    "gemv_tc": {"sources": ["gemv_tc.cu"], "flags": [], "link": []},
     "gemm_tc": {"sources": ["gemm_tc.cu"], "flags": [], "link": []},
     "attention_decode_static": {"sources": ["attention_decode_static.cu"], "flags": [], "link": []},
 }
-HEADERS = ["common.cuh", "mma_helpers.cuh", "attention_decode.cuh", "attention_decode_mma.cuh",
+HEADERS = ["common.cuh", "mma_helpers.cuh", "tc_helpers.cuh", "attention_decode.cuh", "attention_decode_mma.cuh",
            "attention_decode_static.h"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}

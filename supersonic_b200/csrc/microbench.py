@@ -77,6 +77,13 @@ def linear(args):
     out = torch.empty(B, N, dtype=torch.bfloat16, device=DEV)
     if args.kernel == "skinny":
         fn = lambda i: ops.skinny_gemm(x, ws[i % copies], out, pdl=args.pdl)
+    elif args.kernel.startswith("gv"):                      # gv = automatic splits, gv4 = 4 splits
+        splits = int(args.kernel[2:]) if len(args.kernel) > 2 else ops.gemv_tc_splits(N, K)
+        nf, nc = ops.gemv_tc_scratch(B, N, splits)
+        partials = torch.empty(max(nf, 4), device=DEV)
+        counters = torch.zeros(max(nc, 1), dtype=torch.int32, device=DEV)
+        fn = lambda i: ops.gemv_tc(x, ws[i % copies], out, splits=splits, partials=partials, counters=counters,
+                                   pdl=args.pdl)
     else:
         tile = int(args.kernel[2:])
         fn = lambda i: ops.gemm_tc(x, ws[i % copies], out, tile_n=tile)

@@ -416,3 +416,44 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         _ptr(seq_slot), _ptr(page_table), c_int(page_table.shape[1]), _ptr(out), c_int(out.stride(0)),
         c_int(n_seqs), c_int(max_new), c_int(n_q), c_int(n_kv), c_int(head_dim), c_int(page_shift),
         c_int(int(window) if window else 0), c_float(scale), _stream()), "attention_prefill")
+
+
+# ---- decode projections on tcgen05, weights on the M side ------------------------------------------
+def gemv_tc_splits(n: int, k: int) -> int:
+    """Blocks that share the K range of one 128-row tile of W: enough for about 1.5 blocks per SM,
+    at least 8 k-blocks (512 columns) each."""
+    tiles = (n + 127) // 128
+    return max(1, min(222 // tiles, (k // 64) // 8, 8))
+
+
+def gemv_tc_scratch(rows: int, n: int, splits: int):
+    lib = load_library("gemv_tc")
+    lib.ssb_gemv_tc_scratch_floats.restype = c_longlong
+    return (int(lib.ssb_gemv_tc_scratch_floats(c_int(rows), c_int(n), c_int(splits))),
+            int(lib.ssb_gemv_tc_counters(c_int(n))))
+
+
+def gemv_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_STORE, splits: int = 1,
+            partials: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None,
+            pdl: bool = False) -> None:
+    """out = x @ w^T for up to 64 rows with the weights as the M side of tcgen05.mma (they stream
+    once, 16 KB a stage).  ``splits`` > 1 shares the K range of a row tile among blocks; needs
+    ``partials``/``counters`` sized by :func:`gemv_tc_scratch` (counters zeroed once)."""
+    _need(x, "x", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(out, "out", None, 2)
+    B, K = x.shape
+    N = w.shape[0]
+    n_out = N // 2 if mode == TC_SWIGLU else N
+    if w.shape[1] != K or tuple(out.shape) != (B, n_out) or B > 64:
+        raise KernelError(f"gemv_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if splits > 1:
+        nf, nc = gemv_tc_scratch(B, N, splits)
+        _need(partials, "partials", torch.float32); _need(counters, "counters", torch.int32)
+        if partials.numel() < nf or counters.numel() < nc:
+            raise KernelError(f"gemv_tc: scratch of {nf} floats and {nc} counters needed")
+    global _tc_unchecked
+    _tc_unchecked += 1
+    _check(_fn("gemv_tc", "ssb_gemv_tc")(
+        _ptr(x), c_int(x.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)),
+        c_int(dtype_code(out.dtype)), c_int(B), c_int(N), c_int(K), c_int(mode), c_int(splits),
+        _ptr(partials), _ptr(counters), _ptr(tc_error_word(x.device)), c_int(1 if pdl else 0), _stream()),
+        "gemv_tc")

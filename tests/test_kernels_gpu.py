@@ -529,3 +529,51 @@ def test_skinny_gemm_writes_the_next_norm_of_the_residual(rows, wdtype):
         assert torch.equal(res, want_res) and int(counter.item()) == 0
         # same formula; the sum of squares is added in another order
         torch.testing.assert_close(got.float(), want.float(), atol=0, rtol=2 ** -7)
+
+
+# ---- decode projections on tcgen05, weights on the M side ---------------------------------------
+@pytest.mark.parametrize("rows", [1, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,K,splits", [(304, 72, 1), (1000, 4096, 1), (1000, 4096, 5), (128, 640, 3), (272, 1440, 8)])
+def test_gemv_tc(rows, N, K, splits):
+    g = torch.Generator(device=DEV).manual_seed(70)
+    x = torch.randn(rows, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    ref = x.double() @ w.double().T
+    nf, nc = ops().gemv_tc_scratch(rows, N, splits)
+    partials = torch.full((max(nf, 4),), float("nan"), device=DEV)
+    counters = torch.zeros(max(nc, 1), dtype=torch.int32, device=DEV)
+    kw = dict(splits=splits, partials=partials, counters=counters)
+    for _ in range(2):                                                   # the counters are left ready
+        out = torch.full((rows, N), 9.0, device=DEV)
+        ops().gemv_tc(x, w, out, **kw)
+        ops().check_device_errors()
+        torch.testing.assert_close(out.double(), ref, atol=2e-5 * math.sqrt(K), rtol=1e-4)
+        assert torch.all(counters == 0)
+    ob = torch.empty(rows, N, dtype=torch.bfloat16, device=DEV)
+    ops().gemv_tc(x, w, ob, **kw)
+    torch.testing.assert_close(ob.double(), ref, atol=2e-2, rtol=2e-2)
+    acc = torch.full((rows, N), 2.0, device=DEV)
+    ops().gemv_tc(x, w, acc, mode=1, **kw)
+    torch.testing.assert_close(acc.double(), ref + 2, atol=2e-5 * math.sqrt(K), rtol=1e-4)
+    again = torch.full((rows, N), 9.0, device=DEV)
+    ops().gemv_tc(x, w, again, **kw)
+    assert torch.equal(again, out)                                       # same sum order every time
+    ops().check_device_errors()
+
+
+@pytest.mark.parametrize("rows,splits", [(20, 1), (64, 3)])
+def test_gemv_tc_swiglu(rows, splits):
+    g = torch.Generator(device=DEV).manual_seed(71)
+    K, inter = 576, 200
+    x = torch.randn(rows, K, device=DEV, generator=g).bfloat16()
+    gate = (torch.randn(inter, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    up = (torch.randn(inter, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    from supersonic_b200.csrc.fast_sets import FastKernels
+    packed, layout = FastKernels().pack_gate_up(gate, up)
+    nf, nc = ops().gemv_tc_scratch(rows, 2 * inter, splits)
+    out = torch.empty(rows, inter, dtype=torch.bfloat16, device=DEV)
+    ops().gemv_tc(x, packed, out, mode=2, splits=splits, partials=torch.empty(max(nf, 4), device=DEV),
+                  counters=torch.zeros(max(nc, 1), dtype=torch.int32, device=DEV))
+    ops().check_device_errors()
+    gg, uu = x.double() @ gate.double().T, x.double() @ up.double().T
+    torch.testing.assert_close(out.double(), gg / (1 + torch.exp(-gg)) * uu, atol=2e-2, rtol=2e-2)
