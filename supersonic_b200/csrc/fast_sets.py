@@ -16,7 +16,7 @@ from .kernel_sets import NormedInput, PlainKernels, as_tensor
 FUSED_NORM_MAX_ROWS = 0        # measured: a separate norm launch is faster than the folded one at every batch size
 PREFETCH_BYTES = 64 << 20     # weights pulled into L2 during decode attention (L2 holds 126 MB)
 PREFETCH_MAX_ROWS = 0         # off: measured no gain (the projections are issue-bound, not DRAM-bound)
-SKINNY_MAX_ROWS = 16          # above this the tcgen05 GEMM streams the weights faster (measured)
+SKINNY_MAX_ROWS = 8           # above this the tcgen05 kernels stream the weights faster (measured)
 TARGET_BLOCKS = 1184           # eight small blocks per SM
 
 
@@ -65,8 +65,15 @@ class FastKernels(PlainKernels):
                 return
         x = as_tensor(x)
         if rows > SKINNY_MAX_ROWS and (out.dtype == torch.float32 or not accumulate) and ops.gemm_tc_ok(x, weight, out):
-            ops.gemm_tc(x, weight, out, ops.TC_ACCUMULATE if accumulate else ops.TC_STORE,
-                        tile_n=self._tile_n(rows, weight.shape[0]))
+            n, k = weight.shape
+            if rows <= 64 and accumulate:
+                # weights on the M side, K split over blocks that add with float atomics
+                ops.gemv_tc(x, weight, out, ops.TC_ACCUMULATE, splits=ops.gemv_tc_splits(n, k), pdl=self.pdl)
+            elif rows <= 64 and n >= 16384:
+                ops.gemv_tc(x, weight, out, ops.TC_STORE, pdl=self.pdl)
+            else:
+                ops.gemm_tc(x, weight, out, ops.TC_ACCUMULATE if accumulate else ops.TC_STORE,
+                            tile_n=self._tile_n(rows, n))
             return
         if rows <= 64 and weight.dtype == torch.bfloat16 and (out.dtype == torch.float32 or not accumulate):
             if self._skinny(x, weight, out, ops.SG_ACCUMULATE if accumulate else ops.SG_STORE):
@@ -95,7 +102,10 @@ class FastKernels(PlainKernels):
         if layout == "interleaved" and rows > SKINNY_MAX_ROWS:
             xt = as_tensor(x)
             if w_gate_up.shape[0] % 16 == 0 and ops.gemm_tc_ok(xt, w_gate_up, out):
-                ops.gemm_tc(xt, w_gate_up, out, ops.TC_SWIGLU, tile_n=self._tile_n(rows, w_gate_up.shape[0]))
+                if rows <= 64:
+                    ops.gemv_tc(xt, w_gate_up, out, ops.TC_SWIGLU, pdl=self.pdl)
+                else:
+                    ops.gemm_tc(xt, w_gate_up, out, ops.TC_SWIGLU, tile_n=self._tile_n(rows, w_gate_up.shape[0]))
                 return
         if layout == "interleaved" and rows <= 64 and self._skinny(x, w_gate_up, out, ops.SG_SWIGLU):
             return

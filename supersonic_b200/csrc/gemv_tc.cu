@@ -1,11 +1,13 @@
 // Decode projections for 17 to 64 rows on tcgen05: out[b, n] = sum_k x[b, k] W[n, k], with the
 // weights as the M side of the MMA.  A block owns 128 rows of W and a range of K; 128 x 64 tiles
 // of W (16 KB of useful bytes a stage) and the matching columns of x arrive through TMA into an
-// eight-stage ring; one thread issues tcgen05.mma (M 128, N = rows rounded up to 16/32/64); the
+// four-stage ring; one thread issues tcgen05.mma (M 128, N = rows rounded up to 16/32/64); the
 // accumulator [W row, batch row] sits in tensor memory.  When K is split over several blocks
-// (few row tiles: the small projections), each writes its partial tile to scratch and the block
-// that arrives last for the tile adds them in split order: no atomics on data, same result every
-// time.  Epilogues: store, add into the float32 residual, SwiGLU over [8 gate | 8 up] rows.
+// (few row tiles: the small projections), a store or SwiGLU output goes through scratch: each
+// block writes its partial tile and the block that arrives last for the tile adds them in split
+// order (same result every time); an add into the float32 residual is done by every block with
+// float atomics (cheaper; the order of the shares, and so the last bits, vary between runs).
+// Epilogues: store, add into the float32 residual, SwiGLU over [8 gate | 8 up] rows.
 //
 // The general GEMM (gemm_tc.cu) has the tokens on the M side: with 64 tokens it re-reads the
 // activations for every 64 columns of W and fills few SMs; here the weights stream once and the
@@ -20,11 +22,11 @@
 typedef __nv_bfloat16 bf16;
 
 constexpr int GV_BM = 128;                // rows of W per block
-constexpr int GV_STAGES = 8;
+constexpr int GV_STAGES = 4;              // 96 KB a block: two blocks share an SM, no second wave for 149..296 blocks
 constexpr int GV_THREADS = 192;           // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
 
 template <int BNB>                        // batch rows per tile: 16, 32 or 64
-__global__ void __launch_bounds__(GV_THREADS, 1)
+__global__ void __launch_bounds__(GV_THREADS, 2)
 gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                void* __restrict__ out, int ldo, int out_is_f32, int n_rows, int N, int K, int mode, int splits,
                float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ error_word) {
@@ -135,7 +137,11 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < BNB; ++j) v[j] = 0.f;
         }
-        if (ok && splits > 1) {
+        // Adding into the float32 residual with K split over blocks: each block adds its share
+        // straight in (red.global.add.f32).  The order in which shares meet varies from run to run,
+        // so the last bits of the residual may; store and SwiGLU outputs use the ordered fix-up below.
+        const bool atomic_add = splits > 1 && mode == TC_ACCUMULATE;
+        if (ok && splits > 1 && !atomic_add) {
             // partial tile to scratch; the block that arrives last adds all of them in split order
             float* mine = partials + (((size_t)tile * splits + split) * GV_BM + r) * BNB;
 #pragma unroll
@@ -180,7 +186,8 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 for (int j = 0; j < BNB; ++j) {
                     if (j >= n_rows) break;
                     const size_t o = (size_t)j * ldo + n;
-                    if (mode == TC_ACCUMULATE) ((float*)out)[o] += v[j];
+                    if (atomic_add) { if (my_blocks > 0) atomicAdd((float*)out + o, v[j]); }
+                    else if (mode == TC_ACCUMULATE) ((float*)out)[o] += v[j];
                     else if (out_is_f32) ((float*)out)[o] = v[j];
                     else ((bf16*)out)[o] = __float2bfloat16_rn(v[j]);
                 }
@@ -227,7 +234,7 @@ SSB_API int ssb_gemv_tc(const void* x, int ldx, const void* W, int ldw, void* ou
     if (n_rows <= 0 || N <= 0) return 0;
     if (n_rows > 64 || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || !error_word || splits < 1) return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)x | (uintptr_t)W | (uintptr_t)partials) & 15) return SSB_ERR_BAD_SIZE;
-    if (splits > 1 && (!partials || !counters)) return SSB_ERR_BAD_SIZE;
+    if (splits > 1 && mode != TC_ACCUMULATE && (!partials || !counters)) return SSB_ERR_BAD_SIZE;
     if (splits > (K + TC_BK - 1) / TC_BK) return SSB_ERR_BAD_SIZE;
     if (mode == TC_ACCUMULATE && out_dtype != SSB_F32) return SSB_ERR_BAD_DTYPE;
     if (mode == TC_SWIGLU && (out_dtype != SSB_BF16 || N % 16)) return SSB_ERR_BAD_SIZE;

@@ -82,8 +82,12 @@ def linear(args):
         nf, nc = ops.gemv_tc_scratch(B, N, splits)
         partials = torch.empty(max(nf, 4), device=DEV)
         counters = torch.zeros(max(nc, 1), dtype=torch.int32, device=DEV)
-        fn = lambda i: ops.gemv_tc(x, ws[i % copies], out, splits=splits, partials=partials, counters=counters,
-                                   pdl=args.pdl)
+        if args.accumulate:
+            acc = torch.zeros(B, N, device=DEV)
+            fn = lambda i: ops.gemv_tc(x, ws[i % copies], acc, mode=ops.TC_ACCUMULATE, splits=splits, pdl=args.pdl)
+        else:
+            fn = lambda i: ops.gemv_tc(x, ws[i % copies], out, splits=splits, partials=partials, counters=counters,
+                                       pdl=args.pdl)
     else:
         tile = int(args.kernel[2:])
         fn = lambda i: ops.gemm_tc(x, ws[i % copies], out, tile_n=tile)
@@ -141,6 +145,7 @@ def main(argv=None):
         p.add_argument("--kernel", default="skinny")
         p.add_argument("--tile", type=int, default=256)
         p.add_argument("--kind", type=int, default=0, help="attention_decode: 0 auto, 1 general, 2 tensor-core")
+        p.add_argument("--accumulate", action="store_true", help="linear gv*: add into a float32 output")
         p.add_argument("--pdl", action="store_true", help="launch as programmatic dependents")
         p.add_argument("--seqs", type=int, default=1)
         p.add_argument("--tokens", type=int, default=2048)

@@ -420,10 +420,10 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
 
 # ---- decode projections on tcgen05, weights on the M side ------------------------------------------
 def gemv_tc_splits(n: int, k: int) -> int:
-    """Blocks that share the K range of one 128-row tile of W: enough for about 1.5 blocks per SM,
-    at least 8 k-blocks (512 columns) each."""
+    """Blocks that share the K range of one 128-row tile of W: up to two blocks per SM in all
+    (every SM must pull for the memory system to be busy), at least 8 k-blocks (512 columns) each."""
     tiles = (n + 127) // 128
-    return max(1, min(222 // tiles, (k // 64) // 8, 8))
+    return max(1, min(296 // tiles, (k // 64) // 8, 8))
 
 
 def gemv_tc_scratch(rows: int, n: int, splits: int):
@@ -437,15 +437,17 @@ def gemv_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_
             partials: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None,
             pdl: bool = False) -> None:
     """out = x @ w^T for up to 64 rows with the weights as the M side of tcgen05.mma (they stream
-    once, 16 KB a stage).  ``splits`` > 1 shares the K range of a row tile among blocks; needs
-    ``partials``/``counters`` sized by :func:`gemv_tc_scratch` (counters zeroed once)."""
+    once, 16 KB a stage).  ``splits`` > 1 shares the K range of a row tile among blocks: store
+    and SwiGLU outputs then need ``partials``/``counters`` sized by :func:`gemv_tc_scratch`
+    (counters zeroed once) and are summed in a fixed order; mode accumulate adds with float
+    atomics instead (no scratch; the last bits may differ between runs)."""
     _need(x, "x", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(out, "out", None, 2)
     B, K = x.shape
     N = w.shape[0]
     n_out = N // 2 if mode == TC_SWIGLU else N
     if w.shape[1] != K or tuple(out.shape) != (B, n_out) or B > 64:
         raise KernelError(f"gemv_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
-    if splits > 1:
+    if splits > 1 and mode != TC_ACCUMULATE:
         nf, nc = gemv_tc_scratch(B, N, splits)
         _need(partials, "partials", torch.float32); _need(counters, "counters", torch.int32)
         if partials.numel() < nf or counters.numel() < nc:

@@ -553,7 +553,7 @@ def test_gemv_tc(rows, N, K, splits):
     ops().gemv_tc(x, w, ob, **kw)
     torch.testing.assert_close(ob.double(), ref, atol=2e-2, rtol=2e-2)
     acc = torch.full((rows, N), 2.0, device=DEV)
-    ops().gemv_tc(x, w, acc, mode=1, **kw)
+    ops().gemv_tc(x, w, acc, mode=1, splits=splits)                      # float atomics when K is split
     torch.testing.assert_close(acc.double(), ref + 2, atol=2e-5 * math.sqrt(K), rtol=1e-4)
     again = torch.full((rows, N), 9.0, device=DEV)
     ops().gemv_tc(x, w, again, **kw)
