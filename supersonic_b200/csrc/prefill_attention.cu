@@ -19,7 +19,7 @@ constexpr int PA_BN = 64;            // keys per turn = one cache page
 constexpr int PA_THREADS = 128;
 
 template <int HD>
-__global__ void __launch_bounds__(PA_THREADS)
+__global__ void __launch_bounds__(PA_THREADS, 3)
 prefill_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ k_cache,
                          const bf16* __restrict__ v_cache, const int* __restrict__ cu_new,
                          const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
@@ -28,10 +28,13 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
     constexpr int CHUNKS = HD / 8;                       // 16-byte chunks per row
     constexpr int TILE_BYTES = PA_BN * HD * 2;
     extern __shared__ __align__(128) unsigned char smem[];
-    unsigned char* q_s = smem;                           // [64][HD]
-    unsigned char* k_s = smem + TILE_BYTES;              // 2 stages
-    unsigned char* v_s = smem + 3 * TILE_BYTES;          // 2 stages
-    const int tile = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+    // four tiles: K stage 0, K stage 1, V stage 0, V stage 1; the Q tile borrows V stage 1 until
+    // its fragments are in registers (three blocks fit an SM this way)
+    unsigned char* k_s = smem;                           // 2 stages
+    unsigned char* v_s = smem + 2 * TILE_BYTES;          // 2 stages
+    unsigned char* q_s = smem + 3 * TILE_BYTES;          // [64][HD], dead after the fragment load
+    // long tiles (late queries see many keys) first, so that the tail of the grid is short work
+    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x, head = blockIdx.y, b = blockIdx.z;
     const int row0 = cu_new[b], n_new = cu_new[b + 1] - row0;
     if (tile * PA_BM >= n_new) return;
     const int slot = seq_slot[b];
@@ -79,6 +82,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
         for (int ks = 0; ks < HD / 16; ++ks)
             ldmatrix_x4(qb + tile_offset<HD>(r, ks * 2 + (lane >> 4)), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
     }
+    __syncthreads();                                     // the Q tile's memory is V stage 1 from here on
     float o[HD / 8][4];
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
@@ -210,7 +214,7 @@ SSB_API int ssb_attention_prefill(const void* q, int ldq, const void* k_cache, c
     dim3 grid((max_new + PA_BM - 1) / PA_BM, n_q, n_seqs);
     const float scale_log2 = scale * 1.4426950408889634f;
 #define SSB_PA(HD) do { \
-        constexpr int smem = 5 * PA_BN * HD * 2; \
+        constexpr int smem = 4 * PA_BN * HD * 2; \
         static bool configured = false; \
         if (!configured) { \
             cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
