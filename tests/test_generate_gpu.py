@@ -139,3 +139,26 @@ def test_no_cpu_path():
     c = config_from_dict(tiny_configs.A)
     with pytest.raises(RuntimeError, match="no CPU path"):
         Model.from_config(c, random_store(c, 0), device="cpu")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_widths_the_fast_kernels_refuse_still_give_the_right_logits(tmp_path, dtype):
+    """A width and a feed-forward width that are no multiple of 8, an odd vocabulary, three kv
+    heads: the vector kernels do not take these, the plain ones must, with the same results."""
+    from supersonic_b200.config import config_from_dict
+    from supersonic_b200.engine import Model, StepEntry
+    from supersonic_b200.weights import write_model_folder
+    cfg = dict(architectures=["LlamaForCausalLM"], vocab_size=301, hidden_size=68, intermediate_size=100,
+               num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=3, head_dim=16,
+               max_position_embeddings=256, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=True)
+    d = write_model_folder(config_from_dict(cfg), 9, str(tmp_path / "m"), std=0.1)
+    pc, pw = pl.read_model_folder(d)
+    toks = np.random.default_rng(9).integers(0, 301, 100).tolist()
+    ref = pl.forward(pc, pw, toks)
+    m = Model.from_dir(d, dtype=dtype, max_tokens=128)
+    s = m.open_sequence()
+    got = [m.step([StepEntry(s, toks[:90], range(90))])]
+    got += [m.step([StepEntry(s, [toks[p]], [0])]) for p in range(90, 100)]
+    got = torch.cat(got).double().cpu().numpy()
+    tol = 2e-5 if dtype == "float32" else 2e-2 * np.abs(ref).max()
+    assert np.abs(got - ref).max() < tol
