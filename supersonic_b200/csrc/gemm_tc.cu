@@ -21,32 +21,41 @@ constexpr int TC_BM = 128;
 constexpr int TC_THREADS = 192;           // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
 
 // ---- kernel ---------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Persistent: a block takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulators of
+// consecutive tiles alternate between two regions of tensor memory, so that the epilogue of one
+// tile (tcgen05.ld, conversion, stores) runs while the MMAs of the next are issued.
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                void* __restrict__ C, int ldc, int out_is_f32, int M, int N, int K, int mode, int m_tiles,
-               int* __restrict__ error_word) {
+               int n_tiles_total, int* __restrict__ error_word) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
+    constexpr int N_ACC = BN <= 128 ? 2 : 2;                       // accumulator regions (2 x BN <= 512 columns)
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);     // full[STAGES], empty[STAGES], acc_full
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+    // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 2 * N_ACC);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);     // [0]: a role gave up; [1]: stays zero
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = (blockIdx.x % m_tiles) * TC_BM, n0 = (blockIdx.x / m_tiles) * BN;
     const int k_blocks = (K + TC_BK - 1) / TC_BK;
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), acc_full = smem_u32(bars + 2 * STAGES);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+    const uint32_t acc_full0 = smem_u32(bars + 2 * STAGES), acc_empty0 = smem_u32(bars + 2 * STAGES + N_ACC);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        mbar_init(acc_full, 1);
+        for (int i = 0; i < N_ACC; ++i) { mbar_init(acc_full0 + 8 * i, 1); mbar_init(acc_empty0 + 8 * i, 4); }
         abort_flag[0] = 0;
         abort_flag[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 1) {      // the whole warp allocates BN columns of tensor memory
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+    if (warp == 1) {      // the whole warp allocates the accumulator columns of tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(N_ACC * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -56,23 +65,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t phase = (kb / STAGES) & 1;
-                if (!mbar_wait(empty0 + 8 * s, phase ^ 1, abort_flag)) {
-                    *abort_flag = 1; atomicCAS(error_word, 0, TC_ERR_PRODUCER); break;
+            int c = 0, issued_from = 0;                        // k-blocks issued so far (ring position)
+            for (int tile = blockIdx.x; tile < n_tiles_total && !*abort_flag; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++c) {
+                    const int s = c % STAGES;
+                    const uint32_t phase = (c / STAGES) & 1;
+                    if (!mbar_wait(empty0 + 8 * s, phase ^ 1, abort_flag)) {
+                        *abort_flag = 1; atomicCAS(error_word, 0, TC_ERR_PRODUCER); break;
+                    }
+                    const uint32_t a_dst = smem_u32(smem + s * STAGE_BYTES), w_dst = a_dst + A_BYTES;
+                    mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * TC_BK, m0);
+                    tma_load_2d(w_dst, &map_w, full0 + 8 * s, kb * TC_BK, n0);
                 }
-                const uint32_t a_dst = smem_u32(smem + s * STAGE_BYTES), w_dst = a_dst + A_BYTES;
-                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * TC_BK, m0);
-                tma_load_2d(w_dst, &map_w, full0 + 8 * s, kb * TC_BK, n0);
-                issued = kb + 1;
             }
             if (*abort_flag) {
                 // let copies that were issued but never consumed land before the block ends
-                for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
-                    mbar_wait(full0 + 8 * (kb % STAGES), (kb / STAGES) & 1, abort_flag + 1);
+                issued_from = max(0, c - STAGES);
+                for (int i = issued_from; i < c; ++i)
+                    mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, abort_flag + 1);
             }
         }
     } else if (warp == 1) {
@@ -80,109 +92,128 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // instruction descriptor: D float32, A and B bfloat16, both K-major, N = BN, M = 128
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
             bool ok = true;
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t phase = (kb / STAGES) & 1;
-                if (!mbar_wait(full0 + 8 * s, phase, abort_flag)) {
+            int c = 0, i = 0;
+            for (int tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x, ++i) {
+                const int buf = i % N_ACC;
+                const uint32_t use = (uint32_t)(i / N_ACC) & 1;
+                if (!mbar_wait(acc_empty0 + 8 * buf, use ^ 1, abort_flag)) {    // the epilogue has drained this region
                     *abort_flag = 1; atomicCAS(error_word, 0, TC_ERR_MMA); ok = false; break;
                 }
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-                const uint64_t da = smem_desc(a_addr), dw = smem_desc(a_addr + A_BYTES);
+                const uint32_t acc = tmem + buf * BN;
+                for (int kb = 0; kb < k_blocks && ok; ++kb, ++c) {
+                    const int s = c % STAGES;
+                    const uint32_t phase = (c / STAGES) & 1;
+                    if (!mbar_wait(full0 + 8 * s, phase, abort_flag)) {
+                        *abort_flag = 1; atomicCAS(error_word, 0, TC_ERR_MMA); ok = false; break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+                    const uint64_t da = smem_desc(a_addr), dw = smem_desc(a_addr + A_BYTES);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)        // 16 k = 32 bytes further along the swizzled row
-                    tc_mma(tmem, da + 2 * k, dw + 2 * k, idesc, (kb | k) ? 1u : 0u);
-                tc_commit(empty0 + 8 * s);                  // the stage is free once these MMAs have read it
+                    for (int k = 0; k < TC_BK / 16; ++k)        // 16 k = 32 bytes further along the swizzled row
+                        tc_mma(acc, da + 2 * k, dw + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    tc_commit(empty0 + 8 * s);                  // the stage is free once these MMAs have read it
+                }
+                if (ok) tc_commit(acc_full0 + 8 * buf);         // this tile's accumulators are complete
             }
-            if (ok) tc_commit(acc_full);                    // accumulators complete
         }
     } else {
         // epilogue: warp w may read tensor-memory lanes 32 * (w % 4) .. + 31 = rows of the tile
         const int quarter = warp & 3;
-        const int row = m0 + quarter * 32 + lane;
-        bool ok = mbar_wait(acc_full, 0, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) {
-            if (lane == 0) { *abort_flag = 1; atomicCAS(error_word, 0, TC_ERR_EPILOGUE); }
-        } else {
+        int i = 0;
+        for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++i) {
+            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+            const int row = m0 + quarter * 32 + lane;
+            const int buf = i % N_ACC;
+            const uint32_t use = (uint32_t)(i / N_ACC) & 1;
+            bool ok = mbar_wait(acc_full0 + 8 * buf, use, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0) { *abort_flag = 1; atomicCAS(error_word, 0, TC_ERR_EPILOGUE); }
+                break;
+            }
             tc_fence_after();
+            const uint32_t acc = tmem + buf * BN;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + c * 32, r);
-                const int n = n0 + c * 32;
-                if (row >= M || n >= N) continue;
-                if (mode == TC_SWIGLU) {
-                    bf16* dst = (bf16*)C + (size_t)row * ldc + n / 2;
-                    uint32_t packed[8];
-#pragma unroll
-                    for (int g = 0; g < 2; ++g)
-#pragma unroll
-                        for (int j = 0; j < 8; j += 2) {
-                            const float g0 = __uint_as_float(r[g * 16 + j]), u0 = __uint_as_float(r[g * 16 + 8 + j]);
-                            const float g1 = __uint_as_float(r[g * 16 + j + 1]), u1 = __uint_as_float(r[g * 16 + 9 + j]);
-                            __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u0,
-                                                                      g1 / (1.0f + __expf(-g1)) * u1);
-                            packed[g * 4 + j / 2] = *reinterpret_cast<uint32_t*>(&v);
-                        }
-                    if (n + 32 <= N) {
-                        reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    } else {
-                        for (int j = 0; j < 16; ++j)            // N is a multiple of 16: whole groups only
-                            if (n + (j / 8) * 16 + 16 <= N) dst[j] = reinterpret_cast<bf16*>(packed)[j];
-                    }
-                } else if (out_is_f32) {
-                    float* dst = (float*)C + (size_t)row * ldc + n;
-                    if (n + 32 <= N) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                            if (mode == TC_ACCUMULATE) {
-                                const float4 o = *reinterpret_cast<const float4*>(dst + j);
-                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tc_ld32(acc + ((uint32_t)(quarter * 32) << 16) + c * 32, r);
+                    const int n = n0 + c * 32;
+                    if (row >= M || n >= N) continue;
+                    if (mode == TC_SWIGLU) {
+                        bf16* dst = (bf16*)C + (size_t)row * ldc + n / 2;
+                        uint32_t packed[8];
+    #pragma unroll
+                        for (int g = 0; g < 2; ++g)
+    #pragma unroll
+                            for (int j = 0; j < 8; j += 2) {
+                                const float g0 = __uint_as_float(r[g * 16 + j]), u0 = __uint_as_float(r[g * 16 + 8 + j]);
+                                const float g1 = __uint_as_float(r[g * 16 + j + 1]), u1 = __uint_as_float(r[g * 16 + 9 + j]);
+                                __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u0,
+                                                                          g1 / (1.0f + __expf(-g1)) * u1);
+                                packed[g * 4 + j / 2] = *reinterpret_cast<uint32_t*>(&v);
                             }
-                            *reinterpret_cast<float4*>(dst + j) = v;
+                        if (n + 32 <= N) {
+                            reinterpret_cast<uint4*>(dst)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            reinterpret_cast<uint4*>(dst)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        } else {
+                            for (int j = 0; j < 16; ++j)            // N is a multiple of 16: whole groups only
+                                if (n + (j / 8) * 16 + 16 <= N) dst[j] = reinterpret_cast<bf16*>(packed)[j];
+                        }
+                    } else if (out_is_f32) {
+                        float* dst = (float*)C + (size_t)row * ldc + n;
+                        if (n + 32 <= N) {
+    #pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                       __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                                if (mode == TC_ACCUMULATE) {
+                                    const float4 o = *reinterpret_cast<const float4*>(dst + j);
+                                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                                }
+                                *reinterpret_cast<float4*>(dst + j) = v;
+                            }
+                        } else {
+                            for (int j = 0; j < 32 && n + j < N; ++j)
+                                dst[j] = __uint_as_float(r[j]) + (mode == TC_ACCUMULATE ? dst[j] : 0.f);
                         }
                     } else {
-                        for (int j = 0; j < 32 && n + j < N; ++j)
-                            dst[j] = __uint_as_float(r[j]) + (mode == TC_ACCUMULATE ? dst[j] : 0.f);
-                    }
-                } else {
-                    bf16* dst = (bf16*)C + (size_t)row * ldc + n;
-                    if (n + 32 <= N) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            uint4 v;
-                            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-                            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-                            v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
-                            v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
-                            *reinterpret_cast<uint4*>(dst + j) = v;
+                        bf16* dst = (bf16*)C + (size_t)row * ldc + n;
+                        if (n + 32 <= N) {
+    #pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 v;
+                                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                                v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+                                v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+                                *reinterpret_cast<uint4*>(dst + j) = v;
+                            }
+                        } else {
+                            for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
                         }
-                    } else {
-                        for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
                     }
                 }
-            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);   // this warp has read its quarter of the region
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(N_ACC * BN) : "memory");
     }
 }
 
-// ---- host side --------------------------------------------------------------------------------
 template <int BN, int STAGES>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int out_is_f32, int M, int N,
                      int K, int mode, int* error_word, cudaStream_t stream) {
-    constexpr size_t smem = STAGES * (TC_BM + BN) * TC_BK * 2 + (2 * STAGES + 1) * 8 + 16 + 1024;
+    constexpr size_t smem = STAGES * (TC_BM + BN) * TC_BK * 2 + (2 * STAGES + 4) * 8 + 16 + 1024;
     auto kern = gemm_tc_kernel<BN, STAGES>;
     static bool configured = false;
     if (!configured) {
@@ -191,7 +222,16 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int 
         configured = true;
     }
     const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
-    kern<<<m_tiles * n_tiles, TC_THREADS, smem, stream>>>(ma, mw, C, ldc, out_is_f32, M, N, K, mode, m_tiles, error_word);
+    static int n_sms = 0;
+    if (!n_sms) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sms <= 0)
+            n_sms = 148;
+    }
+    const int total = m_tiles * n_tiles;
+    kern<<<total < n_sms ? total : n_sms, TC_THREADS, smem, stream>>>(ma, mw, C, ldc, out_is_f32, M, N, K, mode,
+                                                                      m_tiles, total, error_word);
     return ssb_launch_status();
 }
 
