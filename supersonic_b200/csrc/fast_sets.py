@@ -34,7 +34,20 @@ class FastKernels(PlainKernels):
         self._retired = []      # outgrown buffers stay alive: captured graphs still point at them
 
     def rmsnorm(self, x, weight, eps, out, rows=None):
-        ops.rmsnorm(x, weight, eps, out, rows, pdl=self.pdl and out.shape[0] <= 64)
+        pdl = self.pdl and out.shape[0] <= 64
+        if ops.rmsnorm_vec_ok(x, weight, out):
+            ops.rmsnorm_vec(x, weight, eps, out, rows, pdl=pdl)
+        else:
+            ops.rmsnorm(x, weight, eps, out, rows, pdl=pdl)
+
+    def rope_append(self, qkv, cos, sin, batch, page_table, k_cache, v_cache, n_q, n_kv, head_dim,
+                    rotary_dim, page_shift, write_cache=True):
+        if ops.rope_append_vec_ok(qkv, cos, head_dim, rotary_dim, write_cache):
+            ops.rope_append_vec(qkv, cos, sin, batch.pos, batch.slot_of_token, page_table, k_cache, v_cache,
+                                n_q, n_kv, head_dim, page_shift)
+        else:
+            super().rope_append(qkv, cos, sin, batch, page_table, k_cache, v_cache, n_q, n_kv, head_dim,
+                                rotary_dim, page_shift, write_cache)
 
     # ---- matrix products -------------------------------------------------------------
     def _skinny(self, x, weight, out, mode, then_norm=None):

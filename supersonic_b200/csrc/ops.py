@@ -459,3 +459,51 @@ def gemv_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_
         c_int(dtype_code(out.dtype)), c_int(B), c_int(N), c_int(K), c_int(mode), c_int(splits),
         _ptr(partials), _ptr(counters), _ptr(tc_error_word(x.device)), c_int(1 if pdl else 0), _stream()),
         "gemv_tc")
+
+
+# ---- vector element-wise kernels ------------------------------------------------------------------
+def rmsnorm_vec_ok(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bool:
+    return (out.dtype == torch.bfloat16 and x.dtype == torch.float32 and x.shape[1] % 4 == 0
+            and x.shape[1] <= 8192 and x.is_contiguous() and out.is_contiguous()
+            and x.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and weight.dtype in _CODES)
+
+
+def rmsnorm_vec(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: Optional[torch.Tensor] = None, pdl: bool = False) -> None:
+    """As :func:`rmsnorm` with bfloat16 output, 16-byte loads and the row kept in registers."""
+    _need(x, "x", torch.float32, 2); _need(weight, "weight", None, 1); _need(out, "out", torch.bfloat16, 2)
+    n = out.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        if rows.shape[0] != n:
+            raise KernelError("rmsnorm_vec: one output row per gathered row")
+    elif x.shape[0] != n:
+        raise KernelError("rmsnorm_vec: x and out differ in rows")
+    if x.shape[1] != out.shape[1] or weight.shape[0] != x.shape[1]:
+        raise KernelError("rmsnorm_vec: widths differ")
+    _check(_fn("elementwise_ops", "ssb_rmsnorm_vec")(
+        _ptr(x), _ptr(rows), _ptr(weight), c_int(dtype_code(weight.dtype)), c_float(eps), _ptr(out), c_int(n),
+        c_int(x.shape[1]), c_int(1 if pdl else 0), _stream()), "rmsnorm_vec")
+
+
+def rope_append_vec_ok(qkv: torch.Tensor, cos, head_dim: int, rotary_dim: int, write_cache: bool) -> bool:
+    return (qkv.dtype == torch.bfloat16 and cos is not None and write_cache and rotary_dim == head_dim
+            and head_dim % 8 == 0 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0)
+
+
+def rope_append_vec(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: torch.Tensor,
+                    slot: torch.Tensor, page_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    n_q: int, n_kv: int, head_dim: int, page_shift: int) -> None:
+    """As :func:`rope_append` for bfloat16, full-width rotation, with vector loads and stores."""
+    _need(qkv, "qkv", torch.bfloat16, 2); _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2); _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+    _need(k_cache, "k_cache", torch.bfloat16); _need(v_cache, "v_cache", torch.bfloat16)
+    T = qkv.shape[0]
+    if qkv.shape[1] < (n_q + 2 * n_kv) * head_dim or pos.shape[0] != T or slot.shape[0] != T:
+        raise KernelError("rope_append_vec: qkv rows too narrow, or not one position and slot per token")
+    if cos.shape != sin.shape or cos.shape[1] * 2 != head_dim or not (cos.is_contiguous() and sin.is_contiguous()):
+        raise KernelError("rope_append_vec: cos/sin must be [positions, head_dim/2], contiguous")
+    _check(_fn("elementwise_ops", "ssb_rope_append_vec")(
+        _ptr(qkv), c_int(qkv.stride(0)), _ptr(cos), _ptr(sin), c_int(cos.shape[0]), _ptr(pos), _ptr(slot),
+        _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(n_q),
+        c_int(n_kv), c_int(head_dim), c_int(page_shift), _stream()), "rope_append_vec")

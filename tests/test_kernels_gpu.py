@@ -577,3 +577,51 @@ def test_gemv_tc_swiglu(rows, splits):
     ops().check_device_errors()
     gg, uu = x.double() @ gate.double().T, x.double() @ up.double().T
     torch.testing.assert_close(out.double(), gg / (1 + torch.exp(-gg)) * uu, atol=2e-2, rtol=2e-2)
+
+
+# ---- vector element-wise kernels ---------------------------------------------------------------------
+@pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("hidden", [72, 1000, 4096, 8192])
+def test_rmsnorm_vec_equals_plain(wdtype, hidden):
+    g = torch.Generator(device=DEV).manual_seed(80)
+    x = torch.randn(70, hidden, device=DEV, generator=g) * 3
+    w = (1 + 0.1 * torch.randn(hidden, device=DEV, generator=g)).to(wdtype)
+    rows = torch.tensor([69, 0, 3, 3], dtype=torch.int32, device=DEV)
+    for r in (None, rows):
+        n = 70 if r is None else 4
+        want = torch.empty(n, hidden, dtype=torch.bfloat16, device=DEV)
+        got = torch.full((n, hidden), 9.0, dtype=torch.bfloat16, device=DEV)
+        ops().rmsnorm(x, w, 1e-5, want, r)
+        ops().rmsnorm_vec(x, w, 1e-5, got, r)
+        # same formula; the sum of squares is added in another order
+        torch.testing.assert_close(got.float(), want.float(), atol=0, rtol=2 ** -7)
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd", [(4, 2, 16), (3, 1, 48), (32, 8, 128), (5, 5, 64)])
+def test_rope_append_vec_equals_plain(n_q, n_kv, hd):
+    g = torch.Generator(device=DEV).manual_seed(81)
+    T = 70
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * hd + 8, device=DEV, generator=g).bfloat16()     # a wider row stride
+    pos = torch.randint(0, 5 * 64, (T,), generator=torch.Generator().manual_seed(82)).to(torch.int32).to(DEV)
+    slot = torch.randint(-1, 3, (T,), generator=torch.Generator().manual_seed(83)).to(torch.int32).to(DEV)
+    key = slot.long() * 1000 + pos.long()                                                    # a cache row is written once
+    keep = torch.ones(T, dtype=torch.bool, device=DEV)
+    seen = set()
+    for t in range(T):
+        k_ = int(key[t])
+        if int(slot[t]) >= 0 and k_ in seen:
+            keep[t] = False
+        seen.add(k_)
+    slot = torch.where(keep, slot, torch.full_like(slot, -1))
+    table = torch.randperm(15, generator=torch.Generator().manual_seed(84)).to(torch.int32).view(3, 5).to(DEV)
+    ang = torch.arange(400, device=DEV, dtype=torch.float64)[:, None] * \
+        (1.0 / 10000 ** (torch.arange(hd // 2, device=DEV, dtype=torch.float64) * 2 / hd))[None, :]
+    cos, sin = ang.cos().float().contiguous(), ang.sin().float().contiguous()
+    k0, v0 = _paged(15, n_kv, hd, torch.bfloat16, 85)
+    qa, ka, va = qkv.clone(), k0.clone(), v0.clone()
+    ops().rope_append(qa, cos, sin, pos, slot, table, ka, va, n_q, n_kv, hd, hd, 6, True)
+    qb, kb, vb = qkv.clone(), k0.clone(), v0.clone()
+    ops().rope_append_vec(qb, cos, sin, pos, slot, table, kb, vb, n_q, n_kv, hd, 6)
+    torch.testing.assert_close(qb.float(), qa.float(), atol=0, rtol=2 ** -7)
+    torch.testing.assert_close(kb.float(), ka.float(), atol=0, rtol=2 ** -7)
+    assert torch.equal(vb, va)
