@@ -35,6 +35,7 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "sampling": {"sources": ["sampling.cu"], "flags": [], "link": []},
     "decode_ops": {"sources": ["decode_ops.cu"], "flags": [], "link": []},
     "prefill_attention": {"sources": ["prefill_attention.cu"], "flags": [], "link": []},
+    "prefill_attention_tc": {"sources": ["prefill_attention_tc.cu"], "flags": [], "link": []},
     "elementwise_ops": {"sources": ["elementwise_ops.cu"], "flags": [], "link": []},
     "gemv_tc": {"sources": ["gemv_tc.cu"], "flags": [], "link": []},
     "gemm_tc": {"sources": ["gemm_tc.cu"], "flags": [], "link": []},

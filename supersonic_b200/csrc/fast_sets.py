@@ -18,6 +18,7 @@ PREFETCH_BYTES = 64 << 20     # weights pulled into L2 during decode attention (
 PREFETCH_MAX_ROWS = 0         # off: measured no gain (the projections are issue-bound, not DRAM-bound)
 SKINNY_MAX_ROWS = 8           # above this the tcgen05 kernels stream the weights faster (measured)
 TARGET_BLOCKS = 1184           # eight small blocks per SM
+TC_ATTENTION_MIN_NEW = 96     # prompts at least this long take the tcgen05 attention (tiles of 128 rows)
 
 
 class FastKernels(PlainKernels):
@@ -192,6 +193,11 @@ class FastKernels(PlainKernels):
                 and q.stride(0) % 8 == 0:
             self._decode_attention(q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim,
                                    page_shift, window, scale)
+            return
+        if not batch.is_decode and batch.max_new >= TC_ATTENTION_MIN_NEW and k_cache.is_contiguous() \
+                and v_cache.is_contiguous() and ops.attention_prefill_tc_ok(q, out, head_dim, page_shift):
+            ops.attention_prefill_tc(q, k_cache, v_cache, batch.cu_new, batch.seq_start, batch.seq_slot,
+                                     page_table, out, batch.max_new, n_q, n_kv, head_dim, page_shift, window, scale)
             return
         if not batch.is_decode and ops.attention_prefill_ok(q, head_dim) and out.stride(0) % 2 == 0:
             ops.attention_prefill(q, k_cache, v_cache, batch.cu_new, batch.seq_start, batch.seq_slot,

@@ -358,7 +358,7 @@ def check_device_errors(device=None) -> None:
         code = int(word.item())
         if code:
             word.zero_()
-            raise KernelError(f"gemm_tc: a bounded wait ran out in {_TC_ERRORS.get(code, code)}; "
+            raise KernelError(f"tcgen05 kernel: a bounded wait ran out in {_TC_ERRORS.get(code, code)}; "
                               "the result of that launch is invalid")
 
 
@@ -416,6 +416,41 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         _ptr(seq_slot), _ptr(page_table), c_int(page_table.shape[1]), _ptr(out), c_int(out.stride(0)),
         c_int(n_seqs), c_int(max_new), c_int(n_q), c_int(n_kv), c_int(head_dim), c_int(page_shift),
         c_int(int(window) if window else 0), c_float(scale), _stream()), "attention_prefill")
+
+
+def attention_prefill_tc_ok(q: torch.Tensor, out: torch.Tensor, head_dim: int, page_shift: int) -> bool:
+    return (q.dtype == torch.bfloat16 and head_dim == 128 and page_shift == 6 and q.stride(0) % 8 == 0
+            and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
+
+
+def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_new: torch.Tensor,
+                         seq_start: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor,
+                         out: torch.Tensor, max_new: int, n_q: int, n_kv: int, head_dim: int, page_shift: int,
+                         window: Optional[int], scale: float) -> None:
+    """``attention_prefill`` on tcgen05: scores and probabilities in tensor memory, pages by TMA.
+    head_dim 128 and 64-token pages only.  A wait that runs out sets the device's error word
+    (``check_device_errors``)."""
+    _need(q, "q", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
+    _need(k_cache, "k_cache", torch.bfloat16); _need(v_cache, "v_cache", torch.bfloat16)
+    for name, t in (("cu_new", cu_new), ("seq_start", seq_start), ("seq_slot", seq_slot)):
+        _need(t, name, torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    n_seqs = seq_slot.shape[0]
+    if cu_new.shape[0] != n_seqs + 1 or seq_start.shape[0] != n_seqs:
+        raise KernelError("attention_prefill_tc: cu_new has one more entry than there are sequences")
+    if out.shape[0] != q.shape[0] or out.shape[1] < n_q * head_dim or q.shape[1] < n_q * head_dim:
+        raise KernelError("attention_prefill_tc: q/out shapes")
+    if not k_cache.is_contiguous() or not v_cache.is_contiguous() or k_cache.shape != v_cache.shape \
+            or tuple(k_cache.shape[1:]) != (n_kv, 1 << page_shift, head_dim):
+        raise KernelError(f"attention_prefill_tc: cache shape {tuple(k_cache.shape)}")
+    global _tc_unchecked
+    _tc_unchecked += 1
+    _check(_fn("prefill_attention_tc", "ssb_attention_prefill_tc")(
+        _ptr(q), c_int(q.stride(0)), c_int(q.shape[0]), _ptr(k_cache), _ptr(v_cache), c_int(k_cache.shape[0]),
+        _ptr(cu_new), _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), c_int(page_table.shape[1]),
+        _ptr(out), c_int(out.stride(0)), c_int(n_seqs), c_int(max_new), c_int(n_q), c_int(n_kv),
+        c_int(head_dim), c_int(page_shift), c_int(int(window) if window else 0), c_float(scale),
+        _ptr(tc_error_word(q.device)), _stream()), "attention_prefill_tc")
 
 
 # ---- decode projections on tcgen05, weights on the M side ------------------------------------------

@@ -22,7 +22,7 @@ def margin_ok(pc, pw, tokens, tol):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_greedy_generation_matches_plain(model_folders, name, dtype):
     import supersonic_b200
     d, pc, pw = model_folders[name]

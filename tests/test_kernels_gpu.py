@@ -411,11 +411,20 @@ def test_gemm_tc_swiglu(M, inter, K):
 
 
 # ---- prefill attention ---------------------------------------------------------------------------
+def _prefill_kernel(impl):
+    return ops().attention_prefill_tc if impl == "tcgen05" else ops().attention_prefill
+
+
+@pytest.mark.parametrize("impl", ["mma", "tcgen05"])
 @pytest.mark.parametrize("n_q,n_kv,hd,window", [(8, 2, 128, None), (4, 4, 64, None), (6, 2, 128, 100),
-                                                (3, 1, 64, 64), (2, 1, 128, 1)])
-def test_attention_prefill(n_q, n_kv, hd, window):
+                                                (3, 1, 64, 64), (2, 1, 128, 1), (3, 1, 128, None),
+                                                (5, 5, 128, 70)])
+def test_attention_prefill(n_q, n_kv, hd, window, impl):
     """A ragged batch: sequences that start at 0 and sequences that continue a cached prefix,
-    lengths that end inside a page, on page borders and inside a 64-row tile."""
+    lengths that end inside a page, on page borders and inside a tile; groups of one, odd and even
+    numbers of query heads (the tcgen05 kernel pairs tiles of a group)."""
+    if impl == "tcgen05" and hd != 128:
+        pytest.skip("the tcgen05 kernel takes head_dim 128")
     g = torch.Generator(device=DEV).manual_seed(40)
     starts = [0, 0, 64, 37, 0, 200]
     news = [1, 150, 64, 91, 64, 130]
@@ -432,9 +441,10 @@ def test_attention_prefill(n_q, n_kv, hd, window):
     slot = torch.arange(n_seqs, dtype=torch.int32, device=DEV)
     scale = 1 / math.sqrt(hd)
     out = torch.full((T, n_q * hd), 5.0, dtype=torch.bfloat16, device=DEV)
-    ops().attention_prefill(q, k, v, torch.tensor(cu, dtype=torch.int32, device=DEV),
-                            torch.tensor(starts, dtype=torch.int32, device=DEV), slot, table, out, max(news),
-                            n_q, n_kv, hd, 6, window, scale)
+    _prefill_kernel(impl)(q, k, v, torch.tensor(cu, dtype=torch.int32, device=DEV),
+                          torch.tensor(starts, dtype=torch.int32, device=DEV), slot, table, out, max(news),
+                          n_q, n_kv, hd, 6, window, scale)
+    ops().check_device_errors()
     pos = torch.tensor([s + i for s, n in zip(starts, news) for i in range(n)], dtype=torch.int32, device=DEV)
     slot_tok = torch.tensor([b for b, n in enumerate(news) for _ in range(n)], dtype=torch.int32, device=DEV)
     ref = _attention_reference(q, k, v, pos, slot_tok, table, n_q, n_kv, hd, window, scale)
@@ -444,8 +454,38 @@ def test_attention_prefill(n_q, n_kv, hd, window):
     torch.testing.assert_close(out.float(), plain.float(), atol=2e-2, rtol=2e-2)
 
 
-def test_attention_prefill_finds_a_far_key():
+@pytest.mark.parametrize("impl", ["mma", "tcgen05"])
+@pytest.mark.parametrize("slope", [0.05, 0.2, -0.05])
+def test_attention_prefill_with_scores_that_drift(impl, slope):
+    """Scores that climb (or fall) steadily along the keys: the running maximum moves a little in
+    every block of keys, by less or by more than the step at which the tcgen05 kernel rescales."""
+    hd, n = 128, 700
+    g = torch.Generator(device=DEV).manual_seed(47)
+    n_pages = (n + 63) // 64
+    table = torch.randperm(n_pages, generator=torch.Generator().manual_seed(48)).to(torch.int32).view(1, -1).to(DEV)
+    k = torch.zeros(n_pages, 1, 64, hd, dtype=torch.bfloat16, device=DEV)
+    v = torch.randn(n_pages, 1, 64, hd, device=DEV, generator=g).bfloat16()
+    ramp = (slope * torch.arange(n, device=DEV, dtype=torch.float32)).bfloat16()
+    for p0 in range(0, n, 64):
+        m = min(64, n - p0)
+        k[int(table[0, p0 // 64]), 0, :m, 0] = ramp[p0:p0 + m]
+    q = 0.1 * torch.randn(n, 3 * hd, device=DEV, generator=g).bfloat16()
+    q[:, 0] = 1.0
+    out = torch.empty(n, hd, dtype=torch.bfloat16, device=DEV)
+    pos = torch.arange(n, dtype=torch.int32, device=DEV)
+    slot_tok = torch.zeros(n, dtype=torch.int32, device=DEV)
+    _prefill_kernel(impl)(q, k, v, torch.tensor([0, n], dtype=torch.int32, device=DEV),
+                          torch.zeros(1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                          table, out, n, 1, 1, hd, 6, None, 1.0)
+    ops().check_device_errors()
+    ref = _attention_reference(q, k, v, pos, slot_tok, table, 1, 1, hd, None, 1.0)
+    torch.testing.assert_close(out.double(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("impl", ["mma", "tcgen05"])
+def test_attention_prefill_finds_a_far_key(impl):
     """One key among hundreds carries the weight for the last query; its neighbours do not."""
+    kernel = _prefill_kernel(impl)
     hd = 128
     k = torch.zeros(8, 1, 64, hd, dtype=torch.bfloat16, device=DEV)
     v = torch.zeros(8, 1, 64, hd, dtype=torch.bfloat16, device=DEV)
@@ -459,11 +499,11 @@ def test_attention_prefill_finds_a_far_key():
     out = torch.empty(330, hd, dtype=torch.bfloat16, device=DEV)
     args = (torch.tensor([0, 330], dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
             torch.zeros(1, dtype=torch.int32, device=DEV), table, out, 330, 1, 1, hd, 6)
-    ops().attention_prefill(q, k, v, *args, None, 1.0)
+    kernel(q, k, v, *args, None, 1.0)
     assert abs(out[329, 0].item() - needle % 128) < 0.51
-    ops().attention_prefill(q, k, v, *args, 329 - needle + 1, 1.0)       # the window's last key is the needle
+    kernel(q, k, v, *args, 329 - needle + 1, 1.0)       # the window's last key is the needle
     assert abs(out[329, 0].item() - needle % 128) < 0.51
-    ops().attention_prefill(q, k, v, *args, 329 - needle, 1.0)           # one shorter: the needle is outside
+    kernel(q, k, v, *args, 329 - needle, 1.0)           # one shorter: the needle is outside
     assert abs(out[329, 0].item() - needle % 128) > 10
 
 

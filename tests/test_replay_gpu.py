@@ -58,7 +58,7 @@ def worst(requests, out, ref, tag):
     return max(rows)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("tag,what", [("w", "alone and whole"), ("t", "last 32 one by one"),
                                       ("b", "unequal batches, slots reused")])
 def test_float32_matches_plain(replayed, name, tag, what):
@@ -67,7 +67,7 @@ def test_float32_matches_plain(replayed, name, tag, what):
     assert err < F32_ATOL, f"{what}: first look at request {rid} position {p} (error {err:.3e})"
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("tag,what", [("w", "alone and whole"), ("t", "last 32 one by one"),
                                       ("b", "unequal batches, slots reused")])
 def test_bfloat16_matches_plain(replayed, name, tag, what):
@@ -76,7 +76,7 @@ def test_bfloat16_matches_plain(replayed, name, tag, what):
     assert rel < BF16_REL, f"{what}: first look at request {rid} position {p} (relative error {rel:.3e})"
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_float32_does_not_depend_on_how_tokens_are_cut(replayed, name):
     requests, out, _ = replayed(name, "float32")
     for rid, toks in requests.items():
@@ -89,7 +89,7 @@ def test_float32_does_not_depend_on_how_tokens_are_cut(replayed, name):
 def test_greedy_continuation_agrees(replayed, model_folders):
     """The argmax of the replayed logits is the plain implementation's next token wherever
     the plain top two are further apart than the tolerance."""
-    for name in ("A", "B", "C", "D"):
+    for name in ("A", "B", "C", "D", "E"):
         requests, out, ref = replayed(name, "bfloat16")
         checked = 0
         for rid, toks in requests.items():

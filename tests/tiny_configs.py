@@ -1,5 +1,5 @@
 """The tests' own tiny configurations of the architecture.  They differ in every size
-and option: layers, width, head counts and groups (4/2, 3/1, 6/2), head sizes (16, 32, 48, 64),
+and option: layers, width, head counts and groups (4/2, 3/1, 6/2), head sizes (16, 32, 48, 64, 128),
 ``num_heads * head_dim`` equal to the width or not, feed-forward width, vocabulary (a power
 of two, a multiple of 128, odd), norm epsilon, rotary base, frequency scaling (none and two
 llama3 blocks), tied and untied heads.  Weights are drawn wider than the usual 0.02 so that
@@ -33,5 +33,11 @@ D = dict(architectures=["LlamaForCausalLM"], vocab_size=512, hidden_size=128, in
                            original_max_position_embeddings=64),
          tie_word_embeddings=False, eos_token_id=[3])
 
+# head_dim 128 with an odd group of query heads: the size at which the tcgen05 prefill attention runs
+E = dict(architectures=["LlamaForCausalLM"], vocab_size=777, hidden_size=192, intermediate_size=448,
+         num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=1, head_dim=128,
+         max_position_embeddings=2048, rms_norm_eps=1e-5, rope_theta=20000.0, rope_scaling=None,
+         tie_word_embeddings=False, eos_token_id=11)
+
 # name -> (config.json contents, weight seed, std of matrices and embeddings)
-CONFIGS = {"A": (A, 0, 0.10), "B": (B, 1, 0.08), "C": (C, 2, 0.09), "D": (D, 3, 0.07)}
+CONFIGS = {"A": (A, 0, 0.10), "B": (B, 1, 0.08), "C": (C, 2, 0.09), "D": (D, 3, 0.07), "E": (E, 4, 0.06)}
