@@ -63,6 +63,7 @@ class KvGroup:
         self.v = torch.zeros(shape, dtype=dtype, device=device)
         pin = device.type == "cuda"
         self.table_host = torch.zeros((max_slots, pages_per_seq), dtype=torch.int32, pin_memory=pin)
+        self._table_np = self.table_host.numpy()          # the same memory, cheap to write element by element
         self.table = torch.zeros((max_slots, pages_per_seq), dtype=torch.int32, device=device)
         # per slot: page index within the sequence -> page id, only for pages now held
         self.held: List[Dict[int, int]] = [dict() for _ in range(max_slots)]
@@ -85,7 +86,7 @@ class KvGroup:
         ids = self.pool.take_many(len(want))
         for p, pid in zip(want, ids):
             self.held[slot][p] = pid
-            self.table_host[slot, p] = pid
+            self._table_np[slot, p] = pid
         self._dirty_lo, self._dirty_hi = min(self._dirty_lo, slot), max(self._dirty_hi, slot)
 
     def trim(self, slot: int, length: int) -> None:

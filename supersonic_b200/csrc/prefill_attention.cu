@@ -34,7 +34,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
     unsigned char* v_s = smem + 2 * TILE_BYTES;          // 2 stages
     unsigned char* q_s = smem + 3 * TILE_BYTES;          // [64][HD], dead after the fragment load
     // long tiles (late queries see many keys) first, so that the tail of the grid is short work
-    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+    // blocks start in the order of blockIdx.x, then y: the longest tiles of all heads come first
+    const int tile = (int)gridDim.y - 1 - (int)blockIdx.y, head = blockIdx.x % n_q, b = blockIdx.x / n_q;
     const int row0 = cu_new[b], n_new = cu_new[b + 1] - row0;
     if (tile * PA_BM >= n_new) return;
     const int slot = seq_slot[b];
@@ -210,8 +211,8 @@ SSB_API int ssb_attention_prefill(const void* q, int ldq, const void* k_cache, c
     if (n_seqs <= 0 || max_new <= 0) return 0;
     if (page_shift != 6 || n_kv <= 0 || n_q % n_kv || ldq % 8 || ldo % 2) return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return SSB_ERR_BAD_SIZE;
-    if (n_seqs > 65535 || n_q > 65535) return SSB_ERR_BAD_SIZE;
-    dim3 grid((max_new + PA_BM - 1) / PA_BM, n_q, n_seqs);
+    if ((max_new + PA_BM - 1) / PA_BM > 65535) return SSB_ERR_BAD_SIZE;
+    dim3 grid(n_q * n_seqs, (max_new + PA_BM - 1) / PA_BM);
     const float scale_log2 = scale * 1.4426950408889634f;
 #define SSB_PA(HD) do { \
         constexpr int smem = 4 * PA_BN * HD * 2; \

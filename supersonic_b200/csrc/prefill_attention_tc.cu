@@ -5,9 +5,9 @@
 // the group over the same rows, or neighbouring row tiles), so a page of keys and values is
 // fetched once for 256 rows.  Warp 0 feeds TMA: the two query tiles once, then a page of keys and
 // a page of values per turn into a ring (128-byte swizzle).  Warp 1 issues tcgen05.mma: per tile
-// S = Q K^T (M 128, N 64, K 128) into tensor memory, and O += P V (M 128, N 128, K 64) with P read
-// from tensor memory, where the softmax wrote it over S, and V read MN-major from the page as it
-// lies in the cache.  Warps 2-5 and 6-9 own one query row of the first and second tile per thread:
+// S = Q K^T (M 128, N 64, K 128) into one of two regions of tensor memory, two blocks ahead of the
+// softmax, and O += P V (M 128, N 128, K 64) with P read from tensor memory, where the softmax
+// wrote it over S, and V read MN-major from the page as it lies in the cache.  Warps 2-5 and 6-9 own one query row of the first and second tile per thread:
 // scores come with tcgen05.ld, are masked on the diagonal only, and leave as bfloat16
 // probabilities with tcgen05.st.  O stays in tensor memory for the whole row of blocks: a row's
 // reference maximum moves only when the true maximum has grown by more than 2^8, and only then is
@@ -32,9 +32,10 @@ constexpr int FT_THREADS = 320;
 constexpr uint32_t FT_Q_BYTES = FT_BM * FT_HD * 2;          // 32 KB: two 64-column boxes
 constexpr uint32_t FT_PAGE_BYTES = FT_BN * FT_HD * 2;       // 16 KB: two 64-column boxes
 constexpr float FT_LAZY = 8.f;             // log2 of how far a probability may exceed 1
-// tensor-memory columns of tile x: scores / probabilities at 64 x, output at 128 + 128 x
-constexpr uint32_t FT_S0 = 0, FT_O0 = 128;
-constexpr int FT_NBARS = 1 + 3 * FT_STAGES + 6;
+// tensor-memory columns of tile x: two regions of scores / probabilities at 128 x and 128 x + 64,
+// output at 256 + 128 x
+constexpr uint32_t FT_S0 = 0, FT_O0 = 256;
+constexpr int FT_NBARS = 1 + 3 * FT_STAGES + 12;
 
 __device__ __forceinline__ void mbar_arrive_cta(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -91,20 +92,22 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     unsigned char* q_s = smem;                                   // two tiles of 32 KB
     unsigned char* kv_s = smem + 2 * FT_Q_BYTES;                 // stages of [K page | V page]
     uint64_t* bars = (uint64_t*)(kv_s + FT_STAGES * 2 * FT_PAGE_BYTES);
-    // q_full, k_full[S], v_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2]
+    // q_full, k_full[S], v_full[S], kv_empty[S], s_full, p_full, o_full: [tile][block & 1] each, so that a role that
+    // runs a block ahead never meets a barrier two phases on
     const uint32_t q_full = smem_u32(bars), k_full0 = q_full + 8, v_full0 = k_full0 + 8 * FT_STAGES,
-                   kv_empty0 = v_full0 + 8 * FT_STAGES, s_full0 = kv_empty0 + 8 * FT_STAGES, p_full0 = s_full0 + 16,
-                   o_full0 = p_full0 + 16;
+                   kv_empty0 = v_full0 + 8 * FT_STAGES, s_full0 = kv_empty0 + 8 * FT_STAGES, p_full0 = s_full0 + 32,
+                   o_full0 = p_full0 + 32;
     uint32_t* tmem_slot = (uint32_t*)(bars + FT_NBARS);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);   // [0]: a role gave up; [1]: stays zero
 
-    const int kvh = blockIdx.y, b = blockIdx.z;
+    // blocks start in the order of blockIdx.x, then y: every head's longest tiles come first
+    const int kvh = blockIdx.x % n_kv, b = blockIdx.x / n_kv;
     const int row0 = cu_new[b], n_new = cu_new[b + 1] - row0;
     const int slot = seq_slot[b];
     if (slot < 0 || n_new <= 0) return;
     const int group = n_q / n_kv;
     const int n_items = ((n_new + FT_BM - 1) / FT_BM) * group;   // (row tile, head of the group), heads fastest
-    const int pair = (int)gridDim.x - 1 - (int)blockIdx.x;       // long tiles first
+    const int pair = (int)gridDim.y - 1 - (int)blockIdx.y;       // long tiles first
     if (2 * pair >= n_items) return;
     const int start = seq_start[b];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -134,7 +137,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int s = 0; s < FT_STAGES; ++s) {
             mbar_init(k_full0 + 8 * s, 1); mbar_init(v_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1);
         }
-        for (int i = 0; i < 2; ++i) { mbar_init(s_full0 + 8 * i, 1); mbar_init(p_full0 + 8 * i, 4); mbar_init(o_full0 + 8 * i, 1); }
+        for (int i = 0; i < 4; ++i) { mbar_init(s_full0 + 8 * i, 1); mbar_init(p_full0 + 8 * i, 4); mbar_init(o_full0 + 8 * i, 1); }
         abort_flag[0] = 0;
         abort_flag[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -188,39 +191,43 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FT_BN >> 3) << 17) | ((uint32_t)(FT_BM >> 4) << 24);
             const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(FT_HD >> 3) << 17) | ((uint32_t)(FT_BM >> 4) << 24);
             bool ok = mbar_wait(q_full, 0, abort_flag);
-            auto issue_s = [&](int x, int j) -> bool {           // scores of block j of tile x
+            const uint64_t q_desc = smem_desc(smem_u32(q_s)), k_desc = smem_desc(smem_u32(kv_s));
+            const uint64_t v_desc = smem_desc_mn(smem_u32(kv_s) + FT_PAGE_BYTES);
+            auto issue_s = [&](int x, int j) -> bool {           // scores of block j of tile x, into region j & 1
                 const int s = j % FT_STAGES;
                 if (!mbar_wait(k_full0 + 8 * s, (j / FT_STAGES) & 1, abort_flag)) return false;
                 tc_fence_after();
-                const uint32_t q_addr = smem_u32(q_s) + x * FT_Q_BYTES;
-                const uint32_t k_addr = smem_u32(kv_s + s * 2 * FT_PAGE_BYTES);
+                const uint64_t da = q_desc + (uint64_t)(x * (FT_Q_BYTES >> 4));
+                const uint64_t db = k_desc + (uint64_t)(s * (2 * FT_PAGE_BYTES >> 4));
+                const uint32_t d = tmem + FT_S0 + x * 128 + (j & 1) * FT_BN;
 #pragma unroll
-                for (int ks = 0; ks < FT_HD / 16; ++ks) {
-                    const uint64_t da = smem_desc(q_addr + (ks / 4) * (FT_Q_BYTES / 2)) + 2 * (ks % 4);
-                    const uint64_t db = smem_desc(k_addr + (ks / 4) * (FT_PAGE_BYTES / 2)) + 2 * (ks % 4);
-                    tc_mma(tmem + FT_S0 + x * FT_BN, da, db, idesc_s, ks ? 1u : 0u);
-                }
-                tc_commit(s_full0 + 8 * x);
+                for (int ks = 0; ks < FT_HD / 16; ++ks)          // descriptors count in units of 16 bytes
+                    tc_mma(d, da + (ks / 4) * (FT_Q_BYTES / 2 >> 4) + 2 * (ks % 4),
+                           db + (ks / 4) * (FT_PAGE_BYTES / 2 >> 4) + 2 * (ks % 4), idesc_s, ks ? 1u : 0u);
+                tc_commit(s_full0 + 8 * (2 * x + (j & 1)));
                 return true;
             };
-            for (int x = 0; x < 2 && ok; ++x)
-                if (nb[x] > 0) ok = issue_s(x, 0);
+            for (int j = 0; j < 2; ++j)                          // scores run two blocks ahead of the values
+                for (int x = 0; x < 2 && ok; ++x)
+                    if (j < nb[x]) ok = issue_s(x, j);
             for (int j = 0; j < nb_max && ok; ++j) {
                 const int s = j % FT_STAGES;
                 for (int x = 0; x < 2 && ok; ++x) {
                     if (j >= nb[x]) continue;
-                    if (!mbar_wait(p_full0 + 8 * x, j & 1, abort_flag) ||
+                    // the softmax may be a block ahead: a barrier for each region keeps the phases apart
+                    if (!mbar_wait(p_full0 + 8 * (2 * x + (j & 1)), (j >> 1) & 1, abort_flag) ||
                         !mbar_wait(v_full0 + 8 * s, (j / FT_STAGES) & 1, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t v_addr = smem_u32(kv_s + s * 2 * FT_PAGE_BYTES) + FT_PAGE_BYTES;
+                    const uint64_t dv = v_desc + (uint64_t)(s * (2 * FT_PAGE_BYTES >> 4));
+                    const uint32_t p_at = tmem + FT_S0 + x * 128 + (j & 1) * FT_BN;
 #pragma unroll
                     for (int ks = 0; ks < FT_BN / 16; ++ks)      // 16 keys = 16 rows of 128 bytes further down
-                        tc_mma_ts(tmem + FT_O0 + x * FT_HD, tmem + FT_S0 + x * FT_BN + ks * 8,
-                                  smem_desc_mn(v_addr + ks * 16 * 128), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-                    tc_commit(o_full0 + 8 * x);
-                    // the next scores go where these probabilities lie: the tensor cores take
-                    // their work in the order of issue
-                    if (j + 1 < nb[x]) ok = issue_s(x, j + 1);
+                        tc_mma_ts(tmem + FT_O0 + x * FT_HD, p_at + ks * 8, dv + ks * (16 * 128 >> 4), idesc_o,
+                                  (j > 0 || ks > 0) ? 1u : 0u);
+                    tc_commit(o_full0 + 8 * (2 * x + (j & 1)));
+                    // the scores after next go where these probabilities lie: the tensor cores
+                    // take their work in the order of issue
+                    if (j + 2 < nb[x]) ok = issue_s(x, j + 2);
                 }
                 tc_commit(kv_empty0 + 8 * s);
             }
@@ -235,13 +242,14 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const int r = quarter * 32 + lane;
             const int p0 = t_p0[x];
             const int pos = p0 + r;
-            const uint32_t t_s = tmem + ((uint32_t)(quarter * 32) << 16) + FT_S0 + x * FT_BN;
+            const uint32_t t_s0 = tmem + ((uint32_t)(quarter * 32) << 16) + FT_S0 + x * 128;
             const uint32_t t_o = tmem + ((uint32_t)(quarter * 32) << 16) + FT_O0 + x * FT_HD;
-            const uint32_t s_full = s_full0 + 8 * x, p_full = p_full0 + 8 * x, o_full = o_full0 + 8 * x;
+            const uint32_t s_full = s_full0 + 16 * x, p_full = p_full0 + 16 * x, o_full = o_full0 + 16 * x;
             float m_ref = -INFINITY, l_run = 0.f;
             bool ok = true;
             for (int j = 0; j < n_mine; ++j) {
-                bool w = mbar_wait(s_full, j & 1, abort_flag);
+                const uint32_t t_s = t_s0 + (j & 1) * FT_BN;
+                bool w = mbar_wait(s_full + 8 * (j & 1), (j >> 1) & 1, abort_flag);
                 w = __all_sync(0xffffffffu, w);
                 if (!w) { ok = false; break; }
                 tc_fence_after();
@@ -266,7 +274,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     m_ref = m_new;
                 } else if (__any_sync(0xffffffffu, m_new > m_ref + FT_LAZY)) {
                     // the maximum has grown too far for this warp's rows: rescale what is summed so far
-                    bool wo = mbar_wait(o_full, (j - 1) & 1, abort_flag);
+                    bool wo = mbar_wait(o_full + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag);
                     wo = __all_sync(0xffffffffu, wo);
                     if (!wo) { ok = false; break; }
                     tc_fence_after();
@@ -298,11 +306,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 tc_st_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cta(p_full);
+                if (lane == 0) mbar_arrive_cta(p_full + 8 * (j & 1));
                 l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             }
             if (ok) {
-                bool w = mbar_wait(o_full, (n_mine - 1) & 1, abort_flag);
+                bool w = mbar_wait(o_full + 8 * ((n_mine - 1) & 1), ((n_mine - 1) >> 1) & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, w);
             }
             if (!ok) {
@@ -350,7 +358,7 @@ SSB_API int ssb_attention_prefill_tc(const void* q, int ldq, int n_rows_q, const
                                      int* error_word, cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
     if (head_dim != FT_HD || page_shift != 6) return SSB_ERR_UNSUPPORTED;
-    if (n_kv <= 0 || n_q % n_kv || ldq % 8 || ldo % 8 || !error_word || n_seqs > 65535 || n_kv > 65535) return SSB_ERR_BAD_SIZE;
+    if (n_kv <= 0 || n_q % n_kv || ldq % 8 || ldo % 8 || !error_word ) return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return SSB_ERR_BAD_SIZE;
     CUtensorMap mq, mk, mv;
     int rc = make_map(&mq, q, n_rows_q, n_q * head_dim, ldq, FT_BM);
@@ -370,7 +378,8 @@ SSB_API int ssb_attention_prefill_tc(const void* q, int ldq, int n_rows_q, const
     }
     const int group = n_q / n_kv;
     const int pairs = (((max_new + FT_BM - 1) / FT_BM) * group + 1) / 2;
-    dim3 grid(pairs, n_kv, n_seqs);
+    if (pairs > 65535) return SSB_ERR_BAD_SIZE;
+    dim3 grid(n_kv * n_seqs, pairs);
     prefill_attention_tc_kernel<<<grid, FT_THREADS, smem, stream>>>(
         mq, mk, mv, cu_new, seq_start, seq_slot, page_table, max_pages, (bf16*)out, ldo, n_q, n_kv, window,
         scale * 1.4426950408889634f, error_word);

@@ -12,6 +12,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
+import numpy as np
 import torch
 
 
@@ -59,37 +60,38 @@ def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], device,
     """Lay the entries out back to back and move the index arrays to ``device`` in one copy."""
     if not entries:
         raise ValueError("a step needs at least one entry")
-    tokens: List[int] = []
-    pos: List[int] = []
-    slot_of: List[int] = []
+    tok_parts, pos_parts, slot_parts = [], [], []
     want: List[int] = []
     cu = [0]
     slots, counts = [], []
     for e, start in zip(entries, starts):
-        n = len(e.tokens)
+        toks = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
+        n = int(toks.shape[0])
         if n == 0:
             raise ValueError(f"slot {e.slot}: an entry must bring at least one token")
-        base = len(tokens)
+        base = cu[-1]
         for w in e.want:
             if not 0 <= w < n:
                 raise ValueError(f"slot {e.slot}: wanted place {w} is outside its {n} tokens")
             want.append(base + w)
-        tokens.extend(int(t) for t in e.tokens)
-        pos.extend(range(start, start + n))
-        slot_of.extend([e.slot] * n)
+        tok_parts.append(toks)
+        pos_parts.append(np.arange(start, start + n, dtype=np.int64))
+        slot_parts.append(np.full(n, e.slot, dtype=np.int64))
         cu.append(base + n)
         slots.append(e.slot)
         counts.append(n)
+    tokens = np.concatenate(tok_parts)
     if vocab_size is not None:
-        bad = [t for t in tokens if not 0 <= t < vocab_size]
-        if bad:
-            raise ValueError(f"token ids {bad[:8]} are outside the vocabulary of {vocab_size}")
+        bad = tokens[(tokens < 0) | (tokens >= vocab_size)]
+        if bad.size:
+            raise ValueError(f"token ids {bad[:8].tolist()} are outside the vocabulary of {vocab_size}")
     if len(set(slots)) != len(slots):
         raise ValueError("a slot appears twice in one step")
-    T, B, W = len(tokens), len(slots), len(want)
+    T, B, W = int(tokens.shape[0]), len(slots), len(want)
     longest = max(s + c for s, c in zip(starts, counts))
-    flat = tokens + pos + slot_of + slots + list(starts) + cu + want
-    host = torch.tensor(flat, dtype=torch.int32)
+    flat = np.concatenate(tok_parts + pos_parts + slot_parts + [
+        np.asarray(slots + list(starts) + cu + want, dtype=np.int64)]).astype(np.int32)
+    host = torch.from_numpy(flat)
     dev = torch.device(device)
     if dev.type == "cuda":
         host = host.pin_memory()
