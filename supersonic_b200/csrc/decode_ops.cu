@@ -29,6 +29,10 @@ typedef __nv_bfloat16 bf16;
 // a lane loads 16 bytes (8 consecutive k) of two W rows per 16-row tile and 16 bytes of one x
 // row per 8-row batch tile, and feeds them to mma.m16n8k16 with a k order permuted the same
 // way on both sides (a dot product does not care).  Warps' partial sums meet in shared memory.
+// Launched as thread-block clusters, the blocks of a cluster share one row tile and split K: a
+// matrix with few rows then still puts several blocks on every SM (bytes in flight are what a
+// short projection lacks), and the partial tiles meet in the first block's shared memory over the
+// cluster's distributed shared memory, in a fixed order.
 constexpr int SG_WARPS = 8;
 constexpr int SG_THREADS = SG_WARPS * 32;
 // chunks whose loads are issued before any is used: fewer for wide batches (registers)
@@ -51,6 +55,19 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsig
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ unsigned cluster_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ unsigned cluster_size() { unsigned r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* local, unsigned rank) {
+    unsigned addr = (unsigned)__cvta_generic_to_shared(local), remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -70,7 +87,11 @@ skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restric
     float* inv_rms = smem + SG_WARPS * ROWS * COLS;     // [COLS] (NORM only)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * ROWS;
+    const int n_split = (int)cluster_size(), split = (int)cluster_rank();   // 1 and 0 without clusters
+    const int n0 = ((int)blockIdx.x / n_split) * ROWS;
+    const int n_chunks = (K + 31) / 32;
+    const int per_split = (n_chunks + n_split - 1) / n_split;
+    const int c_lo = split * per_split, c_hi = min(n_chunks, c_lo + per_split);
 
     // The block's slab of W goes to L2 ahead of use (one bulk prefetch per row): all of it when
     // the whole matrix fits L2 comfortably, else only the head of each row (a full prefetch of a
@@ -79,7 +100,9 @@ skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restric
     if (threadIdx.x < ROWS) {
         const bf16* row = W + (size_t)min(n0 + (int)threadIdx.x, N - 1) * ldw;
         const bool small = (size_t)N * K * 2 <= (size_t)64 << 20;
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(row), "r"(small ? K * 2 : min(K * 2, 4096)) : "memory");
+        const int k_lo = min(c_lo * 32, K), k_n = min(c_hi * 32, K) - k_lo;      // multiples of 8 elements
+        if (k_n > 0)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(row + k_lo), "r"(small ? k_n * 2 : min(k_n * 2, 4096)) : "memory");
     }
     ssb_pdl_launch_dependents();
     ssb_pdl_wait();                                     // x (and out) belong to the predecessor until here
@@ -107,14 +130,13 @@ skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restric
 #pragma unroll
     for (int j = 0; j < NB; ++j) ssq[j] = 0.f;
 
-    const int n_chunks = (K + 31) / 32;
-    for (int c0 = warp; c0 < n_chunks; c0 += SG_WARPS * SG_UNROLL) {
+    for (int c0 = c_lo + warp; c0 < c_hi; c0 += SG_WARPS * SG_UNROLL) {
         uint4 wa[SG_UNROLL][RM][2];
         uint4 xb[SG_UNROLL][NB];
 #pragma unroll
         for (int u = 0; u < SG_UNROLL; ++u) {
             const int k = (c0 + u * SG_WARPS) * 32 + t * 8;
-            const bool live = k < K;                     // K is a multiple of 8: all 8 or none
+            const bool live = k < K && c0 + u * SG_WARPS < c_hi;   // K is a multiple of 8: all 8 or none
 #pragma unroll
             for (int i = 0; i < RM; ++i) {
                 wa[u][i][0] = live ? ldg_stream(w_row[i][0] + k) : make_uint4(0, 0, 0, 0);
@@ -202,18 +224,35 @@ skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restric
         __syncthreads();
     }
 
+    // the warps' partial tiles are summed in place into red[0]; a cluster's tiles meet in its first block
+    for (int e = threadIdx.x; e < ROWS * COLS; e += SG_THREADS) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < SG_WARPS; ++w) v += red[(size_t)w * ROWS * COLS + e];
+        red[e] = v;
+    }
+    if (n_split > 1) {
+        cluster_sync_all();                             // every block's tile is complete
+        if (split != 0) {
+            cluster_sync_all();                         // stay until the first block has read it
+            return;
+        }
+        for (int e = threadIdx.x; e < ROWS * COLS; e += SG_THREADS) {
+            float v = red[e];
+            for (int r = 1; r < n_split; ++r) v += ld_cluster_f32(red + e, (unsigned)r);
+            red[e] = v;
+        }
+        cluster_sync_all();
+    }
+    __syncthreads();
+
     if (mode == SG_SWIGLU) {
         // rows come as [8 gate | 8 up] per 16: out[b, n0/2 + j] = silu(gate_j) * up_j
         for (int e = threadIdx.x; e < (ROWS / 2) * COLS; e += SG_THREADS) {
             const int j = e % (ROWS / 2), b = e / (ROWS / 2);
             const int r_gate = (j / 8) * 16 + (j % 8), n_out = n0 / 2 + j;
             if (b >= n_rows || n0 + r_gate + 8 >= N) continue;
-            float gate = 0.f, up = 0.f;
-#pragma unroll
-            for (int w = 0; w < SG_WARPS; ++w) {
-                gate += red[((size_t)w * ROWS + r_gate) * COLS + b];
-                up += red[((size_t)w * ROWS + r_gate + 8) * COLS + b];
-            }
+            float gate = red[(size_t)r_gate * COLS + b], up = red[(size_t)(r_gate + 8) * COLS + b];
             if (NORM) { gate *= inv_rms[b]; up *= inv_rms[b]; }
             ((bf16*)out)[(size_t)b * ldo + n_out] = __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
         }
@@ -223,9 +262,7 @@ skinny_gemm_kernel(const void* __restrict__ x_in, int ldx, const void* __restric
         const int r = e % ROWS, b = e / ROWS;
         const int n = n0 + r;
         if (b >= n_rows || n >= N) continue;
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < SG_WARPS; ++w) s += red[((size_t)w * ROWS + r) * COLS + b];
+        float s = red[(size_t)r * COLS + b];
         if (NORM) s *= inv_rms[b];
         const size_t o = (size_t)b * ldo + n;
         if (mode == SG_ACCUMULATE) ((float*)out)[o] += s;
@@ -281,7 +318,7 @@ template <int RM, int NB, bool NORM>
 static int launch_skinny(const void* x, int ldx, const void* norm_w, int norm_w_is_f32, float eps,
                          const bf16* W, int ldw, void* out, int ldo, int out_is_f32, int n_rows, int N,
                          int K, int mode, int pdl, const void* post_w, int post_w_is_f32, float post_eps,
-                         bf16* post_out, int* post_counter, cudaStream_t stream) {
+                         bf16* post_out, int* post_counter, int k_split, cudaStream_t stream) {
     constexpr int ROWS = 16 * RM, COLS = 8 * NB;
     const size_t smem = (size_t)(SG_WARPS * ROWS * COLS + COLS + SG_WARPS * COLS) * sizeof(float);
     auto kern = skinny_gemm_kernel<RM, NB, NORM>;
@@ -289,9 +326,25 @@ static int launch_skinny(const void* x, int ldx, const void* norm_w, int norm_w_
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    return ssb_launch(kern, dim3((N + ROWS - 1) / ROWS), dim3(SG_THREADS), smem, stream, pdl != 0, x, ldx, norm_w,
-                      norm_w_is_f32, eps, W, ldw, out, ldo, out_is_f32, n_rows, N, K, mode, post_w, post_w_is_f32,
-                      post_eps, post_out, post_counter);
+    if (k_split <= 1)
+        return ssb_launch(kern, dim3((N + ROWS - 1) / ROWS), dim3(SG_THREADS), smem, stream, pdl != 0, x, ldx, norm_w,
+                          norm_w_is_f32, eps, W, ldw, out, ldo, out_is_f32, n_rows, N, K, mode, post_w, post_w_is_f32,
+                          post_eps, post_out, post_counter);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(((N + ROWS - 1) / ROWS) * k_split);
+    cfg.blockDim = dim3(SG_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = k_split; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, x, ldx, norm_w, norm_w_is_f32, eps, W, ldw, out, ldo, out_is_f32,
+                                       n_rows, N, K, mode, post_w, post_w_is_f32, post_eps, post_out, post_counter);
+    return e == cudaSuccess ? ssb_launch_status() : (int)e;
 }
 
 // x: bfloat16 [n_rows, K] (norm_w == null) or the float32 residual [n_rows, K] normalised on the
@@ -301,11 +354,13 @@ static int launch_skinny(const void* x, int ldx, const void* norm_w, int norm_w_
 // dependent of the kernel before it on the stream (weights are prefetched while that one ends).
 // post_out (mode 1 only): bfloat16 [n_rows, N] that receives RMSNorm(out; post_w, post_eps) of the
 // finished rows, computed by the block that finishes last; post_counter: a zeroed int, left zero.
+// k_split (1..8): blocks per cluster that share a row tile and split K (not with norm_w or post_out).
 SSB_API int ssb_skinny_gemm(const void* x, int ldx, const void* norm_w, int norm_w_dtype, float eps,
                             const void* W, int ldw, void* out, int ldo, int out_dtype, int n_rows, int N,
                             int K, int mode, int pdl, const void* post_w, int post_w_dtype, float post_eps,
-                            void* post_out, int* post_counter, cudaStream_t stream) {
+                            void* post_out, int* post_counter, int k_split, cudaStream_t stream) {
     if (n_rows <= 0 || N <= 0) return 0;
+    if (k_split < 1 || k_split > 8 || (k_split > 1 && (norm_w || post_out))) return SSB_ERR_BAD_SIZE;
     if (n_rows > 64 || K <= 0 || K % 8 || ldw % 8 || ldx % 8) return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)x | (uintptr_t)W | (uintptr_t)norm_w) & 15) return SSB_ERR_BAD_SIZE;
     if (mode == SG_ACCUMULATE && out_dtype != SSB_F32) return SSB_ERR_BAD_DTYPE;
@@ -316,8 +371,8 @@ SSB_API int ssb_skinny_gemm(const void* x, int ldx, const void* norm_w, int norm
         return SSB_ERR_BAD_SIZE;
     const bf16* Wb = (const bf16*)W;
 #define SSB_SG(RM, NB) \
-    return norm_w ? launch_skinny<RM, NB, true>(x, ldx, norm_w, nwf, eps, Wb, ldw, out, ldo, f32o, n_rows, N, K, mode, pdl, post_w, pwf, post_eps, (bf16*)post_out, post_counter, stream) \
-                  : launch_skinny<RM, NB, false>(x, ldx, nullptr, 0, 0.f, Wb, ldw, out, ldo, f32o, n_rows, N, K, mode, pdl, post_w, pwf, post_eps, (bf16*)post_out, post_counter, stream)
+    return norm_w ? launch_skinny<RM, NB, true>(x, ldx, norm_w, nwf, eps, Wb, ldw, out, ldo, f32o, n_rows, N, K, mode, pdl, post_w, pwf, post_eps, (bf16*)post_out, post_counter, k_split, stream) \
+                  : launch_skinny<RM, NB, false>(x, ldx, nullptr, 0, 0.f, Wb, ldw, out, ldo, f32o, n_rows, N, K, mode, pdl, post_w, pwf, post_eps, (bf16*)post_out, post_counter, k_split, stream)
     if (n_rows <= 8) { SSB_SG(1, 1); }
     if (n_rows <= 16) { SSB_SG(2, 2); }
     if (n_rows <= 32) { SSB_SG(2, 4); }

@@ -66,6 +66,8 @@ class FastKernels(PlainKernels):
                 normed = torch.empty(out.shape, dtype=torch.bfloat16, device=out.device)
                 post = (then_norm.weight, then_norm.eps, normed,
                         self._buffer("post_norm_counter", 1, torch.int32, out.device, zero=True))
+            # clusters that split K (k_split > 1) measured slower at every 8B shape: more and shorter
+            # blocks mean more waves, and a wave's fixed cost is what a short projection pays for
             ops.skinny_gemm(x, weight, out, mode, pdl=self.pdl, post_norm=post)
             if post is not None:
                 then_norm.provide(post[2])
@@ -85,6 +87,16 @@ class FastKernels(PlainKernels):
                 ops.gemv_tc(x, weight, out, ops.TC_ACCUMULATE, splits=ops.gemv_tc_splits(n, k), pdl=self.pdl)
             elif rows <= 64 and n >= 16384:
                 ops.gemv_tc(x, weight, out, ops.TC_STORE, pdl=self.pdl)
+            elif rows <= 16:
+                # few row tiles: blocks share a tile's K range and the last one sums their parts in
+                # order (14 us against 23 us for the 8B query/key/value projection at 16 rows; at 64
+                # rows the parts cost more than the narrow-tile GEMM)
+                splits = ops.gemv_tc_splits(n, k)
+                nf, nc = ops.gemv_tc_scratch(rows, n, splits)
+                ops.gemv_tc(x, weight, out, ops.TC_STORE, splits=splits,
+                            partials=self._buffer("gemv_partials", nf, torch.float32, out.device),
+                            counters=self._buffer("gemv_counters", nc, torch.int32, out.device, zero=True),
+                            pdl=self.pdl)
             else:
                 ops.gemm_tc(x, weight, out, ops.TC_ACCUMULATE if accumulate else ops.TC_STORE,
                             tile_n=self._tile_n(rows, n))
@@ -151,7 +163,9 @@ class FastKernels(PlainKernels):
         kind = 1
         if head_dim in (64, 128) and group <= 16 and page_shift == 6 and (batch.n_seqs >= 32 or pages >= 32):
             # tensor-core kernel (many sequences or long contexts): a block streams pages back to
-            # back; at least 8 pages a split, about two blocks per SM
+            # back; at least 8 pages a split, about two blocks per SM.  Alone it is the faster kernel
+            # at every batch size, but inside a step of few sequences its 64 KB of shared memory
+            # cost the neighbouring projections more than it saves (measured at batch 1 and 8).
             kind = 2
             n_splits = max(1, min(296 // (batch.n_seqs * n_kv), pages // 8, 64))
         elif batch.n_seqs <= 2:

@@ -75,8 +75,9 @@ def linear(args):
     ws = [(torch.randn(N, K, device=DEV) * 0.02).bfloat16() for _ in range(copies)]
     x = torch.randn(B, K, device=DEV).bfloat16()
     out = torch.empty(B, N, dtype=torch.bfloat16, device=DEV)
-    if args.kernel == "skinny":
-        fn = lambda i: ops.skinny_gemm(x, ws[i % copies], out, pdl=args.pdl)
+    if args.kernel.startswith("skinny"):                   # skinny = one block per row tile, skinny4 = clusters of 4
+        k_split = int(args.kernel[6:]) if len(args.kernel) > 6 else 1
+        fn = lambda i: ops.skinny_gemm(x, ws[i % copies], out, pdl=args.pdl, k_split=k_split)
     elif args.kernel.startswith("gv"):                      # gv = automatic splits, gv4 = 4 splits
         splits = int(args.kernel[2:]) if len(args.kernel) > 2 else ops.gemv_tc_splits(N, K)
         nf, nc = ops.gemv_tc_scratch(B, N, splits)

@@ -242,13 +242,14 @@ def skinny_gemm_ok(x: torch.Tensor, w: torch.Tensor, normed: bool) -> bool:
 
 def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = SG_STORE,
                 norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, pdl: bool = False,
-                post_norm=None) -> None:
+                post_norm=None, k_split: int = 1) -> None:
     """out = x @ w^T for up to 64 rows.  With ``norm_weight`` x is the float32 residual and is
     RMS-normalised on the way in.  ``pdl``: launch as a programmatic dependent of the kernel
     before it on the stream (its weights are prefetched while that kernel ends).
     ``post_norm`` = (weight, eps, out bfloat16 [rows, N], zeroed int32 counter), with mode accumulate:
     the block that finishes last also writes RMSNorm(out) of the finished rows into it.  mode: store, add into float32 ``out``, or SwiGLU over rows
-    of ``w`` that come as [8 gate | 8 up] per 16 (``out`` is [rows, N/2])."""
+    of ``w`` that come as [8 gate | 8 up] per 16 (``out`` is [rows, N/2]).  ``k_split`` (1..8):
+    blocks per thread-block cluster that share a row tile and split K (see ``skinny_k_split``)."""
     _need(x, "x", torch.float32 if norm_weight is not None else torch.bfloat16, 2)
     _need(w, "w", torch.bfloat16, 2); _need(out, "out", None, 2)
     B, K = x.shape
@@ -274,7 +275,16 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int =
         c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(dtype_code(out.dtype)), c_int(B),
         c_int(N), c_int(K), c_int(mode), c_int(1 if pdl else 0), _ptr(pw),
         c_int(dtype_code(pw.dtype) if pw is not None else 0), c_float(peps), _ptr(pout), _ptr(pcount),
-        _stream()), "skinny_gemm")
+        c_int(k_split), _stream()), "skinny_gemm")
+
+
+def skinny_k_split(rows: int, n: int, k: int, target_blocks: int) -> int:
+    """Cluster size for ``skinny_gemm``: enough blocks to put several on every SM, each with at
+    least 512 columns of K (only the 16-row tiles of up to 8 batch rows are short of blocks)."""
+    if rows > 8:
+        return 1
+    tiles = (n + 15) // 16
+    return max(1, min(8, target_blocks // tiles, k // 512))
 
 
 def attention_decode_scratch(n_seqs: int, n_q: int, n_kv: int, head_dim: int, n_splits: int):

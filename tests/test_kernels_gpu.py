@@ -291,6 +291,32 @@ def test_skinny_gemm_store_and_accumulate(rows, N, K):
     torch.testing.assert_close(out, plain, atol=2e-5 * math.sqrt(K), rtol=1e-4)
 
 
+@pytest.mark.parametrize("k_split", [2, 3, 4, 8])
+@pytest.mark.parametrize("rows,N,K", [(1, 301, 4096), (8, 48, 1000), (5, 272, 1440), (8, 1000, 72)])
+def test_skinny_gemm_clusters_that_split_k(rows, N, K, k_split):
+    """Clusters of blocks that share a row tile and split K give the unsplit kernel's result in all
+    three modes; K ranges that do not divide evenly, and more blocks than K has chunks."""
+    g = torch.Generator(device=DEV).manual_seed(23)
+    x = torch.randn(rows, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    ref = x.double() @ w.double().T
+    out = torch.empty(rows, N, device=DEV)
+    ops().skinny_gemm(x, w, out, k_split=k_split)
+    torch.testing.assert_close(out.double(), ref, atol=2e-5 * math.sqrt(K), rtol=1e-4)
+    acc = torch.full((rows, N), 2.0, device=DEV)
+    ops().skinny_gemm(x, w, acc, mode=1, k_split=k_split)
+    torch.testing.assert_close(acc.double(), ref + 2, atol=2e-5 * math.sqrt(K), rtol=1e-4)
+    if N % 16 == 0:
+        one = torch.empty(rows, N // 2, dtype=torch.bfloat16, device=DEV)
+        ops().skinny_gemm(x, w, one, mode=2)
+        split = torch.empty_like(one)
+        ops().skinny_gemm(x, w, split, mode=2, k_split=k_split)
+        torch.testing.assert_close(split.float(), one.float(), atol=2e-2, rtol=2e-2)
+    from supersonic_b200.csrc.ops import KernelError
+    with pytest.raises(KernelError):
+        ops().skinny_gemm(x.float(), w, out, norm_weight=torch.ones(K, device=DEV), eps=1e-5, k_split=k_split)
+
+
 @pytest.mark.parametrize("rows,wdtype", [(1, torch.bfloat16), (4, torch.float32), (8, torch.bfloat16)])
 def test_skinny_gemm_with_norm_on_the_way_in(rows, wdtype):
     g = torch.Generator(device=DEV).manual_seed(21)
