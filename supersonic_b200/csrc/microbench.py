@@ -3,7 +3,7 @@ so that weights come from DRAM), and reports bytes or FLOPs per second.
 
     python -m supersonic_b200.csrc.microbench attention_decode --batch 64 --context 520
     python -m supersonic_b200.csrc.microbench linear --rows 8 --n 6144 --k 4096 [--kernel skinny|tc64|tc128|tc256]
-    python -m supersonic_b200.csrc.microbench attention_prefill --tokens 2048 --seqs 1
+    python -m supersonic_b200.csrc.microbench attention_prefill --tokens 2048 --seqs 1 [--kernel tc]
     python -m supersonic_b200.csrc.microbench gemm --rows 2048 --n 28672 --k 4096 --tile 256
 
 One JSON line per run.  It is also the small, self-ending workload that profiler captures
@@ -61,11 +61,17 @@ def attention_decode(args):
     nf, nc = ops.attention_decode_scratch(B, n_q, n_kv, hd, splits)
     scratch = torch.empty(max(nf, 1), device=DEV)
     counters = torch.zeros(max(nc, 1), dtype=torch.int32, device=DEV)
+    cos = sin = None
+    if args.fused:                                   # rotation and append inside, as a decode step runs it
+        ang = torch.arange(ctx, device=DEV, dtype=torch.float64)[:, None] * \
+            (1.0 / 10000 ** (torch.arange(hd // 2, device=DEV, dtype=torch.float64) * 2 / hd))[None, :]
+        cos, sin = ang.cos().float().contiguous(), ang.sin().float().contiguous()
     us = _time(lambda i: ops.attention_decode(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, None,
-                                              1 / math.sqrt(hd), splits, scratch, counters, kind=args.kind),
+                                              1 / math.sqrt(hd), splits, scratch, counters, kind=args.kind,
+                                              cos=cos, sin=sin, pdl=args.pdl),
                args.iters)
     nbytes = B * ctx * n_kv * hd * 2 * 2
-    return {"kernel": "attention_decode", "kind": args.kind, "batch": B, "context": ctx, "splits": splits, "us": round(us, 2),
+    return {"kernel": "attention_decode", "kind": args.kind, "fused": bool(args.fused), "batch": B, "context": ctx, "splits": splits, "us": round(us, 2),
             "GB/s": round(nbytes / us / 1e3, 1)}
 
 
@@ -121,10 +127,13 @@ def attention_prefill(args):
     cu = torch.arange(S + 1, dtype=torch.int32, device=DEV) * T
     start = torch.zeros(S, dtype=torch.int32, device=DEV)
     slot = torch.arange(S, dtype=torch.int32, device=DEV)
-    us = _time(lambda i: ops.attention_prefill(q, k, v, cu, start, slot, table, out, T, n_q, n_kv, hd, 6, None,
-                                               1 / math.sqrt(hd)), args.iters)
+    kernel = ops.attention_prefill_tc if args.kernel == "tc" else ops.attention_prefill   # --kernel tc: tcgen05
+    us = _time(lambda i: kernel(q, k, v, cu, start, slot, table, out, T, n_q, n_kv, hd, 6, None,
+                                1 / math.sqrt(hd)), args.iters)
+    ops.check_device_errors()
     flops = S * 4.0 * n_q * hd * T * (T + 1) / 2
-    return {"kernel": "attention_prefill", "seqs": S, "tokens": T, "us": round(us, 2),
+    return {"kernel": "attention_prefill_tc" if args.kernel == "tc" else "attention_prefill", "seqs": S, "tokens": T,
+            "us": round(us, 2),
             "TFLOP/s": round(flops / us / 1e6, 1)}
 
 
@@ -148,6 +157,7 @@ def main(argv=None):
         p.add_argument("--kind", type=int, default=0, help="attention_decode: 0 auto, 1 general, 2 tensor-core")
         p.add_argument("--accumulate", action="store_true", help="linear gv*: add into a float32 output")
         p.add_argument("--pdl", action="store_true", help="launch as programmatic dependents")
+        p.add_argument("--fused", action="store_true", help="attention_decode: rotate and append inside")
         p.add_argument("--seqs", type=int, default=1)
         p.add_argument("--tokens", type=int, default=2048)
     args = ap.parse_args(argv)
