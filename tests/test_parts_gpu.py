@@ -269,3 +269,141 @@ def test_toy_mixer_with_its_own_state(model_folders):
     assert sc == sa
     got = m.step([StepEntry(sc, b, range(9))])
     assert np.abs(got.double().cpu().numpy() - plain(b)).max() < 2e-5
+
+
+def test_toy_feed_forward_with_routing(model_folders):
+    """A feed-forward defined here that routes every token to one of two experts (router logits
+    and the gate in float32, experts cut out of the dense weights) replaces layer 0's: registered,
+    built and stepped with unequal prompts and then token by token."""
+    from dataclasses import replace
+    from supersonic_b200.config.base import PartSpec
+    from supersonic_b200.engine import Model, StepEntry
+    from supersonic_b200.parts import register_feed_forward
+    from supersonic_b200.weights import WeightStore
+
+    @register_feed_forward("toy_top1")
+    class ToyTop1:
+        """logits = x Wr^T; e = argmax; out = softmax(logits)[e] * down_e(silu(gate_e x) * up_e x)."""
+
+        def __init__(self, params, weights, build):
+            self.n_experts = params["n_experts"]
+            get = lambda k: build.weights.as_dtype(weights[k], torch.float32)
+            self.gate, self.up, self.down = get("gate"), get("up"), get("down")
+            self.router = self.gate[: self.n_experts]
+            self.width = self.gate.shape[0] // self.n_experts
+
+        def forward(self, ctx, x, residual):
+            x = x.float()
+            logits = x @ self.router.T
+            prob = torch.softmax(logits, dim=-1)
+            choice = logits.argmax(dim=-1)
+            for e in range(self.n_experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                lo, hi = e * self.width, (e + 1) * self.width
+                xe = x[rows]
+                g, u = xe @ self.gate[lo:hi].T, xe @ self.up[lo:hi].T
+                y = (torch.nn.functional.silu(g) * u) @ self.down[:, lo:hi].T
+                residual[rows] += prob[rows, e, None] * y
+
+    d, pc, pw = model_folders["C"]
+    spec = _spec_with(tiny_configs.C)
+    p0 = "model.layers.0.mlp"
+    toy = PartSpec("toy_top1", {"n_experts": 2}, {"gate": f"{p0}.gate_proj.weight", "up": f"{p0}.up_proj.weight",
+                                                  "down": f"{p0}.down_proj.weight"})
+    spec = replace(spec, blocks=[replace(spec.blocks[0], feed_forward=toy)] + list(spec.blocks[1:]))
+    m = Model(spec, WeightStore.from_dir(d), dtype="float32", device=DEV, max_tokens=256)
+
+    def plain(tokens):
+        T = len(tokens)
+        cos, sin = pl.rope_tables(pc, T)
+        h = pl.embedding(tokens, pw["model.embed_tokens.weight"])
+        h = h + pl.attention_mixer(pl.rms_norm(h, pw["model.layers.0.input_layernorm.weight"], pc["rms_norm_eps"]),
+                                   pw, "model.layers.0", pc, cos, sin)
+        x = pl.rms_norm(h, pw["model.layers.0.post_attention_layernorm.weight"], pc["rms_norm_eps"])
+        gate, up, down = (pw[f"{p0}.{n}_proj.weight"] for n in ("gate", "up", "down"))
+        width = gate.shape[0] // 2
+        logits = x @ gate[:2].T
+        prob = np.exp(logits - logits.max(-1, keepdims=True))
+        prob /= prob.sum(-1, keepdims=True)
+        out = np.zeros_like(h)
+        used.update(int(e) for e in logits.argmax(-1))
+        for t in range(T):
+            e = int(logits[t].argmax())
+            lo, hi = e * width, (e + 1) * width
+            g, u = gate[lo:hi] @ x[t], up[lo:hi] @ x[t]
+            out[t] = prob[t, e] * (down[:, lo:hi] @ (g / (1 + np.exp(-g)) * u))
+        h = h + out
+        for layer in range(1, pc["num_hidden_layers"]):
+            h = pl.block(h, pw, layer, pc, cos, sin)
+        return pl.output_head(h, pw, pc)
+
+    used = set()
+    rng = np.random.default_rng(8)
+    a, b = rng.integers(0, 301, 23).tolist(), rng.integers(0, 301, 11).tolist()
+    ra, rb = plain(a), plain(b)
+    assert used == {0, 1}                                       # else the routing was not exercised
+    sa, sb = m.open_sequence(), m.open_sequence()
+    got = m.step([StepEntry(sa, a[:18], range(18)), StepEntry(sb, b[:6], range(6))])
+    ga, gb = [got[:18]], [got[18:]]
+    for i in range(5):
+        got = m.step([StepEntry(sa, [a[18 + i]], [0]), StepEntry(sb, [b[6 + i]], [0])])
+        ga.append(got[:1]); gb.append(got[1:])
+    assert np.abs(torch.cat(ga).double().cpu().numpy() - ra).max() < 2e-5
+    assert np.abs(torch.cat(gb).double().cpu().numpy() - rb).max() < 2e-5
+
+
+def test_toy_position_encoding(model_folders):
+    """A position encoding defined here (a learned vector per position added to every query and
+    key head, no rotation) replaces the rotary one in every layer: registered, built, stepped."""
+    from dataclasses import replace
+    from supersonic_b200.cache import PAGE_SHIFT
+    from supersonic_b200.config.base import PartSpec
+    from supersonic_b200.engine import Model, StepEntry
+    from supersonic_b200.parts import register_position_encoding
+    from supersonic_b200.weights import WeightStore
+
+    @register_position_encoding("toy_learned")
+    class ToyLearned:
+        def __init__(self, params, weights, build):
+            self.head_dim = params["head_dim"]
+            self.table = build.weights.as_dtype(weights["table"], torch.float32)[:, : self.head_dim].contiguous()
+
+        def encode_and_append(self, ctx, qkv, kv, n_q, n_kv, write_cache=True):
+            k_cache, v_cache, table, _ = kv
+            n_rot = n_q + (n_kv if write_cache else 0)
+            shift = 0.5 * self.table[ctx.batch.pos.long()]                       # [T, head_dim]
+            heads = qkv[:, : n_rot * self.head_dim].view(qkv.shape[0], n_rot, self.head_dim)
+            heads += shift[:, None, :].to(qkv.dtype)
+            ctx.kernels.rope_append(qkv, None, None, ctx.batch, table, k_cache, v_cache, n_q, n_kv,
+                                    self.head_dim, 0, PAGE_SHIFT, write_cache)
+
+    d, pc, pw = model_folders["B"]
+    spec = _spec_with(tiny_configs.B)
+    toy = PartSpec("toy_learned", {"head_dim": pc["head_dim"]}, {"table": "model.embed_tokens.weight"})
+    spec = replace(spec, blocks=[replace(b, position=toy) for b in spec.blocks])
+    m = Model(spec, WeightStore.from_dir(d), dtype="float32", device=DEV, max_tokens=256)
+
+    def plain(tokens):
+        T = len(tokens)
+        nq, nkv, hd = pc["num_attention_heads"], pc["num_key_value_heads"], pc["head_dim"]
+        shift = 0.5 * pw["model.embed_tokens.weight"][:T, :hd]
+        h = pl.embedding(tokens, pw["model.embed_tokens.weight"])
+        for layer in range(pc["num_hidden_layers"]):
+            p = f"model.layers.{layer}"
+            x = pl.rms_norm(h, pw[f"{p}.input_layernorm.weight"], pc["rms_norm_eps"])
+            q = (x @ pw[f"{p}.self_attn.q_proj.weight"].T).reshape(T, nq, hd) + shift[:, None, :]
+            k = (x @ pw[f"{p}.self_attn.k_proj.weight"].T).reshape(T, nkv, hd) + shift[:, None, :]
+            v = (x @ pw[f"{p}.self_attn.v_proj.weight"].T).reshape(T, nkv, hd)
+            a = pl.attention_scores(q, k, v, 1 / math.sqrt(hd), None).reshape(T, nq * hd)
+            h = h + a @ pw[f"{p}.self_attn.o_proj.weight"].T
+            h = h + pl.swiglu_ffn(pl.rms_norm(h, pw[f"{p}.post_attention_layernorm.weight"], pc["rms_norm_eps"]), pw, p)
+        return pl.output_head(h, pw, pc)
+
+    toks = np.random.default_rng(9).integers(0, 384, 75).tolist()
+    ref = plain(toks)
+    s = m.open_sequence()
+    got = [m.step([StepEntry(s, toks[:66], range(66))])]
+    got += [m.step([StepEntry(s, [toks[p]], [0])]) for p in range(66, 75)]
+    assert np.abs(torch.cat(got).double().cpu().numpy() - ref).max() < 2e-5
