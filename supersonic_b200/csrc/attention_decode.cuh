@@ -106,9 +106,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
                         long long prefetch_bytes) {
     __shared__ float sm_m[NW][AD_GROUP], sm_l[NW][AD_GROUP];
     __shared__ float sm_acc[NW][AD_GROUP][32 * VEC];
-    __shared__ float sm_f[AD_GROUP][AD_MAX_SPLITS];          // per split: exp(max_split - max_all)
-    __shared__ float sm_pm[AD_GROUP][AD_MAX_SPLITS], sm_pl[AD_GROUP][AD_MAX_SPLITS];
-    __shared__ float sm_L[AD_GROUP];
     __shared__ int is_last;
     const int b = blockIdx.x, split = blockIdx.z;
     const int group = n_q / n_kv;
@@ -170,6 +167,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
     AdRaw<VEC> ka[AD_TOK], va[AD_TOK];
     int j0 = my_lo + warp * AD_TOK;
     if (j0 <= my_hi) issue(j0, ka, va);
+    // rotation of this lane's elements: pairs (i, i + head_dim/2) live in lanes l and l ^ 16.  The
+    // tables are written by no kernel of the step: fetched before the wait as well.
+    float rc[VEC], rs[VEC];
+    if (FUSE) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            const int i = (lane & 15) * VEC + e;
+            rc[e] = cos_t[(size_t)p * (head_dim / 2) + i];
+            rs[e] = (lane < 16 ? -1.f : 1.f) * sin_t[(size_t)p * (head_dim / 2) + i];
+        }
+    }
     if (FUSE) ssb_pdl_wait();                                    // the query (and this token's k, v) come from the predecessor
     // This kernel moves little data and waits on latencies: meanwhile it asks L2 to fetch a slice
     // of the weights that the kernels after it will stream (after the wait: so as not to compete with the projection before it).
@@ -185,16 +193,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
         }
     }
 
-    // rotation of this lane's elements: pairs (i, i + head_dim/2) live in lanes l and l ^ 16
-    float rc[VEC], rs[VEC];
-    if (FUSE) {
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-            const int i = (lane & 15) * VEC + e;
-            rc[e] = cos_t[(size_t)p * (head_dim / 2) + i];
-            rs[e] = (lane < 16 ? -1.f : 1.f) * sin_t[(size_t)p * (head_dim / 2) + i];
-        }
-    }
     float qv[AD_GROUP][VEC];
 #pragma unroll
     for (int gi = 0; gi < AD_GROUP; ++gi) {
@@ -273,6 +271,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
         }
     };
     // one copy of the loop body (instruction fetch matters at this size): use a turn, then fetch the next
+    // (a second set of registers for a turn in flight meanwhile was measured: no faster, the turn is
+    // bound by its shuffles, and 190 registers a thread)
 #pragma unroll 1
     while (j0 <= my_hi) {
         consume(j0, ka, va);
@@ -363,44 +363,36 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    // 1. every split's (max, sum) of every head -> shared memory
-    for (int e = threadIdx.x; e < n_heads * n_splits; e += (NW * 32)) {
-        const int gi = e / n_splits, sp = e % n_splits;
-        const float* part = scratch + (((size_t)b * n_q + h0 + gi) * n_splits + sp) * (head_dim + 2);
-        sm_pm[gi][sp] = __ldcg(part + head_dim);
-        sm_pl[gi][sp] = __ldcg(part + head_dim + 1);
-    }
-    __syncthreads();
-    // 2. per head: overall max, each split's factor, overall sum (in split order)
-    if (threadIdx.x < n_heads) {
-        const int gi = threadIdx.x;
-        float mm = -INFINITY;
-        for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, sm_pm[gi][sp]);
-        float ll = 0.f;
-        for (int sp = 0; sp < n_splits; ++sp) {
-            const float f = (sm_pm[gi][sp] == -INFINITY) ? 0.f : __expf(sm_pm[gi][sp] - mm);
-            sm_f[gi][sp] = f;
-            ll += sm_pl[gi][sp] * f;
-        }
-        sm_L[gi] = ll;
-    }
-    __syncthreads();
-    // 3. weighted sum of the splits' values, in split order, loads four at a time
+    // every thread owns elements (head gi, dim d) of the output and goes through the splits itself,
+    // in split order, eight at a time so that their loads are in flight together: a split's
+    // (max, sum) and its value for d; the factors exp(max_split - max_all) are cheap to recompute
     for (int e = threadIdx.x; e < n_heads * head_dim; e += (NW * 32)) {
         const int gi = e / head_dim, d = e % head_dim;
-        const float* base = scratch + ((size_t)b * n_q + h0 + gi) * n_splits * (head_dim + 2) + d;
-        float a = 0.f;
-        int sp = 0;
-        for (; sp + 4 <= n_splits; sp += 4) {
-            const float v0 = __ldcg(base + (size_t)(sp + 0) * (head_dim + 2));
-            const float v1 = __ldcg(base + (size_t)(sp + 1) * (head_dim + 2));
-            const float v2 = __ldcg(base + (size_t)(sp + 2) * (head_dim + 2));
-            const float v3 = __ldcg(base + (size_t)(sp + 3) * (head_dim + 2));
-            a = fmaf(v0, sm_f[gi][sp], a); a = fmaf(v1, sm_f[gi][sp + 1], a);
-            a = fmaf(v2, sm_f[gi][sp + 2], a); a = fmaf(v3, sm_f[gi][sp + 3], a);
+        const float* base = scratch + ((size_t)b * n_q + h0 + gi) * n_splits * (head_dim + 2);
+        float mm = -INFINITY, ll = 0.f, a = 0.f;
+        for (int s0 = 0; s0 < n_splits; s0 += 8) {
+            float pm[8], pl[8], pv[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const bool live = s0 + i < n_splits;
+                const float* part = base + (size_t)(live ? s0 + i : s0) * (head_dim + 2);
+                pm[i] = live ? __ldcg(part + head_dim) : -INFINITY;
+                pl[i] = __ldcg(part + head_dim + 1);
+                pv[i] = __ldcg(part + d);
+            }
+            float m_new = mm;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) m_new = fmaxf(m_new, pm[i]);
+            const float keep = (mm == -INFINITY) ? 0.f : __expf(mm - m_new);
+            ll *= keep; a *= keep;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float f = (pm[i] == -INFINITY) ? 0.f : __expf(pm[i] - m_new);
+                ll = fmaf(pl[i], f, ll);
+                a = fmaf(pv[i], f, a);
+            }
+            mm = m_new;
         }
-        for (; sp < n_splits; ++sp) a = fmaf(__ldcg(base + (size_t)sp * (head_dim + 2)), sm_f[gi][sp], a);
-        const float ll = sm_L[gi];
         out[(size_t)b * ldo + (size_t)(h0 + gi) * head_dim + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
     }
 }
