@@ -1,4 +1,4 @@
-// Vector versions of the two element-wise kernels that matter in prefill, for bfloat16 activations:
+// Element-wise kernels with 16-byte accesses for bfloat16 activations:
 // RMSNorm of the float32 residual stream (16-byte loads, the row kept in registers between the sum
 // of squares and the scaling) and rotary encoding + paged cache append (bfloat16 pairs, 16-byte
 // copies of the values, one page lookup per token and kv head).  Same arithmetic and the same
@@ -67,6 +67,40 @@ SSB_API int ssb_rmsnorm_vec(const float* x, const int* rows, const void* w, int 
         : ssb_launch(rmsnorm_vec_kernel<RV_, bf16>, dim3(n_rows), dim3(RN_THREADS), 0, stream, pdl != 0, x, rows, (const bf16*)w, eps, (bf16*)out, hidden)
     if (rv <= 1) SSB_RV(1); else if (rv <= 2) SSB_RV(2); else if (rv <= 4) SSB_RV(4); else SSB_RV(8);
 #undef SSB_RV
+    return rc ? rc : ssb_launch_status();
+}
+
+// ---- round a float32 sum to bfloat16 and clear it ---------------------------------------------
+// A projection whose K range is split over blocks that add with float atomics leaves float32 sums
+// in a scratch that was zero before; this writes them out as bfloat16 and zeroes the scratch for
+// the next projection that uses it.  8 elements a thread.
+__global__ void __launch_bounds__(256)
+round_and_clear_kernel(float* __restrict__ sums, bf16* __restrict__ out, int ldo, int n_rows, int n_cols) {
+    ssb_pdl_launch_dependents();
+    ssb_pdl_wait();
+    const int per_row = n_cols / 8;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)n_rows * per_row) return;
+    const int r = (int)(i / per_row), c = (int)(i % per_row) * 8;
+    float4* src = reinterpret_cast<float4*>(sums + (size_t)r * n_cols + c);
+    const float4 a = src[0], b = src[1];
+    src[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    src[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+    uint4 v;
+    v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+    v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+    *reinterpret_cast<uint4*>(out + (size_t)r * ldo + c) = v;
+}
+
+// sums: float32 [n_rows, n_cols] contiguous (left zero); out: bfloat16 [n_rows, n_cols], row stride ldo.
+SSB_API int ssb_round_and_clear(float* sums, void* out, int ldo, int n_rows, int n_cols, int pdl, cudaStream_t stream) {
+    if (n_rows <= 0 || n_cols <= 0) return 0;
+    if (n_cols % 8 || ldo % 8 || (((uintptr_t)sums | (uintptr_t)out) & 15)) return SSB_ERR_BAD_SIZE;
+    const long long n = (long long)n_rows * (n_cols / 8);
+    const int rc = ssb_launch(round_and_clear_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, pdl != 0,
+                              sums, (bf16*)out, ldo, n_rows, n_cols);
     return rc ? rc : ssb_launch_status();
 }
 

@@ -97,6 +97,13 @@ class FastKernels(PlainKernels):
                             partials=self._buffer("gemv_partials", nf, torch.float32, out.device),
                             counters=self._buffer("gemv_counters", nc, torch.int32, out.device, zero=True),
                             pdl=self.pdl)
+            elif rows <= 64 and out.dtype == torch.bfloat16 and n % 8 == 0 and out.stride(0) % 8 == 0:
+                # too few row tiles for the SMs (48 for the 8B query/key/value projection): K is split
+                # over blocks that add with float atomics into a float32 scratch that is zero between
+                # uses; a small kernel rounds the sums into ``out`` and clears the scratch again
+                sums = self._buffer("split_sums", rows * n, torch.float32, out.device, zero=True)[: rows * n].view(rows, n)
+                ops.gemv_tc(x, weight, sums, ops.TC_ACCUMULATE, splits=ops.gemv_tc_splits(n, k), pdl=self.pdl)
+                ops.round_and_clear(sums, out, pdl=self.pdl)
             else:
                 ops.gemm_tc(x, weight, out, ops.TC_ACCUMULATE if accumulate else ops.TC_STORE,
                             tile_n=self._tile_n(rows, n))

@@ -531,6 +531,16 @@ def rmsnorm_vec(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Te
         c_int(x.shape[1]), c_int(1 if pdl else 0), _stream()), "rmsnorm_vec")
 
 
+def round_and_clear(sums: torch.Tensor, out: torch.Tensor, pdl: bool = False) -> None:
+    """out (bfloat16) = sums (float32, contiguous, same shape) rounded; sums is left zero."""
+    _need(sums, "sums", torch.float32, 2); _need(out, "out", torch.bfloat16, 2)
+    if sums.shape != out.shape or not sums.is_contiguous() or sums.shape[1] % 8:
+        raise KernelError(f"round_and_clear: shapes sums{tuple(sums.shape)} out{tuple(out.shape)}")
+    _check(_fn("elementwise_ops", "ssb_round_and_clear")(
+        _ptr(sums), _ptr(out), c_int(out.stride(0)), c_int(sums.shape[0]), c_int(sums.shape[1]),
+        c_int(1 if pdl else 0), _stream()), "round_and_clear")
+
+
 def rope_append_vec_ok(qkv: torch.Tensor, cos, head_dim: int, rotary_dim: int, write_cache: bool) -> bool:
     return (qkv.dtype == torch.bfloat16 and cos is not None and write_cache and rotary_dim == head_dim
             and head_dim % 8 == 0 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0)

@@ -393,6 +393,36 @@ def test_attention_decode(n_q, n_kv, hd, window, n_splits, kind):
     torch.testing.assert_close(out.float(), plain.float(), atol=1e-2, rtol=1e-2)
 
 
+def test_round_and_clear():
+    g = torch.Generator(device=DEV).manual_seed(33)
+    sums = torch.randn(37, 264, device=DEV, generator=g)
+    want = sums.bfloat16()
+    wide = torch.full((37, 272), 3.0, dtype=torch.bfloat16, device=DEV)
+    ops().round_and_clear(sums, wide[:, :264])
+    assert torch.equal(wide[:, :264], want) and torch.all(wide[:, 264:] == 3.0) and torch.all(sums == 0)
+
+
+@pytest.mark.parametrize("rows", [8, 12, 16, 17, 40, 64, 65])
+@pytest.mark.parametrize("N,K", [(6144, 4096), (1000, 1088)])
+def test_fast_linear_picks_a_kernel_for_every_row_count(rows, N, K):
+    """The bfloat16 kernel set's projection at row counts on both sides of every threshold: stored
+    as bfloat16, and added into a float32 residual; twice in a row (scratch is left as it was found)."""
+    from supersonic_b200.csrc.fast_sets import FastKernels
+    ks = FastKernels()
+    g = torch.Generator(device=DEV).manual_seed(34)
+    x = torch.randn(rows, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    ref = x.double() @ w.double().T
+    for _ in range(2):
+        out = torch.empty(rows, N, dtype=torch.bfloat16, device=DEV)
+        ks.linear(x, w, out)
+        torch.testing.assert_close(out.double(), ref, atol=2e-2, rtol=2e-2)
+        res = torch.full((rows, N), 2.0, device=DEV)
+        ks.linear(x, w, res, accumulate=True)
+        torch.testing.assert_close(res.double(), ref + 2, atol=2e-3, rtol=1e-3)
+    ops().check_device_errors()
+
+
 # ---- prefill GEMM on tcgen05 ------------------------------------------------------------------
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (65, 128, 200), (200, 304, 72), (300, 1000, 4096),
                                    (1024, 512, 1024), (129, 8, 64)])
