@@ -16,8 +16,12 @@ from .kernel_sets import NormedInput, PlainKernels, as_tensor
 FUSED_NORM_MAX_ROWS = 0        # measured: a separate norm launch is faster than the folded one at every batch size
 PREFETCH_BYTES = 64 << 20     # weights pulled into L2 during decode attention (L2 holds 126 MB)
 PREFETCH_MAX_ROWS = 0         # off: measured no gain (the projections are issue-bound, not DRAM-bound)
-SKINNY_MAX_ROWS = 8           # above this the tcgen05 kernels stream the weights faster (measured)
+SKINNY_MAX_ROWS = 0           # rows up to which the mma.sync skinny GEMM is tried first: none; the tcgen05 kernels stream the
+                              # weights faster at every row count once the tensor-core attention runs beside them (measured:
+                              # 3.42 against 3.64 ms a step at batch 8, 3.27 against 3.29 at batch 1); it remains the kernel
+                              # for shapes they refuse
 TARGET_BLOCKS = 1184           # eight small blocks per SM
+MMA_PAGES_PER_SPLIT = 4       # decode attention on the tensor cores: at least this many pages a block (2, 4, 8 measured)
 TC_ATTENTION_MIN_NEW = 96     # prompts at least this long take the tcgen05 attention (tiles of 128 rows)
 
 
@@ -87,20 +91,12 @@ class FastKernels(PlainKernels):
                 ops.gemv_tc(x, weight, out, ops.TC_ACCUMULATE, splits=ops.gemv_tc_splits(n, k), pdl=self.pdl)
             elif rows <= 64 and n >= 16384:
                 ops.gemv_tc(x, weight, out, ops.TC_STORE, pdl=self.pdl)
-            elif rows <= 16:
-                # few row tiles: blocks share a tile's K range and the last one sums their parts in
-                # order (14 us against 23 us for the 8B query/key/value projection at 16 rows; at 64
-                # rows the parts cost more than the narrow-tile GEMM)
-                splits = ops.gemv_tc_splits(n, k)
-                nf, nc = ops.gemv_tc_scratch(rows, n, splits)
-                ops.gemv_tc(x, weight, out, ops.TC_STORE, splits=splits,
-                            partials=self._buffer("gemv_partials", nf, torch.float32, out.device),
-                            counters=self._buffer("gemv_counters", nc, torch.int32, out.device, zero=True),
-                            pdl=self.pdl)
             elif rows <= 64 and out.dtype == torch.bfloat16 and n % 8 == 0 and out.stride(0) % 8 == 0:
                 # too few row tiles for the SMs (48 for the 8B query/key/value projection): K is split
                 # over blocks that add with float atomics into a float32 scratch that is zero between
                 # uses; a small kernel rounds the sums into ``out`` and clears the scratch again
+                # (batch 64: 22 us of a layer became 11; the ordered sum of parts through scratch
+                # that gemv_tc also offers is slower from 9 rows on)
                 sums = self._buffer("split_sums", rows * n, torch.float32, out.device, zero=True)[: rows * n].view(rows, n)
                 ops.gemv_tc(x, weight, sums, ops.TC_ACCUMULATE, splits=ops.gemv_tc_splits(n, k), pdl=self.pdl)
                 ops.round_and_clear(sums, out, pdl=self.pdl)
@@ -168,13 +164,13 @@ class FastKernels(PlainKernels):
         if window:
             pages = min(pages, (window >> page_shift) + 2)
         kind = 1
-        if head_dim in (64, 128) and group <= 16 and page_shift == 6 and (batch.n_seqs >= 32 or pages >= 32):
-            # tensor-core kernel (many sequences or long contexts): a block streams pages back to
-            # back; at least 8 pages a split, about two blocks per SM.  Alone it is the faster kernel
-            # at every batch size, but inside a step of few sequences its 64 KB of shared memory
-            # cost the neighbouring projections more than it saves (measured at batch 1 and 8).
+        if head_dim in (64, 128) and group <= 16 and page_shift == 6:
+            # tensor-core kernel: a block streams pages back to back; a few pages a split, about two
+            # blocks per SM.  Beside the mma.sync skinny GEMM it made a step slower (the two compete
+            # for the SM's L1/shared memory); beside the tcgen05 projections it is the faster choice
+            # at every batch size (batch 16: 4.24 to 3.57 ms a step, batch 8: 3.64 to 3.42).
             kind = 2
-            n_splits = max(1, min(296 // (batch.n_seqs * n_kv), pages // 8, 64))
+            n_splits = max(1, min(296 // (batch.n_seqs * n_kv), pages // MMA_PAGES_PER_SPLIT, 64))
         elif batch.n_seqs <= 2:
             n_splits = max(1, min(TARGET_BLOCKS // blocks, pages, 16))    # latency-bound: a page a block
         elif pages < 32:
