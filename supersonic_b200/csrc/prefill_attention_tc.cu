@@ -2,18 +2,18 @@
 // attention of a ragged batch of new tokens over the paged cache.
 //
 // One block works on two tiles of 128 query rows that share a key/value head (two query heads of
-// the group over the same rows, or neighbouring row tiles), so a page of keys and values is
-// fetched once for 256 rows.  Warp 0 feeds TMA: the two query tiles once, then a page of keys and
-// a page of values per turn into a ring (128-byte swizzle).  Warp 1 issues tcgen05.mma: per tile
-// S = Q K^T (M 128, N 64, K 128) into one of two regions of tensor memory, two blocks ahead of the
-// softmax, and O += P V (M 128, N 128, K 64) with P read from tensor memory, where the softmax
-// wrote it over S, and V read MN-major from the page as it lies in the cache.  Warps 2-5 and 6-9 own one query row of the first and second tile per thread:
-// scores come with tcgen05.ld, are masked on the diagonal only, and leave as bfloat16
-// probabilities with tcgen05.st.  O stays in tensor memory for the whole row of blocks: a row's
-// reference maximum moves only when the true maximum has grown by more than 2^8, and only then is
-// O rescaled (tcgen05.ld, multiply, tcgen05.st); the sum uses the same reference, so the quotient
-// is the exact softmax.  While one tile's rows are in the softmax the tensor cores work on the
-// other tile.  Every mbarrier wait is bounded.
+// the group over the same rows, or neighbouring row tiles), so keys and values are fetched once
+// for 256 rows.  Warp 0 feeds TMA: the two query tiles once, then two pages (128 keys) of keys
+// and of values per turn into a two-stage ring (128-byte swizzle).  Warp 1 issues tcgen05.mma: per
+// tile S = Q K^T (M 128, N 128, K 128) into tensor memory, and O += P V (M 128, N 128, K 128) with P
+// read from tensor memory, where the softmax wrote it over S, and V read MN-major from the pages as
+// they lie in the cache.  Warps 2-5 and 6-9 own one query row of the first and second tile per
+// thread: scores come with tcgen05.ld, are masked
+// on the diagonal only, and leave as bfloat16 probabilities with tcgen05.st.  O stays in tensor
+// memory for the whole row of blocks: a row's reference maximum moves only when the true maximum
+// has grown by more than 2^8, and only then is O rescaled (tcgen05.ld, multiply, tcgen05.st); the
+// sum uses the same reference, so the quotient is the exact softmax.  While one tile's rows are in
+// the softmax the tensor cores work on the other tile.  Every mbarrier wait is bounded.
 //
 // Same arithmetic as prefill_attention.cu (mma.sync), which stays as the kernel for head_dim 64
 // and as this one's reference.  Replaces supersonic_qwen35_full_attention_prefill_kernel of the
@@ -26,16 +26,16 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int FT_HD = 128;
 constexpr int FT_BM = 128;                 // query rows per tile
-constexpr int FT_BN = 64;                  // keys per turn = one cache page
-constexpr int FT_STAGES = 4;
+constexpr int FT_BN = 128;                 // keys per turn = two cache pages
+constexpr int FT_STAGES = 2;
 constexpr int FT_THREADS = 320;
 constexpr uint32_t FT_Q_BYTES = FT_BM * FT_HD * 2;          // 32 KB: two 64-column boxes
-constexpr uint32_t FT_PAGE_BYTES = FT_BN * FT_HD * 2;       // 16 KB: two 64-column boxes
+constexpr uint32_t FT_PAGE_BYTES = 64 * FT_HD * 2;          // 16 KB: two 64-column boxes
+constexpr uint32_t FT_KV_BYTES = 2 * FT_PAGE_BYTES;         // keys (or values) of a turn
 constexpr float FT_LAZY = 8.f;             // log2 of how far a probability may exceed 1
-// tensor-memory columns of tile x: two regions of scores / probabilities at 128 x and 128 x + 64,
-// output at 256 + 128 x
+// tensor-memory columns of tile x: scores, later probabilities, at 128 x; output at 256 + 128 x
 constexpr uint32_t FT_S0 = 0, FT_O0 = 256;
-constexpr int FT_NBARS = 1 + 3 * FT_STAGES + 12;
+constexpr int FT_NBARS = 1 + 3 * FT_STAGES + 6;
 
 __device__ __forceinline__ void mbar_arrive_cta(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -90,13 +90,14 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = smem;                                   // two tiles of 32 KB
-    unsigned char* kv_s = smem + 2 * FT_Q_BYTES;                 // stages of [K page | V page]
-    uint64_t* bars = (uint64_t*)(kv_s + FT_STAGES * 2 * FT_PAGE_BYTES);
-    // q_full, k_full[S], v_full[S], kv_empty[S], s_full, p_full, o_full: [tile][block & 1] each, so that a role that
-    // runs a block ahead never meets a barrier two phases on
+    unsigned char* kv_s = smem + 2 * FT_Q_BYTES;                 // stages of [keys of two pages | values of two pages]
+    uint64_t* bars = (uint64_t*)(kv_s + FT_STAGES * 2 * FT_KV_BYTES);
+    // q_full, k_full[S], v_full[S], kv_empty[S], s_full[tile], p_full[tile], o_full[tile]: the scores of a
+    // tile's next block are issued only after its probabilities were handed over, so no role ever
+    // meets a barrier two phases on
     const uint32_t q_full = smem_u32(bars), k_full0 = q_full + 8, v_full0 = k_full0 + 8 * FT_STAGES,
-                   kv_empty0 = v_full0 + 8 * FT_STAGES, s_full0 = kv_empty0 + 8 * FT_STAGES, p_full0 = s_full0 + 32,
-                   o_full0 = p_full0 + 32;
+                   kv_empty0 = v_full0 + 8 * FT_STAGES, s_full0 = kv_empty0 + 8 * FT_STAGES, p_full0 = s_full0 + 16,
+                   o_full0 = p_full0 + 16;
     uint32_t* tmem_slot = (uint32_t*)(bars + FT_NBARS);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);   // [0]: a role gave up; [1]: stays zero
 
@@ -126,9 +127,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     const int p_first = t_p0[0];                                 // tile 0 is never the later one
     const int kb_lo = (window > 0 && p_first - window + 1 > 0) ? (p_first - window + 1) >> 6 : 0;
-    int nb[2];
-    nb[0] = (t_last[0] >> 6) - kb_lo + 1;
-    nb[1] = t_rows[1] > 0 ? (t_last[1] >> 6) - kb_lo + 1 : 0;
+    int nb[2];                                                   // turns of two pages, from page kb_lo on
+    nb[0] = ((t_last[0] >> 6) - kb_lo + 2) >> 1;
+    nb[1] = t_rows[1] > 0 ? ((t_last[1] >> 6) - kb_lo + 2) >> 1 : 0;
+    const int last_page = (start + n_new - 1) >> 6;              // the last page the sequence holds
     const int nb_max = max(nb[0], nb[1]);
     const int* pt = page_table + (size_t)slot * max_pages;
 
@@ -137,7 +139,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int s = 0; s < FT_STAGES; ++s) {
             mbar_init(k_full0 + 8 * s, 1); mbar_init(v_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1);
         }
-        for (int i = 0; i < 4; ++i) { mbar_init(s_full0 + 8 * i, 1); mbar_init(p_full0 + 8 * i, 4); mbar_init(o_full0 + 8 * i, 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(s_full0 + 8 * i, 1); mbar_init(p_full0 + 8 * i, 4); mbar_init(o_full0 + 8 * i, 1); }
         abort_flag[0] = 0;
         abort_flag[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -167,14 +169,20 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (!mbar_wait(kv_empty0 + 8 * s, ((j / FT_STAGES) & 1) ^ 1, abort_flag)) {
                     *abort_flag = 1; atomicCAS(error_word, 0, TC_ERR_PRODUCER); break;
                 }
-                const int y = (pt[kb_lo + j] * n_kv + kvh) * FT_BN;       // first row of the page in the 2-D view
-                const uint32_t k_dst = smem_u32(kv_s + s * 2 * FT_PAGE_BYTES), v_dst = k_dst + FT_PAGE_BYTES;
-                mbar_expect_tx(k_full0 + 8 * s, FT_PAGE_BYTES);
-                tma_load_2d(k_dst, &map_k, k_full0 + 8 * s, 0, y);
-                tma_load_2d(k_dst + FT_PAGE_BYTES / 2, &map_k, k_full0 + 8 * s, 64, y);
-                mbar_expect_tx(v_full0 + 8 * s, FT_PAGE_BYTES);
-                tma_load_2d(v_dst, &map_v, v_full0 + 8 * s, 0, y);
-                tma_load_2d(v_dst + FT_PAGE_BYTES / 2, &map_v, v_full0 + 8 * s, 64, y);
+                // keys: [dim half][page][64 keys x 128 bytes], a K-major tile of 128 rows per half;
+                // values: [page][dim half][64 keys x 128 bytes].  A page past the sequence's last one
+                // (odd page counts) is the last one again: its keys lie beyond every query and are masked.
+                const uint32_t k_dst = smem_u32(kv_s + s * 2 * FT_KV_BYTES), v_dst = k_dst + FT_KV_BYTES;
+                mbar_expect_tx(k_full0 + 8 * s, FT_KV_BYTES);
+                mbar_expect_tx(v_full0 + 8 * s, FT_KV_BYTES);
+#pragma unroll
+                for (int pg = 0; pg < 2; ++pg) {
+                    const int y = (pt[min(kb_lo + 2 * j + pg, last_page)] * n_kv + kvh) * 64;   // first row of the page in the 2-D view
+                    tma_load_2d(k_dst + pg * (FT_PAGE_BYTES / 2), &map_k, k_full0 + 8 * s, 0, y);
+                    tma_load_2d(k_dst + FT_KV_BYTES / 2 + pg * (FT_PAGE_BYTES / 2), &map_k, k_full0 + 8 * s, 64, y);
+                    tma_load_2d(v_dst + pg * FT_PAGE_BYTES, &map_v, v_full0 + 8 * s, 0, y);
+                    tma_load_2d(v_dst + pg * FT_PAGE_BYTES + FT_PAGE_BYTES / 2, &map_v, v_full0 + 8 * s, 64, y);
+                }
                 issued = j + 1;
             }
             if (*abort_flag) {                                   // let issued copies land
@@ -187,47 +195,44 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // S: D float32, A and B bfloat16 K-major, M 128, N 64.  PV: B MN-major (bit 16), N 128.
+            // S: D float32, A and B bfloat16 K-major, M 128, N 128.  PV: B MN-major (bit 16), N 128.
             const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FT_BN >> 3) << 17) | ((uint32_t)(FT_BM >> 4) << 24);
             const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(FT_HD >> 3) << 17) | ((uint32_t)(FT_BM >> 4) << 24);
             bool ok = mbar_wait(q_full, 0, abort_flag);
             const uint64_t q_desc = smem_desc(smem_u32(q_s)), k_desc = smem_desc(smem_u32(kv_s));
-            const uint64_t v_desc = smem_desc_mn(smem_u32(kv_s) + FT_PAGE_BYTES);
-            auto issue_s = [&](int x, int j) -> bool {           // scores of block j of tile x, into region j & 1
+            const uint64_t v_desc = smem_desc_mn(smem_u32(kv_s) + FT_KV_BYTES);
+            auto issue_s = [&](int x, int j) -> bool {           // scores of block j of tile x
                 const int s = j % FT_STAGES;
                 if (!mbar_wait(k_full0 + 8 * s, (j / FT_STAGES) & 1, abort_flag)) return false;
                 tc_fence_after();
                 const uint64_t da = q_desc + (uint64_t)(x * (FT_Q_BYTES >> 4));
-                const uint64_t db = k_desc + (uint64_t)(s * (2 * FT_PAGE_BYTES >> 4));
-                const uint32_t d = tmem + FT_S0 + x * 128 + (j & 1) * FT_BN;
+                const uint64_t db = k_desc + (uint64_t)(s * (2 * FT_KV_BYTES >> 4));
 #pragma unroll
                 for (int ks = 0; ks < FT_HD / 16; ++ks)          // descriptors count in units of 16 bytes
-                    tc_mma(d, da + (ks / 4) * (FT_Q_BYTES / 2 >> 4) + 2 * (ks % 4),
-                           db + (ks / 4) * (FT_PAGE_BYTES / 2 >> 4) + 2 * (ks % 4), idesc_s, ks ? 1u : 0u);
-                tc_commit(s_full0 + 8 * (2 * x + (j & 1)));
+                    tc_mma(tmem + FT_S0 + x * FT_BN, da + (ks / 4) * (FT_Q_BYTES / 2 >> 4) + 2 * (ks % 4),
+                           db + (ks / 4) * (FT_KV_BYTES / 2 >> 4) + 2 * (ks % 4), idesc_s, ks ? 1u : 0u);
+                tc_commit(s_full0 + 8 * x);
                 return true;
             };
-            for (int j = 0; j < 2; ++j)                          // scores run two blocks ahead of the values
-                for (int x = 0; x < 2 && ok; ++x)
-                    if (j < nb[x]) ok = issue_s(x, j);
+            for (int x = 0; x < 2 && ok; ++x)
+                if (nb[x] > 0) ok = issue_s(x, 0);
             for (int j = 0; j < nb_max && ok; ++j) {
                 const int s = j % FT_STAGES;
                 for (int x = 0; x < 2 && ok; ++x) {
                     if (j >= nb[x]) continue;
-                    // the softmax may be a block ahead: a barrier for each region keeps the phases apart
-                    if (!mbar_wait(p_full0 + 8 * (2 * x + (j & 1)), (j >> 1) & 1, abort_flag) ||
+                    if (!mbar_wait(p_full0 + 8 * x, j & 1, abort_flag) ||
                         !mbar_wait(v_full0 + 8 * s, (j / FT_STAGES) & 1, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t dv = v_desc + (uint64_t)(s * (2 * FT_PAGE_BYTES >> 4));
-                    const uint32_t p_at = tmem + FT_S0 + x * 128 + (j & 1) * FT_BN;
+                    const uint64_t dv = v_desc + (uint64_t)(s * (2 * FT_KV_BYTES >> 4));
 #pragma unroll
-                    for (int ks = 0; ks < FT_BN / 16; ++ks)      // 16 keys = 16 rows of 128 bytes further down
-                        tc_mma_ts(tmem + FT_O0 + x * FT_HD, p_at + ks * 8, dv + ks * (16 * 128 >> 4), idesc_o,
+                    for (int ks = 0; ks < FT_BN / 16; ++ks)      // 16 keys: 16 rows of 128 bytes further down, a page every four
+                        tc_mma_ts(tmem + FT_O0 + x * FT_HD, tmem + FT_S0 + x * FT_BN + ks * 8,
+                                  dv + (ks / 4) * (FT_PAGE_BYTES >> 4) + (ks % 4) * (16 * 128 >> 4), idesc_o,
                                   (j > 0 || ks > 0) ? 1u : 0u);
-                    tc_commit(o_full0 + 8 * (2 * x + (j & 1)));
-                    // the scores after next go where these probabilities lie: the tensor cores
-                    // take their work in the order of issue
-                    if (j + 2 < nb[x]) ok = issue_s(x, j + 2);
+                    tc_commit(o_full0 + 8 * x);
+                    // the next scores go where these probabilities lie: the tensor cores take
+                    // their work in the order of issue
+                    if (j + 1 < nb[x]) ok = issue_s(x, j + 1);
                 }
                 tc_commit(kv_empty0 + 8 * s);
             }
@@ -242,25 +247,26 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const int r = quarter * 32 + lane;
             const int p0 = t_p0[x];
             const int pos = p0 + r;
-            const uint32_t t_s0 = tmem + ((uint32_t)(quarter * 32) << 16) + FT_S0 + x * 128;
+            const uint32_t t_s = tmem + ((uint32_t)(quarter * 32) << 16) + FT_S0 + x * FT_BN;
             const uint32_t t_o = tmem + ((uint32_t)(quarter * 32) << 16) + FT_O0 + x * FT_HD;
-            const uint32_t s_full = s_full0 + 16 * x, p_full = p_full0 + 16 * x, o_full = o_full0 + 16 * x;
+            const uint32_t s_full = s_full0 + 8 * x, p_full = p_full0 + 8 * x, o_full = o_full0 + 8 * x;
             float m_ref = -INFINITY, l_run = 0.f;
             bool ok = true;
             for (int j = 0; j < n_mine; ++j) {
-                const uint32_t t_s = t_s0 + (j & 1) * FT_BN;
-                bool w = mbar_wait(s_full + 8 * (j & 1), (j >> 1) & 1, abort_flag);
+                bool w = mbar_wait(s_full, j & 1, abort_flag);
                 w = __all_sync(0xffffffffu, w);
                 if (!w) { ok = false; break; }
                 tc_fence_after();
+                const int key0 = (kb_lo + 2 * j) * 64;
+                const bool edge = key0 + FT_BN - 1 > p0 || window > 0;   // on the diagonal or at a window's edge
+                const int hi = pos - key0;                       // keys 0..hi of the block are seen
+                const int lo = window > 0 ? hi - window + 1 : 0;
+                // the row's 128 scores in registers: four loads in flight, one wait
                 uint32_t raw[FT_BN];
-                tc_ld32_issue(t_s, raw);
-                tc_ld32_issue(t_s + 32, raw + 32);
+#pragma unroll
+                for (int c = 0; c < FT_BN / 32; ++c) tc_ld32_issue(t_s + c * 32, raw + c * 32);
                 tc_ld_wait();
-                const int key0 = (kb_lo + j) * FT_BN;
-                if (key0 + FT_BN - 1 > p0 || window > 0) {       // on the diagonal or at a window's edge
-                    const int hi = pos - key0;                   // keys 0..hi of the block are seen
-                    const int lo = window > 0 ? hi - window + 1 : 0;
+                if (edge) {
 #pragma unroll
                     for (int i = 0; i < FT_BN; ++i)
                         if (i > hi || i < lo) raw[i] = 0xff800000u;
@@ -274,12 +280,12 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     m_ref = m_new;
                 } else if (__any_sync(0xffffffffu, m_new > m_ref + FT_LAZY)) {
                     // the maximum has grown too far for this warp's rows: rescale what is summed so far
-                    bool wo = mbar_wait(o_full + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag);
+                    bool wo = mbar_wait(o_full, (j - 1) & 1, abort_flag);
                     wo = __all_sync(0xffffffffu, wo);
                     if (!wo) { ok = false; break; }
                     tc_fence_after();
                     const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m_ref - m_new);
-#pragma unroll
+#pragma unroll 1
                     for (int c = 0; c < FT_HD / 32; ++c) {
                         uint32_t o[32];
                         tc_ld32_issue(t_o + c * 32, o);
@@ -291,26 +297,30 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     l_run *= alpha;
                     m_ref = m_new;
                 }
+                // exponentials; the probabilities of 64 keys go over the scores of 32 keys (all are in registers)
                 const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
                 float sum[4] = {0.f, 0.f, 0.f, 0.f};
-                uint32_t packed[FT_BN / 2];
 #pragma unroll
-                for (int i = 0; i < FT_BN; i += 2) {
-                    const float pa = ex2(fmaf(__uint_as_float(raw[i]), scale_log2, neg_m));
-                    const float pb = ex2(fmaf(__uint_as_float(raw[i + 1]), scale_log2, neg_m));
-                    sum[(i >> 1) & 3] += pa + pb;
-                    __nv_bfloat162 v = __floats2bfloat162_rn(pa, pb);
-                    packed[i / 2] = *reinterpret_cast<uint32_t*>(&v);
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t packed[32];
+#pragma unroll
+                    for (int i = 0; i < 64; i += 2) {
+                        const float pa = ex2(fmaf(__uint_as_float(raw[half * 64 + i]), scale_log2, neg_m));
+                        const float pb = ex2(fmaf(__uint_as_float(raw[half * 64 + i + 1]), scale_log2, neg_m));
+                        sum[(i >> 1) & 3] += pa + pb;
+                        __nv_bfloat162 v = __floats2bfloat162_rn(pa, pb);
+                        packed[i / 2] = *reinterpret_cast<uint32_t*>(&v);
+                    }
+                    tc_st32(t_s + half * 32, packed);
                 }
-                tc_st32(t_s, packed);
                 tc_st_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cta(p_full + 8 * (j & 1));
+                if (lane == 0) mbar_arrive_cta(p_full);
                 l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             }
             if (ok) {
-                bool w = mbar_wait(o_full + 8 * ((n_mine - 1) & 1), ((n_mine - 1) >> 1) & 1, abort_flag);
+                bool w = mbar_wait(o_full, (n_mine - 1) & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, w);
             }
             if (!ok) {
@@ -363,13 +373,13 @@ SSB_API int ssb_attention_prefill_tc(const void* q, int ldq, int n_rows_q, const
     CUtensorMap mq, mk, mv;
     int rc = make_map(&mq, q, n_rows_q, n_q * head_dim, ldq, FT_BM);
     if (rc) return rc;
-    const long long cache_rows = (long long)n_pages * n_kv * FT_BN;
+    const long long cache_rows = (long long)n_pages * n_kv * 64;
     if (cache_rows > 0x7fffffffLL) return SSB_ERR_BAD_SIZE;
-    rc = make_map(&mk, k_cache, (int)cache_rows, head_dim, head_dim, FT_BN);
+    rc = make_map(&mk, k_cache, (int)cache_rows, head_dim, head_dim, 64);
     if (rc) return rc;
-    rc = make_map(&mv, v_cache, (int)cache_rows, head_dim, head_dim, FT_BN);
+    rc = make_map(&mv, v_cache, (int)cache_rows, head_dim, head_dim, 64);
     if (rc) return rc;
-    constexpr size_t smem = 2 * FT_Q_BYTES + FT_STAGES * 2 * FT_PAGE_BYTES + FT_NBARS * 8 + 32 + 1024;
+    constexpr size_t smem = 2 * FT_Q_BYTES + FT_STAGES * 2 * FT_KV_BYTES + FT_NBARS * 8 + 32 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
