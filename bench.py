@@ -125,12 +125,12 @@ def time_decode(model, batch, prompt_len, steps, warmup, seed=0):
             model.close_sequence(s)
 
 
-def time_prefill(model, tokens, reps=3, seed=1):
+def time_prefill(model, tokens, reps=5, warmup=3, seed=1):
     import torch
     from supersonic_b200.engine import StepEntry
     g = torch.Generator().manual_seed(seed)
     best = None
-    for r in range(reps + 1):
+    for r in range(reps + warmup):
         prompt = torch.randint(0, model.vocab_size, (tokens,), generator=g).tolist()
         slot = model.open_sequence()
         torch.cuda.synchronize()
@@ -140,7 +140,7 @@ def time_prefill(model, tokens, reps=3, seed=1):
         end.record()
         torch.cuda.synchronize()
         model.close_sequence(slot)
-        if r > 0:                                          # the first run is warm-up
+        if r >= warmup:                                    # the first runs are warm-up
             ms = start.elapsed_time(end)
             best = ms if best is None else min(best, ms)
     return best
