@@ -429,7 +429,7 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
 
 
 def attention_prefill_tc_ok(q: torch.Tensor, out: torch.Tensor, head_dim: int, page_shift: int) -> bool:
-    return (q.dtype == torch.bfloat16 and head_dim == 128 and page_shift == 6 and q.stride(0) % 8 == 0
+    return (q.dtype == torch.bfloat16 and head_dim in (64, 128) and page_shift == 6 and q.stride(0) % 8 == 0
             and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
 
 
@@ -438,7 +438,7 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          out: torch.Tensor, max_new: int, n_q: int, n_kv: int, head_dim: int, page_shift: int,
                          window: Optional[int], scale: float) -> None:
     """``attention_prefill`` on tcgen05: scores and probabilities in tensor memory, pages by TMA.
-    head_dim 128 and 64-token pages only.  A wait that runs out sets the device's error word
+    head_dim 64 or 128 and 64-token pages only.  A wait that runs out sets the device's error word
     (``check_device_errors``)."""
     _need(q, "q", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
     _need(k_cache, "k_cache", torch.bfloat16); _need(v_cache, "v_cache", torch.bfloat16)

@@ -1,11 +1,11 @@
-// Prefill attention on the fifth-generation tensor cores (head_dim 128): causal grouped-query
+// Prefill attention on the fifth-generation tensor cores (head_dim 64 or 128): causal grouped-query
 // attention of a ragged batch of new tokens over the paged cache.
 //
 // One block works on two tiles of 128 query rows that share a key/value head (two query heads of
 // the group over the same rows, or neighbouring row tiles), so keys and values are fetched once
 // for 256 rows.  Warp 0 feeds TMA: the two query tiles once, then two pages (128 keys) of keys
 // and of values per turn into a two-stage ring (128-byte swizzle).  Warp 1 issues tcgen05.mma: per
-// tile S = Q K^T (M 128, N 128, K 128) into tensor memory, and O += P V (M 128, N 128, K 128) with P
+// tile S = Q K^T (M 128, N 128, K head_dim) into tensor memory, and O += P V (M 128, N head_dim, K 128) with P
 // read from tensor memory, where the softmax wrote it over S, and V read MN-major from the pages as
 // they lie in the cache.  Warps 2-5 and 6-9 own one query row of the first and second tile per
 // thread: scores come with tcgen05.ld, are masked
@@ -15,7 +15,7 @@
 // sum uses the same reference, so the quotient is the exact softmax.  While one tile's rows are in
 // the softmax the tensor cores work on the other tile.  Every mbarrier wait is bounded.
 //
-// Same arithmetic as prefill_attention.cu (mma.sync), which stays as the kernel for head_dim 64
+// Same arithmetic as prefill_attention.cu (mma.sync), which stays as the kernel for short prompts
 // and as this one's reference.  Replaces supersonic_qwen35_full_attention_prefill_kernel of the
 // reference (kernels/full_attention_cuda.cuh:360-474).
 #include "common.cuh"
@@ -24,14 +24,10 @@
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int FT_HD = 128;
 constexpr int FT_BM = 128;                 // query rows per tile
 constexpr int FT_BN = 128;                 // keys per turn = two cache pages
 constexpr int FT_STAGES = 2;
 constexpr int FT_THREADS = 320;
-constexpr uint32_t FT_Q_BYTES = FT_BM * FT_HD * 2;          // 32 KB: two 64-column boxes
-constexpr uint32_t FT_PAGE_BYTES = 64 * FT_HD * 2;          // 16 KB: two 64-column boxes
-constexpr uint32_t FT_KV_BYTES = 2 * FT_PAGE_BYTES;         // keys (or values) of a turn
 constexpr float FT_LAZY = 8.f;             // log2 of how far a probability may exceed 1
 // tensor-memory columns of tile x: scores, later probabilities, at 128 x; output at 256 + 128 x
 constexpr uint32_t FT_S0 = 0, FT_O0 = 256;
@@ -81,12 +77,17 @@ __device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr) {
     return (uint64_t)((addr >> 4) & 0x3FFF) | (512ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
+template <int FT_HD>                       // head size: 64 or 128 (one or two 64-column boxes a row)
 __global__ void __launch_bounds__(FT_THREADS, 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ cu_new,
                             const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                             const int* __restrict__ page_table, int max_pages, bf16* __restrict__ out, int ldo,
                             int n_q, int n_kv, int window, float scale_log2, int* __restrict__ error_word) {
+    constexpr int HALVES = FT_HD / 64;                           // 64-column boxes a row
+    constexpr uint32_t FT_Q_BYTES = FT_BM * FT_HD * 2;           // a query tile
+    constexpr uint32_t FT_PAGE_BYTES = 64 * FT_HD * 2;           // a page of keys (or values) of one kv head
+    constexpr uint32_t FT_KV_BYTES = 2 * FT_PAGE_BYTES;          // keys (or values) of a turn
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = smem;                                   // two tiles of 32 KB
@@ -160,8 +161,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int x = 0; x < 2; ++x)
                 if (nb[x] > 0) {
-                    tma_load_2d(smem_u32(q_s) + x * FT_Q_BYTES, &map_q, q_full, t_head[x] * FT_HD, t_row[x]);
-                    tma_load_2d(smem_u32(q_s) + x * FT_Q_BYTES + FT_Q_BYTES / 2, &map_q, q_full, t_head[x] * FT_HD + 64, t_row[x]);
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h)
+                        tma_load_2d(smem_u32(q_s) + x * FT_Q_BYTES + h * (FT_Q_BYTES / HALVES), &map_q, q_full,
+                                    t_head[x] * FT_HD + 64 * h, t_row[x]);
                 }
             int issued = 0;
             for (int j = 0; j < nb_max; ++j) {
@@ -169,8 +172,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (!mbar_wait(kv_empty0 + 8 * s, ((j / FT_STAGES) & 1) ^ 1, abort_flag)) {
                     *abort_flag = 1; atomicCAS(error_word, 0, TC_ERR_PRODUCER); break;
                 }
-                // keys: [dim half][page][64 keys x 128 bytes], a K-major tile of 128 rows per half;
-                // values: [page][dim half][64 keys x 128 bytes].  A page past the sequence's last one
+                // keys: [64-column box][page][64 keys x 128 bytes], a K-major tile of 128 rows per box;
+                // values: [page][64-column box][64 keys x 128 bytes].  A page past the sequence's last one
                 // (odd page counts) is the last one again: its keys lie beyond every query and are masked.
                 const uint32_t k_dst = smem_u32(kv_s + s * 2 * FT_KV_BYTES), v_dst = k_dst + FT_KV_BYTES;
                 mbar_expect_tx(k_full0 + 8 * s, FT_KV_BYTES);
@@ -178,10 +181,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int pg = 0; pg < 2; ++pg) {
                     const int y = (pt[min(kb_lo + 2 * j + pg, last_page)] * n_kv + kvh) * 64;   // first row of the page in the 2-D view
-                    tma_load_2d(k_dst + pg * (FT_PAGE_BYTES / 2), &map_k, k_full0 + 8 * s, 0, y);
-                    tma_load_2d(k_dst + FT_KV_BYTES / 2 + pg * (FT_PAGE_BYTES / 2), &map_k, k_full0 + 8 * s, 64, y);
-                    tma_load_2d(v_dst + pg * FT_PAGE_BYTES, &map_v, v_full0 + 8 * s, 0, y);
-                    tma_load_2d(v_dst + pg * FT_PAGE_BYTES + FT_PAGE_BYTES / 2, &map_v, v_full0 + 8 * s, 64, y);
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h) {
+                        tma_load_2d(k_dst + h * (FT_KV_BYTES / HALVES) + pg * 8192, &map_k, k_full0 + 8 * s, 64 * h, y);
+                        tma_load_2d(v_dst + pg * FT_PAGE_BYTES + h * 8192, &map_v, v_full0 + 8 * s, 64 * h, y);
+                    }
                 }
                 issued = j + 1;
             }
@@ -209,8 +213,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const uint64_t db = k_desc + (uint64_t)(s * (2 * FT_KV_BYTES >> 4));
 #pragma unroll
                 for (int ks = 0; ks < FT_HD / 16; ++ks)          // descriptors count in units of 16 bytes
-                    tc_mma(tmem + FT_S0 + x * FT_BN, da + (ks / 4) * (FT_Q_BYTES / 2 >> 4) + 2 * (ks % 4),
-                           db + (ks / 4) * (FT_KV_BYTES / 2 >> 4) + 2 * (ks % 4), idesc_s, ks ? 1u : 0u);
+                    tc_mma(tmem + FT_S0 + x * FT_BN, da + (ks / 4) * (FT_Q_BYTES / HALVES >> 4) + 2 * (ks % 4),
+                           db + (ks / 4) * (FT_KV_BYTES / HALVES >> 4) + 2 * (ks % 4), idesc_s, ks ? 1u : 0u);
                 tc_commit(s_full0 + 8 * x);
                 return true;
             };
@@ -367,7 +371,7 @@ SSB_API int ssb_attention_prefill_tc(const void* q, int ldq, int n_rows_q, const
                                      int n_q, int n_kv, int head_dim, int page_shift, int window, float scale,
                                      int* error_word, cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
-    if (head_dim != FT_HD || page_shift != 6) return SSB_ERR_UNSUPPORTED;
+    if ((head_dim != 64 && head_dim != 128) || page_shift != 6) return SSB_ERR_UNSUPPORTED;
     if (n_kv <= 0 || n_q % n_kv || ldq % 8 || ldo % 8 || !error_word ) return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return SSB_ERR_BAD_SIZE;
     CUtensorMap mq, mk, mv;
@@ -379,19 +383,23 @@ SSB_API int ssb_attention_prefill_tc(const void* q, int ldq, int n_rows_q, const
     if (rc) return rc;
     rc = make_map(&mv, v_cache, (int)cache_rows, head_dim, head_dim, 64);
     if (rc) return rc;
-    constexpr size_t smem = 2 * FT_Q_BYTES + FT_STAGES * 2 * FT_KV_BYTES + FT_NBARS * 8 + 32 + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
     const int group = n_q / n_kv;
     const int pairs = (((max_new + FT_BM - 1) / FT_BM) * group + 1) / 2;
     if (pairs > 65535) return SSB_ERR_BAD_SIZE;
     dim3 grid(n_kv * n_seqs, pairs);
-    prefill_attention_tc_kernel<<<grid, FT_THREADS, smem, stream>>>(
-        mq, mk, mv, cu_new, seq_start, seq_slot, page_table, max_pages, (bf16*)out, ldo, n_q, n_kv, window,
-        scale * 1.4426950408889634f, error_word);
+#define SSB_FT(HD_) do { \
+        constexpr size_t smem = 2 * FT_BM * HD_ * 2 + FT_STAGES * 4 * 64 * HD_ * 2 + FT_NBARS * 8 + 32 + 1024; \
+        static bool configured = false; \
+        if (!configured) { \
+            cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<HD_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e; \
+            configured = true; \
+        } \
+        prefill_attention_tc_kernel<HD_><<<grid, FT_THREADS, smem, stream>>>( \
+            mq, mk, mv, cu_new, seq_start, seq_slot, page_table, max_pages, (bf16*)out, ldo, n_q, n_kv, window, \
+            scale * 1.4426950408889634f, error_word); \
+    } while (0)
+    if (head_dim == 64) SSB_FT(64); else SSB_FT(128);
+#undef SSB_FT
     return ssb_launch_status();
 }
