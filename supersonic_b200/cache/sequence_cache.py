@@ -75,9 +75,19 @@ class KvGroup:
             return 0
         return max(0, length - self.need.window + 1) >> PAGE_SHIFT
 
-    def reserve(self, slot: int, length: int, new_length: int) -> None:
+    def missing_pages(self, slot: int, length: int, new_length: int) -> List[int]:
+        """Pages that ``new_length`` tokens need and the slot does not hold yet.  A sequence that
+        already has tokens holds every page up to its last one (older ones may have been given
+        back by a window): only the last held page and those after it need a look, so a decode
+        step of a long sequence does not walk its whole page list."""
         first = self.first_needed_page(length)
-        want = [p for p in range(first, pages_for(new_length)) if p not in self.held[slot]]
+        if length > 0:
+            first = max(first, pages_for(length) - 1)
+        held = self.held[slot]
+        return [p for p in range(first, pages_for(new_length)) if p not in held]
+
+    def reserve(self, slot: int, length: int, new_length: int) -> None:
+        want = self.missing_pages(slot, length, new_length)
         if not want:
             return
         if pages_for(new_length) > self.pages_per_seq:
@@ -264,8 +274,7 @@ class SequenceCache:
             raise CacheFull(f"slot {slot}: {new_length} tokens exceed the {self.max_seq_tokens} "
                             "one sequence may hold")
         for g in self.kv_groups:
-            need = len([p for p in range(g.first_needed_page(length), pages_for(new_length))
-                        if p not in g.held[slot]])
+            need = len(g.missing_pages(slot, length, new_length))
             if need > g.pool.n_free:
                 raise CacheFull(f"slot {slot} needs {need} more pages of {PAGE_TOKENS} tokens, "
                                 f"{g.pool.n_free} of {g.n_pages} are free")

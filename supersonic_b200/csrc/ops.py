@@ -42,7 +42,14 @@ def _check(status: int, what: str) -> None:
         raise KernelError(f"{what}: {reason}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> c_void_p:
+    """The current stream's handle (the raw query is several times cheaper than building a
+    ``torch.cuda.Stream`` object, and this runs for every launch)."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -370,6 +377,34 @@ def check_device_errors(device=None) -> None:
             word.zero_()
             raise KernelError(f"tcgen05 kernel: a bounded wait ran out in {_TC_ERRORS.get(code, code)}; "
                               "the result of that launch is invalid")
+
+
+_fetch_buffers = {}
+
+
+def fetch_with_errors(values: torch.Tensor) -> list:
+    """The int32 values of a device tensor as a host list, read in the same wait as the device's
+    error word: one synchronisation a step instead of two.  Raises like ``check_device_errors``."""
+    global _tc_unchecked
+    dev = values.device
+    n = values.numel()
+    word = _tc_error_words.get(dev) if _tc_unchecked else None
+    buf = _fetch_buffers.get(dev)
+    if buf is None or buf.numel() < n + 1:
+        buf = _fetch_buffers[dev] = torch.empty(max(n + 1, 4097), dtype=torch.int32, pin_memory=True)
+    buf[:n].copy_(values.view(-1), non_blocking=True)
+    if word is not None:
+        buf[n:n + 1].copy_(word, non_blocking=True)
+    torch.cuda.current_stream(dev).synchronize()
+    out = buf[:n].tolist()
+    if word is not None:
+        _tc_unchecked = 0
+        code = int(buf[n])
+        if code:
+            word.zero_()
+            raise KernelError(f"tcgen05 kernel: a bounded wait ran out in {_TC_ERRORS.get(code, code)}; "
+                              "the result of that launch is invalid")
+    return out
 
 
 def gemm_tc_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:

@@ -102,16 +102,20 @@ class Generator:
         live = list(batch)
         try:
             entries = [StepEntry(slot_of[r], prompts[r], [len(prompts[r]) - 1]) for r in live]
+            slots = None
             while live:
                 logits = model.step(entries)
                 self.steps_run += 1
                 if max_new_tokens <= 0:
                     break
-                slots = torch.tensor([slot_of[r] for r in live], dtype=torch.int32).to(
-                    logits.device, non_blocking=True)
-                tokens = self.sampler(logits, slots, sampling).to("cpu").tolist()
-                if hasattr(model, "check_errors"):
-                    model.check_errors()
+                if slots is None:                        # the live set changed (or this is the first step)
+                    slots = torch.tensor([slot_of[r] for r in live], dtype=torch.int32).to(
+                        logits.device, non_blocking=True)
+                sampled = self.sampler(logits, slots, sampling)
+                if hasattr(model, "fetch"):
+                    tokens = model.fetch(sampled)        # kernel errors are looked at in the same wait
+                else:
+                    tokens = sampled.to("cpu").tolist()
                 if on_step:
                     on_step(live, tokens)
                 still, entries = [], []
@@ -126,6 +130,8 @@ class Generator:
                     else:
                         still.append(r)
                         entries.append(StepEntry(slot_of[r], [tok], [0]))
+                if len(still) != len(live):
+                    slots = None
                 live = still
         finally:
             for slot in slot_of.values():

@@ -73,6 +73,7 @@ class DecodeGraph:
         self.n_seqs = B
         # a ring of pinned staging buffers: the host may run several steps ahead of the device
         self.hosts = [torch.zeros(3 * B, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self.hosts_np = [h.numpy() for h in self.hosts]     # the same memory, cheap to fill from lists
         self.copied = [None] * len(self.hosts)
         self.turn = 0
         self.ints = torch.zeros(3 * B, dtype=torch.int32, device=dev)
@@ -102,7 +103,7 @@ class DecodeGraph:
         if self.copied[i] is not None:
             self.copied[i].synchronize()                    # its last copy has left this buffer
         h = self.hosts[i]
-        h.copy_(torch.tensor(list(tokens) + list(positions) + list(slots), dtype=torch.int32))
+        self.hosts_np[i][:] = list(tokens) + list(positions) + list(slots)     # a numpy view of the pinned buffer
         self.ints.copy_(h, non_blocking=True)
         if self.copied[i] is None:
             self.copied[i] = torch.cuda.Event()
@@ -247,6 +248,14 @@ class Model:
         brought to the host (it reads a device word, which waits for the stream)."""
         from ..csrc import ops
         ops.check_device_errors(self.device)
+
+    def fetch(self, values: torch.Tensor) -> list:
+        """Sampled tokens (an int32 device tensor) as a host list; kernel errors are looked at in
+        the same wait (see ``check_errors``)."""
+        from ..csrc import ops
+        if values.device.type != "cuda":
+            return values.tolist()
+        return ops.fetch_with_errors(values)
 
     # ---- sequences --------------------------------------------------------------------
     def open_sequence(self, rng_seed: Optional[int] = None) -> int:
