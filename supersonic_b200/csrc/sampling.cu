@@ -1,5 +1,5 @@
-// Sampling kernels: argmax, and temperature / top-k / top-p sampling, one block per row of
-// float32 logits.
+// Sampling kernels: argmax, and temperature / top-k / top-p sampling of rows of float32 logits
+// (one block per row; the sampling rule also on a cluster of 8 blocks per row, which is the one used).
 //
 // Rules follow the reference's samplers:
 //   greedy      strict '>' so the lowest index wins ties
@@ -196,11 +196,198 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float i
     if (tid == 0) out[blockIdx.x] = (found == 0x7fffffff) ? 0 : found;
 }
 
+// ---- the same rule on a cluster of blocks ---------------------------------------------------
+// One block walking a row of 128k logits 30 to 60 times (a bisection step each) is bound by that
+// block's path to L2: 320 us for top-k, 690 us for top-k and top-p.  Here a cluster of 8 blocks
+// holds the row, scaled by 1/T, in its distributed shared memory (a slice each, read from global
+// memory once); a bisection step sums over the slice and the 8 partial sums meet through shared
+// memory of the cluster, in rank order, so every block takes the same decision.  The running sum
+// of the draw goes through the slices in rank order: index order, as in the single-block kernel.
+constexpr int SC_CTAS = 8;
+constexpr int SC_THREADS = 512;
+
+__device__ __forceinline__ unsigned sc_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void sc_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float sc_remote_f32(const float* local, unsigned rank) {
+    unsigned addr = (unsigned)__cvta_generic_to_shared(local), remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+struct ScShared {
+    float red[2][SC_THREADS / 32];
+    float pub[2];                  // what this block publishes to the cluster
+    float chunk_sum[SC_THREADS];
+    int found;
+};
+
+// Sum (or maximum) over the cluster: every block gets the same value, combined in rank order.
+// ``turn`` alternates between two sets of slots (every thread keeps its own copy, they agree by
+// construction): a slot is written again only two meetings later, when nobody reads it any more.
+template <bool MAX>
+__device__ __forceinline__ float sc_all(float v, ScShared& sh, int& turn) {
+    for (int o = 16; o > 0; o >>= 1) {
+        const float w = __shfl_xor_sync(0xffffffffu, v, o);
+        v = MAX ? fmaxf(v, w) : v + w;
+    }
+    if ((threadIdx.x & 31) == 0) sh.red[turn][threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float m = MAX ? -INFINITY : 0.f;
+        for (int w = 0; w < SC_THREADS / 32; ++w) m = MAX ? fmaxf(m, sh.red[turn][w]) : m + sh.red[turn][w];
+        sh.pub[turn] = m;
+    }
+    sc_cluster_sync();                                   // every block's value is published
+    float r = MAX ? -INFINITY : 0.f;
+#pragma unroll
+    for (unsigned c = 0; c < SC_CTAS; ++c) {
+        const float o = sc_remote_f32(&sh.pub[turn], c);
+        r = MAX ? fmaxf(r, o) : r + o;
+    }
+    turn ^= 1;
+    return r;
+}
+
+__global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, long long ld, int vocab, float inv_temperature, int top_k,
+                      float top_p, const int* __restrict__ slots, unsigned long long* __restrict__ rng_state,
+                      int* __restrict__ out, float* __restrict__ drawn_u) {
+    extern __shared__ float xs[];                        // this block's slice of the scaled logits
+    __shared__ ScShared sh;
+    const int tid = threadIdx.x, row_id = blockIdx.y;
+    const unsigned rank = sc_rank();
+    const float* row = logits + (size_t)row_id * ld;
+    const int per_cta = (vocab + SC_CTAS - 1) / SC_CTAS;
+    const int lo_i = min((int)rank * per_cta, vocab), hi_i = min(lo_i + per_cta, vocab), n = hi_i - lo_i;
+    int turn = 0;
+    if (tid == 0) sh.found = 0x7fffffff;
+    for (int i = tid; i < n; i += SC_THREADS) xs[i] = row[lo_i + i] * inv_temperature;
+
+    // one draw per row, from the sequence's own generator (every block computes it; the first
+    // block writes the new state back after the first meeting of the cluster)
+    const int seq = slots ? slots[row_id] : row_id;
+    unsigned long long state = rng_state[seq];
+    state ^= state << 13; state ^= state >> 7; state ^= state << 17;
+    const float u = (float)(state >> 40) / 16777216.0f;
+    __syncthreads();
+
+    float mx = -INFINITY;
+    for (int i = tid; i < n; i += SC_THREADS) mx = fmaxf(mx, xs[i]);
+    mx = sc_all<true>(mx, sh, turn);
+    if (rank == 0 && tid == 0) { rng_state[seq] = state; if (drawn_u) drawn_u[row_id] = u; }
+
+    unsigned cut = 0u;
+    if (top_k > 0 && top_k < vocab) {
+        unsigned lo = 0u, hi = float_order_key(mx);      // the largest key there is
+        while (lo < hi) {
+            const unsigned mid = lo + (unsigned)(((unsigned long long)hi - lo + 1ull) >> 1);
+            float cnt = 0.f;
+            for (int i = tid; i < n; i += SC_THREADS) cnt += (float_order_key(xs[i]) >= mid) ? 1.f : 0.f;
+            cnt = sc_all<false>(cnt, sh, turn);
+            if (cnt >= (float)top_k) lo = mid; else hi = mid - 1u;
+        }
+        cut = lo;
+    }
+    float total = 0.f;
+    for (int i = tid; i < n; i += SC_THREADS)
+        if (float_order_key(xs[i]) >= cut) total += expf(xs[i] - mx);
+    total = sc_all<false>(total, sh, turn);
+    if (!(total > 0.f) || isinf(total) || isnan(total)) {                   // degenerate row: greedy, lowest index
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int i = tid; i < n; i += SC_THREADS) if (xs[i] > bv) { bv = xs[i]; bi = lo_i + i; }
+        const float gm = sc_all<true>(bv, sh, turn);
+        if (bv == gm && bi != 0x7fffffff) atomicMin(&sh.found, bi);
+    } else {
+        if (top_p < 1.0f) {
+            const float need = top_p * total;
+            unsigned lo = cut, hi = float_order_key(mx);
+            while (lo < hi) {
+                const unsigned mid = lo + (unsigned)(((unsigned long long)hi - lo + 1ull) >> 1);
+                float mass = 0.f;
+                for (int i = tid; i < n; i += SC_THREADS)
+                    if (float_order_key(xs[i]) >= mid) mass += expf(xs[i] - mx);
+                mass = sc_all<false>(mass, sh, turn);
+                if (mass >= need) lo = mid; else hi = mid - 1u;
+            }
+            cut = lo;
+        }
+        // draw: a contiguous chunk of the slice per thread; positions along the running sum are
+        // P(thread) = (sum of the slices before) + (sum of the chunks before), and a thread owns
+        // [P(thread), P(next thread)], so the intervals tile [0, kept] without gaps
+        const int per = (n + SC_THREADS - 1) / SC_THREADS;
+        const int begin = min(tid * per, n), end = min(begin + per, n);
+        float mine = 0.f;
+        for (int i = begin; i < end; ++i)
+            if (float_order_key(xs[i]) >= cut) mine += expf(xs[i] - mx);
+        sh.chunk_sum[tid] = mine;
+        __syncthreads();
+        float before = 0.f, slice_sum = 0.f;
+        for (int t = 0; t < SC_THREADS; ++t) {           // same order in every thread
+            if (t == tid) before = slice_sum;
+            slice_sum += sh.chunk_sum[t];
+        }
+        if (tid == 0) sh.pub[turn] = slice_sum;
+        sc_cluster_sync();
+        float base = 0.f, kept = 0.f;
+        for (unsigned c = 0; c < SC_CTAS; ++c) {
+            if (c == rank) base = kept;
+            kept += sc_remote_f32(&sh.pub[turn], c);
+        }
+        turn ^= 1;
+        const float r = u * kept;
+        const float p_lo = base + before;
+        const float p_hi = (tid == SC_THREADS - 1) ? base + slice_sum : base + (before + mine);
+        if (mine > 0.f && p_lo <= r && r <= p_hi) {
+            float cum = p_lo;
+            int last = -1, hit = -1;
+            for (int i = begin; i < end; ++i)
+                if (float_order_key(xs[i]) >= cut) {
+                    last = i;
+                    cum += expf(xs[i] - mx);
+                    if (cum >= r) { hit = i; break; }
+                }
+            if (hit < 0) hit = last;                      // rounding left r a hair above this chunk's sum
+            if (hit >= 0) atomicMin(&sh.found, lo_i + hit);
+        }
+    }
+    // the lowest index found in any block
+    sc_cluster_sync();
+    if (rank == 0 && tid == 0) {
+        int best = 0x7fffffff;
+        for (unsigned c = 0; c < SC_CTAS; ++c) {
+            unsigned addr = (unsigned)__cvta_generic_to_shared(&sh.found), remote;
+            int v;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(c));
+            asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+            best = min(best, v);
+        }
+        out[row_id] = (best == 0x7fffffff) ? 0 : best;
+    }
+    sc_cluster_sync();                                   // no block leaves while its shared memory may be read
+}
+
 SSB_API int ssb_sample(const float* logits, long long ld, int n_rows, int vocab, float temperature,
                        int top_k, float top_p, const int* slots, unsigned long long* rng_state, int* out,
                        float* drawn_u, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (vocab <= 0 || vocab >= 0x40000000 || !(temperature > 0.f)) return SSB_ERR_BAD_SIZE;
+    // a cluster of 8 blocks per row where the row's slices fit shared memory (vocabularies up to 400k)
+    const size_t slice = (size_t)((vocab + SC_CTAS - 1) / SC_CTAS) * sizeof(float);
+    if (slice <= 200 * 1024 && n_rows <= 65535) {
+        static size_t configured = 0;
+        if (slice > 48 * 1024 && slice > configured) {
+            cudaError_t e = cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)slice);
+            if (e != cudaSuccess) return (int)e;
+            configured = slice;
+        }
+        sample_cluster_kernel<<<dim3(SC_CTAS, n_rows), SC_THREADS, slice, stream>>>(
+            logits, ld, vocab, 1.0f / temperature, top_k, top_p, slots, rng_state, out, drawn_u);
+        return ssb_launch_status();
+    }
     sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, 1.0f / temperature, top_k,
                                                          top_p, slots, rng_state, out, drawn_u);
     return ssb_launch_status();
