@@ -101,13 +101,31 @@ class FastKernels(PlainKernels):
                 ops.gemv_tc(x, weight, sums, ops.TC_ACCUMULATE, splits=ops.gemv_tc_splits(n, k), pdl=self.pdl)
                 ops.round_and_clear(sums, out, pdl=self.pdl)
             else:
-                ops.gemm_tc(x, weight, out, ops.TC_ACCUMULATE if accumulate else ops.TC_STORE,
-                            tile_n=self._tile_n(rows, n))
+                # a prompt of a few hundred tokens: fewer output tiles than SMs.  K is cut into parts
+                # that add with float atomics, into the residual or, for a stored result, into the
+                # zeroed scratch that round_and_clear turns into bfloat16 (as for decode above)
+                tile_n = self._tile_n(rows, n)
+                splits = self._gemm_splits(rows, n, k, tile_n)
+                if splits > 1 and accumulate:
+                    ops.gemm_tc(x, weight, out, ops.TC_ACCUMULATE, tile_n=tile_n, splits=splits)
+                elif splits > 1 and out.dtype == torch.bfloat16 and n % 8 == 0 and out.stride(0) % 8 == 0:
+                    sums = self._buffer("split_sums", rows * n, torch.float32, out.device, zero=True)[: rows * n].view(rows, n)
+                    ops.gemm_tc(x, weight, sums, ops.TC_ACCUMULATE, tile_n=tile_n, splits=splits)
+                    ops.round_and_clear(sums, out, pdl=self.pdl)
+                else:
+                    ops.gemm_tc(x, weight, out, ops.TC_ACCUMULATE if accumulate else ops.TC_STORE, tile_n=tile_n)
             return
         if rows <= 64 and weight.dtype == torch.bfloat16 and (out.dtype == torch.float32 or not accumulate):
             if self._skinny(x, weight, out, ops.SG_ACCUMULATE if accumulate else ops.SG_STORE):
                 return
         ops.gemm_nt_plain(x, weight, out, accumulate)
+
+    @staticmethod
+    def _gemm_splits(rows: int, n: int, k: int, tile_n: int) -> int:
+        """Parts a tile's K range is cut into so that the work items fill the SMs once (one block
+        per SM walks them); at least 8 k-blocks (512 columns) a part; 1 when the tiles alone do."""
+        tiles = ((rows + 127) // 128) * ((n + tile_n - 1) // tile_n)
+        return max(1, min(148 // tiles, (k // 64) // 8, 16))
 
     @staticmethod
     def _tile_n(rows: int, n: int) -> int:

@@ -28,11 +28,26 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // Persistent: a block takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulators of
 // consecutive tiles alternate between two regions of tensor memory, so that the epilogue of one
 // tile (tcgen05.ld, conversion, stores) runs while the MMAs of the next are issued.
+//
+// splits > 1 (float32 output, mode accumulate): a prompt of a few hundred tokens has fewer output
+// tiles than the GPU has SMs, and the few blocks cannot pull the weights at the memory's rate.
+// The K range of every tile is then cut into ``splits`` parts, each a work item of its own, and
+// the parts add into the output with float atomics.
+struct TcItem {
+    int tile, kb_lo, kb_hi;
+    __device__ TcItem(int item, int n_tiles, int k_blocks, int splits) {
+        tile = item % n_tiles;
+        const int part = item / n_tiles, per = (k_blocks + splits - 1) / splits;
+        kb_lo = min(part * per, k_blocks);
+        kb_hi = min(kb_lo + per, k_blocks);
+    }
+};
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                void* __restrict__ C, int ldc, int out_is_f32, int M, int N, int K, int mode, int m_tiles,
-               int n_tiles_total, int* __restrict__ error_word) {
+               int n_tiles_total, int splits, int* __restrict__ error_word) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
     constexpr int N_ACC = BN <= 128 ? 2 : 2;                       // accumulator regions (2 x BN <= 512 columns)
     extern __shared__ unsigned char smem_raw[];
@@ -66,9 +81,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         if (lane == 0) {
             int c = 0, issued_from = 0;                        // k-blocks issued so far (ring position)
-            for (int tile = blockIdx.x; tile < n_tiles_total && !*abort_flag; tile += gridDim.x) {
-                const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++c) {
+            for (int item = blockIdx.x; item < n_tiles_total * splits && !*abort_flag; item += gridDim.x) {
+                const TcItem it(item, n_tiles_total, k_blocks, splits);
+                const int m0 = (it.tile % m_tiles) * TC_BM, n0 = (it.tile / m_tiles) * BN;
+                for (int kb = it.kb_lo; kb < it.kb_hi; ++kb, ++c) {
                     const int s = c % STAGES;
                     const uint32_t phase = (c / STAGES) & 1;
                     if (!mbar_wait(empty0 + 8 * s, phase ^ 1, abort_flag)) {
@@ -93,7 +109,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
             bool ok = true;
             int c = 0, i = 0;
-            for (int tile = blockIdx.x; tile < n_tiles_total && ok; tile += gridDim.x, ++i) {
+            for (int item = blockIdx.x; item < n_tiles_total * splits && ok; item += gridDim.x, ++i) {
+                const TcItem it(item, n_tiles_total, k_blocks, splits);
                 const int buf = i % N_ACC;
                 const uint32_t use = (uint32_t)(i / N_ACC) & 1;
                 if (!mbar_wait(acc_empty0 + 8 * buf, use ^ 1, abort_flag)) {    // the epilogue has drained this region
@@ -101,7 +118,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 tc_fence_after();
                 const uint32_t acc = tmem + buf * BN;
-                for (int kb = 0; kb < k_blocks && ok; ++kb, ++c) {
+                for (int kb = it.kb_lo; kb < it.kb_hi && ok; ++kb, ++c) {
                     const int s = c % STAGES;
                     const uint32_t phase = (c / STAGES) & 1;
                     if (!mbar_wait(full0 + 8 * s, phase, abort_flag)) {
@@ -112,7 +129,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint64_t da = smem_desc(a_addr), dw = smem_desc(a_addr + A_BYTES);
 #pragma unroll
                     for (int k = 0; k < TC_BK / 16; ++k)        // 16 k = 32 bytes further along the swizzled row
-                        tc_mma(acc, da + 2 * k, dw + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                        tc_mma(acc, da + 2 * k, dw + 2 * k, idesc, (kb > it.kb_lo || k > 0) ? 1u : 0u);
                     tc_commit(empty0 + 8 * s);                  // the stage is free once these MMAs have read it
                 }
                 if (ok) tc_commit(acc_full0 + 8 * buf);         // this tile's accumulators are complete
@@ -122,8 +139,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // epilogue: warp w may read tensor-memory lanes 32 * (w % 4) .. + 31 = rows of the tile
         const int quarter = warp & 3;
         int i = 0;
-        for (int tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++i) {
-            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+        const bool part = splits > 1;                            // parts of a tile add with atomics
+        for (int item = blockIdx.x; item < n_tiles_total * splits; item += gridDim.x, ++i) {
+            const TcItem it(item, n_tiles_total, k_blocks, splits);
+            const int m0 = (it.tile % m_tiles) * TC_BM, n0 = (it.tile / m_tiles) * BN;
             const int row = m0 + quarter * 32 + lane;
             const int buf = i % N_ACC;
             const uint32_t use = (uint32_t)(i / N_ACC) & 1;
@@ -168,6 +187,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             for (int j = 0; j < 32; j += 4) {
                                 float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
                                                        __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                                if (part) { atomicAdd(reinterpret_cast<float4*>(dst + j), v); continue; }
                                 if (mode == TC_ACCUMULATE) {
                                     const float4 o = *reinterpret_cast<const float4*>(dst + j);
                                     v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
@@ -175,8 +195,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 *reinterpret_cast<float4*>(dst + j) = v;
                             }
                         } else {
-                            for (int j = 0; j < 32 && n + j < N; ++j)
-                                dst[j] = __uint_as_float(r[j]) + (mode == TC_ACCUMULATE ? dst[j] : 0.f);
+                            for (int j = 0; j < 32 && n + j < N; ++j) {
+                                if (part) atomicAdd(dst + j, __uint_as_float(r[j]));
+                                else dst[j] = __uint_as_float(r[j]) + (mode == TC_ACCUMULATE ? dst[j] : 0.f);
+                            }
                         }
                     } else {
                         bf16* dst = (bf16*)C + (size_t)row * ldc + n;
@@ -212,7 +234,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
 template <int BN, int STAGES>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int out_is_f32, int M, int N,
-                     int K, int mode, int* error_word, cudaStream_t stream) {
+                     int K, int mode, int splits, int* error_word, cudaStream_t stream) {
     constexpr size_t smem = STAGES * (TC_BM + BN) * TC_BK * 2 + (2 * STAGES + 4) * 8 + 16 + 1024;
     auto kern = gemm_tc_kernel<BN, STAGES>;
     static bool configured = false;
@@ -230,20 +252,28 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int 
             n_sms = 148;
     }
     const int total = m_tiles * n_tiles;
-    kern<<<total < n_sms ? total : n_sms, TC_THREADS, smem, stream>>>(ma, mw, C, ldc, out_is_f32, M, N, K, mode,
-                                                                      m_tiles, total, error_word);
+    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+    if (splits > 1) {                                    // no empty parts: every part has at least one k-block
+        const int per = (k_blocks + splits - 1) / splits;
+        splits = (k_blocks + per - 1) / per;
+    }
+    const long long items = (long long)total * splits;
+    kern<<<items < n_sms ? (int)items : n_sms, TC_THREADS, smem, stream>>>(ma, mw, C, ldc, out_is_f32, M, N, K, mode,
+                                                                           m_tiles, total, splits, error_word);
     return ssb_launch_status();
 }
 
 // A: bfloat16 [M, K] (row stride lda), W: bfloat16 [N, K] (row stride ldw).  mode 0: C[m, n]
 // (bfloat16 or float32); mode 1: C (float32) += ; mode 2: W's rows come as [8 gate | 8 up] per 16
-// and C (bfloat16, [M, N/2]) = silu(gate) * up.  error_word: device int, zero while all is well.
+// and C (bfloat16, [M, N/2]) = silu(gate) * up.  splits > 1 (mode 1 only): K is cut into that many
+// parts per tile, which add with float atomics.  error_word: device int, zero while all is well.
 SSB_API int ssb_gemm_tc(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int out_dtype, int M,
-                        int N, int K, int mode, int tile_n, int* error_word, cudaStream_t stream) {
+                        int N, int K, int mode, int tile_n, int splits, int* error_word, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || lda % 8 || ldw % 8 || N % 8 || !error_word) return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)C) & 15) return SSB_ERR_BAD_SIZE;
     if (mode == TC_ACCUMULATE && out_dtype != SSB_F32) return SSB_ERR_BAD_DTYPE;
+    if (splits < 1 || splits > 64 || (splits > 1 && mode != TC_ACCUMULATE)) return SSB_ERR_BAD_SIZE;
     if (mode == TC_SWIGLU && (out_dtype != SSB_BF16 || N % 16 || ldc % 8)) return SSB_ERR_BAD_SIZE;
     if (mode != TC_SWIGLU && (out_dtype == SSB_F32 ? ldc % 4 : ldc % 8)) return SSB_ERR_BAD_SIZE;
     const int bn = tile_n == 64 ? 64 : (tile_n == 128 ? 128 : 256);
@@ -253,7 +283,7 @@ SSB_API int ssb_gemm_tc(const void* A, int lda, const void* W, int ldw, void* C,
     rc = make_map(&mw, W, N, K, ldw, bn);
     if (rc) return rc;
     const int f32o = out_dtype == SSB_F32;
-    if (bn == 64) return launch_tc<64, 8>(ma, mw, C, ldc, f32o, M, N, K, mode, error_word, stream);
-    if (bn == 128) return launch_tc<128, 6>(ma, mw, C, ldc, f32o, M, N, K, mode, error_word, stream);
-    return launch_tc<256, 4>(ma, mw, C, ldc, f32o, M, N, K, mode, error_word, stream);
+    if (bn == 64) return launch_tc<64, 8>(ma, mw, C, ldc, f32o, M, N, K, mode, splits, error_word, stream);
+    if (bn == 128) return launch_tc<128, 6>(ma, mw, C, ldc, f32o, M, N, K, mode, splits, error_word, stream);
+    return launch_tc<256, 4>(ma, mw, C, ldc, f32o, M, N, K, mode, splits, error_word, stream);
 }

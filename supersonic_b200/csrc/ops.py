@@ -416,9 +416,10 @@ def gemm_tc_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_STORE,
-            tile_n: Optional[int] = None) -> None:
+            tile_n: Optional[int] = None, splits: int = 1) -> None:
     """out = a @ w^T on the tensor cores (tcgen05, TMA-fed).  mode: store, add into float32
-    ``out``, or SwiGLU over rows of ``w`` that come as [8 gate | 8 up] per 16."""
+    ``out``, or SwiGLU over rows of ``w`` that come as [8 gate | 8 up] per 16.  ``splits`` > 1
+    (mode accumulate): every tile's K range is cut into that many parts, which add with float atomics."""
     _need(a, "a", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(out, "out", None, 2)
     M, K = a.shape
     N = w.shape[0]
@@ -431,7 +432,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_
     _tc_unchecked += 1
     _check(_fn("gemm_tc", "ssb_gemm_tc")(
         _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)),
-        c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K), c_int(mode), c_int(tile_n),
+        c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K), c_int(mode), c_int(tile_n), c_int(splits),
         _ptr(tc_error_word(a.device)), _stream()), "gemm_tc")
 
 

@@ -402,7 +402,7 @@ def test_round_and_clear():
     assert torch.equal(wide[:, :264], want) and torch.all(wide[:, 264:] == 3.0) and torch.all(sums == 0)
 
 
-@pytest.mark.parametrize("rows", [8, 12, 16, 17, 40, 64, 65])
+@pytest.mark.parametrize("rows", [8, 12, 16, 17, 40, 64, 65, 130, 300])
 @pytest.mark.parametrize("N,K", [(6144, 4096), (1000, 1088)])
 def test_fast_linear_picks_a_kernel_for_every_row_count(rows, N, K):
     """The bfloat16 kernel set's projection at row counts on both sides of every threshold: stored
@@ -449,6 +449,26 @@ def test_gemm_tc(M, N, K, tile_n):
     out2 = torch.empty(M, N, device=DEV)
     ops().gemm_tc(wide[:, :K], w, out2, tile_n=tile_n)
     assert torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("M,N,K,tile_n,splits", [(130, 512, 4096, 256, 8), (300, 1000, 1088, 128, 3),
+                                                 (128, 4096, 14336, 256, 16), (65, 264, 640, 64, 7)])
+def test_gemm_tc_with_k_cut_into_parts(M, N, K, tile_n, splits):
+    """Few output tiles: every tile's K range is cut into parts that add with float atomics (also a
+    number of parts that does not divide the k-blocks, and more parts than k-blocks allow)."""
+    g = torch.Generator(device=DEV).manual_seed(32)
+    a = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
+    ref = a.double() @ w.double().T
+    base = torch.randn(M, N, device=DEV, generator=g)
+    acc = base.clone()
+    for _ in range(2):
+        ops().gemm_tc(a, w, acc, mode=1, tile_n=tile_n, splits=splits)
+    ops().check_device_errors()
+    torch.testing.assert_close(acc.double(), base.double() + 2 * ref, atol=4e-5 * math.sqrt(K), rtol=1e-4)
+    from supersonic_b200.csrc.ops import KernelError
+    with pytest.raises(KernelError):
+        ops().gemm_tc(a, w, torch.empty(M, N, dtype=torch.bfloat16, device=DEV), tile_n=tile_n, splits=splits)
 
 
 @pytest.mark.parametrize("M,inter,K", [(130, 200, 72), (256, 1024, 512)])
