@@ -1,11 +1,14 @@
 """The bfloat16 kernel set used for serving: a fast kernel where one exists for the shape at
 hand, the plain kernel (same arithmetic, bfloat16 storage) otherwise.
 
-Decode steps (up to 64 rows) run the skinny GEMM, with the RMSNorm folded into its
-input for very small batches and SwiGLU folded into its output, and the split-key
-attention kernel."""
+Decode steps (up to 64 rows) run the tcgen05 projections that stream the weights once
+(``gemv_tc``), with SwiGLU folded into the gate/up projection, and the tensor-core split-key
+attention with rotation and cache append inside; prompts run the persistent tcgen05 GEMM and
+the tcgen05 flash attention.  Which kernel a shape gets is decided here and nowhere else; the
+thresholds are module constants with the measurement that set them beside them."""
 from __future__ import annotations
 
+import math
 from typing import Dict, Optional
 
 import torch
@@ -188,7 +191,10 @@ class FastKernels(PlainKernels):
             # for the SM's L1/shared memory); beside the tcgen05 projections it is the faster choice
             # at every batch size (batch 16: 4.24 to 3.57 ms a step, batch 8: 3.64 to 3.42).
             kind = 2
-            n_splits = max(1, min(296 // (batch.n_seqs * n_kv), pages // MMA_PAGES_PER_SPLIT, 64))
+            # a block's time grows with its pages (0.6 us each), the merge with the splits (0.3 us each):
+            # about sqrt(2 * pages) splits, at least MMA_PAGES_PER_SPLIT pages each, two blocks per SM at most
+            n_splits = max(1, min(296 // (batch.n_seqs * n_kv), pages // MMA_PAGES_PER_SPLIT,
+                                  int(math.sqrt(2.0 * pages) + 0.5), 64))
         elif batch.n_seqs <= 2:
             n_splits = max(1, min(TARGET_BLOCKS // blocks, pages, 16))    # latency-bound: a page a block
         elif pages < 32:
