@@ -393,6 +393,36 @@ def test_attention_decode(n_q, n_kv, hd, window, n_splits, kind):
     torch.testing.assert_close(out.float(), plain.float(), atol=1e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("kind", [1, 2])
+@pytest.mark.parametrize("n_splits,slope", [(13, 0.02), (21, -0.02), (16, 0.0)])
+def test_attention_decode_merges_many_splits(kind, n_splits, slope):
+    """More splits than the merge takes in one go (eight), over 21 pages, with scores that climb
+    or fall along the keys so that the maximum moves from one group of splits to the next."""
+    n_q, n_kv, hd, n = 8, 2, 128, 1300
+    g = torch.Generator(device=DEV).manual_seed(26)
+    n_pages = (n + 63) // 64
+    table = torch.randperm(2 * n_pages, generator=torch.Generator().manual_seed(27)).to(torch.int32).view(2, n_pages).to(DEV)
+    k, v = _paged(2 * n_pages, n_kv, hd, torch.bfloat16, 28)
+    ramp = (slope * torch.arange(n_pages * 64, device=DEV, dtype=torch.float32) * math.sqrt(hd)).bfloat16()
+    for s in range(2):
+        for pg in range(n_pages):
+            k[int(table[s, pg]), :, :, 0] = ramp[pg * 64:(pg + 1) * 64][None, :]
+    pos = torch.tensor([n - 1, 777], dtype=torch.int32, device=DEV)
+    slot = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    q = 0.3 * torch.randn(2, (n_q + 2 * n_kv) * hd, device=DEV, generator=g).bfloat16()
+    q[:, 0:n_q * hd:hd] = 1.0                                          # every head looks along the ramp
+    scale = 1 / math.sqrt(hd)
+    nf, nc = ops().attention_decode_scratch(2, n_q, n_kv, hd, n_splits)
+    scratch = torch.full((nf,), float("nan"), device=DEV)
+    counters = torch.zeros(nc, dtype=torch.int32, device=DEV)
+    out = torch.empty(2, n_q * hd, dtype=torch.bfloat16, device=DEV)
+    ops().attention_decode(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, None, scale, n_splits,
+                           scratch, counters, kind=kind)
+    ref = _attention_reference(q, k, v, pos, slot, table, n_q, n_kv, hd, None, scale)
+    torch.testing.assert_close(out.double(), ref, atol=2e-2, rtol=2e-2)
+    assert torch.all(counters == 0)
+
+
 def test_round_and_clear():
     g = torch.Generator(device=DEV).manual_seed(33)
     sums = torch.randn(37, 264, device=DEV, generator=g)
