@@ -78,6 +78,35 @@ def test_long_decoding_stays_on_the_plain_logits(model_folders, dtype):
     assert err.max() < tol, f"first bad position {30 + int(np.argmax(err > tol))}"
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_long_prompt_then_decoding_over_many_pages(model_folders, name):
+    """bfloat16 with head sizes 64 and 128: a prompt of 1,100 tokens in one step (attention tiles
+    with many blocks of keys), a second piece of 300 tokens that continues the cached prefix, then
+    tokens one by one over 22 pages (decode attention with several splits), beside a short
+    sequence that shares the batch."""
+    from supersonic_b200.engine import Model, StepEntry
+    d, pc, pw = model_folders[name]
+    rng = np.random.default_rng(12)
+    long_toks = rng.integers(0, pc["vocab_size"], 1430).tolist()
+    short = rng.integers(0, pc["vocab_size"], 40).tolist()
+    ref_long, ref_short = pl.forward(pc, pw, long_toks), pl.forward(pc, pw, short)
+    tol = 2e-2 * max(np.abs(ref_long).max(), np.abs(ref_short).max())
+    m = Model.from_dir(d, dtype="bfloat16", max_tokens=2048)
+    a, b = m.open_sequence(), m.open_sequence()
+    want = [0, 127, 128, 640, 1099]
+    got = m.step([StepEntry(a, long_toks[:1100], want)]).double().cpu().numpy()
+    assert np.abs(got - ref_long[want]).max() < tol
+    want2 = [0, 150, 299]
+    got = m.step([StepEntry(a, long_toks[1100:1400], want2), StepEntry(b, short[:10], [9])]).double().cpu().numpy()
+    assert np.abs(got[:3] - ref_long[[1100 + w for w in want2]]).max() < tol
+    assert np.abs(got[3] - ref_short[9]).max() < tol
+    for i in range(30):
+        got = m.step([StepEntry(a, [long_toks[1400 + i]], [0]), StepEntry(b, [short[10 + i]], [0])]).double().cpu().numpy()
+        assert np.abs(got[0] - ref_long[1400 + i]).max() < tol, i
+        assert np.abs(got[1] - ref_short[10 + i]).max() < tol, i
+    m.cache.check()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_first_tokens_of_a_sequence(model_folders, dtype):
     """Positions 0, 1, 2 decoded one by one from an empty slot, for two sequences at once."""
