@@ -68,9 +68,20 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
+            // The weights are written by no kernel of a step: the ring's first tiles of W are asked
+            // for before the dependency wait, so that they stream in while the predecessor still runs
+            // (the block is resident by then, through programmatic dependent launch).  Only x has to
+            // wait; a stage's barrier completes when both of its tiles have landed.
+            const int pre = min(my_blocks, GV_STAGES);
+            for (int i = 0; i < pre; ++i) {                  // the ring is empty: no wait for a free stage
+                mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+                tma_load_2d(smem_u32(smem + i * STAGE_BYTES), &map_w, full0 + 8 * i, (kb0 + i) * TC_BK, n0);
+            }
             ssb_pdl_wait();                                  // x is the predecessor's output
-            int issued = 0;
-            for (int i = 0; i < my_blocks; ++i) {
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(smem_u32(smem + i * STAGE_BYTES) + W_BYTES, &map_x, full0 + 8 * i, (kb0 + i) * TC_BK, 0);
+            int issued = pre;
+            for (int i = pre; i < my_blocks; ++i) {
                 const int s = i % GV_STAGES;
                 const uint32_t phase = (i / GV_STAGES) & 1;
                 if (!mbar_wait(empty0 + 8 * s, phase ^ 1, abort_flag)) {
