@@ -22,7 +22,9 @@
 typedef __nv_bfloat16 bf16;
 
 constexpr int GV_BM = 128;                // rows of W per block
-constexpr int GV_STAGES = 4;              // 96 KB a block: two blocks share an SM, no second wave for 149..296 blocks
+// stages of the ring: as many as let two blocks share an SM (no second wave for 149..296 blocks):
+// 18 KB a stage at up to 16 batch rows, 20 KB at 32, 24 KB at 64
+__host__ __device__ constexpr int gv_stages(int bnb) { return bnb <= 16 ? 6 : (bnb <= 32 ? 5 : 4); }
 constexpr int GV_THREADS = 192;           // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
 
 template <int BNB>                        // batch rows per tile: 16, 32 or 64
@@ -30,6 +32,7 @@ __global__ void __launch_bounds__(GV_THREADS, 2)
 gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                void* __restrict__ out, int ldo, int out_is_f32, int n_rows, int N, int K, int mode, int splits,
                float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ error_word) {
+    constexpr int GV_STAGES = gv_stages(BNB);
     constexpr uint32_t W_BYTES = GV_BM * TC_BK * 2, X_BYTES = BNB * TC_BK * 2, STAGE_BYTES = W_BYTES + X_BYTES;
     constexpr int TMEM_COLS = BNB < 32 ? 32 : BNB;
     extern __shared__ unsigned char smem_raw[];
@@ -217,6 +220,7 @@ template <int BNB>
 static int launch_gv(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int ldo, int out_is_f32, int n_rows,
                      int N, int K, int mode, int splits, float* partials, int* counters, int* error_word, bool pdl,
                      cudaStream_t stream) {
+    constexpr int GV_STAGES = gv_stages(BNB);
     constexpr size_t smem = GV_STAGES * (GV_BM + BNB) * TC_BK * 2 + (2 * GV_STAGES + 1) * 8 + 32 + 1024;
     auto kern = gemv_tc_kernel<BNB>;
     static bool configured = false;
