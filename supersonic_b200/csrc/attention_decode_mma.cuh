@@ -95,7 +95,11 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
         }
         cp_async_commit();
     };
-    if (n_my > 0) load_page(0, 0);                               // earlier steps' keys: safe before the wait
+    // earlier steps' keys: safe before the wait.  Both stages are filled here (a cp.async group each,
+    // empty if there is no such page), so that two pages are on their way while the projection
+    // before this kernel still runs.
+    if (n_my > 0) load_page(0, 0); else cp_async_commit();
+    if (n_my > 1) load_page(1, 1); else cp_async_commit();
     if (FUSE) ssb_pdl_wait();                                    // the query comes from the predecessor
 
     // Query fragments: row = head (g and g + 8), this lane's columns 16 ks + 2t (+1, +8, +9).
@@ -148,8 +152,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
 
     for (int i = 0; i < n_my; ++i) {
         const int stage = i & 1;
-        if (i + 1 < n_my) { load_page(i + 1, stage ^ 1); cp_async_wait<1>(); }
-        else cp_async_wait<0>();
+        cp_async_wait<1>();                                      // all but the newest group: page i is in
         __syncthreads();
         const uint32_t kbase = (uint32_t)__cvta_generic_to_shared(smem + stage * TILE_BYTES);
         const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(smem + (2 + stage) * TILE_BYTES);
@@ -209,7 +212,9 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
             }
         }
         __syncthreads();                                         // the stage may be refilled
+        if (i + 2 < n_my) load_page(i + 2, stage); else cp_async_commit();
     }
+    cp_async_wait<0>();
 
     if (FUSE && owns_new && warp == 0) {
         // the token's own key and value, from the projection's output; all of this is lane-local
