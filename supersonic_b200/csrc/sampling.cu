@@ -218,9 +218,11 @@ __device__ __forceinline__ float sc_remote_f32(const float* local, unsigned rank
     return v;
 }
 
+constexpr int SC_WAYS = 3;         // thresholds tried per search step: the range shrinks four times a step (1 and 7 measured slower)
+
 struct ScShared {
-    float red[2][SC_THREADS / 32];
-    float pub[2];                  // what this block publishes to the cluster
+    float red[2][SC_WAYS][SC_THREADS / 32];
+    float pub[2][SC_WAYS];         // what this block publishes to the cluster
     float chunk_sum[SC_THREADS];
     int found;
 };
@@ -234,22 +236,62 @@ __device__ __forceinline__ float sc_all(float v, ScShared& sh, int& turn) {
         const float w = __shfl_xor_sync(0xffffffffu, v, o);
         v = MAX ? fmaxf(v, w) : v + w;
     }
-    if ((threadIdx.x & 31) == 0) sh.red[turn][threadIdx.x >> 5] = v;
+    if ((threadIdx.x & 31) == 0) sh.red[turn][0][threadIdx.x >> 5] = v;
     __syncthreads();
     if (threadIdx.x == 0) {
         float m = MAX ? -INFINITY : 0.f;
-        for (int w = 0; w < SC_THREADS / 32; ++w) m = MAX ? fmaxf(m, sh.red[turn][w]) : m + sh.red[turn][w];
-        sh.pub[turn] = m;
+        for (int w = 0; w < SC_THREADS / 32; ++w) m = MAX ? fmaxf(m, sh.red[turn][0][w]) : m + sh.red[turn][0][w];
+        sh.pub[turn][0] = m;
     }
     sc_cluster_sync();                                   // every block's value is published
     float r = MAX ? -INFINITY : 0.f;
 #pragma unroll
     for (unsigned c = 0; c < SC_CTAS; ++c) {
-        const float o = sc_remote_f32(&sh.pub[turn], c);
+        const float o = sc_remote_f32(&sh.pub[turn][0], c);
         r = MAX ? fmaxf(r, o) : r + o;
     }
     turn ^= 1;
     return r;
+}
+
+// The same for SC_WAYS sums at once (one meeting of the cluster for all of them).
+__device__ __forceinline__ void sc_all_sums(float (&v)[SC_WAYS], ScShared& sh, int& turn) {
+#pragma unroll
+    for (int k = 0; k < SC_WAYS; ++k) {
+        for (int o = 16; o > 0; o >>= 1) v[k] += __shfl_xor_sync(0xffffffffu, v[k], o);
+        if ((threadIdx.x & 31) == 0) sh.red[turn][k][threadIdx.x >> 5] = v[k];
+    }
+    __syncthreads();
+    if (threadIdx.x < SC_WAYS) {
+        float m = 0.f;
+        for (int w = 0; w < SC_THREADS / 32; ++w) m += sh.red[turn][threadIdx.x][w];
+        sh.pub[turn][threadIdx.x] = m;
+    }
+    sc_cluster_sync();
+#pragma unroll
+    for (int k = 0; k < SC_WAYS; ++k) {
+        float r = 0.f;
+#pragma unroll
+        for (unsigned c = 0; c < SC_CTAS; ++c) r += sc_remote_f32(&sh.pub[turn][k], c);
+        v[k] = r;
+    }
+    turn ^= 1;
+}
+
+// One step of the search for the largest key t in [lo, hi] with f(t) >= need, f falling in t:
+// SC_WAYS thresholds are tried at once (their sums f[0] >= f[1] >= ... are given), and the range
+// shrinks to the part between two of them that holds the answer.
+__device__ __forceinline__ void sc_thresholds(unsigned lo, unsigned hi, unsigned (&t)[SC_WAYS]) {
+    const unsigned long long span = (unsigned long long)hi - lo;
+#pragma unroll
+    for (int k = 0; k < SC_WAYS; ++k) t[k] = lo + (unsigned)((span * (k + 1) + SC_WAYS) / (SC_WAYS + 1));   // > lo, <= hi, rising
+}
+__device__ __forceinline__ void sc_narrow(unsigned& lo, unsigned& hi, const unsigned (&t)[SC_WAYS],
+                                          const float (&f)[SC_WAYS], float need) {
+    int k = SC_WAYS - 1;
+    while (k >= 0 && !(f[k] >= need)) --k;               // the highest threshold that still holds
+    if (k + 1 < SC_WAYS) hi = t[k + 1] - 1u;
+    if (k >= 0) lo = t[k];
 }
 
 __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS)
@@ -284,11 +326,16 @@ sample_cluster_kernel(const float* __restrict__ logits, long long ld, int vocab,
     if (top_k > 0 && top_k < vocab) {
         unsigned lo = 0u, hi = float_order_key(mx);      // the largest key there is
         while (lo < hi) {
-            const unsigned mid = lo + (unsigned)(((unsigned long long)hi - lo + 1ull) >> 1);
-            float cnt = 0.f;
-            for (int i = tid; i < n; i += SC_THREADS) cnt += (float_order_key(xs[i]) >= mid) ? 1.f : 0.f;
-            cnt = sc_all<false>(cnt, sh, turn);
-            if (cnt >= (float)top_k) lo = mid; else hi = mid - 1u;
+            unsigned t[SC_WAYS];
+            sc_thresholds(lo, hi, t);
+            float cnt[SC_WAYS] = {};
+            for (int i = tid; i < n; i += SC_THREADS) {
+                const unsigned key = float_order_key(xs[i]);
+#pragma unroll
+                for (int k = 0; k < SC_WAYS; ++k) cnt[k] += (key >= t[k]) ? 1.f : 0.f;
+            }
+            sc_all_sums(cnt, sh, turn);
+            sc_narrow(lo, hi, t, cnt, (float)top_k);
         }
         cut = lo;
     }
@@ -306,12 +353,19 @@ sample_cluster_kernel(const float* __restrict__ logits, long long ld, int vocab,
             const float need = top_p * total;
             unsigned lo = cut, hi = float_order_key(mx);
             while (lo < hi) {
-                const unsigned mid = lo + (unsigned)(((unsigned long long)hi - lo + 1ull) >> 1);
-                float mass = 0.f;
-                for (int i = tid; i < n; i += SC_THREADS)
-                    if (float_order_key(xs[i]) >= mid) mass += expf(xs[i] - mx);
-                mass = sc_all<false>(mass, sh, turn);
-                if (mass >= need) lo = mid; else hi = mid - 1u;
+                unsigned t[SC_WAYS];
+                sc_thresholds(lo, hi, t);
+                float mass[SC_WAYS] = {};
+                for (int i = tid; i < n; i += SC_THREADS) {
+                    const unsigned key = float_order_key(xs[i]);
+                    if (key >= t[0]) {
+                        const float e = expf(xs[i] - mx);
+#pragma unroll
+                        for (int k = 0; k < SC_WAYS; ++k) mass[k] += (key >= t[k]) ? e : 0.f;
+                    }
+                }
+                sc_all_sums(mass, sh, turn);
+                sc_narrow(lo, hi, t, mass, need);
             }
             cut = lo;
         }
@@ -330,12 +384,12 @@ sample_cluster_kernel(const float* __restrict__ logits, long long ld, int vocab,
             if (t == tid) before = slice_sum;
             slice_sum += sh.chunk_sum[t];
         }
-        if (tid == 0) sh.pub[turn] = slice_sum;
+        if (tid == 0) sh.pub[turn][0] = slice_sum;
         sc_cluster_sync();
         float base = 0.f, kept = 0.f;
         for (unsigned c = 0; c < SC_CTAS; ++c) {
             if (c == rank) base = kept;
-            kept += sc_remote_f32(&sh.pub[turn], c);
+            kept += sc_remote_f32(&sh.pub[turn][0], c);
         }
         turn ^= 1;
         const float r = u * kept;
