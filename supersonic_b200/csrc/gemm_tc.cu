@@ -263,6 +263,27 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int 
     return ssb_launch_status();
 }
 
+// A block that waits on a barrier at which nothing ever arrives: the bounded wait gives up after
+// about a second, the kernel records the producer's code in the error word and returns, and the
+// context stays usable.  It exercises the give-up path that every mbarrier wait of these kernels
+// shares; nothing but tests calls it.
+__global__ void tc_wait_probe_kernel(int* __restrict__ error_word) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!mbar_wait(smem_u32(&bar), 0, &abort_flag)) atomicCAS(error_word, 0, TC_ERR_PRODUCER);
+    }
+}
+
+SSB_API int ssb_tc_wait_probe(int* error_word, cudaStream_t stream) {
+    if (!error_word) return SSB_ERR_BAD_SIZE;
+    tc_wait_probe_kernel<<<1, 32, 0, stream>>>(error_word);
+    return ssb_launch_status();
+}
+
 // A: bfloat16 [M, K] (row stride lda), W: bfloat16 [N, K] (row stride ldw).  mode 0: C[m, n]
 // (bfloat16 or float32); mode 1: C (float32) += ; mode 2: W's rows come as [8 gate | 8 up] per 16
 // and C (bfloat16, [M, N/2]) = silu(gate) * up.  splits > 1 (mode 1 only): K is cut into that many

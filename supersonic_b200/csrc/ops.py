@@ -407,6 +407,14 @@ def fetch_with_errors(values: torch.Tensor) -> list:
     return out
 
 
+def tc_wait_probe(device="cuda:0") -> None:
+    """Launch a block whose only wait can never be satisfied: after about a second it gives up and
+    records that in the device's error word, which ``check_device_errors`` then reports."""
+    global _tc_unchecked
+    _tc_unchecked += 1
+    _check(_fn("gemm_tc", "ssb_tc_wait_probe")(_ptr(tc_error_word(device)), _stream()), "tc_wait_probe")
+
+
 def gemm_tc_ok(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     """Whether the tcgen05 GEMM takes these operands (else the plain kernel does)."""
     return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0

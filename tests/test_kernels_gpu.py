@@ -501,6 +501,26 @@ def test_gemm_tc_with_k_cut_into_parts(M, N, K, tile_n, splits):
         ops().gemm_tc(a, w, torch.empty(M, N, dtype=torch.bfloat16, device=DEV), tile_n=tile_n, splits=splits)
 
 
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable():
+    """A bounded mbarrier wait at which nothing arrives gives up after about a second; the error
+    word carries the role, ``check_device_errors`` raises once and clears it, and the next GEMM is right."""
+    import time
+    from supersonic_b200.csrc.ops import KernelError
+    ops().check_device_errors()
+    t0 = time.perf_counter()
+    ops().tc_wait_probe(DEV)
+    with pytest.raises(KernelError, match="bounded wait ran out in the TMA producer"):
+        ops().check_device_errors()
+    assert 0.2 < time.perf_counter() - t0 < 10.0
+    ops().check_device_errors()                                         # cleared: no second report
+    a = torch.randn(128, 256, device=DEV).bfloat16()
+    w = torch.randn(64, 256, device=DEV).bfloat16()
+    out = torch.empty(128, 64, device=DEV)
+    ops().gemm_tc(a, w, out)
+    ops().check_device_errors()
+    torch.testing.assert_close(out.double(), a.double() @ w.double().T, atol=1e-3, rtol=1e-4)
+
+
 @pytest.mark.parametrize("M,inter,K", [(130, 200, 72), (256, 1024, 512)])
 def test_gemm_tc_swiglu(M, inter, K):
     g = torch.Generator(device=DEV).manual_seed(31)
