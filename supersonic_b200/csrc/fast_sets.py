@@ -34,6 +34,7 @@ class FastKernels(PlainKernels):
     def __init__(self, pdl: bool = True):
         self.pdl = pdl           # decode kernels launch as programmatic dependents of their predecessors
         self.fuse_rope = True    # decode attention rotates q/k and appends to the cache itself
+        self.fuse_rope_prefill = True   # the prompt's q/k/v projection does so in its epilogue
         # a residual-adding projection can also write the next norm of the residual (its last block
         # does it); measured slower than the separate norm launch at batch 1 and 8, so it is off
         self.fuse_post_norm = False
@@ -212,6 +213,28 @@ class FastKernels(PlainKernels):
                              prefetch=self._next_weights if batch.n_seqs <= PREFETCH_MAX_ROWS else None,
                              prefetch_bytes=PREFETCH_BYTES)
         self._next_weights = None
+
+    def project_rope_append(self, x, w_qkv, qkv, position, kv, batch, n_q, n_kv, head_dim, page_shift) -> bool:
+        """Prompts whose tiles alone fill the SMs: the tcgen05 projection rotates q and k from its
+        float32 sums and writes k and v into the cache (no separate rope + append launch, and the
+        key and value columns never go through ``qkv``)."""
+        tables = getattr(position, "rotary_tables", None)
+        rows = batch.n_tokens
+        if not (self.fuse_rope_prefill and tables and not batch.is_decode and rows > 64
+                and w_qkv.dtype == torch.bfloat16 and head_dim in (64, 128)):
+            return False
+        n, k = w_qkv.shape
+        if self._gemm_splits(rows, n, k, 256) > 1:
+            return False                      # a short prompt: K split over blocks is the faster way
+        cos, sin, rotary_dim = tables()
+        k_cache, v_cache, page_table, _ = kv
+        x = as_tensor(x)
+        if rotary_dim != head_dim or not ops.gemm_tc_ok(x, w_qkv, qkv) or k_cache.dtype != torch.bfloat16:
+            return False
+        position.check_range(batch)
+        ops.gemm_tc_rope_append(x, w_qkv, qkv, cos, sin, batch.pos, batch.slot_of_token, page_table, k_cache,
+                                v_cache, n_q, n_kv, head_dim, page_shift)
+        return True
 
     def rope_attention(self, qkv, position, kv, batch, out, n_q, n_kv, head_dim, page_shift, window,
                        scale) -> bool:

@@ -33,6 +33,35 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // tiles than the GPU has SMs, and the few blocks cannot pull the weights at the memory's rate.
 // The K range of every tile is then cut into ``splits`` parts, each a work item of its own, and
 // the parts add into the output with float atomics.
+// Mode rope-and-append: the product is the fused query/key/value projection of packed tokens.  The
+// epilogue rotates query and key heads by each token's position (float32 tables, pairs d and
+// d + head_dim/2, from the float32 accumulators: one rounding), writes the queries as bfloat16
+// into C, and the keys and values straight into the paged cache; C's key and value columns are
+// not written.  Replaces the separate rope + append launch after the projection of a prompt
+// (reference: kernels/prefill_helpers_cuda.cuh:80-111, certified_kv_bridge_cuda.cu:32-51).
+struct TcRope {
+    const int* pos;            // [M] position of each row's token
+    const int* slot;           // [M] cache slot of each row's token
+    const int* page_table;     // [slots, max_pages]
+    __nv_bfloat16* k_cache;    // [pages, n_kv, page tokens, head_dim]
+    __nv_bfloat16* v_cache;
+    const float* cos_t;        // [positions, head_dim / 2]
+    const float* sin_t;
+    int max_pages, n_q, n_kv, head_dim, page_shift;
+};
+
+__device__ __forceinline__ void tc_store32_bf16(__nv_bfloat16* dst, const float (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+        uint4 u;
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+        u.x = *reinterpret_cast<uint32_t*>(&p0); u.y = *reinterpret_cast<uint32_t*>(&p1);
+        u.z = *reinterpret_cast<uint32_t*>(&p2); u.w = *reinterpret_cast<uint32_t*>(&p3);
+        *reinterpret_cast<uint4*>(dst + j) = u;
+    }
+}
+
 struct TcItem {
     int tile, kb_lo, kb_hi;
     __device__ TcItem(int item, int n_tiles, int k_blocks, int splits) {
@@ -47,7 +76,7 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                void* __restrict__ C, int ldc, int out_is_f32, int M, int N, int K, int mode, int m_tiles,
-               int n_tiles_total, int splits, int* __restrict__ error_word) {
+               int n_tiles_total, int splits, int* __restrict__ error_word, const TcRope rope) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
     constexpr int N_ACC = BN <= 128 ? 2 : 2;                       // accumulator regions (2 x BN <= 512 columns)
     extern __shared__ unsigned char smem_raw[];
@@ -154,6 +183,55 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             tc_fence_after();
             const uint32_t acc = tmem + buf * BN;
+            if (mode == TC_ROPE_APPEND) {
+                // a head at a time: its low and high halves meet in this thread (the row's token)
+                const int hd = rope.head_dim, half = hd / 2, halves32 = half / 32;
+                const bool live = row < M;
+                const int p = live ? rope.pos[row] : 0, sl = live ? rope.slot[row] : -1;
+                size_t tok = 0;
+                if (sl >= 0) {
+                    const int page = rope.page_table[(size_t)sl * rope.max_pages + (p >> rope.page_shift)];
+                    tok = (((size_t)page * rope.n_kv) << rope.page_shift) + (size_t)(p & ((1 << rope.page_shift) - 1));
+                }
+                for (int hh = 0; hh * hd < BN && n0 + hh * hd < N; ++hh) {
+                    const int head = (n0 + hh * hd) / hd;
+                    const bool is_q = head < rope.n_q, is_v = head >= rope.n_q + rope.n_kv;
+                    const int kvh = is_q ? 0 : (is_v ? head - rope.n_q - rope.n_kv : head - rope.n_q);
+                    bf16* dst = is_q ? (bf16*)C + (size_t)row * ldc + (size_t)head * hd
+                                     : (is_v ? rope.v_cache : rope.k_cache) +
+                                           (tok + ((size_t)kvh << rope.page_shift)) * hd;
+#pragma unroll 1
+                    for (int pc = 0; pc < halves32; ++pc) {
+                        uint32_t lo_r[32], hi_r[32];
+                        const uint32_t at = acc + ((uint32_t)(quarter * 32) << 16) + hh * hd + pc * 32;
+                        tc_ld32(at, lo_r);                       // every lane takes part in the loads
+                        tc_ld32(at + half, hi_r);
+                        if (!live || sl < 0) continue;
+                        float lo[32], hi[32];
+                        if (is_v) {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) { lo[e] = __uint_as_float(lo_r[e]); hi[e] = __uint_as_float(hi_r[e]); }
+                        } else {
+                            const float4* c4 = reinterpret_cast<const float4*>(rope.cos_t + (size_t)p * half + pc * 32);
+                            const float4* s4 = reinterpret_cast<const float4*>(rope.sin_t + (size_t)p * half + pc * 32);
+#pragma unroll
+                            for (int i4 = 0; i4 < 8; ++i4) {
+                                const float4 c = c4[i4], sn = s4[i4];
+#define TC_ROTATE(e, cv, sv)                                                                         \
+    {                                                                                                \
+        const float a_ = __uint_as_float(lo_r[4 * i4 + e]), b_ = __uint_as_float(hi_r[4 * i4 + e]);  \
+        lo[4 * i4 + e] = a_ * cv - b_ * sv;                                                          \
+        hi[4 * i4 + e] = a_ * sv + b_ * cv;                                                          \
+    }
+                                TC_ROTATE(0, c.x, sn.x) TC_ROTATE(1, c.y, sn.y) TC_ROTATE(2, c.z, sn.z) TC_ROTATE(3, c.w, sn.w)
+#undef TC_ROTATE
+                            }
+                        }
+                        tc_store32_bf16(dst + pc * 32, lo);
+                        tc_store32_bf16(dst + half + pc * 32, hi);
+                    }
+                }
+            } else
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
                     uint32_t r[32];
@@ -234,7 +312,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
 template <int BN, int STAGES>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int out_is_f32, int M, int N,
-                     int K, int mode, int splits, int* error_word, cudaStream_t stream) {
+                     int K, int mode, int splits, int* error_word, const TcRope& rope, cudaStream_t stream) {
     constexpr size_t smem = STAGES * (TC_BM + BN) * TC_BK * 2 + (2 * STAGES + 4) * 8 + 16 + 1024;
     auto kern = gemm_tc_kernel<BN, STAGES>;
     static bool configured = false;
@@ -259,7 +337,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int 
     }
     const long long items = (long long)total * splits;
     kern<<<items < n_sms ? (int)items : n_sms, TC_THREADS, smem, stream>>>(ma, mw, C, ldc, out_is_f32, M, N, K, mode,
-                                                                           m_tiles, total, splits, error_word);
+                                                                           m_tiles, total, splits, error_word, rope);
     return ssb_launch_status();
 }
 
@@ -288,8 +366,9 @@ SSB_API int ssb_tc_wait_probe(int* error_word, cudaStream_t stream) {
 // (bfloat16 or float32); mode 1: C (float32) += ; mode 2: W's rows come as [8 gate | 8 up] per 16
 // and C (bfloat16, [M, N/2]) = silu(gate) * up.  splits > 1 (mode 1 only): K is cut into that many
 // parts per tile, which add with float atomics.  error_word: device int, zero while all is well.
-SSB_API int ssb_gemm_tc(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int out_dtype, int M,
-                        int N, int K, int mode, int tile_n, int splits, int* error_word, cudaStream_t stream) {
+static int gemm_tc_any(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int out_dtype, int M,
+                       int N, int K, int mode, int tile_n, int splits, int* error_word, const TcRope& rope,
+                       cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || lda % 8 || ldw % 8 || N % 8 || !error_word) return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)C) & 15) return SSB_ERR_BAD_SIZE;
@@ -304,7 +383,31 @@ SSB_API int ssb_gemm_tc(const void* A, int lda, const void* W, int ldw, void* C,
     rc = make_map(&mw, W, N, K, ldw, bn);
     if (rc) return rc;
     const int f32o = out_dtype == SSB_F32;
-    if (bn == 64) return launch_tc<64, 8>(ma, mw, C, ldc, f32o, M, N, K, mode, splits, error_word, stream);
-    if (bn == 128) return launch_tc<128, 6>(ma, mw, C, ldc, f32o, M, N, K, mode, splits, error_word, stream);
-    return launch_tc<256, 4>(ma, mw, C, ldc, f32o, M, N, K, mode, splits, error_word, stream);
+    if (bn == 64) return launch_tc<64, 8>(ma, mw, C, ldc, f32o, M, N, K, mode, splits, error_word, rope, stream);
+    if (bn == 128) return launch_tc<128, 6>(ma, mw, C, ldc, f32o, M, N, K, mode, splits, error_word, rope, stream);
+    return launch_tc<256, 4>(ma, mw, C, ldc, f32o, M, N, K, mode, splits, error_word, rope, stream);
+}
+
+SSB_API int ssb_gemm_tc(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int out_dtype, int M,
+                        int N, int K, int mode, int tile_n, int splits, int* error_word, cudaStream_t stream) {
+    if (mode < TC_STORE || mode > TC_SWIGLU) return SSB_ERR_BAD_SIZE;
+    return gemm_tc_any(A, lda, W, ldw, C, ldc, out_dtype, M, N, K, mode, tile_n, splits, error_word, TcRope{}, stream);
+}
+
+// The fused query/key/value projection of packed tokens with rotation and cache append in the
+// epilogue (see TcRope): A [M, K], W [(n_q + 2 n_kv) head_dim, K], C bfloat16 [M, >= n_q head_dim]
+// receives the rotated queries.  head_dim 64 or 128; tables [table_positions, head_dim/2] float32.
+SSB_API int ssb_gemm_tc_rope_append(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int K,
+                                    const int* pos, const int* slot, const int* page_table, int max_pages,
+                                    void* k_cache, void* v_cache, const float* cos_t, const float* sin_t,
+                                    int n_q, int n_kv, int head_dim, int page_shift, int* error_word,
+                                    cudaStream_t stream) {
+    if ((head_dim != 64 && head_dim != 128) || n_q <= 0 || n_kv <= 0 || !pos || !slot || !page_table || !cos_t ||
+        !sin_t || !k_cache || !v_cache || page_shift < 0 || page_shift > 20)
+        return SSB_ERR_BAD_SIZE;
+    if (((uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) return SSB_ERR_BAD_SIZE;
+    TcRope rope{pos, slot, page_table, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, cos_t, sin_t,
+                max_pages, n_q, n_kv, head_dim, page_shift};
+    return gemm_tc_any(A, lda, W, ldw, C, ldc, SSB_BF16, M, (n_q + 2 * n_kv) * head_dim, K, TC_ROPE_APPEND, 256, 1,
+                       error_word, rope, stream);
 }

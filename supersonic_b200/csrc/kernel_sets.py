@@ -81,6 +81,11 @@ class PlainKernels:
         self.linear(x, w_gate_up, gate_up)
         ops.swiglu(gate_up, out, interleaved=(layout == "interleaved"))
 
+    def project_rope_append(self, x, w_qkv, qkv, position, kv, batch, n_q, n_kv, head_dim, page_shift) -> bool:
+        """The q/k/v projection with position encoding and cache append in one kernel: rotated q
+        into ``qkv``'s first columns, k and v into the cache.  False: not taken, nothing was done."""
+        return False
+
     def rope_append(self, qkv, cos, sin, batch, page_table, k_cache, v_cache, n_q, n_kv, head_dim,
                     rotary_dim, page_shift, write_cache=True):
         ops.rope_append(qkv, cos, sin, batch.pos, batch.slot_of_token, page_table, k_cache, v_cache,

@@ -444,6 +444,41 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_
         _ptr(tc_error_word(a.device)), _stream()), "gemm_tc")
 
 
+def gemm_tc_rope_append(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cos: torch.Tensor,
+                        sin: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor, page_table: torch.Tensor,
+                        k_cache: torch.Tensor, v_cache: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
+                        page_shift: int) -> None:
+    """The fused query/key/value projection of packed tokens (``w`` = [q; k; v] rows) on tcgen05
+    whose epilogue rotates q and k from the float32 sums, writes q (bfloat16) into ``q_out`` and
+    k and v into the paged cache entry; nothing else is written.  head_dim 64 or 128, full-width
+    rotation, tables [positions, head_dim/2] float32.  Rows with a negative slot are skipped."""
+    _need(a, "a", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(q_out, "q_out", torch.bfloat16, 2)
+    _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1); _need(page_table, "page_table", torch.int32, 2)
+    _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+    _need(k_cache, "k_cache", torch.bfloat16); _need(v_cache, "v_cache", torch.bfloat16)
+    M, K = a.shape
+    if head_dim not in (64, 128):
+        raise KernelError(f"gemm_tc_rope_append: head_dim {head_dim} (64 or 128)")
+    if tuple(w.shape) != ((n_q + 2 * n_kv) * head_dim, K) or q_out.shape[0] != M or q_out.shape[1] < n_q * head_dim:
+        raise KernelError(f"gemm_tc_rope_append: shapes a{tuple(a.shape)} w{tuple(w.shape)} q_out{tuple(q_out.shape)}")
+    if pos.shape[0] != M or slot.shape[0] != M:
+        raise KernelError("gemm_tc_rope_append: one position and one slot per row")
+    if cos.shape != sin.shape or cos.shape[1] * 2 != head_dim or not (cos.is_contiguous() and sin.is_contiguous()):
+        raise KernelError("gemm_tc_rope_append: cos/sin must be [positions, head_dim/2], contiguous")
+    if not k_cache.is_contiguous() or not v_cache.is_contiguous() or k_cache.shape != v_cache.shape \
+            or tuple(k_cache.shape[1:]) != (n_kv, 1 << page_shift, head_dim):
+        raise KernelError(f"gemm_tc_rope_append: cache shape {tuple(k_cache.shape)}")
+    if not gemm_tc_ok(a, w, q_out):
+        raise KernelError("gemm_tc_rope_append: operands must be 16-byte aligned with strides in multiples of 8")
+    global _tc_unchecked
+    _tc_unchecked += 1
+    _check(_fn("gemm_tc", "ssb_gemm_tc_rope_append")(
+        _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(q_out), c_int(q_out.stride(0)), c_int(M),
+        c_int(K), _ptr(pos), _ptr(slot), _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache),
+        _ptr(cos), _ptr(sin), c_int(n_q), c_int(n_kv), c_int(head_dim), c_int(page_shift),
+        _ptr(tc_error_word(a.device)), _stream()), "gemm_tc_rope_append")
+
+
 # ---- prefill attention -------------------------------------------------------------------------
 def attention_prefill_ok(q: torch.Tensor, head_dim: int) -> bool:
     return q.dtype == torch.bfloat16 and head_dim in (64, 128) and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0

@@ -5,7 +5,7 @@
 #include <cuda.h>
 
 constexpr int TC_BK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
-enum { TC_STORE = 0, TC_ACCUMULATE = 1, TC_SWIGLU = 2 };
+enum { TC_STORE = 0, TC_ACCUMULATE = 1, TC_SWIGLU = 2, TC_ROPE_APPEND = 3 };
 enum { TC_ERR_PRODUCER = 1, TC_ERR_MMA = 2, TC_ERR_EPILOGUE = 3 };   // which role's wait ran out
 
 // ---- PTX wrappers ------------------------------------------------------------------------

@@ -60,8 +60,15 @@ class Attention:
         kv = ctx.cache.kv(cache_id)
         width = (self.n_q + (2 * self.n_kv if writes_cache else 0)) * self.head_dim
         qkv = torch.empty((T, width), dtype=self.dtype, device=residual.device)
-        ctx.kernels.linear(x, self.w_qkv if writes_cache else self.w_q, qkv)
         attn = torch.empty((T, self.n_q * self.head_dim), dtype=self.dtype, device=residual.device)
+        if writes_cache and ctx.kernels.project_rope_append(x, self.w_qkv, qkv, position, kv, ctx.batch, self.n_q,
+                                                           self.n_kv, self.head_dim, PAGE_SHIFT):
+            k_cache, v_cache, table, _ = kv          # q is rotated, k and v are in the cache
+            ctx.kernels.attention(qkv, k_cache, v_cache, ctx.batch, table, attn, self.n_q, self.n_kv,
+                                  self.head_dim, PAGE_SHIFT, self.window, self.scale)
+            ctx.kernels.linear(attn, self.w_o, residual, accumulate=True, then_norm=getattr(ctx, "next_norm", None))
+            return
+        ctx.kernels.linear(x, self.w_qkv if writes_cache else self.w_q, qkv)
         if not (writes_cache and ctx.kernels.rope_attention(qkv, position, kv, ctx.batch, attn, self.n_q,
                                                            self.n_kv, self.head_dim, PAGE_SHIFT,
                                                            self.window, self.scale)):

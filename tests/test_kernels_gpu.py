@@ -761,6 +761,52 @@ def test_rmsnorm_vec_equals_plain(wdtype, hidden):
         torch.testing.assert_close(got.float(), want.float(), atol=0, rtol=2 ** -7)
 
 
+@pytest.mark.parametrize("n_q,n_kv,hd,K,T", [(3, 1, 128, 192, 300), (5, 2, 64, 264, 129), (9, 3, 64, 64, 513)])
+def test_projection_with_rope_and_append_in_its_epilogue(n_q, n_kv, hd, K, T):
+    """gemm_tc_rope_append against float32: rotated queries in the output, rotated keys and plain
+    values at each token's page and place; other cache rows, skipped rows' outputs and the output's
+    spare columns untouched.  Widths end inside a tile of 256 columns and inside a tile of 128 rows."""
+    g = torch.Generator(device=DEV).manual_seed(181)
+    n_slots, max_pages = 3, (T + 63) // 64 + 1
+    a = torch.randn(T, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn((n_q + 2 * n_kv) * hd, K, device=DEV, generator=g) / K ** 0.5).bfloat16()
+    # three sequences that continue at different places; a cache row is written once
+    slot = (torch.arange(T) % n_slots).to(torch.int32)
+    pos = (torch.arange(T) // n_slots + torch.tensor([0, 37, 64])[slot.long()]).to(torch.int32)
+    slot[5], slot[T - 1] = -1, -1
+    slot, pos = slot.to(DEV), pos.to(DEV)
+    n_pages = n_slots * max_pages
+    table = torch.randperm(n_pages, generator=torch.Generator().manual_seed(184)).to(torch.int32).view(n_slots, max_pages).to(DEV)
+    n_pos = int(pos.max()) + 1
+    ang = torch.arange(n_pos, device=DEV, dtype=torch.float64)[:, None] * \
+        (1.0 / 500000 ** (torch.arange(hd // 2, device=DEV, dtype=torch.float64) * 2 / hd))[None, :]
+    cos, sin = ang.cos().float().contiguous(), ang.sin().float().contiguous()
+    k0, v0 = _paged(n_pages, n_kv, hd, torch.bfloat16, 185)
+    kc, vc = k0.clone(), v0.clone()
+    out = torch.full((T, n_q * hd + 8), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops().gemm_tc_rope_append(a, w, out, cos, sin, pos, slot, table, kc, vc, n_q, n_kv, hd, 6)
+    ops().check_device_errors()
+    sums = (a.double() @ w.double().T).view(T, n_q + 2 * n_kv, hd)
+    lo, hi = sums[..., : hd // 2], sums[..., hd // 2:]
+    c, sn = ang.cos()[pos.long()][:, None, :], ang.sin()[pos.long()][:, None, :]
+    rot = torch.cat([lo * c - hi * sn, lo * sn + hi * c], dim=-1)
+    live = slot >= 0
+    tol = dict(atol=2e-2, rtol=2 ** -7)                      # one bfloat16 rounding of sums of size ~1
+    torch.testing.assert_close(out[live, : n_q * hd].double(), rot[live, :n_q].reshape(-1, n_q * hd), **tol)
+    assert (out[:, n_q * hd:] == 7.0).all() and (out[~live] == 7.0).all()
+    want_k, want_v = k0.double(), v0.double()
+    page = table[slot.clamp(min=0).long(), (pos >> 6).long()].long()
+    for t in torch.nonzero(live).flatten().tolist():
+        want_k[page[t], :, int(pos[t]) & 63] = rot[t, n_q: n_q + n_kv]
+        want_v[page[t], :, int(pos[t]) & 63] = sums[t, n_q + n_kv:]
+    torch.testing.assert_close(kc.double(), want_k, **tol)
+    torch.testing.assert_close(vc.double(), want_v, **tol)
+    untouched = torch.ones(n_pages, 64, dtype=torch.bool, device=DEV)
+    untouched[page[live], (pos[live] & 63).long()] = False
+    assert torch.equal(kc.transpose(1, 2)[untouched], k0.transpose(1, 2)[untouched])
+    assert torch.equal(vc.transpose(1, 2)[untouched], v0.transpose(1, 2)[untouched])
+
+
 @pytest.mark.parametrize("n_q,n_kv,hd", [(4, 2, 16), (3, 1, 48), (32, 8, 128), (5, 5, 64)])
 def test_rope_append_vec_equals_plain(n_q, n_kv, hd):
     g = torch.Generator(device=DEV).manual_seed(81)
