@@ -110,6 +110,8 @@ class FastKernels(PlainKernels):
                 # zeroed scratch that round_and_clear turns into bfloat16 (as for decode above)
                 tile_n = self._tile_n(rows, n)
                 splits = self._gemm_splits(rows, n, k, tile_n)
+                if splits == 1 and self._pair_tiles(rows, n):
+                    tile_n = ops.TC_TILE_PAIR
                 if splits > 1 and accumulate:
                     ops.gemm_tc(x, weight, out, ops.TC_ACCUMULATE, tile_n=tile_n, splits=splits)
                 elif splits > 1 and out.dtype == torch.bfloat16 and n % 8 == 0 and out.stride(0) % 8 == 0:
@@ -130,6 +132,14 @@ class FastKernels(PlainKernels):
         per SM walks them); at least 8 k-blocks (512 columns) a part; 1 when the tiles alone do."""
         tiles = ((rows + 127) // 128) * ((n + tile_n - 1) // tile_n)
         return max(1, min(148 // tiles, (k // 64) // 8, 16))
+
+    @staticmethod
+    def _pair_tiles(rows: int, n: int) -> bool:
+        """Tiles of 256 x 256 on SM pairs: each SM fetches a third less per k-block than with a
+        128 x 256 tile of its own, and L2-to-shared-memory bandwidth is what bounds these products
+        (2,048 rows of the 8B shapes: 374 to 347 us gate/up, 202 to 184 down, 89 to 79 q/k/v, 72 to
+        62 o).  Not where the second half of the last 256 rows would be mostly padding."""
+        return n >= 256 and (rows >= 1024 or ((rows + 127) // 128) % 2 == 0)
 
     @staticmethod
     def _tile_n(rows: int, n: int) -> int:
@@ -156,7 +166,9 @@ class FastKernels(PlainKernels):
                 if rows <= 64:
                     ops.gemv_tc(xt, w_gate_up, out, ops.TC_SWIGLU, pdl=self.pdl)
                 else:
-                    ops.gemm_tc(xt, w_gate_up, out, ops.TC_SWIGLU, tile_n=self._tile_n(rows, w_gate_up.shape[0]))
+                    n2 = w_gate_up.shape[0]
+                    ops.gemm_tc(xt, w_gate_up, out, ops.TC_SWIGLU,
+                                tile_n=ops.TC_TILE_PAIR if self._pair_tiles(rows, n2) else self._tile_n(rows, n2))
                 return
         if layout == "interleaved" and rows <= 64 and self._skinny(x, w_gate_up, out, ops.SG_SWIGLU):
             return
@@ -233,7 +245,8 @@ class FastKernels(PlainKernels):
             return False
         position.check_range(batch)
         ops.gemm_tc_rope_append(x, w_qkv, qkv, cos, sin, batch.pos, batch.slot_of_token, page_table, k_cache,
-                                v_cache, n_q, n_kv, head_dim, page_shift)
+                                v_cache, n_q, n_kv, head_dim, page_shift,
+                                tile_n=ops.TC_TILE_PAIR if self._pair_tiles(rows, n) else 256)
         return True
 
     def rope_attention(self, qkv, position, kv, batch, out, n_q, n_kv, head_dim, page_shift, window,

@@ -111,12 +111,13 @@ def gemm(args):
     a = torch.randn(M, K, device=DEV).bfloat16()
     if args.accumulate:                               # add into a float32 output, as the o and down projections do
         out = torch.zeros(M, N, device=DEV)
-        us = _time(lambda i: ops.gemm_tc(a, ws[i % copies], out, mode=ops.TC_ACCUMULATE, tile_n=args.tile), args.iters)
+        us = _time(lambda i: ops.gemm_tc(a, ws[i % copies], out, mode=ops.TC_ACCUMULATE, tile_n=args.tile,
+                                         splits=args.k_parts), args.iters)
     else:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
         us = _time(lambda i: ops.gemm_tc(a, ws[i % copies], out, tile_n=args.tile), args.iters)
     ops.check_device_errors()
-    return {"kernel": f"gemm_tc{args.tile}", "accumulate": bool(args.accumulate), "m": M, "n": N, "k": K, "us": round(us, 2),
+    return {"kernel": f"gemm_tc{args.tile}", "accumulate": bool(args.accumulate), "k_parts": args.k_parts, "m": M, "n": N, "k": K, "us": round(us, 2),
             "TFLOP/s": round(2.0 * M * N * K / us / 1e6, 1)}
 
 
@@ -158,6 +159,7 @@ def main(argv=None):
         p.add_argument("--k", type=int, default=4096)
         p.add_argument("--kernel", default="skinny")
         p.add_argument("--tile", type=int, default=256)
+        p.add_argument("--k-parts", type=int, default=1, help="gemm --accumulate: parts a tile's K range is cut into")
         p.add_argument("--kind", type=int, default=0, help="attention_decode: 0 auto, 1 general, 2 tensor-core")
         p.add_argument("--accumulate", action="store_true", help="linear gv*, gemm: add into a float32 output")
         p.add_argument("--pdl", action="store_true", help="launch as programmatic dependents")

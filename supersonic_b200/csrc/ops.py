@@ -349,6 +349,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
 
 # ---- prefill GEMM on tcgen05 ---------------------------------------------------------------
 TC_STORE, TC_ACCUMULATE, TC_SWIGLU = 0, 1, 2
+TC_TILE_PAIR = 512        # ``tile_n`` that asks for 256 x 256 tiles on SM pairs (tcgen05 cta_group::2)
 _TC_ERRORS = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}
 _tc_error_words = {}
 _tc_unchecked = 0      # tcgen05 launches since the error words were last read
@@ -436,6 +437,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_
         raise KernelError(f"gemm_tc: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
     if tile_n is None:
         tile_n = 256 if N > 128 else 128
+    if tile_n == TC_TILE_PAIR and splits != 1:
+        raise KernelError("gemm_tc: tiles on SM pairs do not split K")
     global _tc_unchecked
     _tc_unchecked += 1
     _check(_fn("gemm_tc", "ssb_gemm_tc")(
@@ -447,7 +450,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_
 def gemm_tc_rope_append(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cos: torch.Tensor,
                         sin: torch.Tensor, pos: torch.Tensor, slot: torch.Tensor, page_table: torch.Tensor,
                         k_cache: torch.Tensor, v_cache: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
-                        page_shift: int) -> None:
+                        page_shift: int, tile_n: int = 256) -> None:
     """The fused query/key/value projection of packed tokens (``w`` = [q; k; v] rows) on tcgen05
     whose epilogue rotates q and k from the float32 sums, writes q (bfloat16) into ``q_out`` and
     k and v into the paged cache entry; nothing else is written.  head_dim 64 or 128, full-width
@@ -475,7 +478,7 @@ def gemm_tc_rope_append(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, c
     _check(_fn("gemm_tc", "ssb_gemm_tc_rope_append")(
         _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(q_out), c_int(q_out.stride(0)), c_int(M),
         c_int(K), _ptr(pos), _ptr(slot), _ptr(page_table), c_int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache),
-        _ptr(cos), _ptr(sin), c_int(n_q), c_int(n_kv), c_int(head_dim), c_int(page_shift),
+        _ptr(cos), _ptr(sin), c_int(n_q), c_int(n_kv), c_int(head_dim), c_int(page_shift), c_int(tile_n),
         _ptr(tc_error_word(a.device)), _stream()), "gemm_tc_rope_append")
 
 

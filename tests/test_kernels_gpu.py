@@ -456,7 +456,7 @@ def test_fast_linear_picks_a_kernel_for_every_row_count(rows, N, K):
 # ---- prefill GEMM on tcgen05 ------------------------------------------------------------------
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (65, 128, 200), (200, 304, 72), (300, 1000, 4096),
                                    (1024, 512, 1024), (129, 8, 64)])
-@pytest.mark.parametrize("tile_n", [64, 128, 256])
+@pytest.mark.parametrize("tile_n", [64, 128, 256, 512])         # 512: tiles of 256 x 256 on SM pairs
 def test_gemm_tc(M, N, K, tile_n):
     g = torch.Generator(device=DEV).manual_seed(30)
     a = torch.randn(M, K, device=DEV, generator=g).bfloat16()
@@ -521,8 +521,9 @@ def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable():
     torch.testing.assert_close(out.double(), a.double() @ w.double().T, atol=1e-3, rtol=1e-4)
 
 
-@pytest.mark.parametrize("M,inter,K", [(130, 200, 72), (256, 1024, 512)])
-def test_gemm_tc_swiglu(M, inter, K):
+@pytest.mark.parametrize("tile_n", [256, 512])
+@pytest.mark.parametrize("M,inter,K", [(130, 200, 72), (256, 1024, 512), (700, 1160, 320)])
+def test_gemm_tc_swiglu(M, inter, K, tile_n):
     g = torch.Generator(device=DEV).manual_seed(31)
     x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
     gate = (torch.randn(inter, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
@@ -530,7 +531,7 @@ def test_gemm_tc_swiglu(M, inter, K):
     from supersonic_b200.csrc.fast_sets import FastKernels
     packed, layout = FastKernels().pack_gate_up(gate, up)
     out = torch.empty(M, inter, dtype=torch.bfloat16, device=DEV)
-    ops().gemm_tc(x, packed, out, mode=2)
+    ops().gemm_tc(x, packed, out, mode=2, tile_n=tile_n)
     ops().check_device_errors()
     gg, uu = x.double() @ gate.double().T, x.double() @ up.double().T
     torch.testing.assert_close(out.double(), gg / (1 + torch.exp(-gg)) * uu, atol=2e-2, rtol=2e-2)
@@ -761,8 +762,9 @@ def test_rmsnorm_vec_equals_plain(wdtype, hidden):
         torch.testing.assert_close(got.float(), want.float(), atol=0, rtol=2 ** -7)
 
 
+@pytest.mark.parametrize("tile_n", [256, 512])
 @pytest.mark.parametrize("n_q,n_kv,hd,K,T", [(3, 1, 128, 192, 300), (5, 2, 64, 264, 129), (9, 3, 64, 64, 513)])
-def test_projection_with_rope_and_append_in_its_epilogue(n_q, n_kv, hd, K, T):
+def test_projection_with_rope_and_append_in_its_epilogue(n_q, n_kv, hd, K, T, tile_n):
     """gemm_tc_rope_append against float32: rotated queries in the output, rotated keys and plain
     values at each token's page and place; other cache rows, skipped rows' outputs and the output's
     spare columns untouched.  Widths end inside a tile of 256 columns and inside a tile of 128 rows."""
@@ -784,7 +786,7 @@ def test_projection_with_rope_and_append_in_its_epilogue(n_q, n_kv, hd, K, T):
     k0, v0 = _paged(n_pages, n_kv, hd, torch.bfloat16, 185)
     kc, vc = k0.clone(), v0.clone()
     out = torch.full((T, n_q * hd + 8), 7.0, device=DEV, dtype=torch.bfloat16)
-    ops().gemm_tc_rope_append(a, w, out, cos, sin, pos, slot, table, kc, vc, n_q, n_kv, hd, 6)
+    ops().gemm_tc_rope_append(a, w, out, cos, sin, pos, slot, table, kc, vc, n_q, n_kv, hd, 6, tile_n=tile_n)
     ops().check_device_errors()
     sums = (a.double() @ w.double().T).view(T, n_q + 2 * n_kv, hd)
     lo, hi = sums[..., : hd // 2], sums[..., hd // 2:]
