@@ -27,14 +27,6 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// Persistent: a block takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulators of
-// consecutive tiles alternate between two regions of tensor memory, so that the epilogue of one
-// tile (tcgen05.ld, conversion, stores) runs while the MMAs of the next are issued.
-//
-// splits > 1 (float32 output, mode accumulate): a prompt of a few hundred tokens has fewer output
-// tiles than the GPU has SMs, and the few blocks cannot pull the weights at the memory's rate.
-// The K range of every tile is then cut into ``splits`` parts, each a work item of its own, and
-// the parts add into the output with float atomics.
 // Mode rope-and-append: the product is the fused query/key/value projection of packed tokens.  The
 // epilogue rotates query and key heads by each token's position (float32 tables, pairs d and
 // d + head_dim/2, from the float32 accumulators: one rounding), writes the queries as bfloat16
@@ -195,13 +187,21 @@ struct TcItem {
     }
 };
 
+// Persistent: a block takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The accumulators of
+// consecutive tiles alternate between two regions of tensor memory, so that the epilogue of one
+// tile (tcgen05.ld, conversion, stores) runs while the MMAs of the next are issued.
+//
+// splits > 1 (float32 output, mode accumulate): a prompt of a few hundred tokens has fewer output
+// tiles than the GPU has SMs, and the few blocks cannot pull the weights at the memory's rate.
+// The K range of every tile is then cut into ``splits`` parts, each a work item of its own, and
+// the parts add into the output with float atomics.
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                void* __restrict__ C, int ldc, int out_is_f32, int M, int N, int K, int mode, int m_tiles,
                int n_tiles_total, int splits, int* __restrict__ error_word, const TcRope rope) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
-    constexpr int N_ACC = BN <= 128 ? 2 : 2;                       // accumulator regions (2 x BN <= 512 columns)
+    constexpr int N_ACC = 2;                                        // accumulator regions (2 x BN <= 512 columns)
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
