@@ -55,6 +55,32 @@ def decode_pages_bucket(longest: int, page_tokens: int = 64) -> int:
     return 1 << (pages.bit_length() - 1)
 
 
+def plan_chunks(counts: Sequence[int], budget: int) -> List[List[tuple]]:
+    """Cut a step of ``counts[i]`` tokens per entry into sub-steps of at most ``budget`` tokens.
+
+    Returns a list of chunks; a chunk is a list of ``(entry, first, end)``: tokens
+    ``first .. end - 1`` of that entry.  Entries keep their order, an entry that does not fit what
+    is left of a chunk goes on in the next one, and no entry appears twice in a chunk, so a chunk
+    is a step of its own whose sequences continue what earlier chunks left in the cache (the
+    reference carries a long prompt through its cache in the same way, chunk by chunk:
+    crates/runner/src/prefill_engine.rs:1081-1094)."""
+    if budget < 1:
+        raise ValueError(f"a step's token budget must be at least 1, not {budget}")
+    chunks: List[List[tuple]] = [[]]
+    room = budget
+    for i, n in enumerate(counts):
+        first = 0
+        while first < n:
+            if room == 0:
+                chunks.append([])
+                room = budget
+            take = min(room, n - first)
+            chunks[-1].append((i, first, first + take))
+            first += take
+            room -= take
+    return [c for c in chunks if c]
+
+
 def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], device,
               vocab_size: Optional[int] = None) -> StepBatch:
     """Lay the entries out back to back and move the index arrays to ``device`` in one copy."""

@@ -16,6 +16,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import KvNeed, SequenceCache, StateNeed
@@ -24,7 +25,7 @@ from ..csrc.kernel_sets import kernel_set_for
 from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
                      BuildContext, WeightAccess, lookup)
 from ..weights import WeightStore
-from .batch import StepBatch, StepEntry, decode_pages_bucket, pack_step
+from .batch import StepBatch, StepEntry, decode_pages_bucket, pack_step, plan_chunks
 
 _DTYPES = {"float32": torch.float32, "fp32": torch.float32, "f32": torch.float32,
            "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
@@ -118,7 +119,7 @@ class Model:
     def __init__(self, spec: ModelSpec, store: WeightStore, dtype="bfloat16", device="cuda:0",
                  max_tokens: int = 4096, max_seq_tokens: Optional[int] = None,
                  max_slots: Optional[int] = None, kernels: Optional[str] = None, config=None,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, step_token_budget: int = 32768):
         spec.validate()
         self.spec, self.config = spec, config
         self.dtype = parse_dtype(dtype)
@@ -157,6 +158,10 @@ class Model:
                                  f"{needs.get(stop.cache)} is not its own {need}")
         self.cache = SequenceCache({c: n for c, n in needs.items() if n is not None}, max_tokens,
                                    max_seq, self.dtype, self.device, max_slots)
+        # a step of more tokens runs as several, chunk by chunk through the cache (``_chunked_step``)
+        self.step_token_budget = int(step_token_budget)
+        if self.step_token_budget < 1:
+            raise ValueError("step_token_budget must be at least 1")
         # decode steps of the serving path replay captured graphs (one per batch size and page bucket)
         self.use_graphs = use_graphs and self.kernels.name == "fast"
         self._graphs: Dict[Any, DecodeGraph] = {}
@@ -191,6 +196,8 @@ class Model:
         starts = [cache.length(e.slot) for e in entries]
         if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             return self._graph_step(entries, starts)
+        if sum(len(e.tokens) for e in entries) > self.step_token_budget:
+            return self._chunked_step(entries)
         batch = pack_step(entries, starts, self.device, self.spec.vocab_size)
         for e in entries:          # pages a failed step reserved stay with their slots
             cache.reserve(e.slot, len(e.tokens))
@@ -199,6 +206,34 @@ class Model:
         for e in entries:
             cache.advance(e.slot, len(e.tokens))
         return logits
+
+    def _chunked_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """A step of more tokens than ``step_token_budget``: the same tokens as several steps, each
+        continuing from the cache the one before left.  Bounds the activations a step holds
+        (a float32 residual, the query/key/value rows and the feed-forward's inner rows per token)
+        whatever the prompts' lengths; the logits are those of the one step, beyond rounding."""
+        slots = [e.slot for e in entries]
+        if len(set(slots)) != len(slots):
+            raise ValueError("a slot appears twice in one step")
+        counts = [len(e.tokens) for e in entries]
+        for e, n in zip(entries, counts):
+            if n == 0:
+                raise ValueError(f"slot {e.slot}: an entry must bring at least one token")
+            bad = [w for w in e.want if not 0 <= w < n]
+            if bad:
+                raise ValueError(f"slot {e.slot}: wanted place {bad[0]} is outside its {n} tokens")
+            toks = np.asarray(e.tokens, dtype=np.int64)
+            off = toks[(toks < 0) | (toks >= self.spec.vocab_size)]
+            if off.size:
+                raise ValueError(f"token ids {off[:8].tolist()} are outside the vocabulary of {self.spec.vocab_size}")
+        for e, n in zip(entries, counts):     # all the room first: nothing runs if the step does not fit
+            self.cache.reserve(e.slot, n)
+        rows = []
+        for chunk in plan_chunks(counts, self.step_token_budget):
+            piece = [StepEntry(entries[i].slot, entries[i].tokens[lo:hi],
+                               [w - lo for w in entries[i].want if lo <= w < hi]) for i, lo, hi in chunk]
+            rows.append(self.step(piece))
+        return torch.cat(rows) if len(rows) > 1 else rows[0]
 
     def _graph_step(self, entries, starts) -> torch.Tensor:
         cache = self.cache

@@ -191,3 +191,39 @@ def test_widths_the_fast_kernels_refuse_still_give_the_right_logits(tmp_path, dt
     got = torch.cat(got).double().cpu().numpy()
     tol = 2e-5 if dtype == "float32" else 2e-2 * np.abs(ref).max()
     assert np.abs(got - ref).max() < tol
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,budget", [("B", 7), ("D", 100), ("E", 129)])
+def test_a_step_over_its_token_budget_runs_in_chunks_with_the_same_logits(model_folders, name, budget, dtype):
+    """Three prompts of unequal lengths in one step that the model cuts into chunks (a prompt ends
+    inside a chunk, a prompt spans three chunks, a chunk holds one token of a prompt), then decoding:
+    the wanted logits come back in the order of the entries and of their places, and equal the
+    plain implementation's."""
+    from supersonic_b200.engine import Model, StepEntry
+    d, pc, pw = model_folders[name]
+    rng = np.random.default_rng(21)
+    lens = [budget + 1, 3, 2 * budget + 5] if name != "B" else [8, 3, 19]
+    seqs = [rng.integers(0, pc["vocab_size"], n + 2).tolist() for n in lens]
+    refs = [pl.forward(pc, pw, s) for s in seqs]
+    tol = 2e-5 if dtype == "float32" else 2e-2 * max(np.abs(r).max() for r in refs)
+    m = Model.from_dir(d, dtype=dtype, max_tokens=1024, step_token_budget=budget)
+    slots = [m.open_sequence() for _ in seqs]
+    wants = [[0, n - 1] for n in lens]
+    wants[2] = [0, budget - 1, budget, lens[2] - 1]
+    got = m.step([StepEntry(s, q[:n], w) for s, q, n, w in zip(slots, seqs, lens, wants)]).double().cpu().numpy()
+    want_rows = np.concatenate([r[w] for r, w in zip(refs, wants)])
+    assert got.shape == want_rows.shape
+    assert np.abs(got - want_rows).max() < tol
+    assert [m.cache.length(s) for s in slots] == lens
+    for t in range(2):
+        got = m.step([StepEntry(s, [q[n + t]], [0]) for s, q, n in zip(slots, seqs, lens)]).double().cpu().numpy()
+        assert np.abs(got - np.stack([r[n + t] for r, n in zip(refs, lens)])).max() < tol
+    for s in slots:
+        m.close_sequence(s)
+    m.cache.check()
+    # a step that does not fit the cache runs nothing
+    s0 = m.open_sequence()
+    with pytest.raises(Exception):
+        m.step([StepEntry(s0, [1] * 2000, [])])
+    assert m.cache.length(s0) == 0

@@ -149,3 +149,34 @@ def test_request_seeds_differ_and_are_stable():
         SamplingParams(top_p=0.0)
     assert SamplingParams().greedy and SamplingParams(temperature=0.7, top_k=1).greedy
     assert not SamplingParams(temperature=0.7).greedy
+
+
+def test_a_long_step_is_cut_into_chunks_that_keep_order_and_budget():
+    """The planner of a step that exceeds its token budget: every token once, in order, no chunk
+    over the budget, no entry twice in a chunk, no empty chunk."""
+    import random
+    from supersonic_b200.engine.batch import plan_chunks
+    assert plan_chunks([5, 3], 100) == [[(0, 0, 5), (1, 0, 3)]]
+    assert plan_chunks([5, 3], 4) == [[(0, 0, 4)], [(0, 4, 5), (1, 0, 3)]]
+    assert plan_chunks([4, 4], 4) == [[(0, 0, 4)], [(1, 0, 4)]]
+    assert plan_chunks([1, 9, 1], 3) == [[(0, 0, 1), (1, 0, 2)], [(1, 2, 5)], [(1, 5, 8)], [(1, 8, 9), (2, 0, 1)]]
+    with pytest.raises(ValueError):
+        plan_chunks([3], 0)
+    rnd = random.Random(5)
+    for _ in range(200):
+        counts = [rnd.randint(1, 40) for _ in range(rnd.randint(1, 9))]
+        budget = rnd.randint(1, 50)
+        chunks = plan_chunks(counts, budget)
+        seen = [[] for _ in counts]
+        for c in chunks:
+            assert c and sum(hi - lo for _, lo, hi in c) <= budget
+            assert len({i for i, _, _ in c}) == len(c)
+            assert [i for i, _, _ in c] == sorted(i for i, _, _ in c)
+            for i, lo, hi in c:
+                assert lo < hi
+                seen[i].append((lo, hi))
+        for n, parts in zip(counts, seen):
+            assert parts[0][0] == 0 and parts[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(parts, parts[1:]))
+        # full chunks except the last
+        assert all(sum(hi - lo for _, lo, hi in c) == budget for c in chunks[:-1])
