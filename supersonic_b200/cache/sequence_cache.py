@@ -137,6 +137,7 @@ class SequenceCache:
         self.pages_per_seq = min(pages_for(max_seq_tokens), self.n_pages)
         self.max_seq_tokens = self.pages_per_seq * PAGE_TOKENS
         self.max_slots = max_slots if max_slots is not None else min(self.n_pages, 4096)
+        self._preflight(needs, max_tokens, max_seq_tokens)
         self.slots = FreeList(self.max_slots, "slot")
         self._length = [0] * self.max_slots
         # groups by need
@@ -158,76 +159,40 @@ class SequenceCache:
             for cid, need in state_entries}
         self.rng_state = torch.zeros(self.max_slots, dtype=torch.int64, device=device)
 
-    # ---- slots ------------------------------------------------------------------------
-    def acquire(self, rng_seed: Optional[int] = None) -> int:
-        """A free slot with length 0, zeroed fixed state and a seeded generator."""
-        slot = self.slots.take()
-        self._length[slot] = 0
-        for t in self._state.values():
-            t[slot].zero_()
-        if rng_seed is not None:
-            self.seed(slot, rng_seed)
-        return slot
-
-    def seed(self, slot: int, seed: int) -> None:
-        """Set the slot's xorshift64 generator state (a non-zero 64-bit value)."""
-        seed &= (1 << 64) - 1
-        if seed == 0:
-            seed = 0x9E3779B97F4A7C15       # xorshift needs a non-zero state (qwen36_moe_decode.rs:1091-1094)
-        if seed >= 1 << 63:
-            seed -= 1 << 64
-        self.rng_state[slot] = seed
-
-    def release(self, slot: int) -> None:
-        for pid in self.held[slot].values():
-            self.pool.give_back(pid)
-        self.held[slot].clear()
-
-    def sync(self) -> None:
-        if self._dirty_hi >= self._dirty_lo:
-            lo, hi = self._dirty_lo, self._dirty_hi + 1
-            self.table[lo:hi].copy_(self.table_host[lo:hi], non_blocking=True)
-            self._dirty_lo, self._dirty_hi = self.table.shape[0], -1
-
-
-class SequenceCache:
-    """Slots, page groups and per-sequence state for one model.
-
-    ``needs`` maps a cache id (as named by the model's schedule) to what its mixer
-    needs.  ``max_tokens`` bounds the tokens all live sequences hold together
-    (each rounded up to whole pages); ``max_seq_tokens`` bounds one sequence.
-    """
-
-    def __init__(self, needs: Dict[int, Need], max_tokens: int, max_seq_tokens: int,
-                 dtype: torch.dtype, device, max_slots: Optional[int] = None):
-        device = torch.device(device)
-        if max_tokens <= 0 or max_seq_tokens <= 0:
-            raise CacheError("the cache needs room for at least one token")
-        self.device, self.dtype = device, dtype
-        self.n_pages = pages_for(max_tokens)
-        self.pages_per_seq = min(pages_for(max_seq_tokens), self.n_pages)
-        self.max_seq_tokens = self.pages_per_seq * PAGE_TOKENS
-        self.max_slots = max_slots if max_slots is not None else min(self.n_pages, 4096)
-        self.slots = FreeList(self.max_slots, "slot")
-        self._length = [0] * self.max_slots
-        # groups by need
-        by_need: Dict[KvNeed, List[int]] = {}
-        state_entries: List[Tuple[int, StateNeed]] = []
-        for cid, need in sorted(needs.items()):
+    @staticmethod
+    def bytes_needed(needs: Dict[int, Need], max_tokens: int, max_seq_tokens: int, dtype: torch.dtype,
+                     max_slots: Optional[int] = None) -> int:
+        """Device bytes a cache of these needs and sizes allocates: keys and values of every entry
+        for every page, the page tables, fixed state and generator state of every slot."""
+        n_pages = pages_for(max_tokens)
+        pages_per_seq = min(pages_for(max_seq_tokens), n_pages)
+        slots = max_slots if max_slots is not None else min(n_pages, 4096)
+        item = torch.empty((), dtype=dtype).element_size()
+        total = slots * 8                                                  # generator state
+        seen = set()
+        for need in needs.values():
             if isinstance(need, KvNeed):
-                by_need.setdefault(need, []).append(cid)
+                total += 2 * n_pages * need.n_kv_heads * PAGE_TOKENS * need.head_dim * item
+                if need not in seen:                                       # one page table a group
+                    seen.add(need)
+                    total += slots * pages_per_seq * 4
             elif isinstance(need, StateNeed):
-                state_entries.append((cid, need))
-            elif need is not None:
-                raise CacheError(f"cache entry {cid}: unknown need {need!r}")
-        self.kv_groups: List[KvGroup] = [
-            KvGroup(need, entries, self.n_pages, self.max_slots, self.pages_per_seq, dtype, device)
-            for need, entries in by_need.items()]
-        self._group_of: Dict[int, KvGroup] = {e: g for g in self.kv_groups for e in g.entries}
-        self._state: Dict[int, torch.Tensor] = {
-            cid: torch.zeros((self.max_slots, need.n_values), dtype=torch.float32, device=device)
-            for cid, need in state_entries}
-        self.rng_state = torch.zeros(self.max_slots, dtype=torch.int64, device=device)
+                total += slots * need.n_values * 4
+        return total
+
+    def _preflight(self, needs, max_tokens, max_seq_tokens) -> None:
+        """Refuse a cache the device cannot hold before any of it is allocated (the reference
+        checks a per-model memory budget before it loads: crates/runner/src/registry.rs:773-785)."""
+        if self.device.type != "cuda":
+            return
+        need = self.bytes_needed(needs, max_tokens, max_seq_tokens, self.dtype, self.max_slots)
+        free, total = torch.cuda.mem_get_info(self.device)
+        free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+        if need > free:
+            gib = 1 << 30
+            raise CacheError(f"a cache of {max_tokens} tokens needs {need / gib:.1f} GiB; {free / gib:.1f} GiB of "
+                             f"the device's {total / gib:.1f} GiB are free (the weights are loaded already): "
+                             "ask for fewer tokens (context size x batch size, or max_tokens)")
 
     # ---- slots ------------------------------------------------------------------------
     def acquire(self, rng_seed: Optional[int] = None) -> int:

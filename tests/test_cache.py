@@ -136,3 +136,17 @@ def test_generator_seed_is_never_zero():
     assert int(c.rng_state[s]) != 0
     c.seed(s, (1 << 64) - 1)
     assert int(c.rng_state[s]) == -1
+
+
+def test_the_size_estimate_is_what_a_cache_allocates():
+    """``bytes_needed`` (what the preflight compares with the device's free memory before anything
+    is allocated) equals the bytes of the tensors a cache of those needs then holds."""
+    needs = {0: KvNeed(2, 16), 1: KvNeed(2, 16, window=32), 2: KvNeed(2, 16), 3: StateNeed(5), 4: KvNeed(1, 32)}
+    for dtype in (torch.float32, torch.bfloat16):
+        for max_tokens, max_seq, slots in ((64 * 8, 64 * 4, None), (1000, 130, 3), (64, 4096, 7)):
+            c = SequenceCache(needs, max_tokens, max_seq, dtype, "cpu", max_slots=slots)
+            assert SequenceCache.bytes_needed(needs, max_tokens, max_seq, dtype, slots) == c.bytes_held()
+    # Llama-3.1-8B sizes, 64 sequences of 8,192 tokens in bfloat16: 64 GiB of keys and values
+    big = {i: KvNeed(8, 128) for i in range(32)}
+    need = SequenceCache.bytes_needed(big, 64 * 8192, 8192, torch.bfloat16, 64)
+    assert 64 * 2 ** 30 <= need < 64 * 2 ** 30 + 2 ** 20

@@ -227,3 +227,15 @@ def test_a_step_over_its_token_budget_runs_in_chunks_with_the_same_logits(model_
     with pytest.raises(Exception):
         m.step([StepEntry(s0, [1] * 2000, [])])
     assert m.cache.length(s0) == 0
+
+
+def test_a_cache_the_device_cannot_hold_is_refused_before_it_is_allocated(model_folders):
+    from supersonic_b200.cache import CacheError
+    from supersonic_b200.engine import Model
+    d, pc, pw = model_folders["A"]
+    free_before = torch.cuda.mem_get_info()[0]
+    with pytest.raises(CacheError, match="GiB are free"):
+        Model.from_dir(d, dtype="float32", max_tokens=1 << 34, max_seq_tokens=256, max_slots=4)
+    torch.cuda.empty_cache()
+    assert torch.cuda.mem_get_info()[0] >= free_before - (64 << 20)      # nothing of it was allocated
+    Model.from_dir(d, dtype="float32", max_tokens=256)                    # and the device is as usable as before
