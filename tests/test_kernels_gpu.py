@@ -455,7 +455,8 @@ def test_fast_linear_picks_a_kernel_for_every_row_count(rows, N, K):
 
 # ---- prefill GEMM on tcgen05 ------------------------------------------------------------------
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (65, 128, 200), (200, 304, 72), (300, 1000, 4096),
-                                   (1024, 512, 1024), (129, 8, 64)])
+                                   (1024, 512, 1024), (129, 8, 64),
+                                   (4400, 520, 128)])       # 18 row tiles of 256: a band of 16 and one of 2
 @pytest.mark.parametrize("tile_n", [64, 128, 256, 512])         # 512: tiles of 256 x 256 on SM pairs
 def test_gemm_tc(M, N, K, tile_n):
     g = torch.Generator(device=DEV).manual_seed(30)
