@@ -45,16 +45,20 @@ class Engine:
 
 
 def load(model_dir: str, dtype: str = "bfloat16", device: int = 0, context_size: Optional[int] = None,
-         batch_size: int = 1, max_tokens: Optional[int] = None) -> Engine:
+         batch_size: int = 1, max_tokens: Optional[int] = None,
+         step_token_budget: Optional[int] = None) -> Engine:
     """Load ``model_dir`` (config.json + safetensors).  The cache holds ``max_tokens`` tokens
     in all, by default ``batch_size`` sequences of ``context_size`` tokens (prompt plus
-    generated; default: the model's position limit, capped at 8192)."""
+    generated; default: the model's position limit, capped at 8192).  A step of more than
+    ``step_token_budget`` tokens (default 32,768) runs in chunks of that many: it bounds the
+    memory a batch of long prompts needs beside the cache."""
     from .cache import PAGE_TOKENS
     from .config import load_config
     cfg = load_config(model_dir)
     ctx = context_size or min(getattr(cfg, "max_position_embeddings", 8192), 8192)
     ctx = -(-ctx // PAGE_TOKENS) * PAGE_TOKENS
     total = max_tokens or ctx * max(batch_size, 1)
+    extra = {} if step_token_budget is None else {"step_token_budget": step_token_budget}
     model = Model.from_dir(model_dir, dtype=dtype, device=f"cuda:{device}", max_tokens=total,
-                           max_seq_tokens=ctx)
+                           max_seq_tokens=ctx, **extra)
     return Engine(model)
