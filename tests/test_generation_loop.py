@@ -180,3 +180,18 @@ def test_a_long_step_is_cut_into_chunks_that_keep_order_and_budget():
             assert all(a[1] == b[0] for a, b in zip(parts, parts[1:]))
         # full chunks except the last
         assert all(sum(hi - lo for _, lo, hi in c) == budget for c in chunks[:-1])
+
+
+def test_which_gemm_a_prompt_gets_is_decided_by_its_rows():
+    """The dispatch rules of the prefill projections are plain functions of the sizes: tiles on SM
+    pairs where the second half of the last 256 rows is not mostly padding, K cut into parts only
+    while the tiles alone leave SMs idle."""
+    from supersonic_b200.csrc.fast_sets import FastKernels as FK
+    assert FK._pair_tiles(2048, 6144) and FK._pair_tiles(512, 28672) and FK._pair_tiles(1030, 4096)
+    assert FK._pair_tiles(256, 256) and FK._pair_tiles(200, 4096)        # two row tiles of 128
+    assert not FK._pair_tiles(300, 28672) and not FK._pair_tiles(100, 4096) and not FK._pair_tiles(2048, 128)
+    assert FK._gemm_splits(2048, 4096, 4096, 256) == 1                    # 256 tiles: more than the SMs
+    assert FK._gemm_splits(128, 4096, 14336, 256) == 9                    # 16 tiles, 224 k-blocks
+    assert FK._gemm_splits(128, 4096, 4096, 256) == 8                     # at least 8 k-blocks a part
+    assert FK._gemm_splits(70, 256, 192, 256) == 1                        # a tiny model: K is too short to cut
+    assert FK._tile_n(2048, 4096) == 256 and FK._tile_n(8, 4096) == 64 and FK._tile_n(8, 128256) == 256
