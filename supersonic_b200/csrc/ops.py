@@ -9,7 +9,6 @@ codes (crates/gpu-hal/src/scalar_type.rs:25-32).
 """
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 

@@ -14,12 +14,12 @@ for one token (crates/runner/src/decode_engine.rs:3631-3993), one sequence each.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Dict, List, Optional, Sequence
+from typing import Any, Dict, Optional, Sequence
 
 import numpy as np
 import torch
 
-from ..cache import KvNeed, SequenceCache, StateNeed
+from ..cache import SequenceCache
 from ..config import ModelSpec, load_config, spec_from_config
 from ..csrc.kernel_sets import kernel_set_for
 from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,

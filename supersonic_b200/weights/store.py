@@ -14,7 +14,7 @@ from __future__ import annotations
 import json
 import os
 import zlib
-from typing import Dict, Iterable, Iterator, List, Optional, Tuple
+from typing import Dict, Iterator, List, Optional, Tuple
 
 import torch
 
