@@ -40,6 +40,7 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "gemv_tc": {"sources": ["gemv_tc.cu"], "flags": [], "link": []},
     "gemm_tc": {"sources": ["gemm_tc.cu"], "flags": [], "link": []},
     "attention_decode_static": {"sources": ["attention_decode_static.cu"], "flags": [], "link": []},
+    "random_fill": {"sources": ["random_fill.cu"], "flags": [], "link": []},
 }
 HEADERS = ["common.cuh", "mma_helpers.cuh", "tc_helpers.cuh", "attention_decode.cuh", "attention_decode_mma.cuh",
            "attention_decode_static.h"]

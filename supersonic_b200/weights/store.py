@@ -13,11 +13,11 @@ from __future__ import annotations
 
 import json
 import os
-import zlib
 from typing import Dict, Iterator, List, Optional, Tuple
 
 import torch
 
+from . import random_fill
 from .safetensors_io import SafetensorsError, SafetensorsFile, write_safetensors
 
 
@@ -138,37 +138,23 @@ class WeightStore:
 
 
 # ---- random weights -----------------------------------------------------------
-def _tensor_seed(seed: int, name: str) -> int:
-    return (int(seed) * 1000003 + zlib.crc32(name.encode("utf-8"))) % (2 ** 63 - 1)
+def random_tensor(config, seed: int, name: str, device: str = "cpu", std: float = 0.02,
+                  norm_jitter: float = 0.1) -> torch.Tensor:
+    """One seeded tensor by name, in bfloat16: matrices and embeddings N(0, std), norm weights
+    1 + N(0, norm_jitter).  Its values depend on (seed, name, element index) alone: the same on the
+    host and on the device, whole or in pieces (see ``random_fill``)."""
+    shape = config.tensor_shapes()[name]
+    is_norm = getattr(config, "is_norm_tensor", lambda n: len(shape) == 1)
+    if is_norm(name):
+        return random_fill.fill(seed, name, shape, 1.0, norm_jitter, device)
+    return random_fill.fill(seed, name, shape, 0.0, std, device)
 
 
 def random_tensors(config, seed: int, device: str = "cpu", std: float = 0.02,
                    norm_jitter: float = 0.1) -> Iterator[Tuple[str, torch.Tensor]]:
-    """Seeded tensors for every name the configuration asks for, in bfloat16:
-    matrices and embeddings N(0, std), norm weights 1 + N(0, norm_jitter).
-    Each tensor's stream depends only on (seed, name), never on the order asked."""
-    is_norm = getattr(config, "is_norm_tensor", lambda n: len(config.tensor_shapes()[n]) == 1)
-    for name, shape in config.tensor_shapes().items():
-        g = torch.Generator(device=device)
-        g.manual_seed(_tensor_seed(seed, name))
-        x = torch.randn(shape, generator=g, device=device, dtype=torch.float32)
-        if is_norm(name):
-            x = 1.0 + norm_jitter * x
-        else:
-            x = std * x
-        yield name, x.to(torch.bfloat16)
-
-
-def random_tensor(config, seed: int, name: str, device: str = "cpu", std: float = 0.02,
-                  norm_jitter: float = 0.1) -> torch.Tensor:
-    """One tensor of :func:`random_tensors`, by name."""
-    shape = config.tensor_shapes()[name]
-    is_norm = getattr(config, "is_norm_tensor", lambda n: len(shape) == 1)
-    g = torch.Generator(device=device)
-    g.manual_seed(_tensor_seed(seed, name))
-    x = torch.randn(shape, generator=g, device=device, dtype=torch.float32)
-    x = 1.0 + norm_jitter * x if is_norm(name) else std * x
-    return x.to(torch.bfloat16)
+    """Seeded tensors for every name the configuration asks for (:func:`random_tensor`)."""
+    for name in config.tensor_shapes():
+        yield name, random_tensor(config, seed, name, device, std, norm_jitter)
 
 
 class RandomWeightStore(WeightStore):

@@ -838,3 +838,33 @@ def test_rope_append_vec_equals_plain(n_q, n_kv, hd):
     torch.testing.assert_close(qb.float(), qa.float(), atol=0, rtol=2 ** -7)
     torch.testing.assert_close(kb.float(), ka.float(), atol=0, rtol=2 ** -7)
     assert torch.equal(vb, va)
+
+
+# ---- random weights ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_random_fill_device_equals_host_bit_for_bit(dtype):
+    """The same (seed, name) gives the same bits from the CUDA kernel, from the package's host
+    version and from the tests' own scalar recipe; the offset of a piece is honoured."""
+    import plain_random as pr
+    from supersonic_b200.weights import random_fill
+    for seed, name, mean, std, shape in ((2, "model.layers.31.mlp.down_proj.weight", 0.0, 0.02, (301, 257)),
+                                         (9, "model.norm.weight", 1.0, 0.1, (4099,))):
+        host = random_fill.fill_host(seed, name, shape, mean, std, dtype)
+        dev = random_fill.fill_device(seed, name, shape, mean, std, DEV, dtype)
+        assert torch.equal(dev.cpu(), host)
+        if dtype == torch.bfloat16:
+            got = dev.view(-1)[:50].view(torch.int16).cpu().tolist()
+            assert [g & 0xFFFF for g in got] == [pr.value_bits(seed, name, i, mean, std) for i in range(50)]
+
+
+def test_random_store_is_the_written_folder(tmp_path):
+    """A folder written on the host and a store that makes its tensors on the device hold one model."""
+    import tiny_configs
+    from supersonic_b200.config import config_from_dict
+    from supersonic_b200.weights import RandomWeightStore, WeightStore, write_model_folder
+    cfg = config_from_dict(tiny_configs.B)
+    write_model_folder(cfg, 5, str(tmp_path), std=0.05)
+    folder = WeightStore.from_dir(str(tmp_path))
+    made = RandomWeightStore(cfg, 5, device=DEV, std=0.05)
+    for name in cfg.tensor_shapes():
+        assert torch.equal(made.get(name).cpu(), folder.get(name)), name
