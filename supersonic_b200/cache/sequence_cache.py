@@ -119,6 +119,12 @@ class KvGroup:
             self._dirty_lo, self._dirty_hi = self.table.shape[0], -1
 
 
+def default_seed(slot: int) -> int:
+    """Generator state of a sequence opened without a seed: the reference's default sampling seed
+    (42, crates/runner/src/main.rs:383) spread over the slots."""
+    return (42 * 0x9E3779B97F4A7C15 + (slot + 1) * 0xD1342543DE82EF95) & ((1 << 64) - 1)
+
+
 class SequenceCache:
     """Slots, page groups and per-sequence state for one model.
 
@@ -135,7 +141,9 @@ class SequenceCache:
         self.device, self.dtype = device, dtype
         self.n_pages = pages_for(max_tokens)
         self.pages_per_seq = min(pages_for(max_seq_tokens), self.n_pages)
-        self.max_seq_tokens = self.pages_per_seq * PAGE_TOKENS
+        # the limit a sequence may reach is the one asked for, not its page-rounded figure: position
+        # tables and other per-position data of the parts are sized by it
+        self.max_seq_tokens = min(int(max_seq_tokens), self.pages_per_seq * PAGE_TOKENS)
         self.max_slots = max_slots if max_slots is not None else min(self.n_pages, 4096)
         self._preflight(needs, max_tokens, max_seq_tokens)
         self.slots = FreeList(self.max_slots, "slot")
@@ -196,13 +204,14 @@ class SequenceCache:
 
     # ---- slots ------------------------------------------------------------------------
     def acquire(self, rng_seed: Optional[int] = None) -> int:
-        """A free slot with length 0, zeroed fixed state and a seeded generator."""
+        """A free slot with length 0, zeroed fixed state and a seeded generator.  Without a seed
+        the generator starts from a fixed state of the slot's own, never from zero (the fixed point
+        of xorshift64) and never from what the slot's last sequence left."""
         slot = self.slots.take()
         self._length[slot] = 0
         for t in self._state.values():
             t[slot].zero_()
-        if rng_seed is not None:
-            self.seed(slot, rng_seed)
+        self.seed(slot, rng_seed if rng_seed is not None else default_seed(slot))
         return slot
 
     def seed(self, slot: int, seed: int) -> None:

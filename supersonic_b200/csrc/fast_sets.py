@@ -30,6 +30,7 @@ TC_ATTENTION_MIN_NEW = 96     # prompts at least this long take the tcgen05 atte
 
 class FastKernels(PlainKernels):
     name = "fast"
+    capturable = True       # no kernel of the set synchronises or allocates: decode steps replay CUDA graphs
 
     def __init__(self, pdl: bool = True):
         self.pdl = pdl           # decode kernels launch as programmatic dependents of their predecessors

@@ -57,6 +57,7 @@ def as_tensor(x) -> torch.Tensor:
 
 class PlainKernels:
     name = "plain"
+    capturable = False      # the float32 path launches every step eagerly: each launch's status is looked at
 
     def embed(self, ids, table, out):
         ops.embed(ids, table, out)

@@ -354,6 +354,18 @@ _tc_error_words = {}
 _tc_unchecked = 0      # tcgen05 launches since the error words were last read
 
 
+def bounded_wait_launches() -> int:
+    """Launches since the last look at the error words of kernels whose waits are bounded."""
+    return _tc_unchecked
+
+
+def note_bounded_wait_launches(n: int) -> None:
+    """A captured graph that holds ``n`` such launches was replayed: they ran without passing
+    through this module, so the error word counts as unread."""
+    global _tc_unchecked
+    _tc_unchecked += int(n)
+
+
 def tc_error_word(device) -> torch.Tensor:
     """The device word in which tcgen05 kernels record a wait that ran out (zero = all well)."""
     key = torch.device(device)

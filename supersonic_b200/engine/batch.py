@@ -26,8 +26,28 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
+class NotOnHost:
+    """Stands where a batch has no host-side copy of a field: a captured decode step serves any
+    sequences at any positions, so what it knows of them lives in device tensors only
+    (``seq_slot``, ``seq_start``, ``pos``, ``slot_of_token``).  Any use raises, so that a part
+    which reads host lists cannot silently do nothing inside a captured step; such a part sets
+    ``capture_safe = False`` and the model then runs its decode steps uncaptured."""
+
+    def __init__(self, name: str):
+        self._name = name
+
+    def _refuse(self, *a, **k):
+        raise RuntimeError(f"batch.{self._name} does not exist in a captured decode step: read the device "
+                           "tensors of the batch, or set capture_safe = False on the part that needs it")
+
+    __iter__ = __len__ = __getitem__ = __bool__ = __contains__ = _refuse
+
+
 @dataclass
 class StepBatch:
+    """The device tensors are the interface every part may rely on; the ``host_*`` lists exist
+    only in steps that are not captured (see :class:`NotOnHost`)."""
+
     n_tokens: int
     n_seqs: int
     max_new: int                   # longest run of new tokens of one sequence

@@ -25,7 +25,7 @@ from ..csrc.kernel_sets import kernel_set_for
 from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
                      BuildContext, WeightAccess, lookup)
 from ..weights import WeightStore
-from .batch import StepBatch, StepEntry, decode_pages_bucket, pack_step, plan_chunks
+from .batch import NotOnHost, StepBatch, StepEntry, decode_pages_bucket, pack_step, plan_chunks
 
 _DTYPES = {"float32": torch.float32, "fp32": torch.float32, "f32": torch.float32,
            "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
@@ -84,7 +84,8 @@ class DecodeGraph:
             n_tokens=B, n_seqs=B, max_new=1, max_total=1, is_decode=True,
             token_ids=self.ints[:B], pos=self.ints[B:2 * B], slot_of_token=self.ints[2 * B:],
             seq_slot=self.ints[2 * B:], seq_start=self.ints[B:2 * B], cu_new=ar, want_rows=ar[:B].clone(),
-            n_want=B, kv_pages=kv_pages, host_slots=[], host_starts=[], host_counts=[1] * B)
+            n_want=B, kv_pages=kv_pages, host_slots=NotOnHost("host_slots"),
+            host_starts=NotOnHost("host_starts"), host_counts=[1] * B)
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):                       # warm-up outside capture (lazy set-up, attributes)
@@ -92,10 +93,14 @@ class DecodeGraph:
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         self.graph = torch.cuda.CUDAGraph()
-        before = ops.LAUNCHES
+        before, waits_before = ops.LAUNCHES, ops.bounded_wait_launches()
         with torch.cuda.graph(self.graph, pool=pool):
             self.logits = model._forward(self.batch)
         self.kernels_per_replay = ops.LAUNCHES - before
+        # launches of the captured step whose bounded waits can run out: each replay runs them again
+        # without passing through their Python faces, so the replay itself must mark the device's
+        # error word as unread
+        self.waiting_kernels = ops.bounded_wait_launches() - waits_before
         self.pool = self.graph.pool()
 
     def run(self, tokens, positions, slots) -> torch.Tensor:
@@ -110,6 +115,9 @@ class DecodeGraph:
             self.copied[i] = torch.cuda.Event()
         self.copied[i].record()
         self.graph.replay()
+        if self.waiting_kernels:
+            from ..csrc import ops
+            ops.note_bounded_wait_launches(self.waiting_kernels)
         return self.logits
 
 
@@ -162,8 +170,18 @@ class Model:
         self.step_token_budget = int(step_token_budget)
         if self.step_token_budget < 1:
             raise ValueError("step_token_budget must be at least 1")
-        # decode steps of the serving path replay captured graphs (one per batch size and page bucket)
-        self.use_graphs = use_graphs and self.kernels.name == "fast"
+        # decode steps of the serving path replay captured graphs (one per batch size and page bucket),
+        # if the kernel set can be captured and no part says that it cannot (``capture_safe = False``:
+        # it reads host lists of the batch, or synchronises)
+        parts = [self.embedding, self.final_norm, self.head]
+        for b in self.blocks:
+            parts += [b] + [p for p in (getattr(b, n, None) for n in ("mixer", "feed_forward", "mixer_norm",
+                                                                     "feed_forward_norm", "position")) if p is not None]
+        self.use_graphs = (use_graphs and getattr(self.kernels, "capturable", False)
+                           and all(getattr(p, "capture_safe", True) for p in parts))
+        # the last position any position encoding of the model can encode
+        limits = [getattr(getattr(b, "position", None), "max_positions", None) for b in self.blocks]
+        self.position_limit = min([int(x) for x in limits if x is not None], default=None)
         self._graphs: Dict[Any, DecodeGraph] = {}
         self._graph_pool = None
         self.graph_replays = 0
@@ -244,6 +262,11 @@ class Model:
         bad = [t for t in tokens if not 0 <= t < self.spec.vocab_size]
         if bad:
             raise ValueError(f"token ids {bad[:8]} are outside the vocabulary of {self.spec.vocab_size}")
+        if self.position_limit is not None and max(starts) + 1 > self.position_limit:
+            # the captured step cannot see positions on the host (``Rotary.check_range`` looks at a
+            # batch of length 1 there), so the bound is checked here
+            raise ValueError(f"a sequence reaches {max(starts) + 1} tokens, beyond the {self.position_limit} "
+                             "positions this model encodes")
         for e in entries:
             cache.reserve(e.slot, 1)
         cache.sync()

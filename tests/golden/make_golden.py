@@ -1,7 +1,7 @@
 """Writes tests/golden/plain_logits.npz: logits of the plain implementation on one tiny
 random model, kept as a guard against accidental changes of the plain implementation
-itself.  The reference's own model code (Rust and CUDA) cannot be run on a CPU-only
-machine without a Rust toolchain, so these numbers rest on its formulas, not on its output.
+itself (what ties the plain implementation to the reference's own output is
+``reference_kernels_logits.npz`` beside it, written by ``make_reference_golden.py``).
 
     python tests/golden/make_golden.py
 """

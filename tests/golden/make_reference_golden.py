@@ -17,7 +17,6 @@ sys.path.insert(0, os.path.dirname(HERE))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
 import plain_llama as pl  # noqa: E402
-import reference_model  # noqa: E402
 import tiny_configs  # noqa: E402
 from supersonic_b200.config import config_from_dict  # noqa: E402
 from supersonic_b200.weights import write_model_folder  # noqa: E402
@@ -34,6 +33,7 @@ def model(name):
 
 
 if __name__ == "__main__":
+    import reference_model      # needs a CUDA device and the compiled reference kernels
     out = sys.argv[1] if len(sys.argv) > 1 else os.path.join(HERE, "reference_kernels_logits.npz")
     arrays = {}
     for name, tokens in TOKENS.items():

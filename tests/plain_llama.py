@@ -1,12 +1,16 @@
 """Plain, slow implementation of the LlamaForCausalLM forward pass in NumPy float64.
 
-It rests on the reference's formulas only: the reference's model code is Rust
-plus CUDA and can be neither imported nor compiled on a CPU-only machine
-without a Rust toolchain, so there is no golden output of the reference itself
-to compare with.  Each function below cites the file and lines of
-DeanoC/SuperSonic whose arithmetic it restates.  Whole sequences, no cache, one
-function per part; it reads the model folder with its own few lines and shares
-no code with ``supersonic_b200``.
+Each function below cites the file and lines of DeanoC/SuperSonic whose arithmetic it restates.
+The reference's model code is Rust and cannot be built without a Rust toolchain, but its CUDA
+kernels can: ``baseline/reference_kernels.py`` compiles them unmodified, and
+``tests/test_reference_ops_gpu.py`` pins each function here (norm, rotary pairing, SwiGLU,
+projections, attention over a prompt and over a cache, the greedy tie rule, and a whole tiny
+model chained as the reference chains it) on their outputs; ``tests/golden/
+reference_kernels_logits.npz`` keeps such outputs for machines without a GPU.  What no kernel
+computes (the llama3 frequency formula, which the reference evaluates in Rust:
+crates/runner/src/llama31_engine.rs:115-145) rests on the formula alone.  Whole sequences, no
+cache, one function per part; it reads the model folder with its own few lines and shares no
+code with ``supersonic_b200``.
 """
 from __future__ import annotations
 

@@ -200,9 +200,17 @@ def test_order_of_layers_is_data(dtype, model_folders):
     assert len(win.held[s]) == 1 and min(win.held[s]) == 1              # the window group dropped page 0
 
 
-def test_toy_mixer_with_its_own_state(model_folders):
+def _tol(dtype, ref):
+    return 2e-5 if dtype == "float32" else 2e-2 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("dtype,on_device", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
+def test_toy_mixer_with_its_own_state(dtype, on_device, model_folders):
     """A mixer defined here, with a fixed-size state per sequence instead of keys and values,
-    is registered, built into a model and stepped: nothing in the framework's files changes."""
+    is registered, built into a model and stepped: nothing in the framework's files changes.
+    In bfloat16 it runs beside the serving kernels.  One variant reads the batch's host lists and
+    says so (``capture_safe = False``: the model then steps uncaptured); the other takes a decode
+    step from the batch's device tensors alone and is replayed inside the captured graphs."""
     from dataclasses import replace
     from supersonic_b200.cache import StateNeed
     from supersonic_b200.config.base import PartSpec
@@ -214,6 +222,8 @@ def test_toy_mixer_with_its_own_state(model_folders):
     class ToyDecay:
         """s <- decay * s + x_t ; out_t = s W^T.  State: one float32 vector per sequence."""
 
+        capture_safe = on_device
+
         def __init__(self, params, weights, build):
             self.hidden, self.decay = params["hidden_size"], params["decay"]
             self.w = build.weights.as_dtype(weights["w"], torch.float32)
@@ -224,6 +234,16 @@ def test_toy_mixer_with_its_own_state(model_folders):
         def forward(self, ctx, x, residual, cache_id, writes_cache, position):
             state = ctx.cache.state(cache_id)
             b, row = ctx.batch, 0
+            if on_device and b.is_decode:
+                # one token a sequence, everything from device tensors; rows whose slot is negative
+                # (a captured step's warm-up) change nothing
+                live = (b.seq_slot >= 0)[:, None]
+                idx = b.seq_slot.clamp(min=0).long()
+                old = state[idx]
+                new = torch.where(live, self.decay * old + x.float(), old)
+                state.index_copy_(0, idx, new)
+                residual += torch.where(live, new @ self.w.T, torch.zeros_like(residual))
+                return
             for slot, n in zip(b.host_slots, b.host_counts):
                 s = state[slot]
                 for t in range(row, row + n):
@@ -236,8 +256,9 @@ def test_toy_mixer_with_its_own_state(model_folders):
     spec = _spec_with(tiny_configs.A)
     toy = PartSpec("toy_decay", {"hidden_size": 64, "decay": 0.5}, {"w": "model.layers.1.self_attn.o_proj.weight"})
     spec = replace(spec, blocks=[spec.blocks[0], replace(spec.blocks[1], mixer=toy, position=None)])
-    m = Model(spec, WeightStore.from_dir(d), dtype="float32", device=DEV, max_tokens=256)
+    m = Model(spec, WeightStore.from_dir(d), dtype=dtype, device=DEV, max_tokens=256)
     assert len(m.cache.kv_groups) == 1 and tuple(m.cache.state(1).shape)[1] == 64
+    assert m.use_graphs == (dtype == "bfloat16" and on_device)
 
     def plain(tokens):
         T = len(tokens)
@@ -261,20 +282,25 @@ def test_toy_mixer_with_its_own_state(model_folders):
     for i in range(5):
         got = m.step([StepEntry(sa, [a[15 + i]], [0]), StepEntry(sb, [b[4 + i]], [0])])
         ga.append(got[:1]); gb.append(got[1:])
-    assert np.abs(torch.cat(ga).double().cpu().numpy() - plain(a)).max() < 2e-5
-    assert np.abs(torch.cat(gb).double().cpu().numpy() - plain(b)).max() < 2e-5
+    assert np.abs(torch.cat(ga).double().cpu().numpy() - plain(a)).max() < _tol(dtype, plain(a))
+    assert np.abs(torch.cat(gb).double().cpu().numpy() - plain(b)).max() < _tol(dtype, plain(b))
+    assert (m.graph_replays == 5) == m.use_graphs
     # a slot that is used again starts from a zeroed state
     m.close_sequence(sa)
     sc = m.open_sequence()
     assert sc == sa
     got = m.step([StepEntry(sc, b, range(9))])
-    assert np.abs(got.double().cpu().numpy() - plain(b)).max() < 2e-5
+    assert np.abs(got.double().cpu().numpy() - plain(b)).max() < _tol(dtype, plain(b))
 
 
-def test_toy_feed_forward_with_routing(model_folders):
+@pytest.mark.parametrize("dtype,sorts", [("float32", True), ("bfloat16", True), ("bfloat16", False)])
+def test_toy_feed_forward_with_routing(dtype, sorts, model_folders):
     """A feed-forward defined here that routes every token to one of two experts (router logits
     and the gate in float32, experts cut out of the dense weights) replaces layer 0's: registered,
-    built and stepped with unequal prompts and then token by token."""
+    built and stepped with unequal prompts and then token by token.  The variant that gathers each
+    expert's rows asks the device how many there are (a synchronisation) and says so
+    (``capture_safe = False``); the other runs every expert on every row and masks, and is replayed
+    inside the captured decode graphs of the bfloat16 path."""
     from dataclasses import replace
     from supersonic_b200.config.base import PartSpec
     from supersonic_b200.engine import Model, StepEntry
@@ -284,6 +310,8 @@ def test_toy_feed_forward_with_routing(model_folders):
     @register_feed_forward("toy_top1")
     class ToyTop1:
         """logits = x Wr^T; e = argmax; out = softmax(logits)[e] * down_e(silu(gate_e x) * up_e x)."""
+
+        capture_safe = not sorts
 
         def __init__(self, params, weights, build):
             self.n_experts = params["n_experts"]
@@ -298,10 +326,15 @@ def test_toy_feed_forward_with_routing(model_folders):
             prob = torch.softmax(logits, dim=-1)
             choice = logits.argmax(dim=-1)
             for e in range(self.n_experts):
+                lo, hi = e * self.width, (e + 1) * self.width
+                if not sorts:
+                    g, u = x @ self.gate[lo:hi].T, x @ self.up[lo:hi].T
+                    y = (torch.nn.functional.silu(g) * u) @ self.down[:, lo:hi].T
+                    residual += torch.where((choice == e)[:, None], prob[:, e, None] * y, torch.zeros_like(y))
+                    continue
                 rows = (choice == e).nonzero().flatten()
                 if rows.numel() == 0:
                     continue
-                lo, hi = e * self.width, (e + 1) * self.width
                 xe = x[rows]
                 g, u = xe @ self.gate[lo:hi].T, xe @ self.up[lo:hi].T
                 y = (torch.nn.functional.silu(g) * u) @ self.down[:, lo:hi].T
@@ -313,7 +346,8 @@ def test_toy_feed_forward_with_routing(model_folders):
     toy = PartSpec("toy_top1", {"n_experts": 2}, {"gate": f"{p0}.gate_proj.weight", "up": f"{p0}.up_proj.weight",
                                                   "down": f"{p0}.down_proj.weight"})
     spec = replace(spec, blocks=[replace(spec.blocks[0], feed_forward=toy)] + list(spec.blocks[1:]))
-    m = Model(spec, WeightStore.from_dir(d), dtype="float32", device=DEV, max_tokens=256)
+    m = Model(spec, WeightStore.from_dir(d), dtype=dtype, device=DEV, max_tokens=256)
+    assert m.use_graphs == (dtype == "bfloat16" and not sorts)
 
     def plain(tokens):
         T = len(tokens)
@@ -329,6 +363,7 @@ def test_toy_feed_forward_with_routing(model_folders):
         prob /= prob.sum(-1, keepdims=True)
         out = np.zeros_like(h)
         used.update(int(e) for e in logits.argmax(-1))
+        margins[tuple(tokens)] = (logits[:, 0] - logits[:, 1]).tolist()
         for t in range(T):
             e = int(logits[t].argmax())
             lo, hi = e * width, (e + 1) * width
@@ -339,7 +374,7 @@ def test_toy_feed_forward_with_routing(model_folders):
             h = pl.block(h, pw, layer, pc, cos, sin)
         return pl.output_head(h, pw, pc)
 
-    used = set()
+    used, margins = set(), {}
     rng = np.random.default_rng(8)
     a, b = rng.integers(0, 301, 23).tolist(), rng.integers(0, 301, 11).tolist()
     ra, rb = plain(a), plain(b)
@@ -350,13 +385,24 @@ def test_toy_feed_forward_with_routing(model_folders):
     for i in range(5):
         got = m.step([StepEntry(sa, [a[18 + i]], [0]), StepEntry(sb, [b[6 + i]], [0])])
         ga.append(got[:1]); gb.append(got[1:])
-    assert np.abs(torch.cat(ga).double().cpu().numpy() - ra).max() < 2e-5
-    assert np.abs(torch.cat(gb).double().cpu().numpy() - rb).max() < 2e-5
+    if dtype == "bfloat16":
+        # a token whose two router logits are nearly equal may go to the other expert in bfloat16:
+        # compare the rows whose choice is clear in the plain implementation
+        clear = lambda toks: np.array([abs(m_) > 0.05 for m_ in margins[tuple(toks)]])
+        ka, kb = clear(a), clear(b)
+        assert ka.sum() >= 18 and kb.sum() >= 8
+    else:
+        ka, kb = np.ones(len(a), bool), np.ones(len(b), bool)
+    assert np.abs(torch.cat(ga).double().cpu().numpy() - ra)[ka].max() < _tol(dtype, ra)
+    assert np.abs(torch.cat(gb).double().cpu().numpy() - rb)[kb].max() < _tol(dtype, rb)
+    assert (m.graph_replays == 5) == m.use_graphs
 
 
-def test_toy_position_encoding(model_folders):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_position_encoding(dtype, model_folders):
     """A position encoding defined here (a learned vector per position added to every query and
-    key head, no rotation) replaces the rotary one in every layer: registered, built, stepped."""
+    key head, no rotation) replaces the rotary one in every layer: registered, built, stepped; in
+    bfloat16 beside the serving kernels, its decode steps inside the captured graphs."""
     from dataclasses import replace
     from supersonic_b200.cache import PAGE_SHIFT
     from supersonic_b200.config.base import PartSpec
@@ -383,7 +429,8 @@ def test_toy_position_encoding(model_folders):
     spec = _spec_with(tiny_configs.B)
     toy = PartSpec("toy_learned", {"head_dim": pc["head_dim"]}, {"table": "model.embed_tokens.weight"})
     spec = replace(spec, blocks=[replace(b, position=toy) for b in spec.blocks])
-    m = Model(spec, WeightStore.from_dir(d), dtype="float32", device=DEV, max_tokens=256)
+    m = Model(spec, WeightStore.from_dir(d), dtype=dtype, device=DEV, max_tokens=256)
+    assert m.use_graphs == (dtype == "bfloat16")
 
     def plain(tokens):
         T = len(tokens)
@@ -406,4 +453,5 @@ def test_toy_position_encoding(model_folders):
     s = m.open_sequence()
     got = [m.step([StepEntry(s, toks[:66], range(66))])]
     got += [m.step([StepEntry(s, [toks[p]], [0])]) for p in range(66, 75)]
-    assert np.abs(torch.cat(got).double().cpu().numpy() - ref).max() < 2e-5
+    assert np.abs(torch.cat(got).double().cpu().numpy() - ref).max() < _tol(dtype, ref)
+    assert m.graph_replays == (9 if dtype == "bfloat16" else 0)

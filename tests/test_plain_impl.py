@@ -93,3 +93,26 @@ def test_golden_file():
     gold = np.load(os.path.join(here, "golden", "plain_logits.npz"))
     assert gold["tokens"].tolist() == mod.TOKENS
     assert np.allclose(mod.compute()[:, :48], gold["logits"], atol=1e-6)
+
+
+def test_plain_against_the_reference_kernels_golden():
+    """tests/golden/reference_kernels_logits.npz holds logits that DeanoC/SuperSonic's own CUDA
+    kernels (compiled unmodified, chained as its prompt engine chains them: tests/reference_model.py)
+    produced on a B200 for two tiny random models.  The plain implementation must agree within the
+    bound of a path that rounds to bfloat16 after every operation (2 % of the largest logit)."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    spec = importlib.util.spec_from_file_location("make_reference_golden",
+                                                  os.path.join(here, "golden", "make_reference_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    gold = np.load(os.path.join(here, "golden", "reference_kernels_logits.npz"))
+    for name, toks in mod.TOKENS.items():
+        assert gold[f"tokens_{name}"].tolist() == toks
+        pc, pw = mod.model(name)
+        want = pl.forward(pc, pw, toks)
+        got = gold[f"logits_{name}"]
+        assert np.abs(got - want[:, :64]).max() <= 0.02 * np.abs(want).max()
+        clear = [t for t in range(len(toks)) if np.diff(np.sort(want[t, :64])[-2:])[0] > 0.04 * np.abs(want).max()]
+        assert len(clear) >= len(toks) // 2
+        for t in clear:           # the same best token among the stored columns wherever the margin is clear
+            assert int(np.argmax(got[t])) == int(np.argmax(want[t, :64]))
