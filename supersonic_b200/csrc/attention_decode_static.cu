@@ -44,10 +44,17 @@ SSB_API int ssb_attention_decode_static(const void* q, int ldq, const void* k_ca
                                         int head_dim, int page_shift, int window, float scale, int n_splits,
                                         cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
-    if (head_dim <= 0 || n_kv <= 0 || n_q <= 0 || n_q % n_kv || n_splits < 1) return SSB_ERR_BAD_SIZE;
-    const long long need_floats = n_splits > 1 ? ad_scratch_floats(n_seqs, n_q, head_dim, n_splits) : 0;
-    const long long need_counters = n_splits > 1 ? (long long)ad_counters(n_seqs, n_q, n_kv) : 0;
-    if (need_floats > SSB_STATIC_SCRATCH_FLOATS || need_counters > SSB_STATIC_COUNTERS)
+    // every size the kernel refuses is refused here, before anything is enqueued
+    if (head_dim <= 0 || head_dim > 32 * AD_MAX_VEC || n_kv <= 0 || n_q <= 0 || n_q % n_kv || n_splits < 1 ||
+        n_splits > AD_MAX_SPLITS)
+        return SSB_ERR_BAD_SIZE;
+    // in 64 bits: a huge batch must not wrap into a small or negative figure
+    const long long group_tiles = ((long long)(n_q / n_kv) + AD_GROUP - 1) / AD_GROUP;
+    const long long need_floats =
+        n_splits > 1 ? (long long)n_seqs * n_q * n_splits * ((long long)head_dim + 2) : 0;
+    const long long need_counters = n_splits > 1 ? (long long)n_seqs * n_kv * group_tiles : 0;
+    if (need_floats < 0 || need_counters < 0 || need_floats > SSB_STATIC_SCRATCH_FLOATS ||
+        need_counters > SSB_STATIC_COUNTERS)
         return SSB_ERR_STATIC_SCRATCH_TOO_SMALL;
     int device = 0;
     const int rc = lookup_for_current_device(&device);

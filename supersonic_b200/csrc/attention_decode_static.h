@@ -24,7 +24,9 @@
  *
  * First call on a device: the addresses of the two arrays on the current device are looked
  * up once (cudaGetSymbolAddress) and remembered per device.  Make this first call, with the
- * device current, before any stream capture begins.
+ * device current, before any stream capture begins.  Several host threads that make their
+ * first call on one device at the same moment each look the addresses up and store the same
+ * two values: harmless, but nothing else about the first call is synchronised.
  *
  * Sharing: all calls on a device use the same arrays, which keep what the last call left.
  * The counters a call uses are cleared on its stream before its kernel runs.  Two calls

@@ -455,3 +455,102 @@ def test_toy_position_encoding(dtype, model_folders):
     got += [m.step([StepEntry(s, [toks[p]], [0])]) for p in range(66, 75)]
     assert np.abs(torch.cat(got).double().cpu().numpy() - ref).max() < _tol(dtype, ref)
     assert m.graph_replays == (9 if dtype == "bfloat16" else 0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_windowed_attention_through_the_engine(dtype, name, model_folders):
+    """A window of 100 keys (no multiple of the page size) on every layer.  A prompt longer than the
+    window runs in chunks of 48 tokens through the cache, decoding crosses a page edge, pages the
+    window left behind go back and are taken by a second sequence whose own cached values are
+    large, so that a read of a stale or recycled page would show."""
+    from supersonic_b200.config.base import ScheduleEntry  # noqa: F401
+    from supersonic_b200.engine import Model, StepEntry
+    from supersonic_b200.weights import WeightStore
+    d, pc, pw = model_folders[name]
+    cfg = tiny_configs.CONFIGS[name][0]
+    L = cfg["num_hidden_layers"]
+    window = {i: 100 for i in range(L)}
+    spec = _spec_with(cfg, None, window)
+    m = Model(spec, WeightStore.from_dir(d), dtype=dtype, device=DEV, max_tokens=512, step_token_budget=48)
+    order = [(i, i, True) for i in range(L)]
+    rng = np.random.default_rng(31)
+    a = rng.integers(0, pc["vocab_size"], 230).tolist()
+    b = rng.integers(0, pc["vocab_size"], 150).tolist()
+    ra, rb = (_plain_forward_scheduled(pc, pw, t, order, window) for t in (a, b))
+    tol = lambda ref: 2e-5 if dtype == "float32" else 2e-2 * np.abs(ref).max()
+    sa = m.open_sequence()
+    got = [m.step([StepEntry(sa, a[:200], range(150, 200))])]          # five chunks; pages 0 and 1 are given back
+    m.cache.check()
+    group = m.cache.kv_groups[0]
+    assert min(group.held[sa]) == 1 and group.need.window == 100
+    free_after_a = group.pool.n_free
+    sb = m.open_sequence()
+    got_b = [m.step([StepEntry(sb, b[:120], range(100, 120))])]       # takes pages, among them what a gave back
+    m.cache.check()
+    for i in range(30):                                                 # both decode; a crosses the edge at 256? no: at 192+64
+        rows = m.step([StepEntry(sa, [a[200 + i]], [0]), StepEntry(sb, [b[120 + i]], [0])])
+        got.append(rows[:1]); got_b.append(rows[1:])
+        m.cache.check()
+    ga, gb = (torch.cat(g).double().cpu().numpy() for g in (got, got_b))
+    assert np.abs(ga - ra[150:]).max() < tol(ra), "sequence a"
+    assert np.abs(gb - rb[100:]).max() < tol(rb), "sequence b"
+    assert group.pool.n_free <= free_after_a                             # b holds pages now
+    m.close_sequence(sa)
+    m.close_sequence(sb)
+    m.cache.check()
+    assert group.pool.n_held == 0
+
+
+def test_a_wait_that_runs_out_inside_a_replayed_graph_is_reported(model_folders):
+    """A decode step of the serving path is a graph replay: no Python launch wrapper runs.  A
+    feed-forward defined here launches the probe whose only wait can never be satisfied (it gives
+    up after about a second and sets the device's error word: no fault, no hang).  The error must be
+    reported after the step that captured the graph and again after a step that only replayed it,
+    and the logits of those steps (the probe touches no data) are right."""
+    from dataclasses import replace
+    from supersonic_b200.config.base import PartSpec
+    from supersonic_b200.csrc import ops
+    from supersonic_b200.engine import Model, StepEntry
+    from supersonic_b200.parts import register_feed_forward
+    from supersonic_b200.weights import WeightStore
+
+    @register_feed_forward("toy_probe")
+    class ToyProbe:
+        def __init__(self, params, weights, build):
+            self.device = build.device
+
+        def forward(self, ctx, x, residual):
+            ops.tc_wait_probe(self.device)
+
+    d, pc, pw = model_folders["A"]
+    spec = _spec_with(tiny_configs.A)
+    spec = replace(spec, blocks=[spec.blocks[0], replace(spec.blocks[1], feed_forward=PartSpec("toy_probe", {}, {}))])
+    m = Model(spec, WeightStore.from_dir(d), dtype="bfloat16", device=DEV, max_tokens=128)
+    assert m.use_graphs
+    ops.check_device_errors(DEV)                       # whatever earlier tests left is looked at and cleared
+    toks = np.random.default_rng(41).integers(0, 256, 12).tolist()
+
+    def plain(tokens):
+        cos, sin = pl.rope_tables(pc, len(tokens))
+        h = pl.block(pl.embedding(tokens, pw["model.embed_tokens.weight"]), pw, 0, pc, cos, sin)
+        x = pl.rms_norm(h, pw["model.layers.1.input_layernorm.weight"], pc["rms_norm_eps"])
+        return pl.output_head(h + pl.attention_mixer(x, pw, "model.layers.1", pc, cos, sin), pw, pc)
+
+    ref = plain(toks)
+    s = m.open_sequence()
+    m.step([StepEntry(s, toks[:10], [])])
+    with pytest.raises(ops.KernelError, match="bounded wait"):
+        m.check_errors()
+    m.check_errors()                                   # reported once
+    first = m.step([StepEntry(s, [toks[10]], [0])])    # builds and captures the graph, then replays it
+    with pytest.raises(ops.KernelError, match="bounded wait"):
+        m.check_errors()
+    replays = m.graph_replays
+    second = m.step([StepEntry(s, [toks[11]], [0])])   # a replay and nothing else
+    assert m.graph_replays == replays + 1
+    with pytest.raises(ops.KernelError, match="bounded wait"):
+        m.fetch(torch.zeros(1, dtype=torch.int32, device=DEV))
+    m.check_errors()
+    got = torch.cat([first, second]).double().cpu().numpy()
+    assert np.abs(got - ref[10:]).max() < 2e-2 * np.abs(ref).max()

@@ -88,3 +88,17 @@ def test_static_entry_point_refuses_what_its_scratch_cannot_hold():
     assert call(fn, q, k, v, pos, slot, table, out, n_q, n_kv, hd, None, 0.1, 4) == 0   # 4 splits fit
     torch.cuda.synchronize()
     assert not torch.any(out == 7.0)
+
+
+def test_static_entry_point_checks_sizes_before_it_enqueues_anything():
+    """Sizes the kernel refuses (more than 64 splits, a head size above 256) are refused by the entry
+    point itself with the size error, not after its counters were cleared on the stream."""
+    lib, fn = bind()
+    n_q, n_kv, hd, n_seqs = 4, 2, 64, 2
+    q, k, v, pos, slot, table = make_case(60, n_q, n_kv, hd, n_seqs)
+    out = torch.full((n_seqs, n_q * hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    assert call(fn, q, k, v, pos, slot, table, out, n_q, n_kv, hd, None, 0.1, 65) == 2002
+    assert call(fn, q, k, v, pos, slot, table, out, n_q, n_kv, 272, None, 0.1, 2) == 2002
+    assert call(fn, q, k, v, pos, slot, table, out, 5, 2, hd, None, 0.1, 2) == 2002
+    torch.cuda.synchronize()
+    assert torch.all(out == 7.0)
