@@ -3,13 +3,21 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
 
 One JSON line on stdout.  ``value`` is decoded tokens per second at batch 8 (one step = one
-decode step of the whole batch, timed on the device with CUDA events around exactly K graph
-replays after W warm-up steps).  ``e2e`` is the same through the Python entry point
-(``Engine.generate``): host token lists in, host token lists out, every step copying its
-token ids from pinned host memory and reading the sampled tokens back.  ``prefill`` is one
-2,048-token prompt; ``points`` holds decode at batch 1 and 64; ``roofline`` is the decode
-step's bytes (every weight once plus the live sequences' keys and values) over its time.
-Weights are ~15 GB, far beyond the 126 MB L2, so no flush is needed between steps.
+decode step of the whole batch and the greedy pick of its tokens, timed on the device with CUDA
+events around exactly K steps after W warm-up steps).  ``e2e`` is the same through the Python
+entry point (``Engine.generate``): host token lists in, host token lists out, every step copying
+its token ids from pinned host memory and reading the sampled tokens back.  ``prefill`` is one
+2,048-token prompt; ``points`` holds decode at batch 1 and 64 and the two further workloads the
+benchmark definition lists (a ragged batch of 16 prompts at Llama-3.2-3B sizes, a ragged batch of
+64 prompts sampled at temperature 1.0 at Llama-3.2-1B sizes), each through the entry point;
+``stages`` is the device time of one uncaptured decode step and one prompt step by stage;
+``roofline`` is the decode step's bytes (every weight the built model's parts hold, once, plus the
+live sequences' keys and values) over its time.  Weights are ~15 GB, far beyond the 126 MB L2, so
+no flush is needed between steps.
+
+``--impl reference``: the reference is a Rust workspace that cannot be built here, so the whole
+engine is ``unavailable``; its CUDA kernels do build (``baseline/reference_kernels.py``), and the
+line carries their times per operation at the same shapes under ``reference_ops``.
 """
 import argparse
 import json
@@ -79,50 +87,119 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def decode_bytes(cfg, layers, batch, context, dtype_bytes=2):
-    """Bytes a decode step must read: each used weight once (embedding rows aside) and the
-    keys and values of the live sequences."""
-    h, i = cfg.hidden_size, cfg.intermediate_size
-    q, kv = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
-    per_layer = h * q + 2 * h * kv + q * h + 3 * h * i + 2 * h
-    weights = (layers * per_layer + h + cfg.vocab_size * h) * dtype_bytes
-    kv_bytes = layers * 2 * kv * dtype_bytes * context * batch
-    return weights + kv_bytes
-
-
-def prefill_flops(cfg, layers, tokens):
-    h, i = cfg.hidden_size, cfg.intermediate_size
-    q, kv = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
-    linear = 2 * tokens * (h * q + 2 * h * kv + q * h + 3 * h * i)
-    attn = 2 * 2 * cfg.num_attention_heads * cfg.head_dim * tokens * (tokens + 1) / 2      # causal QK and PV
-    return layers * (linear + attn) + 2 * cfg.vocab_size * h                              # one row of logits
+def prefill_flops(model, lengths, wanted_rows):
+    """FLOPs of a prompt step: 2 per weight element per token for every matrix the model's parts
+    hold (asked of the built model), causal attention (QK and PV) for the mixers that say how many
+    query heads of which size they have, and the head for the wanted rows."""
+    tokens = sum(lengths)
+    linear = 2 * tokens * model.matrix_elements()
+    attn = 0
+    for stop in model.spec.schedule:
+        mixer = model.blocks[stop.layer].mixer
+        n_q, hd = getattr(mixer, "n_q", 0), getattr(mixer, "head_dim", 0)
+        attn += sum(2 * 2 * n_q * hd * n * (n + 1) / 2 for n in lengths)
+    return linear + attn + 2 * wanted_rows * model.spec.vocab_size * model.spec.hidden_size
 
 
 def time_decode(model, batch, prompt_len, steps, warmup, seed=0):
-    """(ms per step, kernels per step) of decode at ``batch`` sequences after prompts of ``prompt_len``."""
+    """(ms per step, kernels per step, bytes a step reads at the middle of the timed region) of decode
+    at ``batch`` sequences after prompts of ``prompt_len``.  A step is the model's decode step plus
+    the greedy pick of every sequence's token from its logits, all on the device; the tokens fed
+    are given (the pick is not read back: that is what ``e2e`` adds)."""
     import torch
     from supersonic_b200.engine import StepEntry
+    from supersonic_b200.sampling import Sampler, SamplingParams
     g = torch.Generator().manual_seed(seed)
     slots = [model.open_sequence() for _ in range(batch)]
+    sampler, greedy = Sampler(model.kernels, model.cache.rng_state), SamplingParams()
+    slot_t = torch.tensor(slots, dtype=torch.int32, device=model.device)
     try:
         prompts = torch.randint(0, model.vocab_size, (batch, prompt_len), generator=g).tolist()
         for lo in range(0, batch, 8):                     # prompts in groups: bounded activation memory
             model.step([StepEntry(s, p, []) for s, p in zip(slots[lo:lo + 8], prompts[lo:lo + 8])])
         nxt = torch.randint(0, model.vocab_size, (warmup + steps, batch), generator=g).tolist()
         for w in range(warmup):
-            model.step([StepEntry(s, [t], [0]) for s, t in zip(slots, nxt[w])])
+            sampler(model.step([StepEntry(s, [t], [0]) for s, t in zip(slots, nxt[w])]), slot_t, greedy)
         torch.cuda.synchronize()
         k0 = model.graph_kernels
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for k in range(steps):
-            model.step([StepEntry(s, [t], [0]) for s, t in zip(slots, nxt[warmup + k])])
+            sampler(model.step([StepEntry(s, [t], [0]) for s, t in zip(slots, nxt[warmup + k])]), slot_t, greedy)
+            if k == steps // 2:
+                bytes_mid = model.decode_step_bytes(slots)        # host arithmetic only
         end.record()
         torch.cuda.synchronize()
-        return start.elapsed_time(end) / steps, (model.graph_kernels - k0) // max(steps, 1)
+        model.check_errors()
+        return start.elapsed_time(end) / steps, (model.graph_kernels - k0) // max(steps, 1) + 1, bytes_mid
     finally:
         for s in slots:
             model.close_sequence(s)
+
+
+def stage_shares(model, batch, prompt_len, prefill_tokens, seed=5):
+    """Device milliseconds by stage of one uncaptured decode step of ``batch`` sequences and of one
+    prompt step (see supersonic_b200/engine/stage_timings.py)."""
+    import torch
+    from supersonic_b200.engine import StepEntry
+    g = torch.Generator().manual_seed(seed)
+    slots = [model.open_sequence() for _ in range(batch)]
+    out = {}
+    try:
+        prompts = torch.randint(0, model.vocab_size, (batch, prompt_len), generator=g).tolist()
+        model.step([StepEntry(s, p, []) for s, p in zip(slots, prompts)])
+        model.time_stages(True)
+        for rep in range(2):                                   # the first timed step warms the uncaptured path
+            model.step([StepEntry(s, [1], [0]) for s in slots])
+            out["decode"] = {k: round(v, 4) for k, v in model.stage_times().items() if v > 0}
+        model.close_sequence(slots.pop())
+        for rep in range(2):
+            s = model.open_sequence()
+            model.step([StepEntry(s, torch.randint(0, model.vocab_size, (prefill_tokens,), generator=g).tolist(),
+                                  [prefill_tokens - 1])])
+            out["prefill"] = {k: round(v, 3) for k, v in model.stage_times().items() if v > 0}
+            model.close_sequence(s)
+    finally:
+        model.time_stages(False)
+        for s in slots:
+            model.close_sequence(s)
+    return out
+
+
+def ragged_workload(preset, n_prompts, lo, hi, new_tokens, temperature, pk, seed):
+    """A further workload of the benchmark definition through the Python entry point: ``n_prompts``
+    prompts with lengths uniform in [lo, hi] start together (one prompt step, in chunks of the step's
+    token budget), then ``new_tokens`` decode steps.  Host wall time from a step's start to its tokens
+    on the host; the decode fraction uses the bytes at the middle of the run."""
+    import torch
+    import supersonic_b200
+    g = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(lo, hi + 1, (n_prompts,), generator=g).tolist()
+    ctx = -(-(max(lengths) + new_tokens) // 64) * 64
+    eng = supersonic_b200.load(preset=preset, random_seed=seed, context_size=ctx, batch_size=n_prompts,
+                               max_tokens=sum(-(-(n + new_tokens) // 64) * 64 for n in lengths))
+    model = eng.model
+    prompts = [torch.randint(0, model.vocab_size, (n,), generator=g).tolist() for n in lengths]
+    eng.generate([p[:8] for p in prompts[:2]], max_new_tokens=4, temperature=temperature, ignore_eos=True,
+                 batch_size=2)                                      # compiles nothing new; warms the allocator
+    eng.generator.stats = type(eng.generator.stats)()
+    eng.generate(prompts, max_new_tokens=new_tokens, temperature=temperature, ignore_eos=True, batch_size=n_prompts)
+    st = eng.generator.stats
+    mid = [n + new_tokens // 2 for n in lengths]
+    item = 2
+    kv_mid = sum(model.cache.kv_groups[0].need.n_kv_heads * model.cache.kv_groups[0].need.head_dim * 2 * item
+                 * len(model.cache.kv_groups[0].entries) * n for n in mid)
+    step_bytes = model.weight_bytes() + kv_mid
+    decode_ms = st.decode_s * 1e3 / max(st.decode_steps, 1)
+    out = {"prompts": n_prompts, "prompt_tokens": sum(lengths), "new_tokens": new_tokens,
+           "prefill_tok_s": round(st.prefill_tokens / st.prefill_s, 1),
+           "prefill_frac": round(prefill_flops(model, lengths, n_prompts) / st.prefill_s / (pk["bf16_tflops"] * 1e12), 4),
+           "decode_tok_s": round(st.decode_tokens / st.decode_s, 1), "decode_ms_per_step": round(decode_ms, 4),
+           "decode_hbm_frac": round(step_bytes / (decode_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+           "temperature": temperature}
+    del eng, model
+    torch.cuda.empty_cache()
+    return out
 
 
 def time_prefill(model, tokens, reps=5, warmup=3, seed=1):
@@ -163,6 +240,96 @@ def time_e2e(engine, batch, prompt_len, steps, warmup, seed=2):
     return batch * steps / dt
 
 
+def reference_arm(args):
+    """The reference's whole engine cannot run here (Rust, no cargo in the image).  Its CUDA kernels
+    can: compiled unmodified for sm_100a, the ones its Llama lane uses are timed per operation at the
+    shapes of this benchmark (the harness the reference times its engine with is
+    tests/sm86/bench_llama31_8b.sh:31-175).  These figures explain; they are not an engine rate."""
+    line = {"impl": "reference",
+            "unavailable": "DeanoC/SuperSonic is a Rust workspace (Cargo.toml only, no setup.py or pyproject.toml): "
+                           "pip cannot install it and no cargo/rustc is in the image; only its CUDA kernels are timed"}
+    try:
+        line["reference_ops"] = time_reference_ops(args)
+    except Exception as e:      # noqa: BLE001 - the arm must print its line whatever happens
+        line["reference_ops_unavailable"] = f"{type(e).__name__}: {str(e)[:200]}"
+    print(json.dumps(line))
+    return 0
+
+
+def time_reference_ops(args):
+    import torch
+    from baseline import reference_kernels as rk
+    from supersonic_b200.config import preset_config
+    why = rk.available()
+    if why:
+        try:
+            rk.install()
+        except rk.ReferenceUnavailable as e:
+            raise RuntimeError(f"{why}; {e}") from None
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device")
+    cfg = preset_config(args.preset)
+    dev = "cuda:0"
+    H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    nq, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    T, L = args.prefill_tokens, cfg.num_hidden_layers
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape: (torch.randn(*shape, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+
+    def timed(fn, reps=3):
+        fn()                                                    # warm-up (the launchers synchronise)
+        best = None
+        for _ in range(reps):
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            best = a.elapsed_time(b) if best is None else min(best, a.elapsed_time(b))
+        return round(best, 4)
+
+    ops = {}
+    x = rnd(T, H)
+    shapes = {"q": (nq * hd, H), "k": (nkv * hd, H), "v": (nkv * hd, H), "o": (H, nq * hd),
+              "gate": (I, H), "up": (I, H), "down": (H, I)}
+    weights = {n: rnd(*s) for n, s in shapes.items()}
+    # K3: the tiled prompt GEMM (kernels/full_attention_4b_cuda.cuh:2671-2743), M = prompt tokens
+    for n, w in weights.items():
+        a = x if w.shape[1] == H else rnd(T, w.shape[1])
+        ops[f"prefill_gemm_{n}_ms"] = timed(lambda a=a, w=w: rk.matmul_rhs_transposed(a, w), reps=2)
+    # K6: prompt attention, one warp a query row (kernels/full_attention_cuda.cuh:360-474)
+    q, k, v = rnd(1, nq, T, hd), rnd(1, nkv, T, hd), rnd(1, nkv, T, hd)
+    ops["prefill_attention_ms"] = timed(lambda: rk.attention_prefill(q, k, v, hd ** -0.5), reps=1)
+    # K2: RMSNorm over the prompt's rows and over one row
+    wn = rnd(H)
+    ops["prefill_rms_norm_ms"] = timed(lambda: rk.rms_norm(x, wn, 1e-5))
+    x1 = rnd(1, H)
+    ops["decode_rms_norm_ms"] = timed(lambda: rk.rms_norm(x1, wn, 1e-5))
+    # K11: the decode projections, one row through cuBLAS (kernels/full_attention_bridge_4b_cuda.cu:4768-4813)
+    for n, w in weights.items():
+        a = rnd(w.shape[1])
+        ops[f"decode_gemv_{n}_ms"] = timed(lambda a=a, w=w: rk.gemv_bf16(a, w))
+    head = rnd(V, H)
+    ops["decode_lm_head_ms"] = timed(lambda: rk.gemv_bf16(x1[0], head))
+    ops["decode_lm_head_argmax_ms"] = timed(lambda: rk.lm_head_argmax(x1[0], head))
+    # K13: decode attention of one sequence at the benchmark's mean context (kernels/full_attention_cuda.cuh:578-679)
+    ctx = args.prompt_len + 128
+    q1, kc, vc = rnd(1, nq, hd), rnd(1, nkv, 8192, hd), rnd(1, nkv, 8192, hd)
+    ops["decode_attention_ms"] = timed(lambda: rk.attention_decode(q1, kc, vc, hd ** -0.5, kv_len=ctx))
+    gate1, up1 = rnd(I), rnd(I)
+    ops["decode_swiglu_ms"] = timed(lambda: rk.swiglu_mul(gate1, up1))
+    layer = sum(ops[f"decode_gemv_{n}_ms"] for n in shapes) + ops["decode_attention_ms"] \
+        + 2 * ops["decode_rms_norm_ms"] + ops["decode_swiglu_ms"]
+    ops["decode_step_kernel_sum_ms"] = round(L * layer + ops["decode_rms_norm_ms"] + ops["decode_lm_head_ms"], 3)
+    pre = sum(ops[f"prefill_gemm_{n}_ms"] for n in shapes) + ops["prefill_attention_ms"] + 2 * ops["prefill_rms_norm_ms"]
+    ops["prefill_kernel_sum_ms"] = round(L * pre, 1)
+    ops["note"] = ("per-operation device times of the reference's own kernels at these shapes (batch 1, "
+                   f"{T}-token prompt, context {ctx}); the sums count one launch per operation and layer and "
+                   "leave out rope, appends, residual adds and every host step of the reference's engine")
+    return ops
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -176,14 +343,12 @@ def main():
     ap.add_argument("--context", type=int, default=8192, help="tokens per cache slot")
     ap.add_argument("--slots", type=int, default=64)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
-    ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
+    ap.add_argument("--skip-workloads", action="store_true", help="leave out the 3B and 1B ragged workloads")
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "DeanoC/SuperSonic is a Rust workspace (Cargo.toml only, no setup.py or "
-                          "pyproject.toml): pip cannot install it and no cargo/rustc is in the image"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU only (this library has no multi-GPU path); got --gpus {args.gpus}")
         return 2
@@ -212,25 +377,29 @@ def main():
     clocks = ClockSampler()
     clocks.start()
     launches0 = ops.LAUNCHES
-    ms, kernels_per_step = time_decode(model, args.batch, args.prompt_len, args.steps, args.warmup)
-    ctx_mid = args.prompt_len + args.warmup + args.steps / 2
+    ms, kernels_per_step, bytes_step = time_decode(model, args.batch, args.prompt_len, args.steps, args.warmup)
     value = args.batch * 1000.0 / ms
-    bytes_step = decode_bytes(cfg, layers, args.batch, ctx_mid)
     achieved = bytes_step / (ms * 1e-3) / 1e9
 
     engine = Engine(model)
     e2e = time_e2e(engine, args.batch, args.prompt_len, args.steps, args.warmup)
 
     pf_ms = time_prefill(model, args.prefill_tokens)
-    pf_flops = prefill_flops(cfg, layers, args.prefill_tokens)
+    pf_flops = prefill_flops(model, [args.prefill_tokens], 1)
     points = {}
     if not args.skip_points:
         for b in (1, 64):
-            pms, _ = time_decode(model, b, args.prompt_len, min(args.steps, 64), args.warmup, seed=10 + b)
+            pms, _, pbytes = time_decode(model, b, args.prompt_len, min(args.steps, 64), args.warmup, seed=10 + b)
             points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
-            points[f"decode_b{b}_hbm_frac"] = round(
-                decode_bytes(cfg, layers, b, args.prompt_len + args.warmup + min(args.steps, 64) / 2)
-                / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)
+            points[f"decode_b{b}_hbm_frac"] = round(pbytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)
+    stages = stage_shares(model, args.batch, args.prompt_len, args.prefill_tokens)
+    if not args.skip_workloads and layers == full.num_hidden_layers:
+        del engine, model, store
+        torch.cuda.empty_cache()
+        # the benchmark definition's two further workloads: 16 prompts of 64..2,048 tokens then 128 steps at
+        # Llama-3.2-3B sizes; 64 prompts of 1..4,096 tokens then 512 steps at temperature 1.0 at 1B sizes
+        points["llama3.2-3b_ragged16"] = ragged_workload("llama3.2-3b", 16, 64, 2048, 128, 0.0, pk, seed=3)
+        points["llama3.2-1b_ragged64"] = ragged_workload("llama3.2-1b", 64, 1, 4096, 512, 1.0, pk, seed=4)
     clk = clocks.stop()
 
     line = {
@@ -250,11 +419,13 @@ def main():
                 "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": kernels_per_step * args.steps,
         "kernels_per_step": kernels_per_step,
+        "step": "decode step of the batch + greedy pick on the device",
         "prefill": {"value": round(args.prefill_tokens * 1000.0 / pf_ms, 1), "tokens": args.prefill_tokens,
                     "ms": round(pf_ms, 3), "frac": round(pf_flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        "stages": stages,
         "clocks": clk,
     }
     assert ops.LAUNCHES > launches0

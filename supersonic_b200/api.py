@@ -44,21 +44,42 @@ class Engine:
                                        include_stop_token, batch_size)
 
 
-def load(model_dir: str, dtype: str = "bfloat16", device: int = 0, context_size: Optional[int] = None,
-         batch_size: int = 1, max_tokens: Optional[int] = None,
-         step_token_budget: Optional[int] = None) -> Engine:
-    """Load ``model_dir`` (config.json + safetensors).  The cache holds ``max_tokens`` tokens
-    in all, by default ``batch_size`` sequences of ``context_size`` tokens (prompt plus
-    generated; default: the model's position limit, capped at 8192).  A step of more than
-    ``step_token_budget`` tokens (default 32,768) runs in chunks of that many: it bounds the
-    memory a batch of long prompts needs beside the cache."""
+    def score(self, sequences: Sequence[Sequence[int]], decode_step: bool = False):
+        """Teacher-forced scoring of given token sequences (``engine/score.py``): a list of
+        :class:`Score` with total and mean negative log-likelihood, perplexity, bits per token."""
+        from .engine.score import teacher_forced
+        return teacher_forced(self.model, sequences, decode_step)
+
+
+def load(model_dir: Optional[str] = None, dtype: str = "bfloat16", device: int = 0,
+         context_size: Optional[int] = None, batch_size: int = 1, max_tokens: Optional[int] = None,
+         step_token_budget: Optional[int] = None, preset: Optional[str] = None, random_seed: int = 0,
+         allow_unexpected_tensors: bool = False, use_graphs: bool = True) -> Engine:
+    """Load ``model_dir`` (config.json + safetensors), or build the named ``preset`` with random
+    weights made on the device from ``random_seed`` (no folder is read or written).  The cache holds
+    ``max_tokens`` tokens in all, by default ``batch_size`` sequences of ``context_size`` tokens
+    (prompt plus generated; default: the model's position limit, capped at 8192).  A step of more
+    than ``step_token_budget`` tokens (default 32,768) runs in chunks of that many: it bounds the
+    memory a batch of long prompts needs beside the cache.  Weights, cache and workspace are checked
+    against the device's free memory before anything is loaded."""
     from .cache import PAGE_TOKENS
-    from .config import load_config
-    cfg = load_config(model_dir)
+    from .config import load_config, preset_config
+    if (model_dir is None) == (preset is None):
+        raise ValueError("give either a model folder or a preset name")
+    cfg = load_config(model_dir) if model_dir is not None else preset_config(preset)
     ctx = context_size or min(getattr(cfg, "max_position_embeddings", 8192), 8192)
     ctx = -(-ctx // PAGE_TOKENS) * PAGE_TOKENS
     total = max_tokens or ctx * max(batch_size, 1)
-    extra = {} if step_token_budget is None else {"step_token_budget": step_token_budget}
-    model = Model.from_dir(model_dir, dtype=dtype, device=f"cuda:{device}", max_tokens=total,
-                           max_seq_tokens=ctx, **extra)
+    extra = {"use_graphs": use_graphs}
+    if step_token_budget is not None:
+        extra["step_token_budget"] = step_token_budget
+    dev = f"cuda:{device}"
+    if model_dir is not None:
+        model = Model.from_dir(model_dir, dtype=dtype, device=dev, max_tokens=total, max_seq_tokens=ctx,
+                               allow_unexpected_tensors=allow_unexpected_tensors, **extra)
+    else:
+        from .weights import RandomWeightStore
+        # norm weights exactly 1, matrices N(0, 0.02): the sizes-only models of a benchmark
+        store = RandomWeightStore(cfg, random_seed, device=dev, std=0.02, norm_jitter=0.0)
+        model = Model.from_config(cfg, store, dtype=dtype, device=dev, max_tokens=total, max_seq_tokens=ctx, **extra)
     return Engine(model)

@@ -280,6 +280,16 @@ class SequenceCache:
     def free_tokens(self) -> int:
         return min((g.pool.n_free for g in self.kv_groups), default=self.n_pages) * PAGE_TOKENS
 
+    def bytes_read_for(self, slot: int) -> int:
+        """Bytes of keys and values an attention over ``slot`` reads now: every cache entry, the
+        tokens the sequence holds (a window group: at most its window), keys and values."""
+        n = self.length(slot)
+        total = 0
+        for g in self.kv_groups:
+            tokens = n if g.need.window is None else min(n, g.need.window)
+            total += len(g.entries) * 2 * tokens * g.need.n_kv_heads * g.need.head_dim * g.k.element_size()
+        return total + sum(t.shape[1] * 4 for t in self._state.values())
+
     def bytes_held(self) -> int:
         n = sum(g.k.numel() * g.k.element_size() * 2 + g.table.numel() * 4 for g in self.kv_groups)
         return n + sum(t.numel() * 4 for t in self._state.values()) + self.rng_state.numel() * 8

@@ -321,5 +321,10 @@ class LlamaConfig:
             shapes[f"{p}.mlp.down_proj.weight"] = [h, i]
         return shapes
 
+    def ignorable_tensor(self, name: str) -> bool:
+        """Stored tensors that are no parameters: the rotary frequency buffer some exporters write
+        per layer (this engine computes the frequencies from the configuration)."""
+        return name.endswith("rotary_emb.inv_freq")
+
     def is_norm_tensor(self, name: str) -> bool:
         return name.endswith("norm.weight") or name.endswith("layernorm.weight")

@@ -115,6 +115,9 @@ class PlainKernels:
     def argmax(self, logits, out):
         ops.argmax(logits, out)
 
+    def target_nll(self, logits, targets, out):
+        ops.target_nll(logits, targets, out)
+
     def sample(self, logits, temperature, top_k, top_p, slots, rng_state, out, drawn_u=None):
         ops.sample(logits, temperature, top_k, top_p, slots, rng_state, out, drawn_u)
 

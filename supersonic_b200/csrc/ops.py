@@ -213,6 +213,17 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
         _ptr(out), _stream()), "argmax")
 
 
+def target_nll(logits: torch.Tensor, targets: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = -log softmax(logits[r])[targets[r]] (float32; NaN for a target outside the vocabulary)."""
+    _need(logits, "logits", torch.float32, 2); _need(targets, "targets", torch.int32, 1)
+    _need(out, "out", torch.float32, 1)
+    if targets.shape[0] != logits.shape[0] or out.shape[0] != logits.shape[0]:
+        raise KernelError("target_nll: one target and one output per row")
+    _check(_fn("sampling", "ssb_target_nll")(
+        _ptr(logits), c_longlong(logits.stride(0)), c_int(logits.shape[0]), c_int(logits.shape[1]),
+        _ptr(targets), _ptr(out), _stream()), "target_nll")
+
+
 def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
            slots: Optional[torch.Tensor], rng_state: torch.Tensor, out: torch.Tensor,
            drawn_u: Optional[torch.Tensor] = None) -> None:

@@ -84,6 +84,36 @@ SSB_API int ssb_argmax(const float* logits, long long ld, int n_rows, int vocab,
     return ssb_launch_status();
 }
 
+// ---- negative log-likelihood of given targets (teacher-forced scoring) ------------------------
+// nll[r] = max + log(sum_i exp(x_i - max)) - x[target_r] over a row of float32 logits, the
+// reference's formula (crates/runner/src/llama31_engine.rs:465-479 on the host in float64;
+// kernels/prefill_helpers_bridge_cuda.cu:405-463 on the device from bfloat16 logits).  Sums are
+// float32 with a fixed order: per thread ascending, then lanes, then warps.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+target_nll_kernel(const float* __restrict__ logits, long long ld, int vocab, const int* __restrict__ targets,
+                  float* __restrict__ out) {
+    __shared__ float red[SAMPLE_THREADS / 32];
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    float m = -INFINITY;
+    for (int i = threadIdx.x; i < vocab; i += SAMPLE_THREADS) m = fmaxf(m, row[i]);
+    m = block_max(m, red);
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += SAMPLE_THREADS) sum += expf(row[i] - m);
+    sum = block_sum(sum, red);
+    if (threadIdx.x == 0) {
+        const int t = targets[blockIdx.x];
+        out[blockIdx.x] = (t >= 0 && t < vocab) ? m + logf(sum) - row[t] : NAN;
+    }
+}
+
+SSB_API int ssb_target_nll(const float* logits, long long ld, int n_rows, int vocab, const int* targets,
+                           float* out, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (vocab <= 0) return SSB_ERR_BAD_SIZE;
+    target_nll_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, targets, out);
+    return ssb_launch_status();
+}
+
 // ---- temperature / top-k / top-p -------------------------------------------------------
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float inv_temperature, int top_k,

@@ -12,6 +12,7 @@ to the output before the loop sees it; ``max_new_tokens == 0`` still runs the pr
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence
 
@@ -26,6 +27,20 @@ class GenerationResult:
     tokens: List[int] = field(default_factory=list)
     finish_reason: str = "length"         # "stop" (a stop token) or "length" (the budget)
     prompt_tokens: int = 0
+
+
+@dataclass
+class RunStats:
+    """Host-side account of a ``generate`` call: prompt steps (one per batch) and decode steps, with the
+    wall time from a step's start to its tokens being on the host.  The reference prints the same
+    split as ``[prefill]`` and ``[result]`` (crates/runner/src/llama31_engine.rs:1083-1087, 1564-1598)."""
+
+    prefill_steps: int = 0
+    prefill_tokens: int = 0
+    prefill_s: float = 0.0
+    decode_steps: int = 0
+    decode_tokens: int = 0
+    decode_s: float = 0.0
 
 
 def finished(token: int, n_generated: int, max_new_tokens: int, stop_ids) -> Optional[str]:
@@ -64,6 +79,15 @@ class Generator:
         self.model = model
         self.sampler = sampler or Sampler(model.kernels, model.cache.rng_state)
         self.steps_run = 0
+        self.stats = RunStats()
+        self.stage_timings = None          # {"prefill": StageTimings, "decode": StageTimings} while timing is on
+
+    def time_stages(self, on: bool = True) -> None:
+        """Per-stage device timings of the steps that follow (``engine/stage_timings.py``): timed steps
+        run uncaptured, operation by operation, so they are slower than untimed ones."""
+        from .stage_timings import StageTimings
+        self.model.time_stages(on)
+        self.stage_timings = {"prefill": StageTimings(), "decode": StageTimings()} if on else None
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 8,
                  sampling: SamplingParams = SamplingParams(), stop_token_ids=None,
@@ -103,19 +127,33 @@ class Generator:
         try:
             entries = [StepEntry(slot_of[r], prompts[r], [len(prompts[r]) - 1]) for r in live]
             slots = None
+            first = True
             while live:
+                t0 = time.perf_counter()
+                n_step_tokens = sum(len(e.tokens) for e in entries)
                 logits = model.step(entries)
                 self.steps_run += 1
                 if max_new_tokens <= 0:
+                    if getattr(getattr(model, "device", None), "type", "") == "cuda":
+                        torch.cuda.synchronize(model.device)     # nothing is fetched: wait for the prompt step itself
+                    self._account(first, n_step_tokens, t0, None)
                     break
                 if slots is None:                        # the live set changed (or this is the first step)
                     slots = torch.tensor([slot_of[r] for r in live], dtype=torch.int32).to(
                         logits.device, non_blocking=True)
+                timed = self.stage_timings is not None
+                if timed:
+                    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+                    ev[0].record()
                 sampled = self.sampler(logits, slots, sampling)
+                if timed:
+                    ev[1].record()
                 if hasattr(model, "fetch"):
                     tokens = model.fetch(sampled)        # kernel errors are looked at in the same wait
                 else:
                     tokens = sampled.to("cpu").tolist()
+                self._account(first, n_step_tokens, t0, ev if timed else None)
+                first = False
                 if on_step:
                     on_step(live, tokens)
                 still, entries = [], []
@@ -136,3 +174,16 @@ class Generator:
         finally:
             for slot in slot_of.values():
                 model.close_sequence(slot)
+
+    def _account(self, prompt_step: bool, n_tokens: int, t0: float, sampling_events) -> None:
+        dt = time.perf_counter() - t0
+        st = self.stats
+        if prompt_step:
+            st.prefill_steps, st.prefill_tokens, st.prefill_s = st.prefill_steps + 1, st.prefill_tokens + n_tokens, st.prefill_s + dt
+        else:
+            st.decode_steps, st.decode_tokens, st.decode_s = st.decode_steps + 1, st.decode_tokens + n_tokens, st.decode_s + dt
+        if self.stage_timings is not None:
+            ms = self.model.stage_times()
+            if sampling_events is not None:
+                ms["sampling"] = ms.get("sampling", 0.0) + sampling_events[0].elapsed_time(sampling_events[1])
+            self.stage_timings["prefill" if prompt_step else "decode"].add(ms, n_tokens)

@@ -57,6 +57,7 @@ class StepContext:
     kernels: Any
     dtype: torch.dtype
     next_norm: Any = None      # see parts/block.py
+    stage: str = ""            # the part that is running ("embed", "mixer", "feed_forward", "head"): for stage timings
 
 
 class DecodeGraph:
@@ -127,7 +128,7 @@ class Model:
     def __init__(self, spec: ModelSpec, store: WeightStore, dtype="bfloat16", device="cuda:0",
                  max_tokens: int = 4096, max_seq_tokens: Optional[int] = None,
                  max_slots: Optional[int] = None, kernels: Optional[str] = None, config=None,
-                 use_graphs: bool = True, step_token_budget: int = 32768):
+                 use_graphs: bool = True, step_token_budget: int = 32768, preflight: bool = True):
         spec.validate()
         self.spec, self.config = spec, config
         self.dtype = parse_dtype(dtype)
@@ -135,6 +136,12 @@ class Model:
         _require_cuda(self.device)
         self.kernels = kernel_set_for(self.dtype, kernels)
         max_seq = min(max_seq_tokens or spec.max_positions, spec.max_positions, max_tokens)
+        if int(step_token_budget) < 1:
+            raise ValueError("step_token_budget must be at least 1")
+        # weights + cache + the largest step's activations against free memory, before anything is loaded
+        from . import preflight as _preflight
+        self.memory_estimate = (_preflight.check if preflight else _preflight.estimate_only)(
+            spec, store, self.dtype, self.device, max_tokens, max_seq, max_slots, int(step_token_budget))
         weights = WeightAccess(store, self.device)
         build = BuildContext(self.device, self.dtype, self.kernels, weights, max_positions=max_seq + 64)
 
@@ -182,6 +189,7 @@ class Model:
         # the last position any position encoding of the model can encode
         limits = [getattr(getattr(b, "position", None), "max_positions", None) for b in self.blocks]
         self.position_limit = min([int(x) for x in limits if x is not None], default=None)
+        self._timed = None      # a TimedKernels while stage timing is on
         self._graphs: Dict[Any, DecodeGraph] = {}
         self._graph_pool = None
         self.graph_replays = 0
@@ -189,12 +197,15 @@ class Model:
 
     # ---- construction from a folder ---------------------------------------------------
     @staticmethod
-    def from_dir(model_dir: str, **kw) -> "Model":
+    def from_dir(model_dir: str, allow_unexpected_tensors: bool = False, **kw) -> "Model":
         """The model class is chosen by config.json's architecture; weights are checked
-        against the configuration before anything is built."""
+        against the configuration before anything is built.  Tensors the architecture declares
+        as buffers (``ignorable_tensor(name)``) are passed over; any other unexpected tensor is an
+        error unless ``allow_unexpected_tensors`` turns it into a warning."""
         config = load_config(model_dir)
         store = WeightStore.from_dir(model_dir)
-        store.check(config.tensor_shapes())
+        store.check(config.tensor_shapes(), ignorable=getattr(config, "ignorable_tensor", None),
+                    allow_unexpected=allow_unexpected_tensors)
         return Model(spec_from_config(config), store, config=config, **kw)
 
     @staticmethod
@@ -212,7 +223,8 @@ class Model:
         of the entries and of their ``want`` (an empty tensor if nothing is wanted)."""
         cache = self.cache
         starts = [cache.length(e.slot) for e in entries]
-        if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+        if self.use_graphs and self._timed is None \
+                and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             return self._graph_step(entries, starts)
         if sum(len(e.tokens) for e in entries) > self.step_token_budget:
             return self._chunked_step(entries)
@@ -282,8 +294,22 @@ class Model:
             cache.advance(e.slot, 1)
         return logits
 
+    def time_stages(self, on: bool = True):
+        """Switch per-stage timing of the steps that follow on or off (``engine/stage_timings.py``).
+        While it is on, steps run uncaptured through a kernel set that brackets every operation with
+        CUDA events; ``stage_times()`` returns the milliseconds per stage since it was last asked."""
+        from .stage_timings import TimedKernels
+        self._timed = TimedKernels(self.kernels) if on else None
+        return self._timed
+
+    def stage_times(self):
+        return self._timed.collect() if self._timed is not None else {}
+
     def _forward(self, batch: StepBatch) -> torch.Tensor:
-        ctx = StepContext(batch, self.cache, self.kernels, self.dtype)
+        ctx = StepContext(batch, self.cache, self._timed or self.kernels, self.dtype)
+        if self._timed is not None:
+            self._timed.ctx = ctx
+        ctx.stage = "embed"
         residual = self.embedding(ctx, batch.token_ids)
         schedule = self.spec.schedule
         x_in = None
@@ -298,8 +324,42 @@ class Model:
             x_in = next_in
         if batch.n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        ctx.stage = "head"
         normed = self.final_norm(ctx, residual, rows=batch.want_rows)
         return self.head(ctx, normed)
+
+    # ---- what a step must read (for rooflines) ------------------------------------------------
+    def weight_tensors(self) -> list:
+        """Every device tensor the parts that run in a step hold (mixers, feed-forwards, norms, head),
+        each storage once: a tied head and a fused view count with the tensor they share.  Position
+        tables and the embedding table are left out: a step reads a row of them per token."""
+        parts = [self.final_norm, self.head]
+        for b in self.blocks:
+            parts += [getattr(b, n, None) for n in ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")]
+        seen, out = set(), []
+        for p in parts:
+            for v in (vars(p).values() if p is not None and hasattr(p, "__dict__") else ()):
+                if isinstance(v, torch.Tensor) and v.device.type == "cuda" and v.dim() >= 1:
+                    key = v.untyped_storage().data_ptr()
+                    if key not in seen:
+                        seen.add(key)
+                        out.append(v)
+        return out
+
+    def weight_bytes(self) -> int:
+        return sum(t.untyped_storage().nbytes() for t in self.weight_tensors())
+
+    def matrix_elements(self) -> int:
+        """Elements of the two-dimensional weights a token passes through (the head aside)."""
+        head = {t.untyped_storage().data_ptr() for t in vars(self.head).values() if isinstance(t, torch.Tensor)}
+        return sum(t.untyped_storage().nbytes() // t.element_size() for t in self.weight_tensors()
+                   if t.dim() == 2 and t.untyped_storage().data_ptr() not in head)
+
+    def decode_step_bytes(self, slots) -> int:
+        """Bytes one decode step of ``slots`` has to read: every weight once, a row of the embedding
+        per sequence, and the keys and values (and fixed state) of those sequences."""
+        row = self.spec.hidden_size * torch.empty((), dtype=self.dtype).element_size()
+        return self.weight_bytes() + len(slots) * row + sum(self.cache.bytes_read_for(s) for s in slots)
 
     def check_errors(self) -> None:
         """Raise if a kernel reported a bounded wait that ran out.  Call after results have been

@@ -55,6 +55,16 @@ class Attention:
     def cache_need(self):
         return KvNeed(self.n_kv, self.head_dim, self.window)
 
+    @staticmethod
+    def cache_need_from(params):
+        """What ``cache_need()`` will say, from the parameters alone (asked before anything is built)."""
+        return KvNeed(int(params["num_kv_heads"]), int(params["head_dim"]), params.get("window"))
+
+    @staticmethod
+    def activation_elements(params) -> int:
+        """Elements per token this part holds while it runs: [q | k | v] and the attention output."""
+        return (2 * int(params["num_heads"]) + 2 * int(params["num_kv_heads"])) * int(params["head_dim"])
+
     def forward(self, ctx, x, residual, cache_id, writes_cache, position):
         T = ctx.batch.n_tokens
         kv = ctx.cache.kv(cache_id)

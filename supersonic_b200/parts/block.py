@@ -36,7 +36,9 @@ class PreNormBlock:
         if first is not None:
             ctx.kernels.hint_next_weights(first())
         ctx.next_norm = x2
+        ctx.stage = "mixer"           # names the running part for stage timings; nothing depends on it
         self.mixer.forward(ctx, self._give(x, self.mixer), residual, cache_id, writes_cache, self.position)
         ctx.next_norm = next_in
+        ctx.stage = "feed_forward"
         self.feed_forward.forward(ctx, self._give(x2, self.feed_forward), residual)
         ctx.next_norm = None

@@ -32,6 +32,11 @@ class SwiGLU:
         self.w_gate_up, self.layout = build.kernels.pack_gate_up(gate, up)
         self.dtype = build.dtype
 
+    @staticmethod
+    def activation_elements(params) -> int:
+        """Elements per token this part holds while it runs: gate and up, and their product."""
+        return 3 * int(params["intermediate_size"])
+
     def first_weights(self):
         """The weights this part streams first (a mixer before it may warm the cache with them)."""
         return self.w_gate_up

@@ -106,10 +106,19 @@ class WeightStore:
         t = self._tensors[name]
         return t[0].dtype(t[1]) if isinstance(t, tuple) else t.dtype
 
-    def check(self, expected: Dict[str, List[int]]) -> None:
-        """Raise one :class:`WeightError` listing every mismatch with ``expected``."""
+    def check(self, expected: Dict[str, List[int]], ignorable=None, allow_unexpected: bool = False) -> None:
+        """Raise one :class:`WeightError` listing every mismatch with ``expected``.  ``ignorable(name)``
+        names stored tensors that are no parameters (buffers some exporters write, such as
+        ``rotary_emb.inv_freq``): they are passed over.  ``allow_unexpected``: other unexpected
+        tensors are reported with a warning instead of the error (the reference never looks at
+        tensors it does not ask for: crates/qwen35/src/loader.rs:142-159)."""
         missing = [n for n in expected if n not in self._tensors]
-        unexpected = [n for n in self._tensors if n not in expected]
+        unexpected = [n for n in self._tensors if n not in expected and not (ignorable and ignorable(n))]
+        if unexpected and allow_unexpected:
+            import warnings
+            warnings.warn(f"weights in {self.where}: {len(unexpected)} tensors the configuration does not "
+                          f"name are ignored: {', '.join(unexpected[:8])}{' ...' if len(unexpected) > 8 else ''}")
+            unexpected = []
         wrong_shape, wrong_dtype = [], []
         for n, want in expected.items():
             if n in self._tensors:

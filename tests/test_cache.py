@@ -150,3 +150,35 @@ def test_the_size_estimate_is_what_a_cache_allocates():
     big = {i: KvNeed(8, 128) for i in range(32)}
     need = SequenceCache.bytes_needed(big, 64 * 8192, 8192, torch.bfloat16, 64)
     assert 64 * 2 ** 30 <= need < 64 * 2 ** 30 + 2 ** 20
+
+
+def test_a_slot_opened_without_a_seed_starts_from_its_own_fixed_state():
+    """Never zero (the fixed point of xorshift64), never what the slot's last sequence left."""
+    import torch
+    from supersonic_b200.cache import KvNeed, SequenceCache
+    cache = SequenceCache({0: KvNeed(1, 16)}, 256, 128, torch.float32, "cpu", max_slots=3)
+    a = cache.acquire()
+    first = int(cache.rng_state[a])
+    assert first != 0
+    cache.rng_state[a] = 12345                  # a sequence drew from it
+    cache.release(a)
+    b = cache.acquire()
+    assert b == a and int(cache.rng_state[b]) == first
+    c = cache.acquire()
+    assert int(cache.rng_state[c]) not in (0, first)
+    d = cache.acquire(rng_seed=0)               # an explicit zero seed is replaced, as the reference does
+    assert int(cache.rng_state[d]) != 0
+
+
+def test_the_sequence_limit_is_the_one_asked_for_not_its_page_rounding():
+    import pytest
+    import torch
+    from supersonic_b200.cache import CacheFull, KvNeed, SequenceCache
+    cache = SequenceCache({0: KvNeed(1, 16)}, 512, 100, torch.float32, "cpu")
+    assert cache.max_seq_tokens == 100
+    s = cache.acquire()
+    cache.reserve(s, 100)
+    cache.advance(s, 100)
+    with pytest.raises(CacheFull):
+        cache.reserve(s, 1)
+    cache.check()

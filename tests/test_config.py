@@ -117,3 +117,22 @@ def test_registry_and_presets():
     assert preset_config("llama3.2-1b").head_dim == 64 and preset_config("llama3.2-3b").tie_word_embeddings
     with pytest.raises(ConfigError, match="unknown preset"):
         preset_config("llama-9000")
+
+
+def test_memory_estimate_of_the_8b_preset():
+    """Weights + cache + workspace from the model's description alone: 16.06 GB of bfloat16 weights,
+    64 GiB for 64 slots of 8,192 tokens at 131,072 bytes a token."""
+    import torch
+    from supersonic_b200.config import preset_config
+    from supersonic_b200.engine import preflight
+    from supersonic_b200.weights import RandomWeightStore
+    cfg = preset_config("llama3.1-8b")
+    est = preflight.estimate(cfg.build_spec(), RandomWeightStore(cfg, 2), torch.bfloat16, 64 * 8192, 8192, 64, 32768)
+    assert est.weights == 2 * cfg.parameter_count() == 16_060_522_496
+    assert abs(est.cache - 64 * 8192 * cfg.kv_bytes_per_token(2)) < (1 << 20)
+    assert est.cache >= 64 * (1 << 30)
+    # a step of 32,768 tokens: float32 residual, two bfloat16 copies, and the widest part (3 x 14,336)
+    assert est.workspace == 32768 * (4 * 4096 + 2 * (2 * 4096 + 3 * 14336)) + 2 * 64 * 128256 * 4
+    assert "kv_cache=64.0" in est.line(64 * 8192)
+    f32 = preflight.estimate(cfg.build_spec(), RandomWeightStore(cfg, 2), torch.float32, 4096, 4096, 1, 4096)
+    assert f32.weights == 4 * cfg.parameter_count() - 2 * (2 * 32 + 1) * 4096      # norm vectors stay as stored

@@ -229,16 +229,19 @@ def test_a_step_over_its_token_budget_runs_in_chunks_with_the_same_logits(model_
     assert m.cache.length(s0) == 0
 
 
-def test_a_cache_the_device_cannot_hold_is_refused_before_it_is_allocated(model_folders):
-    from supersonic_b200.cache import CacheError
+def test_a_model_the_device_cannot_hold_is_refused_before_anything_is_loaded(model_folders):
     from supersonic_b200.engine import Model
+    from supersonic_b200.engine.preflight import MemoryPreflightError
     d, pc, pw = model_folders["A"]
+    torch.cuda.empty_cache()
     free_before = torch.cuda.mem_get_info()[0]
-    with pytest.raises(CacheError, match="GiB are free"):
+    with pytest.raises(MemoryPreflightError, match=r"\[vram\] estimated=.*kv_cache=.*do not fit"):
         Model.from_dir(d, dtype="float32", max_tokens=1 << 34, max_seq_tokens=256, max_slots=4)
     torch.cuda.empty_cache()
     assert torch.cuda.mem_get_info()[0] >= free_before - (64 << 20)      # nothing of it was allocated
-    Model.from_dir(d, dtype="float32", max_tokens=256)                    # and the device is as usable as before
+    m = Model.from_dir(d, dtype="float32", max_tokens=256)                # and the device is as usable as before
+    est = m.memory_estimate
+    assert est.cache == m.cache.bytes_held() and est.weights > 0 and est.workspace > 0
 
 
 @pytest.mark.parametrize("dtype,graphs", [("float32", False), ("bfloat16", True), ("bfloat16", False)])
@@ -274,3 +277,119 @@ def test_a_position_limit_that_is_no_multiple_of_the_page_size(tmp_path, dtype, 
     assert len(eng.generate([toks[:92]], max_new_tokens=8, ignore_eos=True)[0]) == 8
     with pytest.raises(ValueError, match="exceed"):
         eng.generate([toks[:95]], max_new_tokens=8, ignore_eos=True)
+
+
+def _run_cli(*args):
+    cmd = [sys.executable, os.path.join(rh.ROOT, "bin", "supersonic")] + [str(a) for a in args]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+
+
+def _preset_plain(name, seed, tmp_path):
+    """The plain side of ``--preset NAME --random-seed SEED``: the same generator writes the folder."""
+    from supersonic_b200.config import preset_config
+    from supersonic_b200.weights import write_model_folder
+    write_model_folder(preset_config(name), seed, str(tmp_path), std=0.02, norm_jitter=0.0)
+    return pl.read_model_folder(str(tmp_path))
+
+
+def test_command_line_with_a_preset_a_prompt_file_and_stop_ids(tmp_path):
+    """``--preset tiny-b --random-seed 5`` makes its weights on the device; a folder written on the host
+    from the same seed is the same model, so the plain implementation can check the tokens.  Three
+    prompts from a file at batch size 2: two batches, and [prefill] counts all three prompts."""
+    pc, pw = _preset_plain("tiny-b", 5, tmp_path / "m")
+    rng = np.random.default_rng(51)
+    prompts = [rng.integers(0, pc["vocab_size"], n).tolist() for n in (6, 13, 4)]
+    free = [pl.greedy_generate(pc, pw, p, 7) for p in prompts]
+    stop = free[1][3]
+    f = tmp_path / "prompts.txt"
+    f.write_text("# three prompts\n" + "\n".join(", ".join(map(str, p)) for p in prompts[:2]) + "\n\n"
+                 + " ".join(map(str, prompts[2])) + "  # spaces work too\n")
+    proc = _run_cli("--preset", "tiny-b", "--random-seed", 5, "--prompt-file", f, "--max-new-tokens", 7,
+                    "--dtype", "float32", "--stop-ids", stop, "--batch-size", 2, "--emit-stage-timings")
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    got = [[int(t) for t in l.split()[1:]] for l in proc.stdout.splitlines() if l.startswith("[tokens] ")]
+    assert got == [pl.greedy_generate(pc, pw, p, 7, stop_ids=[stop]) for p in prompts]
+    assert len(got[1]) == 4
+    assert "[prefill] 23 tokens in" in proc.stderr and "(2 batches)" in proc.stderr
+    assert "[vram] estimated=" in proc.stderr
+    stage = [l for l in proc.stderr.splitlines() if l.startswith("[stage] decode")][0]
+    fields = dict(kv.split("=") for kv in stage.split()[2:])
+    assert float(fields["full_attn_proj"]) > 0 and float(fields["full_attn_core"]) > 0 and float(fields["mlp"]) > 0
+    assert float(fields["rms_norm"]) > 0 and float(fields["lm_head"]) > 0 and float(fields["sampling"]) > 0
+    assert abs(float(fields["full_attn"]) - float(fields["full_attn_proj"]) - float(fields["full_attn_core"])) < 0.2
+
+
+def test_command_line_refusals():
+    assert _run_cli("--prompt-ids", "1,2").returncode == 2                         # no model
+    assert _run_cli("--preset", "no-such", "--prompt-ids", "1").returncode == 2
+    assert _run_cli("--preset", "tiny-a", "--prompt-ids", "1,x").returncode == 2
+    assert _run_cli("--preset", "tiny-a", "--prompt-ids", "1,2,3", "--context-size", 4).returncode == 2
+    out = _run_cli("--list-presets")
+    assert out.returncode == 0 and "llama3.1-8b" in out.stdout and "tiny-a" in out.stdout
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("decode_step", [False, True])
+def test_teacher_forced_scoring(model_folders, dtype, decode_step):
+    """Negative log-likelihood of given tokens, through the prompt step (in pieces) or token by token,
+    against the plain logits' log-softmax; three sequences of unequal lengths as one batch."""
+    import supersonic_b200
+    from supersonic_b200.engine.score import teacher_forced
+    d, pc, pw = model_folders["C"]
+    rng = np.random.default_rng(61)
+    seqs = [rng.integers(0, pc["vocab_size"], n).tolist() for n in (40, 2, 17)]
+    eng = supersonic_b200.load(d, dtype=dtype, context_size=64, batch_size=3)
+    got = teacher_forced(eng.model, seqs, decode_step=decode_step, rows_per_step=16)
+    for s, g in zip(seqs, got):
+        logits = pl.forward(pc, pw, s)[:-1]
+        m = logits.max(axis=1, keepdims=True)
+        nll = (m[:, 0] + np.log(np.exp(logits - m).sum(axis=1))) - logits[np.arange(len(s) - 1), s[1:]]
+        assert g.scored_tokens == len(s) - 1 and g.tokens == len(s)
+        tol = 2e-5 if dtype == "float32" else 2e-2 * np.abs(logits).max()
+        assert abs(g.avg_nll - nll.mean()) < tol
+        assert abs(g.perplexity - np.exp(nll.mean())) < 2 * tol * np.exp(nll.mean())
+        assert g.decode_steps == (len(s) - 2 if decode_step else 0)
+    assert eng.model.cache.slots.n_held == 0
+    assert eng.score(seqs[:1])[0].scored_tokens == 39
+
+
+def test_command_line_teacher_forced(model_folders):
+    import json
+    d, pc, pw = model_folders["A"]
+    seq = np.random.default_rng(62).integers(0, 256, 20).tolist()
+    proc = _run_cli("--model-dir", d, "--prompt-ids", ",".join(map(str, seq)), "--teacher-forced", "--dtype", "float32")
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    line = [l for l in proc.stdout.splitlines() if l.startswith("[teacher_forced_json] ")][0]
+    rec = json.loads(line[len("[teacher_forced_json] "):])
+    logits = pl.forward(pc, pw, seq)[:-1]
+    m = logits.max(axis=1, keepdims=True)
+    nll = (m[:, 0] + np.log(np.exp(logits - m).sum(axis=1))) - logits[np.arange(19), seq[1:]]
+    assert rec["scored_tokens"] == 19 and abs(rec["total_nll"] - nll.sum()) < 1e-3
+    assert abs(rec["perplexity"] - np.exp(nll.mean())) < 1e-3 and "[teacher_forced] tokens=20" in proc.stderr
+
+
+def test_a_folder_with_buffer_tensors_loads(tmp_path):
+    """``rotary_emb.inv_freq`` buffers that some exporters store are passed over; any other tensor the
+    configuration does not name is an error that lists it, or a warning if the caller says so."""
+    import tiny_configs
+    import warnings
+    from supersonic_b200.config import config_from_dict
+    from supersonic_b200.engine import Model
+    from supersonic_b200.weights import WeightError, random_tensors, write_safetensors
+    cfg = config_from_dict(tiny_configs.A)
+    tensors = dict(random_tensors(cfg, 0))
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    import json
+    (tmp_path / "config.json").write_text(json.dumps(cfg.to_dict()))
+    write_safetensors(str(tmp_path / "model.safetensors"), [(n, t.dtype, list(t.shape)) for n, t in tensors.items()],
+                      iter(tensors.items()))
+    Model.from_dir(str(tmp_path), dtype="float32", max_tokens=64)
+    tensors["model.extra.weight"] = torch.ones(3)
+    write_safetensors(str(tmp_path / "model.safetensors"), [(n, t.dtype, list(t.shape)) for n, t in tensors.items()],
+                      iter(tensors.items()))
+    with pytest.raises(WeightError, match="unexpected .*model.extra.weight"):
+        Model.from_dir(str(tmp_path), dtype="float32", max_tokens=64)
+    with warnings.catch_warnings(record=True) as seen:
+        warnings.simplefilter("always")
+        Model.from_dir(str(tmp_path), dtype="float32", max_tokens=64, allow_unexpected_tensors=True)
+    assert any("model.extra.weight" in str(w.message) for w in seen)

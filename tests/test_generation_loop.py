@@ -195,3 +195,22 @@ def test_which_gemm_a_prompt_gets_is_decided_by_its_rows():
     assert FK._gemm_splits(128, 4096, 4096, 256) == 8                     # at least 8 k-blocks a part
     assert FK._gemm_splits(70, 256, 192, 256) == 1                        # a tiny model: K is too short to cut
     assert FK._tile_n(2048, 4096) == 256 and FK._tile_n(8, 4096) == 64 and FK._tile_n(8, 128256) == 256
+
+
+def test_command_line_helpers(tmp_path):
+    from supersonic_b200 import cli
+    assert cli.parse_ids("1, 2,3 4") == [1, 2, 3, 4]
+    f = tmp_path / "p.txt"
+    f.write_text("# header\n1,2,3\n\n 7 8 9 # tail\n")
+    assert cli.read_prompt_file(str(f)) == [[1, 2, 3], [7, 8, 9]]
+    f.write_text("1,two\n")
+    with pytest.raises(ValueError, match="p.txt:1"):
+        cli.read_prompt_file(str(f))
+    ap = cli.build_parser()
+    a = ap.parse_args(["--preset", "tiny-a", "--random-seed", "3", "--stop-ids", "5,6", "--prompt-file", "x"])
+    assert a.preset == "tiny-a" and a.random_seed == 3 and a.stop_ids == "5,6" and a.prompt_file == ["x"]
+    # refusals that need no device
+    assert cli.main(["--prompt-ids", "1,2"]) == 2
+    assert cli.main(["--preset", "nope", "--prompt-ids", "1"]) == 2
+    assert cli.main(["--preset", "tiny-a", "--prompt-ids", "1,2,3", "--context-size", "4"]) == 2
+    assert cli.main(["--preset", "tiny-a"]) == 2

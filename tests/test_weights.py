@@ -114,3 +114,22 @@ def test_corrupt_files(tmp_path):
     p.write_bytes(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 4)
     with pytest.raises(SafetensorsError, match="unsupported dtype"):
         SafetensorsFile(str(p))
+
+
+def test_buffers_are_passed_over_and_unexpected_tensors_can_be_a_warning():
+    import warnings
+    import torch
+    from supersonic_b200.weights import WeightError, WeightStore
+    store = WeightStore.from_tensors({"a": torch.zeros(2, 3), "x.rotary_emb.inv_freq": torch.zeros(4),
+                                      "stray": torch.zeros(1)})
+    ignorable = lambda n: n.endswith("rotary_emb.inv_freq")
+    with pytest.raises(WeightError) as e:
+        store.check({"a": [2, 3]}, ignorable=ignorable)
+    assert e.value.unexpected == ["stray"]
+    with warnings.catch_warnings(record=True) as seen:
+        warnings.simplefilter("always")
+        store.check({"a": [2, 3]}, ignorable=ignorable, allow_unexpected=True)
+    assert len(seen) == 1 and "stray" in str(seen[0].message)
+    with pytest.raises(WeightError) as e:                      # missing tensors stay an error
+        store.check({"a": [2, 3], "b": [1]}, ignorable=ignorable, allow_unexpected=True)
+    assert e.value.missing == ["b"] and e.value.unexpected == []
