@@ -1,10 +1,10 @@
 """Times single kernels at given sizes with CUDA events (inputs larger than L2 are rotated
 so that weights come from DRAM), and reports bytes or FLOPs per second.
 
-    python -m supersonic_b200.csrc.microbench attention_decode --batch 64 --context 520
-    python -m supersonic_b200.csrc.microbench linear --rows 8 --n 6144 --k 4096 [--kernel skinny|tc64|tc128|tc256]
-    python -m supersonic_b200.csrc.microbench attention_prefill --tokens 2048 --seqs 1 [--kernel tc]
-    python -m supersonic_b200.csrc.microbench gemm --rows 2048 --n 28672 --k 4096 --tile 256
+    python microbench.py attention_decode --batch 64 --context 520
+    python microbench.py linear --rows 8 --n 6144 --k 4096 [--kernel skinny|tc64|tc128|tc256]
+    python microbench.py attention_prefill --tokens 2048 --seqs 1 [--kernel tc]
+    python microbench.py gemm --rows 2048 --n 28672 --k 4096 --tile 256
 
 One JSON line per run.  It is also the small, self-ending workload that profiler captures
 are taken on.
@@ -14,10 +14,13 @@ from __future__ import annotations
 import argparse
 import json
 import math
+import os
+import sys
 
 import torch
 
-from . import ops
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from supersonic_b200.csrc import ops  # noqa: E402
 
 DEV = "cuda:0"
 
@@ -81,9 +84,8 @@ def linear(args):
     ws = [(torch.randn(N, K, device=DEV) * 0.02).bfloat16() for _ in range(copies)]
     x = torch.randn(B, K, device=DEV).bfloat16()
     out = torch.empty(B, N, dtype=torch.bfloat16, device=DEV)
-    if args.kernel.startswith("skinny"):                   # skinny = one block per row tile, skinny4 = clusters of 4
-        k_split = int(args.kernel[6:]) if len(args.kernel) > 6 else 1
-        fn = lambda i: ops.skinny_gemm(x, ws[i % copies], out, pdl=args.pdl, k_split=k_split)
+    if args.kernel == "skinny":                             # the mma.sync skinny GEMM, one block per row tile
+        fn = lambda i: ops.skinny_gemm(x, ws[i % copies], out, pdl=args.pdl)
     elif args.kernel.startswith("gv"):                      # gv = automatic splits, gv4 = 4 splits
         splits = int(args.kernel[2:]) if len(args.kernel) > 2 else ops.gemv_tc_splits(N, K)
         nf, nc = ops.gemv_tc_scratch(B, N, splits)

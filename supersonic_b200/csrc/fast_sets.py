@@ -16,13 +16,6 @@ import torch
 from . import ops
 from .kernel_sets import NormedInput, PlainKernels, as_tensor
 
-FUSED_NORM_MAX_ROWS = 0        # measured: a separate norm launch is faster than the folded one at every batch size
-PREFETCH_BYTES = 64 << 20     # weights pulled into L2 during decode attention (L2 holds 126 MB)
-PREFETCH_MAX_ROWS = 0         # off: measured no gain (the projections are issue-bound, not DRAM-bound)
-SKINNY_MAX_ROWS = 0           # rows up to which the mma.sync skinny GEMM is tried first: none; the tcgen05 kernels stream the
-                              # weights faster at every row count once the tensor-core attention runs beside them (measured:
-                              # 3.42 against 3.64 ms a step at batch 8, 3.27 against 3.29 at batch 1); it remains the kernel
-                              # for shapes they refuse
 TARGET_BLOCKS = 1184           # eight small blocks per SM
 MMA_PAGES_PER_SPLIT = 4       # decode attention on the tensor cores: at least this many pages a block (2, 4, 8 measured)
 TC_ATTENTION_MIN_NEW = 96     # prompts at least this long take the tcgen05 attention (tiles of 128 rows)
@@ -36,10 +29,6 @@ class FastKernels(PlainKernels):
         self.pdl = pdl           # decode kernels launch as programmatic dependents of their predecessors
         self.fuse_rope = True    # decode attention rotates q/k and appends to the cache itself
         self.fuse_rope_prefill = True   # the prompt's q/k/v projection does so in its epilogue
-        # a residual-adding projection can also write the next norm of the residual (its last block
-        # does it); measured slower than the separate norm launch at batch 1 and 8, so it is off
-        self.fuse_post_norm = False
-        self._next_weights = None
         self._scratch: Dict[str, torch.Tensor] = {}
         self._retired = []      # outgrown buffers stay alive: captured graphs still point at them
 
@@ -60,36 +49,18 @@ class FastKernels(PlainKernels):
                                 rotary_dim, page_shift, write_cache)
 
     # ---- matrix products -------------------------------------------------------------
-    def _skinny(self, x, weight, out, mode, then_norm=None):
-        if isinstance(x, NormedInput):
-            if (x._tensor is None and x.fusable and x.n_rows <= FUSED_NORM_MAX_ROWS
-                    and ops.skinny_gemm_ok(x.residual, weight, True) and x.weight.data_ptr() % 16 == 0):
-                ops.skinny_gemm(x.residual, weight, out, mode, norm_weight=x.weight, eps=x.eps, pdl=self.pdl)
-                return True
-            x = x.tensor()
-        if ops.skinny_gemm_ok(x, weight, False):
-            post = None
-            if (then_norm is not None and mode == ops.SG_ACCUMULATE and self.fuse_post_norm and then_norm.fusable
-                    and then_norm._tensor is None and then_norm.residual is out and out.is_contiguous()
-                    and out.shape[1] % 4 == 0 and then_norm.weight.data_ptr() % 16 == 0):
-                normed = torch.empty(out.shape, dtype=torch.bfloat16, device=out.device)
-                post = (then_norm.weight, then_norm.eps, normed,
-                        self._buffer("post_norm_counter", 1, torch.int32, out.device, zero=True))
-            # clusters that split K (k_split > 1) measured slower at every 8B shape: more and shorter
-            # blocks mean more waves, and a wave's fixed cost is what a short projection pays for
-            ops.skinny_gemm(x, weight, out, mode, pdl=self.pdl, post_norm=post)
-            if post is not None:
-                then_norm.provide(post[2])
-            return True
-        return False
-
-    def linear(self, x, weight, out, accumulate=False, then_norm=None):
-        rows = x.n_rows if isinstance(x, NormedInput) else x.shape[0]
-        if rows <= SKINNY_MAX_ROWS and weight.dtype == torch.bfloat16 and (out.dtype == torch.float32 or not accumulate):
-            if self._skinny(x, weight, out, ops.SG_ACCUMULATE if accumulate else ops.SG_STORE, then_norm):
-                return
+    def _skinny(self, x, weight, out, mode) -> bool:
+        """The mma.sync skinny GEMM, for up to 64 rows of shapes the tcgen05 kernels refuse."""
         x = as_tensor(x)
-        if rows > SKINNY_MAX_ROWS and (out.dtype == torch.float32 or not accumulate) and ops.gemm_tc_ok(x, weight, out):
+        if not ops.skinny_gemm_ok(x, weight):
+            return False
+        ops.skinny_gemm(x, weight, out, mode, pdl=self.pdl)
+        return True
+
+    def linear(self, x, weight, out, accumulate=False):
+        rows = x.n_rows if isinstance(x, NormedInput) else x.shape[0]
+        x = as_tensor(x)
+        if (out.dtype == torch.float32 or not accumulate) and ops.gemm_tc_ok(x, weight, out):
             n, k = weight.shape
             if rows <= 64 and accumulate:
                 # weights on the M side, K split over blocks that add with float atomics
@@ -159,9 +130,7 @@ class FastKernels(PlainKernels):
 
     def gate_up_swiglu(self, x, w_gate_up, layout, out):
         rows = x.n_rows if isinstance(x, NormedInput) else x.shape[0]
-        if layout == "interleaved" and rows <= SKINNY_MAX_ROWS and self._skinny(x, w_gate_up, out, ops.SG_SWIGLU):
-            return
-        if layout == "interleaved" and rows > SKINNY_MAX_ROWS:
+        if layout == "interleaved":
             xt = as_tensor(x)
             if w_gate_up.shape[0] % 16 == 0 and ops.gemm_tc_ok(xt, w_gate_up, out):
                 if rows <= 64:
@@ -184,11 +153,6 @@ class FastKernels(PlainKernels):
             t = (torch.zeros if zero else torch.empty)(max(n, 4096), dtype=dtype, device=device)
             self._scratch[name] = t
         return t
-
-    def hint_next_weights(self, weight) -> None:
-        """The weights that will be streamed after the next latency-bound kernel (attention);
-        that kernel asks L2 to fetch the head of them while it waits on its own small loads."""
-        self._next_weights = weight
 
     def _decode_attention(self, q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim,
                           page_shift, window, scale, cos=None, sin=None):
@@ -222,10 +186,7 @@ class FastKernels(PlainKernels):
             counters = self._buffer("attn_counters", nc, torch.int32, q.device, zero=True)
         ops.attention_decode(q, k_cache, v_cache, batch.pos, batch.slot_of_token, page_table, out,
                              n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters,
-                             pdl=self.pdl, cos=cos, sin=sin, kind=kind,
-                             prefetch=self._next_weights if batch.n_seqs <= PREFETCH_MAX_ROWS else None,
-                             prefetch_bytes=PREFETCH_BYTES)
-        self._next_weights = None
+                             pdl=self.pdl, cos=cos, sin=sin, kind=kind)
 
     def project_rope_append(self, x, w_qkv, qkv, position, kv, batch, n_q, n_kv, head_dim, page_shift) -> bool:
         """Prompts whose tiles alone fill the SMs: the tcgen05 projection rotates q and k from its

@@ -41,10 +41,6 @@ class NormedInput:
     def n_rows(self) -> int:
         return self.residual.shape[0]
 
-    def provide(self, tensor: torch.Tensor) -> None:
-        """A kernel computed the norm on its way: ``tensor()`` will return this."""
-        self._tensor = tensor
-
     def tensor(self) -> torch.Tensor:
         if self._tensor is None:
             self._tensor = self.norm(self.ctx, self.residual)
@@ -65,10 +61,8 @@ class PlainKernels:
     def rmsnorm(self, x, weight, eps, out, rows=None):
         ops.rmsnorm(x, weight, eps, out, rows)
 
-    def linear(self, x, weight, out, accumulate=False, then_norm=None):
-        """out (+)= x @ weight^T; ``x`` may be a :class:`NormedInput`.  ``then_norm``: the
-        :class:`NormedInput` of ``out`` that will be asked for next, if this call is the last
-        change to ``out`` before it; a set may compute it on the way (here it is left alone)."""
+    def linear(self, x, weight, out, accumulate=False):
+        """out (+)= x @ weight^T; ``x`` may be a :class:`NormedInput`."""
         ops.gemm_nt_plain(as_tensor(x), weight, out, accumulate)
 
     def pack_gate_up(self, gate, up):
@@ -91,9 +85,6 @@ class PlainKernels:
                     rotary_dim, page_shift, write_cache=True):
         ops.rope_append(qkv, cos, sin, batch.pos, batch.slot_of_token, page_table, k_cache, v_cache,
                         n_q, n_kv, head_dim, rotary_dim, page_shift, write_cache)
-
-    def hint_next_weights(self, weight) -> None:
-        """Told by a block which weights will be streamed after its mixer; a set may use it."""
 
     def rope_attention(self, qkv, position, kv, batch, out, n_q, n_kv, head_dim, page_shift, window,
                        scale) -> bool:

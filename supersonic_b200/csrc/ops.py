@@ -250,58 +250,29 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
 SG_STORE, SG_ACCUMULATE, SG_SWIGLU = 0, 1, 2
 
 
-def skinny_gemm_ok(x: torch.Tensor, w: torch.Tensor, normed: bool) -> bool:
+def skinny_gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether the skinny GEMM takes these operands (else the plain kernels do)."""
-    return (w.dtype == torch.bfloat16 and x.shape[0] <= 64 and w.shape[1] % 8 == 0
+    return (w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and x.shape[0] <= 64 and w.shape[1] % 8 == 0
             and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
-            and w.data_ptr() % 16 == 0 and x.dtype == (torch.float32 if normed else torch.bfloat16))
+            and w.data_ptr() % 16 == 0)
 
 
 def skinny_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = SG_STORE,
-                norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, pdl: bool = False,
-                post_norm=None, k_split: int = 1) -> None:
-    """out = x @ w^T for up to 64 rows.  With ``norm_weight`` x is the float32 residual and is
-    RMS-normalised on the way in.  ``pdl``: launch as a programmatic dependent of the kernel
-    before it on the stream (its weights are prefetched while that kernel ends).
-    ``post_norm`` = (weight, eps, out bfloat16 [rows, N], zeroed int32 counter), with mode accumulate:
-    the block that finishes last also writes RMSNorm(out) of the finished rows into it.  mode: store, add into float32 ``out``, or SwiGLU over rows
-    of ``w`` that come as [8 gate | 8 up] per 16 (``out`` is [rows, N/2]).  ``k_split`` (1..8):
-    blocks per thread-block cluster that share a row tile and split K (see ``skinny_k_split``)."""
-    _need(x, "x", torch.float32 if norm_weight is not None else torch.bfloat16, 2)
-    _need(w, "w", torch.bfloat16, 2); _need(out, "out", None, 2)
+                pdl: bool = False) -> None:
+    """out = x @ w^T for up to 64 rows on mma.sync (the decode projection for shapes the tcgen05
+    kernels refuse).  ``pdl``: launch as a programmatic dependent of the kernel before it on the
+    stream (its weights are prefetched while that kernel ends).  mode: store, add into float32
+    ``out``, or SwiGLU over rows of ``w`` that come as [8 gate | 8 up] per 16 (``out`` is [rows, N/2])."""
+    _need(x, "x", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(out, "out", None, 2)
     B, K = x.shape
     N = w.shape[0]
     n_out = N // 2 if mode == SG_SWIGLU else N
     if w.shape[1] != K or tuple(out.shape) != (B, n_out):
         raise KernelError(f"skinny_gemm: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
-    if norm_weight is not None:
-        _need(norm_weight, "norm_weight", None, 1)
-        if norm_weight.shape[0] != K:
-            raise KernelError("skinny_gemm: norm weight width")
-    pw = pout = pcount = None
-    peps = 0.0
-    if post_norm is not None:
-        pw, peps, pout, pcount = post_norm
-        _need(pw, "post norm weight", None, 1); _need(pout, "post norm out", torch.bfloat16, 2)
-        _need(pcount, "post norm counter", torch.int32)
-        if mode != SG_ACCUMULATE or pw.shape[0] != N or tuple(pout.shape) != (B, N) or not pout.is_contiguous():
-            raise KernelError("skinny_gemm: the post norm goes with mode accumulate and out-shaped tensors")
     _check(_fn("decode_ops", "ssb_skinny_gemm")(
-        _ptr(x), c_int(x.stride(0)), _ptr(norm_weight),
-        c_int(dtype_code(norm_weight.dtype) if norm_weight is not None else 0), c_float(eps), _ptr(w),
-        c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(dtype_code(out.dtype)), c_int(B),
-        c_int(N), c_int(K), c_int(mode), c_int(1 if pdl else 0), _ptr(pw),
-        c_int(dtype_code(pw.dtype) if pw is not None else 0), c_float(peps), _ptr(pout), _ptr(pcount),
-        c_int(k_split), _stream()), "skinny_gemm")
-
-
-def skinny_k_split(rows: int, n: int, k: int, target_blocks: int) -> int:
-    """Cluster size for ``skinny_gemm``: enough blocks to put several on every SM, each with at
-    least 512 columns of K (only the 16-row tiles of up to 8 batch rows are short of blocks)."""
-    if rows > 8:
-        return 1
-    tiles = (n + 15) // 16
-    return max(1, min(8, target_blocks // tiles, k // 512))
+        _ptr(x), c_int(x.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)),
+        c_int(dtype_code(out.dtype)), c_int(B), c_int(N), c_int(K), c_int(mode), c_int(1 if pdl else 0),
+        _stream()), "skinny_gemm")
 
 
 def attention_decode_scratch(n_seqs: int, n_q: int, n_kv: int, head_dim: int, n_splits: int):

@@ -56,7 +56,6 @@ class StepContext:
     cache: SequenceCache
     kernels: Any
     dtype: torch.dtype
-    next_norm: Any = None      # see parts/block.py
     stage: str = ""            # the part that is running ("embed", "mixer", "feed_forward", "head"): for stage timings
 
 
@@ -311,17 +310,8 @@ class Model:
             self._timed.ctx = ctx
         ctx.stage = "embed"
         residual = self.embedding(ctx, batch.token_ids)
-        schedule = self.spec.schedule
-        x_in = None
-        for i, stop in enumerate(schedule):
-            block = self.blocks[stop.layer]
-            nxt = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
-            next_in = nxt.input_norm(ctx, residual) if nxt is not None and hasattr(nxt, "input_norm") else None
-            if hasattr(block, "input_norm"):
-                block.forward(ctx, residual, stop.cache, stop.writes_cache, x_in=x_in, next_in=next_in)
-            else:                                           # a block arrangement without this protocol
-                block.forward(ctx, residual, stop.cache, stop.writes_cache)
-            x_in = next_in
+        for stop in self.spec.schedule:
+            self.blocks[stop.layer].forward(ctx, residual, stop.cache, stop.writes_cache)
         if batch.n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         ctx.stage = "head"

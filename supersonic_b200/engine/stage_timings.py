@@ -54,7 +54,7 @@ class TimedKernels:
 
     def __getattr__(self, name):
         attr = getattr(self._inner, name)
-        if name.startswith("_") or not callable(attr) or name in ("pack_gate_up", "hint_next_weights"):
+        if name.startswith("_") or not callable(attr) or name == "pack_gate_up":
             return attr
 
         def timed(*args, **kwargs):

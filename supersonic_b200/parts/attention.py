@@ -76,7 +76,7 @@ class Attention:
             k_cache, v_cache, table, _ = kv          # q is rotated, k and v are in the cache
             ctx.kernels.attention(qkv, k_cache, v_cache, ctx.batch, table, attn, self.n_q, self.n_kv,
                                   self.head_dim, PAGE_SHIFT, self.window, self.scale)
-            ctx.kernels.linear(attn, self.w_o, residual, accumulate=True, then_norm=getattr(ctx, "next_norm", None))
+            ctx.kernels.linear(attn, self.w_o, residual, accumulate=True)
             return
         ctx.kernels.linear(x, self.w_qkv if writes_cache else self.w_q, qkv)
         if not (writes_cache and ctx.kernels.rope_attention(qkv, position, kv, ctx.batch, attn, self.n_q,
@@ -86,4 +86,4 @@ class Attention:
             k_cache, v_cache, table, _ = kv
             ctx.kernels.attention(qkv, k_cache, v_cache, ctx.batch, table, attn, self.n_q, self.n_kv,
                                   self.head_dim, PAGE_SHIFT, self.window, self.scale)
-        ctx.kernels.linear(attn, self.w_o, residual, accumulate=True, then_norm=getattr(ctx, "next_norm", None))
+        ctx.kernels.linear(attn, self.w_o, residual, accumulate=True)

@@ -22,23 +22,10 @@ class PreNormBlock:
         their kernels may fold it in; all others get the normed activations."""
         return x if getattr(part, "takes_lazy_input", False) else x.tensor()
 
-    def input_norm(self, ctx, residual):
-        """The (lazy) input of this block's mixer: a block before it may have it computed."""
-        return NormedInput(ctx, residual, self.mixer_norm)
-
-    def forward(self, ctx, residual, cache_id, writes_cache, x_in=None, next_in=None):
-        """``x_in``: this block's ``input_norm`` if the caller made it already; ``next_in``: the
-        next block's, which the feed-forward's last projection may fill on its way.  ``ctx.next_norm``
-        names, for a part, the norm that will be asked for right after its last change to the residual."""
-        x = x_in if x_in is not None else self.input_norm(ctx, residual)
-        x2 = NormedInput(ctx, residual, self.feed_forward_norm)
-        first = getattr(self.feed_forward, "first_weights", None)
-        if first is not None:
-            ctx.kernels.hint_next_weights(first())
-        ctx.next_norm = x2
+    def forward(self, ctx, residual, cache_id, writes_cache):
+        x = NormedInput(ctx, residual, self.mixer_norm)
         ctx.stage = "mixer"           # names the running part for stage timings; nothing depends on it
         self.mixer.forward(ctx, self._give(x, self.mixer), residual, cache_id, writes_cache, self.position)
-        ctx.next_norm = next_in
+        x2 = NormedInput(ctx, residual, self.feed_forward_norm)
         ctx.stage = "feed_forward"
         self.feed_forward.forward(ctx, self._give(x2, self.feed_forward), residual)
-        ctx.next_norm = None

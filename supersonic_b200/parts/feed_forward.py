@@ -37,11 +37,7 @@ class SwiGLU:
         """Elements per token this part holds while it runs: gate and up, and their product."""
         return 3 * int(params["intermediate_size"])
 
-    def first_weights(self):
-        """The weights this part streams first (a mixer before it may warm the cache with them)."""
-        return self.w_gate_up
-
     def forward(self, ctx, x, residual):
         z = torch.empty((residual.shape[0], self.inter), dtype=self.dtype, device=residual.device)
         ctx.kernels.gate_up_swiglu(x, self.w_gate_up, self.layout, z)
-        ctx.kernels.linear(z, self.w_down, residual, accumulate=True, then_norm=getattr(ctx, "next_norm", None))
+        ctx.kernels.linear(z, self.w_down, residual, accumulate=True)

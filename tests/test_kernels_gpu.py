@@ -291,56 +291,6 @@ def test_skinny_gemm_store_and_accumulate(rows, N, K):
     torch.testing.assert_close(out, plain, atol=2e-5 * math.sqrt(K), rtol=1e-4)
 
 
-@pytest.mark.parametrize("k_split", [2, 3, 4, 8])
-@pytest.mark.parametrize("rows,N,K", [(1, 301, 4096), (8, 48, 1000), (5, 272, 1440), (8, 1000, 72)])
-def test_skinny_gemm_clusters_that_split_k(rows, N, K, k_split):
-    """Clusters of blocks that share a row tile and split K give the unsplit kernel's result in all
-    three modes; K ranges that do not divide evenly, and more blocks than K has chunks."""
-    g = torch.Generator(device=DEV).manual_seed(23)
-    x = torch.randn(rows, K, device=DEV, generator=g).bfloat16()
-    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
-    ref = x.double() @ w.double().T
-    out = torch.empty(rows, N, device=DEV)
-    ops().skinny_gemm(x, w, out, k_split=k_split)
-    torch.testing.assert_close(out.double(), ref, atol=2e-5 * math.sqrt(K), rtol=1e-4)
-    acc = torch.full((rows, N), 2.0, device=DEV)
-    ops().skinny_gemm(x, w, acc, mode=1, k_split=k_split)
-    torch.testing.assert_close(acc.double(), ref + 2, atol=2e-5 * math.sqrt(K), rtol=1e-4)
-    if N % 16 == 0:
-        one = torch.empty(rows, N // 2, dtype=torch.bfloat16, device=DEV)
-        ops().skinny_gemm(x, w, one, mode=2)
-        split = torch.empty_like(one)
-        ops().skinny_gemm(x, w, split, mode=2, k_split=k_split)
-        torch.testing.assert_close(split.float(), one.float(), atol=2e-2, rtol=2e-2)
-    from supersonic_b200.csrc.ops import KernelError
-    with pytest.raises(KernelError):
-        ops().skinny_gemm(x.float(), w, out, norm_weight=torch.ones(K, device=DEV), eps=1e-5, k_split=k_split)
-
-
-@pytest.mark.parametrize("rows,wdtype", [(1, torch.bfloat16), (4, torch.float32), (8, torch.bfloat16)])
-def test_skinny_gemm_with_norm_on_the_way_in(rows, wdtype):
-    g = torch.Generator(device=DEV).manual_seed(21)
-    K, N = 1440, 200
-    res = 3 * torch.randn(rows, K, device=DEV, generator=g)
-    nw = (1 + 0.1 * torch.randn(K, device=DEV, generator=g)).to(wdtype)
-    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
-    normed = torch.empty(rows, K, dtype=torch.bfloat16, device=DEV)
-    ops().rmsnorm(res, nw, 1e-5, normed)
-    unfused = torch.empty(rows, N, device=DEV)
-    ops().skinny_gemm(normed, w, unfused)
-    got = torch.empty(rows, N, device=DEV)
-    ops().skinny_gemm(res, w, got, norm_weight=nw, eps=1e-5)
-    # the fused kernel rounds x * w to bfloat16 and applies the row's scale to the float32 sum;
-    # the separate norm rounds x * scale * w: two roundings of equal size, both near the exact value
-    ref = (res.double() * torch.rsqrt((res.double() ** 2).mean(-1, keepdim=True) + 1e-5) * nw.double()) @ w.double().T
-    torch.testing.assert_close(got.double(), ref, atol=2e-2, rtol=2e-2)
-    err_fused, err_unfused = (got.double() - ref).abs().max().item(), (unfused.double() - ref).abs().max().item()
-    assert err_fused < 2.0 * err_unfused + 1e-6
-    acc = torch.full((rows, N), 2.0, device=DEV)
-    ops().skinny_gemm(res, w, acc, mode=1, norm_weight=nw, eps=1e-5)
-    torch.testing.assert_close(acc, got + 2, atol=1e-5, rtol=1e-6)
-
-
 @pytest.mark.parametrize("rows", [1, 5, 40])
 def test_skinny_gemm_swiglu(rows):
     g = torch.Generator(device=DEV).manual_seed(22)
@@ -673,31 +623,6 @@ def test_attention_decode_with_rotation_and_append_inside(n_q, n_kv, hd, window,
     assert torch.all(got[5] == 0) and torch.all(counters == 0)
 
 
-@pytest.mark.parametrize("rows,wdtype", [(1, torch.bfloat16), (8, torch.float32), (16, torch.bfloat16)])
-def test_skinny_gemm_writes_the_next_norm_of_the_residual(rows, wdtype):
-    """Mode accumulate with a post norm: the residual gets the product added, and the block
-    that finishes last leaves RMSNorm(residual) of the finished rows; twice in a row (the counter
-    is left ready)."""
-    g = torch.Generator(device=DEV).manual_seed(60)
-    K, N = 1440, 4096
-    x = torch.randn(rows, K, device=DEV, generator=g).bfloat16()
-    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).bfloat16()
-    nw = (1 + 0.1 * torch.randn(N, device=DEV, generator=g)).to(wdtype)
-    res = torch.randn(rows, N, device=DEV, generator=g)
-    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
-    for _ in range(2):
-        want_res = res.clone()
-        ops().skinny_gemm(x, w, want_res, mode=1)
-        want = torch.empty(rows, N, dtype=torch.bfloat16, device=DEV)
-        ops().rmsnorm(want_res, nw, 1e-5, want)
-        got = torch.full((rows, N), 7.0, dtype=torch.bfloat16, device=DEV)
-        ops().skinny_gemm(x, w, res, mode=1, post_norm=(nw, 1e-5, got, counter))
-        assert torch.equal(res, want_res) and int(counter.item()) == 0
-        # same formula; the sum of squares is added in another order
-        torch.testing.assert_close(got.float(), want.float(), atol=0, rtol=2 ** -7)
-
-
-# ---- decode projections on tcgen05, weights on the M side ---------------------------------------
 @pytest.mark.parametrize("rows", [1, 16, 17, 33, 64])
 @pytest.mark.parametrize("N,K,splits", [(304, 72, 1), (1000, 4096, 1), (1000, 4096, 5), (128, 640, 3), (272, 1440, 8)])
 def test_gemv_tc(rows, N, K, splits):
