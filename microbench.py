@@ -57,11 +57,19 @@ def attention_decode(args):
     v = torch.randn(n_pages, n_kv, 64, hd, device=DEV).bfloat16()
     table = torch.randperm(n_pages).to(torch.int32).view(B, pages_per).to(DEV)
     pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=DEV)
+    if args.ragged:
+        pos = torch.randint(0, ctx, (B,), generator=torch.Generator().manual_seed(0)).to(torch.int32).to(DEV)
     slot = torch.arange(B, dtype=torch.int32, device=DEV)
     q = torch.randn(B, (n_q + 2 * n_kv) * hd, device=DEV).bfloat16()
     out = torch.empty(B, n_q * hd, dtype=torch.bfloat16, device=DEV)
     splits = args.splits
-    nf, nc = ops.attention_decode_scratch(B, n_q, n_kv, hd, splits)
+    pages = (ctx + 63) // 64
+    chunk = args.chunk_pages or -(-pages // splits)
+    max_chunks = -(-pages // chunk)
+    if args.kind == 2:
+        nf, nc = ops.attention_decode_chunked_scratch(B, n_q, n_kv, hd, max_chunks)
+    else:
+        nf, nc = ops.attention_decode_scratch(B, n_q, n_kv, hd, splits)
     scratch = torch.empty(max(nf, 1), device=DEV)
     counters = torch.zeros(max(nc, 1), dtype=torch.int32, device=DEV)
     cos = sin = None
@@ -69,11 +77,15 @@ def attention_decode(args):
         ang = torch.arange(ctx, device=DEV, dtype=torch.float64)[:, None] * \
             (1.0 / 10000 ** (torch.arange(hd // 2, device=DEV, dtype=torch.float64) * 2 / hd))[None, :]
         cos, sin = ang.cos().float().contiguous(), ang.sin().float().contiguous()
-    us = _time(lambda i: ops.attention_decode(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, None,
-                                              1 / math.sqrt(hd), splits, scratch, counters, kind=args.kind,
-                                              cos=cos, sin=sin, pdl=args.pdl),
-               args.iters)
-    nbytes = B * ctx * n_kv * hd * 2 * 2
+    if args.kind == 2:                               # the tensor-core kernel on its persistent grid
+        fn = lambda i: ops.attention_decode_chunked(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, None,
+                                                    1 / math.sqrt(hd), chunk, max_chunks, scratch, counters,
+                                                    cos=cos, sin=sin, pdl=args.pdl)
+    else:
+        fn = lambda i: ops.attention_decode(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, None,
+                                            1 / math.sqrt(hd), splits, scratch, counters, cos=cos, sin=sin, pdl=args.pdl)
+    us = _time(fn, args.iters)
+    nbytes = int((pos.long() + 1).sum()) * n_kv * hd * 2 * 2
     return {"kernel": "attention_decode", "kind": args.kind, "fused": bool(args.fused), "batch": B, "context": ctx, "splits": splits, "us": round(us, 2),
             "GB/s": round(nbytes / us / 1e3, 1)}
 
@@ -162,7 +174,9 @@ def main(argv=None):
         p.add_argument("--kernel", default="skinny")
         p.add_argument("--tile", type=int, default=256)
         p.add_argument("--k-parts", type=int, default=1, help="gemm --accumulate: parts a tile's K range is cut into")
-        p.add_argument("--kind", type=int, default=0, help="attention_decode: 0 auto, 1 general, 2 tensor-core")
+        p.add_argument("--kind", type=int, default=2, help="attention_decode: 1 CUDA cores, 2 tensor cores (persistent grid)")
+        p.add_argument("--chunk-pages", type=int, default=0, help="attention_decode --kind 2: pages per chunk (default: pages / --splits)")
+        p.add_argument("--ragged", action="store_true", help="attention_decode: lengths uniform in [1, --context]")
         p.add_argument("--accumulate", action="store_true", help="linear gv*, gemm: add into a float32 output")
         p.add_argument("--pdl", action="store_true", help="launch as programmatic dependents")
         p.add_argument("--fused", action="store_true", help="attention_decode: rotate and append inside")

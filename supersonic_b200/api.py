@@ -54,14 +54,17 @@ class Engine:
 def load(model_dir: Optional[str] = None, dtype: str = "bfloat16", device: int = 0,
          context_size: Optional[int] = None, batch_size: int = 1, max_tokens: Optional[int] = None,
          step_token_budget: Optional[int] = None, preset: Optional[str] = None, random_seed: int = 0,
-         allow_unexpected_tensors: bool = False, use_graphs: bool = True) -> Engine:
+         allow_unexpected_tensors: bool = False, use_graphs: bool = True,
+         deterministic: bool = False) -> Engine:
     """Load ``model_dir`` (config.json + safetensors), or build the named ``preset`` with random
     weights made on the device from ``random_seed`` (no folder is read or written).  The cache holds
     ``max_tokens`` tokens in all, by default ``batch_size`` sequences of ``context_size`` tokens
     (prompt plus generated; default: the model's position limit, capped at 8192).  A step of more
     than ``step_token_budget`` tokens (default 32,768) runs in chunks of that many: it bounds the
     memory a batch of long prompts needs beside the cache.  Weights, cache and workspace are checked
-    against the device's free memory before anything is loaded."""
+    against the device's free memory before anything is loaded.  ``deterministic``: the bfloat16
+    path without float atomics, so that the same batch gives the same bits every run and sampled
+    tokens are reproducible from their seed (the float32 path always is)."""
     from .cache import PAGE_TOKENS
     from .config import load_config, preset_config
     if (model_dir is None) == (preset is None):
@@ -70,7 +73,7 @@ def load(model_dir: Optional[str] = None, dtype: str = "bfloat16", device: int =
     ctx = context_size or min(getattr(cfg, "max_position_embeddings", 8192), 8192)
     ctx = -(-ctx // PAGE_TOKENS) * PAGE_TOKENS
     total = max_tokens or ctx * max(batch_size, 1)
-    extra = {"use_graphs": use_graphs}
+    extra = {"use_graphs": use_graphs, "deterministic": deterministic}
     if step_token_budget is not None:
         extra["step_token_budget"] = step_token_budget
     dev = f"cuda:{device}"

@@ -102,8 +102,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
                         __nv_bfloat16* __restrict__ out, int ldo, int n_q, int n_kv, int head_dim, int page_shift,
                         int window, float scale, int n_splits, float* __restrict__ scratch,
                         int* __restrict__ counters, const float* __restrict__ cos_t,
-                        const float* __restrict__ sin_t, const char* __restrict__ prefetch_ptr,
-                        long long prefetch_bytes) {
+                        const float* __restrict__ sin_t) {
     __shared__ float sm_m[NW][AD_GROUP], sm_l[NW][AD_GROUP];
     __shared__ float sm_acc[NW][AD_GROUP][32 * VEC];
     __shared__ int is_last;
@@ -179,20 +178,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloa
         }
     }
     if (FUSE) ssb_pdl_wait();                                    // the query (and this token's k, v) come from the predecessor
-    // This kernel moves little data and waits on latencies: meanwhile it asks L2 to fetch a slice
-    // of the weights that the kernels after it will stream (after the wait: so as not to compete with the projection before it).
-    if (prefetch_bytes > 0) {                                    // pieces of 32 KB, spread over the threads
-        const long long n_blocks = (long long)gridDim.x * gridDim.y * gridDim.z;
-        const long long me = ((long long)blockIdx.x * gridDim.y + blockIdx.y) * gridDim.z + blockIdx.z;
-        // one SM can only feed so many of these requests: at most 512 KB a block
-        const long long slice = min(((prefetch_bytes + n_blocks - 1) / n_blocks + 15) & ~15LL, 524288LL);
-        const long long lo_b = me * slice, hi_b = min(lo_b + slice, prefetch_bytes & ~15LL);
-        for (long long o = lo_b + (long long)threadIdx.x * 32768; o < hi_b; o += (long long)blockDim.x * 32768) {
-            const unsigned n = (unsigned)min(32768LL, hi_b - o);
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(prefetch_ptr + o), "r"(n) : "memory");
-        }
-    }
-
     float qv[AD_GROUP][VEC];
 #pragma unroll
     for (int gi = 0; gi < AD_GROUP; ++gi) {
@@ -413,8 +398,7 @@ static inline int ad_launch(const void* q, int ldq, const void* k_cache, const v
                             const int* slot, const int* page_table, int max_pages, void* out, int ldo,
                             int n_seqs, int n_q, int n_kv, int head_dim, int page_shift, int window,
                             float scale, int n_splits, float* scratch, int* counters, cudaStream_t stream,
-                            bool pdl = false, const float* cos_t = nullptr, const float* sin_t = nullptr,
-                            const void* prefetch_ptr = nullptr, long long prefetch_bytes = 0) {
+                            bool pdl = false, const float* cos_t = nullptr, const float* sin_t = nullptr) {
     typedef __nv_bfloat16 bf16;
     if (n_seqs <= 0) return 0;
     if (head_dim <= 0 || head_dim > 32 * AD_MAX_VEC || n_kv <= 0 || n_q % n_kv || n_splits < 1 ||
@@ -429,8 +413,7 @@ static inline int ad_launch(const void* q, int ldq, const void* k_cache, const v
     const int vec = (head_dim + 31) / 32;
     int rc = 0;
 #define SSB_AD_ARGS (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
-        (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters, cos_t, sin_t, \
-        (const char*)prefetch_ptr, (((uintptr_t)prefetch_ptr & 15) ? 0LL : prefetch_bytes)
+        (bf16*)out, ldo, n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters, cos_t, sin_t
     // few blocks (small batches): 8 warps each, so that a page of keys is one turn of the block
     const bool wide = (long long)grid.x * grid.y * grid.z <= 600;
 #define SSB_AD_W(V, FUSE_, FULL_) \

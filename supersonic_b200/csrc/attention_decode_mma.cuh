@@ -2,13 +2,23 @@
 // kv head: the query heads that share a kv head are the rows of one m16n8k16 tile, so a page of
 // 64 keys costs a block 16 + 16 MMAs per warp instead of thousands of scalar instructions.
 //
-// Grid (sequence, kv head, split).  The block's 4 warps fetch a page of keys and values into
-// shared memory together (cp.async, two stages, the swizzled tile layout of the prefill kernel);
-// each warp then takes 16 of the page's 64 keys: S = Q K^T (16 x 16), online softmax in float32,
-// O += P V.  Warps merge in shared memory, splits through scratch and the last block to arrive,
-// exactly as in attention_decode.cuh (same scratch layout, maxima kept in the log2 domain).
+// Work items and a persistent grid.  A sequence's pages are cut into chunks of about
+// ``chunk_pages`` pages (as many chunks as that needs, of even size: the cut depends on the
+// sequence alone, never on what else is in the batch); an item is (sequence, chunk, kv head).
+// About two blocks per SM are launched and block j takes items j, j + grid, j + 2 grid, ...:
+// every block first counts the chunks of all sequences (a prefix sum over the batch in shared
+// memory), so no host-made work list is needed and a captured graph serves any lengths.  A batch
+// of very unequal lengths then keeps every SM busy to the end, which a grid of (sequence, head,
+// split) with one split count for all does not.
+//
+// Per item the block's 4 warps fetch a page of keys and values into shared memory together
+// (cp.async, two stages, the swizzled tile layout of the prefill kernel); each warp takes 16 of
+// the page's 64 keys: S = Q K^T (16 x 16), online softmax in float32, O += P V.  Warps merge in
+// shared memory; a sequence of several chunks leaves partial results in scratch and the item that
+// arrives last for its (sequence, kv head) merges them in chunk order (same scratch layout as
+// attention_decode.cuh, maxima kept in the log2 domain).  Nothing waits on another block.
 // With FUSE the rows of q are the raw fused projection [q | k | v]: queries are rotated while
-// the fragments are built, and the block that owns the token's page rotates its key, appends key
+// the fragments are built, and the item that owns the token's page rotates its key, appends key
 // and value to the cache and attends to them from registers.
 //
 // Replaces supersonic_qwen35_full_attention_decode_*_kernel of the reference (one warp per query
@@ -20,72 +30,120 @@
 constexpr int ADM_WARPS = 4;
 constexpr int ADM_THREADS = ADM_WARPS * 32;
 constexpr int ADM_ROWS = 16;          // query heads per kv head, padded to the MMA's 16 rows
-// Shared memory asked for beyond the four 16 KB tiles of head size 128: 80 KB a block lets two blocks
-// share an SM, not three.  Measured inside decode steps of Llama-3.1-8B sizes: 3.44 ms a step at
-// batch 8 with 76 to 113 KB a block, 3.50 ms with 64 to 72 KB, 3.61 ms with 128 KB (batch 64: 13.6k,
-// 13.1k and 12.1k tokens/s).
-constexpr int ADM_PAD_BYTES = 16384;
-
+constexpr int ADM_MAX_SEQS = 1024;    // sequences a launch can take (their slots, positions and chunk counts sit in shared memory)
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// One work item, decoded from its index (everything block-uniform).
+struct AdmItem {
+    int b, kvh, chunk, n_chunks, slot, p, key_lo, key_hi, page_hi, pf, units, page0, page1;
+    bool owns_new;
+};
+
+template <int N> __device__ __forceinline__ void adm_wait_pending_at_most() { cp_async_wait<N>(); }
+// Wait until at most ``n`` of the newest cp.async groups are pending (a smaller bound is always right).
+__device__ __forceinline__ void adm_wait_pending(int n) {
+    if (n <= 0) cp_async_wait<0>();
+    else if (n == 1) cp_async_wait<1>();
+    else if (n == 2) cp_async_wait<2>();
+    else cp_async_wait<3>();
+}
 
 template <int HD, bool FUSE>
 __global__ void __launch_bounds__(ADM_THREADS)
 attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* k_cache,
                             __nv_bfloat16* v_cache, const int* __restrict__ pos, const int* __restrict__ slot,
                             const int* __restrict__ page_table, int max_pages, __nv_bfloat16* __restrict__ out,
-                            int ldo, int n_q, int n_kv, int window, float scale_log2, int n_splits,
-                            float* __restrict__ scratch, int* __restrict__ counters,
-                            const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                            const char* __restrict__ prefetch_ptr, long long prefetch_bytes) {
+                            int ldo, int n_seqs, int n_q, int n_kv, int window, float scale_log2, int chunk_pages,
+                            int max_chunks, float* __restrict__ scratch, int* __restrict__ counters,
+                            const float* __restrict__ cos_t, const float* __restrict__ sin_t) {
     constexpr int CHUNKS = HD / 8, TILE_BYTES = 64 * HD * 2, KS = HD / 16, HALF = HD / 2;
-    extern __shared__ __align__(128) unsigned char adm_smem[];   // K stage 0, K stage 1, V stage 0, V stage 1
-    unsigned char* smem = adm_smem;
+    const int group = n_q / n_kv;
+    // a query buffer: the item's query rows, the rotation tables' row, the token's own key and value
+    const int Q_OFF = 0, COS_OFF = group * HD * 2, SIN_OFF = COS_OFF + HALF * 4, KN_OFF = SIN_OFF + HALF * 4,
+              VN_OFF = KN_OFF + HD * 2, QBUF_BYTES = VN_OFF + HD * 2;
+    // dynamic shared memory (adm_smem_bytes): tiles, warp sums, two query buffers, the batch's integers
+    extern __shared__ __align__(128) unsigned char adm_smem[];
+    unsigned char* smem = adm_smem;                              // K stage 0, K stage 1, V stage 0, V stage 1
+    constexpr int ACC_LD = HD + 4;       // row pitch of the warp sums: rows g and g + 1 land four banks apart
+    float* sm_acc = reinterpret_cast<float*>(smem + 4 * TILE_BYTES);          // [ADM_WARPS][group][ACC_LD]
+    unsigned char* qbufs = smem + 4 * TILE_BYTES + ADM_WARPS * group * ACC_LD * 4;
+    int* cum = reinterpret_cast<int*>(qbufs + 2 * QBUF_BYTES);   // [n_seqs + 1] chunks of the sequences before each one
+    int* sm_slot = cum + n_seqs + 1;                             // [n_seqs] the batch's slots and positions, read once
+    int* sm_pos = sm_slot + n_seqs;
     __shared__ float sm_m[ADM_WARPS][ADM_ROWS], sm_l[ADM_WARPS][ADM_ROWS];
     __shared__ int is_last;
-    const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
-    const int group = n_q / n_kv, h0 = kvh * group;
+    __shared__ int warp_total[ADM_WARPS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 
     ssb_pdl_launch_dependents();
-    if (split >= n_splits) {
-        // Extra blocks of the grid that only ask L2 to fetch a slice of the weights the next
-        // kernels will stream.  They wait for the predecessor first: the point is to use the
-        // memory system while attention waits on its small loads, not to compete with the
-        // projection before it.  One SM can only feed so many of these requests, so they are
-        // spread over many blocks.
-        ssb_pdl_wait();
-        const long long n_pre = (long long)gridDim.x * gridDim.y * (gridDim.z - n_splits);
-        const long long me = ((long long)blockIdx.x * gridDim.y + blockIdx.y) * (gridDim.z - n_splits) + (split - n_splits);
-        const long long slice = ((prefetch_bytes + n_pre - 1) / n_pre + 15) & ~15LL;
-        const long long lo_b = me * slice, hi_b = min(lo_b + slice, prefetch_bytes & ~15LL);
-        for (long long o = lo_b + (long long)threadIdx.x * 32768; o < hi_b; o += (long long)blockDim.x * 32768) {
-            const unsigned n = (unsigned)min(32768LL, hi_b - o);
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(prefetch_ptr + o), "r"(n) : "memory");
+    // Positions, slots and page tables were written before this chain of kernels began: they may be
+    // read before the dependency wait, and so may pages of earlier steps' keys.
+    for (int b = threadIdx.x; b < n_seqs; b += ADM_THREADS) { sm_slot[b] = slot[b]; sm_pos[b] = pos[b]; }
+    __syncthreads();
+    auto chunks_of = [&](int b) {
+        if (sm_slot[b] < 0) return 0;                            // a padding row is no work item (zeros below)
+        const int p = sm_pos[b];
+        const int key_lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+        return min(((p >> 6) - (key_lo >> 6) + chunk_pages) / chunk_pages, max_chunks);   // ceil(pages / chunk_pages)
+    };
+    {
+        const int per = (n_seqs + ADM_THREADS - 1) / ADM_THREADS;
+        const int b0 = (int)threadIdx.x * per;
+        int local = 0;
+        for (int i = 0; i < per; ++i)
+            if (b0 + i < n_seqs) local += chunks_of(b0 + i);
+        int incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
         }
-        return;
+        if (lane == 31) warp_total[warp] = incl;
+        __syncthreads();
+        int base = 0;
+        for (int w = 0; w < warp; ++w) base += warp_total[w];
+        int running = base + incl - local;
+        for (int i = 0; i < per; ++i)
+            if (b0 + i < n_seqs) { cum[b0 + i] = running; running += chunks_of(b0 + i); }
+        if (threadIdx.x == ADM_THREADS - 1) cum[n_seqs] = base + incl;
+        __syncthreads();
     }
-    if (!FUSE) ssb_pdl_wait();                                   // the cache holds this step's key already
-    const int s = slot[b];
-    if (s < 0) {                                                 // padding row
-        if (FUSE) ssb_pdl_wait();
-        if (split == 0)
-            for (int e = threadIdx.x; e < group * HD; e += ADM_THREADS)
-                out[(size_t)b * ldo + (size_t)h0 * HD + e] = __float2bfloat16_rn(0.f);
-        return;
-    }
-    const int p = pos[b];
-    const int key_lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-    const int key_hi = FUSE ? p - 1 : p;                         // with FUSE the token's own key is not cached yet
-    const int page_lo = key_lo >> 6, page_hi = p >> 6;
-    const int per = (page_hi - page_lo + n_splits) / n_splits;   // ceil(pages / splits)
-    const int pf = page_lo + split * per, pl = min(page_hi, pf + per - 1);
-    const int n_my = pl - pf + 1;                                // pages of this split (<= 0: none)
-    const bool owns_new = FUSE && pf <= page_hi && page_hi <= pl;
-    const int* pt = page_table + (size_t)s * max_pages;
+    const int total_items = cum[n_seqs] * n_kv;
 
-    auto load_page = [&](int i, int stage) {
-        const size_t base = ((size_t)pt[pf + i] * n_kv + kvh) * (size_t)(64 * HD);
+    // An item is decoded two items ahead of its turn: the ids of its first two pages are asked for here
+    // and are in registers long before its pages are issued.
+    auto decode = [&](int idx, AdmItem& I) {
+        const int gc = idx / n_kv;
+        I.kvh = idx - gc * n_kv;
+        int lo = 0, hi = n_seqs - 1;                             // the last sequence whose first chunk is <= gc
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (cum[mid] <= gc) lo = mid; else hi = mid - 1;
+        }
+        I.b = lo;
+        I.chunk = gc - cum[lo];
+        I.n_chunks = cum[lo + 1] - cum[lo];
+        I.slot = sm_slot[lo];
+        I.p = sm_pos[lo];
+        I.key_lo = (window > 0 && I.p - window + 1 > 0) ? I.p - window + 1 : 0;
+        I.key_hi = FUSE ? I.p - 1 : I.p;                         // with FUSE the token's own key is not cached yet
+        const int page_lo = I.key_lo >> 6;
+        I.page_hi = I.p >> 6;
+        const int per = (I.page_hi - page_lo + I.n_chunks) / I.n_chunks;     // even chunks: ceil(pages / chunks)
+        I.pf = page_lo + I.chunk * per;
+        const int pl = min(I.page_hi, I.pf + per - 1);
+        I.units = max(pl - I.pf + 1, 1);                         // an empty chunk still loads a page (all its keys masked)
+        I.owns_new = FUSE && I.pf <= I.page_hi && I.page_hi <= pl;
+        const int* pt = page_table + (size_t)I.slot * max_pages;
+        I.page0 = pt[min(I.pf, I.page_hi)];
+        I.page1 = pt[min(I.pf + 1, I.page_hi)];
+    };
+    int page_ahead = 0, page_ahead_of = -1;      // id of the page two after the one in work, asked for one turn early
+    auto load_page = [&](const AdmItem& I, int i, int stage) {
+        const int page = i == 0 ? I.page0 : (i == 1 ? I.page1 : (i == page_ahead_of ? page_ahead
+                         : page_table[(size_t)I.slot * max_pages + min(I.pf + i, I.page_hi)]));
+        const size_t base = ((size_t)page * n_kv + I.kvh) * (size_t)(64 * HD);
         const uint32_t kd = (uint32_t)__cvta_generic_to_shared(smem + stage * TILE_BYTES);
         const uint32_t vd = (uint32_t)__cvta_generic_to_shared(smem + (2 + stage) * TILE_BYTES);
         for (int e = threadIdx.x; e < 64 * CHUNKS; e += ADM_THREADS) {
@@ -93,267 +151,387 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
             cp_async16(kd + tile_offset<HD>(r, c), k_cache + base + (size_t)r * HD + c * 8);
             cp_async16(vd + tile_offset<HD>(r, c), v_cache + base + (size_t)r * HD + c * 8);
         }
-        cp_async_commit();
     };
-    // earlier steps' keys: safe before the wait.  Both stages are filled here (a cp.async group each,
-    // empty if there is no such page), so that two pages are on their way while the projection
-    // before this kernel still runs.
-    if (n_my > 0) load_page(0, 0); else cp_async_commit();
-    if (n_my > 1) load_page(1, 1); else cp_async_commit();
-    if (FUSE) ssb_pdl_wait();                                    // the query comes from the predecessor
-
-    // Query fragments: row = head (g and g + 8), this lane's columns 16 ks + 2t (+1, +8, +9).
-    // Rotation pairs (d, d + HD/2) are both in this lane (k-steps ks and ks + KS/2).
-    uint32_t qf[KS][4];
-    {
-        float qa[2][KS][4];                                      // [row half][k-step][element]
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int row = g + 8 * i;
-            const __nv_bfloat16* qr = q + (size_t)b * ldq + (size_t)(h0 + row) * HD;
-#pragma unroll
-            for (int ks = 0; ks < KS; ++ks) {
-                uint32_t w0 = 0u, w1 = 0u;
-                if (row < group) {
-                    w0 = *reinterpret_cast<const uint32_t*>(qr + 16 * ks + 2 * t);
-                    w1 = *reinterpret_cast<const uint32_t*>(qr + 16 * ks + 2 * t + 8);
-                }
-                qa[i][ks][0] = bf16lo(w0); qa[i][ks][1] = bf16hi(w0);
-                qa[i][ks][2] = bf16lo(w1); qa[i][ks][3] = bf16hi(w1);
+    auto load_query = [&](const AdmItem& I, int which) {
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(qbufs + which * QBUF_BYTES);
+        const __nv_bfloat16* row = q + (size_t)I.b * ldq;
+        for (int e = threadIdx.x; e < group * CHUNKS; e += ADM_THREADS)
+            cp_async16(dst + Q_OFF + e * 16, row + (size_t)I.kvh * group * HD + e * 8);
+        if (FUSE) {
+            const int e = threadIdx.x;                           // 128 threads: HALF / 4 chunks per table row, CHUNKS per vector
+            if (e < HALF / 4) {
+                cp_async16(dst + COS_OFF + e * 16, cos_t + (size_t)I.p * HALF + e * 4);
+                cp_async16(dst + SIN_OFF + e * 16, sin_t + (size_t)I.p * HALF + e * 4);
+            }
+            if (e < CHUNKS) {
+                cp_async16(dst + KN_OFF + e * 16, row + (size_t)(n_q + I.kvh) * HD + e * 8);
+                cp_async16(dst + VN_OFF + e * 16, row + (size_t)(n_q + n_kv + I.kvh) * HD + e * 8);
             }
         }
-        if (FUSE) {
+    };
+
+    // rows without a sequence (a captured step's warm-up): zeros, shared out over the blocks
+    bool waited = !FUSE;
+    if (!FUSE) ssb_pdl_wait();                                   // the cache holds this step's key already
+    for (int b = blockIdx.x; b < n_seqs; b += gridDim.x)
+        if (sm_slot[b] < 0) {
+            if (!waited) { ssb_pdl_wait(); waited = true; }
+            for (int e = threadIdx.x; e < n_q * HD; e += ADM_THREADS)
+                out[(size_t)b * ldo + e] = __float2bfloat16_rn(0.f);
+        }
+    if ((int)blockIdx.x >= total_items) {
+        if (!waited) ssb_pdl_wait();                             // a block without items still ends after its predecessor
+        return;
+    }
+
+    // The stream of cp.async groups: for every item of this block its query buffer, then its pages
+    // one by one.  Groups are numbered as they are issued; a page goes to stage (page unit & 1), a
+    // query to buffer (item & 1); up to two page units are in flight, across item borders, so the
+    // fixed cost of an item (its slot, position, page ids, query rows) hides behind the item before it.
+    // A chunk's arrival at its (sequence, kv head) counter is counted when the chunk's sums are
+    // written, but the answer (was it the last?) is looked at only when the next item's sums are
+    // written, so that the atomic's round trip hides behind that item's work.
+    int pend_b = -1, pend_kvh = 0, pend_chunks = 0;              // the counted chunk whose answer is still out
+    int pend_arrived = 0;                                        // thread 0: what its atomic returned
+    auto settle = [&]() {                                        // block-uniform; ends with the merge if it was the last
+        if (pend_b < 0) return;
+        if (threadIdx.x == 0) {
+            is_last = (pend_arrived == pend_chunks - 1);
+            if (is_last) counters[(size_t)pend_b * n_kv + pend_kvh] = 0;
+        }
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            const int ph0 = pend_kvh * group;
+            // every thread owns elements (head, dim) of the output and goes through the chunks itself,
+            // in chunk order, eight at a time so that their loads are in flight together
+            for (int e = threadIdx.x; e < group * HD; e += ADM_THREADS) {
+                const int row = e / HD, d = e % HD;
+                const float* base = scratch + ((size_t)pend_b * n_q + ph0 + row) * max_chunks * (HD + 2);
+                float mm = -INFINITY, ll = 0.f, a = 0.f;
+                for (int s0 = 0; s0 < pend_chunks; s0 += 8) {
+                    float pm[8], pl[8], pv[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const bool live = s0 + i < pend_chunks;
+                        const float* part = base + (size_t)(live ? s0 + i : s0) * (HD + 2);
+                        pm[i] = live ? __ldcg(part + HD) : -INFINITY;
+                        pl[i] = __ldcg(part + HD + 1);
+                        pv[i] = __ldcg(part + d);
+                    }
+                    float m_new = mm;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) m_new = fmaxf(m_new, pm[i]);
+                    const float keep = (mm == -INFINITY) ? 0.f : exp2f(mm - m_new);
+                    ll *= keep; a *= keep;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float f = (pm[i] == -INFINITY) ? 0.f : exp2f(pm[i] - m_new);
+                        ll = fmaf(pl[i], f, ll);
+                        a = fmaf(pv[i], f, a);
+                    }
+                    mm = m_new;
+                }
+                out[(size_t)pend_b * ldo + (size_t)(ph0 + row) * HD + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+            }
+        }
+        __syncthreads();                                         // is_last is free again
+        pend_b = -1;
+    };
+
+    AdmItem cur, nxt, nn;                // the item in work, the one after it, and the one after that
+    int item = blockIdx.x;
+    const int G = (int)gridDim.x;
+    decode(item, cur);
+    bool has_nxt = item + G < total_items, has_nn = item + 2 * G < total_items;
+    if (has_nxt) decode(item + G, nxt);
+    if (has_nn) decode(item + 2 * G, nn);
+    int n_groups = 0;                    // groups issued so far
+    int pu_issued = 0, pu_done = 0;      // page units issued / consumed
+    int cursor_item = 0, cursor_pos = 0; // next group to issue: item 0 = cur, 1 = nxt; position -1 = query, else page
+    int grp_of_stage[2] = {0, 0}, grp_of_query[2] = {0, 0};
+    int parity = 0;                      // of cur among this block's items
+
+    auto issue_group = [&]() -> bool {
+        if (cursor_item > 1 || (cursor_item == 1 && !has_nxt)) return false;
+        const AdmItem& I = cursor_item == 0 ? cur : nxt;
+        if (cursor_pos < 0) {
+            const int which = parity ^ cursor_item;
+            load_query(I, which);
+            grp_of_query[which] = n_groups;
+            cursor_pos = 0;
+        } else {
+            load_page(I, cursor_pos, pu_issued & 1);
+            grp_of_stage[pu_issued & 1] = n_groups;
+            ++pu_issued;
+            if (++cursor_pos == I.units) { ++cursor_item; cursor_pos = -1; }
+        }
+        cp_async_commit();
+        ++n_groups;
+        return true;
+    };
+    auto fill = [&]() { while (pu_issued < pu_done + 2 && issue_group()) {} };
+
+    // the first item: its pages may be asked for before the dependency wait; its query, and anything
+    // of the item after it, only after
+    while (pu_issued < 2 && cursor_item == 0) issue_group();
+    if (!waited) { ssb_pdl_wait(); waited = true; }
+    load_query(cur, 0);
+    grp_of_query[0] = n_groups;
+    cp_async_commit();
+    ++n_groups;
+    fill();
+
+    while (true) {
+        const int b = cur.b, kvh = cur.kvh, h0 = kvh * group, p = cur.p;
+        const int key_lo = cur.key_lo, key_hi = cur.key_hi;
+        const unsigned char* qb = qbufs + parity * QBUF_BYTES;
+        adm_wait_pending(n_groups - 1 - grp_of_query[parity]);
+        __syncthreads();
+
+        // Query fragments: row = head (g and g + 8), this lane's columns 16 ks + 2t (+1, +8, +9).
+        // Rotation pairs (d, d + HD/2) are both in this lane (k-steps ks and ks + KS/2).
+        uint32_t qf[KS][4];
+        {
+            float qa[2][KS][4];                                  // [row half][k-step][element]
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int row = g + 8 * i;
+                const unsigned char* qr = qb + Q_OFF + row * HD * 2;
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    uint32_t w0 = 0u, w1 = 0u;
+                    if (row < group) {
+                        w0 = *reinterpret_cast<const uint32_t*>(qr + (16 * ks + 2 * t) * 2);
+                        w1 = *reinterpret_cast<const uint32_t*>(qr + (16 * ks + 2 * t + 8) * 2);
+                    }
+                    qa[i][ks][0] = bf16lo(w0); qa[i][ks][1] = bf16hi(w0);
+                    qa[i][ks][2] = bf16lo(w1); qa[i][ks][3] = bf16hi(w1);
+                }
+            }
+            if (FUSE) {
+                const float* cs = reinterpret_cast<const float*>(qb + COS_OFF);
+                const float* sn_ = reinterpret_cast<const float*>(qb + SIN_OFF);
+#pragma unroll
+                for (int ks = 0; ks < KS / 2; ++ks)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int idx = 16 * ks + 2 * t + (e & 1) + (e >> 1) * 8;      // < HD/2
+                        const float c = cs[idx], sn = sn_[idx];
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            const float x1 = qa[i][ks][e], x2 = qa[i][ks + KS / 2][e];
+                            qa[i][ks][e] = x1 * c - x2 * sn;
+                            qa[i][ks + KS / 2][e] = x1 * sn + x2 * c;
+                        }
+                    }
+            }
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                qf[ks][0] = pack2(qa[0][ks][0] * scale_log2, qa[0][ks][1] * scale_log2);
+                qf[ks][1] = pack2(qa[1][ks][0] * scale_log2, qa[1][ks][1] * scale_log2);
+                qf[ks][2] = pack2(qa[0][ks][2] * scale_log2, qa[0][ks][3] * scale_log2);
+                qf[ks][3] = pack2(qa[1][ks][2] * scale_log2, qa[1][ks][3] * scale_log2);
+            }
+        }
+        float o[HD / 8][4];
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // l: this lane's share of the row sum
+
+        for (int i = 0; i < cur.units; ++i) {
+            if (i + 2 < cur.units) {     // needed when this turn ends: a turn's arithmetic hides the load
+                page_ahead = page_table[(size_t)cur.slot * max_pages + min(cur.pf + i + 2, cur.page_hi)];
+                page_ahead_of = i + 2;
+            }
+            const int stage = pu_done & 1;
+            adm_wait_pending(n_groups - 1 - grp_of_stage[stage]);
+            __syncthreads();
+            const uint32_t kbase = (uint32_t)__cvta_generic_to_shared(smem + stage * TILE_BYTES);
+            const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(smem + (2 + stage) * TILE_BYTES);
+            const int key0 = ((cur.pf + i) << 6) + 16 * warp;    // this warp's 16 keys of the page
+            if (key0 <= key_hi && key0 + 15 >= key_lo) {
+                float sc[2][4];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    uint32_t b0, b1, b2, b3;
+                    const int key = 16 * warp + ((lane >> 4) << 3) + (lane & 7);
+                    ldmatrix_x4(kbase + tile_offset<HD>(key, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
+                    mma16816(sc[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+                    mma16816(sc[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+                }
+                float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + j * 8 + 2 * t + (e & 1);
+                        const float v = (key >= key_lo && key <= key_hi) ? sc[j][e] : -INFINITY;
+                        sc[j][e] = v;
+                        m_new[e >> 1] = fmaxf(m_new[e >> 1], v);
+                    }
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 1));
+                    m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 2));
+                }
+                float alpha[2], row_sum[2] = {0.f, 0.f};
+#pragma unroll
+                for (int r = 0; r < 2; ++r) alpha[r] = (m_new[r] == -INFINITY) ? 1.f : exp2f(m_run[r] - m_new[r]);
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int r = e >> 1;
+                        const float pj = (m_new[r] == -INFINITY) ? 0.f : exp2f(sc[j][e] - m_new[r]);
+                        sc[j][e] = pj;
+                        row_sum[r] += pj;
+                    }
+#pragma unroll
+                for (int r = 0; r < 2; ++r) { l_run[r] = l_run[r] * alpha[r] + row_sum[r]; m_run[r] = m_new[r]; }
+#pragma unroll
+                for (int j = 0; j < HD / 8; ++j) { o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1]; }
+                const uint32_t a0 = pack2(sc[0][0], sc[0][1]), a1 = pack2(sc[0][2], sc[0][3]);
+                const uint32_t a2 = pack2(sc[1][0], sc[1][1]), a3 = pack2(sc[1][2], sc[1][3]);
+#pragma unroll
+                for (int jp = 0; jp < HD / 16; ++jp) {
+                    uint32_t b0, b1, b2, b3;
+                    const int key = 16 * warp + (((lane >> 3) & 1) << 3) + (lane & 7);
+                    ldmatrix_x4_trans(vbase + tile_offset<HD>(key, jp * 2 + (lane >> 4)), b0, b1, b2, b3);
+                    mma16816(o[2 * jp], a0, a1, a2, a3, b0, b1);
+                    mma16816(o[2 * jp + 1], a0, a1, a2, a3, b2, b3);
+                }
+            }
+            __syncthreads();                                     // the stage may be refilled
+            ++pu_done;
+            fill();                                              // this item's next pages, or the next item's query and pages
+        }
+
+        if (FUSE && cur.owns_new && warp == 0) {
+            // the token's own key and value, from the projection's output; all of this is lane-local
+            const unsigned char* k_src = qb + KN_OFF;
+            const unsigned char* v_src = qb + VN_OFF;
+            const float* cs = reinterpret_cast<const float*>(qb + COS_OFF);
+            const float* sn_ = reinterpret_cast<const float*>(qb + SIN_OFF);
+            float kn[KS][4];
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                const uint32_t w0 = *reinterpret_cast<const uint32_t*>(k_src + (16 * ks + 2 * t) * 2);
+                const uint32_t w1 = *reinterpret_cast<const uint32_t*>(k_src + (16 * ks + 2 * t + 8) * 2);
+                kn[ks][0] = bf16lo(w0); kn[ks][1] = bf16hi(w0); kn[ks][2] = bf16lo(w1); kn[ks][3] = bf16hi(w1);
+            }
 #pragma unroll
             for (int ks = 0; ks < KS / 2; ++ks)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int idx = 16 * ks + 2 * t + (e & 1) + (e >> 1) * 8;          // < HD/2
-                    const float c = cos_t[(size_t)p * HALF + idx], sn = sin_t[(size_t)p * HALF + idx];
-#pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        const float x1 = qa[i][ks][e], x2 = qa[i][ks + KS / 2][e];
-                        qa[i][ks][e] = x1 * c - x2 * sn;
-                        qa[i][ks + KS / 2][e] = x1 * sn + x2 * c;
-                    }
+                    const int idx = 16 * ks + 2 * t + (e & 1) + (e >> 1) * 8;
+                    const float c = cs[idx], sn = sn_[idx];
+                    const float x1 = kn[ks][e], x2 = kn[ks + KS / 2][e];
+                    kn[ks][e] = __bfloat162float(__float2bfloat16_rn(x1 * c - x2 * sn));          // as the cache holds it
+                    kn[ks + KS / 2][e] = __bfloat162float(__float2bfloat16_rn(x1 * sn + x2 * c));
                 }
-        }
+            const int page = page_table[(size_t)cur.slot * max_pages + (p >> 6)];
+            const size_t row = ((((size_t)page * n_kv + kvh) << 6) + (p & 63)) * HD;
+            if (g == 0) {
 #pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            qf[ks][0] = pack2(qa[0][ks][0] * scale_log2, qa[0][ks][1] * scale_log2);
-            qf[ks][1] = pack2(qa[1][ks][0] * scale_log2, qa[1][ks][1] * scale_log2);
-            qf[ks][2] = pack2(qa[0][ks][2] * scale_log2, qa[0][ks][3] * scale_log2);
-            qf[ks][3] = pack2(qa[1][ks][2] * scale_log2, qa[1][ks][3] * scale_log2);
-        }
-    }
-    float o[HD / 8][4];
-#pragma unroll
-    for (int j = 0; j < HD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // l: this lane's share of the row sum
-
-    for (int i = 0; i < n_my; ++i) {
-        const int stage = i & 1;
-        cp_async_wait<1>();                                      // all but the newest group: page i is in
-        __syncthreads();
-        const uint32_t kbase = (uint32_t)__cvta_generic_to_shared(smem + stage * TILE_BYTES);
-        const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(smem + (2 + stage) * TILE_BYTES);
-        const int key0 = ((pf + i) << 6) + 16 * warp;            // this warp's 16 keys of the page
-        if (key0 <= key_hi && key0 + 15 >= key_lo) {
-            float sc[2][4];
-#pragma unroll
-            for (int j = 0; j < 2; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
+                for (int ks = 0; ks < KS; ++ks) {
+                    *reinterpret_cast<uint32_t*>(k_cache + row + 16 * ks + 2 * t) = pack2(kn[ks][0], kn[ks][1]);
+                    *reinterpret_cast<uint32_t*>(k_cache + row + 16 * ks + 2 * t + 8) = pack2(kn[ks][2], kn[ks][3]);
+                }
+            }
+            float sn2[2] = {0.f, 0.f};                           // scores of rows g and g + 8 (log2 domain)
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
-                uint32_t b0, b1, b2, b3;
-                const int key = 16 * warp + ((lane >> 4) << 3) + (lane & 7);
-                ldmatrix_x4(kbase + tile_offset<HD>(key, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
-                mma16816(sc[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
-                mma16816(sc[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+                sn2[0] += bf16lo(qf[ks][0]) * kn[ks][0] + bf16hi(qf[ks][0]) * kn[ks][1]
+                        + bf16lo(qf[ks][2]) * kn[ks][2] + bf16hi(qf[ks][2]) * kn[ks][3];
+                sn2[1] += bf16lo(qf[ks][1]) * kn[ks][0] + bf16hi(qf[ks][1]) * kn[ks][1]
+                        + bf16lo(qf[ks][3]) * kn[ks][2] + bf16hi(qf[ks][3]) * kn[ks][3];
             }
-            float m_new[2] = {m_run[0], m_run[1]};
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = key0 + j * 8 + 2 * t + (e & 1);
-                    const float v = (key >= key_lo && key <= key_hi) ? sc[j][e] : -INFINITY;
-                    sc[j][e] = v;
-                    m_new[e >> 1] = fmaxf(m_new[e >> 1], v);
-                }
+            float pn[2], al[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 1));
-                m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 2));
+                sn2[r] += __shfl_xor_sync(0xffffffffu, sn2[r], 1);
+                sn2[r] += __shfl_xor_sync(0xffffffffu, sn2[r], 2);
+                const float m_new = fmaxf(m_run[r], sn2[r]);
+                al[r] = exp2f(m_run[r] - m_new);                 // exp2(-inf) = 0 when nothing came before
+                pn[r] = exp2f(sn2[r] - m_new);
+                l_run[r] = l_run[r] * al[r] + (t == 0 ? pn[r] : 0.f);   // l is shared out over the quad: count once
+                m_run[r] = m_new;
             }
-            float alpha[2], row_sum[2] = {0.f, 0.f};
 #pragma unroll
-            for (int r = 0; r < 2; ++r) alpha[r] = (m_new[r] == -INFINITY) ? 1.f : exp2f(m_run[r] - m_new[r]);
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int r = e >> 1;
-                    const float pj = (m_new[r] == -INFINITY) ? 0.f : exp2f(sc[j][e] - m_new[r]);
-                    sc[j][e] = pj;
-                    row_sum[r] += pj;
-                }
-#pragma unroll
-            for (int r = 0; r < 2; ++r) { l_run[r] = l_run[r] * alpha[r] + row_sum[r]; m_run[r] = m_new[r]; }
-#pragma unroll
-            for (int j = 0; j < HD / 8; ++j) { o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1]; }
-            const uint32_t a0 = pack2(sc[0][0], sc[0][1]), a1 = pack2(sc[0][2], sc[0][3]);
-            const uint32_t a2 = pack2(sc[1][0], sc[1][1]), a3 = pack2(sc[1][2], sc[1][3]);
-#pragma unroll
-            for (int jp = 0; jp < HD / 16; ++jp) {
-                uint32_t b0, b1, b2, b3;
-                const int key = 16 * warp + (((lane >> 3) & 1) << 3) + (lane & 7);
-                ldmatrix_x4_trans(vbase + tile_offset<HD>(key, jp * 2 + (lane >> 4)), b0, b1, b2, b3);
-                mma16816(o[2 * jp], a0, a1, a2, a3, b0, b1);
-                mma16816(o[2 * jp + 1], a0, a1, a2, a3, b2, b3);
+            for (int j = 0; j < HD / 8; ++j) {
+                const uint32_t vw = *reinterpret_cast<const uint32_t*>(v_src + (8 * j + 2 * t) * 2);
+                if (g == 0) *reinterpret_cast<uint32_t*>(v_cache + row + 8 * j + 2 * t) = vw;
+                const float v0 = bf16lo(vw), v1 = bf16hi(vw);
+                o[j][0] = fmaf(pn[0], v0, o[j][0] * al[0]); o[j][1] = fmaf(pn[0], v1, o[j][1] * al[0]);
+                o[j][2] = fmaf(pn[1], v0, o[j][2] * al[1]); o[j][3] = fmaf(pn[1], v1, o[j][3] * al[1]);
             }
         }
-        __syncthreads();                                         // the stage may be refilled
-        if (i + 2 < n_my) load_page(i + 2, stage); else cp_async_commit();
-    }
-    cp_async_wait<0>();
 
-    if (FUSE && owns_new && warp == 0) {
-        // the token's own key and value, from the projection's output; all of this is lane-local
-        const __nv_bfloat16* k_src = q + (size_t)b * ldq + (size_t)(n_q + kvh) * HD;
-        const __nv_bfloat16* v_src = k_src + (size_t)n_kv * HD;
-        float kn[KS][4];
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            const uint32_t w0 = *reinterpret_cast<const uint32_t*>(k_src + 16 * ks + 2 * t);
-            const uint32_t w1 = *reinterpret_cast<const uint32_t*>(k_src + 16 * ks + 2 * t + 8);
-            kn[ks][0] = bf16lo(w0); kn[ks][1] = bf16hi(w0); kn[ks][2] = bf16lo(w1); kn[ks][3] = bf16hi(w1);
-        }
-#pragma unroll
-        for (int ks = 0; ks < KS / 2; ++ks)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int idx = 16 * ks + 2 * t + (e & 1) + (e >> 1) * 8;
-                const float c = cos_t[(size_t)p * HALF + idx], sn = sin_t[(size_t)p * HALF + idx];
-                const float x1 = kn[ks][e], x2 = kn[ks + KS / 2][e];
-                kn[ks][e] = __bfloat162float(__float2bfloat16_rn(x1 * c - x2 * sn));          // as the cache holds it
-                kn[ks + KS / 2][e] = __bfloat162float(__float2bfloat16_rn(x1 * sn + x2 * c));
-            }
-        const size_t row = ((((size_t)pt[p >> 6] * n_kv + kvh) << 6) + (p & 63)) * HD;
-        if (g == 0) {
-#pragma unroll
-            for (int ks = 0; ks < KS; ++ks) {
-                *reinterpret_cast<uint32_t*>(k_cache + row + 16 * ks + 2 * t) = pack2(kn[ks][0], kn[ks][1]);
-                *reinterpret_cast<uint32_t*>(k_cache + row + 16 * ks + 2 * t + 8) = pack2(kn[ks][2], kn[ks][3]);
-            }
-        }
-        float sn2[2] = {0.f, 0.f};                               // scores of rows g and g + 8 (log2 domain)
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            sn2[0] += bf16lo(qf[ks][0]) * kn[ks][0] + bf16hi(qf[ks][0]) * kn[ks][1]
-                    + bf16lo(qf[ks][2]) * kn[ks][2] + bf16hi(qf[ks][2]) * kn[ks][3];
-            sn2[1] += bf16lo(qf[ks][1]) * kn[ks][0] + bf16hi(qf[ks][1]) * kn[ks][1]
-                    + bf16lo(qf[ks][3]) * kn[ks][2] + bf16hi(qf[ks][3]) * kn[ks][3];
-        }
-        float pn[2], al[2];
+        // merge the 4 warps (each saw different keys) in warp order
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-            sn2[r] += __shfl_xor_sync(0xffffffffu, sn2[r], 1);
-            sn2[r] += __shfl_xor_sync(0xffffffffu, sn2[r], 2);
-            const float m_new = fmaxf(m_run[r], sn2[r]);
-            al[r] = exp2f(m_run[r] - m_new);                     // exp2(-inf) = 0 when nothing came before
-            pn[r] = exp2f(sn2[r] - m_new);
-            l_run[r] = l_run[r] * al[r] + (t == 0 ? pn[r] : 0.f);   // l is shared out over the quad: count once
-            m_run[r] = m_new;
+            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+            if (t == 0) { sm_m[warp][g + 8 * r] = m_run[r]; sm_l[warp][g + 8 * r] = l_run[r]; }
         }
 #pragma unroll
         for (int j = 0; j < HD / 8; ++j) {
-            const uint32_t vw = *reinterpret_cast<const uint32_t*>(v_src + 8 * j + 2 * t);
-            if (g == 0) *reinterpret_cast<uint32_t*>(v_cache + row + 8 * j + 2 * t) = vw;
-            const float v0 = bf16lo(vw), v1 = bf16hi(vw);
-            o[j][0] = fmaf(pn[0], v0, o[j][0] * al[0]); o[j][1] = fmaf(pn[0], v1, o[j][1] * al[0]);
-            o[j][2] = fmaf(pn[1], v0, o[j][2] * al[1]); o[j][3] = fmaf(pn[1], v1, o[j][3] * al[1]);
+            float* d0 = sm_acc + ((size_t)warp * group + g) * ACC_LD + 8 * j + 2 * t;
+            float* d1 = sm_acc + ((size_t)warp * group + g + 8) * ACC_LD + 8 * j + 2 * t;
+            if (g < group) *reinterpret_cast<float2*>(d0) = make_float2(o[j][0], o[j][1]);
+            if (g + 8 < group) *reinterpret_cast<float2*>(d1) = make_float2(o[j][2], o[j][3]);
         }
-    }
-
-    // merge the 4 warps (each saw different keys) in warp order; the stages are free now
-    float* sm_acc = reinterpret_cast<float*>(smem);              // [ADM_WARPS][ADM_ROWS][HD]
+        __syncthreads();
+        const int n_chunks = cur.n_chunks;
+        for (int e = threadIdx.x; e < group * HD; e += ADM_THREADS) {
+            const int row = e / HD, d = e % HD;
+            float mm = -INFINITY;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-        if (t == 0) { sm_m[warp][g + 8 * r] = m_run[r]; sm_l[warp][g + 8 * r] = l_run[r]; }
-    }
+            for (int w = 0; w < ADM_WARPS; ++w) mm = fmaxf(mm, sm_m[w][row]);
+            float ll = 0.f, a = 0.f;
 #pragma unroll
-    for (int j = 0; j < HD / 8; ++j) {
-        float* d0 = sm_acc + ((size_t)warp * ADM_ROWS + g) * HD + 8 * j + 2 * t;
-        float* d1 = sm_acc + ((size_t)warp * ADM_ROWS + g + 8) * HD + 8 * j + 2 * t;
-        d0[0] = o[j][0]; d0[1] = o[j][1]; d1[0] = o[j][2]; d1[1] = o[j][3];
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < group * HD; e += ADM_THREADS) {
-        const int row = e / HD, d = e % HD;
-        float mm = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < ADM_WARPS; ++w) mm = fmaxf(mm, sm_m[w][row]);
-        float ll = 0.f, a = 0.f;
-#pragma unroll
-        for (int w = 0; w < ADM_WARPS; ++w) {
-            const float f = (sm_m[w][row] == -INFINITY) ? 0.f : exp2f(sm_m[w][row] - mm);
-            ll += sm_l[w][row] * f;
-            a += sm_acc[((size_t)w * ADM_ROWS + row) * HD + d] * f;
-        }
-        if (n_splits == 1) {
-            out[(size_t)b * ldo + (size_t)(h0 + row) * HD + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
-        } else {
-            float* part = scratch + (((size_t)b * n_q + h0 + row) * n_splits + split) * (HD + 2);
-            part[d] = a;
-            if (d == 0) { part[HD] = mm; part[HD + 1] = ll; }
-        }
-    }
-    if (n_splits == 1) return;
-
-    // the block that arrives last merges the splits, in split order
-    __threadfence();
-    __syncthreads();
-    int* counter = counters + (size_t)b * gridDim.y + blockIdx.y;
-    if (threadIdx.x == 0) {
-        const int arrived = atomicAdd(counter, 1);
-        is_last = (arrived == n_splits - 1);
-        if (is_last) *counter = 0;
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    // every thread owns elements (head, dim) of the output and goes through the splits itself, in
-    // split order, eight at a time so that their loads are in flight together (see attention_decode.cuh)
-    for (int e = threadIdx.x; e < group * HD; e += ADM_THREADS) {
-        const int row = e / HD, d = e % HD;
-        const float* base = scratch + ((size_t)b * n_q + h0 + row) * n_splits * (HD + 2);
-        float mm = -INFINITY, ll = 0.f, a = 0.f;
-        for (int s0 = 0; s0 < n_splits; s0 += 8) {
-            float pm[8], pl[8], pv[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const bool live = s0 + i < n_splits;
-                const float* part = base + (size_t)(live ? s0 + i : s0) * (HD + 2);
-                pm[i] = live ? __ldcg(part + HD) : -INFINITY;
-                pl[i] = __ldcg(part + HD + 1);
-                pv[i] = __ldcg(part + d);
+            for (int w = 0; w < ADM_WARPS; ++w) {
+                const float f = (sm_m[w][row] == -INFINITY) ? 0.f : exp2f(sm_m[w][row] - mm);
+                ll += sm_l[w][row] * f;
+                a += sm_acc[((size_t)w * group + row) * ACC_LD + d] * f;
             }
-            float m_new = mm;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) m_new = fmaxf(m_new, pm[i]);
-            const float keep = (mm == -INFINITY) ? 0.f : exp2f(mm - m_new);
-            ll *= keep; a *= keep;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float f = (pm[i] == -INFINITY) ? 0.f : exp2f(pm[i] - m_new);
-                ll = fmaf(pl[i], f, ll);
-                a = fmaf(pv[i], f, a);
+            if (n_chunks == 1) {
+                out[(size_t)b * ldo + (size_t)(h0 + row) * HD + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+            } else {
+                float* part = scratch + (((size_t)b * n_q + h0 + row) * max_chunks + cur.chunk) * (HD + 2);
+                part[d] = a;
+                if (d == 0) { part[HD] = mm; part[HD + 1] = ll; }
             }
-            mm = m_new;
         }
-        out[(size_t)b * ldo + (size_t)(h0 + row) * HD + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+        __syncthreads();                                         // the sums are read, the partial results written
+        settle();                                                // the chunk counted an item ago: was it the last?
+        if (n_chunks > 1) {
+            // The block's partial results are ordered before the count by the barrier above and one
+            // fence (cumulative at device scope) in the thread that counts.
+            if (threadIdx.x == 0) {
+                __threadfence();
+                pend_arrived = atomicAdd(counters + (size_t)b * n_kv + kvh, 1);
+            }
+            pend_b = b; pend_kvh = kvh; pend_chunks = n_chunks;
+        }
+
+        // next item: the window moves on
+        if (!has_nxt) break;
+        item += G;
+        cur = nxt;
+        nxt = nn;
+        has_nxt = has_nn;
+        parity ^= 1;
+        --cursor_item;                                           // what pointed at nxt now points at cur
+        fill();
+        has_nn = item + 2 * G < total_items;
+        if (has_nn) decode(item + 2 * G, nn);
     }
+    settle();
+    cp_async_wait<0>();
 }
 
 // Whether the tensor-core kernel takes this case (else attention_decode.cuh's kernel does).
@@ -362,36 +540,67 @@ static inline bool adm_supported(int n_q, int n_kv, int head_dim, int ldq, bool 
            ldq % 8 == 0;
 }
 
+// Scratch one launch needs: floats for the chunks' partial results, ints (zero on entry, left zero)
+// for the arrival counters.
+static inline long long adm_scratch_floats(int n_seqs, int n_q, int head_dim, int max_chunks) {
+    return max_chunks > 1 ? (long long)n_seqs * n_q * max_chunks * (head_dim + 2) : 0;
+}
+static inline int adm_counters(int n_seqs, int n_kv) { return n_seqs * n_kv; }
+
+// Dynamic shared memory of a block: four tiles (two stages of keys and values), the warps' sums, two
+// query buffers, and three integers per sequence of the batch.  Head size 128 with four query heads
+// per kv head and 64 sequences: 78 KB, so two blocks share an SM with room to spare.
+static inline int adm_smem_bytes(int head_dim, int group, int n_seqs) {
+    const int tiles = 4 * 64 * head_dim * 2, sums = ADM_WARPS * group * (head_dim + 4) * 4;
+    const int query = group * head_dim * 2 + head_dim * 4 + head_dim * 4;
+    return tiles + sums + 2 * query + ((3 * n_seqs + 1) * 4 + 15) / 16 * 16;
+}
+
+static inline int adm_sm_count() {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+            sms = n;
+        else
+            return 148;
+    }
+    return sms;
+}
+
+// chunk_pages: pages per chunk (>= 1); max_chunks: the most chunks a sequence is cut into (it sizes
+// the scratch): a sequence that would need more gets max_chunks larger ones.
 static inline int adm_launch(const void* q, int ldq, const void* k_cache, const void* v_cache, const int* pos,
                              const int* slot, const int* page_table, int max_pages, void* out, int ldo,
-                             int n_seqs, int n_q, int n_kv, int head_dim, int window, float scale, int n_splits,
-                             float* scratch, int* counters, cudaStream_t stream, bool pdl, const float* cos_t,
-                             const float* sin_t, const void* prefetch_ptr, long long prefetch_bytes) {
+                             int n_seqs, int n_q, int n_kv, int head_dim, int window, float scale, int chunk_pages,
+                             int max_chunks, float* scratch, int* counters, cudaStream_t stream, bool pdl,
+                             const float* cos_t, const float* sin_t) {
     typedef __nv_bfloat16 bf16;
     if (n_seqs <= 0) return 0;
-    if (n_splits < 1 || n_splits > AD_MAX_SPLITS || (n_splits > 1 && (!scratch || !counters))) return SSB_ERR_BAD_SIZE;
+    if (n_seqs > ADM_MAX_SEQS || chunk_pages < 1 || max_chunks < 1 || (max_chunks > 1 && (!scratch || !counters)))
+        return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return SSB_ERR_BAD_SIZE;
     const bool fuse = cos_t != nullptr;
     if (fuse && !sin_t) return SSB_ERR_BAD_SIZE;
     const float scale_log2 = scale * 1.4426950408889634f;
-    const long long pre = (!prefetch_ptr || ((uintptr_t)prefetch_ptr & 15)) ? 0LL : prefetch_bytes;
-    // about 128 extra blocks do the prefetching (see the kernel)
-    const int extra = pre > 0 ? (128 + n_seqs * n_kv - 1) / (n_seqs * n_kv) : 0;
-    dim3 grid(n_seqs, n_kv, n_splits + extra);
+    const long long items = (long long)n_seqs * n_kv * max_chunks;
+    const int blocks = (int)(items < 2LL * adm_sm_count() ? items : 2LL * adm_sm_count());
+    dim3 grid(blocks);
     int rc = 0;
 #define SSB_ADM(HD_, FUSE_) do { \
-        constexpr int smem_bytes = 4 * 64 * HD_ * 2 + (HD_ == 128 ? ADM_PAD_BYTES : 0); \
-        static bool configured = false; \
-        if (!configured) { \
+        const int smem_bytes = adm_smem_bytes(HD_, n_q / n_kv, n_seqs); \
+        static int configured = 0; \
+        if (smem_bytes > configured) { \
             cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD_, FUSE_>, \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes); \
             if (e != cudaSuccess) return (int)e; \
-            configured = true; \
+            configured = smem_bytes; \
         } \
         rc = ssb_launch(attention_decode_mma_kernel<HD_, FUSE_>, grid, dim3(ADM_THREADS), (size_t)smem_bytes, stream, pdl, \
                         (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
-                        (bf16*)out, ldo, n_q, n_kv, window, scale_log2, n_splits, scratch, counters, cos_t, sin_t, \
-                        (const char*)prefetch_ptr, pre); \
+                        (bf16*)out, ldo, n_seqs, n_q, n_kv, window, scale_log2, chunk_pages, max_chunks, scratch, \
+                        counters, cos_t, sin_t); \
     } while (0)
     if (head_dim == 64) { if (fuse) SSB_ADM(64, true); else SSB_ADM(64, false); }
     else if (head_dim == 128) { if (fuse) SSB_ADM(128, true); else SSB_ADM(128, false); }

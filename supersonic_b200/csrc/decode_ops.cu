@@ -211,7 +211,6 @@ SSB_API int ssb_skinny_gemm(const void* x, int ldx, const void* W, int ldw, void
 // zero before the first launch (every launch leaves them zero).  With cos_t/sin_t
 // ([positions, head_dim/2] float32) the rows of q are the raw fused projection [q | k | v]: the
 // kernel rotates queries and the token's key itself and appends key and value to the cache.
-// prefetch_ptr/bytes: read-only memory (the next kernels' weights) to pull into L2 meanwhile.
 SSB_API long long ssb_attention_decode_scratch_floats(int n_seqs, int n_q, int head_dim, int n_splits) {
     return ad_scratch_floats(n_seqs, n_q, head_dim, n_splits);
 }
@@ -225,16 +224,32 @@ SSB_API int ssb_attention_decode(const void* q, int ldq, const void* k_cache, co
                                  void* out, int ldo, int n_seqs, int n_q, int n_kv, int head_dim,
                                  int page_shift, int window, float scale, int n_splits, float* scratch,
                                  int* counters, int pdl, const float* cos_t, const float* sin_t,
-                                 const void* prefetch_ptr, long long prefetch_bytes, int kind,
                                  cudaStream_t stream) {
-    // kind 0: the tensor-core kernel where it applies, else the general one; 1: general; 2: tensor-core
-    const bool mma_ok = page_shift == 6 && adm_supported(n_q, n_kv, head_dim, ldq, cos_t != nullptr);
-    if (kind == 2 && !mma_ok) return SSB_ERR_UNSUPPORTED;
-    if (kind != 1 && mma_ok)
-        return adm_launch(q, ldq, k_cache, v_cache, pos, slot, page_table, max_pages, out, ldo, n_seqs, n_q, n_kv,
-                          head_dim, window, scale, n_splits, scratch, counters, stream, pdl != 0, cos_t, sin_t,
-                          prefetch_ptr, prefetch_bytes);
     return ad_launch(q, ldq, k_cache, v_cache, pos, slot, page_table, max_pages, out, ldo, n_seqs, n_q, n_kv,
                      head_dim, page_shift, window, scale, n_splits, scratch, counters, stream, pdl != 0,
-                     cos_t, sin_t, prefetch_ptr, prefetch_bytes);
+                     cos_t, sin_t);
+}
+
+// The tensor-core kernel (attention_decode_mma.cuh): head sizes 64 and 128, at most 16 query heads
+// per kv head, 64-token pages, at most 1,024 sequences.  chunk_pages and max_chunks: see adm_launch.
+// Scratch: ssb_attention_decode_chunked_scratch_floats floats; counters: n_seqs * n_kv ints, zero
+// before the first launch (every launch leaves them zero).
+SSB_API int ssb_attention_decode_chunked_ok(int n_seqs, int n_q, int n_kv, int head_dim, int ldq, int page_shift) {
+    return page_shift == 6 && n_seqs <= ADM_MAX_SEQS && adm_supported(n_q, n_kv, head_dim, ldq, false);
+}
+
+SSB_API long long ssb_attention_decode_chunked_scratch_floats(int n_seqs, int n_q, int head_dim, int max_chunks) {
+    return adm_scratch_floats(n_seqs, n_q, head_dim, max_chunks);
+}
+
+SSB_API int ssb_attention_decode_chunked(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                         const int* pos, const int* slot, const int* page_table, int max_pages,
+                                         void* out, int ldo, int n_seqs, int n_q, int n_kv, int head_dim,
+                                         int page_shift, int window, float scale, int chunk_pages, int max_chunks,
+                                         float* scratch, int* counters, int pdl, const float* cos_t,
+                                         const float* sin_t, cudaStream_t stream) {
+    if (!ssb_attention_decode_chunked_ok(n_seqs, n_q, n_kv, head_dim, ldq, page_shift)) return SSB_ERR_UNSUPPORTED;
+    return adm_launch(q, ldq, k_cache, v_cache, pos, slot, page_table, max_pages, out, ldo, n_seqs, n_q, n_kv,
+                      head_dim, window, scale, chunk_pages, max_chunks, scratch, counters, stream, pdl != 0, cos_t,
+                      sin_t);
 }

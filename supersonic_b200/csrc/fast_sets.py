@@ -17,7 +17,8 @@ from . import ops
 from .kernel_sets import NormedInput, PlainKernels, as_tensor
 
 TARGET_BLOCKS = 1184           # eight small blocks per SM
-MMA_PAGES_PER_SPLIT = 4       # decode attention on the tensor cores: at least this many pages a block (2, 4, 8 measured)
+MAX_CHUNK_PAGES = 32           # decode attention on the tensor cores: most pages a work item streams
+DETERMINISTIC_CHUNK_PAGES = 16 # ... and its fixed chunk size (1,024 keys) when results must not depend on the batch
 TC_ATTENTION_MIN_NEW = 96     # prompts at least this long take the tcgen05 attention (tiles of 128 rows)
 
 
@@ -25,8 +26,13 @@ class FastKernels(PlainKernels):
     name = "fast"
     capturable = True       # no kernel of the set synchronises or allocates: decode steps replay CUDA graphs
 
-    def __init__(self, pdl: bool = True):
+    def __init__(self, pdl: bool = True, deterministic: bool = False):
         self.pdl = pdl           # decode kernels launch as programmatic dependents of their predecessors
+        # True: no float atomics anywhere, so that two runs of the same batch give the same bits (and a
+        # sampled sequence is reproducible from its seed); the shares of a projection whose K range
+        # is split over blocks then meet through scratch in a fixed order, and short prompts do not
+        # split K at all
+        self.deterministic = deterministic
         self.fuse_rope = True    # decode attention rotates q/k and appends to the cache itself
         self.fuse_rope_prefill = True   # the prompt's q/k/v projection does so in its epilogue
         self._scratch: Dict[str, torch.Tensor] = {}
@@ -63,10 +69,19 @@ class FastKernels(PlainKernels):
         if (out.dtype == torch.float32 or not accumulate) and ops.gemm_tc_ok(x, weight, out):
             n, k = weight.shape
             if rows <= 64 and accumulate:
-                # weights on the M side, K split over blocks that add with float atomics
-                ops.gemv_tc(x, weight, out, ops.TC_ACCUMULATE, splits=ops.gemv_tc_splits(n, k), pdl=self.pdl)
+                # weights on the M side, K split over blocks that add with float atomics, or (deterministic)
+                # whose shares the last block of a row tile sums in split order
+                splits = ops.gemv_tc_splits(n, k)
+                partials, counters = self._split_scratch(rows, n, splits, out.device) if self.deterministic else (None, None)
+                ops.gemv_tc(x, weight, out, ops.TC_ACCUMULATE, splits=splits, partials=partials, counters=counters,
+                            pdl=self.pdl)
             elif rows <= 64 and n >= 16384:
                 ops.gemv_tc(x, weight, out, ops.TC_STORE, pdl=self.pdl)
+            elif rows <= 64 and self.deterministic:
+                splits = ops.gemv_tc_splits(n, k)
+                partials, counters = self._split_scratch(rows, n, splits, out.device)
+                ops.gemv_tc(x, weight, out, ops.TC_STORE, splits=splits, partials=partials, counters=counters,
+                            pdl=self.pdl)
             elif rows <= 64 and out.dtype == torch.bfloat16 and n % 8 == 0 and out.stride(0) % 8 == 0:
                 # too few row tiles for the SMs (48 for the 8B query/key/value projection): K is split
                 # over blocks that add with float atomics into a float32 scratch that is zero between
@@ -81,7 +96,7 @@ class FastKernels(PlainKernels):
                 # that add with float atomics, into the residual or, for a stored result, into the
                 # zeroed scratch that round_and_clear turns into bfloat16 (as for decode above)
                 tile_n = self._tile_n(rows, n)
-                splits = self._gemm_splits(rows, n, k, tile_n)
+                splits = 1 if self.deterministic else self._gemm_splits(rows, n, k, tile_n)
                 if splits == 1 and self._pair_tiles(rows, n):
                     tile_n = ops.TC_TILE_PAIR
                 if splits > 1 and accumulate:
@@ -98,12 +113,20 @@ class FastKernels(PlainKernels):
                 return
         ops.gemm_nt_plain(x, weight, out, accumulate)
 
+    def _split_scratch(self, rows: int, n: int, splits: int, device):
+        """Scratch of the ordered sum of a split projection (partial tiles, zeroed arrival counters)."""
+        if splits <= 1:
+            return None, None
+        nf, nc = ops.gemv_tc_scratch(rows, n, splits)
+        return (self._buffer("gemv_partials", nf, torch.float32, device),
+                self._buffer("gemv_counters", nc, torch.int32, device, zero=True))
+
     @staticmethod
     def _gemm_splits(rows: int, n: int, k: int, tile_n: int) -> int:
         """Parts a tile's K range is cut into so that the work items fill the SMs once (one block
         per SM walks them); at least 8 k-blocks (512 columns) a part; 1 when the tiles alone do."""
         tiles = ((rows + 127) // 128) * ((n + tile_n - 1) // tile_n)
-        return max(1, min(148 // tiles, (k // 64) // 8, 16))
+        return max(1, min(ops.sm_count() // tiles, (k // 64) // 8, 16))
 
     @staticmethod
     def _pair_tiles(rows: int, n: int) -> bool:
@@ -154,25 +177,44 @@ class FastKernels(PlainKernels):
             self._scratch[name] = t
         return t
 
+    def _chunk_pages(self, n_seqs: int, n_kv: int, pages: int) -> int:
+        """Pages per chunk of the tensor-core decode attention for a batch whose longest sequence spans
+        up to ``pages``.  A work item has a fixed cost of about six pages' worth of streaming (its
+        query, the merge of its warps, its partial result), so items are as large as keeps every
+        resident block busy: the batch's pages shared out over two blocks per SM, between 2 and
+        MAX_CHUNK_PAGES (measured at Llama-3.1-8B sizes: 64 x 520 tokens 31 us unsplit against 54 us in
+        two chunks; 8 x 8,192 tokens 49 us in chunks of 32 pages against 94 us in chunks of 8).  In
+        deterministic mode the figure is a constant, so that a sequence is cut the same way in every batch."""
+        if self.deterministic:
+            return DETERMINISTIC_CHUNK_PAGES
+        share = -(-n_seqs * n_kv * pages // (2 * ops.sm_count()))
+        return max(2 if pages > 2 else 1, min(MAX_CHUNK_PAGES, share))
+
     def _decode_attention(self, q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim,
                           page_shift, window, scale, cos=None, sin=None):
         group = n_q // n_kv
-        blocks = batch.n_seqs * n_kv * ((group + 3) // 4)
-        # the bucket's upper end: up to one page per split while the bucket lasts
+        # the bucket's upper end: the most pages a sequence of this batch can span
         pages = 2 * batch.kv_pages - 1 if batch.kv_pages > 1 else 1
         if window:
             pages = min(pages, (window >> page_shift) + 2)
-        kind = 1
-        if head_dim in (64, 128) and group <= 16 and page_shift == 6:
-            # tensor-core kernel: a block streams pages back to back; a few pages a split, about two
-            # blocks per SM.  Beside the mma.sync skinny GEMM it made a step slower (the two compete
-            # for the SM's L1/shared memory); beside the tcgen05 projections it is the faster choice
-            # at every batch size (batch 16: 4.24 to 3.57 ms a step, batch 8: 3.64 to 3.42).
-            kind = 2
-            # a block's time grows with its pages (0.6 us each), the merge with the splits (0.3 us each):
-            # about sqrt(2 * pages) splits, at least MMA_PAGES_PER_SPLIT pages each, two blocks per SM at most
-            n_splits = max(1, min(296 // (batch.n_seqs * n_kv), pages // MMA_PAGES_PER_SPLIT,
-                                  int(math.sqrt(2.0 * pages) + 0.5), 64))
+        if ops.attention_decode_chunked_ok(batch.n_seqs, n_q, n_kv, head_dim, q.stride(0), page_shift):
+            # tensor-core kernel on a persistent grid (beside the mma.sync skinny GEMM it made a step
+            # slower: the two compete for the SM's L1/shared memory; beside the tcgen05 projections it
+            # is the faster choice at every batch size: batch 16: 4.24 to 3.57 ms a step)
+            chunk = self._chunk_pages(batch.n_seqs, n_kv, pages)
+            max_chunks = -(-pages // chunk)
+            scratch = counters = None
+            if max_chunks > 1:
+                nf, nc = ops.attention_decode_chunked_scratch(batch.n_seqs, n_q, n_kv, head_dim, max_chunks)
+                scratch = self._buffer("attn_partials", nf, torch.float32, q.device)
+                counters = self._buffer("attn_counters", nc, torch.int32, q.device, zero=True)
+            ops.attention_decode_chunked(q, k_cache, v_cache, batch.pos, batch.slot_of_token, page_table, out,
+                                         n_q, n_kv, head_dim, page_shift, window, scale, chunk, max_chunks,
+                                         scratch, counters, pdl=self.pdl, cos=cos, sin=sin)
+            return
+        blocks = batch.n_seqs * n_kv * ((group + 3) // 4)
+        if self.deterministic:
+            n_splits = 1                                                  # one order of the keys whatever the batch
         elif batch.n_seqs <= 2:
             n_splits = max(1, min(TARGET_BLOCKS // blocks, pages, 16))    # latency-bound: a page a block
         elif pages < 32:
@@ -186,7 +228,7 @@ class FastKernels(PlainKernels):
             counters = self._buffer("attn_counters", nc, torch.int32, q.device, zero=True)
         ops.attention_decode(q, k_cache, v_cache, batch.pos, batch.slot_of_token, page_table, out,
                              n_q, n_kv, head_dim, page_shift, window, scale, n_splits, scratch, counters,
-                             pdl=self.pdl, cos=cos, sin=sin, kind=kind)
+                             pdl=self.pdl, cos=cos, sin=sin)
 
     def project_rope_append(self, x, w_qkv, qkv, position, kv, batch, n_q, n_kv, head_dim, page_shift) -> bool:
         """Prompts whose tiles alone fill the SMs: the tcgen05 projection rotates q and k from its

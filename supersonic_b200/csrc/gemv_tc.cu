@@ -5,8 +5,9 @@
 // accumulator [W row, batch row] sits in tensor memory.  When K is split over several blocks
 // (few row tiles: the small projections), a store or SwiGLU output goes through scratch: each
 // block writes its partial tile and the block that arrives last for the tile adds them in split
-// order (same result every time); an add into the float32 residual is done by every block with
-// float atomics (cheaper; the order of the shares, and so the last bits, vary between runs).
+// order (same result every time); an add into the float32 residual is done the same way when the
+// caller gives scratch, else by every block with float atomics (cheaper; the order of the shares,
+// and so the last bits, then vary between runs).
 // Epilogues: store, add into the float32 residual, SwiGLU over [8 gate | 8 up] rows.
 //
 // The general GEMM (gemm_tc.cu) has the tokens on the M side: with 64 tokens it re-reads the
@@ -151,10 +152,11 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < BNB; ++j) v[j] = 0.f;
         }
-        // Adding into the float32 residual with K split over blocks: each block adds its share
-        // straight in (red.global.add.f32).  The order in which shares meet varies from run to run,
-        // so the last bits of the residual may; store and SwiGLU outputs use the ordered fix-up below.
-        const bool atomic_add = splits > 1 && mode == TC_ACCUMULATE;
+        // Adding into the float32 residual with K split over blocks and no scratch: each block adds its
+        // share straight in (red.global.add.f32).  The order in which shares meet varies from run to
+        // run, so the last bits of the residual may; everything else uses the ordered fix-up below.
+        // With scratch given, an add is ordered too: the last block of the tile adds the sum of the shares.
+        const bool atomic_add = splits > 1 && mode == TC_ACCUMULATE && partials == nullptr;
         if (ok && splits > 1 && !atomic_add) {
             // partial tile to scratch; the block that arrives last adds all of them in split order
             float* mine = partials + (((size_t)tile * splits + split) * GV_BM + r) * BNB;
@@ -249,7 +251,7 @@ SSB_API int ssb_gemv_tc(const void* x, int ldx, const void* W, int ldw, void* ou
     if (n_rows <= 0 || N <= 0) return 0;
     if (n_rows > 64 || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || !error_word || splits < 1) return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)x | (uintptr_t)W | (uintptr_t)partials) & 15) return SSB_ERR_BAD_SIZE;
-    if (splits > 1 && mode != TC_ACCUMULATE && (!partials || !counters)) return SSB_ERR_BAD_SIZE;
+    if (splits > 1 && (mode != TC_ACCUMULATE || partials) && (!partials || !counters)) return SSB_ERR_BAD_SIZE;
     if (splits > (K + TC_BK - 1) / TC_BK) return SSB_ERR_BAD_SIZE;
     if (mode == TC_ACCUMULATE && out_dtype != SSB_F32) return SSB_ERR_BAD_DTYPE;
     if (mode == TC_SWIGLU && (out_dtype != SSB_BF16 || N % 16)) return SSB_ERR_BAD_SIZE;

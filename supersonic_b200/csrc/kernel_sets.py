@@ -113,9 +113,10 @@ class PlainKernels:
         ops.sample(logits, temperature, top_k, top_p, slots, rng_state, out, drawn_u)
 
 
-def kernel_set_for(dtype: torch.dtype, prefer: Optional[str] = None):
-    """float32 always runs the plain set; bfloat16 runs the fast set unless ``prefer='plain'``."""
+def kernel_set_for(dtype: torch.dtype, prefer: Optional[str] = None, deterministic: bool = False):
+    """float32 always runs the plain set (which has no atomics on data); bfloat16 runs the fast set
+    unless ``prefer='plain'``, with or without float atomics in its split projections."""
     if dtype == torch.float32 or prefer == "plain":
         return PlainKernels()
     from .fast_sets import FastKernels
-    return FastKernels()
+    return FastKernels(deterministic=deterministic)

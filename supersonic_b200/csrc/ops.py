@@ -284,33 +284,35 @@ def attention_decode_scratch(n_seqs: int, n_q: int, n_kv: int, head_dim: int, n_
             int(lib.ssb_attention_decode_counters(c_int(n_seqs), c_int(n_q), c_int(n_kv))))
 
 
-def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor,
-                     slot: torch.Tensor, page_table: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int,
-                     head_dim: int, page_shift: int, window: Optional[int], scale: float, n_splits: int,
-                     scratch: Optional[torch.Tensor], counters: Optional[torch.Tensor],
-                     pdl: bool = False, cos: Optional[torch.Tensor] = None,
-                     sin: Optional[torch.Tensor] = None, prefetch: Optional[torch.Tensor] = None,
-                     prefetch_bytes: int = 0, kind: int = 0) -> None:
-    """One query token per sequence (row) over its cached keys, the keys split ``n_splits`` ways.
-    With ``cos``/``sin`` ([positions, head_dim/2] float32) the rows of ``q`` are the raw fused
-    projection [q | k | v]: queries and the token's key are rotated inside the kernel, and key
-    and value are appended to the cache (no separate rope/append launch).  ``prefetch``: weights
-    that later kernels will stream; the first ``prefetch_bytes`` of it are pulled into L2 meanwhile.
-    ``kind``: 0 picks the tensor-core kernel where it applies (head_dim 64/128, at most 16 query
-    heads per kv head), 1 forces the general kernel, 2 the tensor-core one."""
+def _attention_decode_checks(q, k_cache, v_cache, pos, slot, page_table, out, n_q, n_kv, head_dim, cos, sin, what):
     _need(q, "q", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
     _need(k_cache, "k_cache", torch.bfloat16); _need(v_cache, "v_cache", torch.bfloat16)
     _need(pos, "pos", torch.int32, 1); _need(slot, "slot", torch.int32, 1)
     _need(page_table, "page_table", torch.int32, 2)
     B = q.shape[0]
     if pos.shape[0] != B or slot.shape[0] != B or out.shape[0] != B:
-        raise KernelError("attention_decode: one position, slot and output row per sequence")
+        raise KernelError(f"{what}: one position, slot and output row per sequence")
     if cos is not None:
         _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
         if cos.shape != sin.shape or cos.shape[1] * 2 != head_dim or not (cos.is_contiguous() and sin.is_contiguous()):
-            raise KernelError("attention_decode: cos/sin must be [positions, head_dim/2], contiguous")
+            raise KernelError(f"{what}: cos/sin must be [positions, head_dim/2], contiguous")
         if head_dim not in (32, 64, 128, 256) or q.shape[1] < (n_q + 2 * n_kv) * head_dim:
-            raise KernelError("attention_decode: fused rotation needs head_dim 32/64/128/256 and [q|k|v] rows")
+            raise KernelError(f"{what}: fused rotation needs head_dim 32/64/128/256 and [q|k|v] rows")
+    return B
+
+
+def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor,
+                     slot: torch.Tensor, page_table: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int,
+                     head_dim: int, page_shift: int, window: Optional[int], scale: float, n_splits: int,
+                     scratch: Optional[torch.Tensor], counters: Optional[torch.Tensor],
+                     pdl: bool = False, cos: Optional[torch.Tensor] = None,
+                     sin: Optional[torch.Tensor] = None) -> None:
+    """One query token per sequence (row) over its cached keys, the keys split ``n_splits`` ways, on
+    CUDA cores (any head size up to 256).  With ``cos``/``sin`` ([positions, head_dim/2] float32) the
+    rows of ``q`` are the raw fused projection [q | k | v]: queries and the token's key are rotated
+    inside the kernel, and key and value are appended to the cache (no separate rope/append launch)."""
+    B = _attention_decode_checks(q, k_cache, v_cache, pos, slot, page_table, out, n_q, n_kv, head_dim, cos, sin,
+                                 "attention_decode")
     if n_splits > 64:
         raise KernelError("attention_decode: at most 64 splits")
     if n_splits > 1:
@@ -323,9 +325,50 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         c_int(page_table.shape[1]), _ptr(out), c_int(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv),
         c_int(head_dim), c_int(page_shift), c_int(int(window) if window else 0), c_float(scale),
         c_int(n_splits), _ptr(scratch), _ptr(counters), c_int(1 if pdl else 0), _ptr(cos), _ptr(sin),
-        _ptr(prefetch), c_longlong(min(prefetch_bytes, prefetch.numel() * prefetch.element_size())
-                                   if prefetch is not None else 0), c_int(kind),
         _stream()), "attention_decode")
+
+
+def attention_decode_chunked_ok(n_seqs: int, n_q: int, n_kv: int, head_dim: int, ldq: int, page_shift: int) -> bool:
+    """Whether the tensor-core decode attention takes this case (head sizes 64 and 128, at most 16
+    query heads per kv head, 64-token pages, at most 1,024 sequences)."""
+    return bool(_fn("decode_ops", "ssb_attention_decode_chunked_ok")(
+        c_int(n_seqs), c_int(n_q), c_int(n_kv), c_int(head_dim), c_int(ldq), c_int(page_shift)))
+
+
+def attention_decode_chunked_scratch(n_seqs: int, n_q: int, n_kv: int, head_dim: int, max_chunks: int):
+    """(float32 elements of scratch, int32 counters) a launch needs; counters start at zero."""
+    lib = load_library("decode_ops")
+    lib.ssb_attention_decode_chunked_scratch_floats.restype = c_longlong
+    return (int(lib.ssb_attention_decode_chunked_scratch_floats(c_int(n_seqs), c_int(n_q), c_int(head_dim),
+                                                                c_int(max_chunks))), n_seqs * n_kv)
+
+
+def attention_decode_chunked(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor,
+                             slot: torch.Tensor, page_table: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int,
+                             head_dim: int, page_shift: int, window: Optional[int], scale: float,
+                             chunk_pages: int, max_chunks: int, scratch: Optional[torch.Tensor],
+                             counters: Optional[torch.Tensor], pdl: bool = False,
+                             cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None) -> None:
+    """``attention_decode`` on the tensor cores with a persistent grid: every sequence's pages are cut
+    into chunks of about ``chunk_pages`` pages (a cut that depends on the sequence alone), a work item
+    is (sequence, chunk, kv head), and about two blocks per SM walk the items.  ``max_chunks`` bounds
+    the chunks of one sequence and sizes the scratch (:func:`attention_decode_chunked_scratch`); a
+    longer sequence gets ``max_chunks`` larger chunks."""
+    B = _attention_decode_checks(q, k_cache, v_cache, pos, slot, page_table, out, n_q, n_kv, head_dim, cos, sin,
+                                 "attention_decode_chunked")
+    if chunk_pages < 1 or max_chunks < 1:
+        raise KernelError("attention_decode_chunked: chunk_pages and max_chunks must be at least 1")
+    if max_chunks > 1:
+        need_f, need_c = attention_decode_chunked_scratch(B, n_q, n_kv, head_dim, max_chunks)
+        _need(scratch, "scratch", torch.float32); _need(counters, "counters", torch.int32)
+        if scratch.numel() < need_f or counters.numel() < need_c:
+            raise KernelError(f"attention_decode_chunked: scratch of {need_f} floats and {need_c} counters needed")
+    _check(_fn("decode_ops", "ssb_attention_decode_chunked")(
+        _ptr(q), c_int(q.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(pos), _ptr(slot), _ptr(page_table),
+        c_int(page_table.shape[1]), _ptr(out), c_int(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv),
+        c_int(head_dim), c_int(page_shift), c_int(int(window) if window else 0), c_float(scale),
+        c_int(chunk_pages), c_int(max_chunks), _ptr(scratch), _ptr(counters), c_int(1 if pdl else 0), _ptr(cos),
+        _ptr(sin), _stream()), "attention_decode_chunked")
 
 
 # ---- prefill GEMM on tcgen05 ---------------------------------------------------------------
@@ -539,11 +582,22 @@ def attention_prefill_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
 
 
 # ---- decode projections on tcgen05, weights on the M side ------------------------------------------
+_sm_counts = {}
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (asked once per device)."""
+    dev = torch.cuda.current_device()
+    if dev not in _sm_counts:
+        _sm_counts[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return _sm_counts[dev]
+
+
 def gemv_tc_splits(n: int, k: int) -> int:
     """Blocks that share the K range of one 128-row tile of W: up to two blocks per SM in all
     (every SM must pull for the memory system to be busy), at least 8 k-blocks (512 columns) each."""
     tiles = (n + 127) // 128
-    return max(1, min(296 // tiles, (k // 64) // 8, 8))
+    return max(1, min(2 * sm_count() // tiles, (k // 64) // 8, 8))
 
 
 def gemv_tc_scratch(rows: int, n: int, splits: int):
@@ -567,7 +621,7 @@ def gemv_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_
     n_out = N // 2 if mode == TC_SWIGLU else N
     if w.shape[1] != K or tuple(out.shape) != (B, n_out) or B > 64:
         raise KernelError(f"gemv_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
-    if splits > 1 and mode != TC_ACCUMULATE:
+    if splits > 1 and (mode != TC_ACCUMULATE or partials is not None):
         nf, nc = gemv_tc_scratch(B, N, splits)
         _need(partials, "partials", torch.float32); _need(counters, "counters", torch.int32)
         if partials.numel() < nf or counters.numel() < nc:

@@ -127,13 +127,14 @@ class Model:
     def __init__(self, spec: ModelSpec, store: WeightStore, dtype="bfloat16", device="cuda:0",
                  max_tokens: int = 4096, max_seq_tokens: Optional[int] = None,
                  max_slots: Optional[int] = None, kernels: Optional[str] = None, config=None,
-                 use_graphs: bool = True, step_token_budget: int = 32768, preflight: bool = True):
+                 use_graphs: bool = True, step_token_budget: int = 32768, preflight: bool = True,
+                 deterministic: bool = False):
         spec.validate()
         self.spec, self.config = spec, config
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
         _require_cuda(self.device)
-        self.kernels = kernel_set_for(self.dtype, kernels)
+        self.kernels = kernel_set_for(self.dtype, kernels, deterministic)
         max_seq = min(max_seq_tokens or spec.max_positions, spec.max_positions, max_tokens)
         if int(step_token_budget) < 1:
             raise ValueError("step_token_budget must be at least 1")

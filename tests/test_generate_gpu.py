@@ -393,3 +393,38 @@ def test_a_folder_with_buffer_tensors_loads(tmp_path):
         warnings.simplefilter("always")
         Model.from_dir(str(tmp_path), dtype="float32", max_tokens=64, allow_unexpected_tensors=True)
     assert any("model.extra.weight" in str(w.message) for w in seen)
+
+
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_bfloat16_sampling_is_reproducible_in_deterministic_mode(model_folders, name):
+    """bfloat16 with ``deterministic=True`` (no float atomics; a sequence's keys are cut the same way
+    in every batch): the same seed gives the same tokens twice, in a batch of four, in pairs and
+    alone; and the logits of a sequence are the same bits alone and among others."""
+    import supersonic_b200
+    from supersonic_b200.engine import StepEntry
+    d, pc, pw = model_folders[name]
+    rng = np.random.default_rng(71)
+    prompts = [rng.integers(0, pc["vocab_size"], n).tolist() for n in (9, 3, 150, 70)]
+    eng = supersonic_b200.load(d, dtype="bfloat16", context_size=256, batch_size=4, deterministic=True)
+    assert eng.model.kernels.deterministic and eng.model.use_graphs
+    kw = dict(max_new_tokens=24, temperature=0.8, top_k=50, sampling_seed=1234, ignore_eos=True)
+    together = eng.generate(prompts, batch_size=4, **kw)
+    assert together == eng.generate(prompts, batch_size=4, **kw)          # the seed decides, every time
+    assert eng.generate(prompts, batch_size=2, **kw) == together          # the batch does not
+    assert [eng.generate([p], batch_size=1, **{**kw, "sampling_seed": 1234})[0] for p in prompts[:1]] == together[:1]
+    assert eng.generate(prompts, batch_size=4, **{**kw, "sampling_seed": 99}) != together
+    # logits, bit for bit: a sequence alone against the same sequence among three others, prompt and decode
+    m = eng.model
+    slots = [m.open_sequence() for _ in prompts]
+    batch = m.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+    nxt = [int(t) for t in batch.argmax(-1)]
+    batch2 = m.step([StepEntry(s, [t], [0]) for s, t in zip(slots, nxt)])
+    for s in slots:
+        m.close_sequence(s)
+    for i in (0, 2):
+        s = m.open_sequence()
+        alone = m.step([StepEntry(s, prompts[i], [len(prompts[i]) - 1])])
+        alone2 = m.step([StepEntry(s, [nxt[i]], [0])])
+        m.close_sequence(s)
+        assert torch.equal(alone[0], batch[i]), f"prompt {i}"
+        assert torch.equal(alone2[0], batch2[i]), f"decode {i}"

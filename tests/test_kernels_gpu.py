@@ -313,6 +313,33 @@ def test_skinny_gemm_swiglu(rows):
     torch.testing.assert_close(out.float(), z.float(), atol=2e-2, rtol=2e-2)
 
 
+def _decode_attention(kind, q, k, v, pos, slot, table, out, n_q, n_kv, hd, window, scale, n_splits, max_pages,
+                      cos=None, sin=None, poison=True):
+    """kind 1: the CUDA-core kernel with ``n_splits`` splits; kind 2: the tensor-core kernel on its
+    persistent grid with chunks of ceil(max_pages / n_splits) pages (so that the longest sequence is cut
+    into about ``n_splits`` chunks).  Returns the counters, which every launch must leave zero."""
+    B = q.shape[0]
+    if kind == 1:
+        nf, nc = ops().attention_decode_scratch(B, n_q, n_kv, hd, n_splits)
+    else:
+        chunk = -(-max_pages // n_splits)
+        max_chunks = -(-max_pages // chunk)
+        nf, nc = ops().attention_decode_chunked_scratch(B, n_q, n_kv, hd, max_chunks)
+    scratch = torch.full((max(nf, 1),), float("nan") if poison else 0.0, device=DEV)
+    counters = torch.zeros(max(nc, 1), dtype=torch.int32, device=DEV)
+    for _ in range(2):                                                   # counters are left ready for reuse
+        out.fill_(5.0)
+        if kind == 1:
+            ops().attention_decode(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, window, scale, n_splits,
+                                   scratch, counters, cos=cos, sin=sin)
+        else:
+            ops().attention_decode_chunked(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, window, scale, chunk,
+                                           max_chunks, scratch, counters, cos=cos, sin=sin)
+        if cos is not None:
+            break                                                        # a fused launch appends: once only
+    return counters
+
+
 @pytest.mark.parametrize("n_q,n_kv,hd,window", [(4, 2, 16, None), (3, 1, 48, None), (32, 8, 128, None),
                                                 (6, 2, 128, 100), (2, 2, 256, None), (8, 1, 64, 64),
                                                 (5, 5, 80, None)])
@@ -328,16 +355,11 @@ def test_attention_decode(n_q, n_kv, hd, window, n_splits, kind):
     k, v = _paged(30, n_kv, hd, torch.bfloat16, 25)
     q = torch.randn(len(pos), (n_q + 2 * n_kv) * hd, device=DEV, generator=g).bfloat16()
     scale = 1 / math.sqrt(hd)
-    nf, nc = ops().attention_decode_scratch(len(pos), n_q, n_kv, hd, n_splits)
-    scratch = torch.full((nf,), float("nan"), device=DEV)
-    counters = torch.zeros(nc, dtype=torch.int32, device=DEV)
     ref = _attention_reference(q, k, v, pos, slot, table, n_q, n_kv, hd, window, scale)
-    for _ in range(2):                                                   # counters are left ready for reuse
-        out = torch.full((len(pos), n_q * hd), 5.0, dtype=torch.bfloat16, device=DEV)
-        ops().attention_decode(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, window, scale, n_splits,
-                               scratch, counters, kind=kind)
-        torch.testing.assert_close(out.double(), ref, atol=2e-2, rtol=2e-2)
-        assert torch.all(out[5] == 0) and torch.all(counters == 0)
+    out = torch.empty((len(pos), n_q * hd), dtype=torch.bfloat16, device=DEV)
+    counters = _decode_attention(kind, q, k, v, pos, slot, table, out, n_q, n_kv, hd, window, scale, n_splits, 5)
+    torch.testing.assert_close(out.double(), ref, atol=2e-2, rtol=2e-2)
+    assert torch.all(out[5] == 0) and torch.all(counters == 0)
     plain = torch.empty_like(out)
     ops().attention_plain(q, k, v, pos, slot, table, plain, n_q, n_kv, hd, 6, window, scale)
     torch.testing.assert_close(out.float(), plain.float(), atol=1e-2, rtol=1e-2)
@@ -362,12 +384,8 @@ def test_attention_decode_merges_many_splits(kind, n_splits, slope):
     q = 0.3 * torch.randn(2, (n_q + 2 * n_kv) * hd, device=DEV, generator=g).bfloat16()
     q[:, 0:n_q * hd:hd] = 1.0                                          # every head looks along the ramp
     scale = 1 / math.sqrt(hd)
-    nf, nc = ops().attention_decode_scratch(2, n_q, n_kv, hd, n_splits)
-    scratch = torch.full((nf,), float("nan"), device=DEV)
-    counters = torch.zeros(nc, dtype=torch.int32, device=DEV)
     out = torch.empty(2, n_q * hd, dtype=torch.bfloat16, device=DEV)
-    ops().attention_decode(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, None, scale, n_splits,
-                           scratch, counters, kind=kind)
+    counters = _decode_attention(kind, q, k, v, pos, slot, table, out, n_q, n_kv, hd, None, scale, n_splits, n_pages)
     ref = _attention_reference(q, k, v, pos, slot, table, n_q, n_kv, hd, None, scale)
     torch.testing.assert_close(out.double(), ref, atol=2e-2, rtol=2e-2)
     assert torch.all(counters == 0)
@@ -602,20 +620,16 @@ def test_attention_decode_with_rotation_and_append_inside(n_q, n_kv, hd, window,
         (1.0 / 10000 ** (torch.arange(hd // 2, device=DEV, dtype=torch.float64) * 2 / hd))[None, :]
     cos, sin = ang.cos().float().contiguous(), ang.sin().float().contiguous()
     scale = 1 / math.sqrt(hd)
-    nf, nc = ops().attention_decode_scratch(len(pos), n_q, n_kv, hd, n_splits)
-    scratch = torch.empty(max(nf, 1), device=DEV)
-    counters = torch.zeros(max(nc, 1), dtype=torch.int32, device=DEV)
     # the two-step way
     qkv_a, ka, va = qkv0.clone(), k0.clone(), v0.clone()
     ops().rope_append(qkv_a, cos, sin, pos, slot, table, ka, va, n_q, n_kv, hd, hd, 6, True)
     want = torch.empty(len(pos), n_q * hd, dtype=torch.bfloat16, device=DEV)
-    ops().attention_decode(qkv_a, ka, va, pos, slot, table, want, n_q, n_kv, hd, 6, window, scale, n_splits,
-                           scratch, counters, kind=1)
+    _decode_attention(1, qkv_a, ka, va, pos, slot, table, want, n_q, n_kv, hd, window, scale, n_splits, 5)
     # the fused way
     qkv_b, kb, vb = qkv0.clone(), k0.clone(), v0.clone()
     got = torch.full_like(want, 5.0)
-    ops().attention_decode(qkv_b, kb, vb, pos, slot, table, got, n_q, n_kv, hd, 6, window, scale, n_splits,
-                           scratch, counters, cos=cos, sin=sin, kind=kind)
+    counters = _decode_attention(kind, qkv_b, kb, vb, pos, slot, table, got, n_q, n_kv, hd, window, scale, n_splits, 5,
+                                 cos=cos, sin=sin)
     torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
     assert torch.equal(qkv_b, qkv0)                                       # the projection's output is not touched
     assert torch.equal(vb, va)                                            # values are copied as they are
@@ -793,3 +807,37 @@ def test_random_store_is_the_written_folder(tmp_path):
     made = RandomWeightStore(cfg, 5, device=DEV, std=0.05)
     for name in cfg.tensor_shapes():
         assert torch.equal(made.get(name).cpu(), folder.get(name)), name
+
+
+def test_attention_decode_chunked_over_a_ragged_batch():
+    """The persistent grid of the tensor-core kernel over sequences of 1 to 2,900 keys in one launch,
+    more work items than blocks, several chunk sizes, a far key that stands out in a long sequence;
+    and the cut of a sequence does not depend on the batch: alone or among the others, the same bits."""
+    n_q, n_kv, hd = 8, 2, 128
+    lens = [1, 2900, 64, 65, 700, 5, 1500, 129, 2047, 333, 1, 2048]
+    B, n_pages = len(lens), 46
+    g = torch.Generator(device=DEV).manual_seed(81)
+    k, v = _paged(B * n_pages, n_kv, hd, torch.bfloat16, 82)
+    table = torch.randperm(B * n_pages, generator=torch.Generator().manual_seed(83)).to(torch.int32).view(B, n_pages).to(DEV)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    slot = torch.arange(B, dtype=torch.int32, device=DEV)
+    q = torch.randn(B, n_q * hd, device=DEV, generator=g).bfloat16()
+    # sequence 1: key 37 (page 0) answers head 0's query far more loudly than any of the other 2,899
+    k[int(table[1, 0]), 0, 37] = (q[1, :hd].float() * 4 / q[1, :hd].float().norm() * math.sqrt(hd)).bfloat16()
+    scale = 1 / math.sqrt(hd)
+    ref = _attention_reference(q, k, v, pos, slot, table, n_q, n_kv, hd, None, scale)
+    assert (ref[1, :hd] - v[int(table[1, 0]), 0, 37].double()).abs().max() < 0.05      # the far key decides head 0
+    for chunk, max_chunks in ((1, 46), (3, 16), (8, 6), (8, 3), (64, 1)):
+        nf, nc = ops().attention_decode_chunked_scratch(B, n_q, n_kv, hd, max_chunks)
+        scratch = torch.full((max(nf, 1),), float("nan"), device=DEV)
+        counters = torch.zeros(nc, dtype=torch.int32, device=DEV)
+        out = torch.full((B, n_q * hd), 5.0, dtype=torch.bfloat16, device=DEV)
+        ops().attention_decode_chunked(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, None, scale, chunk,
+                                       max_chunks, scratch, counters)
+        torch.testing.assert_close(out.double(), ref, atol=2e-2, rtol=2e-2)
+        assert torch.all(counters == 0)
+        for b in (1, 4, 10):                                             # alone: the same chunks, the same bits
+            alone = torch.empty((1, n_q * hd), dtype=torch.bfloat16, device=DEV)
+            ops().attention_decode_chunked(q[b:b + 1], k, v, pos[b:b + 1], slot[b:b + 1], table, alone, n_q, n_kv, hd,
+                                           6, None, scale, chunk, max_chunks, scratch, counters)
+            assert torch.equal(alone[0], out[b]), (chunk, b)

@@ -1,6 +1,6 @@
-"""One layer at Llama-3.1-8B sizes (width 4096, 32/8 heads of 128, feed-forward 14336, a
-vocabulary of 128256) with random weights against the plain implementation: the shapes the
-benchmark times, checked for what they compute.  A prompt of 140 tokens in one step (the
+"""Llama-3.1-8B sizes (width 4096, 32/8 heads of 128, feed-forward 14336, a vocabulary of 128256)
+with random weights against the plain implementation: the shapes the benchmark times, checked for
+what they compute; one layer in detail, and all 32 layers in every batching.  A prompt of 140 tokens in one step (the
 tcgen05 GEMM and attention in bfloat16), then tokens one by one (the decode projections and
 attention), in float32 and in bfloat16.  Logits are compared on 2,000 vocabulary rows, so that
 the plain side never multiplies by the whole head."""
@@ -87,3 +87,75 @@ def test_a_batch_of_twenty_at_8b_sizes():
         for i, (r, c) in enumerate(zip(refs, cut)):
             assert np.abs(got[i] - r[c + step]).max() < tol, (step, i)
     model.check_errors()
+
+
+def test_the_whole_model_at_8b_sizes_in_every_batching():
+    """All 32 layers at Llama-3.1-8B sizes: the depth and width the benchmark times.  The float32
+    path against the plain implementation, streamed layer by layer so that the host holds one layer
+    in float64 at a time: a 24-token prompt whole; 16 tokens in one step and the last 8 one by one;
+    three unequal prompts as one batch and two decode steps of it.  Every logit compared is within
+    1e-4 on 2,000 vocabulary rows.  Then the bfloat16 path at the same places against that float32."""
+    from supersonic_b200.config import preset_config
+    from supersonic_b200.engine import Model, StepEntry
+    from supersonic_b200.weights import RandomWeightStore
+    cfg = preset_config("llama3.1-8b")
+    L = cfg.num_hidden_layers
+    store = RandomWeightStore(cfg, seed=7, device="cuda:0", std=0.02, norm_jitter=0.1)
+    pc = cfg.to_dict()
+    rng = np.random.default_rng(15)
+    seqs = [rng.integers(0, cfg.vocab_size, n).tolist() for n in (24, 7, 15)]
+    rows = np.sort(rng.choice(cfg.vocab_size, 2000, replace=False))
+    dev_rows = torch.as_tensor(rows, device="cuda:0")
+
+    def host(name, index=None):
+        t = store.get(name)
+        return (t if index is None else t[torch.as_tensor(index, device=t.device)]).double().cpu().numpy()
+
+    hs = [host("model.embed_tokens.weight", t) for t in seqs]
+    tables = [pl.rope_tables(pc, len(t)) for t in seqs]
+    for n in range(L):
+        pw = {name: host(name) for name in store.names() if name.startswith(f"model.layers.{n}.")}
+        hs = [pl.block(h, pw, n, pc, cos, sin) for h, (cos, sin) in zip(hs, tables)]
+        del pw
+    norm_w, head = host("model.norm.weight"), host("lm_head.weight", rows)
+    refs = [pl.rms_norm(h, norm_w, pc["rms_norm_eps"]) @ head.T for h in hs]
+    scale = max(np.abs(r).max() for r in refs)
+
+    def run(dtype):
+        """{(sequence, position, schedule): logits row}"""
+        m = Model.from_config(cfg, store, dtype=dtype, device="cuda:0", max_tokens=512)
+        out = {}
+        take = lambda t: t[:, dev_rows].double().cpu().numpy()
+        a = seqs[0]
+        s = m.open_sequence()                                   # whole
+        for p, row in enumerate(take(m.step([StepEntry(s, a, range(24))]))):
+            out[(0, p, "whole")] = row
+        m.close_sequence(s)
+        s = m.open_sequence()                                   # 16 at once, 8 one by one (in the slot just freed)
+        out[(0, 15, "cut")] = take(m.step([StepEntry(s, a[:16], [15])]))[0]
+        for p in range(16, 24):
+            out[(0, p, "cut")] = take(m.step([StepEntry(s, [a[p]], [0])]))[0]
+        m.close_sequence(s)
+        slots = [m.open_sequence() for _ in seqs]               # three unequal prompts together
+        cut = [len(t) - 2 for t in seqs]
+        got = take(m.step([StepEntry(sl, t[:c], [c - 1]) for sl, t, c in zip(slots, seqs, cut)]))
+        for i, c in enumerate(cut):
+            out[(i, c - 1, "batch")] = got[i]
+        for step in range(2):
+            got = take(m.step([StepEntry(sl, [t[c + step]], [0]) for sl, t, c in zip(slots, seqs, cut)]))
+            for i, c in enumerate(cut):
+                out[(i, c + step, "batch")] = got[i]
+        m.check_errors()
+        m.cache.check()
+        del m
+        torch.cuda.empty_cache()
+        return out
+
+    f32 = run("float32")
+    assert len(f32) == 24 + 9 + 9
+    for (i, p, how), row in f32.items():
+        err = np.abs(row - refs[i][p]).max()
+        assert err <= 1e-4, f"float32, sequence {i}, position {p}, {how}: {err:.2e}"
+    bf16 = run("bfloat16")
+    for key, row in bf16.items():
+        assert np.abs(row - f32[key]).max() <= 2e-2 * scale, f"bfloat16 {key}"
