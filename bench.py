@@ -345,6 +345,8 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
     ap.add_argument("--skip-workloads", action="store_true", help="leave out the 3B and 1B ragged workloads")
+    ap.add_argument("--deterministic", action="store_true",
+                    help="time the bfloat16 path without float atomics and with one kernel choice whatever the batch")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -369,7 +371,8 @@ def main():
     t0 = time.time()
     store = RandomWeightStore(cfg, seed=2, device="cuda:0", std=0.02, norm_jitter=0.0)
     model = Model.from_config(cfg, store, dtype="bfloat16", device="cuda:0",
-                              max_tokens=args.slots * args.context, max_seq_tokens=args.context)
+                              max_tokens=args.slots * args.context, max_seq_tokens=args.context,
+                              deterministic=args.deterministic)
     torch.cuda.synchronize()
     print(f"[bench] model built in {time.time() - t0:.1f} s, "
           f"{torch.cuda.memory_allocated() / 2**30:.1f} GiB on the device", file=sys.stderr)
@@ -414,7 +417,8 @@ def main():
                    "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "global_batch": args.batch, "seq_len": args.prompt_len, "context_per_slot": args.context,
                    "slots": args.slots, "prefill_tokens": args.prefill_tokens, "parallelism": "none",
-                   "l2": "inputs exceed L2 (15 GB of weights per step)", "peaks": pk_src},
+                   "l2": "inputs exceed L2 (15 GB of weights per step)", "peaks": pk_src,
+                   "deterministic": bool(args.deterministic)},
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": 3 * 4 * args.batch,
                 "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": kernels_per_step * args.steps,

@@ -569,6 +569,43 @@ static inline int adm_sm_count() {
     return sms;
 }
 
+// Blocks of the kernel that are resident at once on the current device (what the persistent grid is
+// sized to): as many per SM as registers and shared memory allow, asked of the runtime once per case.
+// The kernel's limit on dynamic shared memory only ever grows (a launch needs at most what was set).
+template <int HD, bool FUSE>
+static inline cudaError_t adm_ensure_smem(int smem_bytes) {
+    static int allowed = 0;
+    if (smem_bytes <= allowed) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, FUSE>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e == cudaSuccess) allowed = smem_bytes;
+    return e;
+}
+
+template <int HD, bool FUSE>
+static inline int adm_blocks_per_sm(int smem_bytes) {
+    auto kern = attention_decode_mma_kernel<HD, FUSE>;
+    if (adm_ensure_smem<HD, FUSE>(smem_bytes) != cudaSuccess) return 0;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, ADM_THREADS, (size_t)smem_bytes) != cudaSuccess) return 0;
+    return n;
+}
+
+static inline long long adm_resident_blocks(int head_dim, bool fuse, int group, int n_seqs) {
+    static int cached[2][2][ADM_ROWS + 1][4];                    // [head size][fuse][group][batch class]
+    const int cls = n_seqs <= 64 ? 0 : (n_seqs <= 256 ? 1 : (n_seqs <= 512 ? 2 : 3));
+    const int cls_seqs = cls == 0 ? 64 : (cls == 1 ? 256 : (cls == 2 ? 512 : ADM_MAX_SEQS));
+    if (group < 1 || group > ADM_ROWS || (head_dim != 64 && head_dim != 128)) return 0;
+    int& per_sm = cached[head_dim == 128][fuse ? 1 : 0][group][cls];
+    if (per_sm == 0) {
+        const int smem = adm_smem_bytes(head_dim, group, cls_seqs);
+        per_sm = head_dim == 64 ? (fuse ? adm_blocks_per_sm<64, true>(smem) : adm_blocks_per_sm<64, false>(smem))
+                                : (fuse ? adm_blocks_per_sm<128, true>(smem) : adm_blocks_per_sm<128, false>(smem));
+        if (per_sm <= 0) per_sm = -1;
+    }
+    return per_sm > 0 ? (long long)per_sm * adm_sm_count() : 0;
+}
+
 // chunk_pages: pages per chunk (>= 1); max_chunks: the most chunks a sequence is cut into (it sizes
 // the scratch): a sequence that would need more gets max_chunks larger ones.
 static inline int adm_launch(const void* q, int ldq, const void* k_cache, const void* v_cache, const int* pos,
@@ -585,18 +622,14 @@ static inline int adm_launch(const void* q, int ldq, const void* k_cache, const 
     if (fuse && !sin_t) return SSB_ERR_BAD_SIZE;
     const float scale_log2 = scale * 1.4426950408889634f;
     const long long items = (long long)n_seqs * n_kv * max_chunks;
-    const int blocks = (int)(items < 2LL * adm_sm_count() ? items : 2LL * adm_sm_count());
-    dim3 grid(blocks);
+    const long long resident = adm_resident_blocks(head_dim, fuse, n_q / n_kv, n_seqs);
+    if (resident <= 0) return SSB_ERR_UNSUPPORTED;
+    dim3 grid((unsigned)(items < resident ? items : resident));
     int rc = 0;
 #define SSB_ADM(HD_, FUSE_) do { \
         const int smem_bytes = adm_smem_bytes(HD_, n_q / n_kv, n_seqs); \
-        static int configured = 0; \
-        if (smem_bytes > configured) { \
-            cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD_, FUSE_>, \
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes); \
-            if (e != cudaSuccess) return (int)e; \
-            configured = smem_bytes; \
-        } \
+        cudaError_t e = adm_ensure_smem<HD_, FUSE_>(smem_bytes); \
+        if (e != cudaSuccess) return (int)e; \
         rc = ssb_launch(attention_decode_mma_kernel<HD_, FUSE_>, grid, dim3(ADM_THREADS), (size_t)smem_bytes, stream, pdl, \
                         (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
                         (bf16*)out, ldo, n_seqs, n_q, n_kv, window, scale_log2, chunk_pages, max_chunks, scratch, \

@@ -238,6 +238,13 @@ SSB_API int ssb_attention_decode_chunked_ok(int n_seqs, int n_q, int n_kv, int h
     return page_shift == 6 && n_seqs <= ADM_MAX_SEQS && adm_supported(n_q, n_kv, head_dim, ldq, false);
 }
 
+// Blocks of the kernel that the device holds at once for this case (its persistent grid): callers size
+// their chunks by it.
+SSB_API long long ssb_attention_decode_chunked_blocks(int n_seqs, int n_q, int n_kv, int head_dim, int fused) {
+    if (n_kv <= 0 || n_q % n_kv) return 0;
+    return adm_resident_blocks(head_dim, fused != 0, n_q / n_kv, n_seqs);
+}
+
 SSB_API long long ssb_attention_decode_chunked_scratch_floats(int n_seqs, int n_q, int head_dim, int max_chunks) {
     return adm_scratch_floats(n_seqs, n_q, head_dim, max_chunks);
 }

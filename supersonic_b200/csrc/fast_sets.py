@@ -28,13 +28,15 @@ class FastKernels(PlainKernels):
 
     def __init__(self, pdl: bool = True, deterministic: bool = False):
         self.pdl = pdl           # decode kernels launch as programmatic dependents of their predecessors
-        # True: no float atomics anywhere, so that two runs of the same batch give the same bits (and a
-        # sampled sequence is reproducible from its seed); the shares of a projection whose K range
-        # is split over blocks then meet through scratch in a fixed order, and short prompts do not
-        # split K at all
+        # True: no float atomics and one choice of kernel whatever the batch, so that a sequence's
+        # logits are the same bits in every run and in every batch (and a sampled sequence is
+        # reproducible from its seed): projections never split K, prompts always take the tcgen05
+        # attention, the decode attention cuts a sequence's keys in fixed chunks
         self.deterministic = deterministic
         self.fuse_rope = True    # decode attention rotates q/k and appends to the cache itself
-        self.fuse_rope_prefill = True   # the prompt's q/k/v projection does so in its epilogue
+        # the prompt's q/k/v projection does so in its epilogue, if the step is large enough for that
+        # kernel: not in deterministic mode, where a prompt takes one path whatever accompanies it
+        self.fuse_rope_prefill = not deterministic
         self._scratch: Dict[str, torch.Tensor] = {}
         self._retired = []      # outgrown buffers stay alive: captured graphs still point at them
 
@@ -68,20 +70,16 @@ class FastKernels(PlainKernels):
         x = as_tensor(x)
         if (out.dtype == torch.float32 or not accumulate) and ops.gemm_tc_ok(x, weight, out):
             n, k = weight.shape
-            if rows <= 64 and accumulate:
-                # weights on the M side, K split over blocks that add with float atomics, or (deterministic)
-                # whose shares the last block of a row tile sums in split order
-                splits = ops.gemv_tc_splits(n, k)
-                partials, counters = self._split_scratch(rows, n, splits, out.device) if self.deterministic else (None, None)
-                ops.gemv_tc(x, weight, out, ops.TC_ACCUMULATE, splits=splits, partials=partials, counters=counters,
-                            pdl=self.pdl)
+            if self.deterministic:
+                # one kernel for every row count, K never split: a row's sums are taken in the same order
+                # whatever else is in the step (decode steps pay for it: few blocks stream the weights)
+                ops.gemm_tc(x, weight, out, ops.TC_ACCUMULATE if accumulate else ops.TC_STORE,
+                            tile_n=ops.TC_TILE_PAIR if self._pair_tiles(rows, n) else self._tile_n(rows, n))
+            elif rows <= 64 and accumulate:
+                # weights on the M side, K split over blocks that add with float atomics
+                ops.gemv_tc(x, weight, out, ops.TC_ACCUMULATE, splits=ops.gemv_tc_splits(n, k), pdl=self.pdl)
             elif rows <= 64 and n >= 16384:
                 ops.gemv_tc(x, weight, out, ops.TC_STORE, pdl=self.pdl)
-            elif rows <= 64 and self.deterministic:
-                splits = ops.gemv_tc_splits(n, k)
-                partials, counters = self._split_scratch(rows, n, splits, out.device)
-                ops.gemv_tc(x, weight, out, ops.TC_STORE, splits=splits, partials=partials, counters=counters,
-                            pdl=self.pdl)
             elif rows <= 64 and out.dtype == torch.bfloat16 and n % 8 == 0 and out.stride(0) % 8 == 0:
                 # too few row tiles for the SMs (48 for the 8B query/key/value projection): K is split
                 # over blocks that add with float atomics into a float32 scratch that is zero between
@@ -96,7 +94,7 @@ class FastKernels(PlainKernels):
                 # that add with float atomics, into the residual or, for a stored result, into the
                 # zeroed scratch that round_and_clear turns into bfloat16 (as for decode above)
                 tile_n = self._tile_n(rows, n)
-                splits = 1 if self.deterministic else self._gemm_splits(rows, n, k, tile_n)
+                splits = self._gemm_splits(rows, n, k, tile_n)
                 if splits == 1 and self._pair_tiles(rows, n):
                     tile_n = ops.TC_TILE_PAIR
                 if splits > 1 and accumulate:
@@ -112,14 +110,6 @@ class FastKernels(PlainKernels):
             if self._skinny(x, weight, out, ops.SG_ACCUMULATE if accumulate else ops.SG_STORE):
                 return
         ops.gemm_nt_plain(x, weight, out, accumulate)
-
-    def _split_scratch(self, rows: int, n: int, splits: int, device):
-        """Scratch of the ordered sum of a split projection (partial tiles, zeroed arrival counters)."""
-        if splits <= 1:
-            return None, None
-        nf, nc = ops.gemv_tc_scratch(rows, n, splits)
-        return (self._buffer("gemv_partials", nf, torch.float32, device),
-                self._buffer("gemv_counters", nc, torch.int32, device, zero=True))
 
     @staticmethod
     def _gemm_splits(rows: int, n: int, k: int, tile_n: int) -> int:
@@ -156,7 +146,7 @@ class FastKernels(PlainKernels):
         if layout == "interleaved":
             xt = as_tensor(x)
             if w_gate_up.shape[0] % 16 == 0 and ops.gemm_tc_ok(xt, w_gate_up, out):
-                if rows <= 64:
+                if rows <= 64 and not self.deterministic:
                     ops.gemv_tc(xt, w_gate_up, out, ops.TC_SWIGLU, pdl=self.pdl)
                 else:
                     n2 = w_gate_up.shape[0]
@@ -177,17 +167,17 @@ class FastKernels(PlainKernels):
             self._scratch[name] = t
         return t
 
-    def _chunk_pages(self, n_seqs: int, n_kv: int, pages: int) -> int:
+    def _chunk_pages(self, n_seqs: int, n_kv: int, pages: int, blocks: int) -> int:
         """Pages per chunk of the tensor-core decode attention for a batch whose longest sequence spans
         up to ``pages``.  A work item has a fixed cost of about six pages' worth of streaming (its
         query, the merge of its warps, its partial result), so items are as large as keeps every
-        resident block busy: the batch's pages shared out over two blocks per SM, between 2 and
+        resident block busy: the batch's pages shared out over the ``blocks`` the device holds, between 2 and
         MAX_CHUNK_PAGES (measured at Llama-3.1-8B sizes: 64 x 520 tokens 31 us unsplit against 54 us in
         two chunks; 8 x 8,192 tokens 49 us in chunks of 32 pages against 94 us in chunks of 8).  In
         deterministic mode the figure is a constant, so that a sequence is cut the same way in every batch."""
         if self.deterministic:
             return DETERMINISTIC_CHUNK_PAGES
-        share = -(-n_seqs * n_kv * pages // (2 * ops.sm_count()))
+        share = -(-n_seqs * n_kv * pages // max(blocks, 1))
         return max(2 if pages > 2 else 1, min(MAX_CHUNK_PAGES, share))
 
     def _decode_attention(self, q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim,
@@ -201,7 +191,8 @@ class FastKernels(PlainKernels):
             # tensor-core kernel on a persistent grid (beside the mma.sync skinny GEMM it made a step
             # slower: the two compete for the SM's L1/shared memory; beside the tcgen05 projections it
             # is the faster choice at every batch size: batch 16: 4.24 to 3.57 ms a step)
-            chunk = self._chunk_pages(batch.n_seqs, n_kv, pages)
+            chunk = self._chunk_pages(batch.n_seqs, n_kv, pages, ops.attention_decode_chunked_blocks(
+                batch.n_seqs, n_q, n_kv, head_dim, cos is not None))
             max_chunks = -(-pages // chunk)
             scratch = counters = None
             if max_chunks > 1:
@@ -275,7 +266,7 @@ class FastKernels(PlainKernels):
             self._decode_attention(q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim,
                                    page_shift, window, scale)
             return
-        if not batch.is_decode and batch.max_new >= TC_ATTENTION_MIN_NEW and k_cache.is_contiguous() \
+        if not batch.is_decode and (batch.max_new >= TC_ATTENTION_MIN_NEW or self.deterministic) and k_cache.is_contiguous() \
                 and v_cache.is_contiguous() and ops.attention_prefill_tc_ok(q, out, head_dim, page_shift):
             ops.attention_prefill_tc(q, k_cache, v_cache, batch.cu_new, batch.seq_start, batch.seq_slot,
                                      page_table, out, batch.max_new, n_q, n_kv, head_dim, page_shift, window, scale)

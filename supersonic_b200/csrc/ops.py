@@ -335,6 +335,22 @@ def attention_decode_chunked_ok(n_seqs: int, n_q: int, n_kv: int, head_dim: int,
         c_int(n_seqs), c_int(n_q), c_int(n_kv), c_int(head_dim), c_int(ldq), c_int(page_shift)))
 
 
+_chunked_blocks = {}
+
+
+def attention_decode_chunked_blocks(n_seqs: int, n_q: int, n_kv: int, head_dim: int, fused: bool) -> int:
+    """Blocks of the tensor-core decode attention that the current device holds at once for this case
+    (the size of its persistent grid)."""
+    key = (torch.cuda.current_device(), min(n_seqs, 1024) > 64, min(n_seqs, 1024) > 256, n_seqs > 512, n_q, n_kv,
+           head_dim, bool(fused))
+    if key not in _chunked_blocks:
+        lib = load_library("decode_ops")
+        lib.ssb_attention_decode_chunked_blocks.restype = c_longlong
+        _chunked_blocks[key] = int(lib.ssb_attention_decode_chunked_blocks(
+            c_int(n_seqs), c_int(n_q), c_int(n_kv), c_int(head_dim), c_int(1 if fused else 0)))
+    return _chunked_blocks[key]
+
+
 def attention_decode_chunked_scratch(n_seqs: int, n_q: int, n_kv: int, head_dim: int, max_chunks: int):
     """(float32 elements of scratch, int32 counters) a launch needs; counters start at zero."""
     lib = load_library("decode_ops")

@@ -92,7 +92,10 @@ SSB_API int ssb_rmsnorm(const float* x, const int* rows, const void* w, int w_dt
 }
 
 // ---------------------------------------------------------------------------------------
-// C[m, n] (+)= sum_k A[m, k] * W[n, k]; 64x64 tile, 16-wide k steps, float32 FMA in k order
+// C[m, n] (+)= sum_k A[m, k] * W[n, k]; 64x64 tile, 16-wide k steps.  float32 throughout, in a
+// fixed order: the 16 products of a k step are summed with FMAs, and the steps' sums are added
+// with compensation (Kahan), so that the rounding error of a long row (14,336 terms in a
+// feed-forward) stays at a few units in the last place instead of growing with its length.
 // ---------------------------------------------------------------------------------------
 template <typename TA, typename TC, bool ACCUMULATE>
 __global__ void __launch_bounds__(256)
@@ -104,11 +107,11 @@ gemm_nt_plain_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W
     const int tid = threadIdx.x;
     const int tx = tid % 16, ty = tid / 16;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-    float acc[4][4];
+    float acc[4][4], lost[4][4];          // running sums and what their last additions rounded away
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+        for (int j = 0; j < 4; ++j) { acc[i][j] = 0.f; lost[i][j] = 0.f; }
 
     for (int k0 = 0; k0 < K; k0 += BK) {
 #pragma unroll
@@ -121,6 +124,11 @@ gemm_nt_plain_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W
             Ws[c][r] = (n < N && k < K) ? ssb_to_float(W[(size_t)n * ldw + k]) : 0.f;
         }
         __syncthreads();
+        float part[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
             float a[4], b[4];
@@ -131,8 +139,17 @@ gemm_nt_plain_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) part[i][j] = fmaf(a[i], b[j], part[i][j]);
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float y = __fsub_rn(part[i][j], lost[i][j]);       // explicit roundings: nothing is re-associated
+                const float t = __fadd_rn(acc[i][j], y);
+                lost[i][j] = __fsub_rn(__fsub_rn(t, acc[i][j]), y);
+                acc[i][j] = t;
+            }
         __syncthreads();
     }
 #pragma unroll

@@ -94,7 +94,8 @@ def test_the_whole_model_at_8b_sizes_in_every_batching():
     path against the plain implementation, streamed layer by layer so that the host holds one layer
     in float64 at a time: a 24-token prompt whole; 16 tokens in one step and the last 8 one by one;
     three unequal prompts as one batch and two decode steps of it.  Every logit compared is within
-    1e-4 on 2,000 vocabulary rows.  Then the bfloat16 path at the same places against that float32."""
+    1e-4 on 2,000 vocabulary rows.  Then the bfloat16 path at the same places against that float32,
+    within the rounding noise of 32 layers."""
     from supersonic_b200.config import preset_config
     from supersonic_b200.engine import Model, StepEntry
     from supersonic_b200.weights import RandomWeightStore
@@ -156,6 +157,11 @@ def test_the_whole_model_at_8b_sizes_in_every_batching():
     for (i, p, how), row in f32.items():
         err = np.abs(row - refs[i][p]).max()
         assert err <= 1e-4, f"float32, sequence {i}, position {p}, {how}: {err:.2e}"
+    # bfloat16 at this depth: about six roundings of the activations a layer leave a noise of
+    # sqrt(6 * 32) * 2^-9 = 2.7 % of a row's spread; a fault (a wrong page, position or head) leaves
+    # about 100 %.  Per row: the error's root mean square against the spread of the float32 logits.
     bf16 = run("bfloat16")
     for key, row in bf16.items():
-        assert np.abs(row - f32[key]).max() <= 2e-2 * scale, f"bfloat16 {key}"
+        rel = np.sqrt(np.mean((row - f32[key]) ** 2)) / f32[key].std()
+        assert rel < 0.05, f"bfloat16 {key}: {rel:.3f}"
+        assert np.abs(row - f32[key]).max() <= 0.05 * scale, f"bfloat16 {key}"
