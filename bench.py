@@ -180,8 +180,9 @@ def ragged_workload(preset, n_prompts, lo, hi, new_tokens, temperature, pk, seed
                                max_tokens=sum(-(-(n + new_tokens) // 64) * 64 for n in lengths))
     model = eng.model
     prompts = [torch.randint(0, model.vocab_size, (n,), generator=g).tolist() for n in lengths]
-    eng.generate([p[:8] for p in prompts[:2]], max_new_tokens=4, temperature=temperature, ignore_eos=True,
-                 batch_size=2)                                      # compiles nothing new; warms the allocator
+    # once untimed: decode steps replay one captured graph per (batch size, context bucket), and capturing
+    # them (a tenth of a second each) is a cost of a server's first minutes, not of a step
+    eng.generate(prompts, max_new_tokens=new_tokens, temperature=temperature, ignore_eos=True, batch_size=n_prompts)
     eng.generator.stats = type(eng.generator.stats)()
     eng.generate(prompts, max_new_tokens=new_tokens, temperature=temperature, ignore_eos=True, batch_size=n_prompts)
     st = eng.generator.stats

@@ -112,11 +112,11 @@ class FastKernels(PlainKernels):
         ops.gemm_nt_plain(x, weight, out, accumulate)
 
     @staticmethod
-    def _gemm_splits(rows: int, n: int, k: int, tile_n: int) -> int:
+    def _gemm_splits(rows: int, n: int, k: int, tile_n: int, sms: Optional[int] = None) -> int:
         """Parts a tile's K range is cut into so that the work items fill the SMs once (one block
         per SM walks them); at least 8 k-blocks (512 columns) a part; 1 when the tiles alone do."""
         tiles = ((rows + 127) // 128) * ((n + tile_n - 1) // tile_n)
-        return max(1, min(ops.sm_count() // tiles, (k // 64) // 8, 16))
+        return max(1, min((sms or ops.sm_count()) // tiles, (k // 64) // 8, 16))
 
     @staticmethod
     def _pair_tiles(rows: int, n: int) -> bool:

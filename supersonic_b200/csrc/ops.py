@@ -460,6 +460,53 @@ def fetch_with_errors(values: torch.Tensor) -> list:
     return out
 
 
+class Fetch:
+    """An int32 device tensor on its way to the host (:func:`start_fetch`)."""
+
+    __slots__ = ("buf", "n", "event", "with_word", "device")
+
+
+_fetch_ring = {}
+
+
+def start_fetch(values: torch.Tensor) -> Fetch:
+    """Begin copying the int32 ``values`` (and the device's error word, if a kernel that could set it
+    ran since the last look) to pinned host memory on the current stream; nothing waits.  The ring
+    holds four copies in flight per device."""
+    global _tc_unchecked
+    dev = values.device
+    n = values.numel()
+    ring = _fetch_ring.setdefault(dev, {"bufs": [None] * 4, "turn": 0})
+    i = ring["turn"]
+    ring["turn"] = (i + 1) % 4
+    buf = ring["bufs"][i]
+    if buf is None or buf.numel() < n + 1:
+        buf = ring["bufs"][i] = torch.empty(max(n + 1, 4097), dtype=torch.int32, pin_memory=True)
+    f = Fetch()
+    f.buf, f.n, f.device = buf, n, dev
+    f.with_word = bool(_tc_unchecked) and dev in _tc_error_words
+    buf[:n].copy_(values.view(-1), non_blocking=True)
+    if f.with_word:
+        buf[n:n + 1].copy_(_tc_error_words[dev], non_blocking=True)
+        _tc_unchecked = 0
+    f.event = torch.cuda.Event()
+    f.event.record()
+    return f
+
+
+def finish_fetch(f: Fetch) -> list:
+    """Wait for the copy and return the values; raises like ``check_device_errors``."""
+    f.event.synchronize()
+    out = f.buf[:f.n].tolist()
+    if f.with_word:
+        code = int(f.buf[f.n])
+        if code:
+            _tc_error_words[f.device].zero_()
+            raise KernelError(f"tcgen05 kernel: a bounded wait ran out in {_TC_ERRORS.get(code, code)}; "
+                              "the result of that launch is invalid")
+    return out
+
+
 def tc_wait_probe(device="cuda:0") -> None:
     """Launch a block whose only wait can never be satisfied: after about a second it gives up and
     records that in the device's error word, which ``check_device_errors`` then reports."""

@@ -101,9 +101,34 @@ def plan_chunks(counts: Sequence[int], budget: int) -> List[List[tuple]]:
     return [c for c in chunks if c]
 
 
-def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], device,
-              vocab_size: Optional[int] = None) -> StepBatch:
-    """Lay the entries out back to back and move the index arrays to ``device`` in one copy."""
+@dataclass
+class PackedStep:
+    """A step's index arrays as one host array (tokens, positions, slots per token; slot, start per
+    sequence; the offsets of the sequences; the wanted rows) and the sizes that cut it up again."""
+
+    flat: np.ndarray               # int32
+    n_tokens: int
+    n_seqs: int
+    n_want: int
+    max_new: int
+    max_total: int
+    slots: List[int]
+    starts: List[int]
+    counts: List[int]
+
+    @property
+    def kv_pages(self) -> int:
+        return decode_pages_bucket(self.max_total)
+
+    @property
+    def shape_key(self):
+        """What a captured prompt step is valid for: kernels size their grids from these."""
+        return (self.n_tokens, self.n_seqs, self.n_want, self.max_new, self.kv_pages)
+
+
+def pack_entries(entries: Sequence[StepEntry], starts: Sequence[int],
+                 vocab_size: Optional[int] = None) -> PackedStep:
+    """Lay the entries out back to back on the host; every misuse raises before anything runs."""
     if not entries:
         raise ValueError("a step needs at least one entry")
     tok_parts, pos_parts, slot_parts = [], [], []
@@ -133,15 +158,18 @@ def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], device,
             raise ValueError(f"token ids {bad[:8].tolist()} are outside the vocabulary of {vocab_size}")
     if len(set(slots)) != len(slots):
         raise ValueError("a slot appears twice in one step")
-    T, B, W = int(tokens.shape[0]), len(slots), len(want)
-    longest = max(s + c for s, c in zip(starts, counts))
     flat = np.concatenate(tok_parts + pos_parts + slot_parts + [
         np.asarray(slots + list(starts) + cu + want, dtype=np.int64)]).astype(np.int32)
-    host = torch.from_numpy(flat)
-    dev = torch.device(device)
-    if dev.type == "cuda":
-        host = host.pin_memory()
-    buf = host.to(dev, non_blocking=True)
+    return PackedStep(flat=flat, n_tokens=int(tokens.shape[0]), n_seqs=len(slots), n_want=len(want),
+                      max_new=max(counts), max_total=max(s + c for s, c in zip(starts, counts)),
+                      slots=slots, starts=list(starts), counts=counts)
+
+
+def batch_over(buf: torch.Tensor, packed: PackedStep, captured: bool = False) -> StepBatch:
+    """The :class:`StepBatch` whose device tensors are views of ``buf`` (the packed array on the
+    device).  ``captured``: the batch of a step that is recorded once and replayed for other
+    sequences of the same sizes, so it carries no host lists."""
+    T, B, W = packed.n_tokens, packed.n_seqs, packed.n_want
     o = [0]
 
     def take(n):
@@ -151,9 +179,21 @@ def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], device,
     token_ids, pos_t, slot_t = take(T), take(T), take(T)
     seq_slot, seq_start, cu_new, want_rows = take(B), take(B), take(B + 1), take(W)
     return StepBatch(
-        n_tokens=T, n_seqs=B, max_new=max(counts),
-        max_total=longest, kv_pages=decode_pages_bucket(longest),
-        is_decode=all(c == 1 for c in counts),
+        n_tokens=T, n_seqs=B, max_new=packed.max_new, max_total=packed.max_total, kv_pages=packed.kv_pages,
+        is_decode=all(c == 1 for c in packed.counts),
         token_ids=token_ids, pos=pos_t, slot_of_token=slot_t, seq_slot=seq_slot, seq_start=seq_start,
         cu_new=cu_new, want_rows=want_rows, n_want=W,
-        host_slots=slots, host_starts=list(starts), host_counts=counts)
+        host_slots=NotOnHost("host_slots") if captured else packed.slots,
+        host_starts=NotOnHost("host_starts") if captured else packed.starts,
+        host_counts=NotOnHost("host_counts") if captured else packed.counts)
+
+
+def pack_step(entries: Sequence[StepEntry], starts: Sequence[int], device,
+              vocab_size: Optional[int] = None) -> StepBatch:
+    """Lay the entries out back to back and move the index arrays to ``device`` in one copy."""
+    packed = pack_entries(entries, starts, vocab_size)
+    host = torch.from_numpy(packed.flat)
+    dev = torch.device(device)
+    if dev.type == "cuda":
+        host = host.pin_memory()
+    return batch_over(host.to(dev, non_blocking=True), packed)

@@ -121,6 +121,11 @@ class Generator:
 
     def _run_batch(self, batch, prompts, results, max_new_tokens, sampling, stop_ids,
                    include_stop_token, on_step):
+        """One batch from its prompts to its last token.  A model that can take a step's tokens from
+        the device (``feeds_device_tokens``, ``step_ahead``) is driven one step ahead of the host."""
+        if max_new_tokens > 1 and self.stage_timings is None and getattr(self.model, "feeds_device_tokens", False):
+            return self._run_batch_ahead(batch, prompts, results, max_new_tokens, sampling, stop_ids,
+                                         include_stop_token, on_step)
         model = self.model
         slot_of = {r: model.open_sequence(request_seed(sampling.sampling_seed, r)) for r in batch}
         live = list(batch)
@@ -136,7 +141,7 @@ class Generator:
                 if max_new_tokens <= 0:
                     if getattr(getattr(model, "device", None), "type", "") == "cuda":
                         torch.cuda.synchronize(model.device)     # nothing is fetched: wait for the prompt step itself
-                    self._account(first, n_step_tokens, t0, None)
+                    self._account(first, n_step_tokens, time.perf_counter() - t0, None)
                     break
                 if slots is None:                        # the live set changed (or this is the first step)
                     slots = torch.tensor([slot_of[r] for r in live], dtype=torch.int32).to(
@@ -152,7 +157,7 @@ class Generator:
                     tokens = model.fetch(sampled)        # kernel errors are looked at in the same wait
                 else:
                     tokens = sampled.to("cpu").tolist()
-                self._account(first, n_step_tokens, t0, ev if timed else None)
+                self._account(first, n_step_tokens, time.perf_counter() - t0, ev if timed else None)
                 first = False
                 if on_step:
                     on_step(live, tokens)
@@ -175,8 +180,71 @@ class Generator:
             for slot in slot_of.values():
                 model.close_sequence(slot)
 
-    def _account(self, prompt_step: bool, n_tokens: int, t0: float, sampling_events) -> None:
-        dt = time.perf_counter() - t0
+    def _run_batch_ahead(self, batch, prompts, results, max_new_tokens, sampling, stop_ids,
+                         include_stop_token, on_step):
+        """The same batch with the device kept one step ahead: step k + 1 is launched from the tokens
+        step k sampled while those are still on their way to the host; the host then reads them,
+        applies the stop rules and prepares step k + 2.  A sequence that ends at its token budget is
+        known beforehand and is not stepped again; one that ends at a stop token has been stepped once
+        more than needed by then: that step's token is dropped (it wrote one key and value into a slot
+        that is given back right after)."""
+        model = self.model
+        slot_of = {r: model.open_sequence(request_seed(sampling.sampling_seed, r)) for r in batch}
+        device = model.device
+
+        def slots_tensor(rows):
+            return torch.tensor([slot_of[r] for r in rows], dtype=torch.int32).to(device, non_blocking=True)
+        try:
+            rows = list(batch)                           # the requests whose tokens ``sampled`` holds, row by row
+            last = time.perf_counter()
+            logits = model.step([StepEntry(slot_of[r], prompts[r], [len(prompts[r]) - 1]) for r in rows])
+            self.steps_run += 1
+            n_step_tokens = sum(len(prompts[r]) for r in rows)
+            slots = slots_tensor(rows)
+            sampled = self.sampler(logits, slots, sampling)
+            handle = model.start_fetch(sampled)
+            first = True
+            while True:
+                # whoever has budget for more than the token that is on its way is stepped again now
+                ahead = [r for r in rows if r in slot_of and len(results[r].tokens) + 1 < max_new_tokens]
+                if ahead:
+                    if ahead == rows:
+                        fed = sampled
+                    else:
+                        at = {r: i for i, r in enumerate(rows)}
+                        index = torch.tensor([at[r] for r in ahead], dtype=torch.int64).to(device, non_blocking=True)
+                        fed = sampled.index_select(0, index)
+                        slots = slots_tensor(ahead)
+                    logits = model.step_ahead([slot_of[r] for r in ahead], fed)
+                    self.steps_run += 1
+                    sampled_ahead = self.sampler(logits, slots, sampling)
+                    handle_ahead = model.start_fetch(sampled_ahead)
+                tokens = model.finish_fetch(handle)      # kernel errors are looked at in the same wait
+                now = time.perf_counter()
+                self._account(first, n_step_tokens, now - last, None)
+                last, first = now, False
+                alive = [(r, t) for r, t in zip(rows, tokens) if r in slot_of]     # not: ended a step ago at a stop token
+                if on_step:
+                    on_step([r for r, _ in alive], [t for _, t in alive])
+                for r, tok in alive:
+                    res = results[r]
+                    why = finished(tok, len(res.tokens) + 1, max_new_tokens, stop_ids)
+                    if why != "stop" or include_stop_token:
+                        res.tokens.append(tok)
+                    if why:
+                        res.finish_reason = why
+                        model.close_sequence(slot_of.pop(r))
+                if not ahead:
+                    break
+                rows, sampled, handle, n_step_tokens = ahead, sampled_ahead, handle_ahead, len(ahead)
+                if not any(r in slot_of for r in rows):  # all of them ended at stop tokens meanwhile
+                    model.finish_fetch(handle)
+                    break
+        finally:
+            for slot in slot_of.values():
+                model.close_sequence(slot)
+
+    def _account(self, prompt_step: bool, n_tokens: int, dt: float, sampling_events) -> None:
         st = self.stats
         if prompt_step:
             st.prefill_steps, st.prefill_tokens, st.prefill_s = st.prefill_steps + 1, st.prefill_tokens + n_tokens, st.prefill_s + dt

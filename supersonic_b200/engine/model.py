@@ -25,7 +25,8 @@ from ..csrc.kernel_sets import kernel_set_for
 from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
                      BuildContext, WeightAccess, lookup)
 from ..weights import WeightStore
-from .batch import NotOnHost, StepBatch, StepEntry, decode_pages_bucket, pack_step, plan_chunks
+from .batch import (NotOnHost, PackedStep, StepBatch, StepEntry, batch_over, decode_pages_bucket, pack_entries,
+                    pack_step, plan_chunks)
 
 _DTYPES = {"float32": torch.float32, "fp32": torch.float32, "f32": torch.float32,
            "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
@@ -104,16 +105,74 @@ class DecodeGraph:
         self.pool = self.graph.pool()
 
     def run(self, tokens, positions, slots) -> torch.Tensor:
+        """``tokens``: a host list, or an int32 device tensor (what a sampler just wrote: the step is then
+        launched without the host ever seeing them)."""
         i = self.turn
         self.turn = (i + 1) % len(self.hosts)
         if self.copied[i] is not None:
             self.copied[i].synchronize()                    # its last copy has left this buffer
         h = self.hosts[i]
-        self.hosts_np[i][:] = list(tokens) + list(positions) + list(slots)     # a numpy view of the pinned buffer
-        self.ints.copy_(h, non_blocking=True)
+        B = self.n_seqs
+        if isinstance(tokens, torch.Tensor):
+            self.hosts_np[i][B:] = list(positions) + list(slots)
+            self.ints[B:].copy_(h[B:], non_blocking=True)
+            self.ints[:B].copy_(tokens.view(-1), non_blocking=True)
+        else:
+            self.hosts_np[i][:] = list(tokens) + list(positions) + list(slots)     # a numpy view of the pinned buffer
+            self.ints.copy_(h, non_blocking=True)
         if self.copied[i] is None:
             self.copied[i] = torch.cuda.Event()
         self.copied[i].record()
+        self.graph.replay()
+        if self.waiting_kernels:
+            from ..csrc import ops
+            ops.note_bounded_wait_launches(self.waiting_kernels)
+        return self.logits
+
+
+class PromptGraph:
+    """A captured step of prompts (or of pieces of them) for one set of sizes: tokens in all, sequences,
+    wanted rows, longest run of new tokens, context bucket.  Recorded the second time a set of sizes
+    comes up (the first time runs uncaptured, which also sizes every scratch buffer), then replayed
+    for any sequences of those sizes: the step's index arrays are copied into a fixed device buffer
+    that the captured kernels read.  What it saves is the host's share of a step, which for prompts of
+    a few hundred tokens is larger than the device's.  The reference launches every operation from
+    the host, one sequence at a time (crates/runner/src/prefill_engine.rs:974-1382)."""
+
+    def __init__(self, model: "Model", packed: PackedStep, pool=None):
+        from ..csrc import ops
+        dev = model.device
+        n = int(packed.flat.shape[0])
+        self.hosts = [torch.zeros(n, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.copied = [None, None]
+        self.turn = 0
+        self.ints = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.batch = batch_over(self.ints, packed, captured=True)
+        self._load(packed)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        before, waits_before = ops.LAUNCHES, ops.bounded_wait_launches()
+        with torch.cuda.graph(self.graph, pool=pool):
+            self.logits = model._forward(self.batch)
+        self.kernels_per_replay = ops.LAUNCHES - before
+        self.waiting_kernels = ops.bounded_wait_launches() - waits_before
+        self.pool = self.graph.pool()
+
+    def _load(self, packed: PackedStep) -> None:
+        i = self.turn
+        self.turn = 1 - i
+        if self.copied[i] is not None:
+            self.copied[i].synchronize()
+        self.hosts[i].numpy()[:] = packed.flat
+        self.ints.copy_(self.hosts[i], non_blocking=True)
+        if self.copied[i] is None:
+            self.copied[i] = torch.cuda.Event()
+        self.copied[i].record()
+
+    def run(self, packed: Optional[PackedStep]) -> torch.Tensor:
+        """``packed`` None: the inputs were loaded by the constructor (the step that recorded the graph)."""
+        if packed is not None:
+            self._load(packed)
         self.graph.replay()
         if self.waiting_kernels:
             from ..csrc import ops
@@ -184,8 +243,17 @@ class Model:
         for b in self.blocks:
             parts += [b] + [p for p in (getattr(b, n, None) for n in ("mixer", "feed_forward", "mixer_norm",
                                                                      "feed_forward_norm", "position")) if p is not None]
-        self.use_graphs = (use_graphs and getattr(self.kernels, "capturable", False)
-                           and all(getattr(p, "capture_safe", True) for p in parts))
+        # ``capture_safe``: True (the default), False, or "decode" for a part whose decode steps can be
+        # captured but whose prompt steps cannot
+        safe = [getattr(p, "capture_safe", True) for p in parts]
+        capturable = use_graphs and getattr(self.kernels, "capturable", False)
+        self.use_graphs = capturable and all(x is True or x == "decode" for x in safe)
+        # prompt steps whose sizes recur are captured too (see PromptGraph)
+        self.use_prompt_graphs = capturable and all(x is True for x in safe)
+        self.max_prompt_graphs = 32
+        self._prompt_graphs: Dict[Any, PromptGraph] = {}
+        self._prompt_seen: Dict[Any, int] = {}
+        self.prompt_graph_replays = 0
         # the last position any position encoding of the model can encode
         limits = [getattr(getattr(b, "position", None), "max_positions", None) for b in self.blocks]
         self.position_limit = min([int(x) for x in limits if x is not None], default=None)
@@ -228,14 +296,46 @@ class Model:
             return self._graph_step(entries, starts)
         if sum(len(e.tokens) for e in entries) > self.step_token_budget:
             return self._chunked_step(entries)
-        batch = pack_step(entries, starts, self.device, self.spec.vocab_size)
+        packed = pack_entries(entries, starts, self.spec.vocab_size)
         for e in entries:          # pages a failed step reserved stay with their slots
             cache.reserve(e.slot, len(e.tokens))
         cache.sync()
-        logits = self._forward(batch)
+        logits = self._prompt_step(packed)
         for e in entries:
             cache.advance(e.slot, len(e.tokens))
         return logits
+
+    def _prompt_step(self, packed: PackedStep) -> torch.Tensor:
+        """Run a packed step: through its captured graph if these sizes have one, recording one if
+        they come up for the second time, else launch by launch."""
+        if self.use_prompt_graphs and self._timed is None:
+            key = packed.shape_key
+            graph = self._prompt_graphs.get(key)
+            if graph is None:
+                seen = self._prompt_seen.get(key, 0) + 1
+                self._prompt_seen[key] = seen
+                if len(self._prompt_seen) > 4096:
+                    self._prompt_seen.clear()
+                if seen >= 2 and len(self._prompt_graphs) < self.max_prompt_graphs:
+                    self._check_positions(packed.max_total)
+                    graph = self._prompt_graphs[key] = PromptGraph(self, packed, self._graph_pool)
+                    self._graph_pool = graph.pool
+                    packed = None                         # its inputs are loaded
+            else:
+                self._check_positions(packed.max_total)
+            if graph is not None:
+                self.prompt_graph_replays += 1
+                self.graph_kernels += graph.kernels_per_replay
+                return graph.run(packed).clone()          # the graph's own buffer is reused by its next replay
+        host = torch.from_numpy(packed.flat).pin_memory()
+        return self._forward(batch_over(host.to(self.device, non_blocking=True), packed))
+
+    def _check_positions(self, longest: int) -> None:
+        """A captured step cannot look at positions on the host (``Rotary.check_range`` sees the sizes
+        the graph was recorded with), so the bound is checked before it is replayed."""
+        if self.position_limit is not None and longest > self.position_limit:
+            raise ValueError(f"a sequence reaches {longest} tokens, beyond the {self.position_limit} "
+                             "positions this model encodes")
 
     def _chunked_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """A step of more tokens than ``step_token_budget``: the same tokens as several steps, each
@@ -265,24 +365,38 @@ class Model:
             rows.append(self.step(piece))
         return torch.cat(rows) if len(rows) > 1 else rows[0]
 
+    @property
+    def feeds_device_tokens(self) -> bool:
+        """Whether ``step_ahead`` can run: decode steps replay captured graphs and are not being timed."""
+        return self.use_graphs and self._timed is None
+
+    def step_ahead(self, slots: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
+        """One decode step of ``slots`` whose next tokens are the int32 device tensor ``tokens`` (the
+        sampler's output of the step before): launched without the host reading them, so that the
+        host's share of a step (bookkeeping, the read-back of the tokens) overlaps the device's.
+        Returns the logits of every row."""
+        if not self.feeds_device_tokens:
+            raise RuntimeError("step_ahead needs captured decode steps (the bfloat16 path with graphs on)")
+        if tokens.dtype != torch.int32 or tokens.numel() != len(slots) or tokens.device != self.device:
+            raise ValueError("step_ahead: one int32 token per slot, on the model's device")
+        return self._graph_decode(list(slots), tokens, [self.cache.length(s) for s in slots])
+
     def _graph_step(self, entries, starts) -> torch.Tensor:
-        cache = self.cache
-        slots = [e.slot for e in entries]
         tokens = [int(e.tokens[0]) for e in entries]
-        if len(set(slots)) != len(slots):
-            raise ValueError("a slot appears twice in one step")
         bad = [t for t in tokens if not 0 <= t < self.spec.vocab_size]
         if bad:
             raise ValueError(f"token ids {bad[:8]} are outside the vocabulary of {self.spec.vocab_size}")
-        if self.position_limit is not None and max(starts) + 1 > self.position_limit:
-            # the captured step cannot see positions on the host (``Rotary.check_range`` looks at a
-            # batch of length 1 there), so the bound is checked here
-            raise ValueError(f"a sequence reaches {max(starts) + 1} tokens, beyond the {self.position_limit} "
-                             "positions this model encodes")
-        for e in entries:
-            cache.reserve(e.slot, 1)
+        return self._graph_decode([e.slot for e in entries], tokens, starts)
+
+    def _graph_decode(self, slots, tokens, starts) -> torch.Tensor:
+        cache = self.cache
+        if len(set(slots)) != len(slots):
+            raise ValueError("a slot appears twice in one step")
+        self._check_positions(max(starts) + 1)
+        for s in slots:
+            cache.reserve(s, 1)
         cache.sync()
-        key = (len(entries), decode_pages_bucket(max(starts) + 1))
+        key = (len(slots), decode_pages_bucket(max(starts) + 1))
         graph = self._graphs.get(key)
         if graph is None:
             graph = self._graphs[key] = DecodeGraph(self, key[0], key[1], self._graph_pool)
@@ -290,8 +404,8 @@ class Model:
         logits = graph.run(tokens, starts, slots).clone()     # the graph's own buffer is reused next step
         self.graph_replays += 1
         self.graph_kernels += graph.kernels_per_replay
-        for e in entries:
-            cache.advance(e.slot, 1)
+        for s in slots:
+            cache.advance(s, 1)
         return logits
 
     def time_stages(self, on: bool = True):
@@ -357,6 +471,15 @@ class Model:
         brought to the host (it reads a device word, which waits for the stream)."""
         from ..csrc import ops
         ops.check_device_errors(self.device)
+
+    def start_fetch(self, values: torch.Tensor):
+        """Begin bringing sampled tokens to the host without waiting (``finish_fetch`` waits)."""
+        from ..csrc import ops
+        return ops.start_fetch(values)
+
+    def finish_fetch(self, handle) -> list:
+        from ..csrc import ops
+        return ops.finish_fetch(handle)
 
     def fetch(self, values: torch.Tensor) -> list:
         """Sampled tokens (an int32 device tensor) as a host list; kernel errors are looked at in

@@ -428,3 +428,43 @@ def test_bfloat16_sampling_is_reproducible_in_deterministic_mode(model_folders, 
         m.close_sequence(s)
         assert torch.equal(alone[0], batch[i]), f"prompt {i}"
         assert torch.equal(alone2[0], batch2[i]), f"decode {i}"
+
+
+@pytest.mark.parametrize("name", ["B", "E"])
+def test_prompt_steps_of_recurring_sizes_are_captured_and_stay_right(model_folders, name):
+    """The second time a prompt step of the same sizes comes up it is recorded as a graph, the third
+    time replayed: other tokens, other slots, other pages each time, the logits those of the plain
+    implementation.  A step in pieces (a small token budget) recurs by construction."""
+    from supersonic_b200.engine import Model, StepEntry
+    d, pc, pw = model_folders[name]
+    rng = np.random.default_rng(91)
+    m = Model.from_dir(d, dtype="bfloat16", max_tokens=2048)
+    assert m.use_prompt_graphs
+    held = []
+    for round_ in range(4):
+        a = rng.integers(0, pc["vocab_size"], 130).tolist()
+        b = rng.integers(0, pc["vocab_size"], 37).tolist()
+        if round_ == 2:
+            held.append(m.open_sequence())               # shifts the slots and pages the next rounds get
+        sa, sb = m.open_sequence(), m.open_sequence()
+        got = m.step([StepEntry(sa, a, [0, 129]), StepEntry(sb, b, [36])]).double().cpu().numpy()
+        ra, rb = pl.forward(pc, pw, a), pl.forward(pc, pw, b)
+        want = np.stack([ra[0], ra[129], rb[36]])
+        assert np.abs(got - want).max() < 2e-2 * np.abs(want).max(), round_
+        nxt = m.step([StepEntry(sa, [5], [0]), StepEntry(sb, [6], [0])]).double().cpu().numpy()     # the cache it left is right
+        wa, wb = pl.forward(pc, pw, a + [5])[-1], pl.forward(pc, pw, b + [6])[-1]
+        assert np.abs(nxt - np.stack([wa, wb])).max() < 2e-2 * max(np.abs(wa).max(), np.abs(wb).max())
+        m.close_sequence(sa); m.close_sequence(sb)
+    assert m.prompt_graph_replays == 3 and len(m._prompt_graphs) == 1
+    m.check_errors()
+    # in pieces: 300 tokens with a budget of 64 are four steps of 64 tokens and one of 44; by the second
+    # prompt every size has come up before
+    m2 = Model.from_dir(d, dtype="bfloat16", max_tokens=1024, step_token_budget=64)
+    for round_ in range(2):
+        t = rng.integers(0, pc["vocab_size"], 300).tolist()
+        s = m2.open_sequence()
+        got = m2.step([StepEntry(s, t, [299])]).double().cpu().numpy()
+        want = pl.forward(pc, pw, t)[-1]
+        assert np.abs(got[0] - want).max() < 2e-2 * np.abs(want).max()
+        m2.close_sequence(s)
+    assert m2.prompt_graph_replays >= 4

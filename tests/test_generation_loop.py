@@ -48,6 +48,33 @@ class ScriptedModel:
         return torch.stack(rows)
 
 
+class ScriptedModelAhead(ScriptedModel):
+    """The same model with the interface of a device that runs one step ahead of the host: tokens of a
+    step may come as a tensor (here on the CPU), and reading them back is split in two."""
+
+    feeds_device_tokens = True
+
+    def __init__(self, *a, **k):
+        super().__init__(*a, **k)
+        self.device = torch.device("cpu")
+        self.ahead_steps = 0
+
+    def step_ahead(self, slots, tokens):
+        from supersonic_b200.engine import StepEntry
+        assert isinstance(tokens, torch.Tensor) and tokens.dtype == torch.int32 and tokens.numel() == len(slots)
+        self.ahead_steps += 1
+        return self.step([StepEntry(s, [int(t)], [0]) for s, t in zip(slots, tokens.tolist())])
+
+    def start_fetch(self, values):
+        return values.clone()
+
+    def finish_fetch(self, handle):
+        return handle.tolist()
+
+
+MODELS = [ScriptedModel, ScriptedModelAhead]
+
+
 def greedy(logits, slots, params):
     return logits.argmax(-1).to(torch.int32)
 
@@ -80,8 +107,9 @@ def test_plan_batch_respects_pages_slots_and_batch_size():
     assert plan_batch([1], lens, 8, 64, 8, 64, None) == []                         # does not fit at all
 
 
-def test_unequal_prompts_early_ends_and_slot_reuse():
-    m = ScriptedModel(max_tokens=64 * 3, max_seq=128)
+@pytest.mark.parametrize("Model", MODELS)
+def test_unequal_prompts_early_ends_and_slot_reuse(Model):
+    m = Model(max_tokens=64 * 3, max_seq=128)
     g = Generator(m, sampler=greedy)
     prompts = [[1, 2], [5, 6, 7, 8, 9], [2], [4, 4, 4], [10, 1, 1, 1, 1, 1, 1], [6]]
     res = g.generate(prompts, max_new_tokens=6, batch_size=3)
@@ -98,11 +126,20 @@ def test_unequal_prompts_early_ends_and_slot_reuse():
     # steps shrink as sequences end
     sizes = [len(s) for s in m.step_sizes]
     assert any(a > b for a, b in zip(sizes, sizes[1:]))
+    if Model is ScriptedModelAhead:
+        assert m.ahead_steps > 0                           # the loop did run ahead
+        # a sequence that ends at a stop token was stepped once more than the simple loop steps it;
+        # one that ends at its budget was not
+        simple = ScriptedModel(max_tokens=64 * 3, max_seq=128)
+        Generator(simple, sampler=greedy).generate(prompts, max_new_tokens=6, batch_size=3)
+        stops = sum(1 for p in prompts if expected(p, 6)[1] == "stop" and len(expected(p, 6)[0]) < 6)
+        assert sum(sizes) - sum(len(x) for x in simple.step_sizes) == stops
 
 
-def test_stop_token_options_and_zero_budget():
+@pytest.mark.parametrize("Model", MODELS)
+def test_stop_token_options_and_zero_budget(Model):
     prompts = [[1, 2], [7, 7]]
-    m = ScriptedModel()
+    m = Model()
     g = Generator(m, sampler=greedy)
     res = g.generate(prompts, max_new_tokens=5, include_stop_token=False)
     assert [r.tokens for r in res] == [expected(p, 5, include_stop=False)[0] for p in prompts]
@@ -116,8 +153,9 @@ def test_stop_token_options_and_zero_budget():
     assert m.cache.slots.n_held == 0
 
 
-def test_requests_that_cannot_fit_are_refused():
-    m = ScriptedModel(max_tokens=64 * 2, max_seq=128)
+@pytest.mark.parametrize("Model", MODELS)
+def test_requests_that_cannot_fit_are_refused(Model):
+    m = Model(max_tokens=64 * 2, max_seq=128)
     g = Generator(m, sampler=greedy)
     with pytest.raises(ValueError, match="exceed"):
         g.generate([[1] * 125], max_new_tokens=8)
@@ -126,8 +164,9 @@ def test_requests_that_cannot_fit_are_refused():
     assert m.cache.slots.n_held == 0
 
 
-def test_a_failing_step_gives_slots_back():
-    m = ScriptedModel()
+@pytest.mark.parametrize("Model", MODELS)
+def test_a_failing_step_gives_slots_back(Model):
+    m = Model()
     calls = []
 
     def bad_sampler(logits, slots, params):
@@ -190,10 +229,10 @@ def test_which_gemm_a_prompt_gets_is_decided_by_its_rows():
     assert FK._pair_tiles(2048, 6144) and FK._pair_tiles(512, 28672) and FK._pair_tiles(1030, 4096)
     assert FK._pair_tiles(256, 256) and FK._pair_tiles(200, 4096)        # two row tiles of 128
     assert not FK._pair_tiles(300, 28672) and not FK._pair_tiles(100, 4096) and not FK._pair_tiles(2048, 128)
-    assert FK._gemm_splits(2048, 4096, 4096, 256) == 1                    # 256 tiles: more than the SMs
-    assert FK._gemm_splits(128, 4096, 14336, 256) == 9                    # 16 tiles, 224 k-blocks
-    assert FK._gemm_splits(128, 4096, 4096, 256) == 8                     # at least 8 k-blocks a part
-    assert FK._gemm_splits(70, 256, 192, 256) == 1                        # a tiny model: K is too short to cut
+    assert FK._gemm_splits(2048, 4096, 4096, 256, 148) == 1                    # 256 tiles: more than the SMs
+    assert FK._gemm_splits(128, 4096, 14336, 256, 148) == 9                    # 16 tiles, 224 k-blocks
+    assert FK._gemm_splits(128, 4096, 4096, 256, 148) == 8                     # at least 8 k-blocks a part
+    assert FK._gemm_splits(70, 256, 192, 256, 148) == 1                        # a tiny model: K is too short to cut
     assert FK._tile_n(2048, 4096) == 256 and FK._tile_n(8, 4096) == 64 and FK._tile_n(8, 128256) == 256
 
 
