@@ -13,6 +13,7 @@ for one token (crates/runner/src/decode_engine.rs:3631-3993), one sequence each.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Any, Dict, Optional, Sequence
 
@@ -258,6 +259,9 @@ class Model:
         limits = [getattr(getattr(b, "position", None), "max_positions", None) for b in self.blocks]
         self.position_limit = min([int(x) for x in limits if x is not None], default=None)
         self._timed = None      # a TimedKernels while stage timing is on
+        # NVTX ranges per layer (SSB200_NVTX=1): for a profiler's timeline of uncaptured steps; the reference
+        # marks stages with host timers only (crates/runner/src/decode_engine.rs:10157-10162)
+        self.nvtx = os.environ.get("SSB200_NVTX", "") not in ("", "0")
         self._graphs: Dict[Any, DecodeGraph] = {}
         self._graph_pool = None
         self.graph_replays = 0
@@ -425,8 +429,14 @@ class Model:
             self._timed.ctx = ctx
         ctx.stage = "embed"
         residual = self.embedding(ctx, batch.token_ids)
-        for stop in self.spec.schedule:
-            self.blocks[stop.layer].forward(ctx, residual, stop.cache, stop.writes_cache)
+        if self.nvtx:                                       # a named range per stop of the schedule, for timelines
+            for i, stop in enumerate(self.spec.schedule):
+                torch.cuda.nvtx.range_push(f"stop {i} layer {stop.layer}")
+                self.blocks[stop.layer].forward(ctx, residual, stop.cache, stop.writes_cache)
+                torch.cuda.nvtx.range_pop()
+        else:
+            for stop in self.spec.schedule:
+                self.blocks[stop.layer].forward(ctx, residual, stop.cache, stop.writes_cache)
         if batch.n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         ctx.stage = "head"

@@ -841,3 +841,40 @@ def test_attention_decode_chunked_over_a_ragged_batch():
             ops().attention_decode_chunked(q[b:b + 1], k, v, pos[b:b + 1], slot[b:b + 1], table, alone, n_q, n_kv, hd,
                                            6, None, scale, chunk, max_chunks, scratch, counters)
             assert torch.equal(alone[0], out[b]), (chunk, b)
+
+
+def test_kernels_with_scratch_stay_inside_it():
+    """Guard words behind the scratch a kernel is told it may use: the chunked decode attention's partial
+    results and counters, the split projection's partial tiles.  Nothing past the stated sizes changes."""
+    n_q, n_kv, hd, B = 8, 2, 128, 5
+    g = torch.Generator(device=DEV).manual_seed(91)
+    k, v = _paged(B * 20, n_kv, hd, torch.bfloat16, 92)
+    table = torch.randperm(B * 20, generator=torch.Generator().manual_seed(93)).to(torch.int32).view(B, 20).to(DEV)
+    pos = torch.tensor([1279, 5, 640, 64, 1000], dtype=torch.int32, device=DEV)
+    slot = torch.arange(B, dtype=torch.int32, device=DEV)
+    q = torch.randn(B, n_q * hd, device=DEV, generator=g).bfloat16()
+    out = torch.empty(B, n_q * hd, dtype=torch.bfloat16, device=DEV)
+    chunk, max_chunks = 3, 7
+    nf, nc = ops().attention_decode_chunked_scratch(B, n_q, n_kv, hd, max_chunks)
+    scratch = torch.full((nf + 64,), 7.5, device=DEV)
+    counters = torch.zeros(nc + 64, dtype=torch.int32, device=DEV)
+    counters[nc:] = 12345
+    ops().attention_decode_chunked(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, None, 1 / math.sqrt(hd), chunk,
+                                   max_chunks, scratch, counters)
+    torch.cuda.synchronize()
+    assert torch.all(scratch[nf:] == 7.5) and torch.all(counters[nc:] == 12345) and torch.all(counters[:nc] == 0)
+    ref = _attention_reference(q, k, v, pos, slot, table, n_q, n_kv, hd, None, 1 / math.sqrt(hd))
+    torch.testing.assert_close(out.double(), ref, atol=2e-2, rtol=2e-2)
+    rows, N, K, splits = 20, 1000, 4096, 5
+    nf, nc = ops().gemv_tc_scratch(rows, N, splits)
+    partials = torch.full((nf + 64,), 7.5, device=DEV)
+    cnt = torch.zeros(nc + 64, dtype=torch.int32, device=DEV)
+    cnt[nc:] = 12345
+    x = torch.randn(rows, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    y = torch.empty(rows, N, dtype=torch.bfloat16, device=DEV)
+    ops().gemv_tc(x, w, y, splits=splits, partials=partials, counters=cnt)
+    torch.cuda.synchronize()
+    assert torch.all(partials[nf:] == 7.5) and torch.all(cnt[nc:] == 12345) and torch.all(cnt[:nc] == 0)
+    torch.testing.assert_close(y.float(), x.float() @ w.float().T, atol=0.15, rtol=2e-2)
+    ops().check_device_errors()

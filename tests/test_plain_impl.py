@@ -116,3 +116,60 @@ def test_plain_against_the_reference_kernels_golden():
         assert len(clear) >= len(toks) // 2
         for t in clear:           # the same best token among the stored columns wherever the margin is clear
             assert int(np.argmax(got[t])) == int(np.argmax(want[t, :64]))
+
+
+def _cpp_plain(tmp_path):
+    """Compile tests/plain_cpp/plain_llama.cpp once; None if there is no C++ compiler."""
+    import shutil
+    import subprocess
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        return None
+    exe = str(tmp_path / "plain_llama")
+    src = os.path.join(os.path.dirname(os.path.abspath(__file__)), "plain_cpp", "plain_llama.cpp")
+    subprocess.run([cxx, "-O2", "-std=c++17", "-o", exe, src], check=True)
+    return exe
+
+
+def test_two_plain_statements_agree(model_folders, tmp_path):
+    """The NumPy statement and the C++ one (tests/plain_cpp/plain_llama.cpp), written separately from
+    the reference's formulas, give the same logits on two tiny models that differ in every option:
+    tied and untied heads, with and without llama3 frequency scaling, positions past the scaling's
+    original context."""
+    import struct
+    import subprocess
+    import pytest
+    exe = _cpp_plain(tmp_path)
+    if exe is None:
+        pytest.skip("no C++ compiler")
+    for name, n_tokens in (("A", 21), ("B", 40)):
+        _, pc, pw = model_folders[name]
+        tokens = np.random.default_rng(5).integers(0, pc["vocab_size"], n_tokens).tolist()
+        sc = pc.get("rope_scaling")
+        nq = pc["num_attention_heads"]
+        hdr = [pc["vocab_size"], pc["hidden_size"], pc["intermediate_size"], pc["num_hidden_layers"], nq,
+               pc.get("num_key_value_heads") or nq, pl.head_dim_of(pc), int(bool(pc.get("tie_word_embeddings"))),
+               n_tokens, int(bool(sc))]
+        par = [pc["rms_norm_eps"], pc.get("rope_theta", 10000.0)] + (
+            [sc["factor"], sc["low_freq_factor"], sc["high_freq_factor"], sc["original_max_position_embeddings"]]
+            if sc else [1.0, 1.0, 1.0, 1.0])
+        order = ["model.embed_tokens.weight"]
+        for n in range(pc["num_hidden_layers"]):
+            p = f"model.layers.{n}"
+            order += [f"{p}.input_layernorm.weight", f"{p}.self_attn.q_proj.weight", f"{p}.self_attn.k_proj.weight",
+                      f"{p}.self_attn.v_proj.weight", f"{p}.self_attn.o_proj.weight", f"{p}.post_attention_layernorm.weight",
+                      f"{p}.mlp.gate_proj.weight", f"{p}.mlp.up_proj.weight", f"{p}.mlp.down_proj.weight"]
+        order.append("model.norm.weight")
+        if not pc.get("tie_word_embeddings"):
+            order.append("lm_head.weight")
+        src, dst = tmp_path / f"{name}.in", tmp_path / f"{name}.out"
+        with open(src, "wb") as f:
+            f.write(struct.pack("<10q", *hdr))
+            f.write(struct.pack("<6d", *[float(x) for x in par]))
+            f.write(np.asarray(tokens, dtype="<i8").tobytes())
+            for key in order:
+                f.write(np.ascontiguousarray(pw[key], dtype="<f8").tobytes())
+        subprocess.run([exe, str(src), str(dst)], check=True)
+        got = np.fromfile(dst, dtype="<f8").reshape(n_tokens, pc["vocab_size"])
+        want = pl.forward(pc, pw, tokens)
+        assert np.abs(got - want).max() < 1e-9, name

@@ -4,6 +4,7 @@ whose shorter requests end earlier, one batch after another so that slots and pa
 used again."""
 import numpy as np
 import pytest
+import torch
 
 import plain_llama as pl
 import replay_helpers as rh
@@ -99,3 +100,31 @@ def test_greedy_continuation_agrees(replayed, model_folders):
                     assert int(out[(f"b{rid}", p)].argmax()) == int(ref[rid][p].argmax())
                     checked += 1
         assert checked > 50
+
+
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_float32_is_bitwise_repeatable_and_scratch_is_respected(model_folders, name):
+    """No sanitizer runs on these devices, so races are looked for the other way: the float32 path has
+    no atomics on data and a fixed order of every sum, so three runs of the same ragged batch (prompts in
+    one step, then token by token, slots reused in between) must give the same bits; a race between
+    blocks, or a read of memory another request left, would show as a difference."""
+    from supersonic_b200.engine import Model, StepEntry
+    d, pc, pw = model_folders[name]
+    rng = np.random.default_rng(17)
+    seqs = [rng.integers(0, pc["vocab_size"], n).tolist() for n in (70, 3, 129)]
+    m = Model.from_dir(d, dtype="float32", max_tokens=1024)
+    runs = []
+    for rep in range(3):
+        if rep == 1:
+            extra = m.open_sequence()
+            m.step([StepEntry(extra, rng.integers(0, pc["vocab_size"], 200).tolist(), [])])     # dirties other pages
+            m.close_sequence(extra)
+        slots = [m.open_sequence() for _ in seqs]
+        rows = [m.step([StepEntry(s, t[:-2], [len(t) - 3]) for s, t in zip(slots, seqs)])]
+        for k in (2, 1):
+            rows.append(m.step([StepEntry(s, [t[-k]], [0]) for s, t in zip(slots, seqs)]))
+        runs.append(torch.cat(rows).cpu())
+        for s in slots:
+            m.close_sequence(s)
+        m.cache.check()
+    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])
