@@ -203,25 +203,46 @@ def ragged_workload(preset, n_prompts, lo, hi, new_tokens, temperature, pk, seed
     return out
 
 
-def time_prefill(model, tokens, reps=5, warmup=3, seed=1):
+def time_prefill(model, tokens, reps=5, warmup=3, seed=1, seqs=1):
+    """Best device time of one step that brings ``seqs`` prompts of ``tokens`` tokens each (new random
+    tokens every time; the wanted row is each prompt's last).  The first runs are warm-up; a step whose
+    sizes recur replays a captured graph from its second run on, as it would when serving."""
     import torch
     from supersonic_b200.engine import StepEntry
     g = torch.Generator().manual_seed(seed)
     best = None
     for r in range(reps + warmup):
-        prompt = torch.randint(0, model.vocab_size, (tokens,), generator=g).tolist()
-        slot = model.open_sequence()
+        prompts = torch.randint(0, model.vocab_size, (seqs, tokens), generator=g).tolist()
+        slots = [model.open_sequence() for _ in range(seqs)]
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        model.step([StepEntry(slot, prompt, [tokens - 1])])
+        model.step([StepEntry(s, p, [tokens - 1]) for s, p in zip(slots, prompts)])
         end.record()
         torch.cuda.synchronize()
-        model.close_sequence(slot)
-        if r >= warmup:                                    # the first runs are warm-up
+        for s in slots:
+            model.close_sequence(s)
+        if r >= warmup:
             ms = start.elapsed_time(end)
             best = ms if best is None else min(best, ms)
     return best
+
+
+def sweep(model, pk, steps, warmup):
+    """Decode at further batch sizes and context lengths, prompts of further sizes: the table of README.md."""
+    out = {"decode": [], "prefill": []}
+    for batch, ctx in ((1, 512), (1, 8000), (8, 512), (8, 8000), (32, 512), (64, 512), (64, 4096)):
+        ms, _, nbytes = time_decode(model, batch, ctx, min(steps, 48), warmup, seed=20 + batch)
+        out["decode"].append({"batch": batch, "context": ctx, "ms_per_step": round(ms, 3),
+                              "tokens_s": round(batch * 1000.0 / ms, 1),
+                              "hbm_frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)})
+    for seqs, tokens in ((1, 128), (1, 512), (1, 2048), (1, 8192), (8, 512), (4, 2048), (16, 128)):
+        ms = time_prefill(model, tokens, reps=4, warmup=3, seed=30 + seqs, seqs=seqs)
+        flops = prefill_flops(model, [tokens] * seqs, seqs)
+        out["prefill"].append({"seqs": seqs, "tokens": tokens, "ms": round(ms, 3),
+                               "tokens_s": round(seqs * tokens * 1000.0 / ms, 1),
+                               "bf16_frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 3)})
+    return out
 
 
 def time_e2e(engine, batch, prompt_len, steps, warmup, seed=2):
@@ -346,6 +367,8 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
     ap.add_argument("--skip-workloads", action="store_true", help="leave out the 3B and 1B ragged workloads")
+    ap.add_argument("--sweep", action="store_true",
+                    help="also time decode and prompts at further sizes (adds a 'sweep' key to the line)")
     ap.add_argument("--deterministic", action="store_true",
                     help="time the bfloat16 path without float atomics and with one kernel choice whatever the batch")
     args = ap.parse_args()
@@ -397,6 +420,7 @@ def main():
             points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
             points[f"decode_b{b}_hbm_frac"] = round(pbytes / (pms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)
     stages = stage_shares(model, args.batch, args.prompt_len, args.prefill_tokens)
+    swept = sweep(model, pk, args.steps, args.warmup) if args.sweep else None
     if not args.skip_workloads and layers == full.num_hidden_layers:
         del engine, model, store
         torch.cuda.empty_cache()
@@ -431,6 +455,7 @@ def main():
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
         "stages": stages,
+        **({"sweep": swept} if swept else {}),
         "clocks": clk,
     }
     assert ops.LAUNCHES > launches0
