@@ -64,8 +64,8 @@ def attention_decode(args):
     out = torch.empty(B, n_q * hd, dtype=torch.bfloat16, device=DEV)
     splits = args.splits
     pages = (ctx + 63) // 64
-    chunk = args.chunk_pages or -(-pages // splits)
-    max_chunks = -(-pages // chunk)
+    chunk = 0 if args.chunk_pages < 0 else (args.chunk_pages or -(-pages // splits))     # negative: the kernel decides
+    max_chunks = -(-pages // chunk) if chunk else min(-(-pages // 2), 296 // n_kv + 1)
     if args.kind == 2:
         nf, nc = ops.attention_decode_chunked_scratch(B, n_q, n_kv, hd, max_chunks)
     else:

@@ -73,7 +73,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
     int* sm_pos = sm_slot + n_seqs;
     __shared__ float sm_m[ADM_WARPS][ADM_ROWS], sm_l[ADM_WARPS][ADM_ROWS];
     __shared__ int is_last;
-    __shared__ int warp_total[ADM_WARPS];
+    __shared__ int warp_total[ADM_WARPS], warp_longest[ADM_WARPS], warp_live[ADM_WARPS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 
     ssb_pdl_launch_dependents();
@@ -81,11 +81,48 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
     // read before the dependency wait, and so may pages of earlier steps' keys.
     for (int b = threadIdx.x; b < n_seqs; b += ADM_THREADS) { sm_slot[b] = slot[b]; sm_pos[b] = pos[b]; }
     __syncthreads();
-    auto chunks_of = [&](int b) {
+    auto pages_of = [&](int b) {
         if (sm_slot[b] < 0) return 0;                            // a padding row is no work item (zeros below)
         const int p = sm_pos[b];
         const int key_lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-        return min(((p >> 6) - (key_lo >> 6) + chunk_pages) / chunk_pages, max_chunks);   // ceil(pages / chunk_pages)
+        return (p >> 6) - (key_lo >> 6) + 1;
+    };
+    // chunk_pages <= 0: the kernel sizes the chunks itself from the batch's pages; every block computes
+    // the same figure.  Sequences of about equal length: items about as many as the blocks (a fifth of
+    // them spare, for the items that rounding adds), since an item's fixed cost is worth some six pages
+    // of streaming.  Very unequal lengths (the longest more than one and a half times the mean) with
+    // enough work for it: two to three items a block, of at least eight pages, so that the blocks end
+    // together.  A caller that wants a sequence cut the same way in every batch gives chunk_pages itself.
+    if (chunk_pages <= 0) {
+        int local = 0, longest = 0, live = 0;
+        for (int b = threadIdx.x; b < n_seqs; b += ADM_THREADS) {
+            const int n = pages_of(b);
+            local += n;
+            longest = max(longest, n);
+            live += n > 0;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            local += __shfl_xor_sync(0xffffffffu, local, o);
+            live += __shfl_xor_sync(0xffffffffu, live, o);
+            longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, o));
+        }
+        if (lane == 0) { warp_total[warp] = local; warp_longest[warp] = longest; warp_live[warp] = live; }
+        __syncthreads();
+        long long units = 0;
+        int seqs = 0;
+        longest = 0;
+        for (int w = 0; w < ADM_WARPS; ++w) { units += warp_total[w]; seqs += warp_live[w]; longest = max(longest, warp_longest[w]); }
+        const bool unequal = 2LL * longest * seqs > 3LL * units;            // longest > 1.5 x mean
+        units *= n_kv;
+        const long long coarse = max(1LL, (long long)gridDim.x * 4 / 5), fine = max(1LL, (long long)gridDim.x * 5 / 2);
+        const long long fine_pages = (units + fine - 1) / fine;
+        chunk_pages = (unequal && fine_pages >= 8) ? (int)fine_pages : (int)max(2LL, (units + coarse - 1) / coarse);
+        __syncthreads();                                         // warp_total is used again below
+    }
+    auto chunks_of = [&](int b) {
+        const int n = pages_of(b);
+        return n == 0 ? 0 : min((n + chunk_pages - 1) / chunk_pages, max_chunks);
     };
     {
         const int per = (n_seqs + ADM_THREADS - 1) / ADM_THREADS;
@@ -606,8 +643,9 @@ static inline long long adm_resident_blocks(int head_dim, bool fuse, int group, 
     return per_sm > 0 ? (long long)per_sm * adm_sm_count() : 0;
 }
 
-// chunk_pages: pages per chunk (>= 1); max_chunks: the most chunks a sequence is cut into (it sizes
-// the scratch): a sequence that would need more gets max_chunks larger ones.
+// chunk_pages: pages per chunk, or 0 for the kernel to size the chunks from the batch (see there);
+// max_chunks: the most chunks a sequence is cut into (it sizes the scratch): a sequence that would need
+// more gets max_chunks larger ones.
 static inline int adm_launch(const void* q, int ldq, const void* k_cache, const void* v_cache, const int* pos,
                              const int* slot, const int* page_table, int max_pages, void* out, int ldo,
                              int n_seqs, int n_q, int n_kv, int head_dim, int window, float scale, int chunk_pages,
@@ -615,7 +653,7 @@ static inline int adm_launch(const void* q, int ldq, const void* k_cache, const 
                              const float* cos_t, const float* sin_t) {
     typedef __nv_bfloat16 bf16;
     if (n_seqs <= 0) return 0;
-    if (n_seqs > ADM_MAX_SEQS || chunk_pages < 1 || max_chunks < 1 || (max_chunks > 1 && (!scratch || !counters)))
+    if (n_seqs > ADM_MAX_SEQS || chunk_pages < 0 || max_chunks < 1 || (max_chunks > 1 && (!scratch || !counters)))
         return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return SSB_ERR_BAD_SIZE;
     const bool fuse = cos_t != nullptr;

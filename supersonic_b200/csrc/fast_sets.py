@@ -17,7 +17,6 @@ from . import ops
 from .kernel_sets import NormedInput, PlainKernels, as_tensor
 
 TARGET_BLOCKS = 1184           # eight small blocks per SM
-MAX_CHUNK_PAGES = 32           # decode attention on the tensor cores: most pages a work item streams
 DETERMINISTIC_CHUNK_PAGES = 16 # ... and its fixed chunk size (1,024 keys) when results must not depend on the batch
 TC_ATTENTION_MIN_NEW = 96     # prompts at least this long take the tcgen05 attention (tiles of 128 rows)
 
@@ -167,18 +166,17 @@ class FastKernels(PlainKernels):
             self._scratch[name] = t
         return t
 
-    def _chunk_pages(self, n_seqs: int, n_kv: int, pages: int, blocks: int) -> int:
-        """Pages per chunk of the tensor-core decode attention for a batch whose longest sequence spans
-        up to ``pages``.  A work item has a fixed cost of about six pages' worth of streaming (its
-        query, the merge of its warps, its partial result), so items are as large as keeps every
-        resident block busy: the batch's pages shared out over the ``blocks`` the device holds, between 2 and
-        MAX_CHUNK_PAGES (measured at Llama-3.1-8B sizes: 64 x 520 tokens 31 us unsplit against 54 us in
-        two chunks; 8 x 8,192 tokens 49 us in chunks of 32 pages against 94 us in chunks of 8).  In
-        deterministic mode the figure is a constant, so that a sequence is cut the same way in every batch."""
+    def _chunks(self, n_kv: int, pages: int, blocks: int):
+        """(pages per chunk, most chunks of one sequence) for the tensor-core decode attention over a batch
+        whose longest sequence spans up to ``pages``.  Normally the kernel sizes the chunks itself from
+        the batch's real lengths (0): a work item has a fixed cost of about six pages' worth of
+        streaming, so items should be as large as still fills the ``blocks`` the device holds; what is
+        decided here is only how much scratch that can need: a sequence is never cut finer than two
+        pages a chunk, nor into more chunks than there are blocks for its kv heads.  In deterministic
+        mode the chunk is a constant, so that a sequence is cut the same way in every batch."""
         if self.deterministic:
-            return DETERMINISTIC_CHUNK_PAGES
-        share = -(-n_seqs * n_kv * pages // max(blocks, 1))
-        return max(2 if pages > 2 else 1, min(MAX_CHUNK_PAGES, share))
+            return DETERMINISTIC_CHUNK_PAGES, -(-pages // DETERMINISTIC_CHUNK_PAGES)
+        return 0, max(1, min(-(-pages // 2), blocks // max(n_kv, 1) + 1))
 
     def _decode_attention(self, q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim,
                           page_shift, window, scale, cos=None, sin=None):
@@ -191,9 +189,8 @@ class FastKernels(PlainKernels):
             # tensor-core kernel on a persistent grid (beside the mma.sync skinny GEMM it made a step
             # slower: the two compete for the SM's L1/shared memory; beside the tcgen05 projections it
             # is the faster choice at every batch size: batch 16: 4.24 to 3.57 ms a step)
-            chunk = self._chunk_pages(batch.n_seqs, n_kv, pages, ops.attention_decode_chunked_blocks(
+            chunk, max_chunks = self._chunks(n_kv, pages, ops.attention_decode_chunked_blocks(
                 batch.n_seqs, n_q, n_kv, head_dim, cos is not None))
-            max_chunks = -(-pages // chunk)
             scratch = counters = None
             if max_chunks > 1:
                 nf, nc = ops.attention_decode_chunked_scratch(batch.n_seqs, n_q, n_kv, head_dim, max_chunks)

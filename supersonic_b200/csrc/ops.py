@@ -367,13 +367,14 @@ def attention_decode_chunked(q: torch.Tensor, k_cache: torch.Tensor, v_cache: to
                              cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None) -> None:
     """``attention_decode`` on the tensor cores with a persistent grid: every sequence's pages are cut
     into chunks of about ``chunk_pages`` pages (a cut that depends on the sequence alone), a work item
-    is (sequence, chunk, kv head), and about two blocks per SM walk the items.  ``max_chunks`` bounds
-    the chunks of one sequence and sizes the scratch (:func:`attention_decode_chunked_scratch`); a
-    longer sequence gets ``max_chunks`` larger chunks."""
+    is (sequence, chunk, kv head), and as many blocks as the device holds at once walk the items.
+    ``chunk_pages`` 0: the kernel sizes the chunks itself so that the items about fill those blocks.
+    ``max_chunks`` bounds the chunks of one sequence and sizes the scratch
+    (:func:`attention_decode_chunked_scratch`); a longer sequence gets ``max_chunks`` larger chunks."""
     B = _attention_decode_checks(q, k_cache, v_cache, pos, slot, page_table, out, n_q, n_kv, head_dim, cos, sin,
                                  "attention_decode_chunked")
-    if chunk_pages < 1 or max_chunks < 1:
-        raise KernelError("attention_decode_chunked: chunk_pages and max_chunks must be at least 1")
+    if chunk_pages < 0 or max_chunks < 1:
+        raise KernelError("attention_decode_chunked: chunk_pages must not be negative, max_chunks at least 1")
     if max_chunks > 1:
         need_f, need_c = attention_decode_chunked_scratch(B, n_q, n_kv, head_dim, max_chunks)
         _need(scratch, "scratch", torch.float32); _need(counters, "counters", torch.int32)
