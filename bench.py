@@ -122,15 +122,15 @@ def time_decode(model, batch, prompt_len, steps, warmup, seed=0):
             sampler(model.step([StepEntry(s, [t], [0]) for s, t in zip(slots, nxt[w])]), slot_t, greedy)
         torch.cuda.synchronize()
         k0 = model.graph_kernels
+        bytes_first = model.decode_step_bytes(slots)              # host arithmetic, outside the timed region
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for k in range(steps):
             sampler(model.step([StepEntry(s, [t], [0]) for s, t in zip(slots, nxt[warmup + k])]), slot_t, greedy)
-            if k == steps // 2:
-                bytes_mid = model.decode_step_bytes(slots)        # host arithmetic only
         end.record()
         torch.cuda.synchronize()
         model.check_errors()
+        bytes_mid = (bytes_first + model.decode_step_bytes(slots)) // 2     # the cache grows by a token a step
         return start.elapsed_time(end) / steps, (model.graph_kernels - k0) // max(steps, 1) + 1, bytes_mid
     finally:
         for s in slots:

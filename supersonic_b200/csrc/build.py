@@ -15,6 +15,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -42,8 +43,23 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "attention_decode_static": {"sources": ["attention_decode_static.cu"], "flags": [], "link": []},
     "random_fill": {"sources": ["random_fill.cu"], "flags": [], "link": []},
 }
-HEADERS = ["common.cuh", "mma_helpers.cuh", "tc_helpers.cuh", "attention_decode.cuh", "attention_decode_mma.cuh",
-           "attention_decode_static.h"]
+_INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)
+
+
+def _sources_of(name: str) -> List[str]:
+    """The library's sources and every header beside them that they include, directly or not: what its
+    digest is taken over, so that a change to one kernel's header rebuilds only the libraries that use it."""
+    todo, seen = list(LIBRARIES[name]["sources"]), []
+    while todo:
+        f = todo.pop()
+        if f in seen:
+            continue
+        seen.append(f)
+        with open(os.path.join(_HERE, f), "r", encoding="utf-8") as fh:
+            for inc in _INCLUDE.findall(fh.read()):
+                if os.path.isfile(os.path.join(_HERE, inc)):
+                    todo.append(inc)
+    return sorted(seen)
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -87,7 +103,7 @@ def _build_dir() -> str:
 def _digest(name: str) -> str:
     spec = LIBRARIES[name]
     h = hashlib.sha256()
-    for f in list(spec["sources"]) + HEADERS:
+    for f in _sources_of(name):
         with open(os.path.join(_HERE, f), "rb") as fh:
             h.update(f.encode() + b"\0" + fh.read())
     h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + spec["flags"] + spec["link"]).encode())
