@@ -252,6 +252,7 @@ class Model:
         # prompt steps whose sizes recur are captured too (see PromptGraph)
         self.use_prompt_graphs = capturable and all(x is True for x in safe)
         self.max_prompt_graphs = 32
+        self.prompt_graph_max_tokens = 8192
         self._prompt_graphs: Dict[Any, PromptGraph] = {}
         self._prompt_seen: Dict[Any, int] = {}
         self.prompt_graph_replays = 0
@@ -312,7 +313,11 @@ class Model:
     def _prompt_step(self, packed: PackedStep) -> torch.Tensor:
         """Run a packed step: through its captured graph if these sizes have one, recording one if
         they come up for the second time, else launch by launch."""
-        if self.use_prompt_graphs and self._timed is None:
+        # a captured step keeps its logits and activations for as long as the model lives: only steps
+        # that are small enough for the host's share to matter, with few wanted rows, are recorded
+        small = packed.n_tokens <= self.prompt_graph_max_tokens and \
+            packed.n_want * self.spec.vocab_size * 4 <= (64 << 20)
+        if self.use_prompt_graphs and self._timed is None and small:
             key = packed.shape_key
             graph = self._prompt_graphs.get(key)
             if graph is None:
