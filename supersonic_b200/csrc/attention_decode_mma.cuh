@@ -11,8 +11,9 @@
 // of very unequal lengths then keeps every SM busy to the end, which a grid of (sequence, head,
 // split) with one split count for all does not.
 //
-// Per item the block's 4 warps fetch a page of keys and values into shared memory together
-// (cp.async, two stages, the swizzled tile layout of the prefill kernel); each warp takes 16 of
+// Per item one thread asks the TMA unit for a page of keys and values (tiled loads of 64 keys x 64
+// dims with the 128-byte swizzle, two stages, an mbarrier per stage that counts the bytes; every
+// wait is bounded and a wait that runs out is recorded in a device word); each warp takes 16 of
 // the page's 64 keys: S = Q K^T (16 x 16), online softmax in float32, O += P V.  Warps merge in
 // shared memory; a sequence of several chunks leaves partial results in scratch and the item that
 // arrives last for its (sequence, kv head) merges them in chunk order (same scratch layout as
@@ -26,10 +27,16 @@
 #pragma once
 #include "attention_decode.cuh"
 #include "mma_helpers.cuh"
+#include "tc_helpers.cuh"
+#include <mutex>
 
 constexpr int ADM_WARPS = 4;
 constexpr int ADM_THREADS = ADM_WARPS * 32;
 constexpr int ADM_ROWS = 16;          // query heads per kv head, padded to the MMA's 16 rows
+// Stages of the page ring (a stage: one page of keys and one of values, 32 KB at head size 128).  Three
+// and four stages measured the same as two at every batch and context tried: with two blocks on every
+// SM the loads in flight already cover the memory's latency.
+__host__ __device__ constexpr int adm_stages(int /*head_dim*/) { return 2; }
 constexpr int ADM_MAX_SEQS = 1024;    // sequences a launch can take (their slots, positions and chunk counts sit in shared memory)
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
@@ -40,13 +47,10 @@ struct AdmItem {
     bool owns_new;
 };
 
-template <int N> __device__ __forceinline__ void adm_wait_pending_at_most() { cp_async_wait<N>(); }
-// Wait until at most ``n`` of the newest cp.async groups are pending (a smaller bound is always right).
-__device__ __forceinline__ void adm_wait_pending(int n) {
-    if (n <= 0) cp_async_wait<0>();
-    else if (n == 1) cp_async_wait<1>();
-    else if (n == 2) cp_async_wait<2>();
-    else cp_async_wait<3>();
+// Byte offset of 16-byte chunk ``chunk`` of key ``row`` in a page tile as the TMA unit leaves it: one
+// box of 64 keys x 64 dims (128-byte rows, chunk c of row r at c ^ (r & 7)) per 64 dims, 8 KB apart.
+__device__ __forceinline__ uint32_t adm_tile_offset(int row, int chunk) {
+    return (uint32_t)(((chunk >> 3) << 13) + (row << 7) + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
 template <int HD, bool FUSE>
@@ -56,23 +60,30 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
                             const int* __restrict__ page_table, int max_pages, __nv_bfloat16* __restrict__ out,
                             int ldo, int n_seqs, int n_q, int n_kv, int window, float scale_log2, int chunk_pages,
                             int max_chunks, float* __restrict__ scratch, int* __restrict__ counters,
-                            const float* __restrict__ cos_t, const float* __restrict__ sin_t) {
-    constexpr int CHUNKS = HD / 8, TILE_BYTES = 64 * HD * 2, KS = HD / 16, HALF = HD / 2;
+                            const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                            const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            int* __restrict__ error_word) {
+    constexpr int CHUNKS = HD / 8, TILE_BYTES = 64 * HD * 2, KS = HD / 16, HALF = HD / 2, STAGES = adm_stages(HD);
     const int group = n_q / n_kv;
     // a query buffer: the item's query rows, the rotation tables' row, the token's own key and value
     const int Q_OFF = 0, COS_OFF = group * HD * 2, SIN_OFF = COS_OFF + HALF * 4, KN_OFF = SIN_OFF + HALF * 4,
               VN_OFF = KN_OFF + HD * 2, QBUF_BYTES = VN_OFF + HD * 2;
     // dynamic shared memory (adm_smem_bytes): tiles, warp sums, two query buffers, the batch's integers
     extern __shared__ __align__(128) unsigned char adm_smem[];
-    unsigned char* smem = adm_smem;                              // K stage 0, K stage 1, V stage 0, V stage 1
+    // the stages' key tiles, then their value tiles: swizzled tiles start on 1,024-byte boundaries
+    unsigned char* smem = adm_smem + ((1024u - (smem_u32(adm_smem) & 1023u)) & 1023u);
     constexpr int ACC_LD = HD + 4;       // row pitch of the warp sums: rows g and g + 1 land four banks apart
-    float* sm_acc = reinterpret_cast<float*>(smem + 4 * TILE_BYTES);          // [ADM_WARPS][group][ACC_LD]
-    unsigned char* qbufs = smem + 4 * TILE_BYTES + ADM_WARPS * group * ACC_LD * 4;
+    float* sm_acc = reinterpret_cast<float*>(smem + 2 * STAGES * TILE_BYTES);          // [ADM_WARPS][group][ACC_LD]
+    unsigned char* qbufs = smem + 2 * STAGES * TILE_BYTES + ADM_WARPS * group * ACC_LD * 4;
     int* cum = reinterpret_cast<int*>(qbufs + 2 * QBUF_BYTES);   // [n_seqs + 1] chunks of the sequences before each one
     int* sm_slot = cum + n_seqs + 1;                             // [n_seqs] the batch's slots and positions, read once
     int* sm_pos = sm_slot + n_seqs;
     __shared__ float sm_m[ADM_WARPS][ADM_ROWS], sm_l[ADM_WARPS][ADM_ROWS];
     __shared__ int is_last;
+    __shared__ __align__(8) unsigned long long full_bar[STAGES];      // a stage's bytes have landed
+    __shared__ int sm_abort[2];                                  // [0]: a wait ran out; [1]: stays zero
+    volatile int* abort_flag = sm_abort;
+    const uint32_t full0 = smem_u32(full_bar);
     __shared__ int warp_total[ADM_WARPS], warp_longest[ADM_WARPS], warp_live[ADM_WARPS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 
@@ -80,6 +91,13 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
     // Positions, slots and page tables were written before this chain of kernels began: they may be
     // read before the dependency wait, and so may pages of earlier steps' keys.
     for (int b = threadIdx.x; b < n_seqs; b += ADM_THREADS) { sm_slot[b] = slot[b]; sm_pos[b] = pos[b]; }
+    if (threadIdx.x == 0) {
+        for (int st = 0; st < STAGES; ++st) mbar_init(full0 + 8 * st, 1);
+        abort_flag[0] = 0;
+        abort_flag[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
     __syncthreads();
     auto pages_of = [&](int b) {
         if (sm_slot[b] < 0) return 0;                            // a padding row is no work item (zeros below)
@@ -176,17 +194,19 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
         I.page0 = pt[min(I.pf, I.page_hi)];
         I.page1 = pt[min(I.pf + 1, I.page_hi)];
     };
-    int page_ahead = 0, page_ahead_of = -1;      // id of the page two after the one in work, asked for one turn early
+    int page_ahead = 0, page_ahead_of = -1;      // id of the page STAGES after the one in work, asked for one turn early
     auto load_page = [&](const AdmItem& I, int i, int stage) {
+        if (threadIdx.x != 0) return;
         const int page = i == 0 ? I.page0 : (i == 1 ? I.page1 : (i == page_ahead_of ? page_ahead
                          : page_table[(size_t)I.slot * max_pages + min(I.pf + i, I.page_hi)]));
-        const size_t base = ((size_t)page * n_kv + I.kvh) * (size_t)(64 * HD);
-        const uint32_t kd = (uint32_t)__cvta_generic_to_shared(smem + stage * TILE_BYTES);
-        const uint32_t vd = (uint32_t)__cvta_generic_to_shared(smem + (2 + stage) * TILE_BYTES);
-        for (int e = threadIdx.x; e < 64 * CHUNKS; e += ADM_THREADS) {
-            const int r = e / CHUNKS, c = e % CHUNKS;
-            cp_async16(kd + tile_offset<HD>(r, c), k_cache + base + (size_t)r * HD + c * 8);
-            cp_async16(vd + tile_offset<HD>(r, c), v_cache + base + (size_t)r * HD + c * 8);
+        const int y = (page * n_kv + I.kvh) << 6;                // the page's first key among the cache's rows
+        const uint32_t kd = smem_u32(smem + stage * TILE_BYTES), vd = smem_u32(smem + (STAGES + stage) * TILE_BYTES);
+        const uint32_t bar = full0 + 8 * stage;
+        mbar_expect_tx(bar, 2 * TILE_BYTES);
+#pragma unroll
+        for (int h = 0; h < HD / 64; ++h) {
+            tma_load_2d(kd + h * 8192, &map_k, bar, 64 * h, y);
+            tma_load_2d(vd + h * 8192, &map_v, bar, 64 * h, y);
         }
     };
     auto load_query = [&](const AdmItem& I, int which) {
@@ -221,9 +241,9 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
         return;
     }
 
-    // The stream of cp.async groups: for every item of this block its query buffer, then its pages
-    // one by one.  Groups are numbered as they are issued; a page goes to stage (page unit & 1), a
-    // query to buffer (item & 1); up to two page units are in flight, across item borders, so the
+    // The stream of loads: for every item of this block its query buffer (cp.async by all threads, one
+    // group), then its pages one by one (TMA, thread 0).  A page goes to stage (page unit % STAGES), a
+    // query to buffer (item & 1); up to STAGES page units are in flight, across item borders, so the
     // fixed cost of an item (its slot, position, page ids, query rows) hides behind the item before it.
     // A chunk's arrival at its (sequence, kv head) counter is counted when the chunk's sums are
     // written, but the answer (was it the last?) is looked at only when the next item's sums are
@@ -283,47 +303,40 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
     bool has_nxt = item + G < total_items, has_nn = item + 2 * G < total_items;
     if (has_nxt) decode(item + G, nxt);
     if (has_nn) decode(item + 2 * G, nn);
-    int n_groups = 0;                    // groups issued so far
     int pu_issued = 0, pu_done = 0;      // page units issued / consumed
-    int cursor_item = 0, cursor_pos = 0; // next group to issue: item 0 = cur, 1 = nxt; position -1 = query, else page
-    int grp_of_stage[2] = {0, 0}, grp_of_query[2] = {0, 0};
+    int cursor_item = 0, cursor_pos = 0; // next load to issue: item 0 = cur, 1 = nxt; position -1 = query, else page
     int parity = 0;                      // of cur among this block's items
+    bool dead = false;                   // a bounded wait ran out: the block stops (block-uniform)
 
     auto issue_group = [&]() -> bool {
         if (cursor_item > 1 || (cursor_item == 1 && !has_nxt)) return false;
         const AdmItem& I = cursor_item == 0 ? cur : nxt;
         if (cursor_pos < 0) {
-            const int which = parity ^ cursor_item;
-            load_query(I, which);
-            grp_of_query[which] = n_groups;
+            load_query(I, parity ^ cursor_item);
+            cp_async_commit();
             cursor_pos = 0;
         } else {
-            load_page(I, cursor_pos, pu_issued & 1);
-            grp_of_stage[pu_issued & 1] = n_groups;
+            load_page(I, cursor_pos, pu_issued % STAGES);
             ++pu_issued;
             if (++cursor_pos == I.units) { ++cursor_item; cursor_pos = -1; }
         }
-        cp_async_commit();
-        ++n_groups;
         return true;
     };
-    auto fill = [&]() { while (pu_issued < pu_done + 2 && issue_group()) {} };
+    auto fill = [&]() { while (pu_issued < pu_done + STAGES && issue_group()) {} };
 
     // the first item: its pages may be asked for before the dependency wait; its query, and anything
     // of the item after it, only after
-    while (pu_issued < 2 && cursor_item == 0) issue_group();
+    while (pu_issued < STAGES && cursor_item == 0) issue_group();
     if (!waited) { ssb_pdl_wait(); waited = true; }
     load_query(cur, 0);
-    grp_of_query[0] = n_groups;
     cp_async_commit();
-    ++n_groups;
     fill();
 
     while (true) {
         const int b = cur.b, kvh = cur.kvh, h0 = kvh * group, p = cur.p;
         const int key_lo = cur.key_lo, key_hi = cur.key_hi;
         const unsigned char* qb = qbufs + parity * QBUF_BYTES;
-        adm_wait_pending(n_groups - 1 - grp_of_query[parity]);
+        cp_async_wait<0>();                                      // this item's query (and, harmlessly, the next one's)
         __syncthreads();
 
         // Query fragments: row = head (g and g + 8), this lane's columns 16 ks + 2t (+1, +8, +9).
@@ -377,15 +390,16 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
         float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // l: this lane's share of the row sum
 
         for (int i = 0; i < cur.units; ++i) {
-            if (i + 2 < cur.units) {     // needed when this turn ends: a turn's arithmetic hides the load
-                page_ahead = page_table[(size_t)cur.slot * max_pages + min(cur.pf + i + 2, cur.page_hi)];
-                page_ahead_of = i + 2;
+            if (i + STAGES < cur.units) {     // needed when this turn ends: a turn's arithmetic hides the load
+                page_ahead = page_table[(size_t)cur.slot * max_pages + min(cur.pf + i + STAGES, cur.page_hi)];
+                page_ahead_of = i + STAGES;
             }
-            const int stage = pu_done & 1;
-            adm_wait_pending(n_groups - 1 - grp_of_stage[stage]);
-            __syncthreads();
+            const int stage = pu_done % STAGES;
+            const bool landed = mbar_wait(full0 + 8 * stage, (pu_done / STAGES) & 1, abort_flag);
+            if (!landed) abort_flag[0] = 1;
+            if (!__syncthreads_and(landed)) { dead = true; break; }
             const uint32_t kbase = (uint32_t)__cvta_generic_to_shared(smem + stage * TILE_BYTES);
-            const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(smem + (2 + stage) * TILE_BYTES);
+            const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(smem + (STAGES + stage) * TILE_BYTES);
             const int key0 = ((cur.pf + i) << 6) + 16 * warp;    // this warp's 16 keys of the page
             if (key0 <= key_hi && key0 + 15 >= key_lo) {
                 float sc[2][4];
@@ -395,7 +409,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
                 for (int ks = 0; ks < KS; ++ks) {
                     uint32_t b0, b1, b2, b3;
                     const int key = 16 * warp + ((lane >> 4) << 3) + (lane & 7);
-                    ldmatrix_x4(kbase + tile_offset<HD>(key, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
+                    ldmatrix_x4(kbase + adm_tile_offset(key, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
                     mma16816(sc[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
                     mma16816(sc[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
                 }
@@ -436,7 +450,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
                 for (int jp = 0; jp < HD / 16; ++jp) {
                     uint32_t b0, b1, b2, b3;
                     const int key = 16 * warp + (((lane >> 3) & 1) << 3) + (lane & 7);
-                    ldmatrix_x4_trans(vbase + tile_offset<HD>(key, jp * 2 + (lane >> 4)), b0, b1, b2, b3);
+                    ldmatrix_x4_trans(vbase + adm_tile_offset(key, jp * 2 + (lane >> 4)), b0, b1, b2, b3);
                     mma16816(o[2 * jp], a0, a1, a2, a3, b0, b1);
                     mma16816(o[2 * jp + 1], a0, a1, a2, a3, b2, b3);
                 }
@@ -445,6 +459,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
             ++pu_done;
             fill();                                              // this item's next pages, or the next item's query and pages
         }
+        if (dead) break;
 
         if (FUSE && cur.owns_new && warp == 0) {
             // the token's own key and value, from the projection's output; all of this is lane-local
@@ -567,8 +582,15 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
         has_nn = item + 2 * G < total_items;
         if (has_nn) decode(item + 2 * G, nn);
     }
-    settle();
     cp_async_wait<0>();
+    if (!dead) { settle(); return; }
+    // A page did not land in time: the launch's result is invalid and the host is told.  Loads that were
+    // asked for may still arrive, so the block stays (for a bounded time) until its shared memory is quiet.
+    if (threadIdx.x == 0) {
+        atomicCAS(error_word, 0, TC_ERR_PRODUCER);
+        for (int u = pu_done; u < pu_issued; ++u) mbar_wait(full0 + 8 * (u % STAGES), (u / STAGES) & 1, abort_flag + 1);
+    }
+    __syncthreads();
 }
 
 // Whether the tensor-core kernel takes this case (else attention_decode.cuh's kernel does).
@@ -584,13 +606,13 @@ static inline long long adm_scratch_floats(int n_seqs, int n_q, int head_dim, in
 }
 static inline int adm_counters(int n_seqs, int n_kv) { return n_seqs * n_kv; }
 
-// Dynamic shared memory of a block: four tiles (two stages of keys and values), the warps' sums, two
+// Dynamic shared memory of a block: the ring's tiles (two stages of keys and values), the warps' sums, two
 // query buffers, and three integers per sequence of the batch.  Head size 128 with four query heads
 // per kv head and 64 sequences: 78 KB, so two blocks share an SM with room to spare.
 static inline int adm_smem_bytes(int head_dim, int group, int n_seqs) {
-    const int tiles = 4 * 64 * head_dim * 2, sums = ADM_WARPS * group * (head_dim + 4) * 4;
+    const int tiles = 2 * adm_stages(head_dim) * 64 * head_dim * 2, sums = ADM_WARPS * group * (head_dim + 4) * 4;
     const int query = group * head_dim * 2 + head_dim * 4 + head_dim * 4;
-    return tiles + sums + 2 * query + ((3 * n_seqs + 1) * 4 + 15) / 16 * 16;
+    return 1024 + tiles + sums + 2 * query + ((3 * n_seqs + 1) * 4 + 15) / 16 * 16;      // 1,024: the tiles' alignment
 }
 
 static inline int adm_sm_count() {
@@ -643,16 +665,39 @@ static inline long long adm_resident_blocks(int head_dim, bool fuse, int group, 
     return per_sm > 0 ? (long long)per_sm * adm_sm_count() : 0;
 }
 
+// The tensor map of a cache (keys or values): cache_rows x head_dim bfloat16, boxes of one page's 64
+// keys x 64 dims.  Encoding one costs the host a microsecond or two, so the maps of the caches seen
+// so far are kept (a map depends on the address and the sizes alone).
+struct AdmMapEntry { const void* base; long long rows; int head_dim; CUtensorMap map; };
+static inline int adm_cache_map(const void* base, long long rows, int head_dim, CUtensorMap* map) {
+    constexpr int KEPT = 256;
+    static AdmMapEntry kept[KEPT];
+    static int n_kept = 0;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < n_kept; ++i)
+        if (kept[i].base == base && kept[i].rows == rows && kept[i].head_dim == head_dim) { *map = kept[i].map; return 0; }
+    if (rows <= 0 || rows > 0x7fffffffLL) return SSB_ERR_BAD_SIZE;
+    const int rc = make_map(map, base, (int)rows, head_dim, head_dim, 64);
+    if (rc) return rc;
+    if (n_kept == KEPT) n_kept = 0;
+    kept[n_kept].base = base; kept[n_kept].rows = rows; kept[n_kept].head_dim = head_dim; kept[n_kept].map = *map;
+    ++n_kept;
+    return 0;
+}
+
 // chunk_pages: pages per chunk, or 0 for the kernel to size the chunks from the batch (see there);
 // max_chunks: the most chunks a sequence is cut into (it sizes the scratch): a sequence that would need
-// more gets max_chunks larger ones.
+// more gets max_chunks larger ones.  cache_rows: keys the caches have room for (pages x kv heads x 64);
+// error_word: where a wait that ran out is recorded (zero otherwise).
 static inline int adm_launch(const void* q, int ldq, const void* k_cache, const void* v_cache, const int* pos,
                              const int* slot, const int* page_table, int max_pages, void* out, int ldo,
                              int n_seqs, int n_q, int n_kv, int head_dim, int window, float scale, int chunk_pages,
                              int max_chunks, float* scratch, int* counters, cudaStream_t stream, bool pdl,
-                             const float* cos_t, const float* sin_t) {
+                             const float* cos_t, const float* sin_t, long long cache_rows, int* error_word) {
     typedef __nv_bfloat16 bf16;
     if (n_seqs <= 0) return 0;
+    if (!error_word) return SSB_ERR_BAD_SIZE;
     if (n_seqs > ADM_MAX_SEQS || chunk_pages < 0 || max_chunks < 1 || (max_chunks > 1 && (!scratch || !counters)))
         return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return SSB_ERR_BAD_SIZE;
@@ -663,7 +708,10 @@ static inline int adm_launch(const void* q, int ldq, const void* k_cache, const 
     const long long resident = adm_resident_blocks(head_dim, fuse, n_q / n_kv, n_seqs);
     if (resident <= 0) return SSB_ERR_UNSUPPORTED;
     dim3 grid((unsigned)(items < resident ? items : resident));
-    int rc = 0;
+    CUtensorMap map_k, map_v;
+    int rc = adm_cache_map(k_cache, cache_rows, head_dim, &map_k);
+    if (!rc) rc = adm_cache_map(v_cache, cache_rows, head_dim, &map_v);
+    if (rc) return rc;
 #define SSB_ADM(HD_, FUSE_) do { \
         const int smem_bytes = adm_smem_bytes(HD_, n_q / n_kv, n_seqs); \
         cudaError_t e = adm_ensure_smem<HD_, FUSE_>(smem_bytes); \
@@ -671,7 +719,7 @@ static inline int adm_launch(const void* q, int ldq, const void* k_cache, const 
         rc = ssb_launch(attention_decode_mma_kernel<HD_, FUSE_>, grid, dim3(ADM_THREADS), (size_t)smem_bytes, stream, pdl, \
                         (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
                         (bf16*)out, ldo, n_seqs, n_q, n_kv, window, scale_log2, chunk_pages, max_chunks, scratch, \
-                        counters, cos_t, sin_t); \
+                        counters, cos_t, sin_t, map_k, map_v, error_word); \
     } while (0)
     if (head_dim == 64) { if (fuse) SSB_ADM(64, true); else SSB_ADM(64, false); }
     else if (head_dim == 128) { if (fuse) SSB_ADM(128, true); else SSB_ADM(128, false); }

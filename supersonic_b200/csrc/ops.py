@@ -370,7 +370,9 @@ def attention_decode_chunked(q: torch.Tensor, k_cache: torch.Tensor, v_cache: to
     is (sequence, chunk, kv head), and as many blocks as the device holds at once walk the items.
     ``chunk_pages`` 0: the kernel sizes the chunks itself so that the items about fill those blocks.
     ``max_chunks`` bounds the chunks of one sequence and sizes the scratch
-    (:func:`attention_decode_chunked_scratch`); a longer sequence gets ``max_chunks`` larger chunks."""
+    (:func:`attention_decode_chunked_scratch`); a longer sequence gets ``max_chunks`` larger chunks.
+    Pages come in through the TMA unit with bounded waits (:func:`check_device_errors`)."""
+    global _tc_unchecked
     B = _attention_decode_checks(q, k_cache, v_cache, pos, slot, page_table, out, n_q, n_kv, head_dim, cos, sin,
                                  "attention_decode_chunked")
     if chunk_pages < 0 or max_chunks < 1:
@@ -385,7 +387,9 @@ def attention_decode_chunked(q: torch.Tensor, k_cache: torch.Tensor, v_cache: to
         c_int(page_table.shape[1]), _ptr(out), c_int(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv),
         c_int(head_dim), c_int(page_shift), c_int(int(window) if window else 0), c_float(scale),
         c_int(chunk_pages), c_int(max_chunks), _ptr(scratch), _ptr(counters), c_int(1 if pdl else 0), _ptr(cos),
-        _ptr(sin), _stream()), "attention_decode_chunked")
+        _ptr(sin), c_longlong(k_cache.numel() // head_dim), _ptr(tc_error_word(q.device)), _stream()),
+        "attention_decode_chunked")
+    _tc_unchecked += 1
 
 
 # ---- prefill GEMM on tcgen05 ---------------------------------------------------------------
