@@ -1,7 +1,7 @@
 """The bfloat16 kernel set used for serving: a fast kernel where one exists for the shape at
 hand, the plain kernel (same arithmetic, bfloat16 storage) otherwise.
 
-Decode steps (up to 64 rows) run the tcgen05 projections that stream the weights once
+Steps of up to 128 rows (decode, short prompts) run the tcgen05 projections that stream the weights once
 (``gemv_tc``), with SwiGLU folded into the gate/up projection, and the tensor-core split-key
 attention with rotation and cache append inside; prompts run the persistent tcgen05 GEMM and
 the tcgen05 flash attention.  Which kernel a shape gets is decided here and nowhere else; the
@@ -18,6 +18,7 @@ from .kernel_sets import NormedInput, PlainKernels, as_tensor
 
 TARGET_BLOCKS = 1184           # eight small blocks per SM
 DETERMINISTIC_CHUNK_PAGES = 16 # ... and its fixed chunk size (1,024 keys) when results must not depend on the batch
+STREAM_ROWS = ops.GEMV_TC_MAX_ROWS   # steps of up to this many rows take the projections that stream the weights once
 TC_ATTENTION_MIN_NEW = 96     # prompts at least this long take the tcgen05 attention (tiles of 128 rows)
 
 
@@ -74,12 +75,12 @@ class FastKernels(PlainKernels):
                 # whatever else is in the step (decode steps pay for it: few blocks stream the weights)
                 ops.gemm_tc(x, weight, out, ops.TC_ACCUMULATE if accumulate else ops.TC_STORE,
                             tile_n=ops.TC_TILE_PAIR if self._pair_tiles(rows, n) else self._tile_n(rows, n))
-            elif rows <= 64 and accumulate:
+            elif rows <= STREAM_ROWS and accumulate:
                 # weights on the M side, K split over blocks that add with float atomics
                 ops.gemv_tc(x, weight, out, ops.TC_ACCUMULATE, splits=ops.gemv_tc_splits(n, k), pdl=self.pdl)
-            elif rows <= 64 and n >= 16384:
+            elif rows <= STREAM_ROWS and n >= 16384:
                 ops.gemv_tc(x, weight, out, ops.TC_STORE, pdl=self.pdl)
-            elif rows <= 64 and out.dtype == torch.bfloat16 and n % 8 == 0 and out.stride(0) % 8 == 0:
+            elif rows <= STREAM_ROWS and out.dtype == torch.bfloat16 and n % 8 == 0 and out.stride(0) % 8 == 0:
                 # too few row tiles for the SMs (48 for the 8B query/key/value projection): K is split
                 # over blocks that add with float atomics into a float32 scratch that is zero between
                 # uses; a small kernel rounds the sums into ``out`` and clears the scratch again
@@ -145,7 +146,7 @@ class FastKernels(PlainKernels):
         if layout == "interleaved":
             xt = as_tensor(x)
             if w_gate_up.shape[0] % 16 == 0 and ops.gemm_tc_ok(xt, w_gate_up, out):
-                if rows <= 64 and not self.deterministic:
+                if rows <= STREAM_ROWS and not self.deterministic:
                     ops.gemv_tc(xt, w_gate_up, out, ops.TC_SWIGLU, pdl=self.pdl)
                 else:
                     n2 = w_gate_up.shape[0]

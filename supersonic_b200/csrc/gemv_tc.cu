@@ -1,7 +1,7 @@
-// Decode projections for 17 to 64 rows on tcgen05: out[b, n] = sum_k x[b, k] W[n, k], with the
+// Projections of up to 128 rows (decode steps, short prompts) on tcgen05: out[b, n] = sum_k x[b, k] W[n, k], with the
 // weights as the M side of the MMA.  A block owns 128 rows of W and a range of K; 128 x 64 tiles
 // of W (16 KB of useful bytes a stage) and the matching columns of x arrive through TMA into an
-// four-stage ring; one thread issues tcgen05.mma (M 128, N = rows rounded up to 16/32/64); the
+// four-stage ring; one thread issues tcgen05.mma (M 128, N = rows rounded up to 16/32/64/128); the
 // accumulator [W row, batch row] sits in tensor memory.  When K is split over several blocks
 // (few row tiles: the small projections), a store or SwiGLU output goes through scratch: each
 // block writes its partial tile and the block that arrives last for the tile adds them in split
@@ -24,11 +24,12 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int GV_BM = 128;                // rows of W per block
 // stages of the ring: as many as let two blocks share an SM (no second wave for 149..296 blocks):
-// 18 KB a stage at up to 16 batch rows, 20 KB at 32, 24 KB at 64
-__host__ __device__ constexpr int gv_stages(int bnb) { return bnb <= 16 ? 6 : (bnb <= 32 ? 5 : 4); }
+// 18 KB a stage at up to 16 batch rows, 20 KB at 32, 24 KB at 64, 32 KB at 128
+__host__ __device__ constexpr int gv_stages(int bnb) { return bnb <= 16 ? 6 : (bnb <= 32 ? 5 : (bnb <= 64 ? 4 : 3)); }
+constexpr int GV_MAX_ROWS = 128;
 constexpr int GV_THREADS = 192;           // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
 
-template <int BNB>                        // batch rows per tile: 16, 32 or 64
+template <int BNB>                        // batch rows per tile: 16, 32, 64 or 128
 __global__ void __launch_bounds__(GV_THREADS, 2)
 gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                void* __restrict__ out, int ldo, int out_is_f32, int n_rows, int N, int K, int mode, int splits,
@@ -123,11 +124,13 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (ok) tc_commit(acc_full);
         }
     } else {
-        // epilogue: thread = one row of W (tensor-memory lane), BNB batch columns
+        // epilogue: thread = one row of W (tensor-memory lane); the BNB batch columns are taken CW at a
+        // time so that a pass's sums fit the registers
+        constexpr int CW = BNB < 64 ? BNB : 64;
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;                   // row within the tile
         const int n = n0 + r;
-        float v[BNB];
+        float v[CW];
         ssb_pdl_wait();                                      // out and the scratch may still be the predecessor's
         bool ok = true;
         if (my_blocks > 0) {
@@ -136,33 +139,38 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps agree on the outcome
         ok = abort_flag[0] == 0;
-        if (my_blocks > 0) {
-            if (ok) {
-                tc_fence_after();
+        if (ok && my_blocks > 0) tc_fence_after();
+        // this block's sums of columns c0 .. c0 + CW - 1 (zeros for a block without k-blocks)
+        auto own_sums = [&](int c0) {
+            if (my_blocks > 0) {
 #pragma unroll
-                for (int c = 0; c < (BNB + 31) / 32; ++c) {
+                for (int c = 0; c < (CW + 31) / 32; ++c) {
                     uint32_t raw[32];
-                    tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + c * 32, raw);
+                    tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + c0 + c * 32, raw);
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
-                        if (c * 32 + j < BNB) v[c * 32 + j] = __uint_as_float(raw[j]);
+                        if (c * 32 + j < CW) v[c * 32 + j] = __uint_as_float(raw[j]);
                 }
-            }
-        } else {
+            } else {
 #pragma unroll
-            for (int j = 0; j < BNB; ++j) v[j] = 0.f;
-        }
+                for (int j = 0; j < CW; ++j) v[j] = 0.f;
+            }
+        };
         // Adding into the float32 residual with K split over blocks and no scratch: each block adds its
         // share straight in (red.global.add.f32).  The order in which shares meet varies from run to
         // run, so the last bits of the residual may; everything else uses the ordered fix-up below.
         // With scratch given, an add is ordered too: the last block of the tile adds the sum of the shares.
         const bool atomic_add = splits > 1 && mode == TC_ACCUMULATE && partials == nullptr;
-        if (ok && splits > 1 && !atomic_add) {
+        const bool through_scratch = splits > 1 && !atomic_add;
+        if (ok && through_scratch) {
             // partial tile to scratch; the block that arrives last adds all of them in split order
             float* mine = partials + (((size_t)tile * splits + split) * GV_BM + r) * BNB;
+            for (int c0 = 0; c0 < BNB; c0 += CW) {
+                own_sums(c0);
 #pragma unroll
-            for (int j = 0; j < BNB; j += 4)
-                *reinterpret_cast<float4*>(mine + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                for (int j = 0; j < CW; j += 4)
+                    *reinterpret_cast<float4*>(mine + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
             if (warp == 2 && lane == 0) {
@@ -172,40 +180,44 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             ok = *is_last != 0;
-            if (ok) {
-                __threadfence();
-#pragma unroll
-                for (int j = 0; j < BNB; ++j) v[j] = 0.f;
-                for (int sp = 0; sp < splits; ++sp) {
-                    const float* p = partials + (((size_t)tile * splits + sp) * GV_BM + r) * BNB;
-#pragma unroll
-                    for (int j = 0; j < BNB; j += 4) {
-                        const float4 t4 = __ldcg(reinterpret_cast<const float4*>(p + j));
-                        v[j] += t4.x; v[j + 1] += t4.y; v[j + 2] += t4.z; v[j + 3] += t4.w;
-                    }
-                }
-            }
+            if (ok) __threadfence();
         }
         if (ok) {
-            if (mode == TC_SWIGLU) {
-                // rows come as [8 gate | 8 up] per 16: the up value of gate row r sits 8 lanes further
-                const bool is_gate = (r & 15) < 8;
-                const int n_out = n0 / 2 + (r >> 4) * 8 + (r & 7);
+            for (int c0 = 0; c0 < BNB; c0 += CW) {
+                if (through_scratch) {
 #pragma unroll
-                for (int j = 0; j < BNB; ++j) {
-                    const float up = __shfl_down_sync(0xffffffffu, v[j], 8);
-                    if (is_gate && j < n_rows && n + 8 < N)
-                        ((bf16*)out)[(size_t)j * ldo + n_out] = __float2bfloat16_rn(v[j] / (1.0f + __expf(-v[j])) * up);
+                    for (int j = 0; j < CW; ++j) v[j] = 0.f;
+                    for (int sp = 0; sp < splits; ++sp) {
+                        const float* p = partials + (((size_t)tile * splits + sp) * GV_BM + r) * BNB + c0;
+#pragma unroll
+                        for (int j = 0; j < CW; j += 4) {
+                            const float4 t4 = __ldcg(reinterpret_cast<const float4*>(p + j));
+                            v[j] += t4.x; v[j + 1] += t4.y; v[j + 2] += t4.z; v[j + 3] += t4.w;
+                        }
+                    }
+                } else {
+                    own_sums(c0);
                 }
-            } else if (n < N) {
+                if (mode == TC_SWIGLU) {
+                    // rows come as [8 gate | 8 up] per 16: the up value of gate row r sits 8 lanes further
+                    const bool is_gate = (r & 15) < 8;
+                    const int n_out = n0 / 2 + (r >> 4) * 8 + (r & 7);
 #pragma unroll
-                for (int j = 0; j < BNB; ++j) {
-                    if (j >= n_rows) break;
-                    const size_t o = (size_t)j * ldo + n;
-                    if (atomic_add) { if (my_blocks > 0) atomicAdd((float*)out + o, v[j]); }
-                    else if (mode == TC_ACCUMULATE) ((float*)out)[o] += v[j];
-                    else if (out_is_f32) ((float*)out)[o] = v[j];
-                    else ((bf16*)out)[o] = __float2bfloat16_rn(v[j]);
+                    for (int j = 0; j < CW; ++j) {
+                        const float up = __shfl_down_sync(0xffffffffu, v[j], 8);
+                        if (is_gate && c0 + j < n_rows && n + 8 < N)
+                            ((bf16*)out)[(size_t)(c0 + j) * ldo + n_out] = __float2bfloat16_rn(v[j] / (1.0f + __expf(-v[j])) * up);
+                    }
+                } else if (n < N) {
+#pragma unroll
+                    for (int j = 0; j < CW; ++j) {
+                        if (c0 + j >= n_rows) break;
+                        const size_t o = (size_t)(c0 + j) * ldo + n;
+                        if (atomic_add) { if (my_blocks > 0) atomicAdd((float*)out + o, v[j]); }
+                        else if (mode == TC_ACCUMULATE) ((float*)out)[o] += v[j];
+                        else if (out_is_f32) ((float*)out)[o] = v[j];
+                        else ((bf16*)out)[o] = __float2bfloat16_rn(v[j]);
+                    }
                 }
             }
         }
@@ -236,26 +248,29 @@ static int launch_gv(const CUtensorMap& mw, const CUtensorMap& mx, void* out, in
     return rc ? rc : ssb_launch_status();
 }
 
+static inline int gv_bnb(int n_rows) { return n_rows <= 16 ? 16 : (n_rows <= 32 ? 32 : (n_rows <= 64 ? 64 : 128)); }
+SSB_API int ssb_gemv_tc_max_rows() { return GV_MAX_ROWS; }
+
 // Scratch for a launch with splits > 1: floats for the partial tiles, ints (zeroed once) for the counters.
 SSB_API long long ssb_gemv_tc_scratch_floats(int n_rows, int N, int splits) {
-    const int bnb = n_rows <= 16 ? 16 : (n_rows <= 32 ? 32 : 64);
+    const int bnb = gv_bnb(n_rows);
     return splits > 1 ? (long long)((N + GV_BM - 1) / GV_BM) * splits * GV_BM * bnb : 0;
 }
 SSB_API int ssb_gemv_tc_counters(int N) { return (N + GV_BM - 1) / GV_BM; }
 
-// x: bfloat16 [n_rows <= 64, K]; W: bfloat16 [N, K]; modes as ssb_gemm_tc.  splits: blocks that
+// x: bfloat16 [n_rows <= 128, K]; W: bfloat16 [N, K]; modes as ssb_gemm_tc.  splits: blocks that
 // share the K range of a row tile (1 = none).
 SSB_API int ssb_gemv_tc(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int out_dtype,
                         int n_rows, int N, int K, int mode, int splits, float* partials, int* counters,
                         int* error_word, int pdl, cudaStream_t stream) {
     if (n_rows <= 0 || N <= 0) return 0;
-    if (n_rows > 64 || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || !error_word || splits < 1) return SSB_ERR_BAD_SIZE;
+    if (n_rows > GV_MAX_ROWS || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || !error_word || splits < 1) return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)x | (uintptr_t)W | (uintptr_t)partials) & 15) return SSB_ERR_BAD_SIZE;
     if (splits > 1 && (mode != TC_ACCUMULATE || partials) && (!partials || !counters)) return SSB_ERR_BAD_SIZE;
     if (splits > (K + TC_BK - 1) / TC_BK) return SSB_ERR_BAD_SIZE;
     if (mode == TC_ACCUMULATE && out_dtype != SSB_F32) return SSB_ERR_BAD_DTYPE;
     if (mode == TC_SWIGLU && (out_dtype != SSB_BF16 || N % 16)) return SSB_ERR_BAD_SIZE;
-    const int bnb = n_rows <= 16 ? 16 : (n_rows <= 32 ? 32 : 64);
+    const int bnb = gv_bnb(n_rows);
     CUtensorMap mw, mx;
     int rc = make_map(&mw, W, N, K, ldw, GV_BM);
     if (rc) return rc;
@@ -264,5 +279,6 @@ SSB_API int ssb_gemv_tc(const void* x, int ldx, const void* W, int ldw, void* ou
     const int f32o = out_dtype == SSB_F32;
     if (bnb == 16) return launch_gv<16>(mw, mx, out, ldo, f32o, n_rows, N, K, mode, splits, partials, counters, error_word, pdl != 0, stream);
     if (bnb == 32) return launch_gv<32>(mw, mx, out, ldo, f32o, n_rows, N, K, mode, splits, partials, counters, error_word, pdl != 0, stream);
-    return launch_gv<64>(mw, mx, out, ldo, f32o, n_rows, N, K, mode, splits, partials, counters, error_word, pdl != 0, stream);
+    if (bnb == 64) return launch_gv<64>(mw, mx, out, ldo, f32o, n_rows, N, K, mode, splits, partials, counters, error_word, pdl != 0, stream);
+    return launch_gv<128>(mw, mx, out, ldo, f32o, n_rows, N, K, mode, splits, partials, counters, error_word, pdl != 0, stream);
 }

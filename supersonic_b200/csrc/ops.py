@@ -661,6 +661,9 @@ def sm_count() -> int:
     return _sm_counts[dev]
 
 
+GEMV_TC_MAX_ROWS = 128     # rows of x that gemv_tc takes (the N side of its MMA: 16, 32, 64 or 128)
+
+
 def gemv_tc_splits(n: int, k: int) -> int:
     """Blocks that share the K range of one 128-row tile of W: up to two blocks per SM in all
     (every SM must pull for the memory system to be busy), at least 8 k-blocks (512 columns) each."""
@@ -678,7 +681,7 @@ def gemv_tc_scratch(rows: int, n: int, splits: int):
 def gemv_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_STORE, splits: int = 1,
             partials: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None,
             pdl: bool = False) -> None:
-    """out = x @ w^T for up to 64 rows with the weights as the M side of tcgen05.mma (they stream
+    """out = x @ w^T for up to 128 rows with the weights as the M side of tcgen05.mma (they stream
     once, 16 KB a stage).  ``splits`` > 1 shares the K range of a row tile among blocks: store
     and SwiGLU outputs then need ``partials``/``counters`` sized by :func:`gemv_tc_scratch`
     (counters zeroed once) and are summed in a fixed order; mode accumulate adds with float
@@ -687,7 +690,7 @@ def gemv_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = TC_
     B, K = x.shape
     N = w.shape[0]
     n_out = N // 2 if mode == TC_SWIGLU else N
-    if w.shape[1] != K or tuple(out.shape) != (B, n_out) or B > 64:
+    if w.shape[1] != K or tuple(out.shape) != (B, n_out) or B > GEMV_TC_MAX_ROWS:
         raise KernelError(f"gemv_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
     if splits > 1 and (mode != TC_ACCUMULATE or partials is not None):
         nf, nc = gemv_tc_scratch(B, N, splits)

@@ -637,7 +637,7 @@ def test_attention_decode_with_rotation_and_append_inside(n_q, n_kv, hd, window,
     assert torch.all(got[5] == 0) and torch.all(counters == 0)
 
 
-@pytest.mark.parametrize("rows", [1, 16, 17, 33, 64])
+@pytest.mark.parametrize("rows", [1, 16, 17, 33, 64, 65, 100, 128])
 @pytest.mark.parametrize("N,K,splits", [(304, 72, 1), (1000, 4096, 1), (1000, 4096, 5), (128, 640, 3), (272, 1440, 8)])
 def test_gemv_tc(rows, N, K, splits):
     g = torch.Generator(device=DEV).manual_seed(70)
@@ -666,7 +666,7 @@ def test_gemv_tc(rows, N, K, splits):
     ops().check_device_errors()
 
 
-@pytest.mark.parametrize("rows,splits", [(20, 1), (64, 3)])
+@pytest.mark.parametrize("rows,splits", [(20, 1), (64, 3), (97, 1), (128, 2)])
 def test_gemv_tc_swiglu(rows, splits):
     g = torch.Generator(device=DEV).manual_seed(71)
     K, inter = 576, 200
