@@ -229,6 +229,40 @@ def test_a_step_over_its_token_budget_runs_in_chunks_with_the_same_logits(model_
     assert m.cache.length(s0) == 0
 
 
+@pytest.mark.parametrize("head_dim,tokens", [(128, 20000), (64, 12000)])
+def test_a_far_context_in_bfloat16_stays_on_the_float32_path(head_dim, tokens):
+    """Hundreds of pages: a prompt of ``tokens`` tokens cut into chunks of 8,192 (the tcgen05 attention
+    over a long cached prefix), then 24 tokens one by one beside a short sequence (decode attention
+    in many chunks, lengths that differ by a factor of 60).  The plain implementation would take
+    minutes here, so the oracle is the engine's own float32 path, which the other tests pin to it:
+    every wanted row of bfloat16 logits lies within 5 % (root mean square, relative) of float32's."""
+    from supersonic_b200.config import preset_config
+    from supersonic_b200.engine import Model, StepEntry
+    from supersonic_b200.weights import RandomWeightStore
+    cfg = preset_config("llama3.1-8b", num_hidden_layers=2, hidden_size=256, num_attention_heads=4,
+                        num_key_value_heads=2, head_dim=head_dim, intermediate_size=512, vocab_size=1000,
+                        eos_token_id=1, bos_token_id=0)
+    g = torch.Generator().manual_seed(5)
+    toks = torch.randint(0, cfg.vocab_size, (tokens + 24,), generator=g).tolist()
+    short = torch.randint(0, cfg.vocab_size, (224,), generator=g).tolist()
+    want = [0, 8191, 8192, tokens - 1]
+    rows = {}
+    for dtype in ("bfloat16", "float32"):
+        store = RandomWeightStore(cfg, seed=7, device="cuda:0", std=0.05, norm_jitter=0.1)
+        m = Model.from_config(cfg, store, dtype=dtype, device="cuda:0", max_tokens=tokens + 1024,
+                              max_seq_tokens=tokens + 64, step_token_budget=8192)
+        a, b = m.open_sequence(), m.open_sequence()
+        got = [m.step([StepEntry(a, toks[:tokens], want), StepEntry(b, short[:200], [199])]).float().cpu()]
+        for i in range(24):
+            got.append(m.step([StepEntry(a, [toks[tokens + i]], [0]), StepEntry(b, [short[200 + i]], [0])]).float().cpu())
+        rows[dtype] = torch.cat(got)
+        m.cache.check()
+        del m, store
+    ref, got = rows["float32"], rows["bfloat16"]
+    rel = (got - ref).pow(2).mean(dim=1).sqrt() / ref.pow(2).mean(dim=1).sqrt()
+    assert float(rel.max()) < 0.05, rel
+
+
 def test_a_model_the_device_cannot_hold_is_refused_before_anything_is_loaded(model_folders):
     from supersonic_b200.engine import Model
     from supersonic_b200.engine.preflight import MemoryPreflightError
