@@ -22,7 +22,8 @@ from typing import Dict, List, Optional, Tuple, Union
 
 import torch
 
-from .allocators import CacheError, CacheFull, FreeList
+from ..host import CacheBook
+from .allocators import CacheError
 
 PAGE_SHIFT = 6
 PAGE_TOKENS = 1 << PAGE_SHIFT
@@ -47,8 +48,52 @@ def pages_for(n_tokens: int) -> int:
     return (n_tokens + PAGE_TOKENS - 1) >> PAGE_SHIFT
 
 
+class _Pool:
+    """The page pool of one group as the bookkeeping sees it."""
+
+    def __init__(self, book: CacheBook, group: int, capacity: int):
+        self._book, self._group, self.capacity = book, group, capacity
+
+    @property
+    def n_free(self) -> int:
+        return self._book.free_pages(self._group)
+
+    @property
+    def n_held(self) -> int:
+        return self._book.held_pages(self._group)
+
+
+class _HeldPages:
+    """``held[slot]``: page index within the sequence -> page id, for the pages the slot holds now."""
+
+    def __init__(self, book: CacheBook, group: int):
+        self._book, self._group = book, group
+
+    def __getitem__(self, slot: int) -> Dict[int, int]:
+        return self._book.pages_of(self._group, slot)
+
+
+class _Slots:
+    """The slot pool as the bookkeeping sees it."""
+
+    def __init__(self, book: CacheBook, capacity: int):
+        self._book, self.capacity = book, capacity
+
+    @property
+    def n_free(self) -> int:
+        return self._book.free_slots
+
+    @property
+    def n_held(self) -> int:
+        return self.capacity - self._book.free_slots
+
+    def is_held(self, slot: int) -> bool:
+        return self._book.is_held(slot)
+
+
 class KvGroup:
-    """Storage and page bookkeeping of the cache entries that share one need."""
+    """Storage of the cache entries that share one need.  Which pages a slot holds is kept by the
+    cache's native book, which writes the page ids into ``table_host``; ``pool`` and ``held`` show it."""
 
     def __init__(self, need: KvNeed, entries: List[int], n_pages: int, max_slots: int,
                  pages_per_seq: int, dtype: torch.dtype, device: torch.device):
@@ -57,66 +102,26 @@ class KvGroup:
         self.index_of = {e: i for i, e in enumerate(self.entries)}
         self.n_pages = n_pages
         self.pages_per_seq = pages_per_seq
-        self.pool = FreeList(n_pages, "page")
         shape = (len(entries), n_pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
         self.v = torch.zeros(shape, dtype=dtype, device=device)
         pin = device.type == "cuda"
         self.table_host = torch.zeros((max_slots, pages_per_seq), dtype=torch.int32, pin_memory=pin)
-        self._table_np = self.table_host.numpy()          # the same memory, cheap to write element by element
         self.table = torch.zeros((max_slots, pages_per_seq), dtype=torch.int32, device=device)
-        # per slot: page index within the sequence -> page id, only for pages now held
-        self.held: List[Dict[int, int]] = [dict() for _ in range(max_slots)]
-        self._dirty_lo, self._dirty_hi = max_slots, -1
+        self.pool: Optional[_Pool] = None          # set by the cache once its book exists
+        self.held: Optional[_HeldPages] = None
+        self._book: Optional[CacheBook] = None
+        self._index = -1
 
-    def first_needed_page(self, length: int) -> int:
-        """First page a query at position >= ``length`` can still read."""
-        if self.need.window is None:
-            return 0
-        return max(0, length - self.need.window + 1) >> PAGE_SHIFT
-
-    def missing_pages(self, slot: int, length: int, new_length: int) -> List[int]:
-        """Pages that ``new_length`` tokens need and the slot does not hold yet.  A sequence that
-        already has tokens holds every page up to its last one (older ones may have been given
-        back by a window): only the last held page and those after it need a look, so a decode
-        step of a long sequence does not walk its whole page list."""
-        first = self.first_needed_page(length)
-        if length > 0:
-            first = max(first, pages_for(length) - 1)
-        held = self.held[slot]
-        return [p for p in range(first, pages_for(new_length)) if p not in held]
-
-    def reserve(self, slot: int, length: int, new_length: int) -> None:
-        want = self.missing_pages(slot, length, new_length)
-        if not want:
-            return
-        if pages_for(new_length) > self.pages_per_seq:
-            raise CacheFull(f"{new_length} tokens exceed the {self.pages_per_seq * PAGE_TOKENS} "
-                            "a sequence may hold")
-        ids = self.pool.take_many(len(want))
-        for p, pid in zip(want, ids):
-            self.held[slot][p] = pid
-            self._table_np[slot, p] = pid
-        self._dirty_lo, self._dirty_hi = min(self._dirty_lo, slot), max(self._dirty_hi, slot)
-
-    def trim(self, slot: int, length: int) -> None:
-        """Give back pages that no later query reads (window groups only)."""
-        if self.need.window is None:
-            return
-        first = self.first_needed_page(length)
-        for p in [p for p in self.held[slot] if p < first]:
-            self.pool.give_back(self.held[slot].pop(p))
-
-    def release(self, slot: int) -> None:
-        for pid in self.held[slot].values():
-            self.pool.give_back(pid)
-        self.held[slot].clear()
+    def bind(self, book: CacheBook, index: int) -> None:
+        self._book, self._index = book, index
+        self.pool = _Pool(book, index, self.n_pages)
+        self.held = _HeldPages(book, index)
 
     def sync(self) -> None:
-        if self._dirty_hi >= self._dirty_lo:
-            lo, hi = self._dirty_lo, self._dirty_hi + 1
+        lo, hi = self._book.take_dirty(self._index)
+        if hi > lo:
             self.table[lo:hi].copy_(self.table_host[lo:hi], non_blocking=True)
-            self._dirty_lo, self._dirty_hi = self.table.shape[0], -1
 
 
 def default_seed(slot: int) -> int:
@@ -146,8 +151,6 @@ class SequenceCache:
         self.max_seq_tokens = min(int(max_seq_tokens), self.pages_per_seq * PAGE_TOKENS)
         self.max_slots = max_slots if max_slots is not None else min(self.n_pages, 4096)
         self._preflight(needs, max_tokens, max_seq_tokens)
-        self.slots = FreeList(self.max_slots, "slot")
-        self._length = [0] * self.max_slots
         # groups by need
         by_need: Dict[KvNeed, List[int]] = {}
         state_entries: List[Tuple[int, StateNeed]] = []
@@ -161,6 +164,12 @@ class SequenceCache:
         self.kv_groups: List[KvGroup] = [
             KvGroup(need, entries, self.n_pages, self.max_slots, self.pages_per_seq, dtype, device)
             for need, entries in by_need.items()]
+        # who holds which slot and page: the native book, which fills the groups' host page tables
+        self._book = CacheBook([g.need.window for g in self.kv_groups], self.n_pages, self.pages_per_seq,
+                               self.max_slots, self.max_seq_tokens, [g.table_host.numpy() for g in self.kv_groups])
+        for i, g in enumerate(self.kv_groups):
+            g.bind(self._book, i)
+        self.slots = _Slots(self._book, self.max_slots)
         self._group_of: Dict[int, KvGroup] = {e: g for g in self.kv_groups for e in g.entries}
         self._state: Dict[int, torch.Tensor] = {
             cid: torch.zeros((self.max_slots, need.n_values), dtype=torch.float32, device=device)
@@ -207,8 +216,7 @@ class SequenceCache:
         """A free slot with length 0, zeroed fixed state and a seeded generator.  Without a seed
         the generator starts from a fixed state of the slot's own, never from zero (the fixed point
         of xorshift64) and never from what the slot's last sequence left."""
-        slot = self.slots.take()
-        self._length[slot] = 0
+        slot = self._book.acquire()
         for t in self._state.values():
             t[slot].zero_()
         self.seed(slot, rng_seed if rng_seed is not None else default_seed(slot))
@@ -224,17 +232,13 @@ class SequenceCache:
 
     def release(self, slot: int) -> None:
         """Give the slot and every page it holds back."""
-        if not self.slots.is_held(slot):
-            raise CacheError(f"slot {slot} is released but is not held")
-        for g in self.kv_groups:
-            g.release(slot)
-        self._length[slot] = 0
-        self.slots.give_back(slot)
+        self._book.release(slot)
 
     def length(self, slot: int) -> int:
-        if not self.slots.is_held(slot):
-            raise CacheError(f"slot {slot} is not held")
-        return self._length[slot]
+        return self._book.length(slot)
+
+    def lengths(self, slots) -> List[int]:
+        return self._book.lengths(list(slots))
 
     def live_slots(self) -> List[int]:
         return [s for s in range(self.max_slots) if self.slots.is_held(s)]
@@ -242,24 +246,18 @@ class SequenceCache:
     # ---- per step -----------------------------------------------------------------------
     def reserve(self, slot: int, n_new: int) -> None:
         """Make room for ``n_new`` more tokens of ``slot`` in every group (all or nothing)."""
-        length = self.length(slot)
-        new_length = length + n_new
-        if new_length > self.max_seq_tokens:
-            raise CacheFull(f"slot {slot}: {new_length} tokens exceed the {self.max_seq_tokens} "
-                            "one sequence may hold")
-        for g in self.kv_groups:
-            need = len(g.missing_pages(slot, length, new_length))
-            if need > g.pool.n_free:
-                raise CacheFull(f"slot {slot} needs {need} more pages of {PAGE_TOKENS} tokens, "
-                                f"{g.pool.n_free} of {g.n_pages} are free")
-        for g in self.kv_groups:
-            g.reserve(slot, length, new_length)
+        self._book.reserve(slot, n_new)
 
     def advance(self, slot: int, n_new: int) -> None:
         """Record that ``n_new`` tokens were appended; window groups drop what nothing reads."""
-        self._length[slot] = self.length(slot) + n_new
-        for g in self.kv_groups:
-            g.trim(slot, self._length[slot])
+        self._book.advance(slot, n_new)
+
+    def reserve_each(self, slots, n_new: int = 1) -> None:
+        """``reserve`` for every slot of a decode step, in one call."""
+        self._book.reserve_each(list(slots), n_new)
+
+    def advance_each(self, slots, n_new: int = 1) -> None:
+        self._book.advance_each(list(slots), n_new)
 
     def sync(self) -> None:
         """Upload page-table rows that changed since the last call."""
@@ -296,18 +294,4 @@ class SequenceCache:
 
     def check(self) -> None:
         """Invariants: no slot or page lost or held twice; held pages match the tables."""
-        self.slots.check()
-        for g in self.kv_groups:
-            g.pool.check()
-            seen = set()
-            for slot in range(self.max_slots):
-                if g.held[slot] and not self.slots.is_held(slot):
-                    raise CacheError(f"free slot {slot} still holds pages")
-                for p, pid in g.held[slot].items():
-                    if pid in seen:
-                        raise CacheError(f"page {pid} is held twice")
-                    seen.add(pid)
-                    if int(g.table_host[slot, p]) != pid:
-                        raise CacheError(f"page table of slot {slot} disagrees at {p}")
-            if len(seen) != g.pool.n_held:
-                raise CacheError(f"{g.pool.n_held} pages are marked held but {len(seen)} are in use")
+        self._book.check()

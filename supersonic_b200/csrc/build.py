@@ -1,5 +1,6 @@
 """Compiles the ``.cu`` files beside this module with nvcc for sm_100a, one shared
-library each, and loads them with ctypes.
+library each, and loads them with ctypes; the host runtime (``../host/runtime.cpp``, plain
+C++ without CUDA) is built the same way with the C++ compiler.
 
 A library is built the first time something asks for it (so a run compiles only
 what its model needs) and again whenever its sources or flags change; a progress
@@ -42,7 +43,11 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "gemm_tc": {"sources": ["gemm_tc.cu"], "flags": [], "link": []},
     "attention_decode_static": {"sources": ["attention_decode_static.cu"], "flags": [], "link": []},
     "random_fill": {"sources": ["random_fill.cu"], "flags": [], "link": []},
+    # the host side's native core: no CUDA in it, so it is compiled by the C++ compiler alone
+    "host_runtime": {"sources": ["runtime.cpp"], "flags": [], "link": [], "dir": os.path.join(os.path.dirname(_HERE), "host"),
+                     "compiler": "c++"},
 }
+HOST_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
 _INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)
 
 
@@ -50,16 +55,27 @@ def _sources_of(name: str) -> List[str]:
     """The library's sources and every header beside them that they include, directly or not: what its
     digest is taken over, so that a change to one kernel's header rebuilds only the libraries that use it."""
     todo, seen = list(LIBRARIES[name]["sources"]), []
+    base = _dir_of(name)
     while todo:
         f = todo.pop()
         if f in seen:
             continue
         seen.append(f)
-        with open(os.path.join(_HERE, f), "r", encoding="utf-8") as fh:
+        with open(os.path.join(base, f), "r", encoding="utf-8") as fh:
             for inc in _INCLUDE.findall(fh.read()):
-                if os.path.isfile(os.path.join(_HERE, inc)):
+                if os.path.isfile(os.path.join(base, inc)):
                     todo.append(inc)
     return sorted(seen)
+
+
+def _dir_of(name: str) -> str:
+    return LIBRARIES[name].get("dir", _HERE)
+
+
+def _flags_of(name: str) -> List[str]:
+    spec = LIBRARIES[name]
+    base = HOST_FLAGS if spec.get("compiler") == "c++" else ARCH_FLAGS + BASE_FLAGS
+    return base + spec["flags"] + spec["link"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -71,6 +87,15 @@ class BuildError(RuntimeError):
 
 def register_library(name: str, sources: List[str], flags: List[str] = (), link: List[str] = ()):
     LIBRARIES[name] = {"sources": list(sources), "flags": list(flags), "link": list(link)}
+
+
+def find_cxx() -> str:
+    for cand in (os.environ.get("SSB200_CXX"), os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"),
+                 shutil.which("clang++")):
+        if cand and (os.path.isfile(cand) or shutil.which(cand)):
+            return cand
+    raise BuildError("no C++ compiler found (looked at $SSB200_CXX, $CXX, g++, c++, clang++): "
+                     "the host runtime cannot be built and there is no other path")
 
 
 def find_nvcc() -> str:
@@ -104,9 +129,9 @@ def _digest(name: str) -> str:
     spec = LIBRARIES[name]
     h = hashlib.sha256()
     for f in _sources_of(name):
-        with open(os.path.join(_HERE, f), "rb") as fh:
+        with open(os.path.join(_dir_of(name), f), "rb") as fh:
             h.update(f.encode() + b"\0" + fh.read())
-    h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + spec["flags"] + spec["link"]).encode())
+    h.update(" ".join(_flags_of(name)).encode())
     return h.hexdigest()[:20]
 
 
@@ -140,10 +165,16 @@ def build_library(name: str, verbose: bool = True, force: bool = False) -> str:
     out_dir = _build_dir()
     so = os.path.join(out_dir, f"libssb200_{name}.so")
     tmp = so + f".{os.getpid()}.tmp"
-    cmd = ([find_nvcc()] + ARCH_FLAGS + BASE_FLAGS + spec["flags"] + ["-I", _HERE]
-           + [os.path.join(_HERE, s) for s in spec["sources"]] + spec["link"] + ["-o", tmp])
+    src_dir = _dir_of(name)
+    if spec.get("compiler") == "c++":
+        cmd = ([find_cxx()] + HOST_FLAGS + spec["flags"] + ["-I", src_dir]
+               + [os.path.join(src_dir, s) for s in spec["sources"]] + spec["link"] + ["-o", tmp])
+    else:
+        cmd = ([find_nvcc()] + ARCH_FLAGS + BASE_FLAGS + spec["flags"] + ["-I", src_dir]
+               + [os.path.join(src_dir, s) for s in spec["sources"]] + spec["link"] + ["-o", tmp])
     if verbose:
-        print(f"[supersonic_b200] compiling {name} for sm_100a ...", file=sys.stderr, flush=True)
+        print(f"[supersonic_b200] compiling {name}" + ("" if spec.get("compiler") == "c++" else " for sm_100a") + " ...",
+              file=sys.stderr, flush=True)
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                             cwd=out_dir)
@@ -165,7 +196,7 @@ def build_library(name: str, verbose: bool = True, force: bool = False) -> str:
             os.remove(tmp)
         except OSError:
             pass
-        raise BuildError(f"nvcc failed for {name} (exit {proc.returncode}):\n{' '.join(cmd)}\n{out}")
+        raise BuildError(f"the compiler failed for {name} (exit {proc.returncode}):\n{' '.join(cmd)}\n{out}")
     os.replace(tmp, so)
     with open(so + ".digest", "w") as f:
         f.write(_digest(name) + "\n")

@@ -38,7 +38,18 @@ class FastKernels(PlainKernels):
         # kernel: not in deterministic mode, where a prompt takes one path whatever accompanies it
         self.fuse_rope_prefill = not deterministic
         self._scratch: Dict[str, torch.Tensor] = {}
+        self._zeroed = set()    # names of the buffers that are zero between uses (sums of K parts, arrival counters)
         self._retired = []      # outgrown buffers stay alive: captured graphs still point at them
+        ops.after_device_error(self._after_device_error)
+
+    def _after_device_error(self) -> None:
+        """A launch gave up on a wait: its arrival counters and partial sums may be left half-way.  The
+        buffers that must be zero between uses are zeroed again, so that the steps after the error
+        that is about to be raised start from a clean state."""
+        for name in self._zeroed:
+            t = self._scratch.get(name)
+            if t is not None:
+                t.zero_()
 
     def rmsnorm(self, x, weight, eps, out, rows=None):
         pdl = self.pdl and out.shape[0] <= 64
@@ -165,6 +176,8 @@ class FastKernels(PlainKernels):
                 self._retired.append(t)
             t = (torch.zeros if zero else torch.empty)(max(n, 4096), dtype=dtype, device=device)
             self._scratch[name] = t
+        if zero:
+            self._zeroed.add(name)
         return t
 
     def _chunks(self, n_kv: int, pages: int, blocks: int):

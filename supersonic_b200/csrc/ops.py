@@ -400,6 +400,28 @@ _tc_error_words = {}
 _tc_unchecked = 0      # tcgen05 launches since the error words were last read
 
 
+_after_error = []       # weak references to callables that put scratch back in order after a failed launch
+
+
+def after_device_error(method) -> None:
+    """Register a bound method to be called when a bounded wait is found to have run out, before the
+    error is raised: a launch that gave up may have left arrival counters and zero-between-uses
+    scratch in a state that later launches would trip over.  Held weakly."""
+    import weakref
+    _after_error.append(weakref.WeakMethod(method))
+
+
+def _raise_wait_ran_out(code: int):
+    for ref in list(_after_error):
+        fn = ref()
+        if fn is None:
+            _after_error.remove(ref)
+        else:
+            fn()
+    raise KernelError(f"tcgen05 kernel: a bounded wait ran out in {_TC_ERRORS.get(code, code)}; "
+                      "the result of that launch is invalid")
+
+
 def bounded_wait_launches() -> int:
     """Launches since the last look at the error words of kernels whose waits are bounded."""
     return _tc_unchecked
@@ -433,8 +455,7 @@ def check_device_errors(device=None) -> None:
         code = int(word.item())
         if code:
             word.zero_()
-            raise KernelError(f"tcgen05 kernel: a bounded wait ran out in {_TC_ERRORS.get(code, code)}; "
-                              "the result of that launch is invalid")
+            _raise_wait_ran_out(code)
 
 
 _fetch_buffers = {}
@@ -460,8 +481,7 @@ def fetch_with_errors(values: torch.Tensor) -> list:
         code = int(buf[n])
         if code:
             word.zero_()
-            raise KernelError(f"tcgen05 kernel: a bounded wait ran out in {_TC_ERRORS.get(code, code)}; "
-                              "the result of that launch is invalid")
+            _raise_wait_ran_out(code)
     return out
 
 
@@ -507,8 +527,7 @@ def finish_fetch(f: Fetch) -> list:
         code = int(f.buf[f.n])
         if code:
             _tc_error_words[f.device].zero_()
-            raise KernelError(f"tcgen05 kernel: a bounded wait ran out in {_TC_ERRORS.get(code, code)}; "
-                              "the result of that launch is invalid")
+            _raise_wait_ran_out(code)
     return out
 
 

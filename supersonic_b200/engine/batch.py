@@ -15,6 +15,8 @@ from typing import List, Optional, Sequence
 import numpy as np
 import torch
 
+from .. import host
+
 
 @dataclass
 class StepEntry:
@@ -67,12 +69,11 @@ class StepBatch:
     host_counts: List[int] = field(default_factory=list)
 
 
-def decode_pages_bucket(longest: int, page_tokens: int = 64) -> int:
-    """Pages spanned by ``longest`` tokens, rounded down to a power of two: kernels size their
-    grids from it (a sequence in the bucket spans fewer than twice as many pages), and a captured
+def decode_pages_bucket(longest: int) -> int:
+    """Pages (of 64 tokens) spanned by ``longest`` tokens, rounded down to a power of two: kernels size
+    their grids from it (a sequence in the bucket spans fewer than twice as many pages), and a captured
     decode step stays valid while the bucket does."""
-    pages = max(1, -(-longest // page_tokens))
-    return 1 << (pages.bit_length() - 1)
+    return host.decode_pages_bucket(longest)
 
 
 def plan_chunks(counts: Sequence[int], budget: int) -> List[List[tuple]]:
@@ -83,22 +84,8 @@ def plan_chunks(counts: Sequence[int], budget: int) -> List[List[tuple]]:
     is left of a chunk goes on in the next one, and no entry appears twice in a chunk, so a chunk
     is a step of its own whose sequences continue what earlier chunks left in the cache (the
     reference carries a long prompt through its cache in the same way, chunk by chunk:
-    crates/runner/src/prefill_engine.rs:1081-1094)."""
-    if budget < 1:
-        raise ValueError(f"a step's token budget must be at least 1, not {budget}")
-    chunks: List[List[tuple]] = [[]]
-    room = budget
-    for i, n in enumerate(counts):
-        first = 0
-        while first < n:
-            if room == 0:
-                chunks.append([])
-                room = budget
-            take = min(room, n - first)
-            chunks[-1].append((i, first, first + take))
-            first += take
-            room -= take
-    return [c for c in chunks if c]
+    crates/runner/src/prefill_engine.rs:1081-1094).  The arithmetic is the host runtime's."""
+    return host.plan_chunks(list(counts), budget)
 
 
 @dataclass
@@ -128,41 +115,20 @@ class PackedStep:
 
 def pack_entries(entries: Sequence[StepEntry], starts: Sequence[int],
                  vocab_size: Optional[int] = None) -> PackedStep:
-    """Lay the entries out back to back on the host; every misuse raises before anything runs."""
+    """Lay the entries out back to back on the host; every misuse raises before anything runs.  The
+    layout and its checks are the host runtime's (``ssb_pack_step``); here the entries' Python lists
+    become the arrays it reads."""
     if not entries:
         raise ValueError("a step needs at least one entry")
-    tok_parts, pos_parts, slot_parts = [], [], []
-    want: List[int] = []
-    cu = [0]
-    slots, counts = [], []
-    for e, start in zip(entries, starts):
-        toks = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
-        n = int(toks.shape[0])
-        if n == 0:
-            raise ValueError(f"slot {e.slot}: an entry must bring at least one token")
-        base = cu[-1]
-        for w in e.want:
-            if not 0 <= w < n:
-                raise ValueError(f"slot {e.slot}: wanted place {w} is outside its {n} tokens")
-            want.append(base + w)
-        tok_parts.append(toks)
-        pos_parts.append(np.arange(start, start + n, dtype=np.int64))
-        slot_parts.append(np.full(n, e.slot, dtype=np.int64))
-        cu.append(base + n)
-        slots.append(e.slot)
-        counts.append(n)
-    tokens = np.concatenate(tok_parts)
-    if vocab_size is not None:
-        bad = tokens[(tokens < 0) | (tokens >= vocab_size)]
-        if bad.size:
-            raise ValueError(f"token ids {bad[:8].tolist()} are outside the vocabulary of {vocab_size}")
-    if len(set(slots)) != len(slots):
-        raise ValueError("a slot appears twice in one step")
-    flat = np.concatenate(tok_parts + pos_parts + slot_parts + [
-        np.asarray(slots + list(starts) + cu + want, dtype=np.int64)]).astype(np.int32)
-    return PackedStep(flat=flat, n_tokens=int(tokens.shape[0]), n_seqs=len(slots), n_want=len(want),
-                      max_new=max(counts), max_total=max(s + c for s, c in zip(starts, counts)),
-                      slots=slots, starts=list(starts), counts=counts)
+    slots = [int(e.slot) for e in entries]
+    tok_parts = [np.asarray(e.tokens, dtype=np.int64).reshape(-1) for e in entries]
+    counts = [int(t.shape[0]) for t in tok_parts]
+    want = [int(w) for e in entries for w in e.want]
+    flat, (T, B, W, max_new, max_total, _) = host.pack_step(
+        slots, [int(s) for s in starts], counts, np.concatenate(tok_parts) if len(tok_parts) > 1 else tok_parts[0],
+        [len(e.want) for e in entries], want, vocab_size)
+    return PackedStep(flat=flat, n_tokens=T, n_seqs=B, n_want=W, max_new=max_new, max_total=max_total,
+                      slots=slots, starts=[int(s) for s in starts], counts=counts)
 
 
 def batch_over(buf: torch.Tensor, packed: PackedStep, captured: bool = False) -> StepBatch:

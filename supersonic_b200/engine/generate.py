@@ -18,6 +18,7 @@ from typing import Callable, List, Optional, Sequence
 
 import torch
 
+from .. import host
 from ..sampling import Sampler, SamplingParams, request_seed
 from .batch import StepEntry
 
@@ -45,11 +46,7 @@ class RunStats:
 
 def finished(token: int, n_generated: int, max_new_tokens: int, stop_ids) -> Optional[str]:
     """Why a sequence ends after producing ``token`` as its ``n_generated``-th, or None."""
-    if token in stop_ids:
-        return "stop"
-    if n_generated >= max_new_tokens:
-        return "length"
-    return None
+    return host.finished(token, n_generated, max_new_tokens, stop_ids)
 
 
 def plan_batch(waiting: Sequence[int], prompt_lens: Sequence[int], max_new_tokens: int,
@@ -57,17 +54,9 @@ def plan_batch(waiting: Sequence[int], prompt_lens: Sequence[int], max_new_token
                batch_size: Optional[int]) -> List[int]:
     """The next batch: requests in arrival order while their prompts plus budgets fit
     the free pages and slots (each sequence's need rounded up to whole pages)."""
-    chosen: List[int] = []
-    room = free_tokens
-    for r in waiting:
-        if len(chosen) >= free_slots or (batch_size and len(chosen) >= batch_size):
-            break
-        need = -(-(prompt_lens[r] + max(max_new_tokens, 1)) // page_tokens) * page_tokens
-        if need > room:
-            break
-        chosen.append(r)
-        room -= need
-    return chosen
+    n = host.plan_batch([prompt_lens[r] for r in waiting], max_new_tokens, free_tokens, free_slots,
+                        page_tokens, batch_size)
+    return list(waiting[:n])
 
 
 class Generator:

@@ -295,7 +295,7 @@ class Model:
         """Run the entries' tokens; returns float32 logits ``[wanted, vocab]`` in the order
         of the entries and of their ``want`` (an empty tensor if nothing is wanted)."""
         cache = self.cache
-        starts = [cache.length(e.slot) for e in entries]
+        starts = cache.lengths([e.slot for e in entries])
         if self.use_graphs and self._timed is None \
                 and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             return self._graph_step(entries, starts)
@@ -388,7 +388,7 @@ class Model:
             raise RuntimeError("step_ahead needs captured decode steps (the bfloat16 path with graphs on)")
         if tokens.dtype != torch.int32 or tokens.numel() != len(slots) or tokens.device != self.device:
             raise ValueError("step_ahead: one int32 token per slot, on the model's device")
-        return self._graph_decode(list(slots), tokens, [self.cache.length(s) for s in slots])
+        return self._graph_decode(list(slots), tokens, self.cache.lengths(slots))
 
     def _graph_step(self, entries, starts) -> torch.Tensor:
         tokens = [int(e.tokens[0]) for e in entries]
@@ -402,8 +402,7 @@ class Model:
         if len(set(slots)) != len(slots):
             raise ValueError("a slot appears twice in one step")
         self._check_positions(max(starts) + 1)
-        for s in slots:
-            cache.reserve(s, 1)
+        cache.reserve_each(slots, 1)
         cache.sync()
         key = (len(slots), decode_pages_bucket(max(starts) + 1))
         graph = self._graphs.get(key)
@@ -413,8 +412,7 @@ class Model:
         logits = graph.run(tokens, starts, slots).clone()     # the graph's own buffer is reused next step
         self.graph_replays += 1
         self.graph_kernels += graph.kernels_per_replay
-        for s in slots:
-            cache.advance(s, 1)
+        cache.advance_each(slots, 1)
         return logits
 
     def time_stages(self, on: bool = True):
