@@ -43,6 +43,36 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}"
                  ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
+// Four k-steps of one product in a row.  Issued as separate statements, every tcgen05.mma pays for its own
+// predicate set-up and the issuing thread gets 93 cycles an instruction out (measured alone on an SM; 168
+// beside busy warps); four in one block with one predicate set-up run at the tensor cores' own pace (64
+// cycles for N 128; 74 beside busy warps).  The descriptors of step i are those of step 0 plus i times the
+// given increments; the first step accumulates only if ``accumulate`` is set, the others always do.
+__device__ __forceinline__ void tc_mma_x4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p, q;\n.reg .b64 a1, a2, a3, b1, b2, b3;\n"
+                 "setp.ne.b32 p, %4, 0;\nsetp.eq.b32 q, %5, 0;\n"
+                 "add.u64 a1, %1, 2;\nadd.u64 a2, %1, 4;\nadd.u64 a3, %1, 6;\n"
+                 "add.u64 b1, %2, 2;\nadd.u64 b2, %2, 4;\nadd.u64 b3, %2, 6;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, {%5, %5, %5, %5}, q;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, {%5, %5, %5, %5}, q;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, {%5, %5, %5, %5}, q;\n}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// The same with A in tensor memory (8 columns a step) and B's descriptor 128 units (16 rows of 128 bytes) a step.
+__device__ __forceinline__ void tc_mma_ts_x4(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p, q;\n.reg .b32 a1, a2, a3;\n.reg .b64 b1, b2, b3;\n"
+                 "setp.ne.b32 p, %4, 0;\nsetp.eq.b32 q, %5, 0;\n"
+                 "add.u32 a1, %1, 8;\nadd.u32 a2, %1, 16;\nadd.u32 a3, %1, 24;\n"
+                 "add.u64 b1, %2, 128;\nadd.u64 b2, %2, 256;\nadd.u64 b3, %2, 384;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, {%5, %5, %5, %5}, q;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %3, {%5, %5, %5, %5}, q;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %3, {%5, %5, %5, %5}, q;\n}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
 __device__ __forceinline__ void tc_ld32_issue(uint32_t taddr, uint32_t* r) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                  "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -212,9 +242,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const uint64_t da = q_desc + (uint64_t)(x * (FT_Q_BYTES >> 4));
                 const uint64_t db = k_desc + (uint64_t)(s * (2 * FT_KV_BYTES >> 4));
 #pragma unroll
-                for (int ks = 0; ks < FT_HD / 16; ++ks)          // descriptors count in units of 16 bytes
-                    tc_mma(tmem + FT_S0 + x * FT_BN, da + (ks / 4) * (FT_Q_BYTES / HALVES >> 4) + 2 * (ks % 4),
-                           db + (ks / 4) * (FT_KV_BYTES / HALVES >> 4) + 2 * (ks % 4), idesc_s, ks ? 1u : 0u);
+                for (int h = 0; h < HALVES; ++h)                 // 64 dims a box, four steps of 16; descriptors count in units of 16 bytes
+                    tc_mma_x4(tmem + FT_S0 + x * FT_BN, da + h * (FT_Q_BYTES / HALVES >> 4),
+                              db + h * (FT_KV_BYTES / HALVES >> 4), idesc_s, h ? 1u : 0u);
                 tc_commit(s_full0 + 8 * x);
                 return true;
             };
@@ -229,10 +259,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     tc_fence_after();
                     const uint64_t dv = v_desc + (uint64_t)(s * (2 * FT_KV_BYTES >> 4));
 #pragma unroll
-                    for (int ks = 0; ks < FT_BN / 16; ++ks)      // 16 keys: 16 rows of 128 bytes further down, a page every four
-                        tc_mma_ts(tmem + FT_O0 + x * FT_HD, tmem + FT_S0 + x * FT_BN + ks * 8,
-                                  dv + (ks / 4) * (FT_PAGE_BYTES >> 4) + (ks % 4) * (16 * 128 >> 4), idesc_o,
-                                  (j > 0 || ks > 0) ? 1u : 0u);
+                    for (int pg = 0; pg < 2; ++pg)               // a page: four steps of 16 keys, 16 rows of 128 bytes apart
+                        tc_mma_ts_x4(tmem + FT_O0 + x * FT_HD, tmem + FT_S0 + x * FT_BN + pg * 32,
+                                     dv + pg * (FT_PAGE_BYTES >> 4), idesc_o, (j > 0 || pg > 0) ? 1u : 0u);
                     tc_commit(o_full0 + 8 * x);
                     // the next scores go where these probabilities lie: the tensor cores take
                     // their work in the order of issue
