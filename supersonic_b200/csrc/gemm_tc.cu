@@ -292,9 +292,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
                     const uint64_t da = smem_desc(a_addr), dw = smem_desc(a_addr + A_BYTES);
-#pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k)        // 16 k = 32 bytes further along the swizzled row
-                        tc_mma(acc, da + 2 * k, dw + 2 * k, idesc, (kb > it.kb_lo || k > 0) ? 1u : 0u);
+                    static_assert(TC_BK == 64, "four k-steps a k-block");
+                    tc_mma_x4(acc, da, dw, idesc, kb > it.kb_lo ? 1u : 0u);     // 16 k = 32 bytes further along the swizzled row
                     tc_commit(empty0 + 8 * s);                  // the stage is free once these MMAs have read it
                 }
                 if (ok) tc_commit(acc_full0 + 8 * buf);         // this tile's accumulators are complete
@@ -433,9 +432,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
                     const uint64_t da = smem_desc(a_addr), dw = smem_desc(a_addr + A_BYTES);
-#pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k)
-                        tc_mma_pair(acc, da + 2 * k, dw + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_mma_pair_x4(acc, da, dw, idesc, kb > 0 ? 1u : 0u);
                     tc_commit_pair(empty0 + 8 * s, 3);              // the stage is free in both blocks
                 }
                 if (ok) tc_commit_pair(acc_full0 + 8 * buf, 3);     // both blocks' accumulators are complete

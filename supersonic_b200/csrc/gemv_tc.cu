@@ -122,9 +122,8 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 tc_fence_after();
                 const uint32_t w_addr = smem_u32(smem + s * STAGE_BYTES);
                 const uint64_t dw = smem_desc(w_addr), dx = smem_desc(w_addr + W_BYTES);
-#pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)
-                    tc_mma(tmem, dw + 2 * k, dx + 2 * k, idesc, (i | k) ? 1u : 0u);
+                static_assert(TC_BK == 64, "four k-steps a k-block");
+                tc_mma_x4(tmem, dw, dx, idesc, i ? 1u : 0u);
                 tc_commit(empty0 + 8 * s);
             }
             if (ok) tc_commit(acc_full);

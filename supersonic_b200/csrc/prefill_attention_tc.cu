@@ -43,24 +43,8 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}"
                  ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
-// Four k-steps of one product in a row.  Issued as separate statements, every tcgen05.mma pays for its own
-// predicate set-up and the issuing thread gets 93 cycles an instruction out (measured alone on an SM; 168
-// beside busy warps); four in one block with one predicate set-up run at the tensor cores' own pace (64
-// cycles for N 128; 74 beside busy warps).  The descriptors of step i are those of step 0 plus i times the
-// given increments; the first step accumulates only if ``accumulate`` is set, the others always do.
-__device__ __forceinline__ void tc_mma_x4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p, q;\n.reg .b64 a1, a2, a3, b1, b2, b3;\n"
-                 "setp.ne.b32 p, %4, 0;\nsetp.eq.b32 q, %5, 0;\n"
-                 "add.u64 a1, %1, 2;\nadd.u64 a2, %1, 4;\nadd.u64 a3, %1, 6;\n"
-                 "add.u64 b1, %2, 2;\nadd.u64 b2, %2, 4;\nadd.u64 b3, %2, 6;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, {%5, %5, %5, %5}, q;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, {%5, %5, %5, %5}, q;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, {%5, %5, %5, %5}, q;\n}"
-                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-// The same with A in tensor memory (8 columns a step) and B's descriptor 128 units (16 rows of 128 bytes) a step.
+// tc_mma_x4 (tc_helpers.cuh) with A in tensor memory (8 columns a step) and B's descriptor 128 units (16 rows of
+// 128 bytes) a step.
 __device__ __forceinline__ void tc_mma_ts_x4(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
                                              uint32_t accumulate) {
     asm volatile("{\n.reg .pred p, q;\n.reg .b32 a1, a2, a3;\n.reg .b64 b1, b2, b3;\n"
