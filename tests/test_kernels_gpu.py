@@ -490,6 +490,27 @@ def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable():
     torch.testing.assert_close(out.double(), a.double() @ w.double().T, atol=1e-3, rtol=1e-4)
 
 
+def test_scratch_that_must_be_zero_between_uses_is_zeroed_after_a_reported_error():
+    """A launch that gave up may leave arrival counters and partial sums half-way: when the error is
+    reported, every kernel set alive puts its zero-between-uses buffers back to zero (and sets that
+    were dropped are no longer called)."""
+    from supersonic_b200.csrc.fast_sets import FastKernels
+    from supersonic_b200.csrc.ops import KernelError
+    ops().check_device_errors()
+    kept, dropped = FastKernels(), FastKernels()
+    counters = kept._buffer("attn_counters", 64, torch.int32, torch.device(DEV), zero=True)
+    sums = kept._buffer("split_sums", 256, torch.float32, torch.device(DEV), zero=True)
+    plain = kept._buffer("attn_partials", 256, torch.float32, torch.device(DEV))
+    counters.fill_(3); sums.fill_(1.5); plain.fill_(7.0)
+    del dropped
+    ops().tc_wait_probe(DEV)
+    with pytest.raises(KernelError, match="bounded wait ran out"):
+        ops().check_device_errors()
+    assert int(counters.abs().sum()) == 0 and float(sums.abs().sum()) == 0.0
+    assert float(plain[0]) == 7.0                                        # ordinary scratch is left alone
+    ops().check_device_errors()
+
+
 @pytest.mark.parametrize("tile_n", [256, 512])
 @pytest.mark.parametrize("M,inter,K", [(130, 200, 72), (256, 1024, 512), (700, 1160, 320)])
 def test_gemm_tc_swiglu(M, inter, K, tile_n):
