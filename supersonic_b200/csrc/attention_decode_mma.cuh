@@ -16,8 +16,8 @@
 // wait is bounded and a wait that runs out is recorded in a device word); each warp takes 16 of
 // the page's 64 keys: S = Q K^T (16 x 16), online softmax in float32, O += P V.  Warps merge in
 // shared memory; a sequence of several chunks leaves partial results in scratch and the item that
-// arrives last for its (sequence, kv head) merges them in chunk order (same scratch layout as
-// attention_decode.cuh, maxima kept in the log2 domain).  Nothing waits on another block.
+// arrives last for its (sequence, kv head) merges them in chunk order (maxima kept in the log2
+// domain; a partial result is head_dim sums, the maximum, the sum of weights, in 16-byte units).  Nothing waits on another block.
 // With FUSE the rows of q are the raw fused projection [q | k | v]: queries are rotated while
 // the fragments are built, and the item that owns the token's page rotates its key, appends key
 // and value to the cache and attends to them from registers.
@@ -32,6 +32,8 @@
 
 constexpr int ADM_WARPS = 4;
 constexpr int ADM_THREADS = ADM_WARPS * 32;
+// floats of one partial result in scratch: the head's sums, its maximum and its sum of weights, padded to 16 bytes
+#define ADM_PITCH(hd) ((hd) + 4)
 constexpr int ADM_ROWS = 16;          // query heads per kv head, padded to the MMA's 16 rows
 // Stages of the page ring (a stage: one page of keys and one of values, 32 KB at head size 128).  Three
 // and four stages measured the same as two at every batch and context tried: with two blocks on every
@@ -260,36 +262,46 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
         if (is_last) {
             __threadfence();
             const int ph0 = pend_kvh * group;
-            // every thread owns elements (head, dim) of the output and goes through the chunks itself,
-            // in chunk order, eight at a time so that their loads are in flight together
-            for (int e = threadIdx.x; e < group * HD; e += ADM_THREADS) {
-                const int row = e / HD, d = e % HD;
-                const float* base = scratch + ((size_t)pend_b * n_q + ph0 + row) * max_chunks * (HD + 2);
-                float mm = -INFINITY, ll = 0.f, a = 0.f;
+            // every thread owns four neighbouring dims of a head's output and goes through the chunks
+            // itself, in chunk order, eight at a time: a chunk's four sums come as one 16-byte load and
+            // all of the loads are in flight together, so the merge costs one trip to L2, not one per dim
+            for (int e = threadIdx.x; e < group * (HD / 4); e += ADM_THREADS) {
+                const int row = e / (HD / 4), d = (e % (HD / 4)) * 4;
+                const float* base = scratch + ((size_t)pend_b * n_q + ph0 + row) * max_chunks * ADM_PITCH(HD);
+                float mm = -INFINITY, ll = 0.f, a[4] = {0.f, 0.f, 0.f, 0.f};
                 for (int s0 = 0; s0 < pend_chunks; s0 += 8) {
-                    float pm[8], pl[8], pv[8];
+                    float pm[8], pl[8];
+                    float4 pv[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const bool live = s0 + i < pend_chunks;
-                        const float* part = base + (size_t)(live ? s0 + i : s0) * (HD + 2);
-                        pm[i] = live ? __ldcg(part + HD) : -INFINITY;
-                        pl[i] = __ldcg(part + HD + 1);
-                        pv[i] = __ldcg(part + d);
+                        const float* part = base + (size_t)(live ? s0 + i : s0) * ADM_PITCH(HD);
+                        const float2 ml = __ldcg(reinterpret_cast<const float2*>(part + HD));
+                        pm[i] = live ? ml.x : -INFINITY;
+                        pl[i] = ml.y;
+                        pv[i] = __ldcg(reinterpret_cast<const float4*>(part + d));
                     }
                     float m_new = mm;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) m_new = fmaxf(m_new, pm[i]);
                     const float keep = (mm == -INFINITY) ? 0.f : exp2f(mm - m_new);
-                    ll *= keep; a *= keep;
+                    ll *= keep;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) a[k] *= keep;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const float f = (pm[i] == -INFINITY) ? 0.f : exp2f(pm[i] - m_new);
                         ll = fmaf(pl[i], f, ll);
-                        a = fmaf(pv[i], f, a);
+                        a[0] = fmaf(pv[i].x, f, a[0]); a[1] = fmaf(pv[i].y, f, a[1]);
+                        a[2] = fmaf(pv[i].z, f, a[2]); a[3] = fmaf(pv[i].w, f, a[3]);
                     }
                     mm = m_new;
                 }
-                out[(size_t)pend_b * ldo + (size_t)(ph0 + row) * HD + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+                const float inv = ll > 0.f ? 1.f / ll : 0.f;
+                uint2 w;
+                w.x = pack2(a[0] * inv, a[1] * inv);
+                w.y = pack2(a[2] * inv, a[3] * inv);
+                *reinterpret_cast<uint2*>(out + (size_t)pend_b * ldo + (size_t)(ph0 + row) * HD + d) = w;
             }
         }
         __syncthreads();                                         // is_last is free again
@@ -538,24 +550,29 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
         }
         __syncthreads();
         const int n_chunks = cur.n_chunks;
-        for (int e = threadIdx.x; e < group * HD; e += ADM_THREADS) {
-            const int row = e / HD, d = e % HD;
+        for (int e = threadIdx.x; e < group * (HD / 4); e += ADM_THREADS) {
+            const int row = e / (HD / 4), d = (e % (HD / 4)) * 4;
             float mm = -INFINITY;
 #pragma unroll
             for (int w = 0; w < ADM_WARPS; ++w) mm = fmaxf(mm, sm_m[w][row]);
-            float ll = 0.f, a = 0.f;
+            float ll = 0.f, a[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int w = 0; w < ADM_WARPS; ++w) {
                 const float f = (sm_m[w][row] == -INFINITY) ? 0.f : exp2f(sm_m[w][row] - mm);
                 ll += sm_l[w][row] * f;
-                a += sm_acc[((size_t)w * group + row) * ACC_LD + d] * f;
+                const float4 v = *reinterpret_cast<const float4*>(sm_acc + ((size_t)w * group + row) * ACC_LD + d);
+                a[0] += v.x * f; a[1] += v.y * f; a[2] += v.z * f; a[3] += v.w * f;
             }
             if (n_chunks == 1) {
-                out[(size_t)b * ldo + (size_t)(h0 + row) * HD + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+                const float inv = ll > 0.f ? 1.f / ll : 0.f;
+                uint2 w;
+                w.x = pack2(a[0] * inv, a[1] * inv);
+                w.y = pack2(a[2] * inv, a[3] * inv);
+                *reinterpret_cast<uint2*>(out + (size_t)b * ldo + (size_t)(h0 + row) * HD + d) = w;
             } else {
-                float* part = scratch + (((size_t)b * n_q + h0 + row) * max_chunks + cur.chunk) * (HD + 2);
-                part[d] = a;
-                if (d == 0) { part[HD] = mm; part[HD + 1] = ll; }
+                float* part = scratch + (((size_t)b * n_q + h0 + row) * max_chunks + cur.chunk) * ADM_PITCH(HD);
+                *reinterpret_cast<float4*>(part + d) = make_float4(a[0], a[1], a[2], a[3]);
+                if (d == 0) *reinterpret_cast<float2*>(part + HD) = make_float2(mm, ll);
             }
         }
         __syncthreads();                                         // the sums are read, the partial results written
@@ -602,7 +619,7 @@ static inline bool adm_supported(int n_q, int n_kv, int head_dim, int ldq, bool 
 // Scratch one launch needs: floats for the chunks' partial results, ints (zero on entry, left zero)
 // for the arrival counters.
 static inline long long adm_scratch_floats(int n_seqs, int n_q, int head_dim, int max_chunks) {
-    return max_chunks > 1 ? (long long)n_seqs * n_q * max_chunks * (head_dim + 2) : 0;
+    return max_chunks > 1 ? (long long)n_seqs * n_q * max_chunks * ADM_PITCH(head_dim) : 0;
 }
 static inline int adm_counters(int n_seqs, int n_kv) { return n_seqs * n_kv; }
 
@@ -700,7 +717,8 @@ static inline int adm_launch(const void* q, int ldq, const void* k_cache, const 
     if (!error_word) return SSB_ERR_BAD_SIZE;
     if (n_seqs > ADM_MAX_SEQS || chunk_pages < 0 || max_chunks < 1 || (max_chunks > 1 && (!scratch || !counters)))
         return SSB_ERR_BAD_SIZE;
-    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return SSB_ERR_BAD_SIZE;
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)scratch) & 15) return SSB_ERR_BAD_SIZE;
+    if (ldo % 4 || ((uintptr_t)out & 7)) return SSB_ERR_BAD_SIZE;      // four dims of a head leave as one 8-byte store
     const bool fuse = cos_t != nullptr;
     if (fuse && !sin_t) return SSB_ERR_BAD_SIZE;
     const float scale_log2 = scale * 1.4426950408889634f;
