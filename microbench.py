@@ -80,7 +80,7 @@ def attention_decode(args):
     if args.kind == 2:                               # the tensor-core kernel on its persistent grid
         fn = lambda i: ops.attention_decode_chunked(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, None,
                                                     1 / math.sqrt(hd), chunk, max_chunks, scratch, counters,
-                                                    cos=cos, sin=sin, pdl=args.pdl)
+                                                    cos=cos, sin=sin, pdl=args.pdl, cluster=args.cluster)
     else:
         fn = lambda i: ops.attention_decode(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, None,
                                             1 / math.sqrt(hd), splits, scratch, counters, cos=cos, sin=sin, pdl=args.pdl)
@@ -176,6 +176,8 @@ def main(argv=None):
         p.add_argument("--k-parts", type=int, default=1, help="gemm --accumulate: parts a tile's K range is cut into")
         p.add_argument("--kind", type=int, default=2, help="attention_decode: 1 CUDA cores, 2 tensor cores (persistent grid)")
         p.add_argument("--chunk-pages", type=int, default=0, help="attention_decode --kind 2: pages per chunk (default: pages / --splits)")
+        p.add_argument("--cluster", type=int, default=0,
+                       help="attention_decode --kind 2: chunks a sequence as a thread-block cluster (2, 4, 8; 0: the persistent grid)")
         p.add_argument("--ragged", action="store_true", help="attention_decode: lengths uniform in [1, --context]")
         p.add_argument("--accumulate", action="store_true", help="linear gv*, gemm: add into a float32 output")
         p.add_argument("--pdl", action="store_true", help="launch as programmatic dependents")

@@ -55,7 +55,29 @@ __device__ __forceinline__ uint32_t adm_tile_offset(int row, int chunk) {
     return (uint32_t)(((chunk >> 3) << 13) + (row << 7) + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-template <int HD, bool FUSE>
+// Thread-block clusters (CL): the chunks of one (sequence, kv head) are the blocks of one cluster and
+// merge through the cluster's shared memory.
+__device__ __forceinline__ unsigned adm_cluster_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ unsigned adm_cluster_size() { unsigned r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void adm_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 adm_ld_cluster4(const float* local, unsigned rank) {
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ float2 adm_ld_cluster2(const float* local, unsigned rank) {
+    uint32_t remote;
+    float2 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(remote) : "memory");
+    return v;
+}
+
+template <int HD, bool FUSE, bool CL>
 __global__ void __launch_bounds__(ADM_THREADS)
 attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* k_cache,
                             __nv_bfloat16* v_cache, const int* __restrict__ pos, const int* __restrict__ slot,
@@ -82,6 +104,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
     int* sm_pos = sm_slot + n_seqs;
     __shared__ float sm_m[ADM_WARPS][ADM_ROWS], sm_l[ADM_WARPS][ADM_ROWS];
     __shared__ int is_last;
+    __shared__ float2 cl_ml[ADM_ROWS];                           // CL: this chunk's maximum and sum of weights per head
     __shared__ __align__(8) unsigned long long full_bar[STAGES];      // a stage's bytes have landed
     __shared__ int sm_abort[2];                                  // [0]: a wait ran out; [1]: stays zero
     volatile int* abort_flag = sm_abort;
@@ -113,7 +136,8 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
     // of streaming.  Very unequal lengths (the longest more than one and a half times the mean) with
     // enough work for it: two to three items a block, of at least eight pages, so that the blocks end
     // together.  A caller that wants a sequence cut the same way in every batch gives chunk_pages itself.
-    if (chunk_pages <= 0) {
+    const int n_cl = CL ? (int)adm_cluster_size() : 1;          // blocks of a cluster: the chunks of every sequence
+    if (!CL && chunk_pages <= 0) {
         int local = 0, longest = 0, live = 0;
         for (int b = threadIdx.x; b < n_seqs; b += ADM_THREADS) {
             const int n = pages_of(b);
@@ -144,7 +168,11 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
         const int n = pages_of(b);
         return n == 0 ? 0 : min((n + chunk_pages - 1) / chunk_pages, max_chunks);
     };
-    {
+    if (CL) {
+        // every sequence has as many chunks as its clusters have blocks (some may be empty)
+        for (int b = threadIdx.x; b <= n_seqs; b += ADM_THREADS) cum[b] = b * n_cl;
+        __syncthreads();
+    } else {
         const int per = (n_seqs + ADM_THREADS - 1) / ADM_THREADS;
         const int b0 = (int)threadIdx.x * per;
         int local = 0;
@@ -171,16 +199,25 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
     // An item is decoded two items ahead of its turn: the ids of its first two pages are asked for here
     // and are in registers long before its pages are issued.
     auto decode = [&](int idx, AdmItem& I) {
-        const int gc = idx / n_kv;
-        I.kvh = idx - gc * n_kv;
-        int lo = 0, hi = n_seqs - 1;                             // the last sequence whose first chunk is <= gc
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (cum[mid] <= gc) lo = mid; else hi = mid - 1;
+        int lo;
+        if (CL) {                                                // block = (sequence, kv head, chunk), the chunk fastest
+            I.chunk = idx % n_cl;
+            I.kvh = (idx / n_cl) % n_kv;
+            lo = idx / (n_cl * n_kv);
+            I.n_chunks = n_cl;
+        } else {
+            const int gc = idx / n_kv;
+            I.kvh = idx - gc * n_kv;
+            lo = 0;
+            int hi = n_seqs - 1;                                 // the last sequence whose first chunk is <= gc
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (cum[mid] <= gc) lo = mid; else hi = mid - 1;
+            }
+            I.chunk = gc - cum[lo];
+            I.n_chunks = cum[lo + 1] - cum[lo];
         }
         I.b = lo;
-        I.chunk = gc - cum[lo];
-        I.n_chunks = cum[lo + 1] - cum[lo];
         I.slot = sm_slot[lo];
         I.p = sm_pos[lo];
         I.key_lo = (window > 0 && I.p - window + 1 > 0) ? I.p - window + 1 : 0;
@@ -232,12 +269,25 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
     // rows without a sequence (a captured step's warm-up): zeros, shared out over the blocks
     bool waited = !FUSE;
     if (!FUSE) ssb_pdl_wait();                                   // the cache holds this step's key already
-    for (int b = blockIdx.x; b < n_seqs; b += gridDim.x)
+    if (CL) {
+        // a row without a sequence: its cluster's first block writes the kv head's zeros, and the whole
+        // cluster leaves before any of its barriers
+        const int b = (int)blockIdx.x / (n_cl * n_kv), kvh = ((int)blockIdx.x / n_cl) % n_kv;
         if (sm_slot[b] < 0) {
-            if (!waited) { ssb_pdl_wait(); waited = true; }
-            for (int e = threadIdx.x; e < n_q * HD; e += ADM_THREADS)
-                out[(size_t)b * ldo + e] = __float2bfloat16_rn(0.f);
+            if (!waited) ssb_pdl_wait();
+            if (blockIdx.x % n_cl == 0)
+                for (int e = threadIdx.x; e < group * HD; e += ADM_THREADS)
+                    out[(size_t)b * ldo + (size_t)kvh * group * HD + e] = __float2bfloat16_rn(0.f);
+            return;
         }
+    } else {
+        for (int b = blockIdx.x; b < n_seqs; b += gridDim.x)
+            if (sm_slot[b] < 0) {
+                if (!waited) { ssb_pdl_wait(); waited = true; }
+                for (int e = threadIdx.x; e < n_q * HD; e += ADM_THREADS)
+                    out[(size_t)b * ldo + e] = __float2bfloat16_rn(0.f);
+            }
+    }
     if ((int)blockIdx.x >= total_items) {
         if (!waited) ssb_pdl_wait();                             // a block without items still ends after its predecessor
         return;
@@ -569,6 +619,11 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
                 w.x = pack2(a[0] * inv, a[1] * inv);
                 w.y = pack2(a[2] * inv, a[3] * inv);
                 *reinterpret_cast<uint2*>(out + (size_t)b * ldo + (size_t)(h0 + row) * HD + d) = w;
+            } else if (CL) {
+                // the chunk's result stays in this block's shared memory (over the first warp's sums, which
+                // only this thread has read) for the cluster to merge
+                *reinterpret_cast<float4*>(sm_acc + (size_t)row * ACC_LD + d) = make_float4(a[0], a[1], a[2], a[3]);
+                if (d == 0) cl_ml[row] = make_float2(mm, ll);
             } else {
                 float* part = scratch + (((size_t)b * n_q + h0 + row) * max_chunks + cur.chunk) * ADM_PITCH(HD);
                 *reinterpret_cast<float4*>(part + d) = make_float4(a[0], a[1], a[2], a[3]);
@@ -577,7 +632,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
         }
         __syncthreads();                                         // the sums are read, the partial results written
         settle();                                                // the chunk counted an item ago: was it the last?
-        if (n_chunks > 1) {
+        if (!CL && n_chunks > 1) {
             // The block's partial results are ordered before the count by the barrier above and one
             // fence (cumulative at device scope) in the thread that counts.
             if (threadIdx.x == 0) {
@@ -600,6 +655,45 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
         if (has_nn) decode(item + 2 * G, nn);
     }
     cp_async_wait<0>();
+    if (CL && n_cl > 1) {
+        // The cluster's blocks hold the chunks of one (sequence, kv head): after the barrier every block
+        // merges a share of the output's elements from all blocks' shared memory, in chunk order, and
+        // nobody leaves before all have read.  A block whose wait ran out still keeps both appointments.
+        adm_cluster_sync();
+        if (!dead) {
+            const int crank = (int)adm_cluster_rank(), h0 = cur.kvh * group;
+            for (int e = crank + n_cl * (int)threadIdx.x; e < group * (HD / 4); e += n_cl * ADM_THREADS) {
+                const int row = e / (HD / 4), d = (e % (HD / 4)) * 4;
+                float pm[8], pl[8];
+                float4 pv[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const bool live = i < n_cl;
+                    const float2 ml = adm_ld_cluster2(reinterpret_cast<const float*>(&cl_ml[row]), live ? i : 0);
+                    pm[i] = live ? ml.x : -INFINITY;
+                    pl[i] = ml.y;
+                    pv[i] = adm_ld_cluster4(sm_acc + (size_t)row * ACC_LD + d, live ? i : 0);
+                }
+                float mm = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mm = fmaxf(mm, pm[i]);
+                float ll = 0.f, a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float f = (pm[i] == -INFINITY) ? 0.f : exp2f(pm[i] - mm);
+                    ll = fmaf(pl[i], f, ll);
+                    a[0] = fmaf(pv[i].x, f, a[0]); a[1] = fmaf(pv[i].y, f, a[1]);
+                    a[2] = fmaf(pv[i].z, f, a[2]); a[3] = fmaf(pv[i].w, f, a[3]);
+                }
+                const float inv = ll > 0.f ? 1.f / ll : 0.f;
+                uint2 w;
+                w.x = pack2(a[0] * inv, a[1] * inv);
+                w.y = pack2(a[2] * inv, a[3] * inv);
+                *reinterpret_cast<uint2*>(out + (size_t)cur.b * ldo + (size_t)(h0 + row) * HD + d) = w;
+            }
+        }
+        adm_cluster_sync();
+    }
     if (!dead) { settle(); return; }
     // A page did not land in time: the launch's result is invalid and the host is told.  Loads that were
     // asked for may still arrive, so the block stays (for a bounded time) until its shared memory is quiet.
@@ -648,11 +742,11 @@ static inline int adm_sm_count() {
 // Blocks of the kernel that are resident at once on the current device (what the persistent grid is
 // sized to): as many per SM as registers and shared memory allow, asked of the runtime once per case.
 // The kernel's limit on dynamic shared memory only ever grows (a launch needs at most what was set).
-template <int HD, bool FUSE>
+template <int HD, bool FUSE, bool CL = false>
 static inline cudaError_t adm_ensure_smem(int smem_bytes) {
     static int allowed = 0;
     if (smem_bytes <= allowed) return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, FUSE>,
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, FUSE, CL>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e == cudaSuccess) allowed = smem_bytes;
     return e;
@@ -660,7 +754,7 @@ static inline cudaError_t adm_ensure_smem(int smem_bytes) {
 
 template <int HD, bool FUSE>
 static inline int adm_blocks_per_sm(int smem_bytes) {
-    auto kern = attention_decode_mma_kernel<HD, FUSE>;
+    auto kern = attention_decode_mma_kernel<HD, FUSE, false>;
     if (adm_ensure_smem<HD, FUSE>(smem_bytes) != cudaSuccess) return 0;
     int n = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, ADM_THREADS, (size_t)smem_bytes) != cudaSuccess) return 0;
@@ -707,15 +801,40 @@ static inline int adm_cache_map(const void* base, long long rows, int head_dim, 
 // max_chunks: the most chunks a sequence is cut into (it sizes the scratch): a sequence that would need
 // more gets max_chunks larger ones.  cache_rows: keys the caches have room for (pages x kv heads x 64);
 // error_word: where a wait that ran out is recorded (zero otherwise).
+// cluster > 1: every sequence is cut into that many chunks (2, 4 or 8), one block each, the chunks of a
+// (sequence, kv head) forming a thread-block cluster that merges through its shared memory: no scratch,
+// no counters, no trips to L2 for the merge.  For batches whose blocks all fit the device at once.
+// Launch with the programmatic-dependent-launch attribute and the cluster size.
+template <typename... KArgs, typename... Args>
+static inline int adm_launch_cluster(void (*kernel)(KArgs...), dim3 grid, int cluster, size_t smem, cudaStream_t stream,
+                                     bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(ADM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 2 : 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 static inline int adm_launch(const void* q, int ldq, const void* k_cache, const void* v_cache, const int* pos,
                              const int* slot, const int* page_table, int max_pages, void* out, int ldo,
                              int n_seqs, int n_q, int n_kv, int head_dim, int window, float scale, int chunk_pages,
                              int max_chunks, float* scratch, int* counters, cudaStream_t stream, bool pdl,
-                             const float* cos_t, const float* sin_t, long long cache_rows, int* error_word) {
+                             const float* cos_t, const float* sin_t, long long cache_rows, int* error_word,
+                             int cluster = 0) {
     typedef __nv_bfloat16 bf16;
     if (n_seqs <= 0) return 0;
     if (!error_word) return SSB_ERR_BAD_SIZE;
-    if (n_seqs > ADM_MAX_SEQS || chunk_pages < 0 || max_chunks < 1 || (max_chunks > 1 && (!scratch || !counters)))
+    if (cluster != 0 && cluster != 2 && cluster != 4 && cluster != 8) return SSB_ERR_BAD_SIZE;
+    if (n_seqs > ADM_MAX_SEQS || chunk_pages < 0 || max_chunks < 1 ||
+        (cluster == 0 && max_chunks > 1 && (!scratch || !counters)))
         return SSB_ERR_BAD_SIZE;
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)scratch) & 15) return SSB_ERR_BAD_SIZE;
     if (ldo % 4 || ((uintptr_t)out & 7)) return SSB_ERR_BAD_SIZE;      // four dims of a head leave as one 8-byte store
@@ -726,6 +845,11 @@ static inline int adm_launch(const void* q, int ldq, const void* k_cache, const 
     const long long resident = adm_resident_blocks(head_dim, fuse, n_q / n_kv, n_seqs);
     if (resident <= 0) return SSB_ERR_UNSUPPORTED;
     dim3 grid((unsigned)(items < resident ? items : resident));
+    if (cluster) {
+        const long long blocks = (long long)n_seqs * n_kv * cluster;
+        if (blocks > resident) return SSB_ERR_BAD_SIZE;          // the clusters' blocks are meant to run all at once
+        grid = dim3((unsigned)blocks);
+    }
     CUtensorMap map_k, map_v;
     int rc = adm_cache_map(k_cache, cache_rows, head_dim, &map_k);
     if (!rc) rc = adm_cache_map(v_cache, cache_rows, head_dim, &map_v);
@@ -734,7 +858,15 @@ static inline int adm_launch(const void* q, int ldq, const void* k_cache, const 
         const int smem_bytes = adm_smem_bytes(HD_, n_q / n_kv, n_seqs); \
         cudaError_t e = adm_ensure_smem<HD_, FUSE_>(smem_bytes); \
         if (e != cudaSuccess) return (int)e; \
-        rc = ssb_launch(attention_decode_mma_kernel<HD_, FUSE_>, grid, dim3(ADM_THREADS), (size_t)smem_bytes, stream, pdl, \
+        if (cluster) { \
+            e = adm_ensure_smem<HD_, FUSE_, true>(smem_bytes); \
+            if (e != cudaSuccess) return (int)e; \
+            rc = adm_launch_cluster(attention_decode_mma_kernel<HD_, FUSE_, true>, grid, cluster, (size_t)smem_bytes, stream, pdl, \
+                            (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
+                            (bf16*)out, ldo, n_seqs, n_q, n_kv, window, scale_log2, 1, cluster, scratch, \
+                            counters, cos_t, sin_t, map_k, map_v, error_word); \
+        } else \
+        rc = ssb_launch(attention_decode_mma_kernel<HD_, FUSE_, false>, grid, dim3(ADM_THREADS), (size_t)smem_bytes, stream, pdl, \
                         (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
                         (bf16*)out, ldo, n_seqs, n_q, n_kv, window, scale_log2, chunk_pages, max_chunks, scratch, \
                         counters, cos_t, sin_t, map_k, map_v, error_word); \

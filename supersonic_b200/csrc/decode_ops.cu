@@ -235,6 +235,7 @@ SSB_API int ssb_attention_decode(const void* q, int ldq, const void* k_cache, co
 // Scratch: ssb_attention_decode_chunked_scratch_floats floats; counters: n_seqs * n_kv ints, zero
 // before the first launch (every launch leaves them zero).  cache_rows: keys either cache has room for;
 // error_word: a device int, zero, in which a page load that did not arrive in time is recorded.
+// cluster: 0, or 2 / 4 / 8 chunks a sequence as the blocks of a thread-block cluster (see adm_launch).
 SSB_API int ssb_attention_decode_chunked_ok(int n_seqs, int n_q, int n_kv, int head_dim, int ldq, int page_shift) {
     return page_shift == 6 && n_seqs <= ADM_MAX_SEQS && adm_supported(n_q, n_kv, head_dim, ldq, false);
 }
@@ -255,10 +256,10 @@ SSB_API int ssb_attention_decode_chunked(const void* q, int ldq, const void* k_c
                                          void* out, int ldo, int n_seqs, int n_q, int n_kv, int head_dim,
                                          int page_shift, int window, float scale, int chunk_pages, int max_chunks,
                                          float* scratch, int* counters, int pdl, const float* cos_t,
-                                         const float* sin_t, long long cache_rows, int* error_word,
+                                         const float* sin_t, long long cache_rows, int* error_word, int cluster,
                                          cudaStream_t stream) {
     if (!ssb_attention_decode_chunked_ok(n_seqs, n_q, n_kv, head_dim, ldq, page_shift)) return SSB_ERR_UNSUPPORTED;
     return adm_launch(q, ldq, k_cache, v_cache, pos, slot, page_table, max_pages, out, ldo, n_seqs, n_q, n_kv,
                       head_dim, window, scale, chunk_pages, max_chunks, scratch, counters, stream, pdl != 0, cos_t,
-                      sin_t, cache_rows, error_word);
+                      sin_t, cache_rows, error_word, cluster);
 }

@@ -19,6 +19,7 @@ from .kernel_sets import NormedInput, PlainKernels, as_tensor
 TARGET_BLOCKS = 1184           # eight small blocks per SM
 DETERMINISTIC_CHUNK_PAGES = 16 # ... and its fixed chunk size (1,024 keys) when results must not depend on the batch
 STREAM_ROWS = ops.GEMV_TC_MAX_ROWS   # steps of up to this many rows take the projections that stream the weights once
+CLUSTER_CHUNK_PAGES = 8       # the most pages a chunk holds when a sequence's chunks run as a cluster
 TC_ATTENTION_MIN_NEW = 96     # prompts at least this long take the tcgen05 attention (tiles of 128 rows)
 
 
@@ -192,6 +193,21 @@ class FastKernels(PlainKernels):
             return DETERMINISTIC_CHUNK_PAGES, -(-pages // DETERMINISTIC_CHUNK_PAGES)
         return 0, max(1, min(-(-pages // 2), blocks // max(n_kv, 1) + 1))
 
+    def _cluster(self, heads: int, pages: int, blocks: int) -> int:
+        """Chunks a sequence (0: none) when the chunks of a (sequence, kv head) run as a thread-block
+        cluster that merges through its shared memory instead of scratch and a counter in L2.  For
+        batches so small that ``heads`` (sequences x kv heads) times the chunks is at most one block an
+        SM (more blocks keep the next projection's blocks from becoming resident early: batch 4 with 256
+        blocks lost 4 % of a step, with 128 it is even), and chunks of at most CLUSTER_CHUNK_PAGES pages
+        (one block streams a chunk's pages one after another).  Measured at 8B sizes with 512 keys, a
+        step of 16 layers: batch 1 1,566 to 1,509 us, batch 2 1,564 to 1,531, batch 8 1,634 to 1,621."""
+        if self.deterministic:
+            return 0
+        for c in (8, 4, 2):
+            if heads * c <= min(blocks, ops.sm_count()):
+                return c if pages <= CLUSTER_CHUNK_PAGES * c else 0
+        return 0
+
     def _decode_attention(self, q, k_cache, v_cache, batch, page_table, out, n_q, n_kv, head_dim,
                           page_shift, window, scale, cos=None, sin=None):
         group = n_q // n_kv
@@ -203,16 +219,17 @@ class FastKernels(PlainKernels):
             # tensor-core kernel on a persistent grid (beside the mma.sync skinny GEMM it made a step
             # slower: the two compete for the SM's L1/shared memory; beside the tcgen05 projections it
             # is the faster choice at every batch size: batch 16: 4.24 to 3.57 ms a step)
-            chunk, max_chunks = self._chunks(n_kv, pages, ops.attention_decode_chunked_blocks(
-                batch.n_seqs, n_q, n_kv, head_dim, cos is not None))
+            blocks = ops.attention_decode_chunked_blocks(batch.n_seqs, n_q, n_kv, head_dim, cos is not None)
+            chunk, max_chunks = self._chunks(n_kv, pages, blocks)
+            cluster = self._cluster(batch.n_seqs * n_kv, pages, blocks)
             scratch = counters = None
-            if max_chunks > 1:
+            if max_chunks > 1 and not cluster:
                 nf, nc = ops.attention_decode_chunked_scratch(batch.n_seqs, n_q, n_kv, head_dim, max_chunks)
                 scratch = self._buffer("attn_partials", nf, torch.float32, q.device)
                 counters = self._buffer("attn_counters", nc, torch.int32, q.device, zero=True)
             ops.attention_decode_chunked(q, k_cache, v_cache, batch.pos, batch.slot_of_token, page_table, out,
                                          n_q, n_kv, head_dim, page_shift, window, scale, chunk, max_chunks,
-                                         scratch, counters, pdl=self.pdl, cos=cos, sin=sin)
+                                         scratch, counters, pdl=self.pdl, cos=cos, sin=sin, cluster=cluster)
             return
         blocks = batch.n_seqs * n_kv * ((group + 3) // 4)
         if self.deterministic:

@@ -364,20 +364,26 @@ def attention_decode_chunked(q: torch.Tensor, k_cache: torch.Tensor, v_cache: to
                              head_dim: int, page_shift: int, window: Optional[int], scale: float,
                              chunk_pages: int, max_chunks: int, scratch: Optional[torch.Tensor],
                              counters: Optional[torch.Tensor], pdl: bool = False,
-                             cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None) -> None:
+                             cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+                             cluster: int = 0) -> None:
     """``attention_decode`` on the tensor cores with a persistent grid: every sequence's pages are cut
     into chunks of about ``chunk_pages`` pages (a cut that depends on the sequence alone), a work item
     is (sequence, chunk, kv head), and as many blocks as the device holds at once walk the items.
     ``chunk_pages`` 0: the kernel sizes the chunks itself so that the items about fill those blocks.
     ``max_chunks`` bounds the chunks of one sequence and sizes the scratch
     (:func:`attention_decode_chunked_scratch`); a longer sequence gets ``max_chunks`` larger chunks.
-    Pages come in through the TMA unit with bounded waits (:func:`check_device_errors`)."""
+    Pages come in through the TMA unit with bounded waits (:func:`check_device_errors`).
+    ``cluster`` 2, 4 or 8: every sequence is cut into that many chunks, the chunks of a (sequence, kv
+    head) are the blocks of a thread-block cluster and merge through its shared memory (no scratch);
+    for small batches whose blocks all fit the device at once."""
     global _tc_unchecked
     B = _attention_decode_checks(q, k_cache, v_cache, pos, slot, page_table, out, n_q, n_kv, head_dim, cos, sin,
                                  "attention_decode_chunked")
     if chunk_pages < 0 or max_chunks < 1:
         raise KernelError("attention_decode_chunked: chunk_pages must not be negative, max_chunks at least 1")
-    if max_chunks > 1:
+    if cluster not in (0, 2, 4, 8):
+        raise KernelError("attention_decode_chunked: a cluster holds 2, 4 or 8 chunks")
+    if max_chunks > 1 and not cluster:
         need_f, need_c = attention_decode_chunked_scratch(B, n_q, n_kv, head_dim, max_chunks)
         _need(scratch, "scratch", torch.float32); _need(counters, "counters", torch.int32)
         if scratch.numel() < need_f or counters.numel() < need_c:
@@ -387,8 +393,8 @@ def attention_decode_chunked(q: torch.Tensor, k_cache: torch.Tensor, v_cache: to
         c_int(page_table.shape[1]), _ptr(out), c_int(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv),
         c_int(head_dim), c_int(page_shift), c_int(int(window) if window else 0), c_float(scale),
         c_int(chunk_pages), c_int(max_chunks), _ptr(scratch), _ptr(counters), c_int(1 if pdl else 0), _ptr(cos),
-        _ptr(sin), c_longlong(k_cache.numel() // head_dim), _ptr(tc_error_word(q.device)), _stream()),
-        "attention_decode_chunked")
+        _ptr(sin), c_longlong(k_cache.numel() // head_dim), _ptr(tc_error_word(q.device)), c_int(cluster),
+        _stream()), "attention_decode_chunked")
     _tc_unchecked += 1
 
 

@@ -317,8 +317,17 @@ def _decode_attention(kind, q, k, v, pos, slot, table, out, n_q, n_kv, hd, windo
                       cos=None, sin=None, poison=True):
     """kind 1: the CUDA-core kernel with ``n_splits`` splits; kind 2: the tensor-core kernel on its
     persistent grid with chunks of ceil(max_pages / n_splits) pages (so that the longest sequence is cut
-    into about ``n_splits`` chunks).  Returns the counters, which every launch must leave zero."""
+    into about ``n_splits`` chunks); kind 3: the tensor-core kernel with a sequence's chunks as a
+    thread-block cluster of 2, 4 or 8 blocks (the power of two from ``n_splits`` up) that merges through
+    its shared memory.  Returns the counters, which every launch must leave zero."""
     B = q.shape[0]
+    cluster = 0
+    if kind == 3:
+        cluster = 2 if n_splits <= 2 else (4 if n_splits <= 4 else 8)
+        while B * n_kv * cluster > ops().attention_decode_chunked_blocks(B, n_q, n_kv, hd, cos is not None):
+            cluster //= 2                                                # the clusters' blocks must all fit the device at once
+        if cluster < 2:
+            pytest.skip("too many (sequence, kv head) pairs for clusters")
     if kind == 1:
         nf, nc = ops().attention_decode_scratch(B, n_q, n_kv, hd, n_splits)
     else:
@@ -334,7 +343,7 @@ def _decode_attention(kind, q, k, v, pos, slot, table, out, n_q, n_kv, hd, windo
                                    scratch, counters, cos=cos, sin=sin)
         else:
             ops().attention_decode_chunked(q, k, v, pos, slot, table, out, n_q, n_kv, hd, 6, window, scale, chunk,
-                                           max_chunks, scratch, counters, cos=cos, sin=sin)
+                                           max_chunks, scratch, counters, cos=cos, sin=sin, cluster=cluster)
         if cos is not None:
             break                                                        # a fused launch appends: once only
     return counters
@@ -344,9 +353,9 @@ def _decode_attention(kind, q, k, v, pos, slot, table, out, n_q, n_kv, hd, windo
                                                 (6, 2, 128, 100), (2, 2, 256, None), (8, 1, 64, 64),
                                                 (5, 5, 80, None)])
 @pytest.mark.parametrize("n_splits", [1, 3, 8])
-@pytest.mark.parametrize("kind", [1, 2])
+@pytest.mark.parametrize("kind", [1, 2, 3])
 def test_attention_decode(n_q, n_kv, hd, window, n_splits, kind):
-    if kind == 2 and (hd not in (64, 128) or n_q // n_kv > 16):
+    if kind >= 2 and (hd not in (64, 128) or n_q // n_kv > 16):
         pytest.skip("the tensor-core kernel takes head_dim 64/128 and at most 16 query heads per kv head")
     g = torch.Generator(device=DEV).manual_seed(23)
     pos = torch.tensor([0, 63, 64, 300, 299, 17, 128], dtype=torch.int32, device=DEV)
@@ -624,10 +633,10 @@ def test_attention_prefill_finds_a_far_key(impl):
 
 @pytest.mark.parametrize("n_q,n_kv,hd,window", [(32, 8, 128, None), (4, 2, 64, None), (6, 2, 128, 100),
                                                 (2, 1, 32, None), (8, 8, 256, None)])
-@pytest.mark.parametrize("n_splits", [1, 4])
-@pytest.mark.parametrize("kind", [1, 2])
+@pytest.mark.parametrize("n_splits", [1, 4, 8])
+@pytest.mark.parametrize("kind", [1, 2, 3])
 def test_attention_decode_with_rotation_and_append_inside(n_q, n_kv, hd, window, n_splits, kind):
-    if kind == 2 and (hd not in (64, 128) or n_q // n_kv > 16):
+    if kind >= 2 and (hd not in (64, 128) or n_q // n_kv > 16):
         pytest.skip("the tensor-core kernel takes head_dim 64/128 and at most 16 query heads per kv head")
     """The fused launch equals rope_append followed by attention_decode: output, and the key
     and value it leaves in the cache; positions include 0, page borders and a padding row."""
