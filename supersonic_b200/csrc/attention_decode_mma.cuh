@@ -233,6 +233,9 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
         I.page0 = pt[min(I.pf, I.page_hi)];
         I.page1 = pt[min(I.pf + 1, I.page_hi)];
     };
+    // keys and values pass through L2 once a step: they leave it first, so that what every layer reads
+    // again (positions, page tables, rotation tables, activations) stays
+    const uint64_t kv_policy = ssb_policy_evict_first();
     int page_ahead = 0, page_ahead_of = -1;      // id of the page STAGES after the one in work, asked for one turn early
     auto load_page = [&](const AdmItem& I, int i, int stage) {
         if (threadIdx.x != 0) return;
@@ -244,8 +247,8 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
         mbar_expect_tx(bar, 2 * TILE_BYTES);
 #pragma unroll
         for (int h = 0; h < HD / 64; ++h) {
-            tma_load_2d(kd + h * 8192, &map_k, bar, 64 * h, y);
-            tma_load_2d(vd + h * 8192, &map_v, bar, 64 * h, y);
+            tma_load_2d_hint(kd + h * 8192, &map_k, bar, 64 * h, y, kv_policy);
+            tma_load_2d_hint(vd + h * 8192, &map_v, bar, 64 * h, y, kv_policy);
         }
     };
     auto load_query = [&](const AdmItem& I, int which) {

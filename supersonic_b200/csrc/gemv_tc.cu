@@ -83,10 +83,12 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             // (8B gate/up: 38.0 to 35.9 us at 8 rows, 40.7 to 39.3 at 64; a step gains about half a per cent).
             const int rot = my_blocks > 0 ? (int)(((unsigned)tile * GV_ROT) % (unsigned)my_blocks) : 0;
             auto kb_of = [&](int i) { const int j = i + rot; return kb0 + (j >= my_blocks ? j - my_blocks : j); };
+            // the weights pass through L2 once a step: they are the first to leave it again
+            const uint64_t w_policy = ssb_policy_evict_first();
             const int pre = min(my_blocks, GV_STAGES);
             for (int i = 0; i < pre; ++i) {                  // the ring is empty: no wait for a free stage
                 mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
-                tma_load_2d(smem_u32(smem + i * STAGE_BYTES), &map_w, full0 + 8 * i, kb_of(i) * TC_BK, n0);
+                tma_load_2d_hint(smem_u32(smem + i * STAGE_BYTES), &map_w, full0 + 8 * i, kb_of(i) * TC_BK, n0, w_policy);
             }
             ssb_pdl_wait();                                  // x is the predecessor's output
             for (int i = 0; i < pre; ++i)
@@ -100,7 +102,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 const uint32_t w_dst = smem_u32(smem + s * STAGE_BYTES), x_dst = w_dst + W_BYTES;
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-                tma_load_2d(w_dst, &map_w, full0 + 8 * s, kb_of(i) * TC_BK, n0);
+                tma_load_2d_hint(w_dst, &map_w, full0 + 8 * s, kb_of(i) * TC_BK, n0, w_policy);
                 tma_load_2d(x_dst, &map_x, full0 + 8 * s, kb_of(i) * TC_BK, 0);
                 issued = i + 1;
             }
