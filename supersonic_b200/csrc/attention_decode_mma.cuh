@@ -251,17 +251,24 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
             tma_load_2d_hint(vd + h * 8192, &map_v, bar, 64 * h, y, kv_policy);
         }
     };
+    // The rotation tables' row of the item's position: written by no kernel of a step, so it may be
+    // asked for before the dependency wait (it joins the next cp.async group that is committed).
+    auto load_tables = [&](const AdmItem& I, int which) {
+        if (!FUSE) return;
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(qbufs + which * QBUF_BYTES);
+        const int e = threadIdx.x;                               // HALF / 4 chunks per table row
+        if (e < HALF / 4) {
+            cp_async16(dst + COS_OFF + e * 16, cos_t + (size_t)I.p * HALF + e * 4);
+            cp_async16(dst + SIN_OFF + e * 16, sin_t + (size_t)I.p * HALF + e * 4);
+        }
+    };
     auto load_query = [&](const AdmItem& I, int which) {
         const uint32_t dst = (uint32_t)__cvta_generic_to_shared(qbufs + which * QBUF_BYTES);
         const __nv_bfloat16* row = q + (size_t)I.b * ldq;
         for (int e = threadIdx.x; e < group * CHUNKS; e += ADM_THREADS)
             cp_async16(dst + Q_OFF + e * 16, row + (size_t)I.kvh * group * HD + e * 8);
         if (FUSE) {
-            const int e = threadIdx.x;                           // 128 threads: HALF / 4 chunks per table row, CHUNKS per vector
-            if (e < HALF / 4) {
-                cp_async16(dst + COS_OFF + e * 16, cos_t + (size_t)I.p * HALF + e * 4);
-                cp_async16(dst + SIN_OFF + e * 16, sin_t + (size_t)I.p * HALF + e * 4);
-            }
+            const int e = threadIdx.x;                           // CHUNKS per vector
             if (e < CHUNKS) {
                 cp_async16(dst + KN_OFF + e * 16, row + (size_t)(n_q + I.kvh) * HD + e * 8);
                 cp_async16(dst + VN_OFF + e * 16, row + (size_t)(n_q + n_kv + I.kvh) * HD + e * 8);
@@ -377,6 +384,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
         if (cursor_item > 1 || (cursor_item == 1 && !has_nxt)) return false;
         const AdmItem& I = cursor_item == 0 ? cur : nxt;
         if (cursor_pos < 0) {
+            load_tables(I, parity ^ cursor_item);
             load_query(I, parity ^ cursor_item);
             cp_async_commit();
             cursor_pos = 0;
@@ -392,6 +400,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
     // the first item: its pages may be asked for before the dependency wait; its query, and anything
     // of the item after it, only after
     while (pu_issued < STAGES && cursor_item == 0) issue_group();
+    load_tables(cur, 0);
     if (!waited) { ssb_pdl_wait(); waited = true; }
     load_query(cur, 0);
     cp_async_commit();
