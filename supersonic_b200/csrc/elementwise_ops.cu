@@ -19,10 +19,19 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows, co
                    bf16* __restrict__ out, int hidden) {
     __shared__ float red[RN_THREADS / 32];
     ssb_pdl_launch_dependents();
-    ssb_pdl_wait();
     const int r = blockIdx.x;
-    const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * hidden);
     const int n4 = hidden / 4;
+    // The norm's weights are written by no kernel of a step: they are in registers before the dependency
+    // wait, so that after it only the row itself has to come (one trip to L2 on the critical path, not two).
+    float wv[RV][4];
+#pragma unroll
+    for (int i = 0; i < RV; ++i) {
+        const int c = threadIdx.x + i * RN_THREADS;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) wv[i][k] = c < n4 ? ssb_to_float(w[4 * c + k]) : 0.f;
+    }
+    ssb_pdl_wait();
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * hidden);
     float4 v[RV];
     float part = 0.f;
 #pragma unroll
@@ -44,10 +53,8 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows, co
     for (int i = 0; i < RV; ++i) {
         const int c = threadIdx.x + i * RN_THREADS;
         if (c >= n4) continue;
-        const float w0 = ssb_to_float(w[4 * c]), w1 = ssb_to_float(w[4 * c + 1]);
-        const float w2 = ssb_to_float(w[4 * c + 2]), w3 = ssb_to_float(w[4 * c + 3]);
-        __nv_bfloat162 a = __floats2bfloat162_rn(v[i].x * inv * w0, v[i].y * inv * w1);
-        __nv_bfloat162 b = __floats2bfloat162_rn(v[i].z * inv * w2, v[i].w * inv * w3);
+        __nv_bfloat162 a = __floats2bfloat162_rn(v[i].x * inv * wv[i][0], v[i].y * inv * wv[i][1]);
+        __nv_bfloat162 b = __floats2bfloat162_rn(v[i].z * inv * wv[i][2], v[i].w * inv * wv[i][3]);
         uint2 p;
         p.x = *reinterpret_cast<uint32_t*>(&a);
         p.y = *reinterpret_cast<uint32_t*>(&b);
