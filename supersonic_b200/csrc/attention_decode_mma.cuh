@@ -1,6 +1,10 @@
 // Decode attention on the tensor cores, for head sizes 64 and 128 and up to 16 query heads per
-// kv head: the query heads that share a kv head are the rows of one m16n8k16 tile, so a page of
-// 64 keys costs a block 16 + 16 MMAs per warp instead of thousands of scalar instructions.
+// kv head.  The products are taken transposed, S^T = K Q^T and O^T = V^T P^T: a warp's 16 keys of a
+// page are the 16 rows of an m16n8k16 tile (all used) and the query heads that share the kv head its 8
+// columns, so a page costs a warp 8 + 8 MMAs for up to 8 heads per kv head (16 + 16 for 9 to 16).
+// With the heads as rows, as the kernel first had it, three quarters of a tile's rows were padding at
+// four heads per kv head, it took twice the MMAs, and mma.sync is what bounds a page's arithmetic here
+// (64 x 520: 30.0 to 24.8 us; 8 x 8,192: 45.8 to 41.9).
 //
 // Work items and a persistent grid.  A sequence's pages are cut into chunks of about
 // ``chunk_pages`` pages (as many chunks as that needs, of even size: the cut depends on the
@@ -14,10 +18,12 @@
 // Per item one thread asks the TMA unit for a page of keys and values (tiled loads of 64 keys x 64
 // dims with the 128-byte swizzle, two stages, an mbarrier per stage that counts the bytes; every
 // wait is bounded and a wait that runs out is recorded in a device word); each warp takes 16 of
-// the page's 64 keys: S = Q K^T (16 x 16), online softmax in float32, O += P V.  Warps merge in
+// the page's 64 keys: S^T = K Q^T (16 keys x 8 heads), online softmax in float32, O^T += V^T P^T.  Warps merge in
 // shared memory; a sequence of several chunks leaves partial results in scratch and the item that
 // arrives last for its (sequence, kv head) merges them in chunk order (maxima kept in the log2
-// domain; a partial result is head_dim sums, the maximum, the sum of weights, in 16-byte units).  Nothing waits on another block.
+// domain; a partial result is head_dim sums, the maximum, the sum of weights, in 16-byte units).
+// Nothing waits on another block; at small batch a sequence's chunks are instead the blocks of a
+// thread-block cluster that merges through distributed shared memory (CL).
 // With FUSE the rows of q are the raw fused projection [q | k | v]: queries are rotated while
 // the fragments are built, and the item that owns the token's page rotates its key, appends key
 // and value to the cache and attends to them from registers.
@@ -40,6 +46,12 @@ constexpr int ADM_ROWS = 16;          // query heads per kv head, padded to the 
 // SM the loads in flight already cover the memory's latency.
 __host__ __device__ constexpr int adm_stages(int /*head_dim*/) { return 2; }
 constexpr int ADM_MAX_SEQS = 1024;    // sequences a launch can take (their slots, positions and chunk counts sit in shared memory)
+// Transpose an 8 x 8 matrix of 16-bit values held across the warp (lane 4 r + c holds row r, columns 2 c, 2 c + 1).
+__device__ __forceinline__ uint32_t adm_transpose8(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
@@ -77,7 +89,7 @@ __device__ __forceinline__ float2 adm_ld_cluster2(const float* local, unsigned r
     return v;
 }
 
-template <int HD, bool FUSE, bool CL>
+template <int HD, bool FUSE, bool CL, int NT>   // NT: tiles of 8 query heads per kv head (1: up to 8 heads, 2: up to 16)
 __global__ void __launch_bounds__(ADM_THREADS)
 attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_bfloat16* k_cache,
                             __nv_bfloat16* v_cache, const int* __restrict__ pos, const int* __restrict__ slot,
@@ -413,13 +425,14 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
         cp_async_wait<0>();                                      // this item's query (and, harmlessly, the next one's)
         __syncthreads();
 
-        // Query fragments: row = head (g and g + 8), this lane's columns 16 ks + 2t (+1, +8, +9).
-        // Rotation pairs (d, d + HD/2) are both in this lane (k-steps ks and ks + KS/2).
+        // Query fragments, the B operand of S^T = K Q^T: head g (and, with two tiles of heads, g + 8),
+        // this lane's dims 16 ks + 2t (+1, +8, +9).  Rotation pairs (d, d + HD/2) are both in this lane
+        // (k-steps ks and ks + KS/2).  qf[ks][0], [2]: heads 0-7; [1], [3]: heads 8-15.
         uint32_t qf[KS][4];
         {
-            float qa[2][KS][4];                                  // [row half][k-step][element]
+            float qa[2][KS][4];                                  // [tile of heads][k-step][element]
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
+            for (int i = 0; i < NT; ++i) {
                 const int row = g + 8 * i;
                 const unsigned char* qr = qb + Q_OFF + row * HD * 2;
 #pragma unroll
@@ -443,7 +456,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
                         const int idx = 16 * ks + 2 * t + (e & 1) + (e >> 1) * 8;      // < HD/2
                         const float c = cs[idx], sn = sn_[idx];
 #pragma unroll
-                        for (int i = 0; i < 2; ++i) {
+                        for (int i = 0; i < NT; ++i) {
                             const float x1 = qa[i][ks][e], x2 = qa[i][ks + KS / 2][e];
                             qa[i][ks][e] = x1 * c - x2 * sn;
                             qa[i][ks + KS / 2][e] = x1 * sn + x2 * c;
@@ -453,15 +466,25 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
                 qf[ks][0] = pack2(qa[0][ks][0] * scale_log2, qa[0][ks][1] * scale_log2);
-                qf[ks][1] = pack2(qa[1][ks][0] * scale_log2, qa[1][ks][1] * scale_log2);
                 qf[ks][2] = pack2(qa[0][ks][2] * scale_log2, qa[0][ks][3] * scale_log2);
-                qf[ks][3] = pack2(qa[1][ks][2] * scale_log2, qa[1][ks][3] * scale_log2);
+                if (NT == 2) {
+                    qf[ks][1] = pack2(qa[1][ks][0] * scale_log2, qa[1][ks][1] * scale_log2);
+                    qf[ks][3] = pack2(qa[1][ks][2] * scale_log2, qa[1][ks][3] * scale_log2);
+                } else {
+                    qf[ks][1] = qf[ks][3] = 0u;
+                }
             }
         }
-        float o[HD / 8][4];
+        // O^T = V^T P^T: ot[jm][nt][e] is dim 16 jm + g + 8 (e >> 1) of head 8 nt + 2t + (e & 1)
+        float ot[HD / 16][NT][4];
+        float m_run[NT][2], l_run[NT][2];                        // per head 8 nt + 2t + c; l: this lane's keys' share of the sum
 #pragma unroll
-        for (int j = 0; j < HD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
-        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // l: this lane's share of the row sum
+        for (int nt = 0; nt < NT; ++nt) {
+            m_run[nt][0] = m_run[nt][1] = -INFINITY;
+            l_run[nt][0] = l_run[nt][1] = 0.f;
+#pragma unroll
+            for (int j = 0; j < HD / 16; ++j) { ot[j][nt][0] = ot[j][nt][1] = ot[j][nt][2] = ot[j][nt][3] = 0.f; }
+        }
 
         for (int i = 0; i < cur.units; ++i) {
             if (i + STAGES < cur.units) {     // needed when this turn ends: a turn's arithmetic hides the load
@@ -476,57 +499,69 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
             const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(smem + (STAGES + stage) * TILE_BYTES);
             const int key0 = ((cur.pf + i) << 6) + 16 * warp;    // this warp's 16 keys of the page
             if (key0 <= key_hi && key0 + 15 >= key_lo) {
-                float sc[2][4];
+                // S^T = K Q^T: the page's 16 keys of this warp are the rows (all 16 used), the heads the columns
+                float st[NT][4];
 #pragma unroll
-                for (int j = 0; j < 2; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
+                for (int nt = 0; nt < NT; ++nt) { st[nt][0] = st[nt][1] = st[nt][2] = st[nt][3] = 0.f; }
 #pragma unroll
                 for (int ks = 0; ks < KS; ++ks) {
-                    uint32_t b0, b1, b2, b3;
-                    const int key = 16 * warp + ((lane >> 4) << 3) + (lane & 7);
-                    ldmatrix_x4(kbase + adm_tile_offset(key, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
-                    mma16816(sc[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
-                    mma16816(sc[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+                    uint32_t a0, a1, a2, a3;
+                    const int key = 16 * warp + (lane & 7) + (((lane >> 3) & 1) << 3);
+                    ldmatrix_x4(kbase + adm_tile_offset(key, ks * 2 + (lane >> 4)), a0, a1, a2, a3);
+                    mma16816(st[0], a0, a1, a2, a3, qf[ks][0], qf[ks][2]);
+                    if (NT == 2) mma16816(st[NT - 1], a0, a1, a2, a3, qf[ks][1], qf[ks][3]);
                 }
-                float m_new[2] = {m_run[0], m_run[1]};
+                // st[nt][e]: key key0 + g + 8 (e >> 1), head 8 nt + 2t + (e & 1)
+                float m_new[NT][2], alpha[NT][2], row_sum[NT][2];
 #pragma unroll
-                for (int j = 0; j < 2; ++j)
+                for (int nt = 0; nt < NT; ++nt) {
+                    m_new[nt][0] = m_run[nt][0]; m_new[nt][1] = m_run[nt][1];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const int key = key0 + j * 8 + 2 * t + (e & 1);
-                        const float v = (key >= key_lo && key <= key_hi) ? sc[j][e] : -INFINITY;
-                        sc[j][e] = v;
-                        m_new[e >> 1] = fmaxf(m_new[e >> 1], v);
+                        const int key = key0 + g + 8 * (e >> 1);
+                        const float v = (key >= key_lo && key <= key_hi) ? st[nt][e] : -INFINITY;
+                        st[nt][e] = v;
+                        m_new[nt][e & 1] = fmaxf(m_new[nt][e & 1], v);
                     }
 #pragma unroll
-                for (int r = 0; r < 2; ++r) {
-                    m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 1));
-                    m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 2));
-                }
-                float alpha[2], row_sum[2] = {0.f, 0.f};
-#pragma unroll
-                for (int r = 0; r < 2; ++r) alpha[r] = (m_new[r] == -INFINITY) ? 1.f : exp2f(m_run[r] - m_new[r]);
-#pragma unroll
-                for (int j = 0; j < 2; ++j)
+                    for (int c = 0; c < 2; ++c) {                // over the 16 keys: the lanes that differ in g
+                        m_new[nt][c] = fmaxf(m_new[nt][c], __shfl_xor_sync(0xffffffffu, m_new[nt][c], 4));
+                        m_new[nt][c] = fmaxf(m_new[nt][c], __shfl_xor_sync(0xffffffffu, m_new[nt][c], 8));
+                        m_new[nt][c] = fmaxf(m_new[nt][c], __shfl_xor_sync(0xffffffffu, m_new[nt][c], 16));
+                        alpha[nt][c] = (m_new[nt][c] == -INFINITY) ? 1.f : exp2f(m_run[nt][c] - m_new[nt][c]);
+                        row_sum[nt][c] = 0.f;
+                    }
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const int r = e >> 1;
-                        const float pj = (m_new[r] == -INFINITY) ? 0.f : exp2f(sc[j][e] - m_new[r]);
-                        sc[j][e] = pj;
-                        row_sum[r] += pj;
+                        const int c = e & 1;
+                        const float pj = (m_new[nt][c] == -INFINITY) ? 0.f : exp2f(st[nt][e] - m_new[nt][c]);
+                        st[nt][e] = pj;
+                        row_sum[nt][c] += pj;
                     }
 #pragma unroll
-                for (int r = 0; r < 2; ++r) { l_run[r] = l_run[r] * alpha[r] + row_sum[r]; m_run[r] = m_new[r]; }
+                    for (int c = 0; c < 2; ++c) { l_run[nt][c] = l_run[nt][c] * alpha[nt][c] + row_sum[nt][c]; m_run[nt][c] = m_new[nt][c]; }
 #pragma unroll
-                for (int j = 0; j < HD / 8; ++j) { o[j][0] *= alpha[0]; o[j][1] *= alpha[0]; o[j][2] *= alpha[1]; o[j][3] *= alpha[1]; }
-                const uint32_t a0 = pack2(sc[0][0], sc[0][1]), a1 = pack2(sc[0][2], sc[0][3]);
-                const uint32_t a2 = pack2(sc[1][0], sc[1][1]), a3 = pack2(sc[1][2], sc[1][3]);
+                    for (int j = 0; j < HD / 16; ++j) {
+                        ot[j][nt][0] *= alpha[nt][0]; ot[j][nt][1] *= alpha[nt][1];
+                        ot[j][nt][2] *= alpha[nt][0]; ot[j][nt][3] *= alpha[nt][1];
+                    }
+                }
+                // P^T as the B operand (keys 2t, 2t + 1 (+ 8) of head g): the 8 x 8 halves of the scores, transposed
+                uint32_t pb0[NT], pb1[NT];
 #pragma unroll
-                for (int jp = 0; jp < HD / 16; ++jp) {
-                    uint32_t b0, b1, b2, b3;
-                    const int key = 16 * warp + (((lane >> 3) & 1) << 3) + (lane & 7);
-                    ldmatrix_x4_trans(vbase + adm_tile_offset(key, jp * 2 + (lane >> 4)), b0, b1, b2, b3);
-                    mma16816(o[2 * jp], a0, a1, a2, a3, b0, b1);
-                    mma16816(o[2 * jp + 1], a0, a1, a2, a3, b2, b3);
+                for (int nt = 0; nt < NT; ++nt) {
+                    pb0[nt] = adm_transpose8(pack2(st[nt][0], st[nt][1]));
+                    pb1[nt] = adm_transpose8(pack2(st[nt][2], st[nt][3]));
+                }
+                // O^T += V^T P^T: 16 dims a tile are the rows
+#pragma unroll
+                for (int jm = 0; jm < HD / 16; ++jm) {
+                    uint32_t a0, a1, a2, a3;
+                    const int mi = lane >> 3;
+                    const int key = 16 * warp + (lane & 7) + ((mi >> 1) << 3);
+                    ldmatrix_x4_trans(vbase + adm_tile_offset(key, jm * 2 + (mi & 1)), a0, a1, a2, a3);
+                    mma16816(ot[jm][0], a0, a1, a2, a3, pb0[0], pb1[0]);
+                    if (NT == 2) mma16816(ot[jm][NT - 1], a0, a1, a2, a3, pb0[NT - 1], pb1[NT - 1]);
                 }
             }
             __syncthreads();                                     // the stage may be refilled
@@ -567,49 +602,67 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ldq, __nv_b
                     *reinterpret_cast<uint32_t*>(k_cache + row + 16 * ks + 2 * t + 8) = pack2(kn[ks][2], kn[ks][3]);
                 }
             }
-            float sn2[2] = {0.f, 0.f};                           // scores of rows g and g + 8 (log2 domain)
+            // the token's value: four dims a lane, copied into the cache as they are
+            for (int d = lane * 4; d < HD; d += 128)
+                *reinterpret_cast<uint2*>(v_cache + row + d) = *reinterpret_cast<const uint2*>(v_src + d * 2);
+            // scores (log2 domain) of head g, and g + 8, from the query fragments; then each lane fetches
+            // those of its own heads 2t, 2t + 1 from the lanes that hold them
+            float sn2[NT];
 #pragma unroll
-            for (int ks = 0; ks < KS; ++ks) {
-                sn2[0] += bf16lo(qf[ks][0]) * kn[ks][0] + bf16hi(qf[ks][0]) * kn[ks][1]
-                        + bf16lo(qf[ks][2]) * kn[ks][2] + bf16hi(qf[ks][2]) * kn[ks][3];
-                sn2[1] += bf16lo(qf[ks][1]) * kn[ks][0] + bf16hi(qf[ks][1]) * kn[ks][1]
-                        + bf16lo(qf[ks][3]) * kn[ks][2] + bf16hi(qf[ks][3]) * kn[ks][3];
+            for (int nt = 0; nt < NT; ++nt) {
+                sn2[nt] = 0.f;
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks)
+                    sn2[nt] += bf16lo(qf[ks][nt]) * kn[ks][0] + bf16hi(qf[ks][nt]) * kn[ks][1]
+                             + bf16lo(qf[ks][2 + nt]) * kn[ks][2] + bf16hi(qf[ks][2 + nt]) * kn[ks][3];
+                sn2[nt] += __shfl_xor_sync(0xffffffffu, sn2[nt], 1);
+                sn2[nt] += __shfl_xor_sync(0xffffffffu, sn2[nt], 2);
             }
-            float pn[2], al[2];
+            float pn[NT][2], al[NT][2];
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                sn2[r] += __shfl_xor_sync(0xffffffffu, sn2[r], 1);
-                sn2[r] += __shfl_xor_sync(0xffffffffu, sn2[r], 2);
-                const float m_new = fmaxf(m_run[r], sn2[r]);
-                al[r] = exp2f(m_run[r] - m_new);                 // exp2(-inf) = 0 when nothing came before
-                pn[r] = exp2f(sn2[r] - m_new);
-                l_run[r] = l_run[r] * al[r] + (t == 0 ? pn[r] : 0.f);   // l is shared out over the quad: count once
-                m_run[r] = m_new;
-            }
+            for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int j = 0; j < HD / 8; ++j) {
-                const uint32_t vw = *reinterpret_cast<const uint32_t*>(v_src + (8 * j + 2 * t) * 2);
-                if (g == 0) *reinterpret_cast<uint32_t*>(v_cache + row + 8 * j + 2 * t) = vw;
-                const float v0 = bf16lo(vw), v1 = bf16hi(vw);
-                o[j][0] = fmaf(pn[0], v0, o[j][0] * al[0]); o[j][1] = fmaf(pn[0], v1, o[j][1] * al[0]);
-                o[j][2] = fmaf(pn[1], v0, o[j][2] * al[1]); o[j][3] = fmaf(pn[1], v1, o[j][3] * al[1]);
+                for (int c = 0; c < 2; ++c) {
+                    const float sc_new = __shfl_sync(0xffffffffu, sn2[nt], (2 * t + c) * 4);
+                    const float m_new = fmaxf(m_run[nt][c], sc_new);
+                    al[nt][c] = exp2f(m_run[nt][c] - m_new);     // exp2(-inf) = 0 when nothing came before
+                    pn[nt][c] = exp2f(sc_new - m_new);
+                    l_run[nt][c] = l_run[nt][c] * al[nt][c] + (g == 0 ? pn[nt][c] : 0.f);   // l is shared out over the keys' lanes: count once
+                    m_run[nt][c] = m_new;
+                }
+#pragma unroll
+            for (int j = 0; j < HD / 16; ++j) {
+                const float v0 = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(v_src)[16 * j + g]);
+                const float v1 = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(v_src)[16 * j + g + 8]);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    ot[j][nt][0] = fmaf(pn[nt][0], v0, ot[j][nt][0] * al[nt][0]); ot[j][nt][1] = fmaf(pn[nt][1], v0, ot[j][nt][1] * al[nt][1]);
+                    ot[j][nt][2] = fmaf(pn[nt][0], v1, ot[j][nt][2] * al[nt][0]); ot[j][nt][3] = fmaf(pn[nt][1], v1, ot[j][nt][3] * al[nt][1]);
+                }
             }
         }
 
         // merge the 4 warps (each saw different keys) in warp order
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-            if (t == 0) { sm_m[warp][g + 8 * r] = m_run[r]; sm_l[warp][g + 8 * r] = l_run[r]; }
-        }
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int j = 0; j < HD / 8; ++j) {
-            float* d0 = sm_acc + ((size_t)warp * group + g) * ACC_LD + 8 * j + 2 * t;
-            float* d1 = sm_acc + ((size_t)warp * group + g + 8) * ACC_LD + 8 * j + 2 * t;
-            if (g < group) *reinterpret_cast<float2*>(d0) = make_float2(o[j][0], o[j][1]);
-            if (g + 8 < group) *reinterpret_cast<float2*>(d1) = make_float2(o[j][2], o[j][3]);
-        }
+            for (int c = 0; c < 2; ++c) {
+                float l = l_run[nt][c];
+                l += __shfl_xor_sync(0xffffffffu, l, 4);
+                l += __shfl_xor_sync(0xffffffffu, l, 8);
+                l += __shfl_xor_sync(0xffffffffu, l, 16);
+                const int head = 8 * nt + 2 * t + c;
+                if (g == 0 && head < ADM_ROWS) { sm_m[warp][head] = m_run[nt][c]; sm_l[warp][head] = l; }
+            }
+#pragma unroll
+        for (int j = 0; j < HD / 16; ++j)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int head = 8 * nt + 2 * t + (e & 1), dim = 16 * j + g + 8 * (e >> 1);
+                    if (head < group) sm_acc[((size_t)warp * group + head) * ACC_LD + dim] = ot[j][nt][e];
+                }
         __syncthreads();
         const int n_chunks = cur.n_chunks;
         for (int e = threadIdx.x; e < group * (HD / 4); e += ADM_THREADS) {
@@ -754,20 +807,20 @@ static inline int adm_sm_count() {
 // Blocks of the kernel that are resident at once on the current device (what the persistent grid is
 // sized to): as many per SM as registers and shared memory allow, asked of the runtime once per case.
 // The kernel's limit on dynamic shared memory only ever grows (a launch needs at most what was set).
-template <int HD, bool FUSE, bool CL = false>
+template <int HD, bool FUSE, bool CL, int NT>
 static inline cudaError_t adm_ensure_smem(int smem_bytes) {
     static int allowed = 0;
     if (smem_bytes <= allowed) return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, FUSE, CL>,
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, FUSE, CL, NT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e == cudaSuccess) allowed = smem_bytes;
     return e;
 }
 
-template <int HD, bool FUSE>
+template <int HD, bool FUSE, int NT>
 static inline int adm_blocks_per_sm(int smem_bytes) {
-    auto kern = attention_decode_mma_kernel<HD, FUSE, false>;
-    if (adm_ensure_smem<HD, FUSE>(smem_bytes) != cudaSuccess) return 0;
+    auto kern = attention_decode_mma_kernel<HD, FUSE, false, NT>;
+    if (adm_ensure_smem<HD, FUSE, false, NT>(smem_bytes) != cudaSuccess) return 0;
     int n = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, ADM_THREADS, (size_t)smem_bytes) != cudaSuccess) return 0;
     return n;
@@ -781,8 +834,12 @@ static inline long long adm_resident_blocks(int head_dim, bool fuse, int group, 
     int& per_sm = cached[head_dim == 128][fuse ? 1 : 0][group][cls];
     if (per_sm == 0) {
         const int smem = adm_smem_bytes(head_dim, group, cls_seqs);
-        per_sm = head_dim == 64 ? (fuse ? adm_blocks_per_sm<64, true>(smem) : adm_blocks_per_sm<64, false>(smem))
-                                : (fuse ? adm_blocks_per_sm<128, true>(smem) : adm_blocks_per_sm<128, false>(smem));
+        if (group <= 8)
+            per_sm = head_dim == 64 ? (fuse ? adm_blocks_per_sm<64, true, 1>(smem) : adm_blocks_per_sm<64, false, 1>(smem))
+                                    : (fuse ? adm_blocks_per_sm<128, true, 1>(smem) : adm_blocks_per_sm<128, false, 1>(smem));
+        else
+            per_sm = head_dim == 64 ? (fuse ? adm_blocks_per_sm<64, true, 2>(smem) : adm_blocks_per_sm<64, false, 2>(smem))
+                                    : (fuse ? adm_blocks_per_sm<128, true, 2>(smem) : adm_blocks_per_sm<128, false, 2>(smem));
         if (per_sm <= 0) per_sm = -1;
     }
     return per_sm > 0 ? (long long)per_sm * adm_sm_count() : 0;
@@ -866,26 +923,28 @@ static inline int adm_launch(const void* q, int ldq, const void* k_cache, const 
     int rc = adm_cache_map(k_cache, cache_rows, head_dim, &map_k);
     if (!rc) rc = adm_cache_map(v_cache, cache_rows, head_dim, &map_v);
     if (rc) return rc;
-#define SSB_ADM(HD_, FUSE_) do { \
+#define SSB_ADM(HD_, FUSE_, NT_) do { \
         const int smem_bytes = adm_smem_bytes(HD_, n_q / n_kv, n_seqs); \
-        cudaError_t e = adm_ensure_smem<HD_, FUSE_>(smem_bytes); \
+        cudaError_t e = adm_ensure_smem<HD_, FUSE_, false, NT_>(smem_bytes); \
         if (e != cudaSuccess) return (int)e; \
         if (cluster) { \
-            e = adm_ensure_smem<HD_, FUSE_, true>(smem_bytes); \
+            e = adm_ensure_smem<HD_, FUSE_, true, NT_>(smem_bytes); \
             if (e != cudaSuccess) return (int)e; \
-            rc = adm_launch_cluster(attention_decode_mma_kernel<HD_, FUSE_, true>, grid, cluster, (size_t)smem_bytes, stream, pdl, \
+            rc = adm_launch_cluster(attention_decode_mma_kernel<HD_, FUSE_, true, NT_>, grid, cluster, (size_t)smem_bytes, stream, pdl, \
                             (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
                             (bf16*)out, ldo, n_seqs, n_q, n_kv, window, scale_log2, 1, cluster, scratch, \
                             counters, cos_t, sin_t, map_k, map_v, error_word); \
         } else \
-        rc = ssb_launch(attention_decode_mma_kernel<HD_, FUSE_, false>, grid, dim3(ADM_THREADS), (size_t)smem_bytes, stream, pdl, \
+        rc = ssb_launch(attention_decode_mma_kernel<HD_, FUSE_, false, NT_>, grid, dim3(ADM_THREADS), (size_t)smem_bytes, stream, pdl, \
                         (const bf16*)q, ldq, (bf16*)k_cache, (bf16*)v_cache, pos, slot, page_table, max_pages, \
                         (bf16*)out, ldo, n_seqs, n_q, n_kv, window, scale_log2, chunk_pages, max_chunks, scratch, \
                         counters, cos_t, sin_t, map_k, map_v, error_word); \
     } while (0)
-    if (head_dim == 64) { if (fuse) SSB_ADM(64, true); else SSB_ADM(64, false); }
-    else if (head_dim == 128) { if (fuse) SSB_ADM(128, true); else SSB_ADM(128, false); }
+#define SSB_ADM_NT(HD_, FUSE_) do { if (n_q / n_kv <= 8) SSB_ADM(HD_, FUSE_, 1); else SSB_ADM(HD_, FUSE_, 2); } while (0)
+    if (head_dim == 64) { if (fuse) SSB_ADM_NT(64, true); else SSB_ADM_NT(64, false); }
+    else if (head_dim == 128) { if (fuse) SSB_ADM_NT(128, true); else SSB_ADM_NT(128, false); }
     else return SSB_ERR_UNSUPPORTED;
+#undef SSB_ADM_NT
 #undef SSB_ADM
     return rc ? rc : ssb_launch_status();
 }

@@ -351,7 +351,7 @@ def _decode_attention(kind, q, k, v, pos, slot, table, out, n_q, n_kv, hd, windo
 
 @pytest.mark.parametrize("n_q,n_kv,hd,window", [(4, 2, 16, None), (3, 1, 48, None), (32, 8, 128, None),
                                                 (6, 2, 128, 100), (2, 2, 256, None), (8, 1, 64, 64),
-                                                (5, 5, 80, None)])
+                                                (5, 5, 80, None), (12, 1, 128, None), (32, 2, 64, 150)])
 @pytest.mark.parametrize("n_splits", [1, 3, 8])
 @pytest.mark.parametrize("kind", [1, 2, 3])
 def test_attention_decode(n_q, n_kv, hd, window, n_splits, kind):
@@ -632,7 +632,8 @@ def test_attention_prefill_finds_a_far_key(impl):
 
 
 @pytest.mark.parametrize("n_q,n_kv,hd,window", [(32, 8, 128, None), (4, 2, 64, None), (6, 2, 128, 100),
-                                                (2, 1, 32, None), (8, 8, 256, None)])
+                                                (2, 1, 32, None), (8, 8, 256, None), (10, 1, 128, None),
+                                                (32, 2, 64, 90)])
 @pytest.mark.parametrize("n_splits", [1, 4, 8])
 @pytest.mark.parametrize("kind", [1, 2, 3])
 def test_attention_decode_with_rotation_and_append_inside(n_q, n_kv, hd, window, n_splits, kind):
