@@ -845,6 +845,45 @@ static inline long long adm_resident_blocks(int head_dim, bool fuse, int group, 
     return per_sm > 0 ? (long long)per_sm * adm_sm_count() : 0;
 }
 
+// Clusters of ``cluster`` blocks of the kernel that the device holds at once (0 if it cannot place one):
+// what the runtime says for the kernel's registers and shared memory, asked once per case.
+template <int HD, bool FUSE, int NT>
+static inline int adm_max_clusters_of(int cluster, int smem_bytes) {
+    auto kern = attention_decode_mma_kernel<HD, FUSE, true, NT>;
+    if (adm_ensure_smem<HD, FUSE, true, NT>(smem_bytes) != cudaSuccess) return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(cluster * 64));
+    cfg.blockDim = dim3(ADM_THREADS);
+    cfg.dynamicSmemBytes = (size_t)smem_bytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
+static inline int adm_max_clusters(int head_dim, bool fuse, int group, int cluster) {
+    static int cached[2][2][2][4];                               // [head size][fuse][tiles of heads][cluster 2/4/8]
+    if (group < 1 || group > ADM_ROWS || (head_dim != 64 && head_dim != 128)) return 0;
+    const int ci = cluster == 2 ? 1 : (cluster == 4 ? 2 : (cluster == 8 ? 3 : 0));
+    if (!ci) return 0;
+    int& n = cached[head_dim == 128][fuse ? 1 : 0][group > 8][ci];
+    if (n == 0) {
+        const int smem = adm_smem_bytes(head_dim, group, 64);
+        if (group <= 8)
+            n = head_dim == 64 ? (fuse ? adm_max_clusters_of<64, true, 1>(cluster, smem) : adm_max_clusters_of<64, false, 1>(cluster, smem))
+                               : (fuse ? adm_max_clusters_of<128, true, 1>(cluster, smem) : adm_max_clusters_of<128, false, 1>(cluster, smem));
+        else
+            n = head_dim == 64 ? (fuse ? adm_max_clusters_of<64, true, 2>(cluster, smem) : adm_max_clusters_of<64, false, 2>(cluster, smem))
+                               : (fuse ? adm_max_clusters_of<128, true, 2>(cluster, smem) : adm_max_clusters_of<128, false, 2>(cluster, smem));
+        if (n <= 0) n = -1;
+    }
+    return n > 0 ? n : 0;
+}
+
 // The tensor map of a cache (keys or values): cache_rows x head_dim bfloat16, boxes of one page's 64
 // keys x 64 dims.  Encoding one costs the host a microsecond or two, so the maps of the caches seen
 // so far are kept (a map depends on the address and the sizes alone).
@@ -916,7 +955,8 @@ static inline int adm_launch(const void* q, int ldq, const void* k_cache, const 
     dim3 grid((unsigned)(items < resident ? items : resident));
     if (cluster) {
         const long long blocks = (long long)n_seqs * n_kv * cluster;
-        if (blocks > resident) return SSB_ERR_BAD_SIZE;          // the clusters' blocks are meant to run all at once
+        // the clusters' blocks are meant to run all at once
+        if (blocks > resident || (long long)n_seqs * n_kv > adm_max_clusters(head_dim, fuse, n_q / n_kv, cluster)) return SSB_ERR_BAD_SIZE;
         grid = dim3((unsigned)blocks);
     }
     CUtensorMap map_k, map_v;

@@ -247,6 +247,13 @@ SSB_API long long ssb_attention_decode_chunked_blocks(int n_seqs, int n_q, int n
     return adm_resident_blocks(head_dim, fused != 0, n_q / n_kv, n_seqs);
 }
 
+// Clusters of ``cluster`` (2, 4, 8) blocks of the kernel that the device holds at once for this case: a
+// caller that wants a sequence's chunks as a cluster needs sequences x kv heads of them.
+SSB_API int ssb_attention_decode_chunked_clusters(int n_q, int n_kv, int head_dim, int fused, int cluster) {
+    if (n_kv <= 0 || n_q % n_kv) return 0;
+    return adm_max_clusters(head_dim, fused != 0, n_q / n_kv, cluster);
+}
+
 SSB_API long long ssb_attention_decode_chunked_scratch_floats(int n_seqs, int n_q, int head_dim, int max_chunks) {
     return adm_scratch_floats(n_seqs, n_q, head_dim, max_chunks);
 }

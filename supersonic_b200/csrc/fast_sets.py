@@ -222,6 +222,8 @@ class FastKernels(PlainKernels):
             blocks = ops.attention_decode_chunked_blocks(batch.n_seqs, n_q, n_kv, head_dim, cos is not None)
             chunk, max_chunks = self._chunks(n_kv, pages, blocks)
             cluster = self._cluster(batch.n_seqs * n_kv, pages, blocks)
+            if cluster and batch.n_seqs * n_kv > ops.attention_decode_chunked_clusters(n_q, n_kv, head_dim, cos is not None, cluster):
+                cluster = 0                              # the device cannot hold that many clusters of this kernel at once
             scratch = counters = None
             if max_chunks > 1 and not cluster:
                 nf, nc = ops.attention_decode_chunked_scratch(batch.n_seqs, n_q, n_kv, head_dim, max_chunks)

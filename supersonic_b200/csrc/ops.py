@@ -351,6 +351,19 @@ def attention_decode_chunked_blocks(n_seqs: int, n_q: int, n_kv: int, head_dim: 
     return _chunked_blocks[key]
 
 
+_chunked_clusters = {}
+
+
+def attention_decode_chunked_clusters(n_q: int, n_kv: int, head_dim: int, fused: bool, cluster: int) -> int:
+    """Thread-block clusters of ``cluster`` (2, 4 or 8) blocks of the tensor-core decode attention that the
+    current device holds at once (0: it cannot place one)."""
+    key = (torch.cuda.current_device(), n_q, n_kv, head_dim, bool(fused), cluster)
+    if key not in _chunked_clusters:
+        _chunked_clusters[key] = int(_fn("decode_ops", "ssb_attention_decode_chunked_clusters")(
+            c_int(n_q), c_int(n_kv), c_int(head_dim), c_int(1 if fused else 0), c_int(cluster)))
+    return _chunked_clusters[key]
+
+
 def attention_decode_chunked_scratch(n_seqs: int, n_q: int, n_kv: int, head_dim: int, max_chunks: int):
     """(float32 elements of scratch, int32 counters) a launch needs; counters start at zero."""
     lib = load_library("decode_ops")

@@ -324,7 +324,8 @@ def _decode_attention(kind, q, k, v, pos, slot, table, out, n_q, n_kv, hd, windo
     cluster = 0
     if kind == 3:
         cluster = 2 if n_splits <= 2 else (4 if n_splits <= 4 else 8)
-        while B * n_kv * cluster > ops().attention_decode_chunked_blocks(B, n_q, n_kv, hd, cos is not None):
+        while cluster >= 2 and (B * n_kv * cluster > ops().attention_decode_chunked_blocks(B, n_q, n_kv, hd, cos is not None)
+                                or B * n_kv > ops().attention_decode_chunked_clusters(n_q, n_kv, hd, cos is not None, cluster)):
             cluster //= 2                                                # the clusters' blocks must all fit the device at once
         if cluster < 2:
             pytest.skip("too many (sequence, kv head) pairs for clusters")
