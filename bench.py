@@ -231,7 +231,10 @@ def time_prefill(model, tokens, reps=5, warmup=3, seed=1, seqs=1):
 def sweep(model, pk, steps, warmup):
     """Decode at further batch sizes and context lengths, prompts of further sizes: the table of README.md."""
     out = {"decode": [], "prefill": []}
-    for batch, ctx in ((1, 512), (1, 8000), (8, 512), (8, 8000), (32, 512), (64, 512), (64, 4096)):
+    sizes = [(1, 512), (1, 8000), (8, 512), (8, 8000), (32, 512), (64, 512), (64, 4096)]
+    if model.cache.max_seq_tokens >= 131072:               # --context 131072 --slots 4: the position limit too
+        sizes.insert(2, (1, 131000))
+    for batch, ctx in sizes:
         ms, _, nbytes = time_decode(model, batch, ctx, min(steps, 48), warmup, seed=20 + batch)
         out["decode"].append({"batch": batch, "context": ctx, "ms_per_step": round(ms, 3),
                               "tokens_s": round(batch * 1000.0 / ms, 1),
