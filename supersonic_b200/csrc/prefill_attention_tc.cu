@@ -10,10 +10,12 @@
 // they lie in the cache.  Warps 2-5 and 6-9 own one query row of the first and second tile per
 // thread: scores come with tcgen05.ld, are masked
 // on the diagonal only, and leave as bfloat16 probabilities with tcgen05.st.  O stays in tensor
-// memory for the whole row of blocks: a row's reference maximum moves only when the true maximum
-// has grown by more than 2^8, and only then is O rescaled (tcgen05.ld, multiply, tcgen05.st); the
-// sum uses the same reference, so the quotient is the exact softmax.  While one tile's rows are in
-// the softmax the tensor cores work on the other tile.  Every mbarrier wait is bounded.
+// memory for the whole row of blocks: a row's reference maximum is set by its first block and moves
+// only when a later block's probabilities against it sum to more than 2^8 (no probability is ever
+// larger than that), and only then is the block's maximum looked for and O rescaled (tcgen05.ld,
+// multiply, tcgen05.st); the sum uses the same reference, so the quotient is the exact softmax.
+// While one tile's rows are in the softmax the tensor cores work on the other tile.  Every mbarrier
+// wait is bounded.
 //
 // Same arithmetic as prefill_attention.cu (mma.sync), which stays as the kernel for short prompts
 // and as this one's reference.  Replaces supersonic_qwen35_full_attention_prefill_kernel of the
@@ -29,6 +31,7 @@ constexpr int FT_BN = 128;                 // keys per turn = two cache pages
 constexpr int FT_STAGES = 2;
 constexpr int FT_THREADS = 320;
 constexpr float FT_LAZY = 8.f;             // log2 of how far a probability may exceed 1
+constexpr float FT_LAZY_P = 256.f;         // 2^FT_LAZY
 // tensor-memory columns of tile x: scores, later probabilities, at 128 x; output at 256 + 128 x
 constexpr uint32_t FT_S0 = 0, FT_O0 = 256;
 constexpr int FT_NBARS = 1 + 3 * FT_STAGES + 6;
@@ -288,53 +291,70 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     for (int i = 0; i < FT_BN; ++i)
                         if (i > hi || i < lo) raw[i] = 0xff800000u;
                 }
-                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                // probabilities 2^(score * scale - reference) of the row's 128 scores, as bfloat16 over the scores
+                // in tensor memory (those of 64 keys go over the scores of 32 keys; all scores are in
+                // registers); returns their sum
+                auto probabilities = [&](float neg_ref) -> float {
+                    float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int i = 0; i < FT_BN; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(raw[i]));
-                const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
-                const float m_new = fmaxf(m_ref, m_blk);
-                if (j == 0) {
-                    m_ref = m_new;
-                } else if (__any_sync(0xffffffffu, m_new > m_ref + FT_LAZY)) {
-                    // the maximum has grown too far for this warp's rows: rescale what is summed so far
-                    bool wo = mbar_wait(o_full, (j - 1) & 1, abort_flag);
-                    wo = __all_sync(0xffffffffu, wo);
-                    if (!wo) { ok = false; break; }
-                    tc_fence_after();
-                    const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m_ref - m_new);
-#pragma unroll 1
-                    for (int c = 0; c < FT_HD / 32; ++c) {
-                        uint32_t o[32];
-                        tc_ld32_issue(t_o + c * 32, o);
-                        tc_ld_wait();
+                    for (int half = 0; half < 2; ++half) {
+                        uint32_t packed[32];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tc_st32(t_o + c * 32, o);
+                        for (int i = 0; i < 64; i += 2) {
+                            const float pa = ex2(fmaf(__uint_as_float(raw[half * 64 + i]), scale_log2, neg_ref));
+                            const float pb = ex2(fmaf(__uint_as_float(raw[half * 64 + i + 1]), scale_log2, neg_ref));
+                            sum[(i >> 1) & 3] += pa + pb;
+                            __nv_bfloat162 v = __floats2bfloat162_rn(pa, pb);
+                            packed[i / 2] = *reinterpret_cast<uint32_t*>(&v);
+                        }
+                        tc_st32(t_s + half * 32, packed);
                     }
-                    l_run *= alpha;
-                    m_ref = m_new;
+                    return (sum[0] + sum[1]) + (sum[2] + sum[3]);
+                };
+                // After a row's first block the probabilities are taken against the reference as it stands,
+                // without looking for the block's maximum first (a third of a block's softmax time, which
+                // is the one step of a tile that its own products cannot overlap): a probability above
+                // 2^FT_LAZY makes the row's sum exceed 2^FT_LAZY too, and only then (or while a row has
+                // seen no key yet) is the maximum found, the output rescaled and the block done again.
+                float sum = 0.f;
+                bool find_max = j == 0;
+                if (!find_max) {
+                    sum = probabilities(m_ref == -INFINITY ? 0.f : -m_ref);
+                    find_max = __any_sync(0xffffffffu, !(sum <= FT_LAZY_P) || m_ref == -INFINITY);
                 }
-                // exponentials; the probabilities of 64 keys go over the scores of 32 keys (all are in registers)
-                const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-                float sum[4] = {0.f, 0.f, 0.f, 0.f};
+                if (find_max) {
+                    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t packed[32];
+                    for (int i = 0; i < FT_BN; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(raw[i]));
+                    const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
+                    const float m_new = fmaxf(m_ref, m_blk);
+                    if (j > 0 && __any_sync(0xffffffffu, m_new > m_ref)) {
+                        // rescale what this warp's rows have summed so far to their new maxima
+                        bool wo = mbar_wait(o_full, (j - 1) & 1, abort_flag);
+                        wo = __all_sync(0xffffffffu, wo);
+                        if (!wo) { ok = false; break; }
+                        tc_fence_after();
+                        const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m_ref - m_new);
+#pragma unroll 1
+                        for (int c = 0; c < FT_HD / 32; ++c) {
+                            uint32_t o[32];
+                            tc_ld32_issue(t_o + c * 32, o);
+                            tc_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 64; i += 2) {
-                        const float pa = ex2(fmaf(__uint_as_float(raw[half * 64 + i]), scale_log2, neg_m));
-                        const float pb = ex2(fmaf(__uint_as_float(raw[half * 64 + i + 1]), scale_log2, neg_m));
-                        sum[(i >> 1) & 3] += pa + pb;
-                        __nv_bfloat162 v = __floats2bfloat162_rn(pa, pb);
-                        packed[i / 2] = *reinterpret_cast<uint32_t*>(&v);
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tc_st32(t_o + c * 32, o);
+                        }
+                        l_run *= alpha;
                     }
-                    tc_st32(t_s + half * 32, packed);
+                    m_ref = m_new;
+                    tc_st_wait();                                // what was written against the old reference has landed
+                    sum = probabilities(m_ref == -INFINITY ? 0.f : -m_ref);
                 }
                 tc_st_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cta(p_full);
-                l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+                l_run += sum;
             }
             if (ok) {
                 bool w = mbar_wait(o_full, (n_mine - 1) & 1, abort_flag);
