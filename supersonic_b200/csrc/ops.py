@@ -704,9 +704,11 @@ GEMV_TC_MAX_ROWS = 128     # rows of x that gemv_tc takes (the N side of its MMA
 
 def gemv_tc_splits(n: int, k: int) -> int:
     """Blocks that share the K range of one 128-row tile of W: up to two blocks per SM in all
-    (every SM must pull for the memory system to be busy), at least 8 k-blocks (512 columns) each."""
+    (every SM must pull for the memory system to be busy), at least 4 k-blocks (256 columns) each and
+    at most 16 (measured on decode steps of 1B, 3B and 8B sizes: with 8 and 8 the small projections
+    of a narrow model filled a third of the SMs, and its steps took 5 to 7 % longer)."""
     tiles = (n + 127) // 128
-    return max(1, min(2 * sm_count() // tiles, (k // 64) // 8, 8))
+    return max(1, min(2 * sm_count() // tiles, (k // 64) // 4, 16))
 
 
 def gemv_tc_scratch(rows: int, n: int, splits: int):
