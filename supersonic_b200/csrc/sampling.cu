@@ -1,5 +1,6 @@
 // Sampling kernels: argmax, and temperature / top-k / top-p sampling of rows of float32 logits
-// (one block per row; the sampling rule also on a cluster of 8 blocks per row, which is the one used).
+// (one block per row; the sampling rule also on a cluster of 8 blocks per row, which is the one used: the row
+// held in the cluster's shared memory when a cut has to be searched for, read in place when not).
 //
 // Rules follow the reference's samplers:
 //   greedy      strict '>' so the lowest index wins ties
@@ -454,11 +455,178 @@ sample_cluster_kernel(const float* __restrict__ logits, long long ld, int vocab,
     sc_cluster_sync();                                   // no block leaves while its shared memory may be read
 }
 
+// ---- temperature alone: the row is read, not held --------------------------------------------
+// Without a top-k or top-p cut nothing is searched for, so nothing needs the row in shared memory:
+// two passes over the slice (maximum; sums of exponentials), two meetings of the cluster, and the
+// one warp whose stretch of the running sum holds r = u * total looks at its 128 logits again.
+// With no slice to hold, all 8 blocks of every row of a batch of 64 are resident at once (with
+// 64 KB slices three blocks share an SM and 512 blocks come in two waves: 101 us; this form 23 us;
+// one row: 26 and 12 us).
+// The running sum goes in index order: a block takes its slice in stretches of 2,048 logits,
+// a warp 128 of them, a lane 4; sums meet in that order (stretches through a scan over their sums).
+constexpr int ST_EL = 4;                                 // logits in a row per lane
+constexpr int ST_TILE = SC_THREADS * ST_EL;              // a stretch
+constexpr int ST_MAX_IT = 32;                            // stretches per slice: one per lane of the warp that scans them
+constexpr int ST_WARPS = SC_THREADS / 32;
+
+__global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS)
+sample_stream_kernel(const float* __restrict__ logits, long long ld, int vocab, float inv_temperature,
+                     const int* __restrict__ slots, unsigned long long* __restrict__ rng_state,
+                     int* __restrict__ out, float* __restrict__ drawn_u) {
+    __shared__ ScShared sh;                              // chunk_sum holds [stretch][warp] here
+    __shared__ float it_before[ST_MAX_IT];               // sum of the stretches before a stretch
+    __shared__ float it_sum[ST_MAX_IT];
+    __shared__ int sel_it, sel_warp;
+    __shared__ float sel_before;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, row_id = blockIdx.y;
+    const unsigned rank = sc_rank();
+    const float* row = logits + (size_t)row_id * ld;
+    const int per_cta = (vocab + SC_CTAS - 1) / SC_CTAS;
+    const int lo_i = min((int)rank * per_cta, vocab), hi_i = min(lo_i + per_cta, vocab), n = hi_i - lo_i;
+    const int n_it = (n + ST_TILE - 1) / ST_TILE;
+    int turn = 0;
+    if (tid == 0) sh.found = 0x7fffffff;
+
+    const int seq = slots ? slots[row_id] : row_id;
+    unsigned long long state = rng_state[seq];
+    state ^= state << 13; state ^= state >> 7; state ^= state << 17;
+    const float u = (float)(state >> 40) / 16777216.0f;
+
+    float mx = -INFINITY;
+    for (int it = 0; it < n_it; ++it) {
+        const int i0 = (it * SC_THREADS + tid) * ST_EL;
+#pragma unroll
+        for (int e = 0; e < ST_EL; ++e)
+            if (i0 + e < n) mx = fmaxf(mx, row[lo_i + i0 + e] * inv_temperature);
+    }
+    mx = sc_all<true>(mx, sh, turn);
+    if (rank == 0 && tid == 0) { rng_state[seq] = state; if (drawn_u) drawn_u[row_id] = u; }
+
+    // exponentials of lane's 4 logits of a stretch (0 beyond the slice)
+    auto weights = [&](int it, float (&w)[ST_EL]) {
+        const int i0 = (it * SC_THREADS + tid) * ST_EL;
+#pragma unroll
+        for (int e = 0; e < ST_EL; ++e) w[e] = (i0 + e < n) ? expf(row[lo_i + i0 + e] * inv_temperature - mx) : 0.f;
+    };
+    for (int it = 0; it < n_it; ++it) {
+        float w[ST_EL];
+        weights(it, w);
+        float v = (w[0] + w[1]) + (w[2] + w[3]);
+        // lanes in order: an inclusive scan, whose last lane holds the warp's sum as the draw will walk it
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, v, o);
+            if (lane >= o) v += t;
+        }
+        if (lane == 31) sh.chunk_sum[it * ST_WARPS + warp] = v;
+    }
+    __syncthreads();
+    float slice_sum = 0.f;
+    if (warp == 0) {
+        // lane = stretch: its warps in order, then the stretches by an inclusive scan
+        float v = 0.f;
+        if (lane < n_it)
+            for (int w = 0; w < ST_WARPS; ++w) v += sh.chunk_sum[lane * ST_WARPS + w];
+        float incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        it_before[lane] = incl - v;
+        it_sum[lane] = v;
+        slice_sum = __shfl_sync(0xffffffffu, incl, 31);
+        if (lane == 0) sh.pub[turn][0] = slice_sum;
+    }
+    sc_cluster_sync();
+    float base = 0.f, kept = 0.f;
+    for (unsigned c = 0; c < SC_CTAS; ++c) {
+        if (c == rank) base = kept;
+        kept += sc_remote_f32(&sh.pub[turn][0], c);
+    }
+    const float mine = sc_remote_f32(&sh.pub[turn][0], rank);
+    turn ^= 1;
+    if (!(kept > 0.f) || isinf(kept) || isnan(kept)) {                       // degenerate row: greedy, lowest index
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int it = 0; it < n_it; ++it) {
+            const int i0 = (it * SC_THREADS + tid) * ST_EL;
+            for (int e = 0; e < ST_EL; ++e)
+                if (i0 + e < n) { const float x = row[lo_i + i0 + e] * inv_temperature; if (x > bv) { bv = x; bi = lo_i + i0 + e; } }
+        }
+        const float gm = sc_all<true>(bv, sh, turn);
+        if (bv == gm && bi != 0x7fffffff) atomicMin(&sh.found, bi);
+    } else {
+        const float r = u * kept;
+        const bool owner = mine > 0.f && base <= r && r <= base + mine;      // the slices tile [0, kept]
+        if (owner && warp == 0) {
+            // the last stretch with any weight that starts at or before r, then the last such warp of it
+            // (the first stretch with weight starts at base, which is not above r: there is one)
+            const unsigned at = __ballot_sync(0xffffffffu, lane < n_it && it_sum[lane] > 0.f && base + it_before[lane] <= r);
+            const int it = at ? 31 - __clz(at) : 0;
+            float before = base + it_before[it];
+            float run = before;
+            for (int w = 0; w < lane && w < ST_WARPS; ++w) run += sh.chunk_sum[it * ST_WARPS + w];
+            const unsigned aw = __ballot_sync(0xffffffffu, lane < ST_WARPS && sh.chunk_sum[it * ST_WARPS + min(lane, ST_WARPS - 1)] > 0.f && run <= r);
+            const int w_sel = aw ? 31 - __clz(aw) : 0;
+            before = __shfl_sync(0xffffffffu, run, w_sel);
+            if (lane == 0) { sel_it = it; sel_warp = w_sel; sel_before = before; }
+        }
+        __syncthreads();
+        if (owner && warp == sel_warp) {
+            float w[ST_EL];
+            weights(sel_it, w);
+            const float v = (w[0] + w[1]) + (w[2] + w[3]);
+            float incl = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            const float start = sel_before + (incl - v);
+            const int i0 = (sel_it * SC_THREADS + tid) * ST_EL;
+            const unsigned al = __ballot_sync(0xffffffffu, v > 0.f && start <= r);
+            if (al && lane == 31 - __clz(al)) {
+                float cum = start;
+                int last = -1, hit = -1;
+#pragma unroll
+                for (int e = 0; e < ST_EL; ++e)
+                    if (hit < 0 && w[e] > 0.f) {
+                        last = i0 + e;
+                        cum += w[e];
+                        if (cum >= r) hit = i0 + e;
+                    }
+                if (hit < 0) hit = last;                 // rounding left r a hair above this lane's sum
+                if (hit >= 0) atomicMin(&sh.found, lo_i + hit);
+            }
+        }
+    }
+    sc_cluster_sync();
+    if (rank == 0 && tid == 0) {
+        int best = 0x7fffffff;
+        for (unsigned c = 0; c < SC_CTAS; ++c) {
+            unsigned addr = (unsigned)__cvta_generic_to_shared(&sh.found), remote;
+            int v;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(c));
+            asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+            best = min(best, v);
+        }
+        out[row_id] = (best == 0x7fffffff) ? 0 : best;
+    }
+    sc_cluster_sync();                                   // no block leaves while its shared memory may be read
+}
+
 SSB_API int ssb_sample(const float* logits, long long ld, int n_rows, int vocab, float temperature,
                        int top_k, float top_p, const int* slots, unsigned long long* rng_state, int* out,
                        float* drawn_u, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (vocab <= 0 || vocab >= 0x40000000 || !(temperature > 0.f)) return SSB_ERR_BAD_SIZE;
+    // temperature alone: nothing to search, the row stays where it is
+    if ((top_k <= 0 || top_k >= vocab) && !(top_p < 1.0f) && n_rows <= 65535 &&
+        (vocab + SC_CTAS - 1) / SC_CTAS <= ST_MAX_IT * ST_TILE) {
+        sample_stream_kernel<<<dim3(SC_CTAS, n_rows), SC_THREADS, 0, stream>>>(
+            logits, ld, vocab, 1.0f / temperature, slots, rng_state, out, drawn_u);
+        return ssb_launch_status();
+    }
     // a cluster of 8 blocks per row where the row's slices fit shared memory (vocabularies up to 400k)
     const size_t slice = (size_t)((vocab + SC_CTAS - 1) / SC_CTAS) * sizeof(float);
     if (slice <= 200 * 1024 && n_rows <= 65535) {

@@ -243,6 +243,42 @@ def test_sample_follows_the_reference_rule(temperature, top_k, top_p):
     assert torch.equal(out2, out[:3])
 
 
+@pytest.mark.parametrize("vocab,temperature", [(128256, 1.0), (50021, 0.3), (2049, 1.7)])
+def test_sample_by_temperature_alone_reads_the_row_in_stretches(vocab, temperature):
+    """Without a cut the row is not held but read twice, in stretches of 2,048 logits per block of the
+    cluster; rows here have their weight in a few far-apart places, whole stretches without any
+    (minus infinity), or none at all."""
+    import numpy as np
+    import plain_llama as pl
+    n = 40
+    g = torch.Generator(device=DEV).manual_seed(vocab)
+    lg = 2 * torch.randn(n, vocab, device=DEV, generator=g)
+    lg[0, :] = -float("inf")                                            # nothing to draw from: token 0
+    lg[1, : vocab // 2] = -float("inf")                                 # the first blocks of the cluster hold nothing
+    lg[2, vocab // 3:] = -float("inf")
+    lg[3, 5] = lg[3, vocab - 1] = 40.0                                  # two tokens share all the weight, at both ends
+    lg[4, vocab // 2 + 1] = 60.0
+    lg[5, :] = -float("inf"); lg[5, vocab - 3] = 1.0
+    lg[6, 2048:] = -float("inf"); lg[6, :2040] = -float("inf")          # eight tokens at the end of the first stretch
+    seeds = [0x9E3779B97F4A7C15 * (i + 3) % (1 << 63) for i in range(n)]
+    state = torch.tensor(seeds, dtype=torch.int64, device=DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    u = torch.empty(n, device=DEV)
+    ops().sample(lg, temperature, 0, 1.0, None, state, out, u)
+    assert int(out[0]) == 0
+    for i in range(1, n):
+        p = pl.sampling_distribution(lg[i].double().cpu().numpy(), temperature, 0, 1.0)
+        cdf = np.cumsum(p)
+        t = int(out[i])
+        assert p[t] > 0, f"row {i}: token {t} has no weight"
+        assert cdf[t] - p[t] - 1e-4 <= u[i].item() <= cdf[t] + 1e-4, f"row {i}"
+    # one row alone draws what it drew among the others
+    state2 = torch.tensor(seeds[7:8], dtype=torch.int64, device=DEV)
+    out2 = torch.empty(1, dtype=torch.int32, device=DEV)
+    ops().sample(lg[7:8].contiguous(), temperature, 0, 1.0, None, state2, out2)
+    assert int(out2[0]) == int(out[7])
+
+
 def test_sample_uses_slots_for_its_generator():
     lg = torch.randn(2, 500, device=DEV)
     state = torch.tensor([11, 22, 33, 44], dtype=torch.int64, device=DEV) * 0x2545F4914F6CDD1D % (1 << 62)
