@@ -279,6 +279,45 @@ def test_sample_by_temperature_alone_reads_the_row_in_stretches(vocab, temperatu
     assert int(out2[0]) == int(out[7])
 
 
+@pytest.mark.parametrize("vocab", [128256, 40003])
+@pytest.mark.parametrize("temperature,top_k,top_p", [(0.7, 40, 1.0), (1.0, 0, 0.9), (1.3, 25, 0.6), (1.0, 1, 1.0),
+                                                     (0.5, 0, 0.01), (1.0, 3000, 0.999)])
+def test_sample_with_cuts_at_a_large_vocabulary(vocab, temperature, top_k, top_p):
+    """The cuts are found a byte of the key at a time over a cluster that holds the row: rows here have
+    many tokens tied at a cut (logits on a grid of halves: all of them are kept), all their weight on one
+    token, weight only far from the row's start, and ordinary random logits."""
+    import numpy as np
+    import plain_llama as pl
+    n = 24
+    g = torch.Generator(device=DEV).manual_seed(vocab + top_k)
+    lg = 2 * torch.randn(n, vocab, device=DEV, generator=g)
+    lg[0] = (lg[0] * 2).round() / 2                                     # ties everywhere
+    lg[1] = (lg[1] * 2).round() / 2; lg[1, 7] = lg[1, vocab - 9] = 9.0  # two tied at the top
+    lg[2, vocab // 2] = 80.0                                            # one token holds everything
+    lg[3, : vocab - 100] = -float("inf")                                # only the last block of the cluster has weight
+    lg[4, :] = 1.25                                                     # every token tied with every other
+    seeds = [0x9E3779B97F4A7C15 * (i + 5) % (1 << 63) for i in range(n)]
+    state = torch.tensor(seeds, dtype=torch.int64, device=DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    u = torch.empty(n, device=DEV)
+    ops().sample(lg, temperature, top_k, top_p, None, state, out, u)
+    for i in range(n):
+        p = pl.sampling_distribution(lg[i].double().cpu().numpy(), temperature, top_k, top_p)
+        cdf = np.cumsum(p)
+        t = int(out[i])
+        assert p[t] > 0, f"row {i}: token {t} lies outside the kept set"
+        assert cdf[t] - p[t] - 1e-4 <= u[i].item() <= cdf[t] + 1e-4, f"row {i}"
+    # the same draw again, and one row alone
+    state2 = torch.tensor(seeds, dtype=torch.int64, device=DEV)
+    out2 = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops().sample(lg, temperature, top_k, top_p, None, state2, out2)
+    assert torch.equal(out, out2)
+    state3 = torch.tensor(seeds[5:6], dtype=torch.int64, device=DEV)
+    out3 = torch.empty(1, dtype=torch.int32, device=DEV)
+    ops().sample(lg[5:6].contiguous(), temperature, top_k, top_p, None, state3, out3)
+    assert int(out3[0]) == int(out[5])
+
+
 def test_sample_uses_slots_for_its_generator():
     lg = torch.randn(2, 500, device=DEV)
     state = torch.tensor([11, 22, 33, 44], dtype=torch.int64, device=DEV) * 0x2545F4914F6CDD1D % (1 << 62)
