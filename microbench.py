@@ -5,6 +5,7 @@ so that weights come from DRAM), and reports bytes or FLOPs per second.
     python microbench.py linear --rows 8 --n 6144 --k 4096 [--kernel skinny|tc64|tc128|tc256]
     python microbench.py attention_prefill --tokens 2048 --seqs 1 [--kernel tc]
     python microbench.py gemm --rows 2048 --n 28672 --k 4096 --tile 256
+    python microbench.py sampling --rows 64 --vocab 128256 --temperature 0.7 --top-k 40 --top-p 0.9
 
 One JSON line per run.  It is also the small, self-ending workload that profiler captures
 are taken on.
@@ -156,10 +157,28 @@ def attention_prefill(args):
             "TFLOP/s": round(flops / us / 1e6, 1)}
 
 
+def sampling(args):
+    """The pick of a step: argmax at temperature 0, else a draw under the given cuts.  Eight sets of
+    logits in turn (64 rows of 128,256 are 33 MB each)."""
+    rows, V = args.rows, args.vocab
+    g = torch.Generator(device=DEV).manual_seed(3)
+    logits = [3 * torch.randn(rows, V, device=DEV, generator=g) for _ in range(8)]
+    slots = torch.arange(rows, dtype=torch.int32, device=DEV)
+    state = (torch.arange(1, rows + 1, dtype=torch.int64, device=DEV) * 0x9E3779B97F4A7C15) & ((1 << 62) - 1)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    if args.temperature <= 0:
+        us = _time(lambda i: ops.argmax(logits[i % 8], out), args.iters)
+    else:
+        us = _time(lambda i: ops.sample(logits[i % 8], args.temperature, args.top_k, args.top_p, slots, state, out), args.iters)
+    return {"kernel": "argmax" if args.temperature <= 0 else "sample", "rows": rows, "vocab": V,
+            "temperature": args.temperature, "top_k": args.top_k, "top_p": args.top_p, "us": round(us, 2),
+            "GB/s": round(rows * V * 4 / us / 1e3, 1)}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="what", required=True)
-    for name in ("attention_decode", "linear", "gemm", "attention_prefill"):
+    for name in ("attention_decode", "linear", "gemm", "attention_prefill", "sampling"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--heads", type=int, default=32)
@@ -184,6 +203,10 @@ def main(argv=None):
         p.add_argument("--fused", action="store_true", help="attention_decode: rotate and append inside")
         p.add_argument("--seqs", type=int, default=1)
         p.add_argument("--tokens", type=int, default=2048)
+        p.add_argument("--vocab", type=int, default=128256)
+        p.add_argument("--temperature", type=float, default=0.0, help="sampling: 0 is the greedy pick")
+        p.add_argument("--top-k", type=int, default=0)
+        p.add_argument("--top-p", type=float, default=1.0)
     args = ap.parse_args(argv)
     print(json.dumps(globals()[args.what](args)))
 
