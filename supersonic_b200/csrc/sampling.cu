@@ -539,7 +539,7 @@ sample_cluster_kernel(const float* __restrict__ logits, long long ld, int vocab,
     const int lo_i = min((int)rank * per_cta, vocab), hi_i = min(lo_i + per_cta, vocab), n = hi_i - lo_i;
     const int n_it = (n + ST_TILE - 1) / ST_TILE;
     int turn = 0;
-    if (tid == 0) sh.found = 0x7fffffff;
+    if (tid == 0) { sh.found = 0x7fffffff; rx.bin = 0; rx.need_left = 0; }   // a row without any weight finds no bin
 
     const int seq = slots ? slots[row_id] : row_id;
     unsigned long long state = rng_state[seq];

@@ -296,12 +296,16 @@ def test_sample_with_cuts_at_a_large_vocabulary(vocab, temperature, top_k, top_p
     lg[2, vocab // 2] = 80.0                                            # one token holds everything
     lg[3, : vocab - 100] = -float("inf")                                # only the last block of the cluster has weight
     lg[4, :] = 1.25                                                     # every token tied with every other
+    lg[6, :] = -float("inf")                                            # nothing to draw from: token 0
     seeds = [0x9E3779B97F4A7C15 * (i + 5) % (1 << 63) for i in range(n)]
     state = torch.tensor(seeds, dtype=torch.int64, device=DEV)
     out = torch.empty(n, dtype=torch.int32, device=DEV)
     u = torch.empty(n, device=DEV)
     ops().sample(lg, temperature, top_k, top_p, None, state, out, u)
+    assert int(out[6]) == 0
     for i in range(n):
+        if i == 6:
+            continue
         p = pl.sampling_distribution(lg[i].double().cpu().numpy(), temperature, top_k, top_p)
         cdf = np.cumsum(p)
         t = int(out[i])
