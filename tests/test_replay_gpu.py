@@ -14,7 +14,8 @@ pytestmark = pytest.mark.gpu
 LENGTHS = {"r0": 1, "r1": 7, "r2": 19, "r3": 40, "r4": 70, "r5": 33, "r6": 131, "r7": 64, "r8": 65}
 GROUPS = [["r0", "r1", "r2", "r3"], ["r4", "r5", "r8"], ["r6", "r7"]]
 F32_ATOL = 2e-5            # float32 accumulation on logits of order one
-BF16_REL = 2e-2            # a few bfloat16 roundings (2^-8 each) of logits' own scale
+BF16_REL = 2e-2            # a few bfloat16 roundings (2^-8 each) of logits' own scale; the worst seen over the five
+                           # configurations and three ways of cutting is 0.0094, most lie at 0.007 - 0.008
 
 
 def make_requests(vocab, seed):
