@@ -322,6 +322,26 @@ def test_sample_with_cuts_at_a_large_vocabulary(vocab, temperature, top_k, top_p
     assert int(out3[0]) == int(out[5])
 
 
+@pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 1.0), (0.8, 20, 0.9)])
+def test_sample_at_a_vocabulary_beyond_the_cluster_kernels(temperature, top_k, top_p):
+    """More than 524,288 logits a row: one block per row walks the row itself."""
+    import numpy as np
+    import plain_llama as pl
+    n, vocab = 3, 530001
+    lg = 2 * torch.randn(n, vocab, device=DEV, generator=torch.Generator(device=DEV).manual_seed(4))
+    seeds = [0x9E3779B97F4A7C15 * (i + 9) % (1 << 63) for i in range(n)]
+    state = torch.tensor(seeds, dtype=torch.int64, device=DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    u = torch.empty(n, device=DEV)
+    ops().sample(lg, temperature, top_k, top_p, None, state, out, u)
+    for i in range(n):
+        p = pl.sampling_distribution(lg[i].double().cpu().numpy(), temperature, top_k, top_p)
+        cdf = np.cumsum(p)
+        t = int(out[i])
+        assert p[t] > 0
+        assert cdf[t] - p[t] - 1e-4 <= u[i].item() <= cdf[t] + 1e-4
+
+
 def test_sample_uses_slots_for_its_generator():
     lg = torch.randn(2, 500, device=DEV)
     state = torch.tensor([11, 22, 33, 44], dtype=torch.int64, device=DEV) * 0x2545F4914F6CDD1D % (1 << 62)
